@@ -1,0 +1,93 @@
+"""Builds the sm_100a kernel library in-tree with nvcc.
+
+Every ``csrc/*.cu`` file is compiled with ``-gencode arch=compute_100a,code=sm_100a`` and linked
+into ``ultraattn_b200/lib/libultraattn_sm100.so``. The library exposes a plain C ABI (loaded with
+ctypes by :mod:`ultraattn_b200._lib`), so no PyTorch headers are involved and a full rebuild
+takes well under a minute. nvcc cross-compiles, so this works on a machine without a GPU.
+
+The reference ships no native code of its own (it builds NCCL and a flash-attention fork through
+``scripts/Makefile:47-96``); this is the equivalent build step of this framework.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+CSRC = PKG_DIR / "csrc"
+LIB_DIR = PKG_DIR / "lib"
+LIB_PATH = LIB_DIR / "libultraattn_sm100.so"
+OBJ_DIR = LIB_DIR / "obj"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC",
+    "--expt-relaxed-constexpr",
+]
+
+
+def _nvcc() -> str:
+    cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(cand).exists():
+        raise RuntimeError("nvcc not found; set NVCC or add /usr/local/cuda/bin to PATH")
+    return cand
+
+
+def sources() -> list[Path]:
+    return sorted(CSRC.glob("*.cu"))
+
+
+def _newest_header_mtime() -> float:
+    return max((p.stat().st_mtime for p in CSRC.glob("*.cuh")), default=0.0)
+
+
+def needs_build() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    t = LIB_PATH.stat().st_mtime
+    hdr = _newest_header_mtime()
+    return any(s.stat().st_mtime > t for s in sources()) or hdr > t
+
+
+def build_all(force: bool = False, verbose: bool = False) -> Path:
+    """Compile (if stale) and return the path of the shared library."""
+    if not force and not needs_build():
+        return LIB_PATH
+    nvcc = _nvcc()
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    hdr = _newest_header_mtime()
+
+    def compile_one(src: Path) -> Path:
+        obj = OBJ_DIR / (src.stem + ".o")
+        if (not force and obj.exists() and obj.stat().st_mtime > src.stat().st_mtime
+                and obj.stat().st_mtime > hdr):
+            return obj
+        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        if verbose:
+            cmd.insert(1, "-Xptxas")
+            cmd.insert(2, "-v")
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if verbose and r.stderr:
+            sys.stderr.write(r.stderr)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
+        objs = list(ex.map(compile_one, sources()))
+    cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs),
+           "-gencode", "arch=compute_100a,code=sm_100a"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    path = build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print(path)

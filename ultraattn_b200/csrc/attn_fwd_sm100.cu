@@ -1,0 +1,480 @@
+// Block-sparse flash-attention forward for sm_100a: TMA-fed tcgen05.mma with S/P and O
+// accumulators in tensor memory.
+//
+// Replaces, for this framework, the forward of the flash-attention fork that the reference calls
+// at orchestrated_attn/orchestrated_attn_impl.py:326-337 (one call per scheduled tile) and the
+// running-state Triton kernel at easy_context/dist_flash_attn/lightseq_async_attn.py:110-215.
+// Differences by design: one launch walks a whole list of key/value segments per query block
+// (carrying the running max / sum / O in registers and TMEM, so no merge kernel between tiles),
+// segments may live in different buffers (own K/V, a staging ring, a peer GPU's memory reached
+// through a unicast TMA tensor map), and the epilogue can either overwrite (O, lse) or merge into
+// an existing partial (O, lse) — possibly a mailbox in a peer GPU's memory.
+//
+// CTA = 256 query rows x 1 head: two 128-row sub-tiles processed ping-pong so that the tensor
+// core works on one sub-tile while the softmax warps work on the other.
+//   warps 0-3 : softmax / correction / epilogue for sub-tile 0 (one thread per query row)
+//   warps 4-7 : same for sub-tile 1
+//   warp  8   : TMA producer (Q once, then the K and V rings)
+//   warp  9   : tcgen05.mma issuer (one elected thread), TMEM allocation
+// TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P (bf16) overwrites the first
+// 64 columns of its S region and is consumed from TMEM as the A operand of the PV product.
+#include "attn_common.cuh"
+#include "host_common.cuh"
+#include "ptx.cuh"
+
+namespace ua {
+
+constexpr int FWD_THREADS = 320;
+constexpr int FWD_KV_STAGES = 2;
+constexpr int FWD_TILE_BYTES = ATTN_TILE * ATTN_D * 2;  // 32 KB: [2 d-halves][128 rows][128 B]
+
+struct FwdRow {
+  int q_src;      // slot in tmQ
+  int q_start;    // first query token inside that source
+  int q_len;      // query tokens in this block row
+  int seg_begin;  // [seg_begin, seg_end) into segs
+  int seg_end;
+  int o_slot;     // slot in the output tables
+  int o_start;    // first output row inside that slot
+  int accumulate; // 1: merge with the (O, lse) already stored there
+};
+
+struct FwdParams {
+  CUtensorMap tmQ[ATTN_MAX_SRC];
+  CUtensorMap tmK[ATTN_MAX_SRC];
+  CUtensorMap tmV[ATTN_MAX_SRC];
+  __nv_bfloat16* o_ptr[ATTN_MAX_SRC];
+  float* lse_ptr[ATTN_MAX_SRC];
+  long o_row_stride[ATTN_MAX_SRC];   // elements between consecutive tokens (Nh * D)
+  long o_batch_stride[ATTN_MAX_SRC];
+  long lse_head_stride[ATTN_MAX_SRC];
+  long lse_batch_stride[ATTN_MAX_SRC];
+  const FwdRow* rows;
+  const AttnSeg* segs;
+  const int2* tiles;   // (row index, 256-row tile index inside the row), heaviest first
+  int n_tiles;
+  int n_heads;
+  int kv_group;        // query heads per key/value head
+  float scale_log2;    // softmax scale * log2(e)
+  int* status;
+};
+
+struct __align__(1024) FwdSmem {
+  uint8_t q[2][FWD_TILE_BYTES];
+  uint8_t k[FWD_KV_STAGES][FWD_TILE_BYTES];
+  uint8_t v[FWD_KV_STAGES][FWD_TILE_BYTES];
+  uint64_t q_full[2];
+  uint64_t k_full[FWD_KV_STAGES];
+  uint64_t k_empty[FWD_KV_STAGES];
+  uint64_t v_full[FWD_KV_STAGES];
+  uint64_t v_empty[FWD_KV_STAGES];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t o_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Number of 128-key tiles of a segment that the 256-row tile starting at block-relative row r0
+// has to visit (tiles entirely above the causal diagonal for both sub-tiles are skipped).
+__device__ __forceinline__ int seg_tiles(const AttnSeg& sg, int r0, int rows_here) {
+  int n = (sg.len + ATTN_TILE - 1) / ATTN_TILE;
+  if (sg.causal) {
+    const int last = r0 + rows_here - 1 + sg.diag;  // largest allowed key index
+    if (last < 0) return 0;
+    const int nc = last / ATTN_TILE + 1;
+    n = nc < n ? nc : n;
+  }
+  return n;
+}
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  FwdSmem& s = *reinterpret_cast<FwdSmem*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int head = blockIdx.x / p.n_tiles;
+  const int2 tl = p.tiles[blockIdx.x % p.n_tiles];
+  const int batch = blockIdx.y;
+  const FwdRow row = p.rows[tl.x];
+  const int r0 = tl.y * 256;                                    // block-relative first row
+  const int rows_here = min(256, row.q_len - r0);               // valid query rows of this CTA
+  const int kv_head = head / p.kv_group;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.q_full[i], 1);
+      mbar_init(&s.s_full[i], 1);
+      mbar_init(&s.p_full[i], 128);
+    }
+    for (int i = 0; i < FWD_KV_STAGES; ++i) {
+      mbar_init(&s.k_full[i], 1);
+      mbar_init(&s.k_empty[i], 1);
+      mbar_init(&s.v_full[i], 1);
+      mbar_init(&s.v_empty[i], 1);
+    }
+    mbar_init(&s.o_full, 1);
+    s.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = s.tmem_base;
+  WaitCtx wc{&s.abort_flag, p.status, 4000000000ull};
+
+  // total number of key tiles this CTA visits (identical in every role)
+  int n_total = 0;
+  for (int e = row.seg_begin; e < row.seg_end; ++e) n_total += seg_tiles(p.segs[e], r0, rows_here);
+
+  if (warp == 8) {
+    // =============================== TMA producer ===========================================
+    if (lane == 0 && n_total > 0) {
+      const CUtensorMap* tq = &p.tmQ[row.q_src];
+      tma_prefetch_desc(tq);
+      for (int w = 0; w < 2; ++w) {
+        mbar_arrive_expect_tx(&s.q_full[w], FWD_TILE_BYTES);
+        const int qrow = row.q_start + r0 + w * ATTN_TILE;
+        tma_load_4d(s.q[w], tq, &s.q_full[w], 0, head, qrow, batch);
+        tma_load_4d(s.q[w] + 16384, tq, &s.q_full[w], 64, head, qrow, batch);
+      }
+      uint32_t j = 0;
+      bool ok = true;
+      for (int e = row.seg_begin; e < row.seg_end && ok; ++e) {
+        const AttnSeg sg = p.segs[e];
+        const int nt = seg_tiles(sg, r0, rows_here);
+        const CUtensorMap* tk = &p.tmK[sg.src];
+        const CUtensorMap* tv = &p.tmV[sg.src];
+        for (int t = 0; t < nt; ++t, ++j) {
+          const int st = j % FWD_KV_STAGES;
+          const uint32_t ph = (j / FWD_KV_STAGES) & 1;
+          const int krow = sg.start + t * ATTN_TILE;
+          if (!mbar_wait(&s.k_empty[st], ph ^ 1, wc, 100)) { ok = false; break; }
+          mbar_arrive_expect_tx(&s.k_full[st], FWD_TILE_BYTES);
+          tma_load_4d(s.k[st], tk, &s.k_full[st], 0, kv_head, krow, batch);
+          tma_load_4d(s.k[st] + 16384, tk, &s.k_full[st], 64, kv_head, krow, batch);
+          if (!mbar_wait(&s.v_empty[st], ph ^ 1, wc, 101)) { ok = false; break; }
+          mbar_arrive_expect_tx(&s.v_full[st], FWD_TILE_BYTES);
+          tma_load_4d(s.v[st], tv, &s.v_full[st], 0, kv_head, krow, batch);
+          tma_load_4d(s.v[st] + 16384, tv, &s.v_full[st], 64, kv_head, krow, batch);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // =============================== MMA issuer =============================================
+    if (lane == 0 && n_total > 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // S = Q K^T, both K-major
+      const uint32_t idesc_o = make_idesc_bf16(128, 128, 0, 1);   // O += P V, V is N-major
+      const uint32_t tS[2] = {tmem_base + 0, tmem_base + 128};
+      const uint32_t tO[2] = {tmem_base + 256, tmem_base + 384};
+      auto issue_s = [&](int w, int st) {
+        const uint32_t qa = smem_u32(s.q[w]);
+        const uint32_t ka = smem_u32(s.k[st]);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_ss(tS[w], make_smem_desc_sw128(qa + off, 16, 1024),
+                  make_smem_desc_sw128(ka + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int w, int st, bool acc) {
+        const uint32_t va = smem_u32(s.v[st]);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // A: 16 keys = 8 packed columns of P; B: 16 key rows = 2048 B, d-halves 16384 B apart
+          umma_ts(tO[w], tS[w] + kk * 8, make_smem_desc_sw128(va + kk * 2048, 16384, 1024),
+                  idesc_o, (acc || kk > 0) ? 1u : 0u);
+        }
+      };
+      bool ok = true;
+      do {
+        if (!mbar_wait(&s.q_full[0], 0, wc, 200)) { ok = false; break; }
+        if (!mbar_wait(&s.k_full[0], 0, wc, 201)) { ok = false; break; }
+        tc_fence_after_sync();
+        issue_s(0, 0);
+        tc_commit(&s.s_full[0]);
+        if (!mbar_wait(&s.q_full[1], 0, wc, 202)) { ok = false; break; }
+        tc_fence_after_sync();
+        issue_s(1, 0);
+        tc_commit(&s.s_full[1]);
+        tc_commit(&s.k_empty[0]);
+        for (int j = 0; j < n_total; ++j) {
+          const int st = j % FWD_KV_STAGES;
+          const uint32_t ph = (j / FWD_KV_STAGES) & 1;
+          const int stn = (j + 1) % FWD_KV_STAGES;
+          const uint32_t phn = ((j + 1) / FWD_KV_STAGES) & 1;
+          const bool more = (j + 1 < n_total);
+          if (!mbar_wait(&s.v_full[st], ph, wc, 203)) { ok = false; break; }
+          if (!mbar_wait(&s.p_full[0], j & 1, wc, 204)) { ok = false; break; }
+          tc_fence_after_sync();
+          issue_pv(0, st, j > 0);
+          if (more) {
+            if (!mbar_wait(&s.k_full[stn], phn, wc, 205)) { ok = false; break; }
+            tc_fence_after_sync();
+            issue_s(0, stn);
+            tc_commit(&s.s_full[0]);
+          }
+          if (!mbar_wait(&s.p_full[1], j & 1, wc, 206)) { ok = false; break; }
+          tc_fence_after_sync();
+          issue_pv(1, st, j > 0);
+          tc_commit(&s.v_empty[st]);
+          if (more) {
+            issue_s(1, stn);
+            tc_commit(&s.s_full[1]);
+            tc_commit(&s.k_empty[stn]);
+          }
+        }
+        if (ok) tc_commit(&s.o_full);
+      } while (false);
+      (void)ok;
+    }
+  } else {
+    // =============================== softmax + epilogue =====================================
+    const int w = warp >> 2;                 // sub-tile
+    const int quad = warp & 3;               // TMEM lane quadrant of this warp
+    const int r_tile = quad * 32 + lane;     // row inside the 128-row sub-tile
+    const int r_blk = r0 + w * ATTN_TILE + r_tile;   // row inside the query block
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + w * 128;
+    const uint32_t tO = tmem_base + lane_base + 256 + w * 128;
+    const float NEG_INF = -INFINITY;
+
+    float m_use = NEG_INF;   // running reference max, log2 units (already scaled)
+    float l = 0.f;
+    bool ok = true;
+    uint32_t j = 0;
+    for (int e = row.seg_begin; e < row.seg_end && ok; ++e) {
+      const AttnSeg sg = p.segs[e];
+      const int nt = seg_tiles(sg, r0, rows_here);
+      for (int t = 0; t < nt; ++t, ++j) {
+        if (!mbar_wait(&s.s_full[w], j & 1, wc, 300 + w)) { ok = false; break; }
+        tc_fence_after_sync();
+        float sv[128];
+        {
+          uint32_t(&raw)[128] = reinterpret_cast<uint32_t(&)[128]>(sv);
+          tmem_ld_x32(tS + 0, reinterpret_cast<uint32_t(&)[32]>(raw[0]));
+          tmem_ld_x32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(raw[32]));
+          tmem_ld_x32(tS + 64, reinterpret_cast<uint32_t(&)[32]>(raw[64]));
+          tmem_ld_x32(tS + 96, reinterpret_cast<uint32_t(&)[32]>(raw[96]));
+          tmem_wait_ld();
+        }
+        // masking: key index c (segment-relative) allowed iff c < len and (c <= r + diag)
+        const int c0 = t * ATTN_TILE;
+        int limit = sg.len - c0;                               // columns < limit are in range
+        if (sg.causal) limit = min(limit, r_blk + sg.diag - c0 + 1);
+        if (limit < ATTN_TILE) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i) sv[i] = (i < limit) ? sv[i] : NEG_INF;
+        }
+        float mx = sv[0];
+#pragma unroll
+        for (int i = 1; i < 128; ++i) mx = fmaxf(mx, sv[i]);
+        mx *= p.scale_log2;
+        const float m_new = fmaxf(m_use, mx);
+        // lazy rescale: only when the running max grew by more than 2^8 (warp-uniform branch,
+        // because the TMEM accesses below are warp-collective)
+        const bool need = (m_new - m_use > 8.0f) || (m_use == NEG_INF && m_new > NEG_INF);
+        if (j == 0) {
+          m_use = m_new;
+        } else if (__any_sync(0xFFFFFFFFu, need)) {
+          const float alpha = need ? fast_exp2(m_use - m_new) : 1.0f;
+          if (need) m_use = m_new;
+          l *= alpha;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t ov[32];
+            tmem_ld_x32(tO + c * 32, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st_x32(tO + c * 32, ov);
+          }
+        }
+        const float m_eff = (m_use == NEG_INF) ? 0.f : m_use;
+        float lsum = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = fast_exp2(fmaf(sv[c * 32 + 2 * i], p.scale_log2, -m_eff));
+            const float p1 = fast_exp2(fmaf(sv[c * 32 + 2 * i + 1], p.scale_log2, -m_eff));
+            lsum += p0 + p1;
+            pk[i] = pack_bf16x2(p0, p1);
+          }
+          tmem_st_x16(tS + c * 16, pk);
+        }
+        l += lsum;
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&s.p_full[w]);
+      }
+    }
+
+    // ---------------------------------- epilogue --------------------------------------------
+    const bool valid_row = (w * ATTN_TILE + r_tile) < rows_here;
+    const long orow = static_cast<long>(row.o_start + r_blk);
+    __nv_bfloat16* optr = p.o_ptr[row.o_slot] + batch * p.o_batch_stride[row.o_slot] +
+                          orow * p.o_row_stride[row.o_slot] + static_cast<long>(head) * ATTN_D;
+    float* lptr = p.lse_ptr[row.o_slot] + batch * p.lse_batch_stride[row.o_slot] +
+                  head * p.lse_head_stride[row.o_slot] + orow;
+    if (n_total > 0 && ok) ok = mbar_wait(&s.o_full, 0, wc, 310 + w);
+    tc_fence_after_sync();
+    float lse = NEG_INF;
+    float inv = 0.f;
+    if (n_total > 0 && l > 0.f) {
+      lse = (m_use + log2f(l)) * 0.6931471805599453f;
+      inv = 1.0f / l;
+    }
+    float w_old = 0.f, w_new = 1.f;
+    if (row.accumulate && valid_row) {
+      const float lse_old = *lptr;
+      const float mx = fmaxf(lse_old, lse);
+      if (mx == NEG_INF) {
+        w_old = 0.f; w_new = 0.f;
+      } else {
+        const float eo = __expf(lse_old - mx), en = __expf(lse - mx);
+        const float tot = eo + en;
+        w_old = eo / tot; w_new = en / tot;
+        lse = mx + __logf(tot);
+      }
+    }
+    const float fnew = inv * w_new;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t ov[32];
+      if (n_total > 0) {
+        tmem_ld_x32(tO + c * 32, ov);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ov[i] = 0u;
+      }
+      if (valid_row) {
+        uint4* d4 = reinterpret_cast<uint4*>(optr + c * 32);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = (fnew == 0.f) ? 0.f : __uint_as_float(ov[q * 8 + i]) * fnew;
+          if (row.accumulate) {
+            const uint4 old = d4[q];
+            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float lo = __uint_as_float(ow[i] << 16);
+              const float hi = __uint_as_float(ow[i] & 0xFFFF0000u);
+              f[2 * i] += w_old * lo;
+              f[2 * i + 1] += w_old * hi;
+            }
+          }
+          uint4 o;
+          o.x = pack_bf16x2(f[0], f[1]);
+          o.y = pack_bf16x2(f[2], f[3]);
+          o.z = pack_bf16x2(f[4], f[5]);
+          o.w = pack_bf16x2(f[6], f[7]);
+          d4[q] = o;
+        }
+      }
+    }
+    if (valid_row) *lptr = lse;
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace ua
+
+using namespace ua;
+
+// Host-side description of one tensor source: [batch, tokens, heads, 128] bf16 with the given
+// strides (elements).
+struct UaTensorSrc {
+  const void* ptr;
+  long tokens;
+  long heads;
+  long batch;
+  long token_stride;
+  long head_stride;
+  long batch_stride;
+};
+struct UaOutDst {
+  void* o_ptr;
+  float* lse_ptr;
+  long o_row_stride;
+  long o_batch_stride;
+  long lse_head_stride;
+  long lse_batch_stride;
+};
+
+static int encode_src(CUtensorMap* tm, const UaTensorSrc& t) {
+  uint64_t dims[4] = {ATTN_D, static_cast<uint64_t>(t.heads), static_cast<uint64_t>(t.tokens),
+                      static_cast<uint64_t>(t.batch)};
+  uint64_t str[3] = {static_cast<uint64_t>(t.head_stride) * 2,
+                     static_cast<uint64_t>(t.token_stride) * 2,
+                     static_cast<uint64_t>(t.batch_stride > 0 ? t.batch_stride : t.token_stride * t.tokens) * 2};
+  uint32_t box[4] = {64, 1, ATTN_TILE, 1};
+  return make_tmap_2byte(tm, t.ptr, 4, dims, str, box);
+}
+
+static int g_fwd_smem_set[64] = {0};
+
+// rows / segs / tiles are device pointers (prepared once per plan); q/k/v/out tables are host
+// arrays of n_q / n_kv / n_out entries.
+extern "C" int ua_attn_fwd(const UaTensorSrc* q_src, int n_q, const UaTensorSrc* k_src,
+                           const UaTensorSrc* v_src, int n_kv, const UaOutDst* outs, int n_out,
+                           const void* rows_dev, const void* segs_dev, const void* tiles_dev,
+                           int n_tiles, int n_heads, int n_kv_heads, int batch,
+                           float softmax_scale, int* status, cudaStream_t stream) {
+  if (n_q > ATTN_MAX_SRC || n_kv > ATTN_MAX_SRC || n_out > ATTN_MAX_SRC)
+    UA_FAIL("ua_attn_fwd: too many sources (max %d)", ATTN_MAX_SRC);
+  if (n_tiles <= 0) return 0;
+  FwdParams p;
+  memset(&p, 0, sizeof(p));
+  for (int i = 0; i < n_q; ++i)
+    if (encode_src(&p.tmQ[i], q_src[i])) return -1;
+  for (int i = 0; i < n_kv; ++i) {
+    if (encode_src(&p.tmK[i], k_src[i])) return -1;
+    if (encode_src(&p.tmV[i], v_src[i])) return -1;
+  }
+  for (int i = 0; i < n_out; ++i) {
+    p.o_ptr[i] = static_cast<__nv_bfloat16*>(outs[i].o_ptr);
+    p.lse_ptr[i] = outs[i].lse_ptr;
+    p.o_row_stride[i] = outs[i].o_row_stride;
+    p.o_batch_stride[i] = outs[i].o_batch_stride;
+    p.lse_head_stride[i] = outs[i].lse_head_stride;
+    p.lse_batch_stride[i] = outs[i].lse_batch_stride;
+  }
+  p.rows = static_cast<const FwdRow*>(rows_dev);
+  p.segs = static_cast<const AttnSeg*>(segs_dev);
+  p.tiles = static_cast<const int2*>(tiles_dev);
+  p.n_tiles = n_tiles;
+  p.n_heads = n_heads;
+  p.kv_group = n_heads / n_kv_heads;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = status;
+  const int smem_bytes = sizeof(FwdSmem) + 1024;
+  int dev = 0;
+  UA_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !g_fwd_smem_set[dev]) {
+    UA_CUDA(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 smem_bytes));
+    g_fwd_smem_set[dev] = 1;
+  }
+  dim3 grid(n_tiles * n_heads, batch, 1);
+  attn_fwd_kernel<<<grid, FWD_THREADS, smem_bytes, stream>>>(p);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,294 @@
+// bf16 GEMM on tcgen05 tensor cores with TMEM accumulators (sm_100a).
+//
+//   C[M,N] = A[M,K] * B[K,N]      (fp32 accumulate, bf16 out)
+//
+// A may be stored K-contiguous ([M,K] row-major) or M-contiguous ([K,M] row-major); B may be
+// stored K-contiguous ([N,K] row-major, the torch `linear` weight) or N-contiguous ([K,N]
+// row-major). That covers y = x W^T, dx = dy W and dW = dy^T x without any transpose copy.
+//
+// One persistent CTA per SM walks output tiles of 128 x 256. Warp 0 feeds a 4-stage shared
+// memory ring with TMA, warp 1 issues tcgen05.mma, warps 2..5 drain the accumulator from TMEM.
+// The accumulator is double-buffered (2 x 256 TMEM columns) so the epilogue of tile i overlaps
+// the main loop of tile i+1.
+//
+// Two optional fusions serve the head-parallel (Ulysses) attention path, where an all-to-all
+// normally sits next to a projection GEMM (reference: comm_lib/comm_utils.py:32-45 A2AComm and
+// head_parallel_attn/deepspeed_ulysses_attn.py):
+//  * scatter epilogue: output columns are split into `n_dst` equal groups and group g is stored
+//    to base pointer c_dst[g] (a peer GPU's buffer) at row offset `dst_row_off` — the GEMM
+//    writes the all-to-all's result directly;
+//  * gather prologue: the K dimension is split into `n_src` equal groups and group g of A is
+//    loaded by TMA (unicast) from tensor map tmA[g] (a peer GPU's buffer) at row offset
+//    `a_row_off` — the GEMM reads the all-to-all's input directly.
+#include "host_common.cuh"
+#include "ptx.cuh"
+
+namespace ua {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BN = 256;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_STAGES = 4;
+constexpr int GEMM_MAX_PEERS = 8;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmParams {
+  CUtensorMap tmA[GEMM_MAX_PEERS];
+  CUtensorMap tmB;
+  __nv_bfloat16* c_dst[GEMM_MAX_PEERS];
+  int M, N, K;
+  int ldc;            // leading dimension of every destination buffer (elements)
+  int a_mn_major;     // 1: A stored [K,M] (M contiguous)
+  int b_mn_major;     // 1: B stored [K,N] (N contiguous)
+  int n_src;          // gather prologue: number of K groups (1 = plain)
+  int k_per_src;      // K / n_src
+  int a_row_off;      // row offset of A inside every source buffer
+  int n_dst;          // scatter epilogue: number of column groups (1 = plain)
+  int cols_per_dst;   // N / n_dst
+  int dst_row_off;    // row offset inside every destination buffer
+  int* status;
+};
+
+struct __align__(1024) GemmSmem {
+  uint8_t a[GEMM_STAGES][GEMM_BM * GEMM_BK * 2];   // 16 KB per stage
+  uint8_t b[GEMM_STAGES][GEMM_BN * GEMM_BK * 2];   // 32 KB per stage
+  uint64_t full[GEMM_STAGES];
+  uint64_t empty[GEMM_STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  GemmSmem& s = *reinterpret_cast<GemmSmem*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < GEMM_STAGES; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.acc_full[i], 1);
+      mbar_init(&s.acc_empty[i], 128);
+    }
+    s.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = s.tmem_base;
+  WaitCtx wc{&s.abort_flag, p.status, 4000000000ull};
+
+  const int m_tiles = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int n_tiles = (p.N + GEMM_BN - 1) / GEMM_BN;
+  const int total = m_tiles * n_tiles;
+  const int k_blocks = (p.K + GEMM_BK - 1) / GEMM_BK;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------------
+    if (lane == 0) {
+      for (int i = 0; i < p.n_src; ++i) tma_prefetch_desc(&p.tmA[i]);
+      tma_prefetch_desc(&p.tmB);
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * GEMM_BM;
+        const int n0 = (tile / m_tiles) * GEMM_BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int st = it % GEMM_STAGES;
+          const uint32_t ph = (it / GEMM_STAGES) & 1;
+          if (!mbar_wait(&s.empty[st], ph ^ 1, wc, 10)) break;
+          mbar_arrive_expect_tx(&s.full[st], (GEMM_BM + GEMM_BN) * GEMM_BK * 2);
+          const int k0 = kb * GEMM_BK;
+          const int src = k0 / p.k_per_src;
+          const int ksrc = k0 - src * p.k_per_src;
+          if (!p.a_mn_major) {
+            tma_load_2d(s.a[st], &p.tmA[src], &s.full[st], ksrc, p.a_row_off + m0);
+          } else {
+            // [K,M] storage: two 64-wide M panels of 64 k-rows each
+            tma_load_2d(s.a[st], &p.tmA[src], &s.full[st], m0, p.a_row_off + ksrc);
+            tma_load_2d(s.a[st] + 8192, &p.tmA[src], &s.full[st], m0 + 64, p.a_row_off + ksrc);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d(s.b[st], &p.tmB, &s.full[st], k0, n0);
+          } else {
+            for (int pn = 0; pn < GEMM_BN / 64; ++pn)
+              tma_load_2d(s.b[st] + pn * 8192, &p.tmB, &s.full[st], n0 + pn * 64, k0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ---------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(GEMM_BM, GEMM_BN, p.a_mn_major, p.b_mn_major);
+      // K-major tile: rows of 128 B, 8-row groups 1024 B apart; 16 k-elements = 32 B.
+      // MN-major tile: 64-element panels 8192 B apart (LBO), 8 k-rows = 1024 B (SBO);
+      //                16 k-rows = 2048 B.
+      const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u;
+      const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u;
+      const uint32_t a_kstep = p.a_mn_major ? 2048u : 32u;
+      const uint32_t b_kstep = p.b_mn_major ? 2048u : 32u;
+      uint32_t it = 0;
+      uint32_t tcount = 0;
+      for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++tcount) {
+        const int buf = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbar_wait(&s.acc_empty[buf], aph ^ 1, wc, 20)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * GEMM_BN;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int st = it % GEMM_STAGES;
+          const uint32_t ph = (it / GEMM_STAGES) & 1;
+          if (!mbar_wait(&s.full[st], ph, wc, 21)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(s.a[st]);
+          const uint32_t b_addr = smem_u32(s.b[st]);
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            const uint64_t ad = make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
+            const uint64_t bd = make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
+            umma_ss(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&s.empty[st]);
+        }
+        if (!ok) break;
+        tc_commit(&s.acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (4 warps) -------------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+    const int row_in_tile = quad * 32 + lane;
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++tcount) {
+      const int buf = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      const int m0 = (tile % m_tiles) * GEMM_BM;
+      const int n0 = (tile / m_tiles) * GEMM_BN;
+      if (!mbar_wait(&s.acc_full[buf], aph, wc, 30)) break;
+      tc_fence_after_sync();
+      const int row = m0 + row_in_tile;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * GEMM_BN;
+#pragma unroll 1
+      for (int c = 0; c < GEMM_BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(taddr + c * 32, v);
+        tmem_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          const int g = col0 / p.cols_per_dst;
+          const int cin = col0 - g * p.cols_per_dst;
+          __nv_bfloat16* dst = p.c_dst[g] + static_cast<size_t>(p.dst_row_off + row) * p.ldc + cin;
+          if (col0 + 32 <= p.N) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+              d4[q] = o;
+            }
+          } else {
+            for (int q = 0; q < 32 && col0 + q < p.N; ++q)
+              dst[q] = __float2bfloat16(__uint_as_float(v[q]));
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&s.acc_empty[buf]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace ua
+
+using namespace ua;
+
+static int g_gemm_smem_set[64] = {0};
+
+// a_ptrs / c_ptrs: arrays of n_src / n_dst device pointers (host arrays).
+// lda / ldb / ldc in elements. Requirements: K % 8 == 0, lda % 8 == 0, ldb % 8 == 0,
+// cols_per_dst % 32 == 0 when n_dst > 1, k_per_src % 64 == 0 when n_src > 1.
+extern "C" int ua_gemm_bf16(const void* const* a_ptrs, int n_src, long a_rows_total, int lda,
+                            int a_row_off, int a_mn_major, const void* b, int ldb, int b_mn_major,
+                            void* const* c_ptrs, int n_dst, int ldc, int dst_row_off, int M, int N,
+                            int K, int* status, int num_sms, cudaStream_t stream) {
+  if (n_src < 1 || n_src > GEMM_MAX_PEERS || n_dst < 1 || n_dst > GEMM_MAX_PEERS)
+    UA_FAIL("ua_gemm_bf16: n_src/n_dst out of range");
+  if (K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0)
+    UA_FAIL("ua_gemm_bf16: K, lda, ldb, ldc must be multiples of 8");
+  if (K % n_src != 0 || N % n_dst != 0) UA_FAIL("ua_gemm_bf16: K %% n_src or N %% n_dst != 0");
+  if (n_src > 1 && (K / n_src) % GEMM_BK != 0) UA_FAIL("ua_gemm_bf16: K/n_src must be a multiple of 64");
+  if (n_dst > 1 && (N / n_dst) % 32 != 0) UA_FAIL("ua_gemm_bf16: N/n_dst must be a multiple of 32");
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+  p.n_src = n_src; p.k_per_src = K / n_src; p.a_row_off = a_row_off;
+  p.n_dst = n_dst; p.cols_per_dst = N / n_dst; p.dst_row_off = dst_row_off;
+  p.status = status;
+  for (int i = 0; i < n_dst; ++i) p.c_dst[i] = static_cast<__nv_bfloat16*>(c_ptrs[i]);
+  for (int i = 0; i < n_src; ++i) {
+    if (!a_mn_major) {
+      // [rows, k_per_src] K contiguous
+      uint64_t dims[2] = {static_cast<uint64_t>(p.k_per_src), static_cast<uint64_t>(a_rows_total)};
+      uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
+      uint32_t box[2] = {GEMM_BK, GEMM_BM};
+      if (make_tmap_2byte(&p.tmA[i], a_ptrs[i], 2, dims, str, box)) return -1;
+    } else {
+      // [k rows, M] M contiguous; a_rows_total counts k rows
+      uint64_t dims[2] = {static_cast<uint64_t>(M), static_cast<uint64_t>(a_rows_total)};
+      uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
+      uint32_t box[2] = {64, GEMM_BK};
+      if (make_tmap_2byte(&p.tmA[i], a_ptrs[i], 2, dims, str, box)) return -1;
+    }
+  }
+  if (!b_mn_major) {
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
+    uint32_t box[2] = {GEMM_BK, GEMM_BN};
+    if (make_tmap_2byte(&p.tmB, b, 2, dims, str, box)) return -1;
+  } else {
+    uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+    uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
+    uint32_t box[2] = {64, GEMM_BK};
+    if (make_tmap_2byte(&p.tmB, b, 2, dims, str, box)) return -1;
+  }
+  const int smem_bytes = sizeof(GemmSmem) + 1024;
+  int dev = 0;
+  UA_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !g_gemm_smem_set[dev]) {
+    UA_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 smem_bytes));
+    g_gemm_smem_set[dev] = 1;
+  }
+  const int m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
+  const int n_tiles = (N + GEMM_BN - 1) / GEMM_BN;
+  int grid = m_tiles * n_tiles;
+  if (grid > num_sms) grid = num_sms;
+  if (grid < 1) return 0;
+  gemm_bf16_kernel<<<grid, GEMM_THREADS, smem_bytes, stream>>>(p);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,254 @@
+"""Launch plans and Python entry points for the block-sparse attention kernels.
+
+A *forward plan* is a list of :class:`Row` objects: a block of query tokens plus the key/value
+segments it attends to. A *backward plan* is the transposed view: a list of :class:`Col` objects,
+a block of key/value tokens plus the query segments that attend to it. Segments name the buffer
+they live in by slot number, so one launch can mix this GPU's own tensors, staging buffers filled
+from peers and peer memory itself.
+
+Every entry point exists twice: the sm_100a kernel (``*_cuda``) and an fp32 PyTorch restatement of
+the same plan semantics (``*_reference``) that runs on CPU and is the oracle of the kernel tests.
+
+Reference behaviour covered: one flash-attention call per scheduled tile with ``causal`` only on
+diagonal tiles (orchestrated_attn/orchestrated_attn_impl.py:320-340, 574-597), the LSE-weighted
+merge of partial outputs (ring_flash_attn/utils.py:38-52) and the precomputed ``softmax_d``
+input of the backward (orchestrated_attn/utils.py:148-188).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from .. import _lib
+
+TILE = 128
+CTA_ROWS = 256
+
+
+@dataclass(frozen=True)
+class Seg:
+    """A run of tokens in source slot ``src`` starting at ``start``.
+
+    ``causal``: key c of the segment is visible to query r of the block iff ``c <= r + diag``
+    (both 0-based inside their block / segment).
+    """
+    src: int
+    start: int
+    length: int
+    causal: bool = False
+    diag: int = 0
+
+
+@dataclass
+class Row:
+    """Forward work item: ``q_len`` queries at ``q_start`` of source ``q_src`` attend ``segs``;
+    the result goes to rows ``o_start...`` of output slot ``o_slot`` (merged into what is there
+    when ``accumulate``)."""
+    q_src: int
+    q_start: int
+    q_len: int
+    segs: Sequence[Seg]
+    o_slot: int = 0
+    o_start: int = 0
+    accumulate: bool = False
+
+
+@dataclass
+class Col:
+    """Backward work item: ``kv_len`` keys at ``kv_start`` of source ``kv_src`` are attended by the
+    query segments ``segs`` (``Seg.src`` indexes the query-side sources; causal condition as in
+    :class:`Seg` with r the query index inside the segment and c the key index inside this
+    block: visible iff ``c <= r + diag``). dK/dV are accumulated (fp32) at rows ``g_start...`` of
+    gradient slot ``g_slot``."""
+    kv_src: int
+    kv_start: int
+    kv_len: int
+    segs: Sequence[Seg]
+    g_slot: int = 0
+    g_start: int = 0
+
+
+def _seg_tiles(seg: Seg, r0: int, rows_here: int) -> int:
+    n = (seg.length + TILE - 1) // TILE
+    if seg.causal:
+        last = r0 + rows_here - 1 + seg.diag
+        if last < 0:
+            return 0
+        n = min(n, last // TILE + 1)
+    return n
+
+
+class FwdPlan:
+    """Device-resident tables for one forward launch (rows, segments, heaviest-first tile list)."""
+
+    def __init__(self, rows: Sequence[Row], device: torch.device | str = "cpu"):
+        self.rows = list(rows)
+        row_arr = np.zeros((max(len(self.rows), 1), 8), dtype=np.int32)
+        segs = []
+        tiles = []
+        for ri, r in enumerate(self.rows):
+            b = len(segs)
+            for s in r.segs:
+                segs.append((s.src, s.start, s.length, int(s.causal), s.diag, 0, 0, 0))
+            row_arr[ri] = (r.q_src, r.q_start, r.q_len, b, len(segs), r.o_slot, r.o_start,
+                           int(r.accumulate))
+            for t in range((r.q_len + CTA_ROWS - 1) // CTA_ROWS):
+                r0 = t * CTA_ROWS
+                rows_here = min(CTA_ROWS, r.q_len - r0)
+                cost = sum(_seg_tiles(s, r0, rows_here) for s in r.segs)
+                tiles.append((cost, ri, t))
+        tiles.sort(key=lambda x: -x[0])
+        self.n_tiles = len(tiles)
+        self.total_key_tiles = sum(c for c, _, _ in tiles)
+        seg_arr = np.array(segs, dtype=np.int32).reshape(-1, 8) if segs else np.zeros((1, 8), np.int32)
+        tile_arr = (np.array([(ri, t) for _, ri, t in tiles], dtype=np.int32).reshape(-1, 2)
+                    if tiles else np.zeros((1, 2), np.int32))
+        self.device = torch.device(device)
+        self.rows_t = torch.from_numpy(row_arr).to(self.device)
+        self.segs_t = torch.from_numpy(seg_arr).to(self.device)
+        self.tiles_t = torch.from_numpy(tile_arr).to(self.device)
+
+
+_status: dict[int, torch.Tensor] = {}
+
+
+def status_buffer(device: torch.device) -> torch.Tensor:
+    """int32[4] per device: [code, where, block, extra]; written by a kernel whose wait ran out."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _status[idx]
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronises and raises if any kernel on ``device`` reported a bounded wait that ran out."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    st = status_buffer(device).cpu().tolist()
+    if st[0] != 0:
+        status_buffer(device).zero_()
+        raise RuntimeError(f"ultraattn kernel error code={st[0]} where={st[1]} block={st[2]} extra={st[3]}")
+
+
+def _src_struct(t: torch.Tensor) -> _lib.UaTensorSrc:
+    assert t.dim() == 4 and t.dtype == torch.bfloat16 and t.stride(3) == 1 and t.shape[3] == 128, \
+        "attention sources must be bf16 [batch, tokens, heads, 128] with contiguous head dim"
+    return _lib.UaTensorSrc(t.data_ptr(), t.shape[1], t.shape[2], t.shape[0], t.stride(1),
+                            t.stride(2), t.stride(0))
+
+
+def attn_fwd_cuda(q_srcs: Sequence[torch.Tensor], k_srcs: Sequence[torch.Tensor],
+                  v_srcs: Sequence[torch.Tensor], outs: Sequence[tuple[torch.Tensor, torch.Tensor]],
+                  plan: FwdPlan, softmax_scale: float | None = None) -> None:
+    """Run the sm_100a forward. Tensors are ``[batch, tokens, heads, 128]`` bf16; each output is a
+    pair ``(O [batch, tokens, heads, 128] bf16, lse [batch, heads, tokens] fp32)`` written in
+    place."""
+    lib = _lib.load()
+    q0 = q_srcs[0]
+    n_heads = q0.shape[2]
+    n_kv_heads = k_srcs[0].shape[2]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q0.shape[3])
+    qs = (_lib.UaTensorSrc * len(q_srcs))(*[_src_struct(t) for t in q_srcs])
+    ks = (_lib.UaTensorSrc * len(k_srcs))(*[_src_struct(t) for t in k_srcs])
+    vs = (_lib.UaTensorSrc * len(v_srcs))(*[_src_struct(t) for t in v_srcs])
+    od = []
+    for o, lse in outs:
+        assert o.dtype == torch.bfloat16 and lse.dtype == torch.float32 and o.stride(3) == 1
+        assert o.stride(2) == 128 and lse.stride(2) == 1
+        od.append(_lib.UaOutDst(o.data_ptr(), lse.data_ptr(), o.stride(1), o.stride(0),
+                                lse.stride(1), lse.stride(0)))
+    ods = (_lib.UaOutDst * len(od))(*od)
+    st = status_buffer(q0.device)
+    rc = lib.ua_attn_fwd(qs, len(q_srcs), ks, vs, len(k_srcs), ods, len(od),
+                         plan.rows_t.data_ptr(), plan.segs_t.data_ptr(), plan.tiles_t.data_ptr(),
+                         plan.n_tiles, n_heads, n_kv_heads, q0.shape[0], scale, st.data_ptr(),
+                         torch.cuda.current_stream(q0.device).cuda_stream)
+    _lib.check(rc, "ua_attn_fwd")
+
+
+def _mask_for(seg: Seg, q_len: int, device) -> torch.Tensor | None:
+    if not seg.causal:
+        return None
+    r = torch.arange(q_len, device=device)[:, None]
+    c = torch.arange(seg.length, device=device)[None, :]
+    return c <= r + seg.diag
+
+
+def attn_fwd_reference(q_srcs, k_srcs, v_srcs, outs, rows: Sequence[Row],
+                       softmax_scale: float | None = None) -> None:
+    """fp32 PyTorch restatement of :func:`attn_fwd_cuda` (any device, any head dim)."""
+    d = q_srcs[0].shape[3]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    group = q_srcs[0].shape[2] // k_srcs[0].shape[2]
+    for r in rows:
+        q = q_srcs[r.q_src][:, r.q_start:r.q_start + r.q_len].float()       # [B, q, H, D]
+        scores = []
+        vals = []
+        for s in r.segs:
+            k = k_srcs[s.src][:, s.start:s.start + s.length].float()
+            v = v_srcs[s.src][:, s.start:s.start + s.length].float()
+            if group > 1:
+                k = k.repeat_interleave(group, dim=2)
+                v = v.repeat_interleave(group, dim=2)
+            sc = torch.einsum("bqhd,bkhd->bhqk", q, k) * scale
+            m = _mask_for(s, r.q_len, q.device)
+            if m is not None:
+                sc = sc.masked_fill(~m[None, None], float("-inf"))
+            scores.append(sc)
+            vals.append(v)
+        o_t, lse_t = outs[r.o_slot]
+        osl = slice(r.o_start, r.o_start + r.q_len)
+        if scores:
+            sc = torch.cat(scores, dim=-1)
+            v = torch.cat(vals, dim=1)
+            lse = torch.logsumexp(sc, dim=-1)                                # [B, H, q]
+            p = torch.exp(sc - lse.masked_fill(lse == float("-inf"), 0.0)[..., None])
+            p = torch.where(torch.isfinite(sc), p, torch.zeros_like(p))
+            o = torch.einsum("bhqk,bkhd->bqhd", p, v)
+        else:
+            o = torch.zeros_like(q)
+            lse = torch.full((q.shape[0], q.shape[2], r.q_len), float("-inf"), device=q.device)
+        if r.accumulate:
+            lse_old = lse_t[:, :, osl].float()
+            o_old = o_t[:, osl].float()
+            tot = torch.logaddexp(lse_old, lse)
+            safe = tot.masked_fill(tot == float("-inf"), 0.0)
+            w_old = torch.where(torch.isfinite(lse_old), torch.exp(lse_old - safe), torch.zeros_like(tot))
+            w_new = torch.where(torch.isfinite(lse), torch.exp(lse - safe), torch.zeros_like(tot))
+            o = o_old * w_old.transpose(1, 2)[..., None] + o * w_new.transpose(1, 2)[..., None]
+            lse = tot
+        o_t[:, osl] = o.to(o_t.dtype)
+        lse_t[:, :, osl] = lse.to(lse_t.dtype)
+
+
+def attn_fwd(q_srcs, k_srcs, v_srcs, outs, plan: FwdPlan, softmax_scale=None) -> None:
+    """Dispatch on the device of the inputs: CUDA tensors run the sm_100a kernel, CPU tensors the
+    fp32 restatement."""
+    if q_srcs[0].is_cuda:
+        attn_fwd_cuda(q_srcs, k_srcs, v_srcs, outs, plan, softmax_scale)
+    else:
+        attn_fwd_reference(q_srcs, k_srcs, v_srcs, outs, plan.rows, softmax_scale)
+
+
+def rows_from_block_table(table: np.ndarray, block: int, kv_block: int | None = None) -> list[Row]:
+    """Single-buffer forward rows for a square block table (0 empty, 1 full, 2 causal)."""
+    kv_block = kv_block or block
+    rows = []
+    for i in range(table.shape[0]):
+        segs = []
+        for j in range(table.shape[1]):
+            t = int(table[i, j])
+            if t == 0:
+                continue
+            # merge with the previous segment when both are full and contiguous
+            if t == 1 and segs and not segs[-1].causal and segs[-1].start + segs[-1].length == j * kv_block:
+                p = segs[-1]
+                segs[-1] = Seg(0, p.start, p.length + kv_block, False, 0)
+            else:
+                segs.append(Seg(0, j * kv_block, kv_block, t == 2, 0))
+        rows.append(Row(0, i * block, block, tuple(segs), 0, i * block, False))
+    return rows
