@@ -26,6 +26,17 @@ class UaOutDst(Structure):
                 ("lse_batch_stride", c_long)]
 
 
+class UaBwdQSide(Structure):
+    _fields_ = [("lse", c_void_p), ("dvec", c_void_p), ("lse_head_stride", c_long),
+                ("lse_batch_stride", c_long), ("dq", c_void_p), ("dq_row_stride", c_long),
+                ("dq_batch_stride", c_long)]
+
+
+class UaBwdKvOut(Structure):
+    _fields_ = [("dk", c_void_p), ("dv", c_void_p), ("row_stride", c_long),
+                ("batch_stride", c_long), ("add_f32", c_int), ("pad", c_int)]
+
+
 def _declare(lib):
     vp, i, l, f = c_void_p, c_int, c_long, c_float
     lib.ua_last_error.restype = c_char_p
@@ -35,6 +46,9 @@ def _declare(lib):
                          vp],
         "ua_attn_fwd": [POINTER(UaTensorSrc), i, POINTER(UaTensorSrc), POINTER(UaTensorSrc), i,
                         POINTER(UaOutDst), i, vp, vp, vp, i, i, i, i, f, vp, vp],
+        "ua_attn_bwd": [POINTER(UaTensorSrc), POINTER(UaTensorSrc), POINTER(UaBwdQSide), i,
+                        POINTER(UaTensorSrc), POINTER(UaTensorSrc), i, POINTER(UaBwdKvOut), i,
+                        vp, vp, vp, i, i, i, i, f, vp, vp],
         "ua_lse_merge": [POINTER(vp), POINTER(vp), POINTER(l), POINTER(l), i, vp, vp, l, l, i, i,
                          vp],
         "ua_rowdot": [vp, vp, vp, l, l, l, i, i, vp],

@@ -1,0 +1,564 @@
+// Block-sparse flash-attention backward for sm_100a (tcgen05 + TMEM + TMA), five GEMMs per tile.
+//
+// Replaces the backward of the flash-attention fork that the reference calls with a precomputed
+// softmax_d (orchestrated_attn/orchestrated_attn_impl.py:574-597): inputs are Q, K, V, dO, the
+// forward's lse and D = rowsum(dO * O); O itself is never read.
+//
+// CTA = one 128-key tile of one key/value head. It keeps dK and dV for that tile in tensor memory
+// while it walks every 64-query sub-tile that attends to the tile (all query heads of the GQA
+// group, all query segments of the block column):
+//     S^T  = K Q^T                 (128 keys x 64 queries, TMEM)
+//     dP^T = V dO^T                (TMEM)
+//     P^T  = exp2(S^T * scale - lse)            -> bf16 into TMEM (A operand of the next GEMM)
+//     dS^T = P^T * (dP^T - D)                    -> bf16 into shared memory
+//     dV  += P^T dO                (A from TMEM, B = dO as an N-major operand)
+//     dK  += dS^T Q                (A from shared memory, B = Q as an N-major operand)
+//     dQ^T = K^T dS^T              (TMEM, drained by a second warpgroup with fp32 red.add)
+// Everything is computed transposed so that P^T and dS^T come out with keys on the TMEM lanes,
+// which is the layout the dV / dK products need for their A operand.
+//
+//   warps 0-3 : softmax warpgroup (one thread per key) and the dK/dV epilogue
+//   warps 4-7 : dQ drain warpgroup (one thread per head-dim element): fp32 red.add to the dQ
+//               accumulator — this GPU's or, through a peer pointer, the owning GPU's
+//   warp  8   : TMA producer (K, V once; Q/dO sub-tile ring)
+//   warp  9   : tcgen05.mma issuer, TMEM allocation
+// TMEM (512 columns): dK 128 | dV 128 | S^T/P^T x2 (64 each) | dP^T/dQ^T x2 (64 each).
+// dK/dV leave the CTA either as bf16 stores (the CTA is their only producer) or as fp32
+// red.add into an accumulator that may live in a peer GPU's memory (partial gradients of a
+// key/value block computed away from its owner).
+#include "attn_common.cuh"
+#include "host_common.cuh"
+#include "ptx.cuh"
+
+namespace ua {
+
+constexpr int BWD_THREADS = 320;
+constexpr int BWD_QT = 64;                 // queries per sub-tile
+constexpr int BWD_STAGES = 3;              // Q/dO ring depth
+constexpr int BWD_KV_BYTES = ATTN_TILE * ATTN_D * 2;   // 32 KB
+constexpr int BWD_QT_BYTES = BWD_QT * ATTN_D * 2;      // 16 KB: [2 d-halves][64 rows][128 B]
+
+struct BwdCol {
+  int kv_src;     // slot in tmK / tmV
+  int kv_start;   // first key token inside that source
+  int kv_len;     // keys in this block column
+  int seg_begin;  // [seg_begin, seg_end) into segs (query segments)
+  int seg_end;
+  int g_slot;     // slot in the dK/dV output tables
+  int g_start;    // first output row inside that slot
+  int pad;
+};
+
+struct BwdParams {
+  CUtensorMap tmK[ATTN_MAX_SRC];
+  CUtensorMap tmV[ATTN_MAX_SRC];
+  CUtensorMap tmQ[ATTN_MAX_SRC];    // box of 64 rows
+  CUtensorMap tmdO[ATTN_MAX_SRC];   // box of 64 rows
+  const float* lse_ptr[ATTN_MAX_SRC];
+  const float* dvec_ptr[ATTN_MAX_SRC];
+  long lse_head_stride[ATTN_MAX_SRC];
+  long lse_batch_stride[ATTN_MAX_SRC];
+  int q_tokens[ATTN_MAX_SRC];       // tokens in each query-side source (bounds for lse / D)
+  float* dq_ptr[ATTN_MAX_SRC];      // fp32 [tokens, q heads, 128] accumulators
+  long dq_row_stride[ATTN_MAX_SRC];
+  long dq_batch_stride[ATTN_MAX_SRC];
+  void* dk_ptr[ATTN_MAX_SRC];       // bf16 (store mode) or fp32 (add mode) [tokens, kv heads, 128]
+  void* dv_ptr[ATTN_MAX_SRC];
+  long dkv_row_stride[ATTN_MAX_SRC];
+  long dkv_batch_stride[ATTN_MAX_SRC];
+  int dkv_add_f32[ATTN_MAX_SRC];    // 1: fp32 red.add, 0: bf16 store
+  const BwdCol* cols;
+  const AttnSeg* segs;
+  const int2* tiles;                // (column index, 128-key tile inside the column)
+  int n_tiles;
+  int n_kv_heads;
+  int kv_group;
+  float scale;                      // softmax scale
+  float scale_log2;
+  int* status;
+};
+
+struct __align__(1024) BwdSmem {
+  uint8_t k[BWD_KV_BYTES];
+  uint8_t v[BWD_KV_BYTES];
+  uint8_t q[BWD_STAGES][BWD_QT_BYTES];
+  uint8_t d_o[BWD_STAGES][BWD_QT_BYTES];
+  uint8_t ds[2][ATTN_TILE * BWD_QT * 2];   // dS^T: [128 keys][64 queries] bf16, 128-byte swizzle
+  float lse[2][4][BWD_QT];    // per softmax warp copies (no cross-warp barrier needed)
+  float dvec[2][4][BWD_QT];
+  uint64_t kv_full;
+  uint64_t qdo_full[BWD_STAGES];
+  uint64_t qdo_empty[BWD_STAGES];
+  uint64_t sdp_full[2];
+  uint64_t pds_full[2];
+  uint64_t dq_full[2];
+  uint64_t dq_free[2];
+  uint64_t dkv_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// First 64-query sub-tile of a segment that can see the key tile starting at column c0.
+__device__ __forceinline__ int seg_first_qt(const AttnSeg& sg, int c0) {
+  if (!sg.causal) return 0;
+  const int r_min = c0 - sg.diag;   // smallest query index that sees key c0
+  return r_min <= 0 ? 0 : r_min / BWD_QT;
+}
+__device__ __forceinline__ int seg_num_qt(const AttnSeg& sg) {
+  return (sg.len + BWD_QT - 1) / BWD_QT;
+}
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  BwdSmem& s = *reinterpret_cast<BwdSmem*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int kv_head = blockIdx.x / p.n_tiles;
+  const int2 tl = p.tiles[blockIdx.x % p.n_tiles];
+  const int batch = blockIdx.y;
+  const BwdCol col = p.cols[tl.x];
+  const int c0 = tl.y * ATTN_TILE;              // column-relative first key of this CTA
+
+  if (threadIdx.x == 0) {
+    mbar_init(&s.kv_full, 1);
+    for (int i = 0; i < BWD_STAGES; ++i) {
+      mbar_init(&s.qdo_full[i], 1);
+      mbar_init(&s.qdo_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.sdp_full[i], 1);
+      mbar_init(&s.pds_full[i], 128);
+      mbar_init(&s.dq_full[i], 1);
+      mbar_init(&s.dq_free[i], 128);
+    }
+    mbar_init(&s.dkv_full, 1);
+    s.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = s.tmem_base;
+  WaitCtx wc{&s.abort_flag, p.status, 4000000000ull};
+
+  // number of (head, segment, sub-tile) steps; identical in every role
+  int steps_per_head = 0;
+  for (int e = col.seg_begin; e < col.seg_end; ++e) {
+    const AttnSeg sg = p.segs[e];
+    const int n = seg_num_qt(sg) - seg_first_qt(sg, c0);
+    steps_per_head += n > 0 ? n : 0;
+  }
+  const int n_steps = steps_per_head * p.kv_group;
+
+  if (warp == 8) {
+    // =============================== TMA producer ===========================================
+    if (lane == 0 && n_steps > 0) {
+      const int krow = col.kv_start + c0;
+      mbar_arrive_expect_tx(&s.kv_full, 2 * BWD_KV_BYTES);
+      tma_load_4d(s.k, &p.tmK[col.kv_src], &s.kv_full, 0, kv_head, krow, batch);
+      tma_load_4d(s.k + 16384, &p.tmK[col.kv_src], &s.kv_full, 64, kv_head, krow, batch);
+      tma_load_4d(s.v, &p.tmV[col.kv_src], &s.kv_full, 0, kv_head, krow, batch);
+      tma_load_4d(s.v + 16384, &p.tmV[col.kv_src], &s.kv_full, 64, kv_head, krow, batch);
+      uint32_t i = 0;
+      bool ok = true;
+      for (int g = 0; g < p.kv_group && ok; ++g) {
+        const int head = kv_head * p.kv_group + g;
+        for (int e = col.seg_begin; e < col.seg_end && ok; ++e) {
+          const AttnSeg sg = p.segs[e];
+          const int nq = seg_num_qt(sg);
+          for (int t = seg_first_qt(sg, c0); t < nq; ++t, ++i) {
+            const int st = i % BWD_STAGES;
+            const uint32_t ph = (i / BWD_STAGES) & 1;
+            if (!mbar_wait(&s.qdo_empty[st], ph ^ 1, wc, 100)) { ok = false; break; }
+            mbar_arrive_expect_tx(&s.qdo_full[st], 2 * BWD_QT_BYTES);
+            const int qrow = sg.start + t * BWD_QT;
+            tma_load_4d(s.q[st], &p.tmQ[sg.src], &s.qdo_full[st], 0, head, qrow, batch);
+            tma_load_4d(s.q[st] + 8192, &p.tmQ[sg.src], &s.qdo_full[st], 64, head, qrow, batch);
+            tma_load_4d(s.d_o[st], &p.tmdO[sg.src], &s.qdo_full[st], 0, head, qrow, batch);
+            tma_load_4d(s.d_o[st] + 8192, &p.tmdO[sg.src], &s.qdo_full[st], 64, head, qrow, batch);
+          }
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // =============================== MMA issuer =============================================
+    if (lane == 0 && n_steps > 0) {
+      const uint32_t idesc_st = make_idesc_bf16(128, BWD_QT, 0, 0);   // S^T, dP^T
+      const uint32_t idesc_acc = make_idesc_bf16(128, 128, 0, 1);     // dV, dK (B N-major)
+      const uint32_t idesc_dq = make_idesc_bf16(128, BWD_QT, 1, 1);   // dQ^T (A, B MN-major)
+      const uint32_t t_dk = tmem_base + 0;
+      const uint32_t t_dv = tmem_base + 128;
+      const uint32_t t_st[2] = {tmem_base + 256, tmem_base + 320};
+      const uint32_t t_dp[2] = {tmem_base + 384, tmem_base + 448};   // also dQ^T
+      const uint32_t ka = smem_u32(s.k);
+      const uint32_t va = smem_u32(s.v);
+      auto issue_sdp = [&](int b, int st) {
+        const uint32_t qa = smem_u32(s.q[st]);
+        const uint32_t da = smem_u32(s.d_o[st]);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offa = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t offb = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_ss(t_st[b], make_smem_desc_sw128(ka + offa, 16, 1024),
+                  make_smem_desc_sw128(qa + offb, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offa = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t offb = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_ss(t_dp[b], make_smem_desc_sw128(va + offa, 16, 1024),
+                  make_smem_desc_sw128(da + offb, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
+        }
+      };
+      bool ok = true;
+      do {
+        if (!mbar_wait(&s.kv_full, 0, wc, 200)) { ok = false; break; }
+        if (!mbar_wait(&s.qdo_full[0], 0, wc, 201)) { ok = false; break; }
+        tc_fence_after_sync();
+        issue_sdp(0, 0);
+        tc_commit(&s.sdp_full[0]);
+        for (int i = 0; i < n_steps; ++i) {
+          const int b = i & 1;
+          const int st = i % BWD_STAGES;
+          if (i + 1 < n_steps) {
+            const int bn = (i + 1) & 1;
+            const int stn = (i + 1) % BWD_STAGES;
+            const uint32_t phn = ((i + 1) / BWD_STAGES) & 1;
+            if (!mbar_wait(&s.qdo_full[stn], phn, wc, 202)) { ok = false; break; }
+            // dP^T(i+1) lands where dQ^T(i-1) was: wait until that has been drained
+            if (i >= 1 && !mbar_wait(&s.dq_free[bn], ((i - 1) >> 1) & 1, wc, 203)) { ok = false; break; }
+            tc_fence_after_sync();
+            issue_sdp(bn, stn);
+            tc_commit(&s.sdp_full[bn]);
+          }
+          if (!mbar_wait(&s.pds_full[b], (i >> 1) & 1, wc, 204)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t qa = smem_u32(s.q[st]);
+          const uint32_t da = smem_u32(s.d_o[st]);
+          const uint32_t dsa = smem_u32(s.ds[b]);
+          // dV += P^T dO : A = P^T in TMEM (16 queries = 8 packed columns per step)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ts(t_dv, t_st[b] + kk * 8, make_smem_desc_sw128(da + kk * 2048, 8192, 1024),
+                    idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
+          // dK += dS^T Q : A = dS^T in shared memory (K-major over queries)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ss(t_dk, make_smem_desc_sw128(dsa + kk * 32, 16, 1024),
+                    make_smem_desc_sw128(qa + kk * 2048, 8192, 1024), idesc_acc,
+                    (i > 0 || kk > 0) ? 1u : 0u);
+          // dQ^T = K^T dS^T : A = K as an M-major operand, B = dS^T as an N-major operand
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(t_dp[b], make_smem_desc_sw128(ka + kk * 2048, 16384, 1024),
+                    make_smem_desc_sw128(dsa + kk * 2048, 16, 1024), idesc_dq, kk > 0 ? 1u : 0u);
+          tc_commit(&s.dq_full[b]);
+          tc_commit(&s.qdo_empty[st]);
+        }
+        if (ok) tc_commit(&s.dkv_full);
+      } while (false);
+    }
+  } else if (warp < 4) {
+    // =============================== softmax warpgroup ======================================
+    const int quad = warp & 3;
+    const int key_t = quad * 32 + lane;              // key inside the tile
+    const int key_c = c0 + key_t;                    // key inside the block column
+    const bool key_ok = key_c < col.kv_len;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const float LOG2E = 1.4426950408889634f;
+    bool ok = true;
+    uint32_t i = 0;
+    for (int g = 0; g < p.kv_group && ok; ++g) {
+      const int head = kv_head * p.kv_group + g;
+      for (int e = col.seg_begin; e < col.seg_end && ok; ++e) {
+        const AttnSeg sg = p.segs[e];
+        const int nq = seg_num_qt(sg);
+        const float* lse_g = p.lse_ptr[sg.src] + batch * p.lse_batch_stride[sg.src] +
+                             head * p.lse_head_stride[sg.src];
+        const float* dv_g = p.dvec_ptr[sg.src] + batch * p.lse_batch_stride[sg.src] +
+                            head * p.lse_head_stride[sg.src];
+        for (int t = seg_first_qt(sg, c0); t < nq; ++t, ++i) {
+          const int b = i & 1;
+          // stage lse / D of the 64 queries, one private copy per warp
+          // (rows outside the segment get lse = +inf -> P = 0)
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int qi = hh * 32 + lane;
+            const int r = t * BWD_QT + qi;
+            float lv = INFINITY, dv = 0.f;
+            if (r < sg.len && sg.start + r < p.q_tokens[sg.src]) {
+              lv = lse_g[sg.start + r];
+              dv = dv_g[sg.start + r];
+              if (lv == -INFINITY) lv = INFINITY;
+            }
+            s.lse[b][quad][qi] = lv * LOG2E;
+            s.dvec[b][quad][qi] = dv;
+          }
+          __syncwarp();
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.sdp_full[b], (i >> 1) & 1, wc, 300))) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t t_st = tmem_base + lane_base + 256 + b * 64;
+          const uint32_t t_dp = tmem_base + lane_base + 384 + b * 64;
+          float pv[64];
+          {
+            uint32_t(&raw)[64] = reinterpret_cast<uint32_t(&)[64]>(pv);
+            tmem_ld_x32(t_st, reinterpret_cast<uint32_t(&)[32]>(raw[0]));
+            tmem_ld_x32(t_st + 32, reinterpret_cast<uint32_t(&)[32]>(raw[32]));
+            tmem_wait_ld();
+          }
+          // visible iff key_c <= r + diag  <=>  r >= key_c - diag
+          const int r_first = sg.causal ? (key_c - sg.diag - t * BWD_QT) : 0;   // sub-tile relative
+#pragma unroll
+          for (int c = 0; c < 64; ++c) {
+            float pr = fast_exp2(fmaf(pv[c], p.scale_log2, -s.lse[b][quad][c]));
+            pr = (key_ok && c >= r_first) ? pr : 0.f;
+            pv[c] = pr;
+          }
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) pk[c] = pack_bf16x2(pv[h * 32 + 2 * c], pv[h * 32 + 2 * c + 1]);
+            tmem_st_x16(t_st + h * 16, pk);
+          }
+          // dS^T = P^T * (dP^T - D)
+          uint8_t* ds_row = s.ds[b];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t dp[32];
+            tmem_ld_x32(t_dp + h * 32, dp);
+            tmem_wait_ld();
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {      // 8 queries = one 16-byte chunk
+              uint32_t w4[4];
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                const int q0 = h * 32 + ch * 8 + 2 * c;
+                const float d0 = pv[q0] * (__uint_as_float(dp[ch * 8 + 2 * c]) - s.dvec[b][quad][q0]);
+                const float d1 = pv[q0 + 1] * (__uint_as_float(dp[ch * 8 + 2 * c + 1]) - s.dvec[b][quad][q0 + 1]);
+                w4[c] = pack_bf16x2(d0, d1);
+              }
+              *reinterpret_cast<uint4*>(ds_row + sw128_offset(key_t, h * 4 + ch)) =
+                  make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+          }
+          tmem_wait_st();
+          fence_proxy_async_smem();
+          tc_fence_before_sync();
+          mbar_arrive(&s.pds_full[b]);
+        }
+      }
+    }
+    // ---------------------------------- dK / dV epilogue ------------------------------------
+    if (n_steps > 0 && ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait(&s.dkv_full, 0, wc, 310));
+    tc_fence_after_sync();
+    const int slot = col.g_slot;
+    const long grow = static_cast<long>(col.g_start + key_c);
+    const long goff = batch * p.dkv_batch_stride[slot] + grow * p.dkv_row_stride[slot] +
+                      static_cast<long>(kv_head) * ATTN_D;
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+      const uint32_t t_acc = tmem_base + lane_base + which * 128;
+      const float mul = which == 0 ? p.scale : 1.0f;
+      void* base = which == 0 ? p.dk_ptr[slot] : p.dv_ptr[slot];
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t av[32];
+        if (n_steps > 0) {
+          tmem_ld_x32(t_acc + c * 32, av);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int q = 0; q < 32; ++q) av[q] = 0u;
+        }
+        if (!key_ok) continue;
+        if (p.dkv_add_f32[slot]) {
+          if (n_steps == 0) continue;
+          float* dst = static_cast<float*>(base) + goff + c * 32;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + q * 4),
+                         "f"(__uint_as_float(av[q * 4 + 0]) * mul),
+                         "f"(__uint_as_float(av[q * 4 + 1]) * mul),
+                         "f"(__uint_as_float(av[q * 4 + 2]) * mul),
+                         "f"(__uint_as_float(av[q * 4 + 3]) * mul)
+                         : "memory");
+          }
+        } else {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(base) + goff + c * 32;
+          uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(av[q * 8 + 0]) * mul, __uint_as_float(av[q * 8 + 1]) * mul);
+            o.y = pack_bf16x2(__uint_as_float(av[q * 8 + 2]) * mul, __uint_as_float(av[q * 8 + 3]) * mul);
+            o.z = pack_bf16x2(__uint_as_float(av[q * 8 + 4]) * mul, __uint_as_float(av[q * 8 + 5]) * mul);
+            o.w = pack_bf16x2(__uint_as_float(av[q * 8 + 6]) * mul, __uint_as_float(av[q * 8 + 7]) * mul);
+            d4[q] = o;
+          }
+        }
+      }
+    }
+  } else {
+    // =============================== dQ drain warpgroup =====================================
+    const int quad = warp & 3;
+    const int d_idx = quad * 32 + lane;              // head-dim element (TMEM lane of dQ^T)
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    bool ok = true;
+    uint32_t i = 0;
+    for (int g = 0; g < p.kv_group && ok; ++g) {
+      const int head = kv_head * p.kv_group + g;
+      for (int e = col.seg_begin; e < col.seg_end && ok; ++e) {
+        const AttnSeg sg = p.segs[e];
+        const int nq = seg_num_qt(sg);
+        float* dq_base = p.dq_ptr[sg.src] + batch * p.dq_batch_stride[sg.src] +
+                         static_cast<long>(head) * ATTN_D + d_idx;
+        const long rs = p.dq_row_stride[sg.src];
+        for (int t = seg_first_qt(sg, c0); t < nq; ++t, ++i) {
+          const int b = i & 1;
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.dq_full[b], (i >> 1) & 1, wc, 400))) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t t_dq = tmem_base + lane_base + 384 + b * 64;
+          const int r_base = t * BWD_QT;
+          const int n_valid = min(BWD_QT, sg.len - r_base);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t dv[32];
+            tmem_ld_x32(t_dq + h * 32, dv);
+            tmem_wait_ld();
+            if (h == 1) {
+              // all TMEM reads of this buffer are done: hand it back before the slow part
+              tc_fence_before_sync();
+              mbar_arrive(&s.dq_free[b]);
+            }
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const int r = h * 32 + c;
+              if (r < n_valid) {
+                float* dst = dq_base + static_cast<long>(sg.start + r_base + r) * rs;
+                asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst),
+                             "f"(__uint_as_float(dv[c]) * p.scale)
+                             : "memory");
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace ua
+
+using namespace ua;
+
+struct UaTensorSrc {
+  const void* ptr;
+  long tokens;
+  long heads;
+  long batch;
+  long token_stride;
+  long head_stride;
+  long batch_stride;
+};
+// query-side extras of one source
+struct UaBwdQSide {
+  const float* lse;        // [batch, heads, tokens]
+  const float* dvec;       // same layout
+  long lse_head_stride;
+  long lse_batch_stride;
+  float* dq;               // fp32 [batch, tokens, heads, 128]
+  long dq_row_stride;
+  long dq_batch_stride;
+};
+struct UaBwdKvOut {
+  void* dk;
+  void* dv;
+  long row_stride;
+  long batch_stride;
+  int add_f32;
+  int pad;
+};
+
+static int encode_src_box(CUtensorMap* tm, const UaTensorSrc& t, uint32_t rows) {
+  uint64_t dims[4] = {ATTN_D, static_cast<uint64_t>(t.heads), static_cast<uint64_t>(t.tokens),
+                      static_cast<uint64_t>(t.batch)};
+  uint64_t str[3] = {static_cast<uint64_t>(t.head_stride) * 2,
+                     static_cast<uint64_t>(t.token_stride) * 2,
+                     static_cast<uint64_t>(t.batch_stride > 0 ? t.batch_stride : t.token_stride * t.tokens) * 2};
+  uint32_t box[4] = {64, 1, rows, 1};
+  return make_tmap_2byte(tm, t.ptr, 4, dims, str, box);
+}
+
+static int g_bwd_smem_set[64] = {0};
+
+extern "C" int ua_attn_bwd(const UaTensorSrc* q_src, const UaTensorSrc* do_src,
+                           const UaBwdQSide* q_side, int n_q, const UaTensorSrc* k_src,
+                           const UaTensorSrc* v_src, int n_kv, const UaBwdKvOut* kv_out, int n_out,
+                           const void* cols_dev, const void* segs_dev, const void* tiles_dev,
+                           int n_tiles, int n_heads, int n_kv_heads, int batch,
+                           float softmax_scale, int* status, cudaStream_t stream) {
+  if (n_q > ATTN_MAX_SRC || n_kv > ATTN_MAX_SRC || n_out > ATTN_MAX_SRC)
+    UA_FAIL("ua_attn_bwd: too many sources (max %d)", ATTN_MAX_SRC);
+  if (n_tiles <= 0) return 0;
+  BwdParams p;
+  memset(&p, 0, sizeof(p));
+  for (int i = 0; i < n_q; ++i) {
+    if (encode_src_box(&p.tmQ[i], q_src[i], BWD_QT)) return -1;
+    if (encode_src_box(&p.tmdO[i], do_src[i], BWD_QT)) return -1;
+    p.lse_ptr[i] = q_side[i].lse;
+    p.dvec_ptr[i] = q_side[i].dvec;
+    p.lse_head_stride[i] = q_side[i].lse_head_stride;
+    p.lse_batch_stride[i] = q_side[i].lse_batch_stride;
+    p.q_tokens[i] = static_cast<int>(q_src[i].tokens);
+    p.dq_ptr[i] = q_side[i].dq;
+    p.dq_row_stride[i] = q_side[i].dq_row_stride;
+    p.dq_batch_stride[i] = q_side[i].dq_batch_stride;
+  }
+  for (int i = 0; i < n_kv; ++i) {
+    if (encode_src_box(&p.tmK[i], k_src[i], ATTN_TILE)) return -1;
+    if (encode_src_box(&p.tmV[i], v_src[i], ATTN_TILE)) return -1;
+  }
+  for (int i = 0; i < n_out; ++i) {
+    p.dk_ptr[i] = kv_out[i].dk;
+    p.dv_ptr[i] = kv_out[i].dv;
+    p.dkv_row_stride[i] = kv_out[i].row_stride;
+    p.dkv_batch_stride[i] = kv_out[i].batch_stride;
+    p.dkv_add_f32[i] = kv_out[i].add_f32;
+  }
+  p.cols = static_cast<const BwdCol*>(cols_dev);
+  p.segs = static_cast<const AttnSeg*>(segs_dev);
+  p.tiles = static_cast<const int2*>(tiles_dev);
+  p.n_tiles = n_tiles;
+  p.n_kv_heads = n_kv_heads;
+  p.kv_group = n_heads / n_kv_heads;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = status;
+  const int smem_bytes = sizeof(BwdSmem) + 1024;
+  int dev = 0;
+  UA_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !g_bwd_smem_set[dev]) {
+    UA_CUDA(cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 smem_bytes));
+    g_bwd_smem_set[dev] = 1;
+  }
+  dim3 grid(n_tiles * n_kv_heads, batch, 1);
+  attn_bwd_kernel<<<grid, BWD_THREADS, smem_bytes, stream>>>(p);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}

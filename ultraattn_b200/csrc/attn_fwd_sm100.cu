@@ -254,7 +254,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       const AttnSeg sg = p.segs[e];
       const int nt = seg_tiles(sg, r0, rows_here);
       for (int t = 0; t < nt; ++t, ++j) {
-        if (!mbar_wait(&s.s_full[w], j & 1, wc, 300 + w)) { ok = false; break; }
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.s_full[w], j & 1, wc, 300 + w))) { ok = false; break; }
         tc_fence_after_sync();
         float sv[128];
         {
@@ -325,7 +325,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
                           orow * p.o_row_stride[row.o_slot] + static_cast<long>(head) * ATTN_D;
     float* lptr = p.lse_ptr[row.o_slot] + batch * p.lse_batch_stride[row.o_slot] +
                   head * p.lse_head_stride[row.o_slot] + orow;
-    if (n_total > 0 && ok) ok = mbar_wait(&s.o_full, 0, wc, 310 + w);
+    if (n_total > 0 && ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait(&s.o_full, 0, wc, 310 + w));
     tc_fence_after_sync();
     float lse = NEG_INF;
     float inv = 0.f;

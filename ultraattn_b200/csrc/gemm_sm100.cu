@@ -177,7 +177,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t aph = (tcount >> 1) & 1;
       const int m0 = (tile % m_tiles) * GEMM_BM;
       const int n0 = (tile / m_tiles) * GEMM_BN;
-      if (!mbar_wait(&s.acc_full[buf], aph, wc, 30)) break;
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.acc_full[buf], aph, wc, 30))) break;
       tc_fence_after_sync();
       const int row = m0 + row_in_tile;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * GEMM_BN;

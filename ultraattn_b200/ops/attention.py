@@ -252,3 +252,176 @@ def rows_from_block_table(table: np.ndarray, block: int, kv_block: int | None = 
                 segs.append(Seg(0, j * kv_block, kv_block, t == 2, 0))
         rows.append(Row(0, i * block, block, tuple(segs), 0, i * block, False))
     return rows
+
+
+# =================================================================================================
+# backward
+# =================================================================================================
+BWD_QT = 64
+
+
+def _col_steps(c: Col, c0: int) -> int:
+    n = 0
+    for s in c.segs:
+        nq = (s.length + BWD_QT - 1) // BWD_QT
+        first = 0
+        if s.causal:
+            r_min = c0 - s.diag
+            first = 0 if r_min <= 0 else r_min // BWD_QT
+        n += max(0, nq - first)
+    return n
+
+
+class BwdPlan:
+    """Device-resident tables for one backward launch (columns, query segments, tile list)."""
+
+    def __init__(self, cols: Sequence[Col], device: torch.device | str = "cpu"):
+        self.cols = list(cols)
+        col_arr = np.zeros((max(len(self.cols), 1), 8), dtype=np.int32)
+        segs = []
+        tiles = []
+        for ci, c in enumerate(self.cols):
+            b = len(segs)
+            for s in c.segs:
+                segs.append((s.src, s.start, s.length, int(s.causal), s.diag, 0, 0, 0))
+            col_arr[ci] = (c.kv_src, c.kv_start, c.kv_len, b, len(segs), c.g_slot, c.g_start, 0)
+            for t in range((c.kv_len + TILE - 1) // TILE):
+                tiles.append((_col_steps(c, t * TILE), ci, t))
+        tiles.sort(key=lambda x: -x[0])
+        self.n_tiles = len(tiles)
+        self.total_steps = sum(c for c, _, _ in tiles)
+        seg_arr = np.array(segs, dtype=np.int32).reshape(-1, 8) if segs else np.zeros((1, 8), np.int32)
+        tile_arr = (np.array([(ci, t) for _, ci, t in tiles], dtype=np.int32).reshape(-1, 2)
+                    if tiles else np.zeros((1, 2), np.int32))
+        self.device = torch.device(device)
+        self.cols_t = torch.from_numpy(col_arr).to(self.device)
+        self.segs_t = torch.from_numpy(seg_arr).to(self.device)
+        self.tiles_t = torch.from_numpy(tile_arr).to(self.device)
+
+
+@dataclass
+class BwdQSide:
+    """Query-side tensors of one source: q, dO ``[B, T, H, 128]`` bf16; lse, dvec ``[B, H, T]``
+    fp32; dq ``[B, T, H, 128]`` fp32 accumulator (added into)."""
+    q: torch.Tensor
+    d_o: torch.Tensor
+    lse: torch.Tensor
+    dvec: torch.Tensor
+    dq: torch.Tensor
+
+
+@dataclass
+class BwdKvOut:
+    """dK / dV destination ``[B, T, Hkv, 128]``: bf16 (overwritten) or fp32 (added into)."""
+    dk: torch.Tensor
+    dv: torch.Tensor
+
+    @property
+    def add_f32(self) -> bool:
+        return self.dk.dtype == torch.float32
+
+
+def attn_bwd_cuda(q_sides: Sequence[BwdQSide], k_srcs, v_srcs, kv_outs: Sequence[BwdKvOut],
+                  plan: BwdPlan, softmax_scale: float | None = None) -> None:
+    lib = _lib.load()
+    q0 = q_sides[0].q
+    n_heads = q0.shape[2]
+    n_kv_heads = k_srcs[0].shape[2]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q0.shape[3])
+    nq = len(q_sides)
+    qs = (_lib.UaTensorSrc * nq)(*[_src_struct(s.q) for s in q_sides])
+    dos = (_lib.UaTensorSrc * nq)(*[_src_struct(s.d_o) for s in q_sides])
+    side = []
+    for s in q_sides:
+        assert s.lse.dtype == torch.float32 and s.dvec.dtype == torch.float32 and s.dq.dtype == torch.float32
+        assert s.lse.stride(2) == 1 and s.lse.stride() == s.dvec.stride()
+        assert s.dq.stride(3) == 1 and s.dq.stride(2) == 128
+        side.append(_lib.UaBwdQSide(s.lse.data_ptr(), s.dvec.data_ptr(), s.lse.stride(1),
+                                    s.lse.stride(0), s.dq.data_ptr(), s.dq.stride(1), s.dq.stride(0)))
+    sides = (_lib.UaBwdQSide * nq)(*side)
+    ks = (_lib.UaTensorSrc * len(k_srcs))(*[_src_struct(t) for t in k_srcs])
+    vs = (_lib.UaTensorSrc * len(v_srcs))(*[_src_struct(t) for t in v_srcs])
+    ko = []
+    for o in kv_outs:
+        assert o.dk.stride(3) == 1 and o.dk.stride(2) == 128 and o.dk.stride() == o.dv.stride()
+        ko.append(_lib.UaBwdKvOut(o.dk.data_ptr(), o.dv.data_ptr(), o.dk.stride(1), o.dk.stride(0),
+                                  int(o.add_f32), 0))
+    kos = (_lib.UaBwdKvOut * len(ko))(*ko)
+    st = status_buffer(q0.device)
+    rc = lib.ua_attn_bwd(qs, dos, sides, nq, ks, vs, len(k_srcs), kos, len(ko),
+                         plan.cols_t.data_ptr(), plan.segs_t.data_ptr(), plan.tiles_t.data_ptr(),
+                         plan.n_tiles, n_heads, n_kv_heads, q0.shape[0], scale, st.data_ptr(),
+                         torch.cuda.current_stream(q0.device).cuda_stream)
+    _lib.check(rc, "ua_attn_bwd")
+
+
+def attn_bwd_reference(q_sides: Sequence[BwdQSide], k_srcs, v_srcs, kv_outs: Sequence[BwdKvOut],
+                       cols: Sequence[Col], softmax_scale: float | None = None) -> None:
+    """fp32 PyTorch restatement of :func:`attn_bwd_cuda` (uses lse and D exactly like the kernel)."""
+    d = q_sides[0].q.shape[3]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    group = q_sides[0].q.shape[2] // k_srcs[0].shape[2]
+    for c in cols:
+        k = k_srcs[c.kv_src][:, c.kv_start:c.kv_start + c.kv_len].float()
+        v = v_srcs[c.kv_src][:, c.kv_start:c.kv_start + c.kv_len].float()
+        kk = k.repeat_interleave(group, dim=2) if group > 1 else k
+        vv = v.repeat_interleave(group, dim=2) if group > 1 else v
+        dk = torch.zeros_like(kk)
+        dv = torch.zeros_like(vv)
+        for s in c.segs:
+            qs = q_sides[s.src]
+            sl = slice(s.start, s.start + s.length)
+            q = qs.q[:, sl].float()
+            do = qs.d_o[:, sl].float()
+            lse = qs.lse[:, :, sl].float()
+            dvec = qs.dvec[:, :, sl].float()
+            sc = torch.einsum("bqhd,bkhd->bhqk", q, kk) * scale
+            lse_safe = torch.where(torch.isfinite(lse), lse, torch.full_like(lse, float("inf")))
+            p = torch.exp(sc - lse_safe[..., None])
+            if s.causal:
+                r = torch.arange(s.length, device=q.device)[:, None]
+                cc = torch.arange(c.kv_len, device=q.device)[None, :]
+                p = p * (cc <= r + s.diag)[None, None].to(p.dtype)
+            dp = torch.einsum("bqhd,bkhd->bhqk", do, vv)
+            ds = p * (dp - dvec[..., None])
+            dv += torch.einsum("bhqk,bqhd->bkhd", p, do)
+            dk += torch.einsum("bhqk,bqhd->bkhd", ds, q) * scale
+            qs.dq[:, sl] += (torch.einsum("bhqk,bkhd->bqhd", ds, kk) * scale).to(qs.dq.dtype)
+        if group > 1:
+            B, T, H, D = dk.shape
+            dk = dk.view(B, T, H // group, group, D).sum(3)
+            dv = dv.view(B, T, H // group, group, D).sum(3)
+        out = kv_outs[c.g_slot]
+        gsl = slice(c.g_start, c.g_start + c.kv_len)
+        if out.add_f32:
+            out.dk[:, gsl] += dk
+            out.dv[:, gsl] += dv
+        else:
+            out.dk[:, gsl] = dk.to(out.dk.dtype)
+            out.dv[:, gsl] = dv.to(out.dv.dtype)
+
+
+def attn_bwd(q_sides, k_srcs, v_srcs, kv_outs, plan: BwdPlan, softmax_scale=None) -> None:
+    if q_sides[0].q.is_cuda:
+        attn_bwd_cuda(q_sides, k_srcs, v_srcs, kv_outs, plan, softmax_scale)
+    else:
+        attn_bwd_reference(q_sides, k_srcs, v_srcs, kv_outs, plan.cols, softmax_scale)
+
+
+def cols_from_block_table(table: np.ndarray, block: int, kv_block: int | None = None) -> list[Col]:
+    """Single-buffer backward columns for a block table (0 empty, 1 full, 2 causal)."""
+    kv_block = kv_block or block
+    cols = []
+    for j in range(table.shape[1]):
+        segs = []
+        for i in range(table.shape[0]):
+            t = int(table[i, j])
+            if t == 0:
+                continue
+            if t == 1 and segs and not segs[-1].causal and segs[-1].start + segs[-1].length == i * block:
+                p = segs[-1]
+                segs[-1] = Seg(0, p.start, p.length + block, False, 0)
+            else:
+                segs.append(Seg(0, i * block, block, t == 2, 0))
+        cols.append(Col(0, j * kv_block, kv_block, tuple(segs), 0, j * kv_block))
+    return cols
