@@ -13,13 +13,16 @@
 //     dS^T = P^T * (dP^T - D)                    -> bf16 into shared memory
 //     dV  += P^T dO                (A from TMEM, B = dO as an N-major operand)
 //     dK  += dS^T Q                (A from shared memory, B = Q as an N-major operand)
-//     dQ^T = K^T dS^T              (TMEM, drained by a second warpgroup with fp32 red.add)
+//     dQ^T = K^T dS^T              (TMEM, drained by a second warpgroup: registers -> shared
+//                                   memory -> TMA reduce-add into the fp32 dQ accumulator)
 // Everything is computed transposed so that P^T and dS^T come out with keys on the TMEM lanes,
 // which is the layout the dV / dK products need for their A operand.
 //
 //   warps 0-3 : softmax warpgroup (one thread per key) and the dK/dV epilogue
-//   warps 4-7 : dQ drain warpgroup (one thread per head-dim element): fp32 red.add to the dQ
-//               accumulator — this GPU's or, through a peer pointer, the owning GPU's
+//   warps 4-7 : dQ drain warpgroup (one thread per head-dim element): each warp transposes its
+//               32 x 64 slice through shared memory and issues cp.reduce.async.bulk.tensor (fp32
+//               add at the memory side) into the dQ accumulator — this GPU's or, through a
+//               tensor map over a peer mapping, the owning GPU's
 //   warp  8   : TMA producer (K, V once; Q/dO sub-tile ring)
 //   warp  9   : tcgen05.mma issuer, TMEM allocation
 // TMEM (512 columns): dK 128 | dV 128 | S^T/P^T x2 (64 each) | dP^T/dQ^T x2 (64 each).
@@ -59,9 +62,7 @@ struct BwdParams {
   long lse_head_stride[ATTN_MAX_SRC];
   long lse_batch_stride[ATTN_MAX_SRC];
   int q_tokens[ATTN_MAX_SRC];       // tokens in each query-side source (bounds for lse / D)
-  float* dq_ptr[ATTN_MAX_SRC];      // fp32 [tokens, q heads, 128] accumulators
-  long dq_row_stride[ATTN_MAX_SRC];
-  long dq_batch_stride[ATTN_MAX_SRC];
+  CUtensorMap tmdQ[ATTN_MAX_SRC];   // fp32 [batch, tokens, q heads, 128] accumulators, box 32x1x32
   void* dk_ptr[ATTN_MAX_SRC];       // bf16 (store mode) or fp32 (add mode) [tokens, kv heads, 128]
   void* dv_ptr[ATTN_MAX_SRC];
   long dkv_row_stride[ATTN_MAX_SRC];
@@ -84,6 +85,7 @@ struct __align__(1024) BwdSmem {
   uint8_t q[BWD_STAGES][BWD_QT_BYTES];
   uint8_t d_o[BWD_STAGES][BWD_QT_BYTES];
   uint8_t ds[2][ATTN_TILE * BWD_QT * 2];   // dS^T: [128 keys][64 queries] bf16, 128-byte swizzle
+  float dq_stage[4][32 * 32];              // per drain warp: [32 queries][32 head-dim] fp32
   float lse[2][4][BWD_QT];    // per softmax warp copies (no cross-warp barrier needed)
   float dvec[2][4][BWD_QT];
   uint64_t kv_full;
@@ -199,9 +201,8 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       const uint32_t t_dp[2] = {tmem_base + 384, tmem_base + 448};   // also dQ^T
       const uint32_t ka = smem_u32(s.k);
       const uint32_t va = smem_u32(s.v);
-      auto issue_sdp = [&](int b, int st) {
+      auto issue_st = [&](int b, int st) {
         const uint32_t qa = smem_u32(s.q[st]);
-        const uint32_t da = smem_u32(s.d_o[st]);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t offa = (kk >> 2) * 16384 + (kk & 3) * 32;
@@ -209,6 +210,9 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
           umma_ss(t_st[b], make_smem_desc_sw128(ka + offa, 16, 1024),
                   make_smem_desc_sw128(qa + offb, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
         }
+      };
+      auto issue_dp = [&](int b, int st) {
+        const uint32_t da = smem_u32(s.d_o[st]);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t offa = (kk >> 2) * 16384 + (kk & 3) * 32;
@@ -220,29 +224,31 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       bool ok = true;
       do {
         if (!mbar_wait(&s.kv_full, 0, wc, 200)) { ok = false; break; }
-        if (!mbar_wait(&s.qdo_full[0], 0, wc, 201)) { ok = false; break; }
-        tc_fence_after_sync();
-        issue_sdp(0, 0);
-        tc_commit(&s.sdp_full[0]);
+        // two steps of S^T / dP^T are kept in flight ahead of the accumulating products
+        for (int pre = 0; pre < 2 && pre < n_steps; ++pre) {
+          if (!mbar_wait(&s.qdo_full[pre], 0, wc, 201)) { ok = false; break; }
+          tc_fence_after_sync();
+          issue_st(pre, pre);
+          issue_dp(pre, pre);
+          tc_commit(&s.sdp_full[pre]);
+        }
+        if (!ok) break;
         for (int i = 0; i < n_steps; ++i) {
           const int b = i & 1;
           const int st = i % BWD_STAGES;
-          if (i + 1 < n_steps) {
-            const int bn = (i + 1) & 1;
-            const int stn = (i + 1) % BWD_STAGES;
-            const uint32_t phn = ((i + 1) / BWD_STAGES) & 1;
-            if (!mbar_wait(&s.qdo_full[stn], phn, wc, 202)) { ok = false; break; }
-            // dP^T(i+1) lands where dQ^T(i-1) was: wait until that has been drained
-            if (i >= 1 && !mbar_wait(&s.dq_free[bn], ((i - 1) >> 1) & 1, wc, 203)) { ok = false; break; }
-            tc_fence_after_sync();
-            issue_sdp(bn, stn);
-            tc_commit(&s.sdp_full[bn]);
-          }
-          if (!mbar_wait(&s.pds_full[b], (i >> 1) & 1, wc, 204)) { ok = false; break; }
+          const uint32_t ph2 = (i >> 1) & 1;
+          if (!mbar_wait(&s.pds_full[b], ph2, wc, 204)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t qa = smem_u32(s.q[st]);
           const uint32_t da = smem_u32(s.d_o[st]);
           const uint32_t dsa = smem_u32(s.ds[b]);
+          // dQ^T = K^T dS^T first, so that its drain overlaps the two products below.
+          // A = K as an M-major operand, B = dS^T as an N-major operand; lands where dP^T was.
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(t_dp[b], make_smem_desc_sw128(ka + kk * 2048, 16384, 1024),
+                    make_smem_desc_sw128(dsa + kk * 2048, 16, 1024), idesc_dq, kk > 0 ? 1u : 0u);
+          tc_commit(&s.dq_full[b]);
           // dV += P^T dO : A = P^T in TMEM (16 queries = 8 packed columns per step)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
@@ -254,13 +260,19 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
             umma_ss(t_dk, make_smem_desc_sw128(dsa + kk * 32, 16, 1024),
                     make_smem_desc_sw128(qa + kk * 2048, 8192, 1024), idesc_acc,
                     (i > 0 || kk > 0) ? 1u : 0u);
-          // dQ^T = K^T dS^T : A = K as an M-major operand, B = dS^T as an N-major operand
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_ss(t_dp[b], make_smem_desc_sw128(ka + kk * 2048, 16384, 1024),
-                    make_smem_desc_sw128(dsa + kk * 2048, 16, 1024), idesc_dq, kk > 0 ? 1u : 0u);
-          tc_commit(&s.dq_full[b]);
           tc_commit(&s.qdo_empty[st]);
+          if (i + 2 < n_steps) {
+            const int stn = (i + 2) % BWD_STAGES;
+            const uint32_t phn = ((i + 2) / BWD_STAGES) & 1;
+            if (!mbar_wait(&s.qdo_full[stn], phn, wc, 202)) { ok = false; break; }
+            tc_fence_after_sync();
+            issue_st(b, stn);       // overwrites P^T(i), already consumed by dV(i) above
+            // dP^T(i+2) lands where dQ^T(i) is: wait until the drain warpgroup has read it
+            if (!mbar_wait(&s.dq_free[b], ph2, wc, 203)) { ok = false; break; }
+            tc_fence_after_sync();
+            issue_dp(b, stn);
+            tc_commit(&s.sdp_full[b]);
+          }
         }
         if (ok) tc_commit(&s.dkv_full);
       } while (false);
@@ -341,8 +353,10 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
 #pragma unroll
               for (int c = 0; c < 4; ++c) {
                 const int q0 = h * 32 + ch * 8 + 2 * c;
-                const float d0 = pv[q0] * (__uint_as_float(dp[ch * 8 + 2 * c]) - s.dvec[b][quad][q0]);
-                const float d1 = pv[q0 + 1] * (__uint_as_float(dp[ch * 8 + 2 * c + 1]) - s.dvec[b][quad][q0 + 1]);
+                float d0 = pv[q0] * (__uint_as_float(dp[ch * 8 + 2 * c]) - s.dvec[b][quad][q0]);
+                float d1 = pv[q0 + 1] * (__uint_as_float(dp[ch * 8 + 2 * c + 1]) - s.dvec[b][quad][q0 + 1]);
+                d0 = pv[q0] == 0.f ? 0.f : d0;          // masked entries stay exactly zero
+                d1 = pv[q0 + 1] == 0.f ? 0.f : d1;
                 w4[c] = pack_bf16x2(d0, d1);
               }
               *reinterpret_cast<uint4*>(ds_row + sw128_offset(key_t, h * 4 + ch)) =
@@ -408,9 +422,9 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     }
   } else {
     // =============================== dQ drain warpgroup =====================================
-    const int quad = warp & 3;
-    const int d_idx = quad * 32 + lane;              // head-dim element (TMEM lane of dQ^T)
+    const int quad = warp & 3;                       // TMEM lanes quad*32.. = head-dim slice
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    float* stage = s.dq_stage[quad];
     bool ok = true;
     uint32_t i = 0;
     for (int g = 0; g < p.kv_group && ok; ++g) {
@@ -418,40 +432,40 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       for (int e = col.seg_begin; e < col.seg_end && ok; ++e) {
         const AttnSeg sg = p.segs[e];
         const int nq = seg_num_qt(sg);
-        float* dq_base = p.dq_ptr[sg.src] + batch * p.dq_batch_stride[sg.src] +
-                         static_cast<long>(head) * ATTN_D + d_idx;
-        const long rs = p.dq_row_stride[sg.src];
+        const CUtensorMap* tdq = &p.tmdQ[sg.src];
         for (int t = seg_first_qt(sg, c0); t < nq; ++t, ++i) {
           const int b = i & 1;
           if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.dq_full[b], (i >> 1) & 1, wc, 400))) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t t_dq = tmem_base + lane_base + 384 + b * 64;
-          const int r_base = t * BWD_QT;
-          const int n_valid = min(BWD_QT, sg.len - r_base);
+          uint32_t dv0[32], dv1[32];
+          tmem_ld_x32(t_dq, dv0);
+          tmem_ld_x32(t_dq + 32, dv1);
+          tmem_wait_ld();
+          // TMEM buffer read: hand it back before the slower shared-memory / TMA part
+          tc_fence_before_sync();
+          mbar_arrive(&s.dq_free[b]);
+          const int qrow = sg.start + t * BWD_QT;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            uint32_t dv[32];
-            tmem_ld_x32(t_dq + h * 32, dv);
-            tmem_wait_ld();
-            if (h == 1) {
-              // all TMEM reads of this buffer are done: hand it back before the slow part
-              tc_fence_before_sync();
-              mbar_arrive(&s.dq_free[b]);
-            }
+            // the previous reduce must have finished reading the staging buffer
+            if (lane == 0) tma_store_wait_read_all();
+            __syncwarp();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              const int r = h * 32 + c;
-              if (r < n_valid) {
-                float* dst = dq_base + static_cast<long>(sg.start + r_base + r) * rs;
-                asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst),
-                             "f"(__uint_as_float(dv[c]) * p.scale)
-                             : "memory");
-              }
+            for (int c = 0; c < 32; ++c)
+              stage[c * 32 + lane] = __uint_as_float(h == 0 ? dv0[c] : dv1[c]) * p.scale;
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_4d(tdq, stage, quad * 32, head, qrow + h * 32, batch);
+              tma_store_commit();
             }
           }
         }
       }
     }
+    if (lane == 0) tma_store_wait_all();
+    __syncwarp();
   }
 
   tc_fence_before_sync();
@@ -481,8 +495,8 @@ struct UaBwdQSide {
   const float* dvec;       // same layout
   long lse_head_stride;
   long lse_batch_stride;
-  float* dq;               // fp32 [batch, tokens, heads, 128]
-  long dq_row_stride;
+  float* dq;               // fp32 [batch, tokens, heads, 128], heads*128 contiguous per token
+  long dq_row_stride;      // elements between tokens
   long dq_batch_stride;
 };
 struct UaBwdKvOut {
@@ -525,9 +539,17 @@ extern "C" int ua_attn_bwd(const UaTensorSrc* q_src, const UaTensorSrc* do_src,
     p.lse_head_stride[i] = q_side[i].lse_head_stride;
     p.lse_batch_stride[i] = q_side[i].lse_batch_stride;
     p.q_tokens[i] = static_cast<int>(q_src[i].tokens);
-    p.dq_ptr[i] = q_side[i].dq;
-    p.dq_row_stride[i] = q_side[i].dq_row_stride;
-    p.dq_batch_stride[i] = q_side[i].dq_batch_stride;
+    {
+      const UaTensorSrc& t = q_src[i];
+      uint64_t dims[4] = {ATTN_D, static_cast<uint64_t>(t.heads), static_cast<uint64_t>(t.tokens),
+                          static_cast<uint64_t>(t.batch)};
+      const long bstr = q_side[i].dq_batch_stride > 0 ? q_side[i].dq_batch_stride
+                                                      : q_side[i].dq_row_stride * t.tokens;
+      uint64_t str[3] = {ATTN_D * 4ull, static_cast<uint64_t>(q_side[i].dq_row_stride) * 4,
+                         static_cast<uint64_t>(bstr) * 4};
+      uint32_t box[4] = {32, 1, 32, 1};
+      if (make_tmap_f32(&p.tmdQ[i], q_side[i].dq, 4, dims, str, box)) return -1;
+    }
   }
   for (int i = 0; i < n_kv; ++i) {
     if (encode_src_box(&p.tmK[i], k_src[i], ATTN_TILE)) return -1;

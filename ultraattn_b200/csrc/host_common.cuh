@@ -72,4 +72,30 @@ inline int make_tmap_2byte(CUtensorMap* out, const void* base, int rank, const u
   return 0;
 }
 
+// fp32 tiled map without swizzle (used as the destination of TMA reduce-add stores).
+inline int make_tmap_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                         const uint64_t* strides_bytes, const uint32_t* box) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) UA_FAIL("cuTensorMapEncodeTiled entry point not found");
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[5];
+  cuuint32_t bx[5];
+  cuuint32_t estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    estr[i] = 1;
+    if (i > 0) gstr[i - 1] = strides_bytes[i - 1];
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) UA_FAIL("TMA base not 16-byte aligned");
+  for (int i = 0; i + 1 < rank; ++i)
+    if (gstr[i] % 16 != 0) UA_FAIL("TMA stride %d (%llu B) not a multiple of 16", i,
+                                   (unsigned long long)gstr[i]);
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank, const_cast<void*>(base), gdim, gstr,
+                  bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) UA_FAIL("cuTensorMapEncodeTiled (f32) failed with code %d", (int)r);
+  return 0;
+}
+
 }  // namespace ua
