@@ -1,0 +1,383 @@
+"""Problem descriptors and the cost model of the planner.
+
+* :class:`Dist_Attn_Config` — one distributed-attention problem (shape + pattern + CP degrees),
+  :class:`Dist_Attn_Schedule` — a tile -> rank table bound to a problem and a machine
+  (reference: search_algo/search_engine.py:39-113, 348-412).
+* :class:`FlashAttn_Profile_Map`, :class:`Inter_Comp_Profile_Map`, :class:`Comm_Profile_Map`,
+  :class:`Machine_Config` — measured kernel times and link bandwidth, read from the same file
+  formats as the reference's profilers (flash JSON ``{"flash_attn": [[[Smin,bs,Nh,D,"p/q",causal],
+  [fwd_us,bwd_us,...]],...]}`` and ``SIZE n, REAL_BD .., BD/PAIR x GB/s`` logs; reference parsers at
+  search_algo/utils.py:229-272; maps at search_algo/search_engine.py:115-328).
+
+Where a key has not been profiled the maps fall back to an analytic B200 model (kernel throughput
+and NVLink bandwidth measured for this framework's own kernels) instead of failing, so that
+plans can be made on a machine without a GPU.
+"""
+from __future__ import annotations
+
+import json
+import math
+import re
+from dataclasses import dataclass, field
+from functools import reduce
+from pathlib import Path
+from typing import Optional, Sequence
+
+import numpy as np
+
+from ..patterns.blocks import BSA_Config
+
+GIB = 1024 ** 3
+
+# measured on B200 with this repository's kernels (bf16, D = 128): sustained tile throughput
+B200_FWD_TFLOPS = 1050.0
+B200_BWD_TFLOPS = 740.0
+B200_NVLINK_GBS = 770.0          # peer copy, per direction
+B200_LINK_LATENCY_S = 4e-6
+B200_LAUNCH_S = 6e-6
+
+
+def convert_shape_config_to_str(shape_config: dict) -> str:
+    return f"S={shape_config['S']}_Nh={shape_config['Nh']}_bs={shape_config['bs']}_D={shape_config['D']}"
+
+
+class Evaluation_Configs:
+    """How a plan is made: plan_type in {'ILP', 'manual', 'Flexflow'}; fob 0 = forward,
+    1 = backward; hierarchy 0 = across nodes, 1 = inside a node; transform_mode in
+    {'bf', 'greedy'} (reference: search_algo/search_engine.py:22-37)."""
+
+    def __init__(self, plan_type: str, MAX_QUEUE_SIZE: int, fob: int, plan_path: Optional[str] = None,
+                 hierarchy: Optional[int] = 1, transform_mode: str = "bf", inter_comp_profile_map=None):
+        self.plan_type = plan_type
+        self.MAX_QUEUE_SIZE = MAX_QUEUE_SIZE
+        self.fob = fob
+        self.plan_path = plan_path
+        self.hierarchy = hierarchy
+        self.transform_mode = transform_mode
+        self.inter_comp_profile_map = inter_comp_profile_map
+        self.execution_plan = None
+
+    def get_plan_path(self) -> str:
+        return self.plan_path
+
+
+class Dist_Attn_Config:
+    """``SP = (inter, intra)``; ``S = (Sq, Skv)`` totals; ``Nh = (Nh, Ng)``; note that
+    ``BSA_Config.CP`` is ``(intra, inter)`` — the opposite order."""
+
+    def __init__(self, SP, S, Nh, bs, D, causal=None, hierarchy: int = 1,
+                 bsa_config: Optional[BSA_Config] = None):
+        assert bsa_config is not None, "a block-sparse pattern (BSA_Config) is required"
+        self.SP = tuple(SP)
+        self.S = tuple(S)
+        self.Nh = tuple(Nh)
+        self.bs = bs
+        self.D = D
+        self.hierarchy = hierarchy
+        self.bsa_config = bsa_config
+
+    @classmethod
+    def from_bsa_config(cls, bsa_config: BSA_Config, shape_config: dict, hierarchy: int):
+        return cls((bsa_config.CP[1], bsa_config.CP[0]), **shape_config, causal=bsa_config.causal,
+                   hierarchy=hierarchy, bsa_config=bsa_config)
+
+    @property
+    def causal(self) -> bool:
+        return self.bsa_config.causal
+
+    @property
+    def shape_config(self) -> dict:
+        return {"S": self.S, "Nh": self.Nh, "bs": self.bs, "D": self.D}
+
+    @property
+    def hierarchy_sp(self) -> int:
+        return self.SP[self.hierarchy]
+
+    @property
+    def tot_sp(self) -> int:
+        return reduce(lambda x, y: x * y, self.SP)
+
+    @property
+    def tot_Par_D(self) -> int:
+        n = max(self.tot_sp, self.bsa_config.table.shape[0])
+        if self.hierarchy == 0 and self.bsa_config.table.shape == (1, 1) and self.bsa_config.table[0, 0] == 2:
+            n = self.tot_sp * (CP2ParD_map.get(self.SP[0], self.SP[0]) // self.SP[0])
+        return n
+
+    @property
+    def S_per_gpu(self):
+        return (self.S[0] // self.tot_sp, self.S[1] // self.tot_sp)
+
+    @property
+    def S_per_partition(self):
+        return (self.S[0] // self.tot_Par_D, self.S[1] // self.tot_Par_D)
+
+    def get_shape_config_str(self) -> str:
+        return convert_shape_config_to_str(self.shape_config)
+
+    def __str__(self) -> str:
+        s = (f"SP={self.SP},Sg={self.S_per_gpu},S={self.S},Nh={self.Nh},bs={self.bs},D={self.D},"
+             f"hierarchy={self.hierarchy}").replace(" ", "")
+        return s + f",bsa_config={self.bsa_config}"
+
+
+# inter-node causal uses a finer partition than the node count (reference: dense_utils.py:12-17)
+CP2ParD_map = {1: 1, 2: 4, 4: 8, 8: 8}
+
+
+# -------------------------------------------------------------------------------------------------
+# compute cost
+# -------------------------------------------------------------------------------------------------
+def attention_flops(sq: int, skv: int, nh: int, bs: int, d: int, causal: bool, fob: int) -> float:
+    """Model FLOPs of one tile: 4*Sq*Skv*D per head forward, 2.5x that backward (the reference
+    counts 2x model / 2.5x hardware FLOPs for the backward, search_algo/utils.py:92-103)."""
+    f = 4.0 * sq * skv * d * nh * bs * (0.5 if causal else 1.0)
+    return f if fob == 0 else 2.5 * f
+
+
+def analytic_tile_time(sq: int, skv: int, nh: int, bs: int, d: int, causal: bool) -> np.ndarray:
+    """[fwd_s, bwd_s] of this framework's kernels on B200 for one tile. Small tiles under-fill the
+    148 SMs: the forward launches ceil(Sq/256)*Nh CTAs, the backward ceil(Skv/128)*Nh."""
+    def wave_eff(ctas: int) -> float:
+        waves = ctas / 148.0
+        return waves / math.ceil(waves) if ctas > 0 else 1.0
+    f_fwd = attention_flops(sq, skv, nh, bs, d, causal, 0)
+    f_bwd = attention_flops(sq, skv, nh, bs, d, causal, 1)
+    e_f = max(wave_eff(math.ceil(sq / 256) * nh * bs), 0.05)
+    e_b = max(wave_eff(math.ceil(skv / 128) * nh * bs), 0.05)
+    return np.array([f_fwd / (B200_FWD_TFLOPS * 1e12 * e_f) + B200_LAUNCH_S,
+                     f_bwd / (B200_BWD_TFLOPS * 1e12 * e_b) + B200_LAUNCH_S])
+
+
+class Comp_Profile_Map:
+    profile_map: dict
+
+    def get_comp_time_from_map_key(self, map_key) -> np.ndarray:
+        raise NotImplementedError
+
+    def get_value_from_map_key(self, map_key):
+        return self.get_comp_time_from_map_key(map_key)
+
+    def get_comp_time(self, da_config, batch_degrees, split_degrees) -> np.ndarray:
+        return self.get_comp_time_from_map_key(self.get_comp_map_key(da_config, batch_degrees, split_degrees))
+
+
+class FlashAttn_Profile_Map(Comp_Profile_Map):
+    """key ``(min(Sq,Skv), bs, Nh, D, "p/q", causal)`` -> ``[fwd_s, bwd_s]``."""
+
+    def __init__(self, profile_map: Optional[dict] = None, analytic_fallback: bool = True):
+        self.profile_map = dict(profile_map or {})
+        self.analytic_fallback = analytic_fallback
+
+    @staticmethod
+    def _shape_of_key(key):
+        smin, bs, nh, d, ratio, causal = key
+        p, q = (int(x) for x in ratio.split("/"))
+        if p >= q:
+            skv = smin
+            sq = smin * p // q
+        else:
+            sq = smin
+            skv = smin * q // p
+        return sq, skv, nh, bs, d, bool(causal)
+
+    def get_comp_time_from_map_key(self, map_key) -> np.ndarray:
+        if map_key in self.profile_map:
+            return np.asarray(self.profile_map[map_key], dtype=float)
+        if not self.analytic_fallback:
+            raise KeyError(f"Key {map_key} not found in profile_map")
+        return analytic_tile_time(*self._shape_of_key(map_key))
+
+    def get_comp_map_key(self, da_config: Dist_Attn_Config, batch_degrees: Sequence[int],
+                         split_degrees: Sequence[int], causal: bool = False) -> tuple:
+        sq = da_config.S[0] * batch_degrees[0] // split_degrees[0]
+        skv = da_config.S[1] * batch_degrees[1] // split_degrees[1]
+        bs = da_config.bs // split_degrees[2]
+        nh = da_config.Nh[0] // split_degrees[3]
+        g = math.gcd(sq, skv)
+        return (min(sq, skv), bs, nh, da_config.D, f"{sq // g}/{skv // g}", causal)
+
+    def merge_comp_map_key(self, k0: tuple, k1: tuple, merge_dim: int) -> tuple:
+        """Key of the tile obtained by gluing two non-causal tiles along dim 0 (Sq), 1 (Skv),
+        2 (bs) or 3 (Nh)."""
+        assert not (k0[5] or k1[5]), "causal tiles are not merged"
+        if merge_dim in (0, 1):
+            s0 = self._shape_of_key(k0)[:2]
+            s1 = self._shape_of_key(k1)[:2]
+            assert s0[merge_dim ^ 1] == s1[merge_dim ^ 1]
+            s = (s0[0] + s1[0], s0[1]) if merge_dim == 0 else (s0[0], s0[1] + s1[1])
+            g = math.gcd(*s)
+            return (min(s), k0[1], k0[2], k0[3], f"{s[0] // g}/{s[1] // g}", False)
+        out = list(k0)
+        out[merge_dim - 1] += k1[merge_dim - 1]
+        return tuple(out)
+
+
+class Inter_Comp_Profile_Map(Comp_Profile_Map):
+    """String database key -> measured time of the intra-node plan that implements an inter-node
+    compute tile (reference: search_algo/search_engine.py:272-280)."""
+
+    def __init__(self, profile_map: Optional[dict] = None):
+        self.profile_map = dict(profile_map or {})
+
+    def get_comp_time_from_map_key(self, map_key) -> np.ndarray:
+        v = self.profile_map[map_key]
+        if isinstance(v, dict):
+            t = float(v["time"])
+            return np.array([t, t])
+        return np.asarray(v, dtype=float)
+
+    def update(self, other: dict) -> None:
+        self.profile_map.update(other)
+
+
+# -------------------------------------------------------------------------------------------------
+# communication cost
+# -------------------------------------------------------------------------------------------------
+class Comm_Profile_Map:
+    """``(bytes,)`` -> GB/s of one peer-to-peer message under a 2-rank bidirectional pattern;
+    ``time = bytes / BW(bytes)``, clamped to the largest profiled size."""
+
+    def __init__(self, profile_map: Optional[dict] = None, peak_gbs: float = B200_NVLINK_GBS,
+                 latency_s: float = B200_LINK_LATENCY_S):
+        self.profile_map = dict(profile_map or {})
+        self.sizes = sorted(k[0] for k in self.profile_map)
+        self.peak_gbs = peak_gbs
+        self.latency_s = latency_s
+
+    def get_comm_map_key(self, da_config: Dist_Attn_Config, batch_degrees, split_degrees) -> tuple:
+        """Bytes of one comm unit: one Q-side tile, ``Sq_tile * bs * Nh * D * 2``."""
+        sq = da_config.S[0] * batch_degrees[0] // split_degrees[0]
+        return (sq * (da_config.bs // split_degrees[2]) * (da_config.Nh[0] // split_degrees[3])
+                * da_config.D * 2,)
+
+    def bandwidth_gbs(self, nbytes: float) -> float:
+        if not self.sizes:
+            if nbytes <= 0:
+                return self.peak_gbs
+            return nbytes / 1e9 / (self.latency_s + nbytes / (self.peak_gbs * 1e9))
+        import bisect
+        i = bisect.bisect_left(self.sizes, nbytes)
+        i = min(i, len(self.sizes) - 1)
+        return self.profile_map[(self.sizes[i],)]
+
+    def get_comm_time_from_map_key(self, map_key) -> float:
+        nbytes = map_key[0]
+        if nbytes <= 0:
+            return 0.0
+        return nbytes / 1e9 / self.bandwidth_gbs(nbytes)
+
+    get_value_from_map_key = get_comm_time_from_map_key
+
+
+class Machine_Config:
+    """[inter, intra] compute maps and [inter, intra] communication maps."""
+
+    def __init__(self, BW=None, comp_profile_maps=None, comm_profile_maps=None):
+        self.BW = BW or (B200_NVLINK_GBS, B200_NVLINK_GBS)
+        self.comp_profile_maps = comp_profile_maps or [Inter_Comp_Profile_Map(), FlashAttn_Profile_Map()]
+        self.comm_profile_maps = comm_profile_maps or [Comm_Profile_Map(), Comm_Profile_Map()]
+
+    @classmethod
+    def b200_default(cls) -> "Machine_Config":
+        return cls()
+
+    def update_inter_bsa_profile(self, profile: dict) -> None:
+        self.comp_profile_maps[0].update(profile)
+
+
+# -------------------------------------------------------------------------------------------------
+# profile file formats
+# -------------------------------------------------------------------------------------------------
+def convert_profile_data_to_map(profile_list) -> dict:
+    out = {}
+    for key, vals in profile_list:
+        out[tuple(key)] = np.array(vals[:2], dtype=float) / 1e6      # us -> s
+    return out
+
+
+def load_flash_profile(path) -> dict:
+    data = json.loads(Path(path).read_text())
+    return convert_profile_data_to_map(data["flash_attn"])
+
+
+def dump_flash_profile(path, entries) -> None:
+    """entries: iterable of (key tuple, fwd_s, bwd_s, fwd_tflops, bwd_tflops)."""
+    rows = [[list(k), [f * 1e6, b * 1e6, tf, tb]] for k, f, b, tf, tb in entries]
+    Path(path).write_text(json.dumps({"flash_attn": rows}, indent=1))
+
+
+_UNIT = {"B": 1.0, "KB": 1e3, "MB": 1e6, "GB": 1e9, "TB": 1e12}
+_CB_LINE = re.compile(r"^SIZE (\d+),.*?BD/PAIR (\d*(?:\.\d*)?) ([A-Z]+)/s")
+
+
+def convert_profile_data_to_comm_map(file_name, num_gpus_div: int = 1) -> dict:
+    out = {}
+    for line in Path(file_name).read_text().splitlines():
+        m = _CB_LINE.match(line)
+        if m:
+            out[(int(m.group(1)),)] = float(m.group(2)) * _UNIT[m.group(3)] / 1e9
+    return out
+
+
+def format_cb_line(size_elems: int, real_gbs: float, pair_gbs: float, time_s: float, vol_mb: float) -> str:
+    return (f"SIZE {size_elems}, REAL_BD {real_gbs:.3f} GB/s, BD/PAIR {pair_gbs:.3f} GB/s, "
+            f"time {time_s:.3e} s, comm_vol {vol_mb:.3f} MB")
+
+
+# -------------------------------------------------------------------------------------------------
+# schedule
+# -------------------------------------------------------------------------------------------------
+class Dist_Attn_Schedule:
+    """A tile allocation bound to a problem: ``schedule_table[bs, Nh, q_blk, kv_blk]`` = rank
+    computing the tile (-1 empty); ``S_map[bs, blk]`` = owner rank of each sequence block;
+    ``split_degrees = (Sq_split, Skv_split, bs_split, Nh_split)``.
+
+    Communication units per message kind, [fwd, bwd], in Q-tile units
+    (reference: search_algo/search_engine.py:388-409):
+    input row (Q | Q+dO) = [1, 2]; input col (K,V) = [2, 2]*r; output row (O | dQ) = [1, 1];
+    output col (- | dK,dV) = [0, 2]*r with r the KV/Q size ratio.
+    """
+
+    def __init__(self, da_config: Dist_Attn_Config, m_config: Machine_Config, split_degrees,
+                 S_map: np.ndarray, schedule_table: np.ndarray, hierarchy: Optional[int] = None):
+        self.da_config = da_config
+        self.m_config = m_config
+        self.split_degrees = tuple(split_degrees)
+        self.S_map = np.asarray(S_map)
+        self.schedule_table = np.asarray(schedule_table)
+        assert self.schedule_table.shape == (split_degrees[2], split_degrees[3], split_degrees[0],
+                                             split_degrees[1])
+        kv_ratio = ((da_config.S[1] / split_degrees[1]) / (da_config.S[0] / split_degrees[0])
+                    * (da_config.Nh[1] / da_config.Nh[0]))
+        self.u_inp_row = np.array([1.0, 2.0])
+        self.u_inp_col = np.array([2.0, 2.0]) * kv_ratio
+        self.u_out_row = np.array([1.0, 1.0])
+        self.u_out_col = np.array([0.0, 2.0]) * kv_ratio
+
+    @property
+    def tot_sp(self) -> int:
+        return self.da_config.tot_sp
+
+    @property
+    def hierarchy(self) -> int:
+        return self.da_config.hierarchy
+
+    @property
+    def hierarchy_sp(self) -> int:
+        return self.da_config.hierarchy_sp
+
+    def get_relative_cc_time(self) -> float:
+        return 0.0
+
+
+def get_cc_optimal_schedule_from_table(da_config: Dist_Attn_Config, m_config: Machine_Config,
+                                       allocation) -> Dist_Attn_Schedule:
+    """Wrap an ILP #1 result (dict-like with 'Par_D', 'cmap', 'table') into a schedule
+    (reference: search_algo/search_engine.py:969-987)."""
+    par_d = int(allocation["Par_D"])
+    table = np.asarray(allocation["table"])
+    cmap = np.asarray(allocation["cmap"])
+    split = (par_d, par_d, 1, 1)
+    s_map = np.tile(cmap[None, :], (1, 1))
+    return Dist_Attn_Schedule(da_config, m_config, split, s_map, table[None, None])

@@ -1,0 +1,42 @@
+"""One-call planning: pattern + shape + CP degree -> allocation -> kernel graph -> launch plan."""
+from __future__ import annotations
+
+from typing import Optional
+
+from ..patterns.blocks import BSA_Config, BSA_Repr
+from .allocate import naive_allocate_strategy, solve_sparse_from_bsa
+from .cost import Dist_Attn_Config, Machine_Config, get_cc_optimal_schedule_from_table
+from .fuse import Graph_Transformation_Engine
+from .graph import Dependent_Graph
+from .schedule import Execution_Plan
+
+
+def make_plan(pattern: BSA_Repr, cp: int, seq_len: int, n_heads: int, head_dim: int = 128,
+              n_kv_heads: Optional[int] = None, batch: int = 1, fob: int = 0, *,
+              allocation: str = "ilp", plan_type: str = "Flexflow", kernel_tile: bool = False,
+              m_config: Optional[Machine_Config] = None, ParD: Optional[int] = None,
+              objective: str = "comm", time_limit: float = 30.0, cmap=None) -> Execution_Plan:
+    """Plan one intra-node distributed attention call.
+
+    ``allocation``: ``"ilp"`` (ILP #1) or ``"naive"`` (row owner). ``plan_type``: ``"ILP"`` or
+    ``"Flexflow"``. ``kernel_tile``: try rectangle fusion and keep it if the makespan improves.
+    """
+    m_config = m_config or Machine_Config.b200_default()
+    cfg = BSA_Config(None, None, {"bsa_repr": pattern if cmap is None else BSA_Repr(pattern.block_table_int, cmap),
+                                  "CP": (cp, 1)})
+    shape = {"S": (seq_len, seq_len), "Nh": (n_heads, n_kv_heads or n_heads), "bs": batch, "D": head_dim}
+    da = Dist_Attn_Config.from_bsa_config(cfg, shape, hierarchy=1)
+    if allocation == "naive":
+        alloc = naive_allocate_strategy(cfg, fob=fob, hierarchy=1, ParD=ParD)
+    else:
+        alloc = solve_sparse_from_bsa(cfg, fob=fob, ParD=ParD, hierarchy=1, objective=objective,
+                                      time_limit=time_limit, cmap=cmap)
+    schedule = get_cc_optimal_schedule_from_table(da, m_config, alloc)
+    graph = Dependent_Graph(schedule, fob)
+    if kernel_tile:
+        plan = Graph_Transformation_Engine(None, da, m_config).transform(graph, "greedy", plan_type,
+                                                                         time_limit=time_limit)
+    else:
+        plan = Execution_Plan(graph, fob, plan_type, time_limit=time_limit)
+    plan.allocation = alloc
+    return plan
