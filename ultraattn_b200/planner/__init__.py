@@ -6,4 +6,4 @@ from .cost import (Comm_Profile_Map, Dist_Attn_Config, Dist_Attn_Schedule, Evalu
 from .fuse import Comp_Fusion_Substitution, Comp_Fusion_Transformation, Graph_Transformation_Engine
 from .graph import Comm_Kernel, Comp_Kernel, Cuda_Kernel, Dependent_Graph
 from .schedule import Execution_Plan, Fused_Execution_Plan, create_one_node_exe_plan
-from .pipeline import make_plan
+from .pipeline import make_plan, make_plan_collective

@@ -40,3 +40,18 @@ def make_plan(pattern: BSA_Repr, cp: int, seq_len: int, n_heads: int, head_dim: 
         plan = Execution_Plan(graph, fob, plan_type, time_limit=time_limit)
     plan.allocation = alloc
     return plan
+
+
+def make_plan_collective(group=None, src: int = 0, **kwargs) -> Execution_Plan:
+    """Plan on one rank and broadcast the result, so that every rank walks the *same* plan.
+    (A time-limited solver may return different incumbents in different processes; the reference
+    likewise plans on rank 0 only and shares plans through its database,
+    search_algo/task1_bsa.py:917-938.)"""
+    import torch.distributed as dist
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return make_plan(**kwargs)
+    rank = dist.get_rank(group)
+    box = [make_plan(**kwargs) if rank == src else None]
+    dist.broadcast_object_list(box, src=dist.get_global_rank(group, src) if group is not None else src,
+                               group=group)
+    return box[0]
