@@ -1,0 +1,227 @@
+"""Headline benchmark: context-parallel block-sparse attention forward + backward.
+
+Config (fixed): strided block-sparse training attention, S = 512k tokens in 32 blocks of 16k
+(query block i attends key block j iff j <= i and (i - j <= 1 or (i - j) % 4 == 0)), 32 heads,
+head dim 128, batch 1, bf16, Q/K/V/dO ~ N(0,1) seed 1, context-parallel over N GPUs of one node
+(strong scaling: the problem is fixed, N = 1 runs it on one GPU).
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched under torchrun)
+    python bench.py --impl reference ...                      (the reference arm)
+
+Prints one JSON line on rank 0. ``value`` = milliseconds per forward+backward, device-timed with
+CUDA events around exactly K steps, max over ranks. ``e2e`` = the same step through the public
+API (``ultraattn_b200.attention``) including, every step, the host-to-device copy of this rank's
+Q/K/V/dO shards from pinned memory and the device-to-host read of the step's scalar result.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "cp_attn_fwd_bwd_ms_S512k_strided"
+S_TOTAL, N_BLOCKS, N_HEADS, HEAD_DIM = 512 * 1024, 32, 32, 128
+
+
+def reference_arm(args) -> None:
+    why = ("reference is not installable offline: pip reports neither setup.py nor pyproject.toml; its "
+           "runtime also needs the forked flash-attention v2.5.7_burst submodule (empty in this checkout), "
+           "NCCL 2.21.5 at a hard-coded path and a Gurobi licence")
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--path", default="fused", choices=["fused", "nccl"],
+                    help="multi-GPU execution path: fused peer-memory kernels or the NCCL baseline")
+    ap.add_argument("--seq", type=int, default=S_TOTAL, help="(debug) total sequence length")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import ultraattn_b200 as ua
+    from ultraattn_b200 import _lib
+    from ultraattn_b200 import patterns as P
+    from ultraattn_b200.ops import attention as A
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    S = args.seq
+    pattern = P.strided(N_BLOCKS, 4, 2)
+    S_loc = S // world
+    gen = torch.Generator(device="cpu").manual_seed(1 + rank)
+
+    # ---- inputs: pinned host copies (for the end-to-end arm) and device copies (kernel arm) -----
+    def host_tensor():
+        t = torch.empty(1, S_loc, N_HEADS, HEAD_DIM, dtype=torch.bfloat16, pin_memory=True)
+        chunk = 1 << 24
+        flat = t.view(-1)
+        for off in range(0, flat.numel(), chunk):        # bounded temporary fp32 memory
+            n = min(chunk, flat.numel() - off)
+            flat[off:off + n] = torch.randn(n, generator=gen, dtype=torch.float32).to(torch.bfloat16)
+        return t
+    h_q, h_k, h_v, h_do = (host_tensor() for _ in range(4))
+    q, k, v, d_o = (t.to(dev, non_blocking=True) for t in (h_q, h_k, h_v, h_do))
+    torch.cuda.synchronize()
+
+    if world == 1:
+        runtime = None
+        fplan, bplan = ua.api.local_plans(pattern, S, dev)
+        o = torch.empty_like(q)
+        lse = torch.empty(1, N_HEADS, S, dtype=torch.float32, device=dev)
+
+        def step_kernels():
+            A.attn_fwd([q], [k], [v], [(o, lse)], fplan)
+            return ua.api.local_backward(q, k, v, o, lse, d_o, bplan)
+        parallelism = "cp1"
+    else:
+        from ultraattn_b200.runtime import ContextParallelAttention
+        runtime = ContextParallelAttention(pattern, S, N_HEADS, HEAD_DIM, group=dist.group.WORLD,
+                                           device=dev, path=args.path)
+
+        def step_kernels():
+            o_, lse_ = runtime.forward(q, k, v)
+            return runtime.backward(d_o, q, k, v, o_, lse_)
+        parallelism = f"cp{world}-{args.path}"
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0 = _lib.LAUNCHES[0]
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        return ms, _lib.LAUNCHES[0] - n0
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, launches = timed(step_kernels, args.steps, max(args.warmup, 3))
+    A.check_status(dev)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end-to-end arm: public API, H2D of the inputs and D2H of the result every step ---------
+    e2e = None
+    if not args.no_e2e:
+        del q, k, v
+        torch.cuda.empty_cache()
+        bytes_in = 4 * h_q.numel() * 2
+        result = {}
+
+        def step_e2e():
+            qd = h_q.to(dev, non_blocking=True).requires_grad_()
+            kd = h_k.to(dev, non_blocking=True).requires_grad_()
+            vd = h_v.to(dev, non_blocking=True).requires_grad_()
+            wd = h_do.to(dev, non_blocking=True)
+            out = ua.attention(qd, kd, vd, pattern, runtime=runtime)
+            out.backward(wd)
+            # the step's scalar result: a checksum over a slice of dQ, read back to the host
+            result["v"] = float(qd.grad[0, :64].float().sum().cpu())
+        e2e_ms, _ = timed(step_e2e, max(1, min(args.steps, 3)), 3)
+        A.check_status(dev)
+        e2e = {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": 4,
+               "checksum": result.get("v")}
+
+    if rank == 0:
+        vol = pattern.volume * (S / N_BLOCKS) ** 2 * 4 * HEAD_DIM * N_HEADS      # forward model FLOPs
+        tflops = vol * 3.5 / (ms * 1e-3) / 1e12 / world
+        print(json.dumps({
+            "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic N(0,1), seed 1",
+            "config": {"model": "attention-only (Llama2-7B attention shape: 32 heads x 128)",
+                       "pattern": "strided: 32 blocks of 16k, j<=i and (i-j<=1 or (i-j)%4==0)",
+                       "global_batch": 1, "seq_len": S, "parallelism": parallelism,
+                       "l2": "inputs (4 GiB per tensor in total) far exceed the 126 MB L2; no flush needed"},
+            "model_tflops_per_gpu": tflops, "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,221 @@
+"""sm_100a kernels against fp32 PyTorch restatements of the same ops (run on a B200)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA GPU")
+    from ultraattn_b200 import _lib
+    _lib.load()          # fails loudly if the kernel library is missing
+    return torch.device("cuda")
+
+
+def _close(got, ref, tol):
+    err = (got.float() - ref.float()).abs().max().item()
+    scale = ref.float().abs().max().item() + 1e-6
+    assert err <= tol * scale, f"max err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (1000, 520, 264), (2048, 4096, 1024)])
+def test_gemm_tn(dev, M, N, K):
+    from ultraattn_b200.ops import attention as A, gemm as G
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+    c = G.gemm(a, b)
+    A.check_status(dev)
+    _close(c, a.float() @ b.float().t(), 1e-2)
+
+
+def test_gemm_other_layouts(dev):
+    from ultraattn_b200.ops import attention as A, gemm as G
+    torch.manual_seed(1)
+    M, N, K = 512, 768, 512
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    bkn = torch.randn(K, N, device=dev, dtype=torch.bfloat16)
+    _close(G.gemm(a, bkn, b_is_kn=True), a.float() @ bkn.float(), 1e-2)
+    akm = torch.randn(K, M, device=dev, dtype=torch.bfloat16)
+    _close(G.gemm(akm, bkn, a_is_km=True, b_is_kn=True), akm.float().t() @ bkn.float(), 1e-2)
+    A.check_status(dev)
+
+
+def test_gemm_scatter_gather_single_gpu(dev):
+    """The all-to-all fusions with every 'peer' buffer on this GPU: column groups land in
+    different buffers (scatter) and K groups come from different buffers (gather)."""
+    from ultraattn_b200.ops import attention as A, gemm as G
+    torch.manual_seed(2)
+    M, N, K, P = 256, 512, 256, 4
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    dsts = [torch.zeros(2 * M, N // P, device=dev, dtype=torch.bfloat16) for _ in range(P)]
+    G.gemm_scatter(a, w, [d.data_ptr() for d in dsts], N // P, M)
+    for g, d in enumerate(dsts):
+        _close(d[M:], ref[:, g * (N // P):(g + 1) * (N // P)], 1e-2)
+        assert d[:M].abs().max().item() == 0
+    srcs = [torch.randn(3 * M, K // P, device=dev, dtype=torch.bfloat16) for _ in range(P)]
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    G.gemm_gather([s.data_ptr() for s in srcs], 3 * M, K // P, M, M, K // P, w, out)
+    a_full = torch.cat([s[M:2 * M] for s in srcs], dim=1)
+    _close(out, a_full.float() @ w.float().t(), 1e-2)
+    A.check_status(dev)
+
+
+CASES = [
+    ("full", 256, 1, 1, [[1]], 256),
+    ("causal", 256, 2, 2, [[2]], 256),
+    ("causal-1k", 1024, 4, 4, [[2]], 1024),
+    ("bsa", 2048, 4, 4, [[2, 0, 0, 0], [1, 2, 0, 0], [1, 0, 2, 0], [1, 0, 1, 2]], 512),
+    ("gqa", 1024, 8, 2, [[2]], 1024),
+    ("ragged", 320, 2, 2, [[2]], 320),
+    ("global-local", 2048, 2, 2, None, 256),
+]
+
+
+@pytest.mark.parametrize("name,S,H,Hk,table,block", CASES, ids=[c[0] for c in CASES])
+def test_attention_fwd_bwd(dev, name, S, H, Hk, table, block):
+    from ultraattn_b200 import patterns as P
+    from ultraattn_b200.ops import attention as A, elementwise as E
+    torch.manual_seed(0)
+    tab = P.global_local(8, 1, 2).block_table_int if table is None else np.array(table)
+    q = torch.randn(1, S, H, 128, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(1, S, Hk, 128, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(1, S, Hk, 128, device=dev, dtype=torch.bfloat16)
+    d_o = torch.randn(1, S, H, 128, device=dev, dtype=torch.bfloat16)
+    rows = A.rows_from_block_table(tab, block)
+    cols = A.cols_from_block_table(tab, block)
+    o = torch.zeros_like(q)
+    lse = torch.zeros(1, H, S, device=dev, dtype=torch.float32)
+    A.attn_fwd_cuda([q], [k], [v], [(o, lse)], A.FwdPlan(rows, dev))
+    o_ref = torch.zeros(1, S, H, 128, device=dev)
+    lse_ref = torch.zeros(1, H, S, device=dev)
+    A.attn_fwd_reference([q], [k], [v], [(o_ref, lse_ref)], rows)
+    A.check_status(dev)
+    _close(o, o_ref, 1e-2)
+    fin = torch.isfinite(lse_ref)
+    assert (lse[fin] - lse_ref[fin]).abs().max().item() < 2e-3
+    dvec = E.rowdot(o[0], d_o[0]).unsqueeze(0)
+    _close(dvec, (o.float() * d_o.float()).sum(-1).permute(0, 2, 1), 1e-3)
+    dq = torch.zeros(1, S, H, 128, device=dev)
+    dk = torch.zeros(1, S, Hk, 128, device=dev, dtype=torch.bfloat16)
+    dv = torch.zeros_like(dk)
+    A.attn_bwd_cuda([A.BwdQSide(q, d_o, lse, dvec, dq)], [k], [v], [A.BwdKvOut(dk, dv)], A.BwdPlan(cols, dev))
+    dq_r = torch.zeros_like(dq)
+    dk_r = torch.zeros(1, S, Hk, 128, device=dev)
+    dv_r = torch.zeros_like(dk_r)
+    A.attn_bwd_reference([A.BwdQSide(q, d_o, lse_ref, dvec, dq_r)], [k], [v], [A.BwdKvOut(dk_r, dv_r)], cols)
+    A.check_status(dev)
+    _close(dq, dq_r, 2e-2)
+    _close(dk, dk_r, 2e-2)
+    _close(dv, dv_r, 2e-2)
+
+
+def test_attention_accumulate_and_add_modes(dev):
+    """Forward merge-into-existing (the running-state mode) and backward fp32 add mode."""
+    from ultraattn_b200.ops import attention as A, elementwise as E
+    torch.manual_seed(3)
+    S, H = 512, 2
+    q, k, v, d_o = (torch.randn(1, S, H, 128, device=dev, dtype=torch.bfloat16) for _ in range(4))
+    o = torch.zeros_like(q)
+    lse = torch.zeros(1, H, S, device=dev)
+    first = [A.Row(0, 0, S, (A.Seg(0, 0, 256, False, 0),), 0, 0, False)]
+    second = [A.Row(0, 0, S, (A.Seg(0, 256, 256, False, 0),), 0, 0, True)]
+    A.attn_fwd_cuda([q], [k], [v], [(o, lse)], A.FwdPlan(first, dev))
+    A.attn_fwd_cuda([q], [k], [v], [(o, lse)], A.FwdPlan(second, dev))
+    both = [A.Row(0, 0, S, (A.Seg(0, 0, S, False, 0),), 0, 0, False)]
+    o_ref = torch.zeros(1, S, H, 128, device=dev)
+    lse_ref = torch.zeros(1, H, S, device=dev)
+    A.attn_fwd_reference([q], [k], [v], [(o_ref, lse_ref)], both)
+    _close(o, o_ref, 1.5e-2)
+    assert (lse - lse_ref).abs().max().item() < 2e-3
+    dvec = E.rowdot(o[0], d_o[0]).unsqueeze(0)
+    cols = [A.Col(0, 0, S, (A.Seg(0, 0, S, False, 0),), 0, 0)]
+    dq = torch.zeros(1, S, H, 128, device=dev)
+    dk = torch.ones(1, S, H, 128, device=dev)
+    dv = torch.ones(1, S, H, 128, device=dev)
+    A.attn_bwd_cuda([A.BwdQSide(q, d_o, lse, dvec, dq)], [k], [v], [A.BwdKvOut(dk, dv)], A.BwdPlan(cols, dev))
+    dq_r = torch.zeros_like(dq)
+    dk_r = torch.ones_like(dk)
+    dv_r = torch.ones_like(dv)
+    A.attn_bwd_reference([A.BwdQSide(q, d_o, lse, dvec, dq_r)], [k], [v], [A.BwdKvOut(dk_r, dv_r)], cols)
+    A.check_status(dev)
+    _close(dk, dk_r, 2e-2)
+    _close(dv, dv_r, 2e-2)
+
+
+def test_autograd_api(dev):
+    import ultraattn_b200 as ua
+    from ultraattn_b200 import patterns as P
+    torch.manual_seed(4)
+    S, H = 1024, 2
+    pat = P.strided(8, 4, 2)
+    q, k, v = (torch.randn(1, S, H, 128, device=dev, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+    d_o = torch.randn(1, S, H, 128, device=dev, dtype=torch.bfloat16)
+    o = ua.attention(q, k, v, pat)
+    o.backward(d_o)
+    o_ref, _, dq, dk, dv = P.dense_attention_with_grads(q, k, v, d_o, pat)
+    _close(o, o_ref, 1e-2)
+    _close(q.grad, dq, 2e-2)
+    _close(k.grad, dk, 2e-2)
+    _close(v.grad, dv, 2e-2)
+
+
+def test_lse_merge(dev):
+    from ultraattn_b200.ops import elementwise as E
+    torch.manual_seed(5)
+    T, H, k = 300, 3, 4
+    parts = [(torch.randn(T, H, 128, device=dev, dtype=torch.bfloat16),
+              torch.randn(H, T, device=dev) * 3) for _ in range(k)]
+    parts[1][1][0, :17] = float("-inf")
+    o_ref, l_ref = E.lse_merge_reference(parts)
+    out = (torch.empty(T, H, 128, device=dev, dtype=torch.bfloat16), torch.empty(H, T, device=dev))
+    E.lse_merge(parts, out)
+    _close(out[0], o_ref, 1e-2)
+    assert (out[1] - l_ref).abs().max().item() < 1e-4
+
+
+def test_model_ops(dev):
+    from ultraattn_b200.ops import elementwise as E
+    torch.manual_seed(6)
+    rows, Hd, F = 257, 4096, 1024
+    x = torch.randn(rows, Hd, device=dev, dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(Hd, device=dev)).to(torch.bfloat16)
+    g = torch.randn(rows, Hd, device=dev, dtype=torch.bfloat16)
+    y, rstd = E.rmsnorm_fwd(x, w, 1e-5)
+    y_ref, rstd_ref = E.rmsnorm_fwd(x.cpu(), w.cpu(), 1e-5)
+    _close(y, y_ref.to(dev), 1e-2)
+    dx, dw = E.rmsnorm_bwd(x, w, g, rstd)
+    dx_ref, dw_ref = E.rmsnorm_bwd(x.cpu(), w.cpu(), g.cpu(), rstd_ref)
+    _close(dx, dx_ref.to(dev), 1e-2)
+    _close(dw, dw_ref.to(dev), 1e-2)
+    T, Hh = 130, 4
+    xr = torch.randn(T, Hh, 128, device=dev, dtype=torch.bfloat16)
+    cos, sin = E.rope_tables(512, 128, device=dev)
+    pos = torch.randint(0, 512, (T,), device=dev, dtype=torch.int32)
+    yr = E.rope(xr, cos, sin, pos)
+    yr_ref = E.rope(xr.cpu(), cos.cpu(), sin.cpu(), pos.cpu())
+    _close(yr, yr_ref.to(dev), 1e-2)
+    back = E.rope(yr, cos, sin, pos, inverse=True)
+    _close(back, xr, 2e-2)
+    gu = torch.randn(rows, 2 * F, device=dev, dtype=torch.bfloat16)
+    dy = torch.randn(rows, F, device=dev, dtype=torch.bfloat16)
+    _close(E.swiglu_fwd(gu), E.swiglu_fwd(gu.cpu()).to(dev), 1e-2)
+    _close(E.swiglu_bwd(gu, dy), E.swiglu_bwd(gu.cpu(), dy.cpu()).to(dev), 1e-2)
+    n = 1000
+    master = torch.randn(n, device=dev)
+    m = torch.zeros(n, device=dev)
+    vv = torch.zeros(n, device=dev)
+    grad = torch.randn(n, device=dev, dtype=torch.bfloat16)
+    param = master.to(torch.bfloat16)
+    ref = [t.cpu().clone() for t in (master, m, vv, grad, param)]
+    E.adam_step(master, m, vv, grad, param, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1)
+    E.adam_step(*ref, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1)
+    _close(master, ref[0].to(dev), 1e-5)
+    _close(param, ref[4].to(dev), 1e-2)

@@ -13,6 +13,7 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_long, c_void_
 from . import build as _build
 
 _lib = None
+LAUNCHES = [0]      # kernels of this library launched so far (every wrapper reports here)
 
 
 class UaTensorSrc(Structure):
@@ -84,6 +85,7 @@ def load():
 
 
 def check(rc: int, what: str) -> None:
+    LAUNCHES[0] += 1
     if rc != 0:
         msg = load().ua_last_error().decode(errors="replace")
         raise RuntimeError(f"{what} failed: {msg}")

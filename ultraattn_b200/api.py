@@ -1,0 +1,88 @@
+"""The differentiable entry point: ``attention(q, k, v, pattern, ...)``.
+
+On one GPU it runs the block-sparse forward / backward kernels directly. With a process group it
+runs context-parallel: every rank passes its shard of the sequence and gets its shard of the
+output, and gradients flow back the same way. The reference exposes ``orchestrated_attn_func``
+with a forward that returns nothing and a backward that asserts
+(orchestrated_attn/orchestrated_attn_impl.py:688-792); this is the operator it was meant to be.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .ops import attention as A
+from .ops import elementwise as E
+from .patterns.blocks import BSA_Repr
+
+_plan_cache: dict = {}
+
+
+def local_plans(pattern: BSA_Repr, seq_len: int, device) -> tuple:
+    """(FwdPlan, BwdPlan) for the whole pattern on one device, cached."""
+    key = (str(pattern), pattern.block_table_int.shape, seq_len, str(device))
+    if key not in _plan_cache:
+        tab = pattern.block_table_int
+        n = tab.shape[0]
+        assert seq_len % n == 0, f"sequence length {seq_len} is not a multiple of {n} blocks"
+        blk = seq_len // n
+        _plan_cache[key] = (A.FwdPlan(A.rows_from_block_table(tab, blk), device),
+                            A.BwdPlan(A.cols_from_block_table(tab, blk), device))
+    return _plan_cache[key]
+
+
+class _LocalAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, pattern, softmax_scale):
+        fplan, bplan = local_plans(pattern, q.shape[1], q.device)
+        o = torch.empty_like(q)
+        lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
+        A.attn_fwd([q], [k], [v], [(o, lse)], fplan, softmax_scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.bplan = bplan
+        ctx.scale = softmax_scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = local_backward(q, k, v, o, lse, d_o.contiguous(), ctx.bplan, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def local_backward(q, k, v, o, lse, d_o, bplan, softmax_scale=None):
+    """dQ, dK, dV of the single-device operator (bf16 on CUDA, input dtype on CPU)."""
+    B, S, H, D = q.shape
+    dvec = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
+    for b in range(B):
+        E.rowdot(o[b], d_o[b], dvec[b])
+    dq32 = torch.zeros(B, S, H, D, dtype=torch.float32, device=q.device)
+    if q.is_cuda:
+        dk = torch.empty_like(k)
+        dv = torch.empty_like(v)
+    else:
+        dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+        dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+    A.attn_bwd([A.BwdQSide(q, d_o, lse, dvec, dq32)], [k], [v], [A.BwdKvOut(dk, dv)], bplan, softmax_scale)
+    if q.is_cuda:
+        dq = torch.empty_like(q)
+        E.cast_scale(dq32, dq)
+        return dq, dk, dv
+    return dq32.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pattern: BSA_Repr, *,
+              softmax_scale: Optional[float] = None, runtime=None) -> torch.Tensor:
+    """Block-sparse attention ``softmax(mask(Q K^T) * scale) V`` with autograd.
+
+    ``q, k, v``: ``[batch, tokens, heads, head_dim]`` (bf16 with head_dim 128 on CUDA; any float
+    type and head dim on CPU). Without ``runtime`` the tensors hold the whole sequence and the call
+    runs on this device alone. With a :class:`ultraattn_b200.runtime.ContextParallelAttention`
+    (``runtime=``) they hold this rank's shard and the call is context-parallel over its group.
+    """
+    if runtime is not None:
+        return runtime(q, k, v, softmax_scale)
+    return _LocalAttention.apply(q, k, v, pattern, softmax_scale)
