@@ -46,10 +46,12 @@ def _declare(lib):
         "ua_gemm_bf16": [POINTER(vp), i, l, i, i, i, vp, i, i, POINTER(vp), i, i, i, i, i, i, vp, i,
                          vp],
         "ua_attn_fwd": [POINTER(UaTensorSrc), i, POINTER(UaTensorSrc), POINTER(UaTensorSrc), i,
-                        POINTER(UaOutDst), i, vp, vp, vp, i, i, i, i, f, vp, vp],
+                        POINTER(UaOutDst), i, vp, vp, vp, i, i, i, i, f, vp, vp, i, i, vp, i, vp],
         "ua_attn_bwd": [POINTER(UaTensorSrc), POINTER(UaTensorSrc), POINTER(UaBwdQSide), i,
                         POINTER(UaTensorSrc), POINTER(UaTensorSrc), i, POINTER(UaBwdKvOut), i,
-                        vp, vp, vp, i, i, i, i, f, vp, vp],
+                        vp, vp, vp, i, i, i, i, f, vp, vp, i, i, vp, i, vp],
+        "ua_barrier": [POINTER(vp), i, i, i, ctypes.c_uint, ctypes.c_double, vp, vp],
+        "ua_wait_flag": [vp, ctypes.c_uint, ctypes.c_double, vp, vp],
         "ua_lse_merge": [POINTER(vp), POINTER(vp), POINTER(l), POINTER(l), i, vp, vp, l, l, i, i,
                          vp],
         "ua_rowdot": [vp, vp, vp, l, l, l, i, i, vp],

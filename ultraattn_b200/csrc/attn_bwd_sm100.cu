@@ -50,6 +50,8 @@ struct BwdCol {
   int g_slot;     // slot in the dK/dV output tables
   int g_start;    // first output row inside that slot
   int pad;
+  int kv_wait_flag;   // staging flag of the key/value block (0: in place)
+  int kv_wait_count;
 };
 
 struct BwdParams {
@@ -77,6 +79,7 @@ struct BwdParams {
   float scale;                      // softmax scale
   float scale_log2;
   int* status;
+  StageParams stage;                // optional in-kernel staging of remote blocks
 };
 
 struct __align__(1024) BwdSmem {
@@ -117,6 +120,8 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+
+  run_stage_prologue(p.stage, blockIdx.y * gridDim.x + blockIdx.x);
 
   const int kv_head = blockIdx.x / p.n_tiles;
   const int2 tl = p.tiles[blockIdx.x % p.n_tiles];
@@ -163,18 +168,28 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     // =============================== TMA producer ===========================================
     if (lane == 0 && n_steps > 0) {
       const int krow = col.kv_start + c0;
+      bool ok = true;
+      if (!wait_staged(p.stage.flags, col.kv_wait_flag, col.kv_wait_count * p.stage.epoch, wc.budget_ns)) {
+        report_error(wc, UA_ERR_FLAG_TIMEOUT, 120, col.kv_wait_flag);
+        ok = false;
+      }
       mbar_arrive_expect_tx(&s.kv_full, 2 * BWD_KV_BYTES);
       tma_load_4d(s.k, &p.tmK[col.kv_src], &s.kv_full, 0, kv_head, krow, batch);
       tma_load_4d(s.k + 16384, &p.tmK[col.kv_src], &s.kv_full, 64, kv_head, krow, batch);
       tma_load_4d(s.v, &p.tmV[col.kv_src], &s.kv_full, 0, kv_head, krow, batch);
       tma_load_4d(s.v + 16384, &p.tmV[col.kv_src], &s.kv_full, 64, kv_head, krow, batch);
       uint32_t i = 0;
-      bool ok = true;
       for (int g = 0; g < p.kv_group && ok; ++g) {
         const int head = kv_head * p.kv_group + g;
         for (int e = col.seg_begin; e < col.seg_end && ok; ++e) {
           const AttnSeg sg = p.segs[e];
           const int nq = seg_num_qt(sg);
+          if (seg_first_qt(sg, c0) < nq &&
+              !wait_staged(p.stage.flags, sg.wait_flag, sg.wait_count * p.stage.epoch, wc.budget_ns)) {
+            report_error(wc, UA_ERR_FLAG_TIMEOUT, 121, sg.wait_flag);
+            ok = false;
+            break;
+          }
           for (int t = seg_first_qt(sg, c0); t < nq; ++t, ++i) {
             const int st = i % BWD_STAGES;
             const uint32_t ph = (i / BWD_STAGES) & 1;
@@ -292,6 +307,13 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       for (int e = col.seg_begin; e < col.seg_end && ok; ++e) {
         const AttnSeg sg = p.segs[e];
         const int nq = seg_num_qt(sg);
+        if (sg.wait_flag != 0) {
+          // lse / D of a staged segment are read with plain loads below: make sure they landed
+          int w_ok = 1;
+          if (lane == 0) w_ok = wait_staged(p.stage.flags, sg.wait_flag, sg.wait_count * p.stage.epoch, wc.budget_ns) ? 1 : 0;
+          w_ok = __shfl_sync(0xFFFFFFFFu, w_ok, 0);
+          if (!w_ok) { ok = false; break; }
+        }
         const float* lse_g = p.lse_ptr[sg.src] + batch * p.lse_batch_stride[sg.src] +
                              head * p.lse_head_stride[sg.src];
         const float* dv_g = p.dvec_ptr[sg.src] + batch * p.lse_batch_stride[sg.src] +
@@ -525,7 +547,9 @@ extern "C" int ua_attn_bwd(const UaTensorSrc* q_src, const UaTensorSrc* do_src,
                            const UaTensorSrc* v_src, int n_kv, const UaBwdKvOut* kv_out, int n_out,
                            const void* cols_dev, const void* segs_dev, const void* tiles_dev,
                            int n_tiles, int n_heads, int n_kv_heads, int batch,
-                           float softmax_scale, int* status, cudaStream_t stream) {
+                           float softmax_scale, int* status, const void* copy_tasks_dev,
+                           int n_copy_tasks, int n_copy_ctas, unsigned int* stage_flags,
+                           int stage_epoch, cudaStream_t stream) {
   if (n_q > ATTN_MAX_SRC || n_kv > ATTN_MAX_SRC || n_out > ATTN_MAX_SRC)
     UA_FAIL("ua_attn_bwd: too many sources (max %d)", ATTN_MAX_SRC);
   if (n_tiles <= 0) return 0;
@@ -571,6 +595,11 @@ extern "C" int ua_attn_bwd(const UaTensorSrc* q_src, const UaTensorSrc* do_src,
   p.scale = softmax_scale;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
+  p.stage.tasks = static_cast<const CopyTask*>(copy_tasks_dev);
+  p.stage.n_tasks = n_copy_tasks;
+  p.stage.n_copy_ctas = n_copy_ctas;
+  p.stage.flags = stage_flags;
+  p.stage.epoch = stage_epoch;
   const int smem_bytes = sizeof(BwdSmem) + 1024;
   int dev = 0;
   UA_CUDA(cudaGetDevice(&dev));

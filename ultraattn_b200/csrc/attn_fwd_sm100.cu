@@ -37,6 +37,8 @@ struct FwdRow {
   int o_slot;     // slot in the output tables
   int o_start;    // first output row inside that slot
   int accumulate; // 1: merge with the (O, lse) already stored there
+  int q_wait_flag;   // staging flag of the query block (0: in place), see AttnSeg::wait_flag
+  int q_wait_count;
 };
 
 struct FwdParams {
@@ -57,6 +59,7 @@ struct FwdParams {
   int kv_group;        // query heads per key/value head
   float scale_log2;    // softmax scale * log2(e)
   int* status;
+  StageParams stage;   // optional in-kernel staging of remote K/V (and Q) blocks
 };
 
 struct __align__(1024) FwdSmem {
@@ -95,6 +98,8 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+
+  run_stage_prologue(p.stage, blockIdx.y * gridDim.x + blockIdx.x);
 
   const int head = blockIdx.x / p.n_tiles;
   const int2 tl = p.tiles[blockIdx.x % p.n_tiles];
@@ -139,19 +144,28 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     if (lane == 0 && n_total > 0) {
       const CUtensorMap* tq = &p.tmQ[row.q_src];
       tma_prefetch_desc(tq);
-      for (int w = 0; w < 2; ++w) {
+      bool ok = true;
+      if (!wait_staged(p.stage.flags, row.q_wait_flag, row.q_wait_count * p.stage.epoch, wc.budget_ns)) {
+        report_error(wc, UA_ERR_FLAG_TIMEOUT, 110, row.q_wait_flag);
+        ok = false;
+      }
+      for (int w = 0; w < 2 && ok; ++w) {
         mbar_arrive_expect_tx(&s.q_full[w], FWD_TILE_BYTES);
         const int qrow = row.q_start + r0 + w * ATTN_TILE;
         tma_load_4d(s.q[w], tq, &s.q_full[w], 0, head, qrow, batch);
         tma_load_4d(s.q[w] + 16384, tq, &s.q_full[w], 64, head, qrow, batch);
       }
       uint32_t j = 0;
-      bool ok = true;
       for (int e = row.seg_begin; e < row.seg_end && ok; ++e) {
         const AttnSeg sg = p.segs[e];
         const int nt = seg_tiles(sg, r0, rows_here);
         const CUtensorMap* tk = &p.tmK[sg.src];
         const CUtensorMap* tv = &p.tmV[sg.src];
+        if (nt > 0 && !wait_staged(p.stage.flags, sg.wait_flag, sg.wait_count * p.stage.epoch, wc.budget_ns)) {
+          report_error(wc, UA_ERR_FLAG_TIMEOUT, 111, sg.wait_flag);
+          ok = false;
+          break;
+        }
         for (int t = 0; t < nt; ++t, ++j) {
           const int st = j % FWD_KV_STAGES;
           const uint32_t ph = (j / FWD_KV_STAGES) & 1;
@@ -437,7 +451,9 @@ extern "C" int ua_attn_fwd(const UaTensorSrc* q_src, int n_q, const UaTensorSrc*
                            const UaTensorSrc* v_src, int n_kv, const UaOutDst* outs, int n_out,
                            const void* rows_dev, const void* segs_dev, const void* tiles_dev,
                            int n_tiles, int n_heads, int n_kv_heads, int batch,
-                           float softmax_scale, int* status, cudaStream_t stream) {
+                           float softmax_scale, int* status, const void* copy_tasks_dev,
+                           int n_copy_tasks, int n_copy_ctas, unsigned int* stage_flags,
+                           int stage_epoch, cudaStream_t stream) {
   if (n_q > ATTN_MAX_SRC || n_kv > ATTN_MAX_SRC || n_out > ATTN_MAX_SRC)
     UA_FAIL("ua_attn_fwd: too many sources (max %d)", ATTN_MAX_SRC);
   if (n_tiles <= 0) return 0;
@@ -465,6 +481,11 @@ extern "C" int ua_attn_fwd(const UaTensorSrc* q_src, int n_q, const UaTensorSrc*
   p.kv_group = n_heads / n_kv_heads;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
+  p.stage.tasks = static_cast<const CopyTask*>(copy_tasks_dev);
+  p.stage.n_tasks = n_copy_tasks;
+  p.stage.n_copy_ctas = n_copy_ctas;
+  p.stage.flags = stage_flags;
+  p.stage.epoch = stage_epoch;
   const int smem_bytes = sizeof(FwdSmem) + 1024;
   int dev = 0;
   UA_CUDA(cudaGetDevice(&dev));

@@ -1,0 +1,109 @@
+// Device-side synchronisation between the GPUs of one NVSwitch domain over symmetric memory.
+//
+// ua_barrier: every rank writes an epoch number into its slot of every peer's signal pad (a
+// release store at system scope, travelling as a plain peer store over NVLink) and then waits
+// until all peers' epochs have arrived in its own pad. Epochs only grow, so the pads never need
+// resetting and a late reader cannot miss a signal. The wait is bounded: when the time budget
+// runs out the kernel records an error in the status word and returns, leaving the context
+// usable (the host raises). This replaces the reference's host-driven synchronisation — an 8 GiB
+// NCCL all-reduce issued only to line the ranks up before timing (search_algo/benchmark.py:593-594)
+// and 1-element warm-up all-reduces (tests/distributed/device_communicators/pynccl.py:195-199).
+//
+// ua_wait_flag: waits (bounded) for a single 32-bit flag; used by tests of the time-out path: a
+// flag that nothing sets makes the wait run out and the status word is checked on the host.
+#include "host_common.cuh"
+#include "ptx.cuh"
+
+namespace ua {
+
+constexpr int MAX_RANKS = 16;
+
+struct BarrierParams {
+  uint32_t* pads[MAX_RANKS];   // pads[r] = rank r's signal pad (peer-mapped addresses)
+  int rank;
+  int world;
+  int channel;                 // independent barriers use different channels
+  uint32_t epoch;
+  unsigned long long budget_ns;
+  int* status;
+};
+
+__global__ void barrier_kernel(const __grid_constant__ BarrierParams p) {
+  const int peer = threadIdx.x;
+  if (peer >= p.world) return;
+  // make this GPU's earlier writes (to local and peer memory) visible before the signal
+  __threadfence_system();
+  uint32_t* remote = p.pads[peer] + p.channel * MAX_RANKS + p.rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(p.epoch) : "memory");
+  const uint32_t* mine = p.pads[p.rank] + p.channel * MAX_RANKS + peer;
+  unsigned long long t0 = 0;
+  for (unsigned it = 0;; ++it) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (static_cast<int>(v - p.epoch) >= 0) break;
+    if ((it & 0x3F) == 0x3F) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > p.budget_ns) {
+        if (p.status != nullptr && atomicCAS(p.status, 0, UA_ERR_FLAG_TIMEOUT) == 0) {
+          p.status[1] = 900 + p.channel;
+          p.status[2] = peer;
+          p.status[3] = static_cast<int>(p.epoch);
+        }
+        return;
+      }
+    }
+    __nanosleep(100);
+  }
+  __threadfence_system();
+}
+
+__global__ void wait_flag_kernel(const uint32_t* flag, uint32_t target, unsigned long long budget_ns,
+                                 int* status) {
+  unsigned long long t0 = 0;
+  for (unsigned it = 0;; ++it) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (static_cast<int>(v - target) >= 0) return;
+    if ((it & 0x3F) == 0x3F) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > budget_ns) {
+        if (status != nullptr && atomicCAS(status, 0, UA_ERR_FLAG_TIMEOUT) == 0) {
+          status[1] = 950;
+          status[2] = 0;
+          status[3] = static_cast<int>(target);
+        }
+        return;
+      }
+    }
+    __nanosleep(100);
+  }
+}
+
+}  // namespace ua
+
+using namespace ua;
+
+// pads: host array of `world` device pointers (peer-mapped signal pads, >= 16*channels uint32 each)
+extern "C" int ua_barrier(void* const* pads, int rank, int world, int channel, unsigned epoch,
+                          double budget_s, int* status, cudaStream_t stream) {
+  if (world < 1 || world > MAX_RANKS) UA_FAIL("ua_barrier: world must be in [1, %d]", MAX_RANKS);
+  BarrierParams p;
+  memset(&p, 0, sizeof(p));
+  for (int i = 0; i < world; ++i) p.pads[i] = static_cast<uint32_t*>(pads[i]);
+  p.rank = rank; p.world = world; p.channel = channel; p.epoch = epoch;
+  p.budget_ns = static_cast<unsigned long long>(budget_s * 1e9);
+  p.status = status;
+  barrier_kernel<<<1, 32, 0, stream>>>(p);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ua_wait_flag(const void* flag, unsigned target, double budget_s, int* status,
+                            cudaStream_t stream) {
+  wait_flag_kernel<<<1, 1, 0, stream>>>(static_cast<const uint32_t*>(flag), target,
+                                        static_cast<unsigned long long>(budget_s * 1e9), status);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}

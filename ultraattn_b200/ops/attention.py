@@ -42,6 +42,8 @@ class Seg:
     length: int
     causal: bool = False
     diag: int = 0
+    wait_flag: int = 0       # 0: in place; f > 0: wait for staging flag f - 1 to reach wait_count
+    wait_count: int = 0
 
 
 @dataclass
@@ -56,6 +58,8 @@ class Row:
     o_slot: int = 0
     o_start: int = 0
     accumulate: bool = False
+    q_wait_flag: int = 0
+    q_wait_count: int = 0
 
 
 @dataclass
@@ -71,6 +75,20 @@ class Col:
     segs: Sequence[Seg]
     g_slot: int = 0
     g_start: int = 0
+    kv_wait_flag: int = 0
+    kv_wait_count: int = 0
+
+
+@dataclass
+class StagePlan:
+    """In-kernel staging prologue: ``tasks`` is an int64 device tensor [n, 4] of
+    (src pointer, dst pointer, number of 16-byte vectors, flag index); ``flags`` a uint32 device
+    tensor of monotonically increasing counters."""
+    tasks: torch.Tensor
+    n_tasks: int
+    n_copy_ctas: int
+    flags: torch.Tensor
+    epoch: int = 1
 
 
 def _seg_tiles(seg: Seg, r0: int, rows_here: int) -> int:
@@ -88,15 +106,15 @@ class FwdPlan:
 
     def __init__(self, rows: Sequence[Row], device: torch.device | str = "cpu"):
         self.rows = list(rows)
-        row_arr = np.zeros((max(len(self.rows), 1), 8), dtype=np.int32)
+        row_arr = np.zeros((max(len(self.rows), 1), 10), dtype=np.int32)
         segs = []
         tiles = []
         for ri, r in enumerate(self.rows):
             b = len(segs)
             for s in r.segs:
-                segs.append((s.src, s.start, s.length, int(s.causal), s.diag, 0, 0, 0))
+                segs.append((s.src, s.start, s.length, int(s.causal), s.diag, s.wait_flag, s.wait_count, 0))
             row_arr[ri] = (r.q_src, r.q_start, r.q_len, b, len(segs), r.o_slot, r.o_start,
-                           int(r.accumulate))
+                           int(r.accumulate), r.q_wait_flag, r.q_wait_count)
             for t in range((r.q_len + CTA_ROWS - 1) // CTA_ROWS):
                 r0 = t * CTA_ROWS
                 rows_here = min(CTA_ROWS, r.q_len - r0)
@@ -143,7 +161,8 @@ def _src_struct(t: torch.Tensor) -> _lib.UaTensorSrc:
 
 def attn_fwd_cuda(q_srcs: Sequence[torch.Tensor], k_srcs: Sequence[torch.Tensor],
                   v_srcs: Sequence[torch.Tensor], outs: Sequence[tuple[torch.Tensor, torch.Tensor]],
-                  plan: FwdPlan, softmax_scale: float | None = None) -> None:
+                  plan: FwdPlan, softmax_scale: float | None = None,
+                  stage: "StagePlan | None" = None) -> None:
     """Run the sm_100a forward. Tensors are ``[batch, tokens, heads, 128]`` bf16; each output is a
     pair ``(O [batch, tokens, heads, 128] bf16, lse [batch, heads, tokens] fp32)`` written in
     place."""
@@ -166,8 +185,16 @@ def attn_fwd_cuda(q_srcs: Sequence[torch.Tensor], k_srcs: Sequence[torch.Tensor]
     rc = lib.ua_attn_fwd(qs, len(q_srcs), ks, vs, len(k_srcs), ods, len(od),
                          plan.rows_t.data_ptr(), plan.segs_t.data_ptr(), plan.tiles_t.data_ptr(),
                          plan.n_tiles, n_heads, n_kv_heads, q0.shape[0], scale, st.data_ptr(),
+                         *_stage_args(stage),
                          torch.cuda.current_stream(q0.device).cuda_stream)
     _lib.check(rc, "ua_attn_fwd")
+
+
+def _stage_args(stage):
+    if stage is None:
+        return (None, 0, 0, None, 1)
+    return (stage.tasks.data_ptr() if stage.n_tasks else None, stage.n_tasks, stage.n_copy_ctas,
+            stage.flags.data_ptr(), stage.epoch)
 
 
 def _mask_for(seg: Seg, q_len: int, device) -> torch.Tensor | None:
@@ -225,11 +252,11 @@ def attn_fwd_reference(q_srcs, k_srcs, v_srcs, outs, rows: Sequence[Row],
         lse_t[:, :, osl] = lse.to(lse_t.dtype)
 
 
-def attn_fwd(q_srcs, k_srcs, v_srcs, outs, plan: FwdPlan, softmax_scale=None) -> None:
+def attn_fwd(q_srcs, k_srcs, v_srcs, outs, plan: FwdPlan, softmax_scale=None, stage=None) -> None:
     """Dispatch on the device of the inputs: CUDA tensors run the sm_100a kernel, CPU tensors the
-    fp32 restatement."""
+    fp32 restatement (which expects staged data to be in place already)."""
     if q_srcs[0].is_cuda:
-        attn_fwd_cuda(q_srcs, k_srcs, v_srcs, outs, plan, softmax_scale)
+        attn_fwd_cuda(q_srcs, k_srcs, v_srcs, outs, plan, softmax_scale, stage)
     else:
         attn_fwd_reference(q_srcs, k_srcs, v_srcs, outs, plan.rows, softmax_scale)
 
@@ -277,14 +304,15 @@ class BwdPlan:
 
     def __init__(self, cols: Sequence[Col], device: torch.device | str = "cpu"):
         self.cols = list(cols)
-        col_arr = np.zeros((max(len(self.cols), 1), 8), dtype=np.int32)
+        col_arr = np.zeros((max(len(self.cols), 1), 10), dtype=np.int32)
         segs = []
         tiles = []
         for ci, c in enumerate(self.cols):
             b = len(segs)
             for s in c.segs:
-                segs.append((s.src, s.start, s.length, int(s.causal), s.diag, 0, 0, 0))
-            col_arr[ci] = (c.kv_src, c.kv_start, c.kv_len, b, len(segs), c.g_slot, c.g_start, 0)
+                segs.append((s.src, s.start, s.length, int(s.causal), s.diag, s.wait_flag, s.wait_count, 0))
+            col_arr[ci] = (c.kv_src, c.kv_start, c.kv_len, b, len(segs), c.g_slot, c.g_start, 0,
+                           c.kv_wait_flag, c.kv_wait_count)
             for t in range((c.kv_len + TILE - 1) // TILE):
                 tiles.append((_col_steps(c, t * TILE), ci, t))
         tiles.sort(key=lambda x: -x[0])
@@ -322,7 +350,7 @@ class BwdKvOut:
 
 
 def attn_bwd_cuda(q_sides: Sequence[BwdQSide], k_srcs, v_srcs, kv_outs: Sequence[BwdKvOut],
-                  plan: BwdPlan, softmax_scale: float | None = None) -> None:
+                  plan: BwdPlan, softmax_scale: float | None = None, stage=None) -> None:
     lib = _lib.load()
     q0 = q_sides[0].q
     n_heads = q0.shape[2]
@@ -351,6 +379,7 @@ def attn_bwd_cuda(q_sides: Sequence[BwdQSide], k_srcs, v_srcs, kv_outs: Sequence
     rc = lib.ua_attn_bwd(qs, dos, sides, nq, ks, vs, len(k_srcs), kos, len(ko),
                          plan.cols_t.data_ptr(), plan.segs_t.data_ptr(), plan.tiles_t.data_ptr(),
                          plan.n_tiles, n_heads, n_kv_heads, q0.shape[0], scale, st.data_ptr(),
+                         *_stage_args(stage),
                          torch.cuda.current_stream(q0.device).cuda_stream)
     _lib.check(rc, "ua_attn_bwd")
 
@@ -401,9 +430,9 @@ def attn_bwd_reference(q_sides: Sequence[BwdQSide], k_srcs, v_srcs, kv_outs: Seq
             out.dv[:, gsl] = dv.to(out.dv.dtype)
 
 
-def attn_bwd(q_sides, k_srcs, v_srcs, kv_outs, plan: BwdPlan, softmax_scale=None) -> None:
+def attn_bwd(q_sides, k_srcs, v_srcs, kv_outs, plan: BwdPlan, softmax_scale=None, stage=None) -> None:
     if q_sides[0].q.is_cuda:
-        attn_bwd_cuda(q_sides, k_srcs, v_srcs, kv_outs, plan, softmax_scale)
+        attn_bwd_cuda(q_sides, k_srcs, v_srcs, kv_outs, plan, softmax_scale, stage)
     else:
         attn_bwd_reference(q_sides, k_srcs, v_srcs, kv_outs, plan.cols, softmax_scale)
 

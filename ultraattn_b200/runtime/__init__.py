@@ -1,1 +1,3 @@
+from .context_parallel import ContextParallelAttention, plan_allocation
 from .executor import FaultInjector, PlanExecutor
+from .fused import FakeSpace, FusedContextParallel, PeerSpace, SymmMemSpace

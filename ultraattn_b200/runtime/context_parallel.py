@@ -1,0 +1,98 @@
+"""User-facing context-parallel attention: plans once, then runs forward / backward per step.
+
+``path="fused"`` uses the peer-memory kernels of :mod:`ultraattn_b200.runtime.fused`;
+``path="nccl"`` executes the planner's launch plan with NCCL point-to-point messages
+(:mod:`ultraattn_b200.runtime.executor`) and is the baseline the fused path is measured against.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..patterns.blocks import BSA_Config, BSA_Repr
+from ..planner.allocate import naive_allocate_strategy, solve_sparse_from_bsa
+from ..planner.pipeline import make_plan
+
+
+def plan_allocation(pattern: BSA_Repr, cp: int, fob: int = 1, allocation: str = "ilp",
+                    time_limit: float = 20.0, cmap=None):
+    """(table, cmap) of the tile allocation for ``cp`` ranks."""
+    cfg = BSA_Config(None, None, {"bsa_repr": pattern, "CP": (cp, 1)})
+    if allocation == "naive":
+        al = naive_allocate_strategy(cfg, fob=fob)
+    else:
+        al = solve_sparse_from_bsa(cfg, fob=fob, time_limit=time_limit, cmap=cmap)
+    return np.asarray(al.table), np.asarray(al.cmap)
+
+
+class _CPFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, runtime, softmax_scale):
+        o, lse = runtime.forward(q, k, v, softmax_scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.runtime = runtime
+        ctx.scale = softmax_scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = ctx.runtime.backward(d_o.contiguous(), q, k, v, o, lse, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+class ContextParallelAttention:
+    """Context-parallel block-sparse attention over the ranks of ``group`` (one node).
+
+    Each rank passes its shard ``[B, S/CP, H, D]`` (the blocks it owns under the plan's ``cmap``,
+    in increasing block order; contiguous chunks by default) and receives the matching shard of
+    the output / gradients.
+    """
+
+    def __init__(self, pattern: BSA_Repr, seq_len: int, n_heads: int, head_dim: int = 128, *,
+                 group=None, device: Optional[torch.device] = None, path: str = "fused",
+                 n_kv_heads: Optional[int] = None, batch: int = 1, allocation: str = "ilp",
+                 plan_time_limit: float = 20.0, dtype=torch.bfloat16, cmap=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.path = path
+        self.pattern = pattern
+        if path == "fused":
+            from .fused import FusedContextParallel, SymmMemSpace
+            box = [plan_allocation(pattern, self.world, 1, allocation, plan_time_limit, cmap)
+                   if self.rank == 0 else None]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, 0), group=self.group)
+            table, cm = box[0]
+            self.table, self.cmap = table, cm
+            space = SymmMemSpace(self.group, self.device)
+            self.impl = FusedContextParallel(table, cm, pattern, seq_len, n_heads, head_dim, space,
+                                             n_kv_heads, batch, dtype, self.device)
+        elif path == "nccl":
+            from .executor import PlanExecutor
+            kw = dict(pattern=pattern, cp=self.world, seq_len=seq_len, n_heads=n_heads, head_dim=head_dim,
+                      n_kv_heads=n_kv_heads, batch=batch, allocation=allocation, plan_type="Flexflow",
+                      time_limit=plan_time_limit, cmap=cmap)
+            box = [(make_plan(fob=0, **kw), make_plan(fob=1, **kw)) if self.rank == 0 else None]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, 0), group=self.group)
+            pf, pb = box[0]
+            ranks = [dist.get_global_rank(self.group, r) for r in range(self.world)]
+            duplex = (dist.new_group(ranks), dist.new_group(ranks))
+            self.impl = PlanExecutor(pf, pb, group=self.group, device=self.device, p2p_groups=duplex)
+            self.table = np.asarray(pf.allocation.table)
+            self.cmap = np.asarray(pf.allocation.cmap)
+        else:
+            raise ValueError(f"unknown path {path!r}")
+
+    def forward(self, q, k, v, softmax_scale=None):
+        return self.impl.forward(q, k, v, softmax_scale)
+
+    def backward(self, d_o, q, k, v, o, lse, softmax_scale=None):
+        return self.impl.backward(d_o, q, k, v, o, lse, softmax_scale)
+
+    def __call__(self, q, k, v, softmax_scale=None):
+        return _CPFunction.apply(q, k, v, self, softmax_scale)

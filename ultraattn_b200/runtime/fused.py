@@ -1,0 +1,474 @@
+"""Context-parallel attention with the collectives fused into the attention kernels.
+
+Every rank keeps its shard of Q, K, V (and, for the backward, dO, lse, D) in *symmetric memory*:
+buffers allocated identically on all ranks and mapped into every peer's address space over
+NVLink. One forward call is then, per rank:
+
+    copy inputs into the symmetric buffers  ->  device barrier
+    ONE attention kernel: its first CTAs pull the remote K/V (and Q) blocks this rank's tiles
+        need from the peers' memory into local staging mirrors with plain peer loads (each
+        block crosses NVLink once) while the other CTAs already compute tiles whose inputs are
+        local; a tile that needs a staged block waits (bounded) on that block's flag; partial
+        (O, lse) of rows owned by a peer are stored by the epilogue straight into the owner's
+        mailbox through its peer mapping
+    device barrier  ->  owner merges its own partial with the mailbox slots (log-sum-exp merge)
+
+and one backward call is the mirror image: staging of Q / dO / lse / D and K / V blocks inside
+the backward kernel, dQ of foreign rows added into the owner's fp32 accumulator by TMA
+reduce-add through a tensor map over the peer mapping, dK / dV of foreign columns added with
+``red.global.add.v4.f32`` on peer pointers, barrier, cast of the own accumulators to bf16.
+
+Which rank computes which tile comes from the planner's tile-allocation program; the message
+kernels of the plan (reference: one NCCL send/recv per (row-or-column, peer),
+orchestrated_attn/utils.py:300-380, search_algo/dependent_graph.py:268-305) have no separate
+existence here — they are the staging prologue and the epilogues of the two kernels.
+
+``PeerSpace`` abstracts the symmetric memory so that the whole host-side logic (tables, slots,
+staging lists, merge lists) also runs on CPU with all ranks simulated in one process
+(:class:`FakeSpace`), which is how it is tested without GPUs.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+from ..ops import attention as A
+from ..ops import elementwise as E
+from ..patterns.blocks import BSA_Config, BSA_Repr, CAUSAL
+
+CHUNK_BYTES = 1 << 20       # staging granularity: one copy task moves at most this much
+MAX_COPY_CTAS = 148
+
+
+# =================================================================================================
+# peer spaces
+# =================================================================================================
+class PeerSpace:
+    rank: int
+    world: int
+
+    def alloc(self, name: str, shape, dtype) -> torch.Tensor: raise NotImplementedError
+    def finalize(self) -> None: raise NotImplementedError
+    def local(self, name: str) -> torch.Tensor: raise NotImplementedError
+    def peer(self, name: str, r: int) -> torch.Tensor: raise NotImplementedError
+    def barrier(self, channel: int) -> None: raise NotImplementedError
+
+
+class FakeSpace(PeerSpace):
+    """All ranks in one process on CPU; ``peer`` hands out the other rank's tensor itself."""
+
+    def __init__(self, rank: int, world: int, registry: dict, device="cpu"):
+        self.rank, self.world, self.registry, self.device = rank, world, registry, torch.device(device)
+
+    def alloc(self, name, shape, dtype):
+        t = torch.zeros(*shape, dtype=dtype, device=self.device)
+        self.registry[(self.rank, name)] = t
+        return t
+
+    def finalize(self): pass
+    def local(self, name): return self.registry[(self.rank, name)]
+    def peer(self, name, r): return self.registry[(r, name)]
+    def barrier(self, channel): pass
+
+
+class SymmMemSpace(PeerSpace):
+    """Symmetric memory of a process group (``torch.distributed._symmetric_memory`` as the
+    allocator front-end: CUDA VMM allocations exchanged between the ranks of one node). All
+    named buffers are carved out of one allocation, so one rendezvous maps everything."""
+
+    def __init__(self, group, device: torch.device, timeout_s: float = 20.0):
+        self.group = group
+        self.device = device
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.specs: list = []
+        self.offsets: dict = {}
+        self.total = 0
+        self.hdl = None
+        self.timeout_s = timeout_s
+        self.epochs: dict = {}
+        self._views: dict = {}
+
+    def alloc(self, name, shape, dtype):
+        n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+        self.offsets[name] = (self.total, tuple(shape), dtype)
+        self.total += (n + 255) // 256 * 256
+        return None
+
+    def finalize(self):
+        import torch.distributed._symmetric_memory as symm
+        self.heap = symm.empty(self.total, dtype=torch.uint8, device=self.device)
+        self.heap.zero_()
+        self.hdl = symm.rendezvous(self.heap, self.group)
+        torch.cuda.synchronize(self.device)
+        import ctypes
+        self._pads = (ctypes.c_void_p * self.world)(*[int(p) for p in self.hdl.signal_pad_ptrs])
+        dist.barrier(self.group)
+
+    def _view(self, r: int, name: str) -> torch.Tensor:
+        key = (r, name)
+        if key not in self._views:
+            off, shape, dtype = self.offsets[name]
+            es = torch.empty((), dtype=dtype).element_size()
+            self._views[key] = self.hdl.get_buffer(r, shape, dtype, off // es)
+        return self._views[key]
+
+    def local(self, name): return self._view(self.rank, name)
+    def peer(self, name, r): return self._view(r, name)
+
+    def barrier(self, channel: int) -> None:
+        """Device barrier on the current stream (bounded wait; errors land in the status word)."""
+        ep = self.epochs.get(channel, 0) + 1
+        self.epochs[channel] = ep
+        st = A.status_buffer(self.device)
+        rc = _lib.load().ua_barrier(self._pads, self.rank, self.world, channel, ep, self.timeout_s,
+                                    st.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check(rc, "ua_barrier")
+
+
+# =================================================================================================
+# the runtime
+# =================================================================================================
+class FusedContextParallel:
+    """Host-side state of the fused path for one (pattern, shape, group)."""
+
+    def __init__(self, table: np.ndarray, cmap: np.ndarray, pattern: BSA_Repr, seq_len: int,
+                 n_heads: int, head_dim: int, space: PeerSpace, n_kv_heads: Optional[int] = None,
+                 batch: int = 1, dtype=torch.bfloat16, device=None, defer_build: bool = False):
+        self.space = space
+        self.rank, self.world = space.rank, space.world
+        self.table = np.asarray(table)
+        self.cmap = np.asarray(cmap)
+        self.par_d = self.table.shape[0]
+        self.S, self.H, self.D = seq_len, n_heads, head_dim
+        self.Hk = n_kv_heads or n_heads
+        self.B = batch
+        self.dtype = dtype
+        self.device = torch.device(device) if device is not None else torch.device("cpu")
+        self.cuda = self.device.type == "cuda"
+        self.blk = seq_len // self.par_d
+        self.types = pattern.refined(self.par_d)
+        self.owned = {r: [i for i in range(self.par_d) if self.cmap[i] == r] for r in range(self.world)}
+        self.S_loc = len(self.owned[self.rank]) * self.blk
+        assert all(len(v) * self.blk == self.S_loc for v in self.owned.values()), "uneven shards"
+        self.lidx = {b: self.owned[int(self.cmap[b])].index(b) for b in range(self.par_d)}
+        g = self.rank
+        self.my_tiles = [(r, c) for r in range(self.par_d) for c in range(self.par_d) if self.table[r, c] == g]
+        self.my_rows = sorted({r for r, _ in self.my_tiles})
+        self.my_cols = sorted({c for _, c in self.my_tiles})
+        self.remote_rows = [r for r in self.my_rows if self.cmap[r] != g]
+        self.remote_cols = [c for c in self.my_cols if self.cmap[c] != g]
+        # mailbox slots of every owner: (row, contributor) pairs, contributor != owner
+        self.slots = {p: [] for p in range(self.world)}
+        for r in range(self.par_d):
+            p = int(self.cmap[r])
+            for contrib in sorted({int(x) for x in self.table[r] if x >= 0 and x != p}):
+                self.slots[p].append((r, contrib))
+        self.max_slots = max(1, max(len(v) for v in self.slots.values()))
+        self.fwd_calls = 0
+        self.bwd_calls = 0
+        self._alloc()
+        if not defer_build:
+            self.build()
+
+    def build(self) -> None:
+        """Build the launch tables (needs every rank's buffers to exist)."""
+        self._build_fwd()
+        self._build_bwd()
+
+    # ------------------------------- buffers ----------------------------------------------------
+    def _alloc(self) -> None:
+        sp, B, S, H, Hk, D, dt = self.space, self.B, self.S_loc, self.H, self.Hk, self.D, self.dtype
+        for name, shape, dtype in [
+            ("q", (B, S, H, D), dt), ("k", (B, S, Hk, D), dt), ("v", (B, S, Hk, D), dt),
+            ("do", (B, S, H, D), dt), ("lse", (B, H, S), torch.float32), ("dvec", (B, H, S), torch.float32),
+            ("mail_o", (B, self.max_slots * self.blk, H, D), dt),
+            ("mail_lse", (B, H, self.max_slots * self.blk), torch.float32),
+            ("dq_acc", (B, S, H, D), torch.float32), ("dk_acc", (B, S, Hk, D), torch.float32),
+            ("dv_acc", (B, S, Hk, D), torch.float32),
+        ]:
+            sp.alloc(name, shape, dtype)
+        sp.finalize()
+        dev = self.device
+        peers_rows = sorted({int(self.cmap[r]) for r in self.remote_rows})
+        peers_cols = sorted({int(self.cmap[c]) for c in self.remote_cols})
+        self.mir = {}
+        for p in peers_rows:
+            self.mir[("q", p)] = torch.zeros(B, S, H, D, dtype=dt, device=dev)
+            self.mir[("do", p)] = torch.zeros(B, S, H, D, dtype=dt, device=dev)
+            self.mir[("lse", p)] = torch.zeros(B, H, S, dtype=torch.float32, device=dev)
+            self.mir[("dvec", p)] = torch.zeros(B, H, S, dtype=torch.float32, device=dev)
+        for p in peers_cols:
+            self.mir[("k", p)] = torch.zeros(B, S, Hk, D, dtype=dt, device=dev)
+            self.mir[("v", p)] = torch.zeros(B, S, Hk, D, dtype=dt, device=dev)
+        self.peers_rows, self.peers_cols = peers_rows, peers_cols
+
+    def _tok(self, blk_id: int) -> slice:
+        i = self.lidx[blk_id]
+        return slice(i * self.blk, (i + 1) * self.blk)
+
+    # ------------------------------- staging lists ----------------------------------------------
+    def _stage_list(self, kinds_rows: Sequence[str], kinds_cols: Sequence[str]):
+        """[(flag id, src view, dst view)] of contiguous pieces, and pieces-per-flag counts."""
+        pieces = []
+        for r in self.remote_rows:
+            p = int(self.cmap[r])
+            for kind in kinds_rows:
+                src, dst = self.space.peer(kind, p), self.mir[(kind, p)]
+                if kind in ("lse", "dvec"):
+                    for b in range(self.B):
+                        for h in range(self.H):
+                            pieces.append((r, src[b, h, self._tok(r)], dst[b, h, self._tok(r)]))
+                else:
+                    for b in range(self.B):
+                        pieces.append((r, src[b, self._tok(r)], dst[b, self._tok(r)]))
+        for c in self.remote_cols:
+            p = int(self.cmap[c])
+            for kind in kinds_cols:
+                src, dst = self.space.peer(kind, p), self.mir[(kind, p)]
+                for b in range(self.B):
+                    pieces.append((self.par_d + c, src[b, self._tok(c)], dst[b, self._tok(c)]))
+        return pieces
+
+    def _device_tasks(self, pieces):
+        """Chunk the pieces into copy tasks; returns (StagePlan or None, chunks per flag)."""
+        counts = {}
+        rows = []
+        for flag, src, dst in pieces:
+            assert src.is_contiguous() and dst.is_contiguous()
+            nbytes = src.numel() * src.element_size()
+            assert nbytes % 16 == 0 and src.data_ptr() % 16 == 0 and dst.data_ptr() % 16 == 0
+            off = 0
+            while off < nbytes:
+                n = min(CHUNK_BYTES, nbytes - off)
+                rows.append((src.data_ptr() + off, dst.data_ptr() + off, n // 16, flag))
+                counts[flag] = counts.get(flag, 0) + 1
+                off += n
+        return rows, counts
+
+    def _make_stage(self, pieces):
+        if not self.cuda:
+            counts = {}
+            for flag, _, _ in pieces:
+                counts[flag] = counts.get(flag, 0) + 1
+            return None, counts
+        rows, counts = self._device_tasks(pieces)
+        flags = torch.zeros(2 * self.par_d + 1, dtype=torch.int32, device=self.device)
+        if rows:
+            # interleave tasks of different blocks so that blocks complete in parallel
+            tasks = torch.tensor(rows, dtype=torch.int64).to(self.device)
+        else:
+            tasks = torch.zeros(1, 4, dtype=torch.int64, device=self.device)
+        stage = A.StagePlan(tasks, len(rows), min(MAX_COPY_CTAS, max(1, len(rows))), flags, 0)
+        return stage, counts
+
+    # ------------------------------- forward tables ---------------------------------------------
+    def _build_fwd(self) -> None:
+        g = self.rank
+        self.f_pieces = self._stage_list(["q"], ["k", "v"])
+        self.f_stage, counts = self._make_stage(self.f_pieces)
+        q_src = {g: 0}
+        for p in self.peers_rows:
+            q_src[p] = len(q_src)
+        kv_src = {g: 0}
+        for p in self.peers_cols:
+            kv_src[p] = len(kv_src)
+        out_slot = {g: 0}
+        for p in self.peers_rows:
+            out_slot[p] = len(out_slot)
+        self.f_q_src, self.f_kv_src, self.f_out_slot = q_src, kv_src, out_slot
+        assert max(len(q_src), len(kv_src), len(out_slot)) <= 10
+        rows = []
+        for r in self.my_rows:
+            p = int(self.cmap[r])
+            segs = []
+            cols = [c for (rr, c) in self.my_tiles if rr == r]
+            cols.sort(key=lambda c: (self.cmap[c] != g, c))        # local key blocks first
+            for c in cols:
+                pc = int(self.cmap[c])
+                remote = pc != g
+                segs.append(A.Seg(kv_src[pc], self.lidx[c] * self.blk, self.blk,
+                                  self.types[r, c] == CAUSAL, 0,
+                                  (self.par_d + c + 1) if remote else 0,
+                                  counts.get(self.par_d + c, 0) if remote else 0))
+            if p == g:
+                o_start = self.lidx[r] * self.blk
+            else:
+                o_start = self.slots[p].index((r, g)) * self.blk
+            rows.append(A.Row(q_src[p], self.lidx[r] * self.blk, self.blk, tuple(segs), out_slot[p],
+                              o_start, False, (r + 1) if p != g else 0, counts.get(r, 0) if p != g else 0))
+        # rows whose inputs are all local first: they can start while the staging runs
+        rows.sort(key=lambda row: (row.q_wait_flag != 0) + sum(s.wait_flag != 0 for s in row.segs))
+        self.f_rows = rows
+        self.f_plan = A.FwdPlan(rows, self.device)
+        # merge lists for own rows
+        self.f_merge = []
+        for r in self.owned[g]:
+            own = any(rr == r for rr, _ in self.my_tiles)
+            slots = [i for i, (row, _) in enumerate(self.slots[g]) if row == r]
+            if slots or not own:
+                self.f_merge.append((r, own, slots))
+
+    # ------------------------------- backward tables --------------------------------------------
+    def _build_bwd(self) -> None:
+        g = self.rank
+        self.b_pieces = self._stage_list(["do", "lse", "dvec"], [])     # q / k / v mirrors come from the forward
+        self.b_pieces_full = self._stage_list(["q", "do", "lse", "dvec"], ["k", "v"])
+        self.b_stage, counts = self._make_stage(self.b_pieces)
+        self.b_stage_full, counts_full = self._make_stage(self.b_pieces_full)
+        self.b_counts = (counts, counts_full)
+        q_src = {g: 0}
+        for p in self.peers_rows:
+            q_src[p] = len(q_src)
+        kv_src = {g: 0}
+        for p in self.peers_cols:
+            kv_src[p] = len(kv_src)
+        self.b_q_src, self.b_kv_src = q_src, kv_src
+        self.b_plans = []
+        for cnt in (counts, counts_full):
+            cols = []
+            for c in self.my_cols:
+                pc = int(self.cmap[c])
+                rows = [r for (r, cc) in self.my_tiles if cc == c]
+                rows.sort(key=lambda r: (self.cmap[r] != g, r))
+                segs = []
+                for r in rows:
+                    pr = int(self.cmap[r])
+                    remote = pr != g
+                    segs.append(A.Seg(q_src[pr], self.lidx[r] * self.blk, self.blk,
+                                      self.types[r, c] == CAUSAL, 0,
+                                      (r + 1) if remote else 0, cnt.get(r, 0) if remote else 0))
+                kv_remote = pc != g
+                kv_cnt = cnt.get(self.par_d + c, 0)
+                cols.append(A.Col(kv_src[pc], self.lidx[c] * self.blk, self.blk, tuple(segs), kv_src[pc],
+                                  self.lidx[c] * self.blk,
+                                  (self.par_d + c + 1) if (kv_remote and kv_cnt) else 0, kv_cnt if kv_remote else 0))
+            self.b_plans.append(A.BwdPlan(cols, self.device))
+            self.b_cols = cols
+
+    # =============================== forward ====================================================
+    def fwd_prepare(self, q, k, v) -> None:
+        sp = self.space
+        sp.local("q").copy_(q)
+        sp.local("k").copy_(k)
+        sp.local("v").copy_(v)
+
+    def stage_on_host(self, pieces) -> None:
+        """CPU stand-in of the in-kernel staging prologue."""
+        for _, src, dst in pieces:
+            dst.copy_(src)
+
+    def fwd_compute(self, softmax_scale=None):
+        sp, g = self.space, self.rank
+        B, S, H, D = self.B, self.S_loc, self.H, self.D
+        o = torch.zeros(B, S, H, D, dtype=self.dtype, device=self.device)
+        lse = torch.full((B, H, S), float("-inf"), dtype=torch.float32, device=self.device)
+        q_srcs = [None] * len(self.f_q_src)
+        k_srcs = [None] * len(self.f_kv_src)
+        v_srcs = [None] * len(self.f_kv_src)
+        outs = [None] * len(self.f_out_slot)
+        for p, i in self.f_q_src.items():
+            q_srcs[i] = sp.local("q") if p == g else self.mir[("q", p)]
+        for p, i in self.f_kv_src.items():
+            k_srcs[i] = sp.local("k") if p == g else self.mir[("k", p)]
+            v_srcs[i] = sp.local("v") if p == g else self.mir[("v", p)]
+        for p, i in self.f_out_slot.items():
+            outs[i] = (o, lse) if p == g else (sp.peer("mail_o", p), sp.peer("mail_lse", p))
+        self.fwd_calls += 1
+        if self.f_stage is not None:
+            self.f_stage.epoch = self.fwd_calls
+        A.attn_fwd(q_srcs, k_srcs, v_srcs, outs, self.f_plan, softmax_scale, self.f_stage)
+        return o, lse
+
+    def fwd_finish(self, o, lse) -> None:
+        sp = self.space
+        mo, ml = sp.local("mail_o"), sp.local("mail_lse")
+        for r, own, slots in self.f_merge:
+            tok = self._tok(r)
+            for b in range(self.B):
+                parts = [(o[b, tok], lse[b, :, tok])] if own else []
+                for s in slots:
+                    ms = slice(s * self.blk, (s + 1) * self.blk)
+                    parts.append((mo[b, ms], ml[b, :, ms]))
+                if parts:
+                    E.lse_merge(parts, (o[b, tok], lse[b, :, tok]))
+
+    def forward(self, q, k, v, softmax_scale=None):
+        self.fwd_prepare(q, k, v)
+        self.space.barrier(0)
+        if not self.cuda:
+            self.stage_on_host(self.f_pieces)
+        o, lse = self.fwd_compute(softmax_scale)
+        self.space.barrier(1)
+        self.fwd_finish(o, lse)
+        self._staged_inputs = True
+        return o, lse
+
+    # =============================== backward ===================================================
+    def bwd_prepare(self, d_o, q, k, v, o, lse, reuse_inputs: bool) -> None:
+        sp = self.space
+        if not reuse_inputs:
+            sp.local("q").copy_(q)
+            sp.local("k").copy_(k)
+            sp.local("v").copy_(v)
+        sp.local("do").copy_(d_o)
+        sp.local("lse").copy_(lse)
+        dvec = sp.local("dvec")
+        for b in range(self.B):
+            E.rowdot(o[b], d_o[b], dvec[b])
+
+    def bwd_compute(self, reuse_inputs: bool, softmax_scale=None) -> None:
+        sp, g = self.space, self.rank
+        sides = [None] * len(self.b_q_src)
+        for p, i in self.b_q_src.items():
+            if p == g:
+                sides[i] = A.BwdQSide(sp.local("q"), sp.local("do"), sp.local("lse"), sp.local("dvec"),
+                                      sp.local("dq_acc"))
+            else:
+                sides[i] = A.BwdQSide(self.mir[("q", p)], self.mir[("do", p)], self.mir[("lse", p)],
+                                      self.mir[("dvec", p)], sp.peer("dq_acc", p))
+        k_srcs = [None] * len(self.b_kv_src)
+        v_srcs = [None] * len(self.b_kv_src)
+        outs = [None] * len(self.b_kv_src)
+        for p, i in self.b_kv_src.items():
+            k_srcs[i] = sp.local("k") if p == g else self.mir[("k", p)]
+            v_srcs[i] = sp.local("v") if p == g else self.mir[("v", p)]
+            outs[i] = A.BwdKvOut(sp.local("dk_acc") if p == g else sp.peer("dk_acc", p),
+                                 sp.local("dv_acc") if p == g else sp.peer("dv_acc", p))
+        self.bwd_calls += 1
+        which = 0 if reuse_inputs else 1
+        stage = self.b_stage if reuse_inputs else self.b_stage_full
+        if stage is not None:
+            # each of the two staging variants has its own flag counters and call count
+            stage.epoch += 1
+        A.attn_bwd(sides, k_srcs, v_srcs, outs, self.b_plans[which], softmax_scale, stage)
+
+    def bwd_finish(self):
+        sp = self.space
+        outs = []
+        for name, like in (("dq_acc", (self.B, self.S_loc, self.H, self.D)),
+                           ("dk_acc", (self.B, self.S_loc, self.Hk, self.D)),
+                           ("dv_acc", (self.B, self.S_loc, self.Hk, self.D))):
+            acc = sp.local(name)
+            out = torch.empty(like, dtype=self.dtype, device=self.device)
+            E.cast_scale(acc, out)
+            acc.zero_()
+            outs.append(out)
+        return tuple(outs)
+
+    def backward(self, d_o, q, k, v, o, lse, softmax_scale=None, reuse_inputs: Optional[bool] = None):
+        reuse = bool(getattr(self, "_staged_inputs", False)) if reuse_inputs is None else reuse_inputs
+        self.bwd_prepare(d_o, q, k, v, o, lse, reuse)
+        self.space.barrier(2)
+        if not self.cuda:
+            self.stage_on_host(self.b_pieces if reuse else self.b_pieces_full)
+        self.bwd_compute(reuse, softmax_scale)
+        self.space.barrier(3)
+        res = self.bwd_finish()
+        self._staged_inputs = False
+        return res
