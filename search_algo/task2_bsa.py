@@ -1,0 +1,9 @@
+"""Campaign step 4 (reference: search_algo/task2_bsa.py). ``python search_algo/task2_bsa.py --exp-class X``"""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from ultraattn_b200.drivers.task2 import main  # noqa: E402,F401
+
+if __name__ == "__main__":
+    main()
