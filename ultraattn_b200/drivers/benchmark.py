@@ -1,0 +1,91 @@
+"""Measurement harness of the campaign (reference: search_algo/benchmark.py:85-229, 336-619).
+
+``benchmark_ops`` times a callable: warm-up, then ``num_iter`` calls bracketed by CUDA events on the
+launching stream (wall clock on CPU ranks), repeated ``repeats`` times, last value kept, MAX over
+ranks. The reference lines the ranks up with an 8 GiB NCCL all-reduce before each timing
+(benchmark.py:593-594); a barrier plus device synchronisation does the same job here.
+Optional torch.profiler -> TensorBoard traces follow the reference's schedule (wait 4, warm-up 4,
+active 12).
+"""
+from __future__ import annotations
+
+import time
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..utils.misc import calc_flops
+
+
+def benchmark_ops(fn: Callable[[], object], warmup: int = 3, num_iter: int = 4, repeats: int = 3,
+                  device: Optional[torch.device] = None, group=None, tb_dir: Optional[str] = None,
+                  trace_name: str = "trace") -> float:
+    """Seconds per call, max over the ranks of ``group``."""
+    cuda = device is not None and device.type == "cuda"
+
+    def sync():
+        if dist.is_initialized():
+            dist.barrier(group)
+        if cuda:
+            torch.cuda.synchronize(device)
+
+    for _ in range(warmup):
+        fn()
+    if tb_dir:
+        from torch.profiler import ProfilerActivity, profile, schedule, tensorboard_trace_handler
+        acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if cuda else [])
+        with profile(activities=acts, schedule=schedule(wait=4, warmup=4, active=12, repeat=1),
+                     on_trace_ready=tensorboard_trace_handler(tb_dir, worker_name=trace_name),
+                     record_shapes=True, profile_memory=True, with_stack=True) as prof:
+            for i in range(20):
+                fn()
+                if i % 4 == 3:
+                    sync()
+                prof.step()
+    td = 0.0
+    for _ in range(repeats):
+        sync()
+        if cuda:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(num_iter):
+                fn()
+            e1.record()
+            sync()
+            td = e0.elapsed_time(e1) / 1e3 / num_iter
+        else:
+            t0 = time.perf_counter()
+            for _ in range(num_iter):
+                fn()
+            sync()
+            td = (time.perf_counter() - t0) / num_iter
+    if dist.is_initialized():
+        t = torch.tensor([td], dtype=torch.float64, device=device if cuda else "cpu")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        td = float(t.item())
+    return td
+
+
+def benchmark_orchestrate_bsa(plan_fwd, plan_bwd, fob: int, device: torch.device, group=None,
+                              dtype=None, warmup: int = 2, num_iter: int = 2, repeats: int = 2,
+                              p2p_groups=None, tb_dir=None) -> dict:
+    """Execute a plan on the ranks of ``group`` with random inputs and time the pass ``fob``.
+    Returns {'time': s, 'hfu': TFLOP/s per rank, 'sim_time': the plan's predicted makespan}."""
+    from ..runtime.executor import PlanExecutor
+    da = plan_fwd.da_config
+    dtype = dtype or (torch.bfloat16 if device.type == "cuda" else torch.float32)
+    ex = PlanExecutor(plan_fwd, plan_bwd, group=group, device=device, p2p_groups=p2p_groups)
+    S_loc = da.S[0] // ex.cp
+    g = torch.Generator(device="cpu").manual_seed(ex.rank)
+    mk = lambda h: torch.randn(da.bs, S_loc, h, da.D, generator=g).to(dtype).to(device)
+    q, k, v, d_o = mk(da.Nh[0]), mk(da.Nh[1]), mk(da.Nh[1]), mk(da.Nh[0])
+    o, lse = ex.forward(q, k, v)
+    if fob == 0:
+        fn = lambda: ex.forward(q, k, v)
+    else:
+        fn = lambda: ex.backward(d_o, q, k, v, o, lse)
+    t = benchmark_ops(fn, warmup, num_iter, repeats, device, group, tb_dir)
+    _, hw = calc_flops(da.bs, da.S, da.Nh[0], da.D, False, fob, da.bsa_config.total_sparsity)
+    plan = plan_fwd if fob == 0 else plan_bwd
+    return {"time": t, "hfu": hw / t / ex.cp / 1e12, "sim_time": float(plan.end_time)}

@@ -1,0 +1,149 @@
+"""Campaign steps 0-3: decompose -> intra-node plans -> profile them -> inter-node plans.
+
+Reference pipeline: search_algo/task1_bsa.py:901-949 (``main``), :581 (step 1), :699 (step 2),
+:781 (step 3). Everything is keyed in the plan database, so an interrupted campaign resumes where
+it stopped ("Bypassed" entries are skipped).
+
+    torchrun --nproc-per-node 8 search_algo/task1_bsa.py --exp-class bsa_train [--quick]
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.comm import initialize_distribution
+from ..plandb import ABLATION_SUFFIXES, Prof_DB, allocation_key, plan_key_prefix
+from ..planner.allocate import naive_allocate_strategy, solve_sparse_from_bsa
+from ..planner.cost import Dist_Attn_Config, get_cc_optimal_schedule_from_table
+from ..planner.fuse import Graph_Transformation_Engine
+from ..planner.graph import Dependent_Graph
+from ..planner.schedule import Execution_Plan
+from ..utils.misc import print_rank_0
+from .arguments import parse_args
+from .benchmark import benchmark_orchestrate_bsa
+from .exp_configs import step0_top_down_decompose
+
+
+def get_general_bsa_cc_optimal_schedule(fob, da_config, prof_db, gpu_tile_type=None, time_limit=60.0):
+    """Allocation (ILP #1 or the row-owner ablation) with database caching."""
+    hier = da_config.hierarchy
+    key = allocation_key(fob, da_config.bsa_config, gpu_tile_type)
+    hit = prof_db.get_allocation(key, hier)
+    if hit is not None:
+        print_rank_0(f"allocation {key}: bypassed")
+        cp = da_config.bsa_config.CP[0 if hier else 1]
+        par_d = hit["Par_D"]
+        import numpy as np
+        hit["cmap"] = np.arange(par_d) // max(1, par_d // cp)
+        res = hit
+    else:
+        fn = naive_allocate_strategy if gpu_tile_type == "naive" else solve_sparse_from_bsa
+        kw = {} if gpu_tile_type == "naive" else {"time_limit": time_limit}
+        res = fn(da_config.bsa_config, fob=fob, hierarchy=hier, **kw)
+        prof_db.put_allocation(key, res["table"], hier)
+    return get_cc_optimal_schedule_from_table(da_config, prof_db.m_config, res)
+
+
+def generate_bsa_execution_plans(fob, bsa_config, shape_config, prof_db, hierarchy=1, time_limit=20.0) -> list:
+    """The five ablation plans of one (pattern, shape, pass); returns the keys written."""
+    da = Dist_Attn_Config.from_bsa_config(bsa_config, shape_config, hierarchy)
+    prefix = plan_key_prefix(fob, bsa_config.CP, shape_config, bsa_config)
+    keys = [prefix + s for s in ABLATION_SUFFIXES]
+    if all(prof_db.has_plan(k, hierarchy) for k in keys):
+        print_rank_0(f"plans {prefix}: bypassed")
+        return keys
+    naive = get_general_bsa_cc_optimal_schedule(fob, da, prof_db, "naive")
+    tiled = get_general_bsa_cc_optimal_schedule(fob, da, prof_db, None, time_limit)
+    g_naive = Dependent_Graph(naive, fob)
+    g_tiled = Dependent_Graph(tiled, fob)
+    eng = Graph_Transformation_Engine(None, da, prof_db.m_config)
+    plans = [
+        Execution_Plan(g_naive, fob, "Flexflow"),
+        Execution_Plan(Dependent_Graph(tiled, fob), fob, "Flexflow"),
+        eng.transform(g_tiled, "greedy", "Flexflow", time_limit=time_limit),
+        Execution_Plan(Dependent_Graph(tiled, fob), fob, "ILP", time_limit=time_limit),
+        eng.transform(g_tiled, "greedy", "ILP", time_limit=time_limit),
+    ]
+    for k, p in zip(keys, plans):
+        problems = p.verify()
+        assert not problems, (k, problems)
+        prof_db.put_plan(k, p, hierarchy)
+    return keys
+
+
+def step1_generate_intra_bsa_exe_plans(space, prof_db, time_limit=20.0) -> list:
+    work = []
+    for fob in space.fobs:
+        for cfg in space.intra_bsa_configs:
+            for shape in space.shape_configs(cfg.CP[0]):
+                work.append((fob, cfg, shape))
+    if not dist.is_initialized() or dist.get_rank() == 0:
+        for fob, cfg, shape in work:
+            generate_bsa_execution_plans(fob, cfg, shape, prof_db, 1, time_limit)
+    if dist.is_initialized():
+        dist.barrier()
+    return work
+
+
+def step2_profile_intra_bsa_exe_plans(work, prof_db, device, world: int) -> None:
+    """Measure every stored intra plan whose CP equals the number of ranks running now."""
+    for fob, cfg, shape in work:
+        if cfg.CP[0] != world:
+            continue
+        prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
+        for suf in ABLATION_SUFFIXES:
+            key = prefix + suf
+            if prof_db.get_profile(key, 1) is not None:
+                continue
+            plan = prof_db.get_plan(key, 1)
+            other = prof_db.get_plan(plan_key_prefix(0, cfg.CP, shape, cfg) + suf, 1) if fob == 1 else plan
+            res = benchmark_orchestrate_bsa(other, plan if fob == 1 else None, fob, device)
+            if not dist.is_initialized() or dist.get_rank() == 0:
+                prof_db.put_profile(key, res["hfu"], res["time"], res["sim_time"], 1)
+            if dist.is_initialized():
+                dist.barrier()
+
+
+def step3_generate_inter_bsa_exe_plans(space, prof_db, time_limit=20.0) -> list:
+    prof_db.m_config_update_inter_bsa_profile()
+    work = []
+    for fob in space.fobs:
+        for cfg in space.inter_bsa_configs:
+            if cfg.CP[1] == 1:
+                continue            # single node: the intra plan is the whole plan
+            for shape in space.shape_configs(cfg.CP[0] * cfg.CP[1]):
+                work.append((fob, cfg, shape))
+    if not dist.is_initialized() or dist.get_rank() == 0:
+        for fob, cfg, shape in work:
+            da = Dist_Attn_Config.from_bsa_config(cfg, shape, 0)
+            prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
+            tiled = get_general_bsa_cc_optimal_schedule(fob, da, prof_db, None, time_limit)
+            for suf in ABLATION_SUFFIXES:
+                g = Dependent_Graph(tiled, fob, bsa_comp_key_suffixes=[suf])
+                prof_db.put_plan(prefix + suf, Execution_Plan(g, fob, "ILP" if "ILP" in suf else "Flexflow",
+                                                              time_limit=time_limit), 0)
+    if dist.is_initialized():
+        dist.barrier()
+    return work
+
+
+def main(argv=None) -> None:
+    args = parse_args(argv)
+    info = initialize_distribution()
+    quick = bool(args.extra.get("quick"))
+    prof_db = Prof_DB(os.environ.get("CLUSTER_NAME"), os.environ.get("PLATFORM"))
+    space = step0_top_down_decompose(args.exp_class or "bsa_train", max_intra=info["tasks_per_node"],
+                                     max_nodes=info["node_num"], quick=quick)
+    work = step1_generate_intra_bsa_exe_plans(space, prof_db)
+    device = torch.device("cuda", info["local_rank"]) if torch.cuda.is_available() else torch.device("cpu")
+    step2_profile_intra_bsa_exe_plans(work, prof_db, device, info["world_size"])
+    step3_generate_inter_bsa_exe_plans(space, prof_db)
+    print_rank_0("task1 done")
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
