@@ -1,0 +1,321 @@
+"""A Llama-2 style decoder built on this framework's kernels, for the end-to-end training step.
+
+The reference has no model, trainer or optimizer: its "end-to-end Llama2-7B" numbers are attention
+time times the layer count plus a hard-coded constant for everything else (plot/e2e_pick.py:13-31,
+144-177), and its model glue only patches HuggingFace attention modules
+(easy_context/zigzag_ring_attn/monkey_patch.py:9-113). This module is the real thing at the same
+architecture: RMSNorm -> QKV projection -> RoPE -> block-sparse (optionally context-parallel)
+attention -> output projection -> RMSNorm -> SwiGLU FFN, tied together with
+
+  * tcgen05 GEMMs for every projection (forward, dX and dW without transposes),
+  * hand-written RMSNorm / RoPE / SwiGLU kernels,
+  * attention-aware activation checkpointing: a layer keeps only its input and the attention
+    output (O, lse); the backward recomputes the cheap projections but never the attention
+    forward (the idea of the reference's CheckpointFunctionEndWithFlashAttention,
+    easy_context/dist_flash_attn/monkey_patch.py:78-207),
+  * fp32 Adam on a flat master copy, sharded over the context-parallel ranks (ZeRO-1: gradients
+    reduce-scattered, parameters all-gathered),
+  * a chunked cross-entropy so that the [tokens, vocab] logits never exist at once.
+
+On CPU tensors every op falls back to its fp32 PyTorch restatement, which is how small-shape
+parity against a plain PyTorch model is tested without a GPU.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from .. import api
+from ..ops import elementwise as E
+from ..ops import gemm as G
+from ..patterns.blocks import BSA_Repr
+
+
+@dataclass
+class LlamaConfig:
+    n_layers: int = 32
+    hidden: int = 4096
+    n_heads: int = 32
+    head_dim: int = 128
+    ffn: int = 11008
+    vocab: int = 32000
+    n_kv_heads: Optional[int] = None
+    rope_base: float = 10000.0
+    eps: float = 1e-5
+    init_std: float = 0.02
+
+    @property
+    def kv_heads(self) -> int:
+        return self.n_kv_heads or self.n_heads
+
+    @classmethod
+    def llama2_7b(cls) -> "LlamaConfig":
+        return cls()
+
+
+# ------------------------------- differentiable ops over the kernels -----------------------------
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return G.gemm(x, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = G.gemm(dy, w, b_is_kn=True)                       # dy[M,N] @ w[N,K]
+        dw = G.gemm(dy, x, a_is_km=True, b_is_kn=True)          # dy^T[N,M] @ x[M,K]
+        return dx, dw
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        y, rstd = E.rmsnorm_fwd(x, w, eps)
+        ctx.save_for_backward(x, w, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w, rstd = ctx.saved_tensors
+        dx, dw = E.rmsnorm_bwd(x, w, g.contiguous(), rstd)
+        return dx, dw.to(w.dtype), None
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, pos):
+        ctx.save_for_backward(cos, sin, pos)
+        return E.rope(x, cos, sin, pos)
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin, pos = ctx.saved_tensors
+        return E.rope(g.contiguous(), cos, sin, pos, inverse=True), None, None, None
+
+
+class _Swiglu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        ctx.save_for_backward(gu)
+        return E.swiglu_fwd(gu)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (gu,) = ctx.saved_tensors
+        return E.swiglu_bwd(gu, dy.contiguous())
+
+
+def _rope_any(x, cos, sin, pos, head_dim):
+    """RoPE on [T, H, D]; the kernel handles D = 128, other head dims use the fp32 restatement."""
+    if x.is_cuda and head_dim == 128:
+        return _Rope.apply(x, cos, sin, pos)
+    half = head_dim // 2
+    c = cos[pos.long()][:, None, :]
+    s = sin[pos.long()][:, None, :]
+    lo, hi = x[..., :half].float(), x[..., half:].float()
+    return torch.cat([lo * c - hi * s, hi * c + lo * s], dim=-1).to(x.dtype)
+
+
+class _Layer(torch.autograd.Function):
+    """One decoder layer with attention-aware checkpointing."""
+
+    @staticmethod
+    def forward(ctx, x, model, li):
+        with torch.no_grad():
+            q, k, v = model._seg_qkv(x, li)
+            o, lse = model._attn_fwd(q, k, v)
+            y = model._seg_out(x, o, li)
+        ctx.save_for_backward(x, o, lse)
+        ctx.model, ctx.li = model, li
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, o, lse = ctx.saved_tensors
+        model, li = ctx.model, ctx.li
+        with torch.enable_grad():
+            x1 = x.detach().requires_grad_()
+            q, k, v = model._seg_qkv(x1, li)                    # recomputed (cheap)
+            x2 = x.detach().requires_grad_()
+            o2 = o.detach().requires_grad_()
+            y = model._seg_out(x2, o2, li)                      # recomputed, attention is NOT
+            torch.autograd.backward([y], [dy])
+            dq, dk, dv = model._attn_bwd(o2.grad, q.detach(), k.detach(), v.detach(), o, lse)
+            torch.autograd.backward([q, k, v], [dq, dk, dv])
+        return x1.grad + x2.grad, None, None
+
+
+class LlamaModel:
+    """Parameters live in one flat bf16 buffer (fp32 on CPU) so that the optimizer and the
+    gradient collectives work on a single tensor."""
+
+    def __init__(self, cfg: LlamaConfig, device=None, pattern: Optional[BSA_Repr] = None,
+                 runtime=None, group=None, dtype=None, seed: int = 0, lr: float = 1e-4,
+                 betas=(0.9, 0.95), weight_decay: float = 0.0, max_pos: int = 1 << 20):
+        self.cfg = cfg
+        self.device = torch.device(device) if device is not None else torch.device("cpu")
+        self.dtype = dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
+        self.pattern = pattern
+        self.runtime = runtime          # ContextParallelAttention or None
+        self.group = group
+        self.world = dist.get_world_size(group) if (dist.is_initialized() and group is not None) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.lr, self.betas, self.wd = lr, betas, weight_decay
+        self.step_no = 0
+        H, D, Hk, Fd, V = cfg.hidden, cfg.head_dim, cfg.kv_heads, cfg.ffn, cfg.vocab
+        shapes = [("embed", (V, H))]
+        for i in range(cfg.n_layers):
+            shapes += [(f"l{i}.norm1", (H,)), (f"l{i}.wqkv", ((cfg.n_heads + 2 * Hk) * D, H)),
+                       (f"l{i}.wo", (H, cfg.n_heads * D)), (f"l{i}.norm2", (H,)),
+                       (f"l{i}.wgu", (2 * Fd, H)), (f"l{i}.wdown", (H, Fd))]
+        shapes += [("norm_f", (H,)), ("lm_head", (V, H))]
+        total = sum(math.prod(s) for _, s in shapes)
+        pad = (-total) % (8 * max(self.world, 1))
+        self.flat = torch.zeros(total + pad, dtype=self.dtype, device=self.device)
+        self.flat_grad = torch.zeros_like(self.flat)
+        self.p: dict = {}
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        off = 0
+        for name, shape in shapes:
+            n = math.prod(shape)
+            view = self.flat[off:off + n].view(*shape)
+            if "norm" in name:
+                view.fill_(1.0)
+            else:
+                chunk = 1 << 24
+                fl = view.view(-1)
+                for a in range(0, n, chunk):
+                    m = min(chunk, n - a)
+                    fl[a:a + m] = (torch.randn(m, generator=gen) * cfg.init_std).to(self.dtype).to(self.device)
+            view.requires_grad_()
+            view.grad = self.flat_grad[off:off + n].view(*shape)
+            self.p[name] = view
+            off += n
+        # optimizer state for this rank's shard
+        self.shard = self.flat.numel() // max(self.world, 1)
+        sl = slice(self.rank * self.shard, (self.rank + 1) * self.shard)
+        self.master = self.flat[sl].detach().float().clone()
+        self.m = torch.zeros_like(self.master)
+        self.v = torch.zeros_like(self.master)
+        self.cos, self.sin = None, None
+        self.max_pos = max_pos
+
+    # ------------------------------- segments of a layer ---------------------------------------
+    def _tables(self, n_pos: int):
+        if self.cos is None or self.cos.shape[0] < n_pos:
+            self.cos, self.sin = E.rope_tables(n_pos, self.cfg.head_dim, self.cfg.rope_base, self.device)
+        return self.cos, self.sin
+
+    def _seg_qkv(self, x, li):
+        c, p = self.cfg, self.p
+        h = _RMSNorm.apply(x, p[f"l{li}.norm1"], c.eps)
+        qkv = _Linear.apply(h, p[f"l{li}.wqkv"])
+        T = x.shape[0]
+        nq, nk = c.n_heads * c.head_dim, c.kv_heads * c.head_dim
+        q = qkv[:, :nq].reshape(T, c.n_heads, c.head_dim)
+        k = qkv[:, nq:nq + nk].reshape(T, c.kv_heads, c.head_dim)
+        v = qkv[:, nq + nk:].reshape(T, c.kv_heads, c.head_dim)
+        cos, sin = self._tables(self._n_pos)
+        q = _rope_any(q.contiguous(), cos, sin, self._pos, c.head_dim)
+        k = _rope_any(k.contiguous(), cos, sin, self._pos, c.head_dim)
+        return q.unsqueeze(0), k.unsqueeze(0), v.contiguous().unsqueeze(0)
+
+    def _seg_out(self, x, o, li):
+        c, p = self.cfg, self.p
+        a = _Linear.apply(o.reshape(x.shape[0], c.n_heads * c.head_dim), p[f"l{li}.wo"])
+        x = x + a
+        h = _RMSNorm.apply(x, p[f"l{li}.norm2"], c.eps)
+        gu = _Linear.apply(h, p[f"l{li}.wgu"])
+        return x + _Linear.apply(_Swiglu.apply(gu), p[f"l{li}.wdown"])
+
+    def _attn_fwd(self, q, k, v):
+        if self.runtime is not None:
+            return self.runtime.forward(q.contiguous(), k.contiguous(), v.contiguous())
+        from ..ops import attention as A
+        fplan, _ = api.local_plans(self.pattern, q.shape[1], q.device)
+        o = torch.empty_like(q)
+        lse = torch.empty(1, q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
+        A.attn_fwd([q], [k], [v], [(o, lse)], fplan)
+        return o, lse
+
+    def _attn_bwd(self, d_o, q, k, v, o, lse):
+        if self.runtime is not None:
+            return self.runtime.backward(d_o.contiguous(), q.contiguous(), k.contiguous(), v.contiguous(), o, lse)
+        _, bplan = api.local_plans(self.pattern, q.shape[1], q.device)
+        return api.local_backward(q, k, v, o, lse, d_o.contiguous(), bplan)
+
+    # ------------------------------- forward / loss ---------------------------------------------
+    def hidden_states(self, ids: torch.Tensor, pos: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """ids [T] (this rank's tokens) -> final normalised hidden states [T, hidden]."""
+        T = ids.shape[0]
+        self._pos = (pos if pos is not None else torch.arange(T, device=ids.device)).to(torch.int32)
+        self._n_pos = int(self._pos.max().item()) + 1 if pos is not None else T
+        x = F.embedding(ids, self.p["embed"])
+        for li in range(self.cfg.n_layers):
+            x = _Layer.apply(x, self, li)
+        return _RMSNorm.apply(x, self.p["norm_f"], self.cfg.eps)
+
+    def loss(self, ids, targets, pos=None, chunk: int = 8192, n_total_tokens: Optional[int] = None):
+        """Mean next-token cross-entropy over all tokens of the (global) sequence; logits are
+        produced and consumed ``chunk`` tokens at a time."""
+        h = self.hidden_states(ids, pos)
+        n_total = n_total_tokens or ids.shape[0] * self.world
+        total = h.new_zeros((), dtype=torch.float32)
+        for a in range(0, h.shape[0], chunk):
+            total = total + _ChunkLoss.apply(h[a:a + chunk], self.p["lm_head"], targets[a:a + chunk])
+        return total / n_total
+
+    # ------------------------------- optimizer --------------------------------------------------
+    def optimizer_step(self) -> None:
+        self.step_no += 1
+        if self.world > 1:
+            shard_grad = torch.empty(self.shard, dtype=self.dtype, device=self.device)
+            dist.reduce_scatter_tensor(shard_grad, self.flat_grad, group=self.group)
+        else:
+            shard_grad = self.flat_grad
+        sl = slice(self.rank * self.shard, (self.rank + 1) * self.shard)
+        with torch.no_grad():
+            E.adam_step(self.master, self.m, self.v, shard_grad, self.flat[sl], self.lr, self.betas[0],
+                        self.betas[1], 1e-8, self.wd, self.step_no)
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.flat, self.flat[sl].clone(), group=self.group)
+            self.flat_grad.zero_()
+
+    def train_step(self, ids, targets, pos=None, n_total_tokens=None) -> float:
+        loss = self.loss(ids, targets, pos, n_total_tokens=n_total_tokens)
+        loss.backward()
+        self.optimizer_step()
+        lv = loss.detach()
+        if self.world > 1:
+            dist.all_reduce(lv, group=self.group)
+        return float(lv)
+
+
+class _ChunkLoss(torch.autograd.Function):
+    """Sum of token cross-entropies of one chunk; logits live only inside this function."""
+
+    @staticmethod
+    def forward(ctx, h, w, targets):
+        logits = G.gemm(h, w).float()
+        lse = torch.logsumexp(logits, dim=-1)
+        loss = (lse - logits.gather(1, targets[:, None].long()).squeeze(1)).sum()
+        ctx.save_for_backward(h, w, targets, lse)
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        h, w, targets, lse = ctx.saved_tensors
+        logits = G.gemm(h, w).float()
+        p = torch.exp(logits - lse[:, None])
+        p.scatter_add_(1, targets[:, None].long(), -torch.ones_like(lse)[:, None])
+        dl = (p * g).to(h.dtype)
+        dh = G.gemm(dl, w, b_is_kn=True)
+        dw = G.gemm(dl, h, a_is_km=True, b_is_kn=True)
+        return dh, dw, None

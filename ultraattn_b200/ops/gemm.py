@@ -44,7 +44,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_is_km: bool = False, b_is_kn: bo
     if not a.is_cuda:
         af = a.float().t() if a_is_km else a.float()
         bf = b.float() if b_is_kn else b.float().t()
-        res = (af @ bf).to(torch.bfloat16)
+        res = (af @ bf).to(a.dtype)
         if out is not None:
             out.copy_(res)
             return out
