@@ -1,0 +1,146 @@
+"""Pattern algebra, tile allocation (ILP #1), dependent graph, fusion and scheduling (ILP #2)."""
+import copy
+import pickle
+
+import numpy as np
+import pytest
+
+from ultraattn_b200 import patterns as P
+from ultraattn_b200.patterns.blocks import BSA_Config, BSA_Repr, coarsen, refine
+from ultraattn_b200.planner import (Dependent_Graph, Dist_Attn_Config, Execution_Plan,
+                                    Graph_Transformation_Engine, Machine_Config,
+                                    brute_force_allocate, comm_volumes, comp_volumes,
+                                    get_cc_optimal_schedule_from_table, make_plan,
+                                    naive_allocate_strategy, solve_sparse_from_bsa, tile_volumes)
+
+
+def test_canonical_strings():
+    assert str(BSA_Repr(P.create_bsa_block_table(2))) == "[[2000][1200][1020][1002]]"
+    assert str(BSA_Repr(P.create_bsa_block_table(4))) == "[[1]]"
+    assert str(BSA_Repr(P.create_bsa_block_table(5))) == "[[2]]"
+    cfg = BSA_Config(None, None, {"bsa_repr": P.causal(1), "CP": (8, 1)})
+    assert cfg.to_string() == "CP=(8, 1)_repr=[[2]]"
+    assert P.streaming(8, 1, 3) == BSA_Repr(P.create_bsa_block_table(3))
+    assert BSA_Repr.from_string(str(P.strided(8, 4, 2))) == P.strided(8, 4, 2)
+
+
+@pytest.mark.parametrize("pat", [P.causal(1), P.full(1), P.star(4, 1), P.strided(8, 4, 2), P.global_local(8, 1, 2)])
+@pytest.mark.parametrize("rate", [2, 3, 4])
+def test_refine_coarsen_round_trip(pat, rate):
+    fine = refine(pat.table, rate)
+    assert np.array_equal(coarsen(fine), pat.table)
+    assert BSA_Repr(fine) == pat
+    # refinement preserves the token-level mask
+    S = pat.table.shape[0] * rate * 4
+    assert (pat.token_mask(S) == pat.token_mask(S, table=fine)).all()
+
+
+def test_predicates_and_split():
+    assert P.causal(4).check_causal() and not P.full(2).check_causal()
+    assert not P.global_local(8, 1, 2).check_causal()          # row 0 sees the future
+    assert P.strided(32, 4, 2).volume == 159.0
+    subs = P.causal(1).split_n(4)
+    assert sorted(str(s) for s in subs) == ["[[0]]", "[[1]]", "[[2]]"]
+    sub = P.strided(8, 4, 2).create_sub_bsa_repr([4, 4], [[1], [0]])
+    assert sub.table.shape in [(1, 1), (2, 2)]
+
+
+def test_full_8x8_comm_volume_is_8():
+    cfg = BSA_Config(None, None, {"bsa_repr": P.full(8), "CP": (8, 1)})
+    al = solve_sparse_from_bsa(cfg, fob=0, time_limit=2.0)
+    assert al.comm_volume == 8.0 and al.comp_max == 8.0
+    _check_allocation(al, cfg)
+
+
+def _check_allocation(al, cfg, fob=0):
+    cp = cfg.CP[0]
+    vol = tile_volumes(cfg.bsa_repr, al.Par_D)
+    assert ((al.table >= 0) == (vol > 0)).all()              # every non-empty tile exactly once
+    assert al.table.max() < cp
+    cin, cout = comm_volumes(al.table, al.cmap, cp, fob)
+    assert max(cin.max(), cout.max()) == al.comm_volume
+    assert comp_volumes(al.table, vol, cp).max() == al.comp_max
+
+
+@pytest.mark.parametrize("pat,cp,fob", [(P.star(4, 1), 2, 0), (P.star(4, 1), 2, 1), (P.causal(1), 4, 0),
+                                        (P.full(1), 2, 1), (P.streaming(4, 1, 2), 2, 0)])
+def test_ilp_matches_brute_force(pat, cp, fob):
+    cfg = BSA_Config(None, None, {"bsa_repr": pat, "CP": (cp, 1)})
+    a = solve_sparse_from_bsa(cfg, fob=fob, time_limit=10.0)
+    b = brute_force_allocate(cfg, fob=fob)
+    _check_allocation(a, cfg, fob)
+    assert a.comp_max <= b.comp_max + 1e-9 or a.comm_volume <= b.comm_volume
+    assert a.comm_volume == b.comm_volume
+
+
+def test_causal8_beats_row_owner():
+    cfg = BSA_Config.create_causal((8, 1))
+    a = solve_sparse_from_bsa(cfg, fob=0, time_limit=3.0)
+    n = naive_allocate_strategy(cfg, fob=0)
+    assert a.comp_max <= 4.5 and n.comp_max == 7.5
+    assert a.comm_volume <= n.comm_volume
+
+
+def _graph(pat, cp, S, fob, alloc="naive"):
+    cfg = BSA_Config(None, None, {"bsa_repr": pat, "CP": (cp, 1)})
+    da = Dist_Attn_Config.from_bsa_config(cfg, {"S": (S, S), "Nh": (8, 8), "bs": 1, "D": 128}, 1)
+    al = naive_allocate_strategy(cfg, fob) if alloc == "naive" else solve_sparse_from_bsa(cfg, fob, time_limit=3.0)
+    sch = get_cc_optimal_schedule_from_table(da, Machine_Config.b200_default(), al)
+    return Dependent_Graph(sch, fob)
+
+
+@pytest.mark.parametrize("fob", [0, 1])
+def test_graph_structure(fob):
+    g = _graph(P.causal(1), 4, 8192, fob)
+    assert g.is_acyclic()
+    comm = [k for k in g.kernel_dict.values() if k.type == "comm"]
+    # row-owner allocation: only K/V columns travel; forward has no output-column payload
+    assert all(k.key[6] == "c" for k in comm)
+    out = [k for k in comm if k.key[5] == "o"]
+    assert all(k.is_empty(0) for k in out) and all(not k.is_empty(1) for k in out)
+    # messages are de-duplicated per (column, peer)
+    assert len({k.key for k in comm}) == len(comm)
+    g2 = copy.deepcopy(g)
+    assert g2.schedule is g.schedule and g2.kernel_dict is not g.kernel_dict
+
+
+@pytest.mark.parametrize("plan_type", ["Flexflow", "ILP"])
+@pytest.mark.parametrize("fob", [0, 1])
+def test_plans_verify(plan_type, fob):
+    for pat, cp in [(P.causal(1), 4), (P.global_local(8, 1, 2), 2), (P.strided(8, 4, 2), 4)]:
+        g = _graph(pat, cp, 16384, fob, alloc="ilp")
+        plan = Execution_Plan(g, fob, plan_type, time_limit=3.0)
+        assert plan.verify() == []
+        flex = Execution_Plan(copy.deepcopy(g), fob, "Flexflow")
+        assert plan.end_time <= flex.end_time * (1 + 1e-9)
+        assert plan.end_time >= g.critical_path() * (1 - 1e-9)
+        p2 = pickle.loads(pickle.dumps(plan))
+        assert p2.end_time == plan.end_time and len(p2.gpu_kernel_lists) == cp
+        plain = plan.to_plain()
+        assert len(plain["kernels"]) == len(plan.valid_kernels)
+
+
+def test_kernel_tile_fusion():
+    g = _graph(P.full(1), 2, 8192, 0)
+    eng = Graph_Transformation_Engine()
+    chosen = eng.select_greedy(g)
+    assert chosen, "a 2x2 full problem on 2 ranks has fusable rectangles"
+    plan = eng.transform(g, "greedy", "Flexflow")
+    assert plan.verify() == []
+    base = Execution_Plan(copy.deepcopy(g), 0, "Flexflow")
+    assert plan.end_time <= base.end_time * (1 + 1e-9)
+    bf = eng.transform(g, "bf", "Flexflow")
+    assert bf.end_time <= base.end_time * (1 + 1e-9)
+
+
+def test_make_plan_and_remap():
+    plan = make_plan(P.strided(8, 4, 2), cp=4, seq_len=8192, n_heads=4, fob=1, time_limit=3.0)
+    assert plan.verify() == []
+    cm = P.cmap_strided(8, 4)
+    assert sorted(P.remap_permutation(cm).tolist()) == list(range(8))
+    assert (P.cmap_zigzag(8, 2) == np.array([0, 0, 1, 1, 1, 1, 0, 0])).all()
+    # residue-class ownership makes the strided pattern cheaper to tile than contiguous chunks
+    cfg = BSA_Config(None, None, {"bsa_repr": P.strided(8, 4, 2), "CP": (4, 1)})
+    a = solve_sparse_from_bsa(cfg, fob=0, time_limit=3.0)
+    b = solve_sparse_from_bsa(cfg, fob=0, time_limit=3.0, cmap=cm)
+    assert b.comm_volume <= a.comm_volume + 2

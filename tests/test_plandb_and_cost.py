@@ -1,0 +1,62 @@
+"""Plan database (layout, key grammar, restartability) and cost-model file formats."""
+import json
+import os
+
+import numpy as np
+
+from ultraattn_b200 import patterns as P
+from ultraattn_b200.patterns.blocks import BSA_Config
+from ultraattn_b200.plandb import ABLATION_SUFFIXES, Prof_DB, allocation_key, full_plan_key, plan_key_prefix
+from ultraattn_b200.planner import make_plan
+from ultraattn_b200.planner.cost import (Comm_Profile_Map, FlashAttn_Profile_Map, convert_profile_data_to_comm_map,
+                                         dump_flash_profile, format_cb_line, load_flash_profile)
+
+
+def test_key_grammar():
+    cfg = BSA_Config(None, None, {"bsa_repr": P.star(4, 1), "CP": (8, 1)})
+    shape = {"S": (4096, 16384), "Nh": (1, 1), "bs": 1, "D": 128}
+    assert plan_key_prefix(0, (8, 1), shape, cfg) == (
+        "fob=0_CP=(8, 1)_shape_config={S=(4096, 16384)_Nh=(1, 1)_bs=1_D=128}"
+        "_bsa_config={CP=(8, 1)_repr=[[2000][1200][1020][1002]]}")
+    assert allocation_key(1, cfg, "naive") == "fob=1_bsa_config={CP=(8, 1)_repr=[[2000][1200][1020][1002]]}_naive"
+    assert full_plan_key(0, (8, 1), 2, 4) == "fob=0_CP=(8, 1)_shape_config=full_ablation=(Y=2,X=4,dim=0)"
+    assert ABLATION_SUFFIXES[0] == "_ablation=(w/o_gpu_tile,w/o_kernel_tile,Flexflow)"
+
+
+def test_db_round_trip(tmp_path):
+    db = Prof_DB("testcluster", "B200", root=str(tmp_path))
+    for name in ("intra_bsa_allocation.json", "inter_bsa_exe_plans_kv.json", "intra_bsa_exe_plans_profile.json"):
+        assert (tmp_path / "testcluster" / "B200" / name).exists()
+    plan = make_plan(P.causal(1), cp=2, seq_len=4096, n_heads=4, fob=0, allocation="naive")
+    k1, k2 = "k" + ABLATION_SUFFIXES[0], "k" + ABLATION_SUFFIXES[1]
+    assert db.put_plan(k1, plan) == 0 and db.put_plan(k2, plan) == 1 and db.put_plan(k1, plan) == 0
+    got = db.get_plan(k1)
+    assert got.end_time == plan.end_time and got.verify() == []
+    plain = db.get_plan_plain(k2)
+    assert plain["format"] == "ultraattn-plan/1" and plain["gpu_kernel_lists"]
+    db.put_allocation("a", np.array([[0, -1], [1, 1]]))
+    assert db.get_allocation("a")["table"].tolist() == [[0, -1], [1, 1]]
+    db.put_profile(k1, 512.3, 1.234e-3, 1.1e-3)
+    assert db.get_profile(k1) == {"hfu": 512.3, "time": "1.234e-03", "sim_time": "1.100e-03"}
+    # a second instance on the same directory sees everything (restartable campaign)
+    db2 = Prof_DB("testcluster", "B200", root=str(tmp_path))
+    assert db2.has_plan(k2) and db2.get_profile(k1)["hfu"] == 512.3
+    db2.m_config_update_inter_bsa_profile()
+    assert db2.m_config.comp_profile_maps[0].get_comp_time_from_map_key(k1)[0] == 1.234e-3
+
+
+def test_profile_formats(tmp_path):
+    f = tmp_path / "time_x.json"
+    dump_flash_profile(f, [((4096, 1, 32, 128, "1/1", True), 1e-3, 3e-3, 500.0, 400.0)])
+    m = FlashAttn_Profile_Map(load_flash_profile(f))
+    assert np.allclose(m.get_comp_time_from_map_key((4096, 1, 32, 128, "1/1", True)), [1e-3, 3e-3])
+    t = m.get_comp_time_from_map_key((8192, 1, 32, 128, "2/1", False))          # analytic fallback
+    assert t[1] > t[0] > 0
+    assert m.merge_comp_map_key((4096, 1, 32, 128, "1/1", False), (4096, 1, 32, 128, "1/1", False), 0) == \
+        (4096, 1, 32, 128, "2/1", False)
+    log = tmp_path / "cb_8_x.log"
+    log.write_text("[[0, 1], [1, 0]]\n" + format_cb_line(8192, 1.0, 0.5, 1e-3, 1.6) + "\n" +
+                   "SIZE 2621440, REAL_BD 195.2 GB/s, BD/PAIR 97.6 GB/s, time 1.0e-03 s, comm_vol 5 MB\n")
+    cm = Comm_Profile_Map(convert_profile_data_to_comm_map(log))
+    assert cm.bandwidth_gbs(1e9) == 97.6 and cm.bandwidth_gbs(100) == 0.5
+    assert abs(cm.get_comm_time_from_map_key((97.6e9,)) - 1.0) < 1e-9
