@@ -85,6 +85,55 @@ def test_context_parallel_4gpu_fused():
         assert res[r]["rel_err"] < 2e-2, res
 
 
+def _ulysses_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from ultraattn_b200 import patterns as P
+        from ultraattn_b200.ops import attention as A
+        from ultraattn_b200.parallel.ulysses_fused import FusedUlyssesAttention, permute_qkv_weight
+        S, hidden, H = 1024, 512, 4
+        g = torch.Generator().manual_seed(0)
+        x = (torch.randn(S, hidden, generator=g) * 0.5).to(torch.bfloat16)
+        wqkv = (torch.randn(3 * H * 128, hidden, generator=g) * 0.05).to(torch.bfloat16)
+        wo = (torch.randn(hidden, H * 128, generator=g) * 0.05).to(torch.bfloat16)
+        mod = FusedUlyssesAttention(dist.group.WORLD, dev, S, hidden, H)
+        S_loc = S // world
+        xl = x[rank * S_loc:(rank + 1) * S_loc].contiguous().to(dev)
+        wp = permute_qkv_weight(wqkv, H, H, 128, world).to(dev)
+        worst = 0.0
+        for _ in range(2):
+            y = mod.forward(xl, wp, wo.to(dev))
+            torch.cuda.synchronize()
+            A.check_status(dev)
+            qkv = (x.float() @ wqkv.float().t()).to(torch.bfloat16).float()
+            q, k, v = (qkv[:, i * H * 128:(i + 1) * H * 128].view(1, S, H, 128) for i in range(3))
+            o, _ = P.dense_attention(q, k, v, P.causal(1).token_mask(S))
+            y_ref = o.to(torch.bfloat16).float().view(S, H * 128) @ wo.float().t()
+            err = (y.float().cpu() - y_ref[rank * S_loc:(rank + 1) * S_loc]).abs().max().item()
+            worst = max(worst, err / (y_ref.abs().max().item() + 1e-6))
+        ret[rank] = {"rel_err": worst}
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = {"error": f"{type(e).__name__}: {e}\n{traceback.format_exc()}"}
+    finally:
+        dist.destroy_process_group()
+
+
+def test_fused_ulysses_projections_2gpu():
+    """QKV projection with the all-to-all in its epilogue and output projection with the
+    all-to-all in its operand load, against the unfused computation."""
+    _need(2)
+    ret = mp.Manager().dict()
+    mp.spawn(_ulysses_worker, args=(2, 29930 + os.getpid() % 50, ret), nprocs=2, join=True)
+    for r in range(2):
+        assert "error" not in ret[r], ret[r].get("error")
+        assert ret[r]["rel_err"] < 3e-2, dict(ret)
+
+
 def test_flag_wait_times_out_cleanly():
     """A device-side wait on a flag that nothing sets gives up after its budget, records an error
     code in the status word and leaves the context usable (no trap, no hang)."""

@@ -81,9 +81,37 @@ __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t target, unsigned
   }
 }
 
+// dst[i] += src[i] (fp32) with vector reductions; dst may be a peer GPU's memory (the adds travel
+// as NVLink reduction packets). Optionally clears src afterwards so that it can accumulate the
+// next step's partial sums.
+__global__ void __launch_bounds__(256)
+peer_add_kernel(float* __restrict__ dst, float* __restrict__ src, long n_vec4, int zero_src) {
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec4; i += stride) {
+    const float4 v = *reinterpret_cast<const float4*>(src + i * 4);
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i * 4), "f"(v.x),
+                 "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+    if (zero_src) *reinterpret_cast<float4*>(src + i * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
 }  // namespace ua
 
 using namespace ua;
+
+extern "C" int ua_peer_add_f32(void* dst, void* src, long n, int zero_src, int num_sms,
+                               cudaStream_t stream) {
+  if (n % 4 != 0) UA_FAIL("ua_peer_add_f32: n must be a multiple of 4");
+  if (n == 0) return 0;
+  const long n4 = n / 4;
+  long blocks = (n4 + 255) / 256;
+  if (blocks > static_cast<long>(num_sms) * 8) blocks = static_cast<long>(num_sms) * 8;
+  peer_add_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      static_cast<float*>(dst), static_cast<float*>(src), n4, zero_src);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}
 
 // pads: host array of `world` device pointers (peer-mapped signal pads, >= 16*channels uint32 each)
 extern "C" int ua_barrier(void* const* pads, int rank, int world, int channel, unsigned epoch,

@@ -185,3 +185,19 @@ def adam_step(master, m, v, grad, param, lr, beta1, beta2, eps, wd, step, grad_s
                              param.data_ptr(), master.numel(), lr, beta1, beta2, eps, wd, step,
                              grad_scale, _stream(master))
     _lib.check(rc, "ua_adam")
+
+
+def peer_add_(dst: torch.Tensor, src: torch.Tensor, zero_src: bool = False) -> None:
+    """dst += src for contiguous fp32 tensors; ``dst`` may be a view of a peer GPU's memory
+    (this framework's own kernel does the adds — library kernels never touch peer memory)."""
+    assert dst.dtype == torch.float32 and src.dtype == torch.float32
+    assert dst.is_contiguous() and src.is_contiguous() and dst.numel() == src.numel()
+    if not dst.is_cuda:
+        dst.add_(src)
+        if zero_src:
+            src.zero_()
+        return
+    sms = torch.cuda.get_device_properties(src.device).multi_processor_count
+    rc = _lib.load().ua_peer_add_f32(dst.data_ptr(), src.data_ptr(), src.numel(), int(zero_src), sms,
+                                     _stream(src))
+    _lib.check(rc, "ua_peer_add_f32")

@@ -203,6 +203,10 @@ class FusedContextParallel:
             self.mir[("do", p)] = torch.zeros(B, S, H, D, dtype=dt, device=dev)
             self.mir[("lse", p)] = torch.zeros(B, H, S, dtype=torch.float32, device=dev)
             self.mir[("dvec", p)] = torch.zeros(B, H, S, dtype=torch.float32, device=dev)
+            # dQ of foreign rows is accumulated here (every key tile adds into it) and pushed to
+            # the owner once per step; adding straight into the owner's memory would send every
+            # partial sum over NVLink
+            self.mir[("dq", p)] = torch.zeros(B, S, H, D, dtype=torch.float32, device=dev)
         for p in peers_cols:
             self.mir[("k", p)] = torch.zeros(B, S, Hk, D, dtype=dt, device=dev)
             self.mir[("v", p)] = torch.zeros(B, S, Hk, D, dtype=dt, device=dev)
@@ -431,7 +435,7 @@ class FusedContextParallel:
                                       sp.local("dq_acc"))
             else:
                 sides[i] = A.BwdQSide(self.mir[("q", p)], self.mir[("do", p)], self.mir[("lse", p)],
-                                      self.mir[("dvec", p)], sp.peer("dq_acc", p))
+                                      self.mir[("dvec", p)], self.mir[("dq", p)])
         k_srcs = [None] * len(self.b_kv_src)
         v_srcs = [None] * len(self.b_kv_src)
         outs = [None] * len(self.b_kv_src)
@@ -447,6 +451,12 @@ class FusedContextParallel:
             # each of the two staging variants has its own flag counters and call count
             stage.epoch += 1
         A.attn_bwd(sides, k_srcs, v_srcs, outs, self.b_plans[which], softmax_scale, stage)
+        # push the accumulated dQ of every foreign row to its owner, once
+        for r in self.remote_rows:
+            p = int(self.cmap[r])
+            tok = self._tok(r)
+            for b in range(self.B):
+                E.peer_add_(sp.peer("dq_acc", p)[b, tok], self.mir[("dq", p)][b, tok], zero_src=True)
 
     def bwd_finish(self):
         sp = self.space
