@@ -18,13 +18,14 @@
 // Everything is computed transposed so that P^T and dS^T come out with keys on the TMEM lanes,
 // which is the layout the dV / dK products need for their A operand.
 //
-//   warps 0-3 : softmax warpgroup (one thread per key) and the dK/dV epilogue
-//   warps 4-7 : dQ drain warpgroup (one thread per head-dim element): each warp transposes its
+//   warps 0-7 : two softmax warpgroups (one thread per key) that alternate over the steps, and the
+//               dK / dV epilogue (one accumulator each)
+//   warps 8-11: dQ drain warpgroup (one thread per head-dim element): each warp transposes its
 //               32 x 64 slice through shared memory and issues cp.reduce.async.bulk.tensor (fp32
 //               add at the memory side) into the dQ accumulator — this GPU's or, through a
 //               tensor map over a peer mapping, the owning GPU's
-//   warp  8   : TMA producer (K, V once; Q/dO sub-tile ring)
-//   warp  9   : tcgen05.mma issuer, TMEM allocation
+//   warp  12  : TMA producer (K, V once; Q/dO sub-tile ring)
+//   warp  13  : tcgen05.mma issuer, TMEM allocation
 // TMEM (512 columns): dK 128 | dV 128 | S^T/P^T x2 (64 each) | dP^T/dQ^T x2 (64 each).
 // dK/dV leave the CTA either as bf16 stores (the CTA is their only producer) or as fp32
 // red.add into an accumulator that may live in a peer GPU's memory (partial gradients of a
@@ -35,7 +36,9 @@
 
 namespace ua {
 
-constexpr int BWD_THREADS = 320;
+constexpr int BWD_THREADS = 448;
+constexpr int BWD_TMA_WARP = 12;
+constexpr int BWD_MMA_WARP = 13;
 constexpr int BWD_QT = 64;                 // queries per sub-tile
 constexpr int BWD_STAGES = 3;              // Q/dO ring depth
 constexpr int BWD_KV_BYTES = ATTN_TILE * ATTN_D * 2;   // 32 KB
@@ -145,7 +148,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     s.abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 9) {
+  if (warp == BWD_MMA_WARP) {
     tmem_alloc(&s.tmem_base, 512);
     tmem_relinquish();
   }
@@ -164,7 +167,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
   }
   const int n_steps = steps_per_head * p.kv_group;
 
-  if (warp == 8) {
+  if (warp == BWD_TMA_WARP) {
     // =============================== TMA producer ===========================================
     if (lane == 0 && n_steps > 0) {
       const int krow = col.kv_start + c0;
@@ -204,7 +207,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == BWD_MMA_WARP) {
     // =============================== MMA issuer =============================================
     if (lane == 0 && n_steps > 0) {
       const uint32_t idesc_st = make_idesc_bf16(128, BWD_QT, 0, 0);   // S^T, dP^T
@@ -292,8 +295,11 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         if (ok) tc_commit(&s.dkv_full);
       } while (false);
     }
-  } else if (warp < 4) {
-    // =============================== softmax warpgroup ======================================
+  } else if (warp < 8) {
+    // =============================== softmax warpgroups =====================================
+    // two warpgroups alternate: warpgroup w handles the steps with (i & 1) == w, i.e. its own
+    // S^T / dP^T buffer pair, so two steps are in the softmax stage at any time
+    const int wg = warp >> 2;
     const int quad = warp & 3;
     const int key_t = quad * 32 + lane;              // key inside the tile
     const int key_c = c0 + key_t;                    // key inside the block column
@@ -320,6 +326,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
                             head * p.lse_head_stride[sg.src];
         for (int t = seg_first_qt(sg, c0); t < nq; ++t, ++i) {
           const int b = i & 1;
+          if (b != wg) continue;
           // stage lse / D of the 64 queries, one private copy per warp
           // (rows outside the segment get lse = +inf -> P = 0)
 #pragma unroll
@@ -400,7 +407,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     const long goff = batch * p.dkv_batch_stride[slot] + grow * p.dkv_row_stride[slot] +
                       static_cast<long>(kv_head) * ATTN_D;
 #pragma unroll 1
-    for (int which = 0; which < 2; ++which) {
+    for (int which = wg; which <= wg; ++which) {      // warpgroup 0 stores dK, warpgroup 1 dV
       const uint32_t t_acc = tmem_base + lane_base + which * 128;
       const float mul = which == 0 ? p.scale : 1.0f;
       void* base = which == 0 ? p.dk_ptr[slot] : p.dv_ptr[slot];
@@ -492,7 +499,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == BWD_MMA_WARP) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
@@ -610,6 +617,154 @@ extern "C" int ua_attn_bwd(const UaTensorSrc* q_src, const UaTensorSrc* do_src,
   }
   dim3 grid(n_tiles * n_kv_heads, batch, 1);
   attn_bwd_kernel<<<grid, BWD_THREADS, smem_bytes, stream>>>(p);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// =================================================================================================
+// Allocation-free dense backward (declared in ultraattn_noalloc.h)
+// =================================================================================================
+// Same kernel as above, for callers that must not allocate device memory while they run: code
+// inside a CUDA-graph capture or a real-time serving loop, a plug-in living in a host process
+// whose memory pool it may not touch, or a process that has already handed all free HBM to its
+// own allocator (cudaMalloc would fail or stall there). The fp32 dQ accumulator and the small
+// launch tables, which ua_attn_bwd() expects the caller to provide, live in the file-scope
+// device array below instead. Every GPU that loads this library holds the array until the
+// process exits.
+namespace ua {
+
+constexpr long NOALLOC_MAX_QH_TOKENS = 131072;     // tokens * query heads, at most
+constexpr int NOALLOC_MAX_TOKENS = 65536;
+constexpr long NOALLOC_DQ_BYTES = NOALLOC_MAX_QH_TOKENS * ATTN_D * 4;           // 64 MiB
+constexpr long NOALLOC_COL_OFF = NOALLOC_DQ_BYTES;
+constexpr long NOALLOC_SEG_OFF = NOALLOC_COL_OFF + 256;
+constexpr long NOALLOC_TILE_OFF = NOALLOC_SEG_OFF + 256;
+constexpr long NOALLOC_BYTES = NOALLOC_TILE_OFF + (NOALLOC_MAX_TOKENS / ATTN_TILE) * 8;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
+
+// In host code the array's name is only a stand-in: the device address is looked up once per
+// device (with that device current) and cached here.
+static unsigned char* g_noalloc_ptr[64] = {nullptr};
+
+__global__ void noalloc_fill_tables(BwdCol* col, AttnSeg* seg, int2* tiles, int tokens, int causal) {
+  const int n_tiles = (tokens + ATTN_TILE - 1) / ATTN_TILE;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    BwdCol c;
+    c.kv_src = 0; c.kv_start = 0; c.kv_len = tokens; c.seg_begin = 0; c.seg_end = 1;
+    c.g_slot = 0; c.g_start = 0; c.pad = 0; c.kv_wait_flag = 0; c.kv_wait_count = 0;
+    *col = c;
+    AttnSeg s;
+    s.src = 0; s.start = 0; s.len = tokens; s.causal = causal; s.diag = 0;
+    s.wait_flag = 0; s.wait_count = 0; s.pad2 = 0;
+    *seg = s;
+  }
+  // key tile t of a causal problem is visited by all query sub-tiles at or below it, so the
+  // heaviest tiles are the first ones: ascending order is already heaviest-first
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < n_tiles; t += gridDim.x * blockDim.x)
+    tiles[t] = make_int2(0, t);
+}
+
+__global__ void noalloc_cast_dq(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long n) {
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x * 4;
+  for (long i = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
+    const float4 v = *reinterpret_cast<const float4*>(src + i);
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(dst + i) = o;
+  }
+}
+
+}  // namespace ua
+
+extern "C" int ua_attn_bwd_dense_noalloc(const void* q, const void* k, const void* v, const void* d_o,
+                                         const float* lse, const float* dvec, void* dq, void* dk,
+                                         void* dv, int tokens, int n_heads, int n_kv_heads,
+                                         int causal, float softmax_scale, int* status,
+                                         cudaStream_t stream) {
+  if (tokens <= 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
+    UA_FAIL("ua_attn_bwd_dense_noalloc: bad shape (tokens=%d, heads=%d, kv heads=%d)", tokens, n_heads,
+            n_kv_heads);
+  if (tokens > NOALLOC_MAX_TOKENS || static_cast<long>(tokens) * n_heads > NOALLOC_MAX_QH_TOKENS)
+    UA_FAIL("ua_attn_bwd_dense_noalloc: %d tokens x %d heads exceeds the built-in scratch "
+            "(at most %d tokens and tokens*heads <= %ld); use ua_attn_bwd with caller-owned scratch",
+            tokens, n_heads, NOALLOC_MAX_TOKENS, NOALLOC_MAX_QH_TOKENS);
+  int dev = 0;
+  UA_CUDA(cudaGetDevice(&dev));
+  if (dev >= 64) UA_FAIL("ua_attn_bwd_dense_noalloc: device index %d not supported", dev);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // one-time set-up for this device: resolve the device address of the scratch array
+    void* p = nullptr;
+    UA_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  unsigned char* base = g_noalloc_ptr[dev];
+  float* dq32 = reinterpret_cast<float*>(base);
+  BwdCol* col = reinterpret_cast<BwdCol*>(base + NOALLOC_COL_OFF);
+  AttnSeg* seg = reinterpret_cast<AttnSeg*>(base + NOALLOC_SEG_OFF);
+  int2* tiles = reinterpret_cast<int2*>(base + NOALLOC_TILE_OFF);
+  const int n_tiles = (tokens + ATTN_TILE - 1) / ATTN_TILE;
+  const long n_dq = static_cast<long>(tokens) * n_heads * ATTN_D;
+
+  BwdParams p;
+  memset(&p, 0, sizeof(p));
+  UaTensorSrc tq = {q, tokens, n_heads, 1, static_cast<long>(n_heads) * ATTN_D, ATTN_D, 0};
+  UaTensorSrc tdo = {d_o, tokens, n_heads, 1, static_cast<long>(n_heads) * ATTN_D, ATTN_D, 0};
+  UaTensorSrc tk = {k, tokens, n_kv_heads, 1, static_cast<long>(n_kv_heads) * ATTN_D, ATTN_D, 0};
+  UaTensorSrc tv = {v, tokens, n_kv_heads, 1, static_cast<long>(n_kv_heads) * ATTN_D, ATTN_D, 0};
+  if (encode_src_box(&p.tmQ[0], tq, BWD_QT)) return -1;
+  if (encode_src_box(&p.tmdO[0], tdo, BWD_QT)) return -1;
+  if (encode_src_box(&p.tmK[0], tk, ATTN_TILE)) return -1;
+  if (encode_src_box(&p.tmV[0], tv, ATTN_TILE)) return -1;
+  {
+    uint64_t dims[4] = {ATTN_D, static_cast<uint64_t>(n_heads), static_cast<uint64_t>(tokens), 1};
+    uint64_t str[3] = {ATTN_D * 4ull, static_cast<uint64_t>(n_heads) * ATTN_D * 4,
+                       static_cast<uint64_t>(n_dq) * 4};
+    uint32_t box[4] = {32, 1, 32, 1};
+    if (make_tmap_f32(&p.tmdQ[0], dq32, 4, dims, str, box)) return -1;
+  }
+  p.lse_ptr[0] = lse;
+  p.dvec_ptr[0] = dvec;
+  p.lse_head_stride[0] = tokens;
+  p.lse_batch_stride[0] = static_cast<long>(tokens) * n_heads;
+  p.q_tokens[0] = tokens;
+  p.dk_ptr[0] = dk;
+  p.dv_ptr[0] = dv;
+  p.dkv_row_stride[0] = static_cast<long>(n_kv_heads) * ATTN_D;
+  p.dkv_batch_stride[0] = static_cast<long>(tokens) * n_kv_heads * ATTN_D;
+  p.dkv_add_f32[0] = 0;
+  p.cols = col;
+  p.segs = seg;
+  p.tiles = tiles;
+  p.n_tiles = n_tiles;
+  p.n_kv_heads = n_kv_heads;
+  p.kv_group = n_heads / n_kv_heads;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = status;
+  p.stage.tasks = nullptr;
+  p.stage.n_tasks = 0;
+  p.stage.n_copy_ctas = 0;
+  p.stage.flags = nullptr;
+  p.stage.epoch = 1;
+
+  const int smem_bytes = sizeof(BwdSmem) + 1024;
+  if (!g_bwd_smem_set[dev]) {
+    UA_CUDA(cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    g_bwd_smem_set[dev] = 1;
+  }
+  // the array keeps the previous call's contents: the accumulator has to start from zero
+  UA_CUDA(cudaMemsetAsync(dq32, 0, static_cast<size_t>(n_dq) * 4, stream));
+  noalloc_fill_tables<<<4, 256, 0, stream>>>(col, seg, tiles, tokens, causal ? 1 : 0);
+  UA_CUDA(cudaGetLastError());
+  dim3 grid(n_tiles * n_kv_heads, 1, 1);
+  attn_bwd_kernel<<<grid, BWD_THREADS, smem_bytes, stream>>>(p);
+  UA_CUDA(cudaGetLastError());
+  long blocks = (n_dq / 4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  noalloc_cast_dq<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      dq32, static_cast<__nv_bfloat16*>(dq), n_dq);
   UA_CUDA(cudaGetLastError());
   return 0;
 }
