@@ -78,6 +78,10 @@ def load():
     if _lib is not None:
         return _lib
     path = _build.LIB_PATH
+    if os.environ.get("UA_LIB_PATH"):           # explicit library file (development builds)
+        from pathlib import Path
+        _lib = _declare(ctypes.CDLL(os.environ["UA_LIB_PATH"]))
+        return _lib
     if not path.exists() or os.environ.get("UA_REBUILD") == "1":
         try:
             _build.build_all(force=os.environ.get("UA_REBUILD") == "1")

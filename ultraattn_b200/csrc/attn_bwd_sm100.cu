@@ -18,8 +18,8 @@
 // Everything is computed transposed so that P^T and dS^T come out with keys on the TMEM lanes,
 // which is the layout the dV / dK products need for their A operand.
 //
-//   warps 0-7 : two softmax warpgroups (one thread per key) that alternate over the steps, and the
-//               dK / dV epilogue (one accumulator each)
+//   warps 0-7 : two softmax warpgroups; thread (key, half) handles 32 of the 64 query columns of
+//               its key row in every step; in the epilogue one warpgroup stores dK, the other dV
 //   warps 8-11: dQ drain warpgroup (one thread per head-dim element): each warp transposes its
 //               32 x 64 slice through shared memory and issues cp.reduce.async.bulk.tensor (fp32
 //               add at the memory side) into the dQ accumulator — this GPU's or, through a
@@ -92,8 +92,8 @@ struct __align__(1024) BwdSmem {
   uint8_t d_o[BWD_STAGES][BWD_QT_BYTES];
   uint8_t ds[2][ATTN_TILE * BWD_QT * 2];   // dS^T: [128 keys][64 queries] bf16, 128-byte swizzle
   float dq_stage[4][32 * 32];              // per drain warp: [32 queries][32 head-dim] fp32
-  float lse[2][4][BWD_QT];    // per softmax warp copies (no cross-warp barrier needed)
-  float dvec[2][4][BWD_QT];
+  float lse[2][8][32];        // per softmax warp copies (no cross-warp barrier needed)
+  float dvec[2][8][32];
   uint64_t kv_full;
   uint64_t qdo_full[BWD_STAGES];
   uint64_t qdo_empty[BWD_STAGES];
@@ -140,7 +140,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.sdp_full[i], 1);
-      mbar_init(&s.pds_full[i], 128);
+      mbar_init(&s.pds_full[i], 256);
       mbar_init(&s.dq_full[i], 1);
       mbar_init(&s.dq_free[i], 128);
     }
@@ -267,10 +267,12 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
             umma_ss(t_dp[b], make_smem_desc_sw128(ka + kk * 2048, 16384, 1024),
                     make_smem_desc_sw128(dsa + kk * 2048, 16, 1024), idesc_dq, kk > 0 ? 1u : 0u);
           tc_commit(&s.dq_full[b]);
-          // dV += P^T dO : A = P^T in TMEM (16 queries = 8 packed columns per step)
+          // dV += P^T dO : A = P^T in TMEM (16 queries = 8 packed columns per step; queries 0-31 are
+          // packed at columns 0-15, queries 32-63 at columns 32-47)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ts(t_dv, t_st[b] + kk * 8, make_smem_desc_sw128(da + kk * 2048, 8192, 1024),
+            umma_ts(t_dv, t_st[b] + (kk >> 1) * 32 + (kk & 1) * 8,
+                    make_smem_desc_sw128(da + kk * 2048, 8192, 1024),
                     idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
           // dK += dS^T Q : A = dS^T in shared memory (K-major over queries)
 #pragma unroll
@@ -297,9 +299,10 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     }
   } else if (warp < 8) {
     // =============================== softmax warpgroups =====================================
-    // two warpgroups alternate: warpgroup w handles the steps with (i & 1) == w, i.e. its own
-    // S^T / dP^T buffer pair, so two steps are in the softmax stage at any time
-    const int wg = warp >> 2;
+    // the two warpgroups share every step: thread (key row, half) of warpgroup `half` handles the
+    // 32 query columns [32*half, 32*half+32) of its key row, which halves the serial work per
+    // step (a step's softmax is otherwise one long dependent instruction stream per warp)
+    const int wg = warp >> 2;                        // which half of the 64 query columns
     const int quad = warp & 3;
     const int key_t = quad * 32 + lane;              // key inside the tile
     const int key_c = c0 + key_t;                    // key inside the block column
@@ -326,71 +329,70 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
                             head * p.lse_head_stride[sg.src];
         for (int t = seg_first_qt(sg, c0); t < nq; ++t, ++i) {
           const int b = i & 1;
-          if (b != wg) continue;
-          // stage lse / D of the 64 queries, one private copy per warp
+          // stage lse / D of this warp's 32 queries, one private copy per warp
           // (rows outside the segment get lse = +inf -> P = 0)
-#pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            const int qi = hh * 32 + lane;
-            const int r = t * BWD_QT + qi;
+          {
+            const int r = t * BWD_QT + wg * 32 + lane;
             float lv = INFINITY, dv = 0.f;
             if (r < sg.len && sg.start + r < p.q_tokens[sg.src]) {
               lv = lse_g[sg.start + r];
               dv = dv_g[sg.start + r];
               if (lv == -INFINITY) lv = INFINITY;
             }
-            s.lse[b][quad][qi] = lv * LOG2E;
-            s.dvec[b][quad][qi] = dv;
+            s.lse[b][warp][lane] = lv * LOG2E;
+            s.dvec[b][warp][lane] = dv;
           }
           __syncwarp();
           if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.sdp_full[b], (i >> 1) & 1, wc, 300))) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t t_st = tmem_base + lane_base + 256 + b * 64;
           const uint32_t t_dp = tmem_base + lane_base + 384 + b * 64;
-          float pv[64];
+          float pv[32];
+          uint32_t dp[32];
+          tmem_ld_x32(t_st + wg * 32, reinterpret_cast<uint32_t(&)[32]>(pv));
+          tmem_ld_x32(t_dp + wg * 32, dp);
+          tmem_wait_ld();
+          // visible iff key_c <= r + diag  <=>  r >= key_c - diag   (r relative to this half)
+          const int r_first = sg.causal ? (key_c - sg.diag - t * BWD_QT - wg * 32) : 0;
+          const float4* lse4 = reinterpret_cast<const float4*>(s.lse[b][warp]);
+          const float4* dv4 = reinterpret_cast<const float4*>(s.dvec[b][warp]);
+#pragma unroll
+          for (int c4 = 0; c4 < 8; ++c4) {
+            const float4 l = lse4[c4];
+            const float ls[4] = {l.x, l.y, l.z, l.w};
+#pragma unroll
+            for (int k2 = 0; k2 < 4; ++k2) {
+              const int c = c4 * 4 + k2;
+              float pr = fast_exp2(fmaf(pv[c], p.scale_log2, -ls[k2]));
+              pv[c] = (key_ok && c >= r_first) ? pr : 0.f;
+            }
+          }
           {
-            uint32_t(&raw)[64] = reinterpret_cast<uint32_t(&)[64]>(pv);
-            tmem_ld_x32(t_st, reinterpret_cast<uint32_t(&)[32]>(raw[0]));
-            tmem_ld_x32(t_st + 32, reinterpret_cast<uint32_t(&)[32]>(raw[32]));
-            tmem_wait_ld();
-          }
-          // visible iff key_c <= r + diag  <=>  r >= key_c - diag
-          const int r_first = sg.causal ? (key_c - sg.diag - t * BWD_QT) : 0;   // sub-tile relative
-#pragma unroll
-          for (int c = 0; c < 64; ++c) {
-            float pr = fast_exp2(fmaf(pv[c], p.scale_log2, -s.lse[b][quad][c]));
-            pr = (key_ok && c >= r_first) ? pr : 0.f;
-            pv[c] = pr;
-          }
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
             uint32_t pk[16];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) pk[c] = pack_bf16x2(pv[h * 32 + 2 * c], pv[h * 32 + 2 * c + 1]);
-            tmem_st_x16(t_st + h * 16, pk);
+            for (int c = 0; c < 16; ++c) pk[c] = pack_bf16x2(pv[2 * c], pv[2 * c + 1]);
+            // packed P^T of this half goes to the first 16 columns of this half's own S^T
+            // columns (the other warpgroup may still be reading its fp32 half)
+            tmem_st_x16(t_st + wg * 32, pk);
           }
           // dS^T = P^T * (dP^T - D)
           uint8_t* ds_row = s.ds[b];
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t dp[32];
-            tmem_ld_x32(t_dp + h * 32, dp);
-            tmem_wait_ld();
+          for (int ch = 0; ch < 4; ++ch) {          // 8 queries = one 16-byte chunk
+            const float4 da = dv4[ch * 2], db = dv4[ch * 2 + 1];
+            const float dd[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+            uint32_t w4[4];
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {      // 8 queries = one 16-byte chunk
-              uint32_t w4[4];
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                const int q0 = h * 32 + ch * 8 + 2 * c;
-                float d0 = pv[q0] * (__uint_as_float(dp[ch * 8 + 2 * c]) - s.dvec[b][quad][q0]);
-                float d1 = pv[q0 + 1] * (__uint_as_float(dp[ch * 8 + 2 * c + 1]) - s.dvec[b][quad][q0 + 1]);
-                d0 = pv[q0] == 0.f ? 0.f : d0;          // masked entries stay exactly zero
-                d1 = pv[q0 + 1] == 0.f ? 0.f : d1;
-                w4[c] = pack_bf16x2(d0, d1);
-              }
-              *reinterpret_cast<uint4*>(ds_row + sw128_offset(key_t, h * 4 + ch)) =
-                  make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            for (int c = 0; c < 4; ++c) {
+              const int q0 = ch * 8 + 2 * c;
+              float d0 = pv[q0] * (__uint_as_float(dp[q0]) - dd[2 * c]);
+              float d1 = pv[q0 + 1] * (__uint_as_float(dp[q0 + 1]) - dd[2 * c + 1]);
+              d0 = pv[q0] == 0.f ? 0.f : d0;          // masked entries stay exactly zero
+              d1 = pv[q0 + 1] == 0.f ? 0.f : d1;
+              w4[c] = pack_bf16x2(d0, d1);
             }
+            *reinterpret_cast<uint4*>(ds_row + sw128_offset(key_t, wg * 4 + ch)) =
+                make_uint4(w4[0], w4[1], w4[2], w4[3]);
           }
           tmem_wait_st();
           fence_proxy_async_smem();
