@@ -1,0 +1,87 @@
+"""Utilities, configuration, data carriers and model glue (CPU)."""
+import numpy as np
+import torch
+
+from ultraattn_b200 import patterns as P
+
+
+def test_reference_import_paths():
+    import comm_lib.comm_utils
+    import easy_context
+    import head_parallel_attn
+    import hierarchy_attn
+    import orchestrated_attn
+    import ring_flash_attn
+    import search_algo.bsa_config as bc
+    import search_algo.bsa_utils as bu
+    import search_algo.execute_plan as ep
+    import search_algo.search_engine as se
+    import search_algo.utils as su
+    from search_algo.dependent_graph import Comm_Kernel, Comp_Kernel, Dependent_Graph  # noqa: F401
+    from search_algo.graph_transformation_engine import Graph_Transformation_Engine  # noqa: F401
+    from search_algo.workload_partition import naive_allocate_strategy, solve_sparse_from_bsa  # noqa: F401
+    r = bc.BSA_Repr(bu.create_bsa_block_table(2), None)
+    cfg = bc.BSA_Config(None, None, {"bsa_repr": r, "CP": (4, 1)})
+    assert su.Block_Type.CAUSAL.value == 2 and r.block_table_raw[1, 1] is su.Block_Type.CAUSAL
+    assert cfg.to_string() == "CP=(4, 1)_repr=[[2000][1200][1020][1002]]"
+    assert bu.bsa_is_causal(bc.BSA_Config.create_causal((2, 1))) and not bu.bsa_is_dense(cfg)
+    assert hasattr(ep, "Execution_Plan") and hasattr(ep, "Fused_Execution_Plan") and hasattr(se, "Machine_Config")
+    assert callable(orchestrated_attn.orchestrated_attn_func) and callable(ring_flash_attn.stripe_flash_attn_func)
+    assert callable(head_parallel_attn.deepspeed_ulysses_attn_func) and callable(easy_context.prepare_seq_parallel_inputs)
+    assert len(bu.split_to_node_configs(bc.BSA_Config(None, None, {"bsa_repr": P.causal(1), "CP": (4, 2)}))) == 3
+    m = bu.get_b2f_suf_map(8)
+    assert "_ablation=(w/o_kernel_tile,Y=4,X=2,dim=0)" in m["_ablation=(w/o_kernel_tile,ILP)"]
+
+
+def test_utils():
+    from ultraattn_b200.utils.misc import FinitePriorityQueue, calc_flops, get_block_table_type, unique_list
+    q = FinitePriorityQueue(3)
+    for x in [5, 1, 9, 3, 7, 2]:
+        q.push(x)
+    assert q.items() == [1, 2, 3]
+    model, hw = calc_flops(1, 1024, 2, 128, causal=True, fob=1)
+    assert hw == 1.25 * model and model == 2 * 4 * 1024 * 1024 * 2 * 128 * 0.5
+    assert unique_list([1, 2, 1, 3, 2]) == [1, 2, 3]
+    assert get_block_table_type(np.array([[1, 0]])).name == "PARTIAL"
+
+
+def test_yaml_and_cli(tmp_path):
+    from ultraattn_b200.drivers.arguments import parse_args
+    cfg = parse_args(["--config", "configs/stream.yaml", "--Nhq", "8", "--exp-class", "bsa_infer"])
+    assert cfg.SP == (1, 8) and cfg.Nhq == 8 and cfg.exp_class == "bsa_infer"
+    assert cfg.pattern() == P.streaming(32, 1, 2)
+    from ultraattn_b200.drivers.exp_configs import step0_top_down_decompose
+    sp = step0_top_down_decompose("dense_train", max_intra=8, max_nodes=2, quick=True)
+    assert any(c.CP == (8, 2) for c in sp.inter_bsa_configs) and sp.intra_bsa_configs
+    assert all(s["S"][0] // 8 >= 256 for s in sp.shape_configs(8))
+
+
+def test_carriers_reduce():
+    from ultraattn_b200.ops.elementwise import lse_merge_reference
+    from ultraattn_b200.runtime.orchestrated import Input_Row_Bwd, Output_Col_Bwd, Output_Row_Fwd
+    a = Output_Row_Fwd.from_shapes(1, 8, 8, 2, 2, 16, torch.float32)
+    b = Output_Row_Fwd.from_shapes(1, 8, 8, 2, 2, 16, torch.float32)
+    for c in (a, b):
+        c.O.copy_(torch.randn_like(c.O))
+        c.lse.copy_(torch.randn_like(c.lse))
+    ref_o, ref_l = lse_merge_reference([(a.O[0].clone(), a.lse[0].clone()), (b.O[0], b.lse[0])])
+    a.reduce(b)
+    assert torch.allclose(a.O[0], ref_o, atol=1e-6) and torch.allclose(a.lse[0], ref_l, atol=1e-6)
+    assert a.data.dtype == torch.uint8 and a.data.is_contiguous()      # one flat buffer
+    r = Input_Row_Bwd.from_shapes(1, 8, 8, 2, 2, 16, torch.float32)
+    assert r.data.numel() == (2 * 8 * 2 * 16 + 2 * 2 * 8) * 4
+    g1 = Output_Col_Bwd.from_shapes(1, 8, 8, 2, 2, 16)
+    g2 = Output_Col_Bwd.from_shapes(1, 8, 8, 2, 2, 16)
+    g1.dK.fill_(1)
+    g2.dK.fill_(2)
+    g1.reduce(g2)
+    assert g1.dK.eq(3).all()
+
+
+def test_prepare_seq_parallel_inputs():
+    from ultraattn_b200.models.glue import prepare_seq_parallel_inputs
+    ids = torch.arange(16)[None]
+    out = prepare_seq_parallel_inputs("zigzag_ring_attn", ids, ids, ids, rank=1, world_size=2)
+    assert out["local_input_ids"].tolist() == [[4, 5, 6, 7, 8, 9, 10, 11]]
+    out = prepare_seq_parallel_inputs("stripe_attn", ids, ids, None, rank=1, world_size=4)
+    assert out["local_input_ids"].tolist() == [[1, 5, 9, 13]] and out["local_target_ids"] is None
