@@ -219,3 +219,26 @@ def test_model_ops(dev):
     E.adam_step(*ref, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1)
     _close(master, ref[0].to(dev), 1e-5)
     _close(param, ref[4].to(dev), 1e-2)
+
+
+def test_varlen_packed_attention(dev):
+    """Packed sequences of ragged lengths (document mask) through the same kernels."""
+    from ultraattn_b200.api import varlen_attention
+    torch.manual_seed(7)
+    cu = [0, 100, 421, 1000, 1024]
+    T, H = 1024, 2
+    q, k, v = (torch.randn(T, H, 128, device=dev, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+    d_o = torch.randn(T, H, 128, device=dev, dtype=torch.bfloat16)
+    o = varlen_attention(q, k, v, cu, causal=True)
+    o.backward(d_o)
+    mask = torch.zeros(T, T, dtype=torch.bool, device=dev)
+    for a, b in zip(cu[:-1], cu[1:]):
+        mask[a:b, a:b] = torch.tril(torch.ones(b - a, b - a, dtype=torch.bool, device=dev))
+    q2, k2, v2 = (t.detach().float().requires_grad_() for t in (q, k, v))
+    sc = torch.einsum("qhd,khd->hqk", q2, k2) / math.sqrt(128)
+    o2 = torch.einsum("hqk,khd->qhd", torch.softmax(sc.masked_fill(~mask, float("-inf")), -1), v2)
+    o2.backward(d_o.float())
+    _close(o, o2, 1e-2)
+    _close(q.grad, q2.grad, 2e-2)
+    _close(k.grad, k2.grad, 2e-2)
+    _close(v.grad, v2.grad, 2e-2)

@@ -85,3 +85,24 @@ def test_prepare_seq_parallel_inputs():
     assert out["local_input_ids"].tolist() == [[4, 5, 6, 7, 8, 9, 10, 11]]
     out = prepare_seq_parallel_inputs("stripe_attn", ids, ids, None, rank=1, world_size=4)
     assert out["local_input_ids"].tolist() == [[1, 5, 9, 13]] and out["local_target_ids"] is None
+
+
+def test_varlen_attention_cpu():
+    import math
+    from ultraattn_b200.api import varlen_attention
+    torch.manual_seed(0)
+    cu = [0, 37, 100, 228, 256]
+    T, H, D = 256, 2, 16
+    q, k, v = (torch.randn(T, H, D, requires_grad=True) for _ in range(3))
+    o = varlen_attention(q, k, v, cu, causal=True)
+    d_o = torch.randn_like(o)
+    o.backward(d_o)
+    mask = torch.zeros(T, T, dtype=torch.bool)
+    for a, b in zip(cu[:-1], cu[1:]):
+        mask[a:b, a:b] = torch.tril(torch.ones(b - a, b - a, dtype=torch.bool))
+    q2, k2, v2 = (t.detach().clone().requires_grad_() for t in (q, k, v))
+    s = (torch.einsum("qhd,khd->hqk", q2, k2) / math.sqrt(D)).masked_fill(~mask, float("-inf"))
+    o2 = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v2)
+    o2.backward(d_o)
+    for a, b in ((o, o2), (q.grad, q2.grad), (k.grad, k2.grad), (v.grad, v2.grad)):
+        assert (a - b).abs().max().item() < 1e-5

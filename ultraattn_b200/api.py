@@ -86,3 +86,52 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pattern: BSA_Re
     if runtime is not None:
         return runtime(q, k, v, softmax_scale)
     return _LocalAttention.apply(q, k, v, pattern, softmax_scale)
+
+
+# -------------------------------------------------------------------------------------------------
+# variable-length (packed) sequences
+# -------------------------------------------------------------------------------------------------
+def varlen_plans(cu_seqlens, causal: bool, device):
+    """Launch plans for a packed batch: sequence i occupies tokens cu_seqlens[i]..cu_seqlens[i+1]
+    of the packed [1, T, H, D] tensors and attends only itself (the document mask). This is the
+    role of the reference's ``_flash_attn_varlen_forward/backward`` call sites
+    (ring_flash_attn/ring_flash_attn_varlen.py:50-64, 116-137); no separate kernel is needed because
+    the kernels already take a list of (query block, key segments) work items."""
+    cu = [int(x) for x in cu_seqlens]
+    key = ("varlen", tuple(cu), causal, str(device))
+    if key not in _plan_cache:
+        rows, cols = [], []
+        for a, b in zip(cu[:-1], cu[1:]):
+            if b > a:
+                rows.append(A.Row(0, a, b - a, (A.Seg(0, a, b - a, causal, 0),), 0, a, False))
+                cols.append(A.Col(0, a, b - a, (A.Seg(0, a, b - a, causal, 0),), 0, a))
+        _plan_cache[key] = (A.FwdPlan(rows, device), A.BwdPlan(cols, device))
+    return _plan_cache[key]
+
+
+class _VarlenAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, causal, softmax_scale):
+        fplan, bplan = varlen_plans(cu_seqlens, causal, q.device)
+        o = torch.zeros_like(q)
+        lse = torch.full((q.shape[0], q.shape[2], q.shape[1]), float("-inf"), dtype=torch.float32, device=q.device)
+        A.attn_fwd([q], [k], [v], [(o, lse)], fplan, softmax_scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.bplan, ctx.scale = bplan, softmax_scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = local_backward(q, k, v, o, lse, d_o.contiguous(), ctx.bplan, ctx.scale)
+        return dq, dk, dv, None, None, None
+
+
+def varlen_attention(q, k, v, cu_seqlens, causal: bool = True, softmax_scale: Optional[float] = None):
+    """Attention over a packed batch ``[total_tokens, heads, head_dim]`` (or with a leading batch
+    dimension of 1) where ``cu_seqlens`` gives the sequence boundaries."""
+    squeeze = q.dim() == 3
+    if squeeze:
+        q, k, v = q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)
+    o = _VarlenAttention.apply(q, k, v, tuple(int(x) for x in cu_seqlens), causal, softmax_scale)
+    return o.squeeze(0) if squeeze else o
