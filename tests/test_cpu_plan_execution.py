@@ -27,7 +27,9 @@ def _worker(rank, world, port, case, ret):
         S, H, D = case["S"], case["H"], case["D"]
         kw = dict(pattern=pattern, cp=world, seq_len=S, n_heads=H, head_dim=D, allocation=case.get("allocation", "ilp"),
                   plan_type=case.get("plan_type", "ILP"), time_limit=case.get("time_limit", 5.0),
-                  kernel_tile=case.get("kernel_tile", False))
+                  kernel_tile=case.get("kernel_tile", False), cp_inter=case.get("cp_inter", 1))
+        if case.get("cp_inter", 1) > 1:
+            kw["cp"] = world // case["cp_inter"]
         plan_f = make_plan_collective(fob=0, **kw)     # rank 0 plans, everyone gets the same plan
         plan_b = make_plan_collective(fob=1, **kw)
         assert plan_f.verify() == [] and plan_b.verify() == []
@@ -97,7 +99,8 @@ def test_global_local_s4096_world2(plan_type):
     {"pattern": _pat_strided, "S": 1024, "H": 2, "D": 32, "plan_type": "Flexflow"},
     {"pattern": _pat_star, "S": 512, "H": 2, "D": 32, "plan_type": "Flexflow", "allocation": "naive"},
     {"pattern": _pat_causal, "S": 1024, "H": 2, "D": 32, "plan_type": "Flexflow", "kernel_tile": True},
-], ids=["causal", "strided", "star-naive", "causal-kernel-tile"])
+    {"pattern": _pat_strided, "S": 1024, "H": 2, "D": 32, "plan_type": "Flexflow", "cp_inter": 2},
+], ids=["causal", "strided", "star-naive", "causal-kernel-tile", "strided-two-level-2x2"])
 def test_patterns_world4(case):
     res = _run(4, case)
     for r in range(4):

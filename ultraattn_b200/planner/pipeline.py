@@ -15,12 +15,27 @@ def make_plan(pattern: BSA_Repr, cp: int, seq_len: int, n_heads: int, head_dim: 
               n_kv_heads: Optional[int] = None, batch: int = 1, fob: int = 0, *,
               allocation: str = "ilp", plan_type: str = "Flexflow", kernel_tile: bool = False,
               m_config: Optional[Machine_Config] = None, ParD: Optional[int] = None,
-              objective: str = "comm", time_limit: float = 30.0, cmap=None) -> Execution_Plan:
+              objective: str = "comm", time_limit: float = 30.0, cmap=None,
+              cp_inter: int = 1) -> Execution_Plan:
     """Plan one intra-node distributed attention call.
 
     ``allocation``: ``"ilp"`` (ILP #1) or ``"naive"`` (row owner). ``plan_type``: ``"ILP"`` or
     ``"Flexflow"``. ``kernel_tile``: try rectangle fusion and keep it if the makespan improves.
+    ``cp_inter`` > 1 plans two levels (``cp`` ranks per node, ``cp_inter`` nodes) and flattens them
+    into one plan over ``cp * cp_inter`` ranks (rank = node * cp + local rank).
     """
+    if cp_inter > 1:
+        from .hierarchy import flatten_two_level
+        two = BSA_Config(None, None, {"bsa_repr": pattern, "CP": (cp, cp_inter)})
+        alloc = flatten_two_level(two, fob=fob, time_limit=time_limit)
+        m_config = m_config or Machine_Config.b200_default()
+        flat = BSA_Config(None, None, {"bsa_repr": pattern, "CP": (cp * cp_inter, 1)})
+        shape = {"S": (seq_len, seq_len), "Nh": (n_heads, n_kv_heads or n_heads), "bs": batch, "D": head_dim}
+        da = Dist_Attn_Config.from_bsa_config(flat, shape, hierarchy=1)
+        graph = Dependent_Graph(get_cc_optimal_schedule_from_table(da, m_config, alloc), fob)
+        plan = Execution_Plan(graph, fob, plan_type, time_limit=time_limit)
+        plan.allocation = alloc
+        return plan
     m_config = m_config or Machine_Config.b200_default()
     cfg = BSA_Config(None, None, {"bsa_repr": pattern if cmap is None else BSA_Repr(pattern.block_table_int, cmap),
                                   "CP": (cp, 1)})
