@@ -181,7 +181,7 @@ class LlamaModel:
         self.flat = torch.zeros(total + pad, dtype=self.dtype, device=self.device)
         self.flat_grad = torch.zeros_like(self.flat)
         self.p: dict = {}
-        gen = torch.Generator(device="cpu").manual_seed(seed)
+        gen = torch.Generator(device=self.device).manual_seed(seed)
         off = 0
         for name, shape in shapes:
             n = math.prod(shape)
@@ -189,11 +189,11 @@ class LlamaModel:
             if "norm" in name:
                 view.fill_(1.0)
             else:
-                chunk = 1 << 24
+                chunk = 1 << 26
                 fl = view.view(-1)
-                for a in range(0, n, chunk):
+                for a in range(0, n, chunk):        # generated on the device, bounded temporaries
                     m = min(chunk, n - a)
-                    fl[a:a + m] = (torch.randn(m, generator=gen) * cfg.init_std).to(self.dtype).to(self.device)
+                    fl[a:a + m] = (torch.randn(m, generator=gen, device=self.device) * cfg.init_std).to(self.dtype)
             view.requires_grad_()
             view.grad = self.flat_grad[off:off + n].view(*shape)
             self.p[name] = view
