@@ -114,7 +114,8 @@ def main() -> None:
     torch.cuda.set_device(dev)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
 
     S = args.seq
     pattern = P.strided(N_BLOCKS, 4, 2)

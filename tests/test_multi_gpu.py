@@ -18,7 +18,9 @@ def _worker(rank, world, port, case, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
     try:
         from ultraattn_b200 import patterns as P
         from ultraattn_b200.ops import attention as A
@@ -90,7 +92,9 @@ def _ulysses_worker(rank, world, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
     try:
         from ultraattn_b200 import patterns as P
         from ultraattn_b200.ops import attention as A
@@ -110,9 +114,9 @@ def _ulysses_worker(rank, world, port, ret):
             torch.cuda.synchronize()
             A.check_status(dev)
             qkv = (x.float() @ wqkv.float().t()).to(torch.bfloat16).float()
-            q, k, v = (qkv[:, i * H * 128:(i + 1) * H * 128].view(1, S, H, 128) for i in range(3))
+            q, k, v = (qkv[:, i * H * 128:(i + 1) * H * 128].reshape(1, S, H, 128) for i in range(3))
             o, _ = P.dense_attention(q, k, v, P.causal(1).token_mask(S))
-            y_ref = o.to(torch.bfloat16).float().view(S, H * 128) @ wo.float().t()
+            y_ref = o.to(torch.bfloat16).float().reshape(S, H * 128) @ wo.float().t()
             err = (y.float().cpu() - y_ref[rank * S_loc:(rank + 1) * S_loc]).abs().max().item()
             worst = max(worst, err / (y_ref.abs().max().item() + 1e-6))
         ret[rank] = {"rel_err": worst}

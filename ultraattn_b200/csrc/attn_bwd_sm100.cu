@@ -5,28 +5,32 @@
 // forward's lse and D = rowsum(dO * O); O itself is never read.
 //
 // CTA = one 128-key tile of one key/value head. It keeps dK and dV for that tile in tensor memory
-// while it walks every 64-query sub-tile that attends to the tile (all query heads of the GQA
-// group, all query segments of the block column):
-//     S^T  = K Q^T                 (128 keys x 64 queries, TMEM)
+// while it walks every 128-query tile that attends to it (all query heads of the GQA group, all
+// query segments of the block column). Per step (128 keys x 128 queries):
+//     S^T  = K Q^T                 (128 x 128, TMEM)
 //     dP^T = V dO^T                (TMEM)
-//     P^T  = exp2(S^T * scale - lse)            -> bf16 into TMEM (A operand of the next GEMM)
-//     dS^T = P^T * (dP^T - D)                    -> bf16 into shared memory
+//     P^T  = exp2(S^T * scale - lse)            -> bf16 into TMEM (A operand of dV)
 //     dV  += P^T dO                (A from TMEM, B = dO as an N-major operand)
+//     dS^T = P^T * (dP^T - D)                    -> bf16 into shared memory
+//     dQ^T = K^T dS^T              (TMEM, where dP^T was; drained by a warpgroup: registers ->
+//                                   shared memory -> TMA reduce-add into the fp32 dQ accumulator)
 //     dK  += dS^T Q                (A from shared memory, B = Q as an N-major operand)
-//     dQ^T = K^T dS^T              (TMEM, drained by a second warpgroup: registers -> shared
-//                                   memory -> TMA reduce-add into the fp32 dQ accumulator)
 // Everything is computed transposed so that P^T and dS^T come out with keys on the TMEM lanes,
-// which is the layout the dV / dK products need for their A operand.
+// the layout the dV / dK products need for their A operand.
 //
-//   warps 0-7 : two softmax warpgroups; thread (key, half) handles 32 of the 64 query columns of
-//               its key row in every step; in the epilogue one warpgroup stores dK, the other dV
+// Every tcgen05.mma instruction costs about 94 clocks however small it is, so all five products
+// use N = 128 (40 instructions per step). That fills tensor memory (dK 128 | dV 128 | S^T 128 |
+// dP^T/dQ^T 128 columns), so nothing is double-buffered; instead the step is pipelined finely:
+// the softmax warps turn S^T into P^T while the tensor core computes dP^T, they turn dP^T into
+// dS^T while it computes dV, and the dQ^T drain overlaps dK and the next step's S^T.
+//
+//   warps 0-7 : two softmax warpgroups; thread (key, half) handles 64 of the 128 query columns of
+//               its key row; in the epilogue one warpgroup stores dK, the other dV
 //   warps 8-11: dQ drain warpgroup (one thread per head-dim element): each warp transposes its
-//               32 x 64 slice through shared memory and issues cp.reduce.async.bulk.tensor (fp32
-//               add at the memory side) into the dQ accumulator — this GPU's or, through a
-//               tensor map over a peer mapping, the owning GPU's
-//   warp  12  : TMA producer (K, V once; Q/dO sub-tile ring)
+//               32 x 128 slice through shared memory and issues cp.reduce.async.bulk.tensor (fp32
+//               add at the memory side) into the dQ accumulator
+//   warp  12  : TMA producer (K, V once; Q double-buffered; dO single-buffered)
 //   warp  13  : tcgen05.mma issuer, TMEM allocation
-// TMEM (512 columns): dK 128 | dV 128 | S^T/P^T x2 (64 each) | dP^T/dQ^T x2 (64 each).
 // dK/dV leave the CTA either as bf16 stores (the CTA is their only producer) or as fp32
 // red.add into an accumulator that may live in a peer GPU's memory (partial gradients of a
 // key/value block computed away from its owner).
@@ -39,10 +43,8 @@ namespace ua {
 constexpr int BWD_THREADS = 448;
 constexpr int BWD_TMA_WARP = 12;
 constexpr int BWD_MMA_WARP = 13;
-constexpr int BWD_QT = 64;                 // queries per sub-tile
-constexpr int BWD_STAGES = 3;              // Q/dO ring depth
-constexpr int BWD_KV_BYTES = ATTN_TILE * ATTN_D * 2;   // 32 KB
-constexpr int BWD_QT_BYTES = BWD_QT * ATTN_D * 2;      // 16 KB: [2 d-halves][64 rows][128 B]
+constexpr int BWD_QT = 128;                // queries per step
+constexpr int BWD_TILE_BYTES = ATTN_TILE * ATTN_D * 2;   // 32 KB: [2 halves][128 rows][128 B]
 
 struct BwdCol {
   int kv_src;     // slot in tmK / tmV
@@ -60,8 +62,8 @@ struct BwdCol {
 struct BwdParams {
   CUtensorMap tmK[ATTN_MAX_SRC];
   CUtensorMap tmV[ATTN_MAX_SRC];
-  CUtensorMap tmQ[ATTN_MAX_SRC];    // box of 64 rows
-  CUtensorMap tmdO[ATTN_MAX_SRC];   // box of 64 rows
+  CUtensorMap tmQ[ATTN_MAX_SRC];    // box of 128 rows
+  CUtensorMap tmdO[ATTN_MAX_SRC];   // box of 128 rows
   const float* lse_ptr[ATTN_MAX_SRC];
   const float* dvec_ptr[ATTN_MAX_SRC];
   long lse_head_stride[ATTN_MAX_SRC];
@@ -86,27 +88,31 @@ struct BwdParams {
 };
 
 struct __align__(1024) BwdSmem {
-  uint8_t k[BWD_KV_BYTES];
-  uint8_t v[BWD_KV_BYTES];
-  uint8_t q[BWD_STAGES][BWD_QT_BYTES];
-  uint8_t d_o[BWD_STAGES][BWD_QT_BYTES];
-  uint8_t ds[2][ATTN_TILE * BWD_QT * 2];   // dS^T: [128 keys][64 queries] bf16, 128-byte swizzle
+  uint8_t k[BWD_TILE_BYTES];
+  uint8_t v[BWD_TILE_BYTES];
+  uint8_t q[2][BWD_TILE_BYTES];
+  uint8_t d_o[BWD_TILE_BYTES];
+  uint8_t ds[BWD_TILE_BYTES];              // dS^T: two 64-query panels of [128 keys][128 B], swizzled
   float dq_stage[4][32 * 32];              // per drain warp: [32 queries][32 head-dim] fp32
-  float lse[2][8][32];        // per softmax warp copies (no cross-warp barrier needed)
-  float dvec[2][8][32];
+  float lse[8][64];                        // per softmax warp copies (no cross-warp barrier needed)
+  float dvec[8][64];
   uint64_t kv_full;
-  uint64_t qdo_full[BWD_STAGES];
-  uint64_t qdo_empty[BWD_STAGES];
-  uint64_t sdp_full[2];
-  uint64_t pds_full[2];
-  uint64_t dq_full[2];
-  uint64_t dq_free[2];
+  uint64_t q_full[2];
+  uint64_t q_empty[2];
+  uint64_t do_full;
+  uint64_t do_empty;
+  uint64_t s_full;       // S^T ready               (tcgen05.commit)
+  uint64_t dp_full;      // dP^T ready              (tcgen05.commit)
+  uint64_t p_ready;      // P^T written to TMEM     (256 softmax threads)
+  uint64_t ds_ready;     // dS^T written to smem    (256 softmax threads)
+  uint64_t dq_full;      // dQ^T ready              (tcgen05.commit)
+  uint64_t dq_free;      // dQ^T read out of TMEM   (128 drain threads)
   uint64_t dkv_full;
   uint32_t tmem_base;
   int abort_flag;
 };
 
-// First 64-query sub-tile of a segment that can see the key tile starting at column c0.
+// First 128-query tile of a segment that can see the key tile starting at column c0.
 __device__ __forceinline__ int seg_first_qt(const AttnSeg& sg, int c0) {
   if (!sg.causal) return 0;
   const int r_min = c0 - sg.diag;   // smallest query index that sees key c0
@@ -134,16 +140,18 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
 
   if (threadIdx.x == 0) {
     mbar_init(&s.kv_full, 1);
-    for (int i = 0; i < BWD_STAGES; ++i) {
-      mbar_init(&s.qdo_full[i], 1);
-      mbar_init(&s.qdo_empty[i], 1);
-    }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&s.sdp_full[i], 1);
-      mbar_init(&s.pds_full[i], 256);
-      mbar_init(&s.dq_full[i], 1);
-      mbar_init(&s.dq_free[i], 128);
+      mbar_init(&s.q_full[i], 1);
+      mbar_init(&s.q_empty[i], 1);
     }
+    mbar_init(&s.do_full, 1);
+    mbar_init(&s.do_empty, 1);
+    mbar_init(&s.s_full, 1);
+    mbar_init(&s.dp_full, 1);
+    mbar_init(&s.p_ready, 256);
+    mbar_init(&s.ds_ready, 256);
+    mbar_init(&s.dq_full, 1);
+    mbar_init(&s.dq_free, 128);
     mbar_init(&s.dkv_full, 1);
     s.abort_flag = 0;
     fence_mbar_init();
@@ -158,7 +166,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
   const uint32_t tmem_base = s.tmem_base;
   WaitCtx wc{&s.abort_flag, p.status, 4000000000ull};
 
-  // number of (head, segment, sub-tile) steps; identical in every role
+  // number of (head, segment, query tile) steps; identical in every role
   int steps_per_head = 0;
   for (int e = col.seg_begin; e < col.seg_end; ++e) {
     const AttnSeg sg = p.segs[e];
@@ -176,7 +184,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         report_error(wc, UA_ERR_FLAG_TIMEOUT, 120, col.kv_wait_flag);
         ok = false;
       }
-      mbar_arrive_expect_tx(&s.kv_full, 2 * BWD_KV_BYTES);
+      mbar_arrive_expect_tx(&s.kv_full, 2 * BWD_TILE_BYTES);
       tma_load_4d(s.k, &p.tmK[col.kv_src], &s.kv_full, 0, kv_head, krow, batch);
       tma_load_4d(s.k + 16384, &p.tmK[col.kv_src], &s.kv_full, 64, kv_head, krow, batch);
       tma_load_4d(s.v, &p.tmV[col.kv_src], &s.kv_full, 0, kv_head, krow, batch);
@@ -194,15 +202,16 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
             break;
           }
           for (int t = seg_first_qt(sg, c0); t < nq; ++t, ++i) {
-            const int st = i % BWD_STAGES;
-            const uint32_t ph = (i / BWD_STAGES) & 1;
-            if (!mbar_wait(&s.qdo_empty[st], ph ^ 1, wc, 100)) { ok = false; break; }
-            mbar_arrive_expect_tx(&s.qdo_full[st], 2 * BWD_QT_BYTES);
+            const int st = i & 1;
             const int qrow = sg.start + t * BWD_QT;
-            tma_load_4d(s.q[st], &p.tmQ[sg.src], &s.qdo_full[st], 0, head, qrow, batch);
-            tma_load_4d(s.q[st] + 8192, &p.tmQ[sg.src], &s.qdo_full[st], 64, head, qrow, batch);
-            tma_load_4d(s.d_o[st], &p.tmdO[sg.src], &s.qdo_full[st], 0, head, qrow, batch);
-            tma_load_4d(s.d_o[st] + 8192, &p.tmdO[sg.src], &s.qdo_full[st], 64, head, qrow, batch);
+            if (!mbar_wait(&s.q_empty[st], ((i >> 1) & 1) ^ 1, wc, 100)) { ok = false; break; }
+            mbar_arrive_expect_tx(&s.q_full[st], BWD_TILE_BYTES);
+            tma_load_4d(s.q[st], &p.tmQ[sg.src], &s.q_full[st], 0, head, qrow, batch);
+            tma_load_4d(s.q[st] + 16384, &p.tmQ[sg.src], &s.q_full[st], 64, head, qrow, batch);
+            if (!mbar_wait(&s.do_empty, (i & 1) ^ 1, wc, 101)) { ok = false; break; }
+            mbar_arrive_expect_tx(&s.do_full, BWD_TILE_BYTES);
+            tma_load_4d(s.d_o, &p.tmdO[sg.src], &s.do_full, 0, head, qrow, batch);
+            tma_load_4d(s.d_o + 16384, &p.tmdO[sg.src], &s.do_full, 64, head, qrow, batch);
           }
         }
       }
@@ -210,88 +219,88 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
   } else if (warp == BWD_MMA_WARP) {
     // =============================== MMA issuer =============================================
     if (lane == 0 && n_steps > 0) {
-      const uint32_t idesc_st = make_idesc_bf16(128, BWD_QT, 0, 0);   // S^T, dP^T
-      const uint32_t idesc_acc = make_idesc_bf16(128, 128, 0, 1);     // dV, dK (B N-major)
-      const uint32_t idesc_dq = make_idesc_bf16(128, BWD_QT, 1, 1);   // dQ^T (A, B MN-major)
+      const uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);   // S^T, dP^T: both K-major
+      const uint32_t idesc_kn = make_idesc_bf16(128, 128, 0, 1);   // dV, dK: B N-major
+      const uint32_t idesc_nn = make_idesc_bf16(128, 128, 1, 1);   // dQ^T: A, B MN-major
       const uint32_t t_dk = tmem_base + 0;
       const uint32_t t_dv = tmem_base + 128;
-      const uint32_t t_st[2] = {tmem_base + 256, tmem_base + 320};
-      const uint32_t t_dp[2] = {tmem_base + 384, tmem_base + 448};   // also dQ^T
+      const uint32_t t_st = tmem_base + 256;     // S^T, later P^T (packed) at columns 0-31, 64-95
+      const uint32_t t_dp = tmem_base + 384;     // dP^T, later dQ^T
       const uint32_t ka = smem_u32(s.k);
       const uint32_t va = smem_u32(s.v);
-      auto issue_st = [&](int b, int st) {
+      const uint32_t da = smem_u32(s.d_o);
+      const uint32_t dsa = smem_u32(s.ds);
+      auto issue_st = [&](int st) {
         const uint32_t qa = smem_u32(s.q[st]);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t offa = (kk >> 2) * 16384 + (kk & 3) * 32;
-          const uint32_t offb = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_ss(t_st[b], make_smem_desc_sw128(ka + offa, 16, 1024),
-                  make_smem_desc_sw128(qa + offb, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_ss(t_st, make_smem_desc_sw128(ka + off, 16, 1024),
+                  make_smem_desc_sw128(qa + off, 16, 1024), idesc_kk, kk > 0 ? 1u : 0u);
         }
       };
-      auto issue_dp = [&](int b, int st) {
-        const uint32_t da = smem_u32(s.d_o[st]);
+      auto issue_dp = [&]() {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t offa = (kk >> 2) * 16384 + (kk & 3) * 32;
-          const uint32_t offb = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_ss(t_dp[b], make_smem_desc_sw128(va + offa, 16, 1024),
-                  make_smem_desc_sw128(da + offb, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_ss(t_dp, make_smem_desc_sw128(va + off, 16, 1024),
+                  make_smem_desc_sw128(da + off, 16, 1024), idesc_kk, kk > 0 ? 1u : 0u);
         }
       };
       bool ok = true;
       do {
         if (!mbar_wait(&s.kv_full, 0, wc, 200)) { ok = false; break; }
-        // two steps of S^T / dP^T are kept in flight ahead of the accumulating products
-        for (int pre = 0; pre < 2 && pre < n_steps; ++pre) {
-          if (!mbar_wait(&s.qdo_full[pre], 0, wc, 201)) { ok = false; break; }
-          tc_fence_after_sync();
-          issue_st(pre, pre);
-          issue_dp(pre, pre);
-          tc_commit(&s.sdp_full[pre]);
-        }
-        if (!ok) break;
+        if (!mbar_wait(&s.q_full[0], 0, wc, 201)) { ok = false; break; }
+        tc_fence_after_sync();
+        issue_st(0);
+        tc_commit(&s.s_full);
+        if (!mbar_wait(&s.do_full, 0, wc, 202)) { ok = false; break; }
+        tc_fence_after_sync();
+        issue_dp();
+        tc_commit(&s.dp_full);
         for (int i = 0; i < n_steps; ++i) {
-          const int b = i & 1;
-          const int st = i % BWD_STAGES;
-          const uint32_t ph2 = (i >> 1) & 1;
-          if (!mbar_wait(&s.pds_full[b], ph2, wc, 204)) { ok = false; break; }
-          tc_fence_after_sync();
+          const int st = i & 1;
+          const uint32_t ph = i & 1;
           const uint32_t qa = smem_u32(s.q[st]);
-          const uint32_t da = smem_u32(s.d_o[st]);
-          const uint32_t dsa = smem_u32(s.ds[b]);
-          // dQ^T = K^T dS^T first, so that its drain overlaps the two products below.
-          // A = K as an M-major operand, B = dS^T as an N-major operand; lands where dP^T was.
+          // dV += P^T dO : A = P^T in TMEM (queries 0-63 packed at columns 0-31, 64-127 at 64-95),
+          // B = dO as an N-major operand (16 query rows = 2048 B, d-halves 16384 B apart)
+          if (!mbar_wait(&s.p_ready, ph, wc, 203)) { ok = false; break; }
+          tc_fence_after_sync();
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ss(t_dp[b], make_smem_desc_sw128(ka + kk * 2048, 16384, 1024),
-                    make_smem_desc_sw128(dsa + kk * 2048, 16, 1024), idesc_dq, kk > 0 ? 1u : 0u);
-          tc_commit(&s.dq_full[b]);
-          // dV += P^T dO : A = P^T in TMEM (16 queries = 8 packed columns per step; queries 0-31 are
-          // packed at columns 0-15, queries 32-63 at columns 32-47)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ts(t_dv, t_st[b] + (kk >> 1) * 32 + (kk & 1) * 8,
-                    make_smem_desc_sw128(da + kk * 2048, 8192, 1024),
-                    idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
-          // dK += dS^T Q : A = dS^T in shared memory (K-major over queries)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ss(t_dk, make_smem_desc_sw128(dsa + kk * 32, 16, 1024),
-                    make_smem_desc_sw128(qa + kk * 2048, 8192, 1024), idesc_acc,
+            umma_ts(t_dv, t_st + (kk >> 2) * 64 + (kk & 3) * 8,
+                    make_smem_desc_sw128(da + kk * 2048, 16384, 1024), idesc_kn,
                     (i > 0 || kk > 0) ? 1u : 0u);
-          tc_commit(&s.qdo_empty[st]);
-          if (i + 2 < n_steps) {
-            const int stn = (i + 2) % BWD_STAGES;
-            const uint32_t phn = ((i + 2) / BWD_STAGES) & 1;
-            if (!mbar_wait(&s.qdo_full[stn], phn, wc, 202)) { ok = false; break; }
+          tc_commit(&s.do_empty);
+          // dQ^T = K^T dS^T : A = K as an M-major operand, B = dS^T as an N-major operand (two
+          // 64-query panels 16384 B apart); lands where dP^T was
+          if (!mbar_wait(&s.ds_ready, ph, wc, 204)) { ok = false; break; }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(t_dp, make_smem_desc_sw128(ka + kk * 2048, 16384, 1024),
+                    make_smem_desc_sw128(dsa + kk * 2048, 16384, 1024), idesc_nn, kk > 0 ? 1u : 0u);
+          tc_commit(&s.dq_full);
+          // dK += dS^T Q : A = dS^T in shared memory (K-major over queries: panel kk/4, 32 B per
+          // step), B = Q as an N-major operand
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(t_dk, make_smem_desc_sw128(dsa + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                    make_smem_desc_sw128(qa + kk * 2048, 16384, 1024), idesc_kn,
+                    (i > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(&s.q_empty[st]);
+          if (i + 1 < n_steps) {
+            const int stn = (i + 1) & 1;
+            if (!mbar_wait(&s.q_full[stn], ((i + 1) >> 1) & 1, wc, 205)) { ok = false; break; }
             tc_fence_after_sync();
-            issue_st(b, stn);       // overwrites P^T(i), already consumed by dV(i) above
-            // dP^T(i+2) lands where dQ^T(i) is: wait until the drain warpgroup has read it
-            if (!mbar_wait(&s.dq_free[b], ph2, wc, 203)) { ok = false; break; }
+            issue_st(stn);          // overwrites P^T(i), already consumed by dV(i) above
+            tc_commit(&s.s_full);
+            if (!mbar_wait(&s.do_full, (i + 1) & 1, wc, 206)) { ok = false; break; }
+            // dP^T(i+1) lands where dQ^T(i) is: wait until the drain warpgroup has read it
+            if (!mbar_wait(&s.dq_free, ph, wc, 207)) { ok = false; break; }
             tc_fence_after_sync();
-            issue_dp(b, stn);
-            tc_commit(&s.sdp_full[b]);
+            issue_dp();
+            tc_commit(&s.dp_full);
           }
         }
         if (ok) tc_commit(&s.dkv_full);
@@ -299,15 +308,14 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     }
   } else if (warp < 8) {
     // =============================== softmax warpgroups =====================================
-    // the two warpgroups share every step: thread (key row, half) of warpgroup `half` handles the
-    // 32 query columns [32*half, 32*half+32) of its key row, which halves the serial work per
-    // step (a step's softmax is otherwise one long dependent instruction stream per warp)
-    const int wg = warp >> 2;                        // which half of the 64 query columns
+    const int wg = warp >> 2;                        // which half of the 128 query columns
     const int quad = warp & 3;
     const int key_t = quad * 32 + lane;              // key inside the tile
     const int key_c = c0 + key_t;                    // key inside the block column
     const bool key_ok = key_c < col.kv_len;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t t_st = tmem_base + lane_base + 256 + wg * 64;
+    const uint32_t t_dp = tmem_base + lane_base + 384 + wg * 64;
     const float LOG2E = 1.4426950408889634f;
     bool ok = true;
     uint32_t i = 0;
@@ -328,76 +336,90 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         const float* dv_g = p.dvec_ptr[sg.src] + batch * p.lse_batch_stride[sg.src] +
                             head * p.lse_head_stride[sg.src];
         for (int t = seg_first_qt(sg, c0); t < nq; ++t, ++i) {
-          const int b = i & 1;
-          // stage lse / D of this warp's 32 queries, one private copy per warp
+          const uint32_t ph = i & 1;
+          // lse / D of this warp's 64 queries, one private copy per warp
           // (rows outside the segment get lse = +inf -> P = 0)
-          {
-            const int r = t * BWD_QT + wg * 32 + lane;
+          __syncwarp();        // every lane is done reading the previous step's copy
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int r = t * BWD_QT + wg * 64 + hh * 32 + lane;
             float lv = INFINITY, dv = 0.f;
             if (r < sg.len && sg.start + r < p.q_tokens[sg.src]) {
               lv = lse_g[sg.start + r];
               dv = dv_g[sg.start + r];
               if (lv == -INFINITY) lv = INFINITY;
             }
-            s.lse[b][warp][lane] = lv * LOG2E;
-            s.dvec[b][warp][lane] = dv;
+            s.lse[warp][hh * 32 + lane] = lv * LOG2E;
+            s.dvec[warp][hh * 32 + lane] = dv;
           }
           __syncwarp();
-          if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.sdp_full[b], (i >> 1) & 1, wc, 300))) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint32_t t_st = tmem_base + lane_base + 256 + b * 64;
-          const uint32_t t_dp = tmem_base + lane_base + 384 + b * 64;
-          float pv[32];
-          uint32_t dp[32];
-          tmem_ld_x32(t_st + wg * 32, reinterpret_cast<uint32_t(&)[32]>(pv));
-          tmem_ld_x32(t_dp + wg * 32, dp);
-          tmem_wait_ld();
+          const float4* lse4 = reinterpret_cast<const float4*>(s.lse[warp]);
+          const float4* dv4 = reinterpret_cast<const float4*>(s.dvec[warp]);
           // visible iff key_c <= r + diag  <=>  r >= key_c - diag   (r relative to this half)
-          const int r_first = sg.causal ? (key_c - sg.diag - t * BWD_QT - wg * 32) : 0;
-          const float4* lse4 = reinterpret_cast<const float4*>(s.lse[b][warp]);
-          const float4* dv4 = reinterpret_cast<const float4*>(s.dvec[b][warp]);
+          const int r_first = sg.causal ? (key_c - sg.diag - t * BWD_QT - wg * 64) : 0;
+
+          // ---- phase A: P^T = exp2(S^T * scale - lse) -> TMEM (packed bf16) ----------------------
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.s_full, ph, wc, 300))) { ok = false; break; }
+          tc_fence_after_sync();
+          uint32_t pk[32];                 // this thread's 64 probabilities, packed; kept for phase B
 #pragma unroll
-          for (int c4 = 0; c4 < 8; ++c4) {
-            const float4 l = lse4[c4];
-            const float ls[4] = {l.x, l.y, l.z, l.w};
+          for (int h = 0; h < 2; ++h) {
+            float sv[32];
+            tmem_ld_x32(t_st + h * 32, reinterpret_cast<uint32_t(&)[32]>(sv));
+            tmem_wait_ld();
 #pragma unroll
-            for (int k2 = 0; k2 < 4; ++k2) {
-              const int c = c4 * 4 + k2;
-              float pr = fast_exp2(fmaf(pv[c], p.scale_log2, -ls[k2]));
-              pv[c] = (key_ok && c >= r_first) ? pr : 0.f;
+            for (int c4 = 0; c4 < 8; ++c4) {
+              const float4 l = lse4[h * 8 + c4];
+              const float ls[4] = {l.x, l.y, l.z, l.w};
+#pragma unroll
+              for (int k2 = 0; k2 < 4; ++k2) {
+                const int c = c4 * 4 + k2;
+                const float pr = fast_exp2(fmaf(sv[c], p.scale_log2, -ls[k2]));
+                sv[c] = (key_ok && (h * 32 + c) >= r_first) ? pr : 0.f;
+              }
             }
-          }
-          {
-            uint32_t pk[16];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) pk[c] = pack_bf16x2(pv[2 * c], pv[2 * c + 1]);
-            // packed P^T of this half goes to the first 16 columns of this half's own S^T
-            // columns (the other warpgroup may still be reading its fp32 half)
-            tmem_st_x16(t_st + wg * 32, pk);
+            for (int c = 0; c < 16; ++c) pk[h * 16 + c] = pack_bf16x2(sv[2 * c], sv[2 * c + 1]);
           }
-          // dS^T = P^T * (dP^T - D)
-          uint8_t* ds_row = s.ds[b];
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {          // 8 queries = one 16-byte chunk
-            const float4 da = dv4[ch * 2], db = dv4[ch * 2 + 1];
-            const float dd[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
-            uint32_t w4[4];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const int q0 = ch * 8 + 2 * c;
-              float d0 = pv[q0] * (__uint_as_float(dp[q0]) - dd[2 * c]);
-              float d1 = pv[q0 + 1] * (__uint_as_float(dp[q0 + 1]) - dd[2 * c + 1]);
-              d0 = pv[q0] == 0.f ? 0.f : d0;          // masked entries stay exactly zero
-              d1 = pv[q0 + 1] == 0.f ? 0.f : d1;
-              w4[c] = pack_bf16x2(d0, d1);
-            }
-            *reinterpret_cast<uint4*>(ds_row + sw128_offset(key_t, wg * 4 + ch)) =
-                make_uint4(w4[0], w4[1], w4[2], w4[3]);
-          }
+          // packed P^T of this half goes to the first 32 columns of this half's own S^T columns
+          // (the other warpgroup may still be reading its fp32 half)
+          tmem_st_x32(t_st, pk);
           tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(&s.p_ready);
+
+          // ---- phase B: dS^T = P^T * (dP^T - D) -> shared memory ------------------------------
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.dp_full, ph, wc, 301))) { ok = false; break; }
+          tc_fence_after_sync();
+          uint8_t* ds_panel = s.ds + wg * 16384;     // this half's 64-query panel
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t dp[32];
+            tmem_ld_x32(t_dp + h * 32, dp);
+            tmem_wait_ld();
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {          // 8 queries = one 16-byte chunk
+              const float4 da4 = dv4[h * 8 + ch * 2], db4 = dv4[h * 8 + ch * 2 + 1];
+              const float dd[8] = {da4.x, da4.y, da4.z, da4.w, db4.x, db4.y, db4.z, db4.w};
+              uint32_t w4[4];
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                const uint32_t pw = pk[h * 16 + ch * 4 + c];
+                const float p0 = __uint_as_float(pw << 16);
+                const float p1 = __uint_as_float(pw & 0xFFFF0000u);
+                float d0 = p0 * (__uint_as_float(dp[ch * 8 + 2 * c]) - dd[2 * c]);
+                float d1 = p1 * (__uint_as_float(dp[ch * 8 + 2 * c + 1]) - dd[2 * c + 1]);
+                d0 = p0 == 0.f ? 0.f : d0;              // masked entries stay exactly zero
+                d1 = p1 == 0.f ? 0.f : d1;
+                w4[c] = pack_bf16x2(d0, d1);
+              }
+              *reinterpret_cast<uint4*>(ds_panel + sw128_offset(key_t, h * 4 + ch)) =
+                  make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+          }
           fence_proxy_async_smem();
           tc_fence_before_sync();
-          mbar_arrive(&s.pds_full[b]);
+          mbar_arrive(&s.ds_ready);
         }
       }
     }
@@ -455,6 +477,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     // =============================== dQ drain warpgroup =====================================
     const int quad = warp & 3;                       // TMEM lanes quad*32.. = head-dim slice
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t t_dq = tmem_base + lane_base + 384;
     float* stage = s.dq_stage[quad];
     bool ok = true;
     uint32_t i = 0;
@@ -465,26 +488,24 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         const int nq = seg_num_qt(sg);
         const CUtensorMap* tdq = &p.tmdQ[sg.src];
         for (int t = seg_first_qt(sg, c0); t < nq; ++t, ++i) {
-          const int b = i & 1;
-          if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.dq_full[b], (i >> 1) & 1, wc, 400))) { ok = false; break; }
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.dq_full, i & 1, wc, 400))) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t t_dq = tmem_base + lane_base + 384 + b * 64;
-          uint32_t dv0[32], dv1[32];
-          tmem_ld_x32(t_dq, dv0);
-          tmem_ld_x32(t_dq + 32, dv1);
-          tmem_wait_ld();
-          // TMEM buffer read: hand it back before the slower shared-memory / TMA part
-          tc_fence_before_sync();
-          mbar_arrive(&s.dq_free[b]);
           const int qrow = sg.start + t * BWD_QT;
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
+#pragma unroll 1
+          for (int h = 0; h < 4; ++h) {              // 32 queries at a time
+            uint32_t dv[32];
+            tmem_ld_x32(t_dq + h * 32, dv);
+            tmem_wait_ld();
+            if (h == 3) {
+              // the whole TMEM buffer has been read: hand it back before the slower part
+              tc_fence_before_sync();
+              mbar_arrive(&s.dq_free);
+            }
             // the previous reduce must have finished reading the staging buffer
             if (lane == 0) tma_store_wait_read_all();
             __syncwarp();
 #pragma unroll
-            for (int c = 0; c < 32; ++c)
-              stage[c * 32 + lane] = __uint_as_float(h == 0 ? dv0[c] : dv1[c]) * p.scale;
+            for (int c = 0; c < 32; ++c) stage[c * 32 + lane] = __uint_as_float(dv[c]) * p.scale;
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {

@@ -44,7 +44,8 @@ def main() -> None:
     group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
         group = dist.group.WORLD
     cfg = LlamaConfig(n_layers=a.layers, hidden=a.hidden, n_heads=a.heads, head_dim=128, ffn=a.ffn, vocab=a.vocab)
     pattern = P.global_local(a.blocks, 1, 2)

@@ -284,7 +284,7 @@ def rows_from_block_table(table: np.ndarray, block: int, kv_block: int | None = 
 # =================================================================================================
 # backward
 # =================================================================================================
-BWD_QT = 64
+BWD_QT = 128
 
 
 def _col_steps(c: Col, c0: int) -> int:

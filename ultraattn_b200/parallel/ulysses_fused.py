@@ -66,9 +66,9 @@ class FusedUlyssesAttention:
         sp.barrier(5)                       # all head groups of all tokens have arrived
         buf = sp.local("qkv")
         nq, nk = self.hq * D, self.hk * D
-        q = buf[:, :nq].view(self.S, self.hq, D)
-        k = buf[:, nq:nq + nk].view(self.S, self.hk, D)
-        v = buf[:, nq + nk:].view(self.S, self.hk, D)
+        q = buf[:, :nq].unflatten(1, (self.hq, D))
+        k = buf[:, nq:nq + nk].unflatten(1, (self.hk, D))
+        v = buf[:, nq + nk:].unflatten(1, (self.hk, D))
         if cos is not None:
             pos = torch.arange(self.S, device=self.device, dtype=torch.int32)
             E.rope(q, cos, sin, pos, out=q)
