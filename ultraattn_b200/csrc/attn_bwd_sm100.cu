@@ -18,11 +18,13 @@
 // Everything is computed transposed so that P^T and dS^T come out with keys on the TMEM lanes,
 // the layout the dV / dK products need for their A operand.
 //
-// Every tcgen05.mma instruction costs about 94 clocks however small it is, so all five products
-// use N = 128 (40 instructions per step). That fills tensor memory (dK 128 | dV 128 | S^T 128 |
-// dP^T/dQ^T 128 columns), so nothing is double-buffered; instead the step is pipelined finely:
-// the softmax warps turn S^T into P^T while the tensor core computes dP^T, they turn dP^T into
-// dS^T while it computes dV, and the dQ^T drain overlaps dK and the next step's S^T.
+// All five products use N = 128 (40 instructions of 64 tensor-pipe clocks per step). That fills
+// tensor memory (dK 128 | dV 128 | S^T 128 | dP^T/dQ^T 128 columns), so nothing is double-buffered;
+// instead the issue order keeps the softmax warps fed: S^T of the next step is issued right behind
+// dV of this one (the tensor pipe runs in issue order, so it may overwrite P^T), which makes it
+// ready while the warps still turn dP^T into dS^T; dK fills the time the drain warpgroup needs to
+// read dQ^T out before dP^T of the next step may overwrite it. lse and D of the next step are
+// fetched into registers one step ahead.
 //
 //   warps 0-7 : two softmax warpgroups; thread (key, half) handles 64 of the 128 query columns of
 //               its key row; in the epilogue one warpgroup stores dK, the other dV
@@ -120,6 +122,70 @@ __device__ __forceinline__ int seg_first_qt(const AttnSeg& sg, int c0) {
 }
 __device__ __forceinline__ int seg_num_qt(const AttnSeg& sg) {
   return (sg.len + BWD_QT - 1) / BWD_QT;
+}
+
+
+// Walks the (query head of the group, query segment, 128-query tile) steps of one key tile in the
+// order every role of the CTA uses.
+struct BwdStepIter {
+  int g, e, t, nq;
+  bool new_seg;      // first step of a (head, segment) pair
+  AttnSeg sg;
+  __device__ __forceinline__ void seek(const BwdParams& p, const BwdCol& col, int c0) {
+    // (g, e) valid; find the next segment with work from here on
+    for (;;) {
+      sg = p.segs[e];
+      nq = seg_num_qt(sg);
+      t = seg_first_qt(sg, c0);
+      if (t < nq) return;
+      if (++e >= col.seg_end) { e = col.seg_begin; ++g; }
+      if (g >= p.kv_group) return;     // callers never step past the last step
+    }
+  }
+  __device__ __forceinline__ void first(const BwdParams& p, const BwdCol& col, int c0) {
+    g = 0; e = col.seg_begin; new_seg = true;
+    seek(p, col, c0);
+  }
+  __device__ __forceinline__ void next(const BwdParams& p, const BwdCol& col, int c0) {
+    new_seg = false;
+    if (++t < nq) return;
+    new_seg = true;
+    if (++e >= col.seg_end) { e = col.seg_begin; ++g; }
+    if (g < p.kv_group) seek(p, col, c0);
+  }
+};
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// P^T of one thread's 64 queries: exp2(S^T * scale + (-lse)), packed to bf16 pairs. MASK applies
+// the causal / key-tail mask (tiles that need none skip the compares).
+template <bool MASK>
+__device__ __forceinline__ void bwd_phase_a(uint32_t t_st, const float4* nlse4, float scale_log2,
+                                            bool key_ok, int r_first, uint32_t (&pk)[32]) {
+  float sv[2][32];
+  tmem_ld_x32(t_st, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
+  tmem_ld_x32(t_st + 32, reinterpret_cast<uint32_t(&)[32]>(sv[1]));
+  tmem_wait_ld();
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+#pragma unroll
+    for (int c4 = 0; c4 < 8; ++c4) {
+      const float4 l = nlse4[h * 8 + c4];
+      const float ls[4] = {l.x, l.y, l.z, l.w};
+#pragma unroll
+      for (int k2 = 0; k2 < 4; ++k2) {
+        const int c = c4 * 4 + k2;
+        const float pr = fast_exp2(fmaf(sv[h][c], scale_log2, ls[k2]));
+        sv[h][c] = (!MASK || (key_ok && (h * 32 + c) >= r_first)) ? pr : 0.f;
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 16; ++c) pk[h * 16 + c] = pack_bf16x2(sv[h][2 * c], sv[h][2 * c + 1]);
+  }
 }
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -262,6 +328,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
           const int st = i & 1;
           const uint32_t ph = i & 1;
           const uint32_t qa = smem_u32(s.q[st]);
+          const bool more = i + 1 < n_steps;
           // dV += P^T dO : A = P^T in TMEM (queries 0-63 packed at columns 0-31, 64-127 at 64-95),
           // B = dO as an N-major operand (16 query rows = 2048 B, d-halves 16384 B apart)
           if (!mbar_wait(&s.p_ready, ph, wc, 203)) { ok = false; break; }
@@ -272,6 +339,14 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
                     make_smem_desc_sw128(da + kk * 2048, 16384, 1024), idesc_kn,
                     (i > 0 || kk > 0) ? 1u : 0u);
           tc_commit(&s.do_empty);
+          // S^T of the next step right behind it: it overwrites P^T(i), which dV(i) reads first
+          // because the tensor pipe executes in issue order
+          if (more) {
+            if (!mbar_wait(&s.q_full[st ^ 1], ((i + 1) >> 1) & 1, wc, 205)) { ok = false; break; }
+            tc_fence_after_sync();
+            issue_st(st ^ 1);
+            tc_commit(&s.s_full);
+          }
           // dQ^T = K^T dS^T : A = K as an M-major operand, B = dS^T as an N-major operand (two
           // 64-query panels 16384 B apart); lands where dP^T was
           if (!mbar_wait(&s.ds_ready, ph, wc, 204)) { ok = false; break; }
@@ -282,19 +357,14 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
                     make_smem_desc_sw128(dsa + kk * 2048, 16384, 1024), idesc_nn, kk > 0 ? 1u : 0u);
           tc_commit(&s.dq_full);
           // dK += dS^T Q : A = dS^T in shared memory (K-major over queries: panel kk/4, 32 B per
-          // step), B = Q as an N-major operand
+          // step), B = Q as an N-major operand; runs while the drain warpgroup reads dQ^T
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
             umma_ss(t_dk, make_smem_desc_sw128(dsa + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
                     make_smem_desc_sw128(qa + kk * 2048, 16384, 1024), idesc_kn,
                     (i > 0 || kk > 0) ? 1u : 0u);
           tc_commit(&s.q_empty[st]);
-          if (i + 1 < n_steps) {
-            const int stn = (i + 1) & 1;
-            if (!mbar_wait(&s.q_full[stn], ((i + 1) >> 1) & 1, wc, 205)) { ok = false; break; }
-            tc_fence_after_sync();
-            issue_st(stn);          // overwrites P^T(i), already consumed by dV(i) above
-            tc_commit(&s.s_full);
+          if (more) {
             if (!mbar_wait(&s.do_full, (i + 1) & 1, wc, 206)) { ok = false; break; }
             // dP^T(i+1) lands where dQ^T(i) is: wait until the drain warpgroup has read it
             if (!mbar_wait(&s.dq_free, ph, wc, 207)) { ok = false; break; }
@@ -318,110 +388,108 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     const uint32_t t_dp = tmem_base + lane_base + 384 + wg * 64;
     const float LOG2E = 1.4426950408889634f;
     bool ok = true;
-    uint32_t i = 0;
-    for (int g = 0; g < p.kv_group && ok; ++g) {
-      const int head = kv_head * p.kv_group + g;
-      for (int e = col.seg_begin; e < col.seg_end && ok; ++e) {
-        const AttnSeg sg = p.segs[e];
-        const int nq = seg_num_qt(sg);
-        if (sg.wait_flag != 0) {
-          // lse / D of a staged segment are read with plain loads below: make sure they landed
-          int w_ok = 1;
-          if (lane == 0) w_ok = wait_staged(p.stage.flags, sg.wait_flag, sg.wait_count * p.stage.epoch, wc.budget_ns) ? 1 : 0;
-          w_ok = __shfl_sync(0xFFFFFFFFu, w_ok, 0);
-          if (!w_ok) { ok = false; break; }
-        }
-        const float* lse_g = p.lse_ptr[sg.src] + batch * p.lse_batch_stride[sg.src] +
-                             head * p.lse_head_stride[sg.src];
-        const float* dv_g = p.dvec_ptr[sg.src] + batch * p.lse_batch_stride[sg.src] +
-                            head * p.lse_head_stride[sg.src];
-        for (int t = seg_first_qt(sg, c0); t < nq; ++t, ++i) {
-          const uint32_t ph = i & 1;
-          // lse / D of this warp's 64 queries, one private copy per warp
-          // (rows outside the segment get lse = +inf -> P = 0)
-          __syncwarp();        // every lane is done reading the previous step's copy
+    // lse / D of the 64 queries of this warp for one step, two per lane; fetched one step ahead
+    // (rows outside the segment get lse = +inf -> P = 0)
+    auto fetch = [&](const BwdStepIter& it, float (&lv)[2], float (&dv)[2]) -> bool {
+      const AttnSeg& sg = it.sg;
+      if (it.new_seg && sg.wait_flag != 0) {
+        // lse / D of a staged segment are read with plain loads: make sure they landed
+        int w_ok = 1;
+        if (lane == 0) w_ok = wait_staged(p.stage.flags, sg.wait_flag, sg.wait_count * p.stage.epoch, wc.budget_ns) ? 1 : 0;
+        w_ok = __shfl_sync(0xFFFFFFFFu, w_ok, 0);
+        if (!w_ok) return false;
+      }
+      const int head = kv_head * p.kv_group + it.g;
+      const long off = batch * p.lse_batch_stride[sg.src] + head * p.lse_head_stride[sg.src];
+      const float* lse_g = p.lse_ptr[sg.src] + off;
+      const float* dv_g = p.dvec_ptr[sg.src] + off;
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            const int r = t * BWD_QT + wg * 64 + hh * 32 + lane;
-            float lv = INFINITY, dv = 0.f;
-            if (r < sg.len && sg.start + r < p.q_tokens[sg.src]) {
-              lv = lse_g[sg.start + r];
-              dv = dv_g[sg.start + r];
-              if (lv == -INFINITY) lv = INFINITY;
-            }
-            s.lse[warp][hh * 32 + lane] = lv * LOG2E;
-            s.dvec[warp][hh * 32 + lane] = dv;
-          }
-          __syncwarp();
-          const float4* lse4 = reinterpret_cast<const float4*>(s.lse[warp]);
-          const float4* dv4 = reinterpret_cast<const float4*>(s.dvec[warp]);
-          // visible iff key_c <= r + diag  <=>  r >= key_c - diag   (r relative to this half)
-          const int r_first = sg.causal ? (key_c - sg.diag - t * BWD_QT - wg * 64) : 0;
-
-          // ---- phase A: P^T = exp2(S^T * scale - lse) -> TMEM (packed bf16) ----------------------
-          if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.s_full, ph, wc, 300))) { ok = false; break; }
-          tc_fence_after_sync();
-          uint32_t pk[32];                 // this thread's 64 probabilities, packed; kept for phase B
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            float sv[32];
-            tmem_ld_x32(t_st + h * 32, reinterpret_cast<uint32_t(&)[32]>(sv));
-            tmem_wait_ld();
-#pragma unroll
-            for (int c4 = 0; c4 < 8; ++c4) {
-              const float4 l = lse4[h * 8 + c4];
-              const float ls[4] = {l.x, l.y, l.z, l.w};
-#pragma unroll
-              for (int k2 = 0; k2 < 4; ++k2) {
-                const int c = c4 * 4 + k2;
-                const float pr = fast_exp2(fmaf(sv[c], p.scale_log2, -ls[k2]));
-                sv[c] = (key_ok && (h * 32 + c) >= r_first) ? pr : 0.f;
-              }
-            }
-#pragma unroll
-            for (int c = 0; c < 16; ++c) pk[h * 16 + c] = pack_bf16x2(sv[2 * c], sv[2 * c + 1]);
-          }
-          // packed P^T of this half goes to the first 32 columns of this half's own S^T columns
-          // (the other warpgroup may still be reading its fp32 half)
-          tmem_st_x32(t_st, pk);
-          tmem_wait_st();
-          tc_fence_before_sync();
-          mbar_arrive(&s.p_ready);
-
-          // ---- phase B: dS^T = P^T * (dP^T - D) -> shared memory ------------------------------
-          if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.dp_full, ph, wc, 301))) { ok = false; break; }
-          tc_fence_after_sync();
-          uint8_t* ds_panel = s.ds + wg * 16384;     // this half's 64-query panel
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t dp[32];
-            tmem_ld_x32(t_dp + h * 32, dp);
-            tmem_wait_ld();
-#pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {          // 8 queries = one 16-byte chunk
-              const float4 da4 = dv4[h * 8 + ch * 2], db4 = dv4[h * 8 + ch * 2 + 1];
-              const float dd[8] = {da4.x, da4.y, da4.z, da4.w, db4.x, db4.y, db4.z, db4.w};
-              uint32_t w4[4];
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                const uint32_t pw = pk[h * 16 + ch * 4 + c];
-                const float p0 = __uint_as_float(pw << 16);
-                const float p1 = __uint_as_float(pw & 0xFFFF0000u);
-                float d0 = p0 * (__uint_as_float(dp[ch * 8 + 2 * c]) - dd[2 * c]);
-                float d1 = p1 * (__uint_as_float(dp[ch * 8 + 2 * c + 1]) - dd[2 * c + 1]);
-                d0 = p0 == 0.f ? 0.f : d0;              // masked entries stay exactly zero
-                d1 = p1 == 0.f ? 0.f : d1;
-                w4[c] = pack_bf16x2(d0, d1);
-              }
-              *reinterpret_cast<uint4*>(ds_panel + sw128_offset(key_t, h * 4 + ch)) =
-                  make_uint4(w4[0], w4[1], w4[2], w4[3]);
-            }
-          }
-          fence_proxy_async_smem();
-          tc_fence_before_sync();
-          mbar_arrive(&s.ds_ready);
+      for (int hh = 0; hh < 2; ++hh) {
+        const int r = it.t * BWD_QT + wg * 64 + hh * 32 + lane;
+        lv[hh] = INFINITY;
+        dv[hh] = 0.f;
+        if (r < sg.len && sg.start + r < p.q_tokens[sg.src]) {
+          lv[hh] = lse_g[sg.start + r];
+          dv[hh] = dv_g[sg.start + r];
+          if (lv[hh] == -INFINITY) lv[hh] = INFINITY;
         }
       }
+      return true;
+    };
+    BwdStepIter cur;
+    float lv[2], dv[2];
+    if (n_steps > 0) {
+      cur.first(p, col, c0);
+      ok = fetch(cur, lv, dv);
+    }
+    for (int i = 0; i < n_steps && ok; ++i) {
+      const uint32_t ph = i & 1;
+      const AttnSeg& sg = cur.sg;
+      __syncwarp();        // every lane is done reading the previous step's copy
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        s.lse[warp][hh * 32 + lane] = -lv[hh] * LOG2E;
+        s.dvec[warp][hh * 32 + lane] = dv[hh];
+      }
+      __syncwarp();
+      // visible iff key_c <= r + diag  <=>  r >= key_c - diag   (r relative to this half)
+      const int r_first = sg.causal ? (key_c - sg.diag - cur.t * BWD_QT - wg * 64) : 0;
+      // the next step's lse / D travel while this step computes
+      BwdStepIter nxt = cur;
+      if (i + 1 < n_steps) {
+        nxt.next(p, col, c0);
+        if (!fetch(nxt, lv, dv)) { ok = false; break; }
+      }
+      const float4* nlse4 = reinterpret_cast<const float4*>(s.lse[warp]);
+      const float4* dv4 = reinterpret_cast<const float4*>(s.dvec[warp]);
+
+      // ---- phase A: P^T = exp2(S^T * scale - lse) -> TMEM (packed bf16) ----------------------
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.s_full, ph, wc, 300))) { ok = false; break; }
+      tc_fence_after_sync();
+      uint32_t pk[32];                 // this thread's 64 probabilities, packed; kept for phase B
+      if (__all_sync(0xFFFFFFFFu, key_ok && r_first <= 0))
+        bwd_phase_a<false>(t_st, nlse4, p.scale_log2, key_ok, r_first, pk);
+      else
+        bwd_phase_a<true>(t_st, nlse4, p.scale_log2, key_ok, r_first, pk);
+      // packed P^T of this half goes to the first 32 columns of this half's own S^T columns
+      // (the other warpgroup may still be reading its fp32 half)
+      tmem_st_x32(t_st, pk);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&s.p_ready);
+
+      // ---- phase B: dS^T = P^T * (dP^T - D) -> shared memory ------------------------------
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.dp_full, ph, wc, 301))) { ok = false; break; }
+      tc_fence_after_sync();
+      uint8_t* ds_panel = s.ds + wg * 16384;     // this half's 64-query panel
+      {
+        uint32_t dp[2][32];
+        tmem_ld_x32(t_dp, dp[0]);
+        tmem_ld_x32(t_dp + 32, dp[1]);
+        tmem_wait_ld();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {          // 8 queries = one 16-byte chunk
+            const float4 da4 = dv4[h * 8 + ch * 2], db4 = dv4[h * 8 + ch * 2 + 1];
+            const float dd[8] = {da4.x, da4.y, da4.z, da4.w, db4.x, db4.y, db4.z, db4.w};
+            uint32_t w4[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              // (dP - D) rounded to bf16 pairs, times the bf16 probabilities (masked ones are 0)
+              const uint32_t x = pack_bf16x2(__uint_as_float(dp[h][ch * 8 + 2 * c]) - dd[2 * c],
+                                             __uint_as_float(dp[h][ch * 8 + 2 * c + 1]) - dd[2 * c + 1]);
+              w4[c] = mul_bf16x2(pk[h * 16 + ch * 4 + c], x);
+            }
+            *reinterpret_cast<uint4*>(ds_panel + sw128_offset(key_t, h * 4 + ch)) =
+                make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&s.ds_ready);
+      cur = nxt;
     }
     // ---------------------------------- dK / dV epilogue ------------------------------------
     if (n_steps > 0 && ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait(&s.dkv_full, 0, wc, 310));
@@ -492,25 +560,29 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
           tc_fence_after_sync();
           const int qrow = sg.start + t * BWD_QT;
 #pragma unroll 1
-          for (int h = 0; h < 4; ++h) {              // 32 queries at a time
-            uint32_t dv[32];
-            tmem_ld_x32(t_dq + h * 32, dv);
+          for (int hp = 0; hp < 2; ++hp) {           // two chunks of 32 queries per TMEM read
+            uint32_t dv[2][32];
+            tmem_ld_x32(t_dq + hp * 64, dv[0]);
+            tmem_ld_x32(t_dq + hp * 64 + 32, dv[1]);
             tmem_wait_ld();
-            if (h == 3) {
+            if (hp == 1) {
               // the whole TMEM buffer has been read: hand it back before the slower part
               tc_fence_before_sync();
               mbar_arrive(&s.dq_free);
             }
-            // the previous reduce must have finished reading the staging buffer
-            if (lane == 0) tma_store_wait_read_all();
-            __syncwarp();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) stage[c * 32 + lane] = __uint_as_float(dv[c]) * p.scale;
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_reduce_add_4d(tdq, stage, quad * 32, head, qrow + h * 32, batch);
-              tma_store_commit();
+            for (int h2 = 0; h2 < 2; ++h2) {
+              // the previous reduce must have finished reading the staging buffer
+              if (lane == 0) tma_store_wait_read_all();
+              __syncwarp();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) stage[c * 32 + lane] = __uint_as_float(dv[h2][c]) * p.scale;
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_reduce_add_4d(tdq, stage, quad * 32, head, qrow + (hp * 2 + h2) * 32, batch);
+                tma_store_commit();
+              }
             }
           }
         }

@@ -9,6 +9,11 @@
 // NCCL all-reduce issued only to line the ranks up before timing (search_algo/benchmark.py:593-594)
 // and 1-element warm-up all-reduces (tests/distributed/device_communicators/pynccl.py:195-199).
 //
+// ua_multimem_bcast / ua_multimem_reduce: NVLS primitives on the multicast address of a symmetric
+// buffer (one-to-all block broadcast, all-to-one gradient reduction, one-shot all-reduce); they
+// replace the reference's per-peer ncclSend/ncclRecv fan-out of shared blocks
+// (orchestrated_attn/orchestrated_attn_impl.py:103-141) and its ring all-reduce call sites.
+//
 // ua_wait_flag: waits (bounded) for a single 32-bit flag; used by tests of the time-out path: a
 // flag that nothing sets makes the wait run out and the status word is checked on the host.
 #include "host_common.cuh"
@@ -96,6 +101,49 @@ peer_add_kernel(float* __restrict__ dst, float* __restrict__ src, long n_vec4, i
   }
 }
 
+
+// ---- NVLS (NVSwitch multicast) primitives ---------------------------------------------------------
+// `mc` is the multicast address of a symmetric buffer: one store to it lands in every rank's
+// replica, one load-reduce from it returns the sum over all replicas, both performed by the switch.
+// None of these kernels waits on another rank: the callers bracket them with the device barrier.
+
+// every replica[i] = src[i]; 16 bytes per thread and iteration (any dtype, copied as bits)
+__global__ void __launch_bounds__(256)
+multimem_bcast_kernel(float4* __restrict__ mc, const float4* __restrict__ src, long n16) {
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride) {
+    const float4 v = src[i];
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc + i),
+                 "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+  }
+}
+
+// dst[i] = sum over replicas of mc[i]  (fp32, or bf16 pairs accumulated in fp32 inside the switch)
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+multimem_reduce_kernel(float4* __restrict__ dst, const float4* __restrict__ mc, long n16,
+                       float4* __restrict__ mc_out) {
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride) {
+    float4 v;
+    if (BF16) {
+      uint32_t a, b, c, d;
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "l"(mc + i) : "memory");
+      v = make_float4(__uint_as_float(a), __uint_as_float(b), __uint_as_float(c), __uint_as_float(d));
+    } else {
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc + i) : "memory");
+    }
+    if (dst != nullptr) dst[i] = v;
+    if (mc_out != nullptr)
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_out + i),
+                   "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                   : "memory");
+  }
+}
+
 }  // namespace ua
 
 using namespace ua;
@@ -132,6 +180,48 @@ extern "C" int ua_wait_flag(const void* flag, unsigned target, double budget_s, 
                             cudaStream_t stream) {
   wait_flag_kernel<<<1, 1, 0, stream>>>(static_cast<const uint32_t*>(flag), target,
                                         static_cast<unsigned long long>(budget_s * 1e9), status);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static unsigned nvls_blocks(long n16, int num_sms) {
+  long blocks = (n16 + 255) / 256;
+  if (blocks > static_cast<long>(num_sms) * 4) blocks = static_cast<long>(num_sms) * 4;
+  return static_cast<unsigned>(blocks);
+}
+
+// Broadcast `nbytes` of local memory into every rank's replica of a symmetric buffer.
+extern "C" int ua_multimem_bcast(void* mc_dst, const void* src, long nbytes, int num_sms,
+                                 cudaStream_t stream) {
+  if (mc_dst == nullptr) UA_FAIL("ua_multimem_bcast: no multicast address (NVLS unavailable)");
+  if (nbytes % 16 != 0 || (reinterpret_cast<uintptr_t>(mc_dst) | reinterpret_cast<uintptr_t>(src)) % 16 != 0)
+    UA_FAIL("ua_multimem_bcast: addresses and size must be multiples of 16 bytes");
+  if (nbytes == 0) return 0;
+  const long n16 = nbytes / 16;
+  multimem_bcast_kernel<<<nvls_blocks(n16, num_sms), 256, 0, stream>>>(
+      static_cast<float4*>(mc_dst), static_cast<const float4*>(src), n16);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// In-switch sum over the replicas of a symmetric buffer. dst (local, may be null) receives the
+// sum; mc_out (multicast, may be null) receives it in every replica (with mc_out == mc_src and
+// every rank covering a disjoint slice this is a one-shot all-reduce). bf16 != 0: elements are
+// bf16 (accumulated in fp32 inside the switch), else fp32.
+extern "C" int ua_multimem_reduce(void* dst, const void* mc_src, void* mc_out, long nbytes, int bf16,
+                                  int num_sms, cudaStream_t stream) {
+  if (mc_src == nullptr) UA_FAIL("ua_multimem_reduce: no multicast address (NVLS unavailable)");
+  if (nbytes % 16 != 0 || (reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(mc_src) |
+                           reinterpret_cast<uintptr_t>(mc_out)) % 16 != 0)
+    UA_FAIL("ua_multimem_reduce: addresses and size must be multiples of 16 bytes");
+  if (nbytes == 0) return 0;
+  const long n16 = nbytes / 16;
+  if (bf16)
+    multimem_reduce_kernel<true><<<nvls_blocks(n16, num_sms), 256, 0, stream>>>(
+        static_cast<float4*>(dst), static_cast<const float4*>(mc_src), n16, static_cast<float4*>(mc_out));
+  else
+    multimem_reduce_kernel<false><<<nvls_blocks(n16, num_sms), 256, 0, stream>>>(
+        static_cast<float4*>(dst), static_cast<const float4*>(mc_src), n16, static_cast<float4*>(mc_out));
   UA_CUDA(cudaGetLastError());
   return 0;
 }

@@ -201,3 +201,32 @@ def peer_add_(dst: torch.Tensor, src: torch.Tensor, zero_src: bool = False) -> N
     rc = _lib.load().ua_peer_add_f32(dst.data_ptr(), src.data_ptr(), src.numel(), int(zero_src), sms,
                                      _stream(src))
     _lib.check(rc, "ua_peer_add_f32")
+
+
+def multimem_bcast_(mc_ptr: int, src: torch.Tensor) -> None:
+    """Store ``src`` (contiguous, size a multiple of 16 bytes) into every rank's replica of a
+    symmetric buffer through its NVSwitch multicast address ``mc_ptr`` (``multimem.st``): the
+    bytes leave this GPU once however many ranks receive them. The caller orders it against the
+    readers with the device barrier."""
+    assert src.is_cuda and src.is_contiguous()
+    sms = torch.cuda.get_device_properties(src.device).multi_processor_count
+    rc = _lib.load().ua_multimem_bcast(mc_ptr, src.data_ptr(), src.numel() * src.element_size(), sms,
+                                       _stream(src))
+    _lib.check(rc, "ua_multimem_bcast")
+
+
+def multimem_reduce(mc_ptr: int, dst, nbytes: int, dtype: torch.dtype, device,
+                    mc_out: int = 0) -> None:
+    """Sum the replicas of a symmetric buffer inside the switch (``multimem.ld_reduce``): the sum of
+    ``nbytes`` at multicast address ``mc_ptr`` goes to the local tensor ``dst`` (or nowhere when
+    None) and, when ``mc_out`` is given, back into every replica at that multicast address (ranks
+    covering disjoint slices with ``mc_out == mc_ptr`` make a one-shot all-reduce). fp32 or bf16
+    (bf16 accumulates in fp32)."""
+    assert dtype in (torch.float32, torch.bfloat16)
+    if dst is not None:
+        assert dst.is_contiguous() and dst.dtype == dtype and dst.numel() * dst.element_size() == nbytes
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    rc = _lib.load().ua_multimem_reduce(dst.data_ptr() if dst is not None else 0, mc_ptr, mc_out, nbytes,
+                                        int(dtype == torch.bfloat16), sms,
+                                        torch.cuda.current_stream(device).cuda_stream)
+    _lib.check(rc, "ua_multimem_reduce")

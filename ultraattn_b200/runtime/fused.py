@@ -30,6 +30,7 @@ staging lists, merge lists) also runs on CPU with all ranks simulated in one pro
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Sequence
 
 import numpy as np
@@ -120,6 +121,14 @@ class SymmMemSpace(PeerSpace):
 
     def local(self, name): return self._view(self.rank, name)
     def peer(self, name, r): return self._view(r, name)
+
+    def multicast_ptr(self, name: str) -> int:
+        """NVSwitch multicast address of a named buffer (0 when the allocation has none: no NVLS
+        on this machine, or ``UA_NVLS=0``)."""
+        if os.environ.get("UA_NVLS", "1") == "0":
+            return 0
+        base = int(getattr(self.hdl, "multicast_ptr", 0) or 0)
+        return base + self.offsets[name][0] if base else 0
 
     def barrier(self, channel: int) -> None:
         """Device barrier on the current stream (bounded wait; errors land in the status word)."""
