@@ -42,11 +42,23 @@
 
 namespace ua {
 
-constexpr int BWD_THREADS = 448;
+constexpr int BWD_THREADS = 512;              // four warpgroups (the last one: TMA, MMA, two idle warps)
 constexpr int BWD_TMA_WARP = 12;
 constexpr int BWD_MMA_WARP = 13;
 constexpr int BWD_QT = 128;                // queries per step
 constexpr int BWD_TILE_BYTES = ATTN_TILE * ATTN_D * 2;   // 32 KB: [2 halves][128 rows][128 B]
+#ifndef UA_BWD_DQ_DIRECT
+#define UA_BWD_DQ_DIRECT 0
+#endif
+// dQ leaves the CTA through a shared-memory transpose and TMA reduce-add (default), or straight
+// from registers (one warp-wide 128-byte red.global.add per query row and 32 head-dim elements).
+// Measured at S = 16k, 32 heads: 1.03 PFLOP/s with the TMA reduce, 0.88 with the direct form (its
+// 512 reduction instructions per step crowd the load/store queue the softmax warps depend on).
+constexpr bool BWD_DQ_DIRECT = UA_BWD_DQ_DIRECT != 0;
+#ifndef UA_BWD_POLY_EXP_OF_8
+#define UA_BWD_POLY_EXP_OF_8 0
+#endif
+constexpr int BWD_POLY_EXP_OF_8 = UA_BWD_POLY_EXP_OF_8;    // of every 8 exponentials, how many are polynomial
 
 struct BwdCol {
   int kv_src;     // slot in tmK / tmV
@@ -72,6 +84,9 @@ struct BwdParams {
   long lse_batch_stride[ATTN_MAX_SRC];
   int q_tokens[ATTN_MAX_SRC];       // tokens in each query-side source (bounds for lse / D)
   CUtensorMap tmdQ[ATTN_MAX_SRC];   // fp32 [batch, tokens, q heads, 128] accumulators, box 32x1x32
+  float* dq_ptr[ATTN_MAX_SRC];      // the same accumulators as plain pointers
+  long dq_row_stride[ATTN_MAX_SRC];     // elements between tokens
+  long dq_batch_stride[ATTN_MAX_SRC];
   void* dk_ptr[ATTN_MAX_SRC];       // bf16 (store mode) or fp32 (add mode) [tokens, kv heads, 128]
   void* dv_ptr[ATTN_MAX_SRC];
   long dkv_row_stride[ATTN_MAX_SRC];
@@ -124,6 +139,16 @@ __device__ __forceinline__ int seg_num_qt(const AttnSeg& sg) {
   return (sg.len + BWD_QT - 1) / BWD_QT;
 }
 
+
+// Optional pipeline trace (compile with -DUA_BWD_PROF): CTA (0, 0) records clock64() at the
+// hand-over points of one step of every role into g_bwd_prof; ua_bwd_prof_read copies it out.
+#ifdef UA_BWD_PROF
+__device__ long long g_bwd_prof[64];
+#define BWD_PROF(cond, slot) do { if ((cond) && blockIdx.x == 0 && blockIdx.y == 0) g_bwd_prof[slot] = clock64(); } while (0)
+#else
+#define BWD_PROF(cond, slot) do { } while (0)
+#endif
+constexpr int BWD_PROF_STEP = 8;
 
 // Walks the (query head of the group, query segment, 128-query tile) steps of one key tile in the
 // order every role of the CTA uses.
@@ -179,7 +204,10 @@ __device__ __forceinline__ void bwd_phase_a(uint32_t t_st, const float4* nlse4, 
 #pragma unroll
       for (int k2 = 0; k2 < 4; ++k2) {
         const int c = c4 * 4 + k2;
-        const float pr = fast_exp2(fmaf(sv[h][c], scale_log2, ls[k2]));
+        // optionally some exponentials run on the FMA pipe; measured slower (the phase is bound by
+        // instruction issue, not by the special-function unit), so the default is none
+        const float x = fmaf(sv[h][c], scale_log2, ls[k2]);
+        const float pr = (c & 7) < BWD_POLY_EXP_OF_8 ? poly_exp2(x) : fast_exp2(x);
         sv[h][c] = (!MASK || (key_ok && (h * 32 + c) >= r_first)) ? pr : 0.f;
       }
     }
@@ -241,6 +269,10 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
   }
   const int n_steps = steps_per_head * p.kv_group;
 
+  if (warp >= BWD_TMA_WARP) {
+    // last warpgroup (TMA, MMA, two idle warps): the drain warpgroup takes most of its registers.
+    // The instruction sits inside this branch so that the other roles keep their full budget.
+    reg_dealloc<96>();
   if (warp == BWD_TMA_WARP) {
     // =============================== TMA producer ===========================================
     if (lane == 0 && n_steps > 0) {
@@ -292,26 +324,32 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       const uint32_t t_dv = tmem_base + 128;
       const uint32_t t_st = tmem_base + 256;     // S^T, later P^T (packed) at columns 0-31, 64-95
       const uint32_t t_dp = tmem_base + 384;     // dP^T, later dQ^T
-      const uint32_t ka = smem_u32(s.k);
-      const uint32_t va = smem_u32(s.v);
-      const uint32_t da = smem_u32(s.d_o);
-      const uint32_t dsa = smem_u32(s.ds);
+      // one base descriptor per operand view; every instruction adds its (16-byte unit) offset to
+      // the address field, which cannot carry out of it for addresses inside shared memory
+      const uint64_t k_kmaj = make_smem_desc_sw128(smem_u32(s.k), 16, 1024);        // A of S^T
+      const uint64_t k_mmaj = make_smem_desc_sw128(smem_u32(s.k), 16384, 1024);     // A of dQ^T
+      const uint64_t v_kmaj = make_smem_desc_sw128(smem_u32(s.v), 16, 1024);        // A of dP^T
+      const uint64_t do_kmaj = make_smem_desc_sw128(smem_u32(s.d_o), 16, 1024);     // B of dP^T
+      const uint64_t do_nmaj = make_smem_desc_sw128(smem_u32(s.d_o), 16384, 1024);  // B of dV
+      const uint64_t ds_kmaj = make_smem_desc_sw128(smem_u32(s.ds), 16, 1024);      // A of dK
+      const uint64_t ds_nmaj = make_smem_desc_sw128(smem_u32(s.ds), 16384, 1024);   // B of dQ^T
+      const uint64_t q_kmaj0 = make_smem_desc_sw128(smem_u32(s.q[0]), 16, 1024);    // B of S^T
+      const uint64_t q_nmaj0 = make_smem_desc_sw128(smem_u32(s.q[0]), 16384, 1024); // B of dK
+      constexpr uint64_t Q_STAGE = BWD_TILE_BYTES >> 4;
+      // K-major operands: 16 elements of the reduction = 32 B, the two 64-element halves 16384 B apart
+      auto koff = [](int kk) -> uint64_t { return static_cast<uint64_t>(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4); };
+      // MN-major operands: 16 rows of the reduction = 2048 B
+      auto noff = [](int kk) -> uint64_t { return static_cast<uint64_t>((kk * 2048) >> 4); };
       auto issue_st = [&](int st) {
-        const uint32_t qa = smem_u32(s.q[st]);
+        const uint64_t qd = q_kmaj0 + st * Q_STAGE;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_ss(t_st, make_smem_desc_sw128(ka + off, 16, 1024),
-                  make_smem_desc_sw128(qa + off, 16, 1024), idesc_kk, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(t_st, k_kmaj + koff(kk), qd + koff(kk), idesc_kk, kk > 0 ? 1u : 0u);
       };
       auto issue_dp = [&]() {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_ss(t_dp, make_smem_desc_sw128(va + off, 16, 1024),
-                  make_smem_desc_sw128(da + off, 16, 1024), idesc_kk, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(t_dp, v_kmaj + koff(kk), do_kmaj + koff(kk), idesc_kk, kk > 0 ? 1u : 0u);
       };
       bool ok = true;
       do {
@@ -327,16 +365,17 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         for (int i = 0; i < n_steps; ++i) {
           const int st = i & 1;
           const uint32_t ph = i & 1;
-          const uint32_t qa = smem_u32(s.q[st]);
+          const uint64_t qn = q_nmaj0 + st * Q_STAGE;
           const bool more = i + 1 < n_steps;
           // dV += P^T dO : A = P^T in TMEM (queries 0-63 packed at columns 0-31, 64-127 at 64-95),
           // B = dO as an N-major operand (16 query rows = 2048 B, d-halves 16384 B apart)
+          BWD_PROF(i == BWD_PROF_STEP, 0);
           if (!mbar_wait(&s.p_ready, ph, wc, 203)) { ok = false; break; }
+          BWD_PROF(i == BWD_PROF_STEP, 1);
           tc_fence_after_sync();
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ts(t_dv, t_st + (kk >> 2) * 64 + (kk & 3) * 8,
-                    make_smem_desc_sw128(da + kk * 2048, 16384, 1024), idesc_kn,
+            umma_ts(t_dv, t_st + (kk >> 2) * 64 + (kk & 3) * 8, do_nmaj + noff(kk), idesc_kn,
                     (i > 0 || kk > 0) ? 1u : 0u);
           tc_commit(&s.do_empty);
           // S^T of the next step right behind it: it overwrites P^T(i), which dV(i) reads first
@@ -344,38 +383,43 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
           if (more) {
             if (!mbar_wait(&s.q_full[st ^ 1], ((i + 1) >> 1) & 1, wc, 205)) { ok = false; break; }
             tc_fence_after_sync();
+            BWD_PROF(i == BWD_PROF_STEP, 2);
             issue_st(st ^ 1);
             tc_commit(&s.s_full);
           }
+          BWD_PROF(i == BWD_PROF_STEP, 3);
           // dQ^T = K^T dS^T : A = K as an M-major operand, B = dS^T as an N-major operand (two
           // 64-query panels 16384 B apart); lands where dP^T was
           if (!mbar_wait(&s.ds_ready, ph, wc, 204)) { ok = false; break; }
+          BWD_PROF(i == BWD_PROF_STEP, 4);
           tc_fence_after_sync();
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ss(t_dp, make_smem_desc_sw128(ka + kk * 2048, 16384, 1024),
-                    make_smem_desc_sw128(dsa + kk * 2048, 16384, 1024), idesc_nn, kk > 0 ? 1u : 0u);
+            umma_ss(t_dp, k_mmaj + noff(kk), ds_nmaj + noff(kk), idesc_nn, kk > 0 ? 1u : 0u);
           tc_commit(&s.dq_full);
           // dK += dS^T Q : A = dS^T in shared memory (K-major over queries: panel kk/4, 32 B per
           // step), B = Q as an N-major operand; runs while the drain warpgroup reads dQ^T
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ss(t_dk, make_smem_desc_sw128(dsa + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
-                    make_smem_desc_sw128(qa + kk * 2048, 16384, 1024), idesc_kn,
-                    (i > 0 || kk > 0) ? 1u : 0u);
+            umma_ss(t_dk, ds_kmaj + koff(kk), qn + noff(kk), idesc_kn, (i > 0 || kk > 0) ? 1u : 0u);
           tc_commit(&s.q_empty[st]);
+          BWD_PROF(i == BWD_PROF_STEP, 5);
           if (more) {
             if (!mbar_wait(&s.do_full, (i + 1) & 1, wc, 206)) { ok = false; break; }
+            BWD_PROF(i == BWD_PROF_STEP, 6);
             // dP^T(i+1) lands where dQ^T(i) is: wait until the drain warpgroup has read it
             if (!mbar_wait(&s.dq_free, ph, wc, 207)) { ok = false; break; }
+            BWD_PROF(i == BWD_PROF_STEP, 7);
             tc_fence_after_sync();
             issue_dp();
             tc_commit(&s.dp_full);
+            BWD_PROF(i == BWD_PROF_STEP, 8);
           }
         }
         if (ok) tc_commit(&s.dkv_full);
       } while (false);
     }
+  }
   } else if (warp < 8) {
     // =============================== softmax warpgroups =====================================
     const int wg = warp >> 2;                        // which half of the 128 query columns
@@ -390,28 +434,35 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     bool ok = true;
     // lse / D of the 64 queries of this warp for one step, two per lane; fetched one step ahead
     // (rows outside the segment get lse = +inf -> P = 0)
+    // per (head, segment) values, looked up once per segment: the kernel parameters they come from
+    // are indexed dynamically, which is too slow for the per-step path
+    const float* lse_g = nullptr;
+    const float* dv_g = nullptr;
+    int row_lim = 0;                     // rows of the segment that exist in its source
     auto fetch = [&](const BwdStepIter& it, float (&lv)[2], float (&dv)[2]) -> bool {
-      const AttnSeg& sg = it.sg;
-      if (it.new_seg && sg.wait_flag != 0) {
-        // lse / D of a staged segment are read with plain loads: make sure they landed
-        int w_ok = 1;
-        if (lane == 0) w_ok = wait_staged(p.stage.flags, sg.wait_flag, sg.wait_count * p.stage.epoch, wc.budget_ns) ? 1 : 0;
-        w_ok = __shfl_sync(0xFFFFFFFFu, w_ok, 0);
-        if (!w_ok) return false;
+      if (it.new_seg) {
+        const AttnSeg& sg = it.sg;
+        if (sg.wait_flag != 0) {
+          // lse / D of a staged segment are read with plain loads: make sure they landed
+          int w_ok = 1;
+          if (lane == 0) w_ok = wait_staged(p.stage.flags, sg.wait_flag, sg.wait_count * p.stage.epoch, wc.budget_ns) ? 1 : 0;
+          w_ok = __shfl_sync(0xFFFFFFFFu, w_ok, 0);
+          if (!w_ok) return false;
+        }
+        const int head = kv_head * p.kv_group + it.g;
+        const long off = batch * p.lse_batch_stride[sg.src] + head * p.lse_head_stride[sg.src] + sg.start;
+        lse_g = p.lse_ptr[sg.src] + off;
+        dv_g = p.dvec_ptr[sg.src] + off;
+        row_lim = min(sg.len, p.q_tokens[sg.src] - sg.start);
       }
-      const int head = kv_head * p.kv_group + it.g;
-      const long off = batch * p.lse_batch_stride[sg.src] + head * p.lse_head_stride[sg.src];
-      const float* lse_g = p.lse_ptr[sg.src] + off;
-      const float* dv_g = p.dvec_ptr[sg.src] + off;
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         const int r = it.t * BWD_QT + wg * 64 + hh * 32 + lane;
         lv[hh] = INFINITY;
         dv[hh] = 0.f;
-        if (r < sg.len && sg.start + r < p.q_tokens[sg.src]) {
-          lv[hh] = lse_g[sg.start + r];
-          dv[hh] = dv_g[sg.start + r];
-          if (lv[hh] == -INFINITY) lv[hh] = INFINITY;
+        if (r < row_lim) {
+          lv[hh] = lse_g[r];      // consumed a step later: nothing waits for it here
+          dv[hh] = dv_g[r];
         }
       }
       return true;
@@ -425,13 +476,19 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     for (int i = 0; i < n_steps && ok; ++i) {
       const uint32_t ph = i & 1;
       const AttnSeg& sg = cur.sg;
+      const bool prof = i == BWD_PROF_STEP && quad == 0 && lane == 0;
+      const int pslot = 16 + wg * 16;
+      (void)prof; (void)pslot;
+      BWD_PROF(prof, pslot + 0);
       __syncwarp();        // every lane is done reading the previous step's copy
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
-        s.lse[warp][hh * 32 + lane] = -lv[hh] * LOG2E;
+        // a row that attends to nothing has lse = -inf: treat it like an absent row (P = 0)
+        s.lse[warp][hh * 32 + lane] = lv[hh] == -INFINITY ? -INFINITY : -lv[hh] * LOG2E;
         s.dvec[warp][hh * 32 + lane] = dv[hh];
       }
       __syncwarp();
+      BWD_PROF(prof, pslot + 7);
       // visible iff key_c <= r + diag  <=>  r >= key_c - diag   (r relative to this half)
       const int r_first = sg.causal ? (key_c - sg.diag - cur.t * BWD_QT - wg * 64) : 0;
       // the next step's lse / D travel while this step computes
@@ -444,7 +501,9 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       const float4* dv4 = reinterpret_cast<const float4*>(s.dvec[warp]);
 
       // ---- phase A: P^T = exp2(S^T * scale - lse) -> TMEM (packed bf16) ----------------------
+      BWD_PROF(prof, pslot + 1);
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.s_full, ph, wc, 300))) { ok = false; break; }
+      BWD_PROF(prof, pslot + 2);
       tc_fence_after_sync();
       uint32_t pk[32];                 // this thread's 64 probabilities, packed; kept for phase B
       if (__all_sync(0xFFFFFFFFu, key_ok && r_first <= 0))
@@ -453,13 +512,16 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         bwd_phase_a<true>(t_st, nlse4, p.scale_log2, key_ok, r_first, pk);
       // packed P^T of this half goes to the first 32 columns of this half's own S^T columns
       // (the other warpgroup may still be reading its fp32 half)
+      BWD_PROF(prof, pslot + 3);
       tmem_st_x32(t_st, pk);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&s.p_ready);
+      BWD_PROF(prof, pslot + 4);
 
       // ---- phase B: dS^T = P^T * (dP^T - D) -> shared memory ------------------------------
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.dp_full, ph, wc, 301))) { ok = false; break; }
+      BWD_PROF(prof, pslot + 5);
       tc_fence_after_sync();
       uint8_t* ds_panel = s.ds + wg * 16384;     // this half's 64-query panel
       {
@@ -467,6 +529,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         tmem_ld_x32(t_dp, dp[0]);
         tmem_ld_x32(t_dp + 32, dp[1]);
         tmem_wait_ld();
+        BWD_PROF(prof, pslot + 8);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -486,9 +549,11 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
           }
         }
       }
+      BWD_PROF(prof, pslot + 9);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&s.ds_ready);
+      BWD_PROF(prof, pslot + 6);
       cur = nxt;
     }
     // ---------------------------------- dK / dV epilogue ------------------------------------
@@ -543,6 +608,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     }
   } else {
     // =============================== dQ drain warpgroup =====================================
+    reg_alloc<160>();        // holds a whole 128-query dQ^T slice in registers
     const int quad = warp & 3;                       // TMEM lanes quad*32.. = head-dim slice
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t t_dq = tmem_base + lane_base + 384;
@@ -555,36 +621,62 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         const AttnSeg sg = p.segs[e];
         const int nq = seg_num_qt(sg);
         const CUtensorMap* tdq = &p.tmdQ[sg.src];
+        const long rs = p.dq_row_stride[sg.src];
+        float* dq_col = p.dq_ptr[sg.src] + batch * p.dq_batch_stride[sg.src] +
+                        static_cast<long>(head) * ATTN_D + quad * 32 + lane;
+        const int tokens = p.q_tokens[sg.src];
         for (int t = seg_first_qt(sg, c0); t < nq; ++t, ++i) {
+          BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0, 48);
           if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.dq_full, i & 1, wc, 400))) { ok = false; break; }
+          BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0, 49);
           tc_fence_after_sync();
           const int qrow = sg.start + t * BWD_QT;
-#pragma unroll 1
-          for (int hp = 0; hp < 2; ++hp) {           // two chunks of 32 queries per TMEM read
-            uint32_t dv[2][32];
-            tmem_ld_x32(t_dq + hp * 64, dv[0]);
-            tmem_ld_x32(t_dq + hp * 64 + 32, dv[1]);
-            tmem_wait_ld();
-            if (hp == 1) {
-              // the whole TMEM buffer has been read: hand it back before the slower part
-              tc_fence_before_sync();
-              mbar_arrive(&s.dq_free);
-            }
+          // read the whole slice and hand TMEM back at once: dP^T of the next step is waiting for it
+          uint32_t dv[4][32];
 #pragma unroll
-            for (int h2 = 0; h2 < 2; ++h2) {
+          for (int h = 0; h < 4; ++h) tmem_ld_x32(t_dq + h * 32, dv[h]);
+          tmem_wait_ld();
+          tc_fence_before_sync();
+          mbar_arrive(&s.dq_free);
+          BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0, 50);
+          if (BWD_DQ_DIRECT) {
+            // lane = head-dim element, register = query: the 32 lanes of one instruction cover 128
+            // contiguous bytes of one query row
+            float* dst = dq_col + static_cast<long>(qrow) * rs;
+            const int n_valid = min(BWD_QT, tokens - qrow);      // rows that exist in the accumulator
+            if (n_valid == BWD_QT) {
+#pragma unroll
+              for (int h = 0; h < 4; ++h)
+#pragma unroll
+                for (int c = 0; c < 32; ++c)
+                  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + (h * 32 + c) * rs),
+                               "f"(__uint_as_float(dv[h][c]) * p.scale) : "memory");
+            } else {
+#pragma unroll
+              for (int h = 0; h < 4; ++h)
+#pragma unroll
+                for (int c = 0; c < 32; ++c)
+                  if (h * 32 + c < n_valid)
+                    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + (h * 32 + c) * rs),
+                                 "f"(__uint_as_float(dv[h][c]) * p.scale) : "memory");
+            }
+          } else {
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {              // 32 queries at a time through the staging tile
               // the previous reduce must have finished reading the staging buffer
               if (lane == 0) tma_store_wait_read_all();
               __syncwarp();
 #pragma unroll
-              for (int c = 0; c < 32; ++c) stage[c * 32 + lane] = __uint_as_float(dv[h2][c]) * p.scale;
+              for (int c = 0; c < 32; ++c) stage[c * 32 + lane] = __uint_as_float(dv[h][c]) * p.scale;
               fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0) {
-                tma_reduce_add_4d(tdq, stage, quad * 32, head, qrow + (hp * 2 + h2) * 32, batch);
+                tma_reduce_add_4d(tdq, stage, quad * 32, head, qrow + h * 32, batch);
                 tma_store_commit();
               }
             }
           }
+          BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0, 51);
         }
       }
     }
@@ -603,6 +695,13 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
 }  // namespace ua
 
 using namespace ua;
+
+#ifdef UA_BWD_PROF
+extern "C" int ua_bwd_prof_read(long long* host64) {
+  UA_CUDA(cudaMemcpyFromSymbol(host64, g_bwd_prof, sizeof(long long) * 64));
+  return 0;
+}
+#endif
 
 struct UaTensorSrc {
   const void* ptr;
@@ -675,6 +774,9 @@ extern "C" int ua_attn_bwd(const UaTensorSrc* q_src, const UaTensorSrc* do_src,
                          static_cast<uint64_t>(bstr) * 4};
       uint32_t box[4] = {32, 1, 32, 1};
       if (make_tmap_f32(&p.tmdQ[i], q_side[i].dq, 4, dims, str, box)) return -1;
+      p.dq_ptr[i] = q_side[i].dq;
+      p.dq_row_stride[i] = q_side[i].dq_row_stride;
+      p.dq_batch_stride[i] = bstr;
     }
   }
   for (int i = 0; i < n_kv; ++i) {
@@ -818,6 +920,9 @@ extern "C" int ua_attn_bwd_dense_noalloc(const void* q, const void* k, const voi
                        static_cast<uint64_t>(n_dq) * 4};
     uint32_t box[4] = {32, 1, 32, 1};
     if (make_tmap_f32(&p.tmdQ[0], dq32, 4, dims, str, box)) return -1;
+    p.dq_ptr[0] = dq32;
+    p.dq_row_stride[0] = static_cast<long>(n_heads) * ATTN_D;
+    p.dq_batch_stride[0] = n_dq;
   }
   p.lse_ptr[0] = lse;
   p.dvec_ptr[0] = dvec;

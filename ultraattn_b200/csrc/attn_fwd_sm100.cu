@@ -26,6 +26,10 @@ namespace ua {
 
 constexpr int FWD_THREADS = 320;
 constexpr int FWD_KV_STAGES = 2;
+#ifndef UA_FWD_POLY_EXP_PERIOD
+#define UA_FWD_POLY_EXP_PERIOD 0
+#endif
+constexpr int FWD_POLY_EXP_PERIOD = UA_FWD_POLY_EXP_PERIOD;   // every n-th pair of exponentials is polynomial (0: none)
 constexpr int FWD_TILE_BYTES = ATTN_TILE * ATTN_D * 2;  // 32 KB: [2 d-halves][128 rows][128 B]
 
 struct FwdRow {
@@ -318,8 +322,13 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float p0 = fast_exp2(fmaf(sv[c * 32 + 2 * i], p.scale_log2, -m_eff));
-            const float p1 = fast_exp2(fmaf(sv[c * 32 + 2 * i + 1], p.scale_log2, -m_eff));
+            // optionally one pair in every FWD_POLY_EXP_PERIOD runs on the FMA pipe; measured slower
+            // (1.10 vs 1.19 PFLOP/s: the loop is bound by instruction issue), so the default is none
+            const float x0 = fmaf(sv[c * 32 + 2 * i], p.scale_log2, -m_eff);
+            const float x1 = fmaf(sv[c * 32 + 2 * i + 1], p.scale_log2, -m_eff);
+            const bool poly = FWD_POLY_EXP_PERIOD > 0 && (i % (FWD_POLY_EXP_PERIOD > 0 ? FWD_POLY_EXP_PERIOD : 1)) == 0;
+            const float p0 = poly ? poly_exp2(x0) : fast_exp2(x0);
+            const float p1 = poly ? poly_exp2(x1) : fast_exp2(x1);
             lsum += p0 + p1;
             pk[i] = pack_bf16x2(p0, p1);
           }
@@ -343,7 +352,9 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     tc_fence_after_sync();
     float lse = NEG_INF;
     float inv = 0.f;
-    if (n_total > 0 && l > 0.f) {
+    // (a row whose keys were all masked has m_use = -inf; the polynomial exponential leaves about
+    // 2^-126 per masked entry in l, which must not count as probability mass)
+    if (n_total > 0 && l > 0.f && m_use > NEG_INF) {
       lse = (m_use + log2f(l)) * 0.6931471805599453f;
       inv = 1.0f / l;
     }

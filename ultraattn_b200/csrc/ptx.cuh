@@ -258,6 +258,18 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t saddr, uint32_
 }
 
 // ----------------------------------------------------------------------------------------------
+// Register re-balancing between the warpgroups of a CTA (every warp of the warpgroup executes it)
+// ----------------------------------------------------------------------------------------------
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// ----------------------------------------------------------------------------------------------
 // tcgen05: MMA (issued by one thread)
 // ----------------------------------------------------------------------------------------------
 // D[tmem] (+)= A[smem] * B[smem]
@@ -342,6 +354,20 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// 2^x on the FMA / integer pipes instead of the special-function unit (16 results per clock and
+// SM, which is what bounds the softmax of a 128-wide head): round x to the nearest integer n with
+// the 1.5 * 2^23 trick, evaluate a cubic for 2^(x - n) on [-0.5, 0.5] (relative error 7.5e-5, far
+// below the bf16 rounding of the probabilities it feeds) and add n to the exponent field.
+// Inputs below -126 (masked entries: -inf) give about 2^-126 instead of 0.
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -126.0f);
+  const float t = x + 12582912.0f;
+  const float f = x - (t - 12582912.0f);
+  float p = fmaf(f, 0.05517164617776871f, 0.2426111251115799f);
+  p = fmaf(p, f, 0.6932609677314758f);
+  p = fmaf(p, f, 0.9999280571937561f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
