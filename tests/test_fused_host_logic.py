@@ -12,11 +12,14 @@ from ultraattn_b200 import patterns as P
 from ultraattn_b200.runtime import FakeSpace, FusedContextParallel, plan_allocation
 
 
-def _run_all_ranks(pattern, world, S, H, D, allocation, seed=0):
+def _run_all_ranks(pattern, world, S, H, D, allocation, seed=0, multicast=False, min_consumers=2):
     table, cmap = plan_allocation(pattern, world, 1, allocation, time_limit=5.0)
     registry = {}
-    ranks = [FusedContextParallel(table, cmap, pattern, S, H, D, FakeSpace(r, world, registry),
-                                  dtype=torch.float32, defer_build=True) for r in range(world)]
+    ranks = [FusedContextParallel(table, cmap, pattern, S, H, D, FakeSpace(r, world, registry, multicast=multicast),
+                                  dtype=torch.float32, defer_build=True, nvls_min_consumers=min_consumers)
+             for r in range(world)]
+    if multicast:
+        assert ranks[0].bc_cols, "the pattern was chosen to have one-to-many blocks"
     for rk in ranks:
         rk.build()
     g = torch.Generator().manual_seed(seed)
@@ -63,4 +66,16 @@ def _run_all_ranks(pattern, world, S, H, D, allocation, seed=0):
 ], ids=lambda x: x if isinstance(x, str) else None)
 def test_fused_host_logic(name, pattern, world, alloc):
     err, table = _run_all_ranks(pattern(), world, 512, 2, 16, alloc)
+    assert err < 2e-4, (err, table)
+
+
+@pytest.mark.parametrize("name,pattern,world,alloc,minc", [
+    ("global-local-4", lambda: P.global_local(8, 1, 2), 4, "ilp", 2),
+    ("star-4", lambda: P.star(8, 1), 4, "naive", 2),
+    ("causal-2-forced", lambda: P.causal(1), 2, "naive", 1),
+], ids=lambda x: x if isinstance(x, str) else None)
+def test_fused_host_logic_with_multicast_blocks(name, pattern, world, alloc, minc):
+    """Blocks that several ranks need are broadcast by their owner (emulated multicast store)
+    instead of being pulled by every consumer; results must not change."""
+    err, table = _run_all_ranks(pattern(), world, 512, 2, 16, alloc, multicast=True, min_consumers=minc)
     assert err < 2e-4, (err, table)

@@ -28,7 +28,11 @@ def _worker(rank, world, port, case, ret):
         pattern = getattr(P, case["pattern"])(*case["args"])
         S, H = case["S"], case["H"]
         rt = ContextParallelAttention(pattern, S, H, 128, device=dev, path=case["path"],
-                                      allocation=case.get("allocation", "ilp"), plan_time_limit=5.0)
+                                      allocation=case.get("allocation", "ilp"), plan_time_limit=5.0,
+                                      nvls_min_consumers=case.get("nvls_min_consumers", 2))
+        if case.get("nvls_min_consumers", 2) == 1 and not rt.impl.bc_cols:
+            ret[rank] = {"skip": "no NVSwitch multicast address for symmetric memory on this machine"}
+            return
         g = torch.Generator().manual_seed(0)
         q, k, v, d_o = (torch.randn(1, S, H, 128, generator=g).to(torch.bfloat16) for _ in range(4))
         par_d = rt.table.shape[0]
@@ -77,6 +81,95 @@ def test_context_parallel_2gpu(path, pattern, args, alloc):
     for r in range(2):
         assert "error" not in res[r], res[r].get("error")
         assert res[r]["rel_err"] < 2e-2, res
+
+
+def test_context_parallel_2gpu_multicast_blocks():
+    """Remote key/value blocks arrive by one multimem store from their owner (forced on for two
+    ranks; by default only blocks with at least two consumers are broadcast)."""
+    _need(2)
+    res = _run(2, {"pattern": "global_local", "args": (8, 1, 2), "S": 2048, "H": 2, "path": "fused",
+                   "allocation": "naive", "nvls_min_consumers": 1})
+    if any("skip" in res[r] for r in range(2)):
+        pytest.skip(res[0].get("skip") or res[1].get("skip"))
+    for r in range(2):
+        assert "error" not in res[r], res[r].get("error")
+        assert res[r]["rel_err"] < 2e-2, res
+
+
+def _nvls_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    try:
+        from ultraattn_b200.ops import attention as A
+        from ultraattn_b200.ops import elementwise as E
+        from ultraattn_b200.runtime.fused import SymmMemSpace
+        sp = SymmMemSpace(dist.group.WORLD, dev)
+        n = 1 << 20
+        sp.alloc("x", (n,), torch.float32)
+        sp.alloc("h", (n,), torch.bfloat16)
+        sp.finalize()
+        if not sp.has_multicast():
+            ret[rank] = {"skip": "no NVSwitch multicast address for symmetric memory on this machine"}
+            return
+        g = torch.Generator().manual_seed(5)
+        parts = [torch.randn(n, generator=g) for _ in range(world)]
+        out = {}
+        # broadcast: rank 1's data lands in every replica
+        if rank == 1:
+            sp.multicast_store("x", slice(None), parts[1].to(dev))
+        sp.barrier(0)
+        out["bcast"] = (sp.local("x").cpu() - parts[1]).abs().max().item()
+        sp.barrier(1)
+        # reduce: every rank holds a partial; rank 0 pulls the in-switch sum
+        sp.local("x").copy_(parts[rank].to(dev))
+        sp.local("h").copy_(parts[rank].to(dev).to(torch.bfloat16))
+        sp.barrier(2)
+        total = sum(parts)
+        if rank == 0:
+            dst = torch.empty(n, dtype=torch.float32, device=dev)
+            E.multimem_reduce(sp.multicast_ptr("x"), dst, n * 4, torch.float32, dev)
+            out["reduce"] = (dst.cpu() - total).abs().max().item()
+            dsth = torch.empty(n, dtype=torch.bfloat16, device=dev)
+            E.multimem_reduce(sp.multicast_ptr("h"), dsth, n * 2, torch.bfloat16, dev)
+            ref = sum(p.to(torch.bfloat16).float() for p in parts)
+            out["reduce_bf16"] = (dsth.float().cpu() - ref).abs().max().item() / ref.abs().max().item()
+        sp.barrier(3)
+        # one-shot all-reduce: each rank reduces its slice and stores the sum back into every replica
+        sl = n // world
+        off = rank * sl * 4
+        E.multimem_reduce(sp.multicast_ptr("x") + off, None, sl * 4, torch.float32, dev,
+                          mc_out=sp.multicast_ptr("x") + off)
+        sp.barrier(4)
+        out["allreduce"] = (sp.local("x").cpu() - total).abs().max().item()
+        torch.cuda.synchronize()
+        A.check_status(dev)
+        ret[rank] = out
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = {"error": f"{type(e).__name__}: {e}\n{traceback.format_exc()}"}
+    finally:
+        dist.destroy_process_group()
+
+
+def test_nvls_primitives_2gpu():
+    """multimem.st broadcast, multimem.ld_reduce reduction (fp32 and bf16) and the one-shot
+    all-reduce built from them, against sums computed on the host."""
+    _need(2)
+    port = 29500 + os.getpid() % 150
+    ret = mp.Manager().dict()
+    mp.spawn(_nvls_worker, args=(2, port, ret), nprocs=2, join=True)
+    res = dict(ret)
+    if any("skip" in res[r] for r in range(2)):
+        pytest.skip(res[0].get("skip") or res[1].get("skip"))
+    for r in range(2):
+        assert "error" not in res[r], res[r].get("error")
+        assert res[r]["bcast"] == 0.0 and res[r]["allreduce"] < 1e-5, res
+    assert res[0]["reduce"] < 1e-5 and res[0]["reduce_bf16"] < 1e-2, res
 
 
 def test_context_parallel_4gpu_fused():

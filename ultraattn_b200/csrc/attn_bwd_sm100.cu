@@ -10,6 +10,8 @@
 //     S^T  = K Q^T                 (128 x 128, TMEM)
 //     dP^T = V dO^T                (TMEM)
 //     P^T  = exp2(S^T * scale - lse)            -> bf16 into TMEM (A operand of dV)
+//            (-lse / scale and -D are added by the tensor core: a ninth 16-wide reduction step
+//            multiplies ones with three bf16 parts of each row term)
 //     dV  += P^T dO                (A from TMEM, B = dO as an N-major operand)
 //     dS^T = P^T * (dP^T - D)                    -> bf16 into shared memory
 //     dQ^T = K^T dS^T              (TMEM, where dP^T was; drained by a warpgroup: registers ->
@@ -111,8 +113,14 @@ struct __align__(1024) BwdSmem {
   uint8_t d_o[BWD_TILE_BYTES];
   uint8_t ds[BWD_TILE_BYTES];              // dS^T: two 64-query panels of [128 keys][128 B], swizzled
   float dq_stage[4][32 * 32];              // per drain warp: [32 queries][32 head-dim] fp32
-  float lse[8][64];                        // per softmax warp copies (no cross-warp barrier needed)
-  float dvec[8][64];
+  // One extra 16-wide reduction step folds the row terms into the products: S^T and dP^T come out
+  // of the tensor core as S^T - lse / scale and dP^T - D. aug[stage]: per query 16 bf16 (columns 0-2:
+  // three bf16 parts of -lse * log2(e) / scale_log2, columns 4-6: parts of -D, rest 0); ones_lse /
+  // ones_d: per key 16 bf16 with ones in columns 0-2 resp. 4-6. Layout: K-major without swizzle,
+  // row r's first 8 columns at r * 16, the other 8 at 2048 + r * 16.
+  uint8_t aug[2][4096];
+  uint8_t ones_lse[4096];
+  uint8_t ones_d[4096];
   uint64_t kv_full;
   uint64_t q_full[2];
   uint64_t q_empty[2];
@@ -125,6 +133,7 @@ struct __align__(1024) BwdSmem {
   uint64_t dq_full;      // dQ^T ready              (tcgen05.commit)
   uint64_t dq_free;      // dQ^T read out of TMEM   (128 drain threads)
   uint64_t dkv_full;
+  uint64_t aug0_ready;   // the first step's row terms are in shared memory (256 softmax threads)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -186,11 +195,12 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   return d;
 }
 
-// P^T of one thread's 64 queries: exp2(S^T * scale + (-lse)), packed to bf16 pairs. MASK applies
-// the causal / key-tail mask (tiles that need none skip the compares).
+// P^T of one thread's 64 queries: exp2(x * scale_log2) with x = S^T - lse / scale as it comes out
+// of the tensor core, packed to bf16 pairs. MASK applies the causal / key-tail mask (tiles that
+// need none skip the compares).
 template <bool MASK>
-__device__ __forceinline__ void bwd_phase_a(uint32_t t_st, const float4* nlse4, float scale_log2,
-                                            bool key_ok, int r_first, uint32_t (&pk)[32]) {
+__device__ __forceinline__ void bwd_phase_a(uint32_t t_st, float scale_log2, bool key_ok, int r_first,
+                                            uint32_t (&pk)[32]) {
   float sv[2][32];
   tmem_ld_x32(t_st, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
   tmem_ld_x32(t_st + 32, reinterpret_cast<uint32_t(&)[32]>(sv[1]));
@@ -198,18 +208,12 @@ __device__ __forceinline__ void bwd_phase_a(uint32_t t_st, const float4* nlse4, 
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
 #pragma unroll
-    for (int c4 = 0; c4 < 8; ++c4) {
-      const float4 l = nlse4[h * 8 + c4];
-      const float ls[4] = {l.x, l.y, l.z, l.w};
-#pragma unroll
-      for (int k2 = 0; k2 < 4; ++k2) {
-        const int c = c4 * 4 + k2;
-        // optionally some exponentials run on the FMA pipe; measured slower (the phase is bound by
-        // instruction issue, not by the special-function unit), so the default is none
-        const float x = fmaf(sv[h][c], scale_log2, ls[k2]);
-        const float pr = (c & 7) < BWD_POLY_EXP_OF_8 ? poly_exp2(x) : fast_exp2(x);
-        sv[h][c] = (!MASK || (key_ok && (h * 32 + c) >= r_first)) ? pr : 0.f;
-      }
+    for (int c = 0; c < 32; ++c) {
+      const float x = sv[h][c] * scale_log2;
+      // optionally some exponentials run on the FMA pipe; measured slower (the phase is bound by
+      // instruction issue, not by the special-function unit), so the default is none
+      const float pr = (c & 7) < BWD_POLY_EXP_OF_8 ? poly_exp2(x) : fast_exp2(x);
+      sv[h][c] = (!MASK || (key_ok && (h * 32 + c) >= r_first)) ? pr : 0.f;
     }
 #pragma unroll
     for (int c = 0; c < 16; ++c) pk[h * 16 + c] = pack_bf16x2(sv[h][2 * c], sv[h][2 * c + 1]);
@@ -247,6 +251,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     mbar_init(&s.dq_full, 1);
     mbar_init(&s.dq_free, 128);
     mbar_init(&s.dkv_full, 1);
+    mbar_init(&s.aug0_ready, 256);
     s.abort_flag = 0;
     fence_mbar_init();
   }
@@ -254,6 +259,21 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     tmem_alloc(&s.tmem_base, 512);
     tmem_relinquish();
   }
+  // constant operands of the extra reduction step; the unused half of the row-term tiles stays 0
+  for (int r = threadIdx.x; r < 256; r += BWD_THREADS) {
+    const int row = r & 127;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    if (r < 128) {
+      *reinterpret_cast<uint4*>(s.ones_lse + row * 16) = make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u);
+      *reinterpret_cast<uint4*>(s.ones_lse + 2048 + row * 16) = zero;
+      *reinterpret_cast<uint4*>(s.aug[0] + 2048 + row * 16) = zero;
+    } else {
+      *reinterpret_cast<uint4*>(s.ones_d + row * 16) = make_uint4(0u, 0u, 0x3F803F80u, 0x00003F80u);
+      *reinterpret_cast<uint4*>(s.ones_d + 2048 + row * 16) = zero;
+      *reinterpret_cast<uint4*>(s.aug[1] + 2048 + row * 16) = zero;
+    }
+  }
+  fence_proxy_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -335,6 +355,10 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       const uint64_t ds_nmaj = make_smem_desc_sw128(smem_u32(s.ds), 16384, 1024);   // B of dQ^T
       const uint64_t q_kmaj0 = make_smem_desc_sw128(smem_u32(s.q[0]), 16, 1024);    // B of S^T
       const uint64_t q_nmaj0 = make_smem_desc_sw128(smem_u32(s.q[0]), 16384, 1024); // B of dK
+      const uint64_t ones_lse_d = make_smem_desc_noswz(smem_u32(s.ones_lse), 2048, 128);
+      const uint64_t ones_d_d = make_smem_desc_noswz(smem_u32(s.ones_d), 2048, 128);
+      const uint64_t aug_d0 = make_smem_desc_noswz(smem_u32(s.aug[0]), 2048, 128);
+      constexpr uint64_t AUG_STAGE = 4096 >> 4;
       constexpr uint64_t Q_STAGE = BWD_TILE_BYTES >> 4;
       // K-major operands: 16 elements of the reduction = 32 B, the two 64-element halves 16384 B apart
       auto koff = [](int kk) -> uint64_t { return static_cast<uint64_t>(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4); };
@@ -345,22 +369,25 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_ss(t_st, k_kmaj + koff(kk), qd + koff(kk), idesc_kk, kk > 0 ? 1u : 0u);
+        umma_ss(t_st, ones_lse_d, aug_d0 + st * AUG_STAGE, idesc_kk, 1u);     // - lse / scale
       };
-      auto issue_dp = [&]() {
+      auto issue_dp = [&](int st) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_ss(t_dp, v_kmaj + koff(kk), do_kmaj + koff(kk), idesc_kk, kk > 0 ? 1u : 0u);
+        umma_ss(t_dp, ones_d_d, aug_d0 + st * AUG_STAGE, idesc_kk, 1u);       // - D
       };
       bool ok = true;
       do {
         if (!mbar_wait(&s.kv_full, 0, wc, 200)) { ok = false; break; }
         if (!mbar_wait(&s.q_full[0], 0, wc, 201)) { ok = false; break; }
+        if (!mbar_wait(&s.aug0_ready, 0, wc, 208)) { ok = false; break; }
         tc_fence_after_sync();
         issue_st(0);
         tc_commit(&s.s_full);
         if (!mbar_wait(&s.do_full, 0, wc, 202)) { ok = false; break; }
         tc_fence_after_sync();
-        issue_dp();
+        issue_dp(0);
         tc_commit(&s.dp_full);
         for (int i = 0; i < n_steps; ++i) {
           const int st = i & 1;
@@ -411,7 +438,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
             if (!mbar_wait(&s.dq_free, ph, wc, 207)) { ok = false; break; }
             BWD_PROF(i == BWD_PROF_STEP, 7);
             tc_fence_after_sync();
-            issue_dp();
+            issue_dp(st ^ 1);
             tc_commit(&s.dp_full);
             BWD_PROF(i == BWD_PROF_STEP, 8);
           }
@@ -430,16 +457,17 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t t_st = tmem_base + lane_base + 256 + wg * 64;
     const uint32_t t_dp = tmem_base + lane_base + 384 + wg * 64;
-    const float LOG2E = 1.4426950408889634f;
     bool ok = true;
-    // lse / D of the 64 queries of this warp for one step, two per lane; fetched one step ahead
-    // (rows outside the segment get lse = +inf -> P = 0)
-    // per (head, segment) values, looked up once per segment: the kernel parameters they come from
-    // are indexed dynamically, which is too slow for the per-step path
+    // Row terms (lse, D) of the 128 queries of a step: warp w, lanes 0-15 handle queries
+    // 16 w .. 16 w + 15. They are fetched two steps ahead and written into the extra operand tile
+    // one step ahead, so that S^T of the next step can be issued as soon as P^T of this one exists.
+    // Per (head, segment) values are looked up once per segment: the kernel parameters they come
+    // from are indexed dynamically, which is too slow for the per-step path.
     const float* lse_g = nullptr;
     const float* dv_g = nullptr;
     int row_lim = 0;                     // rows of the segment that exist in its source
-    auto fetch = [&](const BwdStepIter& it, float (&lv)[2], float (&dv)[2]) -> bool {
+    const float inv_scale_log2 = 1.4426950408889634f / p.scale_log2;
+    auto fetch = [&](const BwdStepIter& it, float& lv, float& dv) -> bool {
       if (it.new_seg) {
         const AttnSeg& sg = it.sg;
         if (sg.wait_flag != 0) {
@@ -455,23 +483,50 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         dv_g = p.dvec_ptr[sg.src] + off;
         row_lim = min(sg.len, p.q_tokens[sg.src] - sg.start);
       }
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const int r = it.t * BWD_QT + wg * 64 + hh * 32 + lane;
-        lv[hh] = INFINITY;
-        dv[hh] = 0.f;
-        if (r < row_lim) {
-          lv[hh] = lse_g[r];      // consumed a step later: nothing waits for it here
-          dv[hh] = dv_g[r];
-        }
+      const int r = it.t * BWD_QT + warp * 16 + lane;
+      lv = INFINITY;                     // rows outside the segment: lse = +inf -> P = 0
+      dv = 0.f;
+      if (lane < 16 && r < row_lim) {
+        lv = lse_g[r];                   // consumed a step later: nothing waits for it here
+        dv = dv_g[r];
       }
       return true;
     };
-    BwdStepIter cur;
-    float lv[2], dv[2];
+    // three bf16 parts of x (their sum has about 24 significant bits)
+    auto split3 = [](float x, uint32_t& hm, uint32_t& l0) {
+      const __nv_bfloat16 h = __float2bfloat16_rn(x);
+      const float r1 = x - __bfloat162float(h);
+      const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+      const __nv_bfloat16 l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+      hm = static_cast<uint32_t>(__bfloat16_as_ushort(h)) | (static_cast<uint32_t>(__bfloat16_as_ushort(m)) << 16);
+      l0 = static_cast<uint32_t>(__bfloat16_as_ushort(l));
+    };
+    auto write_aug = [&](int stage, float lv, float dv) {
+      if (lane < 16) {
+        // a row that attends to nothing (lse = -inf) or does not exist (+inf) gets a huge negative
+        // term: its probabilities come out as exactly 0
+        const float nl = (lv == INFINITY || lv == -INFINITY) ? -3.0e38f : -lv * inv_scale_log2;
+        uint32_t a0, a1, b0, b1;
+        split3(nl, a0, a1);
+        split3(-dv, b0, b1);
+        *reinterpret_cast<uint4*>(s.aug[stage] + (warp * 16 + lane) * 16) = make_uint4(a0, a1, b0, b1);
+      }
+      fence_proxy_async_smem();
+    };
+    BwdStepIter cur, fut;
+    float lv = INFINITY, dv = 0.f;
     if (n_steps > 0) {
       cur.first(p, col, c0);
-      ok = fetch(cur, lv, dv);
+      fut = cur;
+      ok = fetch(fut, lv, dv);
+      if (ok) {
+        write_aug(0, lv, dv);
+        mbar_arrive(&s.aug0_ready);
+        if (n_steps > 1) {
+          fut.next(p, col, c0);
+          ok = fetch(fut, lv, dv);
+        }
+      }
     }
     for (int i = 0; i < n_steps && ok; ++i) {
       const uint32_t ph = i & 1;
@@ -480,36 +535,28 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       const int pslot = 16 + wg * 16;
       (void)prof; (void)pslot;
       BWD_PROF(prof, pslot + 0);
-      __syncwarp();        // every lane is done reading the previous step's copy
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        // a row that attends to nothing has lse = -inf: treat it like an absent row (P = 0)
-        s.lse[warp][hh * 32 + lane] = lv[hh] == -INFINITY ? -INFINITY : -lv[hh] * LOG2E;
-        s.dvec[warp][hh * 32 + lane] = dv[hh];
-      }
-      __syncwarp();
+      // row terms of step i+1 into the operand tile (its previous user, step i-1, is complete: this
+      // thread has consumed dP^T(i-1)); the arrival on p_ready below publishes them
+      if (i + 1 < n_steps) write_aug((i + 1) & 1, lv, dv);
       BWD_PROF(prof, pslot + 7);
       // visible iff key_c <= r + diag  <=>  r >= key_c - diag   (r relative to this half)
       const int r_first = sg.causal ? (key_c - sg.diag - cur.t * BWD_QT - wg * 64) : 0;
-      // the next step's lse / D travel while this step computes
-      BwdStepIter nxt = cur;
-      if (i + 1 < n_steps) {
-        nxt.next(p, col, c0);
-        if (!fetch(nxt, lv, dv)) { ok = false; break; }
+      // the row terms of step i+2 travel while this step computes
+      if (i + 2 < n_steps) {
+        fut.next(p, col, c0);
+        if (!fetch(fut, lv, dv)) { ok = false; break; }
       }
-      const float4* nlse4 = reinterpret_cast<const float4*>(s.lse[warp]);
-      const float4* dv4 = reinterpret_cast<const float4*>(s.dvec[warp]);
 
-      // ---- phase A: P^T = exp2(S^T * scale - lse) -> TMEM (packed bf16) ----------------------
+      // ---- phase A: P^T = exp2((S^T - lse / scale) * scale) -> TMEM (packed bf16) ------------
       BWD_PROF(prof, pslot + 1);
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.s_full, ph, wc, 300))) { ok = false; break; }
       BWD_PROF(prof, pslot + 2);
       tc_fence_after_sync();
       uint32_t pk[32];                 // this thread's 64 probabilities, packed; kept for phase B
       if (__all_sync(0xFFFFFFFFu, key_ok && r_first <= 0))
-        bwd_phase_a<false>(t_st, nlse4, p.scale_log2, key_ok, r_first, pk);
+        bwd_phase_a<false>(t_st, p.scale_log2, key_ok, r_first, pk);
       else
-        bwd_phase_a<true>(t_st, nlse4, p.scale_log2, key_ok, r_first, pk);
+        bwd_phase_a<true>(t_st, p.scale_log2, key_ok, r_first, pk);
       // packed P^T of this half goes to the first 32 columns of this half's own S^T columns
       // (the other warpgroup may still be reading its fp32 half)
       BWD_PROF(prof, pslot + 3);
@@ -534,14 +581,13 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {          // 8 queries = one 16-byte chunk
-            const float4 da4 = dv4[h * 8 + ch * 2], db4 = dv4[h * 8 + ch * 2 + 1];
-            const float dd[8] = {da4.x, da4.y, da4.z, da4.w, db4.x, db4.y, db4.z, db4.w};
             uint32_t w4[4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-              // (dP - D) rounded to bf16 pairs, times the bf16 probabilities (masked ones are 0)
-              const uint32_t x = pack_bf16x2(__uint_as_float(dp[h][ch * 8 + 2 * c]) - dd[2 * c],
-                                             __uint_as_float(dp[h][ch * 8 + 2 * c + 1]) - dd[2 * c + 1]);
+              // (dP - D), as it comes out of the tensor core, rounded to bf16 pairs, times the bf16
+              // probabilities (masked ones are 0)
+              const uint32_t x = pack_bf16x2(__uint_as_float(dp[h][ch * 8 + 2 * c]),
+                                             __uint_as_float(dp[h][ch * 8 + 2 * c + 1]));
               w4[c] = mul_bf16x2(pk[h * 16 + ch * 4 + c], x);
             }
             *reinterpret_cast<uint4*>(ds_panel + sw128_offset(key_t, h * 4 + ch)) =
@@ -554,7 +600,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       tc_fence_before_sync();
       mbar_arrive(&s.ds_ready);
       BWD_PROF(prof, pslot + 6);
-      cur = nxt;
+      if (i + 1 < n_steps) cur.next(p, col, c0);
     }
     // ---------------------------------- dK / dV epilogue ------------------------------------
     if (n_steps > 0 && ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait(&s.dkv_full, 0, wc, 310));
@@ -666,14 +712,17 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
               // the previous reduce must have finished reading the staging buffer
               if (lane == 0) tma_store_wait_read_all();
               __syncwarp();
+              BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0, 52 + h * 3);
 #pragma unroll
               for (int c = 0; c < 32; ++c) stage[c * 32 + lane] = __uint_as_float(dv[h][c]) * p.scale;
               fence_proxy_async_smem();
               __syncwarp();
+              BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0, 53 + h * 3);
               if (lane == 0) {
                 tma_reduce_add_4d(tdq, stage, quad * 32, head, qrow + h * 32, batch);
                 tma_store_commit();
               }
+              BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0, 54 + h * 3);
             }
           }
           BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0, 51);

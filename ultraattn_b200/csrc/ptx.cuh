@@ -257,6 +257,19 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t saddr, uint32_
   return d;
 }
 
+// Shared-memory matrix descriptor without swizzle for a K-major operand: 8-row x 16-byte core
+// matrices, `lbo_bytes` between the core matrices of consecutive 8-element K chunks, `sbo_bytes`
+// between consecutive 8-row groups.
+__device__ __forceinline__ uint64_t make_smem_desc_noswz(uint32_t saddr, uint32_t lbo_bytes,
+                                                         uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= static_cast<uint64_t>(1) << 46;  // descriptor version
+  return d;
+}
+
 // ----------------------------------------------------------------------------------------------
 // Register re-balancing between the warpgroups of a CTA (every warp of the warpgroup executes it)
 // ----------------------------------------------------------------------------------------------

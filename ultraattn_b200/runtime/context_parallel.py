@@ -55,7 +55,8 @@ class ContextParallelAttention:
     def __init__(self, pattern: BSA_Repr, seq_len: int, n_heads: int, head_dim: int = 128, *,
                  group=None, device: Optional[torch.device] = None, path: str = "fused",
                  n_kv_heads: Optional[int] = None, batch: int = 1, allocation: str = "ilp",
-                 plan_time_limit: float = 20.0, dtype=torch.bfloat16, cmap=None):
+                 plan_time_limit: float = 20.0, dtype=torch.bfloat16, cmap=None,
+                 nvls_min_consumers: int = 2):
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
@@ -71,7 +72,8 @@ class ContextParallelAttention:
             self.table, self.cmap = table, cm
             space = SymmMemSpace(self.group, self.device)
             self.impl = FusedContextParallel(table, cm, pattern, seq_len, n_heads, head_dim, space,
-                                             n_kv_heads, batch, dtype, self.device)
+                                             n_kv_heads, batch, dtype, self.device,
+                                             nvls_min_consumers=nvls_min_consumers)
         elif path == "nccl":
             from .executor import PlanExecutor
             kw = dict(pattern=pattern, cp=self.world, seq_len=seq_len, n_heads=n_heads, head_dim=head_dim,

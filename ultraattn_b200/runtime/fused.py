@@ -59,12 +59,28 @@ class PeerSpace:
     def peer(self, name: str, r: int) -> torch.Tensor: raise NotImplementedError
     def barrier(self, channel: int) -> None: raise NotImplementedError
 
+    def has_multicast(self) -> bool:
+        """True when one store can reach every rank's replica of a buffer (NVSwitch multicast)."""
+        return False
+
+    def multicast_store(self, name: str, index, src: torch.Tensor) -> None:
+        """replica[index] = src in every rank's buffer ``name`` (``index``: leading-dimension
+        indices / slices selecting a contiguous piece)."""
+        raise NotImplementedError
+
 
 class FakeSpace(PeerSpace):
     """All ranks in one process on CPU; ``peer`` hands out the other rank's tensor itself."""
 
-    def __init__(self, rank: int, world: int, registry: dict, device="cpu"):
+    def __init__(self, rank: int, world: int, registry: dict, device="cpu", multicast: bool = False):
         self.rank, self.world, self.registry, self.device = rank, world, registry, torch.device(device)
+        self.multicast = multicast
+
+    def has_multicast(self): return self.multicast
+
+    def multicast_store(self, name, index, src):
+        for r in range(self.world):
+            self.registry[(r, name)][index].copy_(src)
 
     def alloc(self, name, shape, dtype):
         t = torch.zeros(*shape, dtype=dtype, device=self.device)
@@ -130,6 +146,15 @@ class SymmMemSpace(PeerSpace):
         base = int(getattr(self.hdl, "multicast_ptr", 0) or 0)
         return base + self.offsets[name][0] if base else 0
 
+    def has_multicast(self) -> bool:
+        return self.hdl is not None and self.multicast_ptr(next(iter(self.offsets))) != 0
+
+    def multicast_store(self, name, index, src):
+        dst = self.local(name)[index]
+        assert dst.is_contiguous() and dst.numel() == src.numel() and dst.dtype == src.dtype
+        off = dst.data_ptr() - self.local(name).data_ptr()
+        E.multimem_bcast_(self.multicast_ptr(name) + off, src.contiguous())
+
     def barrier(self, channel: int) -> None:
         """Device barrier on the current stream (bounded wait; errors land in the status word)."""
         ep = self.epochs.get(channel, 0) + 1
@@ -148,8 +173,10 @@ class FusedContextParallel:
 
     def __init__(self, table: np.ndarray, cmap: np.ndarray, pattern: BSA_Repr, seq_len: int,
                  n_heads: int, head_dim: int, space: PeerSpace, n_kv_heads: Optional[int] = None,
-                 batch: int = 1, dtype=torch.bfloat16, device=None, defer_build: bool = False):
+                 batch: int = 1, dtype=torch.bfloat16, device=None, defer_build: bool = False,
+                 nvls_min_consumers: int = 2):
         self.space = space
+        self.nvls_min_consumers = nvls_min_consumers
         self.rank, self.world = space.rank, space.world
         self.table = np.asarray(table)
         self.cmap = np.asarray(cmap)
@@ -179,6 +206,16 @@ class FusedContextParallel:
             for contrib in sorted({int(x) for x in self.table[r] if x >= 0 and x != p}):
                 self.slots[p].append((r, contrib))
         self.max_slots = max(1, max(len(v) for v in self.slots.values()))
+        # key/value blocks that several other ranks need: their owner broadcasts them through the
+        # switch (one multicast store) instead of every consumer pulling its own copy. Same list
+        # on every rank; dropped again in _alloc when the memory has no multicast address.
+        self.bc_cols = []
+        for c in range(self.par_d):
+            p = int(self.cmap[c])
+            consumers = {int(x) for x in self.table[:, c] if x >= 0 and x != p}
+            if len(consumers) >= max(1, nvls_min_consumers) and self.world > 1:
+                self.bc_cols.append(c)
+        self.bc_slot = {c: i for i, c in enumerate(self.bc_cols)}
         self.fwd_calls = 0
         self.bwd_calls = 0
         self._alloc()
@@ -200,9 +237,12 @@ class FusedContextParallel:
             ("mail_lse", (B, H, self.max_slots * self.blk), torch.float32),
             ("dq_acc", (B, S, H, D), torch.float32), ("dk_acc", (B, S, Hk, D), torch.float32),
             ("dv_acc", (B, S, Hk, D), torch.float32),
-        ]:
+        ] + ([("bc_k", (B, len(self.bc_cols) * self.blk, Hk, D), dt),
+              ("bc_v", (B, len(self.bc_cols) * self.blk, Hk, D), dt)] if self.bc_cols else []):
             sp.alloc(name, shape, dtype)
         sp.finalize()
+        if self.bc_cols and not sp.has_multicast():
+            self.bc_cols, self.bc_slot = [], {}
         dev = self.device
         peers_rows = sorted({int(self.cmap[r]) for r in self.remote_rows})
         peers_cols = sorted({int(self.cmap[c]) for c in self.remote_cols})
@@ -241,6 +281,8 @@ class FusedContextParallel:
                     for b in range(self.B):
                         pieces.append((r, src[b, self._tok(r)], dst[b, self._tok(r)]))
         for c in self.remote_cols:
+            if c in self.bc_slot:
+                continue                  # arrives by multicast before the barrier
             p = int(self.cmap[c])
             for kind in kinds_cols:
                 src, dst = self.space.peer(kind, p), self.mir[(kind, p)]
@@ -291,11 +333,13 @@ class FusedContextParallel:
         kv_src = {g: 0}
         for p in self.peers_cols:
             kv_src[p] = len(kv_src)
+        if self.bc_cols:
+            kv_src["bc"] = len(kv_src)          # the broadcast buffer (this rank's replica)
         out_slot = {g: 0}
         for p in self.peers_rows:
             out_slot[p] = len(out_slot)
         self.f_q_src, self.f_kv_src, self.f_out_slot = q_src, kv_src, out_slot
-        assert max(len(q_src), len(kv_src), len(out_slot)) <= 10
+        assert max(len(q_src), len(kv_src), len(out_slot)) <= 10, "too many source tensors for one launch"
         rows = []
         for r in self.my_rows:
             p = int(self.cmap[r])
@@ -305,6 +349,10 @@ class FusedContextParallel:
             for c in cols:
                 pc = int(self.cmap[c])
                 remote = pc != g
+                if remote and c in self.bc_slot:
+                    segs.append(A.Seg(kv_src["bc"], self.bc_slot[c] * self.blk, self.blk,
+                                      self.types[r, c] == CAUSAL, 0, 0, 0))
+                    continue
                 segs.append(A.Seg(kv_src[pc], self.lidx[c] * self.blk, self.blk,
                                   self.types[r, c] == CAUSAL, 0,
                                   (self.par_d + c + 1) if remote else 0,
@@ -341,6 +389,8 @@ class FusedContextParallel:
         kv_src = {g: 0}
         for p in self.peers_cols:
             kv_src[p] = len(kv_src)
+        if self.bc_cols:
+            kv_src["bc"] = len(kv_src)
         self.b_q_src, self.b_kv_src = q_src, kv_src
         self.b_plans = []
         for cnt in (counts, counts_full):
@@ -358,6 +408,11 @@ class FusedContextParallel:
                                       (r + 1) if remote else 0, cnt.get(r, 0) if remote else 0))
                 kv_remote = pc != g
                 kv_cnt = cnt.get(self.par_d + c, 0)
+                if kv_remote and c in self.bc_slot:
+                    # keys / values from the broadcast buffer, gradients into the owner's accumulators
+                    cols.append(A.Col(kv_src["bc"], self.bc_slot[c] * self.blk, self.blk, tuple(segs),
+                                      kv_src[pc], self.lidx[c] * self.blk, 0, 0))
+                    continue
                 cols.append(A.Col(kv_src[pc], self.lidx[c] * self.blk, self.blk, tuple(segs), kv_src[pc],
                                   self.lidx[c] * self.blk,
                                   (self.par_d + c + 1) if (kv_remote and kv_cnt) else 0, kv_cnt if kv_remote else 0))
@@ -365,11 +420,23 @@ class FusedContextParallel:
             self.b_cols = cols
 
     # =============================== forward ====================================================
+    def _broadcast_kv(self, k, v) -> None:
+        """Owner side of the one-to-many blocks: one multicast store per block and tensor."""
+        for c in self.bc_cols:
+            if int(self.cmap[c]) != self.rank:
+                continue
+            i = self.bc_slot[c]
+            dst = slice(i * self.blk, (i + 1) * self.blk)
+            for b in range(self.B):
+                self.space.multicast_store("bc_k", (b, dst), k[b, self._tok(c)])
+                self.space.multicast_store("bc_v", (b, dst), v[b, self._tok(c)])
+
     def fwd_prepare(self, q, k, v) -> None:
         sp = self.space
         sp.local("q").copy_(q)
         sp.local("k").copy_(k)
         sp.local("v").copy_(v)
+        self._broadcast_kv(k, v)
 
     def stage_on_host(self, pieces) -> None:
         """CPU stand-in of the in-kernel staging prologue."""
@@ -388,6 +455,9 @@ class FusedContextParallel:
         for p, i in self.f_q_src.items():
             q_srcs[i] = sp.local("q") if p == g else self.mir[("q", p)]
         for p, i in self.f_kv_src.items():
+            if p == "bc":
+                k_srcs[i], v_srcs[i] = sp.local("bc_k"), sp.local("bc_v")
+                continue
             k_srcs[i] = sp.local("k") if p == g else self.mir[("k", p)]
             v_srcs[i] = sp.local("v") if p == g else self.mir[("v", p)]
         for p, i in self.f_out_slot.items():
@@ -429,6 +499,7 @@ class FusedContextParallel:
             sp.local("q").copy_(q)
             sp.local("k").copy_(k)
             sp.local("v").copy_(v)
+            self._broadcast_kv(k, v)
         sp.local("do").copy_(d_o)
         sp.local("lse").copy_(lse)
         dvec = sp.local("dvec")
@@ -449,6 +520,10 @@ class FusedContextParallel:
         v_srcs = [None] * len(self.b_kv_src)
         outs = [None] * len(self.b_kv_src)
         for p, i in self.b_kv_src.items():
+            if p == "bc":
+                k_srcs[i], v_srcs[i] = sp.local("bc_k"), sp.local("bc_v")
+                outs[i] = A.BwdKvOut(sp.local("dk_acc"), sp.local("dv_acc"))     # never written through
+                continue
             k_srcs[i] = sp.local("k") if p == g else self.mir[("k", p)]
             v_srcs[i] = sp.local("v") if p == g else self.mir[("v", p)]
             outs[i] = A.BwdKvOut(sp.local("dk_acc") if p == g else sp.peer("dk_acc", p),
