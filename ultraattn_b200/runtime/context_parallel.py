@@ -13,7 +13,7 @@ import torch
 import torch.distributed as dist
 
 from ..patterns.blocks import BSA_Config, BSA_Repr
-from ..planner.allocate import naive_allocate_strategy, solve_sparse_from_bsa
+from ..planner.allocate import tile_volumes, naive_allocate_strategy, solve_sparse_from_bsa
 from ..planner.pipeline import make_plan
 
 
@@ -23,8 +23,24 @@ def plan_allocation(pattern: BSA_Repr, cp: int, fob: int = 1, allocation: str = 
     cfg = BSA_Config(None, None, {"bsa_repr": pattern, "CP": (cp, 1)})
     if allocation == "naive":
         al = naive_allocate_strategy(cfg, fob=fob)
-    else:
-        al = solve_sparse_from_bsa(cfg, fob=fob, time_limit=time_limit, cmap=cmap)
+        return np.asarray(al.table), np.asarray(al.cmap)
+    # A pattern with few blocks (dense causal: one) cannot be balanced at one block per rank: the
+    # diagonal tiles stay with their owners and the rest is too coarse. Refine the partition (each
+    # rank then owns several consecutive blocks, so the caller's shards do not change) until the
+    # busiest rank is within 3 % of the mean.
+    base = max(cp, cfg.table.shape[0])
+    best = None
+    for mult in ((1, 2, 4) if cmap is None and cp > 1 else (1,)):
+        al = solve_sparse_from_bsa(cfg, fob=fob, ParD=base * mult, time_limit=time_limit, cmap=cmap)
+        table = np.asarray(al.table)
+        vol = tile_volumes(pattern, table.shape[0])
+        work = np.array([vol[table == r].sum() for r in range(cp)], dtype=float)
+        imbalance = work.max() / max(work.mean(), 1e-9)
+        if best is None or imbalance < best[0] - 1e-6:
+            best = (imbalance, al)
+        if imbalance <= 1.03:
+            break
+    al = best[1]
     return np.asarray(al.table), np.asarray(al.cmap)
 
 
@@ -79,6 +95,9 @@ class ContextParallelAttention:
             kw = dict(pattern=pattern, cp=self.world, seq_len=seq_len, n_heads=n_heads, head_dim=head_dim,
                       n_kv_heads=n_kv_heads, batch=batch, allocation=allocation, plan_type="Flexflow",
                       time_limit=plan_time_limit, cmap=cmap)
+            if self.rank == 0 and allocation != "naive":
+                # same partition granularity as the fused path (refined until balanced)
+                kw["ParD"] = plan_allocation(pattern, self.world, 1, allocation, plan_time_limit, cmap)[0].shape[0]
             box = [(make_plan(fob=0, **kw), make_plan(fob=1, **kw)) if self.rank == 0 else None]
             dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, 0), group=self.group)
             pf, pb = box[0]
