@@ -194,13 +194,21 @@ def main() -> None:
         torch.cuda.empty_cache()
         bytes_in = 4 * h_q.numel() * 2
         result = {}
+        copy_stream = torch.cuda.Stream(device=dev)
 
         def step_e2e():
+            main = torch.cuda.current_stream(dev)
             qd = h_q.to(dev, non_blocking=True).requires_grad_()
             kd = h_k.to(dev, non_blocking=True).requires_grad_()
             vd = h_v.to(dev, non_blocking=True).requires_grad_()
-            wd = h_do.to(dev, non_blocking=True)
+            # dO is not needed before the backward: its copy follows the other three on a second
+            # stream and overlaps the forward
+            copy_stream.wait_stream(main)
+            with torch.cuda.stream(copy_stream):
+                wd = h_do.to(dev, non_blocking=True)
             out = ua.attention(qd, kd, vd, pattern, runtime=runtime)
+            main.wait_stream(copy_stream)
+            wd.record_stream(main)
             out.backward(wd)
             # the step's scalar result: a checksum over a slice of dQ, read back to the host
             result["v"] = float(qd.grad[0, :64].float().sum().cpu())
