@@ -205,15 +205,19 @@ __device__ __forceinline__ void bwd_phase_a(uint32_t t_st, float scale_log2, boo
   tmem_ld_x32(t_st, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
   tmem_ld_x32(t_st + 32, reinterpret_cast<uint32_t(&)[32]>(sv[1]));
   tmem_wait_ld();
+  const uint64_t sc2 = f2_pack(scale_log2, scale_log2);
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
 #pragma unroll
-    for (int c = 0; c < 32; ++c) {
-      const float x = sv[h][c] * scale_log2;
+    for (int c = 0; c < 32; c += 2) {
+      float x0, x1;
+      f2_unpack(f2_mul(f2_pack(sv[h][c], sv[h][c + 1]), sc2), x0, x1);     // two products per instruction
       // optionally some exponentials run on the FMA pipe; measured slower (the phase is bound by
       // instruction issue, not by the special-function unit), so the default is none
-      const float pr = (c & 7) < BWD_POLY_EXP_OF_8 ? poly_exp2(x) : fast_exp2(x);
-      sv[h][c] = (!MASK || (key_ok && (h * 32 + c) >= r_first)) ? pr : 0.f;
+      const float p0 = (c & 7) < BWD_POLY_EXP_OF_8 ? poly_exp2(x0) : fast_exp2(x0);
+      const float p1 = ((c + 1) & 7) < BWD_POLY_EXP_OF_8 ? poly_exp2(x1) : fast_exp2(x1);
+      sv[h][c] = (!MASK || (key_ok && (h * 32 + c) >= r_first)) ? p0 : 0.f;
+      sv[h][c + 1] = (!MASK || (key_ok && (h * 32 + c + 1) >= r_first)) ? p1 : 0.f;
     }
 #pragma unroll
     for (int c = 0; c < 16; ++c) pk[h * 16 + c] = pack_bf16x2(sv[h][2 * c], sv[h][2 * c + 1]);
@@ -850,7 +854,12 @@ extern "C" int ua_attn_bwd(const UaTensorSrc* q_src, const UaTensorSrc* do_src,
   p.status = status;
   p.stage.tasks = static_cast<const CopyTask*>(copy_tasks_dev);
   p.stage.n_tasks = n_copy_tasks;
-  p.stage.n_copy_ctas = n_copy_ctas;
+  // the copy tasks are shared by the first n_copy_ctas CTAs: never more than the grid has, or the
+  // tasks of the missing CTAs would never run and their consumers would time out
+  {
+    const long grid_ctas = static_cast<long>(n_tiles) * n_kv_heads * batch;
+    p.stage.n_copy_ctas = static_cast<int>(n_copy_ctas < grid_ctas ? n_copy_ctas : grid_ctas);
+  }
   p.stage.flags = stage_flags;
   p.stage.epoch = stage_epoch;
   const int smem_bytes = sizeof(BwdSmem) + 1024;

@@ -291,9 +291,17 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
 #pragma unroll
           for (int i = 0; i < 128; ++i) sv[i] = (i < limit) ? sv[i] : NEG_INF;
         }
-        float mx = sv[0];
+        // eight independent running maxima, two new values per instruction: one dependent chain of
+        // 127 compares would cost more than the exponentials
+        float mx8[8];
 #pragma unroll
-        for (int i = 1; i < 128; ++i) mx = fmaxf(mx, sv[i]);
+        for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(sv[i], sv[8 + i]);
+#pragma unroll
+        for (int i = 16; i < 128; i += 16)
+#pragma unroll
+          for (int k = 0; k < 8; ++k) mx8[k] = fmax3(mx8[k], sv[i + k], sv[i + 8 + k]);
+        float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]));
+        mx = fmax3(mx, mx8[6], mx8[7]);
         mx *= p.scale_log2;
         const float m_new = fmaxf(m_use, mx);
         // lazy rescale: only when the running max grew by more than 2^8 (warp-uniform branch,
@@ -316,25 +324,37 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           }
         }
         const float m_eff = (m_use == NEG_INF) ? 0.f : m_use;
-        float lsum = 0.f;
+        // multiply-add and row sum on packed pairs; four independent partial sums
+        const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2);
+        const uint64_t nm2 = f2_pack(-m_eff, -m_eff);
+        uint64_t ls2[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) ls2[k] = f2_pack(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack(sv[c * 32 + 2 * i], sv[c * 32 + 2 * i + 1]), sc2, nm2), x0, x1);
             // optionally one pair in every FWD_POLY_EXP_PERIOD runs on the FMA pipe; measured slower
             // (1.10 vs 1.19 PFLOP/s: the loop is bound by instruction issue), so the default is none
-            const float x0 = fmaf(sv[c * 32 + 2 * i], p.scale_log2, -m_eff);
-            const float x1 = fmaf(sv[c * 32 + 2 * i + 1], p.scale_log2, -m_eff);
             const bool poly = FWD_POLY_EXP_PERIOD > 0 && (i % (FWD_POLY_EXP_PERIOD > 0 ? FWD_POLY_EXP_PERIOD : 1)) == 0;
             const float p0 = poly ? poly_exp2(x0) : fast_exp2(x0);
             const float p1 = poly ? poly_exp2(x1) : fast_exp2(x1);
-            lsum += p0 + p1;
+            ls2[i & 3] = f2_add(ls2[i & 3], f2_pack(p0, p1));
             pk[i] = pack_bf16x2(p0, p1);
           }
           tmem_st_x16(tS + c * 16, pk);
         }
-        l += lsum;
+        float ls4[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float a, b;
+          f2_unpack(ls2[k], a, b);
+          ls4[k] = a + b;
+        }
+        l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(&s.p_full[w]);
@@ -494,7 +514,12 @@ extern "C" int ua_attn_fwd(const UaTensorSrc* q_src, int n_q, const UaTensorSrc*
   p.status = status;
   p.stage.tasks = static_cast<const CopyTask*>(copy_tasks_dev);
   p.stage.n_tasks = n_copy_tasks;
-  p.stage.n_copy_ctas = n_copy_ctas;
+  // the copy tasks are shared by the first n_copy_ctas CTAs: never more than the grid has, or the
+  // tasks of the missing CTAs would never run and their consumers would time out
+  {
+    const long grid_ctas = static_cast<long>(n_tiles) * n_heads * batch;
+    p.stage.n_copy_ctas = static_cast<int>(n_copy_ctas < grid_ctas ? n_copy_ctas : grid_ctas);
+  }
   p.stage.flags = stage_flags;
   p.stage.epoch = stage_epoch;
   const int smem_bytes = sizeof(FwdSmem) + 1024;
