@@ -100,7 +100,8 @@ def test_global_local_s4096_world2(plan_type):
     {"pattern": _pat_star, "S": 512, "H": 2, "D": 32, "plan_type": "Flexflow", "allocation": "naive"},
     {"pattern": _pat_causal, "S": 1024, "H": 2, "D": 32, "plan_type": "Flexflow", "kernel_tile": True},
     {"pattern": _pat_strided, "S": 1024, "H": 2, "D": 32, "plan_type": "Flexflow", "cp_inter": 2},
-], ids=["causal", "strided", "star-naive", "causal-kernel-tile", "strided-two-level-2x2"])
+    {"pattern": _pat_causal, "S": 512, "H": 2, "D": 32, "plan_type": "Flexflow", "allocation": "lightseq"},
+], ids=["causal", "strided", "star-naive", "causal-kernel-tile", "strided-two-level-2x2", "causal-lightseq"])
 def test_patterns_world4(case):
     res = _run(4, case)
     for r in range(4):

@@ -14,6 +14,9 @@ from ultraattn_b200.runtime import FakeSpace, FusedContextParallel, plan_allocat
 
 def _run_all_ranks(pattern, world, S, H, D, allocation, seed=0, multicast=False, min_consumers=2):
     table, cmap = plan_allocation(pattern, world, 1, allocation, time_limit=5.0)
+    if allocation == "lightseq":
+        tiles = [int((table == r).sum()) for r in range(world)]
+        assert max(tiles) - min(tiles) <= 1, tiles          # the point of the schedule: balance
     registry = {}
     ranks = [FusedContextParallel(table, cmap, pattern, S, H, D, FakeSpace(r, world, registry, multicast=multicast),
                                   dtype=torch.float32, defer_build=True, nvls_min_consumers=min_consumers)
@@ -63,6 +66,8 @@ def _run_all_ranks(pattern, world, S, H, D, allocation, seed=0, multicast=False,
     ("global-local-ilp", lambda: P.global_local(8, 1, 2), 2, "ilp"),
     ("star-naive", lambda: P.star(4, 1), 2, "naive"),
     ("full-ilp", lambda: P.full(1), 4, "ilp"),
+    ("causal-lightseq-4", lambda: P.causal(1), 4, "lightseq"),
+    ("causal-lightseq-8", lambda: P.causal(1), 8, "lightseq"),
 ], ids=lambda x: x if isinstance(x, str) else None)
 def test_fused_host_logic(name, pattern, world, alloc):
     err, table = _run_all_ranks(pattern(), world, 512, 2, 16, alloc)

@@ -60,3 +60,26 @@ def test_profile_formats(tmp_path):
     cm = Comm_Profile_Map(convert_profile_data_to_comm_map(log))
     assert cm.bandwidth_gbs(1e9) == 97.6 and cm.bandwidth_gbs(100) == 0.5
     assert abs(cm.get_comm_time_from_map_key((97.6e9,)) - 1.0) < 1e-9
+
+
+def test_report_tables_from_profile_db(tmp_path):
+    """The figure tables: variants grouped by key prefix, UltraAttn = min over the four variants,
+    speed-ups against the baselines printed as measured."""
+    import json
+    from ultraattn_b200.drivers import report
+    pre = ("fob=1_CP=(8, 1)_shape_config={S=(524288, 524288)_Nh=(32, 32)_bs=1_D=128}"
+           "_bsa_config={CP=(8, 1)_repr=[[2]]}")
+    prof = {pre + "_ablation=(w/o_gpu_tile,w/o_kernel_tile,Flexflow)": {"hfu": 1.0, "time": "4.000e-01", "sim_time": "0"},
+            pre + "_ablation=(w/o_kernel_tile,Flexflow)": {"hfu": 1.0, "time": "3.000e-01", "sim_time": "0"},
+            pre + "_ablation=(w_kernel_tile,ILP)": {"hfu": 1.0, "time": "2.500e-01", "sim_time": "0"},
+            pre + "_ring": {"hfu": 1.0, "time": "5.000e-01", "sim_time": "0"},
+            pre + "_zigzag": {"hfu": 1.0, "time": "2.000e-01", "sim_time": "0"}}
+    (tmp_path / "inter_bsa_exe_plans_profile.json").write_text(json.dumps(prof))
+    rows = report.build_rows(prof)
+    assert len(rows) == 1
+    r = rows[0]
+    assert r["CP"] == "(8, 1)" and r["fob"] == "1"
+    assert r["ultraattn"] == 0.25 and r["node_tile"] == 0.4 and r["node_device_tile"] == 0.3
+    assert abs(r["speedup_vs_ring"] - 2.0) < 1e-9 and abs(r["speedup_vs_best_baseline"] - 0.8) < 1e-9
+    assert report.main(["--db", str(tmp_path), "--csv", str(tmp_path / "out.csv")]) == 0
+    assert (tmp_path / "out.csv").read_text().count("\n") == 2

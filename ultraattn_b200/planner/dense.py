@@ -45,6 +45,22 @@ def get_kv_schedule_table(n: int, causal: bool = False) -> np.ndarray:
     return t
 
 
+def get_lightseq_schedule_table(n: int) -> np.ndarray:
+    """Balanced causal allocation of LightSeq's DistAttn (reference:
+    easy_context/dist_flash_attn/lightseq_async_attn.py:244-435, a vendored baseline that runs
+    n/2 + 1 time steps). Tile (i, j), j <= i, at distance d = i - j runs on its query owner i
+    ("worker": keys/values travel) when d <= n // 2 and on its key owner j ("helper": the query
+    block travels, the partial (O, lse) comes back and is merged) otherwise. Every rank ends up with
+    n // 2 or n // 2 + 1 tiles. Expressed as an allocation table, the schedule runs on any of this
+    framework's executors; the time-step structure of the original (one send/recv pair per step)
+    is what the launch-order scheduler recovers from the dependencies."""
+    t = np.full((n, n), -1, dtype=np.int64)
+    for i in range(n):
+        for j in range(i + 1):
+            t[i, j] = i if i - j <= n // 2 else j
+    return t
+
+
 @functools.lru_cache(maxsize=None)
 def _cc_optimal(n: int, causal: bool, fob: int, time_limit: float):
     pat = causal_pattern(1) if causal else full_pattern(1)

@@ -43,6 +43,16 @@ def make_plan(pattern: BSA_Repr, cp: int, seq_len: int, n_heads: int, head_dim: 
     da = Dist_Attn_Config.from_bsa_config(cfg, shape, hierarchy=1)
     if allocation == "naive":
         alloc = naive_allocate_strategy(cfg, fob=fob, hierarchy=1, ParD=ParD)
+    elif allocation == "lightseq":
+        # LightSeq's balanced causal worker / helper schedule as a fixed table
+        from .allocate import Allocation, comm_volumes, comp_volumes, tile_volumes
+        from .dense import get_lightseq_schedule_table
+        import numpy as np
+        table = get_lightseq_schedule_table(cp)
+        cm = np.arange(cp)
+        cin, cout = comm_volumes(table, cm, cp, fob)
+        alloc = Allocation(cp, cm, table, float(max(cin.max(), cout.max())),
+                           float(comp_volumes(table, tile_volumes(pattern, cp), cp).max()), "lightseq")
     else:
         alloc = solve_sparse_from_bsa(cfg, fob=fob, ParD=ParD, hierarchy=1, objective=objective,
                                       time_limit=time_limit, cmap=cmap)

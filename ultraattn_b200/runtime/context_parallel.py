@@ -24,6 +24,13 @@ def plan_allocation(pattern: BSA_Repr, cp: int, fob: int = 1, allocation: str = 
     if allocation == "naive":
         al = naive_allocate_strategy(cfg, fob=fob)
         return np.asarray(al.table), np.asarray(al.cmap)
+    if allocation == "lightseq":
+        # LightSeq's balanced causal schedule (worker / helper ranks) as a fixed table
+        from ..planner.dense import get_lightseq_schedule_table
+        from ..utils.bsa_helpers import bsa_repr_is_causal
+        assert bsa_repr_is_causal(pattern.simplify() if hasattr(pattern, "simplify") else pattern), \
+            "the LightSeq schedule is defined for dense causal attention"
+        return get_lightseq_schedule_table(cp), np.arange(cp)
     # A pattern with few blocks (dense causal: one) cannot be balanced at one block per rank: the
     # diagonal tiles stay with their owners and the rest is too coarse. Refine the partition (each
     # rank then owns several consecutive blocks, so the caller's shards do not change) until the
@@ -95,7 +102,7 @@ class ContextParallelAttention:
             kw = dict(pattern=pattern, cp=self.world, seq_len=seq_len, n_heads=n_heads, head_dim=head_dim,
                       n_kv_heads=n_kv_heads, batch=batch, allocation=allocation, plan_type="Flexflow",
                       time_limit=plan_time_limit, cmap=cmap)
-            if self.rank == 0 and allocation != "naive":
+            if self.rank == 0 and allocation not in ("naive", "lightseq"):
                 # same partition granularity as the fused path (refined until balanced)
                 kw["ParD"] = plan_allocation(pattern, self.world, 1, allocation, plan_time_limit, cmap)[0].shape[0]
             box = [(make_plan(fob=0, **kw), make_plan(fob=1, **kw)) if self.rank == 0 else None]
