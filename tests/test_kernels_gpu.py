@@ -269,3 +269,24 @@ def test_llama_train_steps_match_cpu(dev):
     assert abs(losses[0][0] - math.log(cfg.vocab)) < 0.3, losses
     for a, b in zip(*losses):
         assert abs(a - b) < 3e-2, losses
+
+
+def test_llama_offloaded_checkpoints_match(dev):
+    """Keeping the layer checkpoints in pinned host memory must not change a training step."""
+    from ultraattn_b200 import patterns as P
+    from ultraattn_b200.models.llama import LlamaConfig, LlamaModel
+    from ultraattn_b200.ops import attention as A
+    cfg = LlamaConfig(n_layers=3, hidden=256, n_heads=2, head_dim=128, ffn=512, vocab=1000)
+    pat = P.causal(1)
+    S = 1024
+    g = torch.Generator().manual_seed(4)
+    ids_all = torch.randint(0, cfg.vocab, (S + 1,), generator=g).to(dev)
+    pos = torch.arange(S, device=dev)
+    out = []
+    for off in (False, True):
+        m = LlamaModel(cfg, device=dev, pattern=pat, seed=1, offload_checkpoints=off)
+        out.append([m.train_step(ids_all[:-1], ids_all[1:], pos, n_total_tokens=S) for _ in range(2)])
+        if off:
+            assert len(m._host_ckpt) == 2 * cfg.n_layers and all(h.is_pinned() for h in m._host_ckpt.values())
+    A.check_status(dev)
+    assert out[0] == out[1], out

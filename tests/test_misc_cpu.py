@@ -106,3 +106,15 @@ def test_varlen_attention_cpu():
     o2.backward(d_o)
     for a, b in ((o, o2), (q.grad, q2.grad), (k.grad, k2.grad), (v.grad, v2.grad)):
         assert (a - b).abs().max().item() < 1e-5
+
+
+def test_launcher_command_and_env():
+    from ultraattn_b200.drivers import launch
+    cmd = launch.build_command(8, 29511, ["bench.py", "--gpus", "8"])
+    assert cmd[1:4] == ["-m", "torch.distributed.run", "--nnodes=1"]
+    assert "--nproc-per-node=8" in cmd and cmd[-3:] == ["bench.py", "--gpus", "8"]
+    assert cmd[cmd.index("--master-addr") + 1] == "127.0.0.1"
+    env = launch.build_env({}, "pool", "B200", True)
+    assert env["CLUSTER_NAME"] == "pool" and env["PLATFORM"] == "B200"
+    assert env["NCCL_NVLS_ENABLE"] == "0" and env["UA_NVLS"] == "0"
+    assert launch.main(["--gpus", "2", "--dry-run", "--", "-m", "x"]) == 0

@@ -36,6 +36,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--path", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--offload-checkpoints", action="store_true",
+                    help="keep the per-layer activation checkpoints in pinned host memory")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -59,7 +61,8 @@ def main() -> None:
         pos = torch.cat([torch.arange(b * blk, (b + 1) * blk) for b in mine])
     else:
         pos = torch.arange(a.seq)
-    model = LlamaModel(cfg, device=dev, pattern=pattern, runtime=runtime, group=group, seed=0)
+    model = LlamaModel(cfg, device=dev, pattern=pattern, runtime=runtime, group=group, seed=0,
+                       offload_checkpoints=a.offload_checkpoints)
     g = torch.Generator().manual_seed(3)
     ids_all = torch.randint(0, a.vocab, (a.seq + 1,), generator=g)
     ids = ids_all[pos].to(dev)

@@ -124,7 +124,10 @@ def _rope_any(x, cos, sin, pos, head_dim):
 
 
 class _Layer(torch.autograd.Function):
-    """One decoder layer with attention-aware checkpointing."""
+    """One decoder layer with attention-aware checkpointing: the layer input, the attention output
+    and its lse are kept (optionally in pinned host memory, reference:
+    easy_context/unsloth_offloaded_gradient_checkpoint/monkey_patch.py:20-94), the projections and
+    the MLP are recomputed in the backward, the attention forward is not."""
 
     @staticmethod
     def forward(ctx, x, model, li):
@@ -132,14 +135,23 @@ class _Layer(torch.autograd.Function):
             q, k, v = model._seg_qkv(x, li)
             o, lse = model._attn_fwd(q, k, v)
             y = model._seg_out(x, o, li)
-        ctx.save_for_backward(x, o, lse)
+        if model.offload_checkpoints and x.is_cuda:
+            ctx.offloaded = (model._offload(x, li, 0), model._offload(o, li, 1))
+            ctx.save_for_backward(lse)
+        else:
+            ctx.offloaded = None
+            ctx.save_for_backward(x, o, lse)
         ctx.model, ctx.li = model, li
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, o, lse = ctx.saved_tensors
         model, li = ctx.model, ctx.li
+        if ctx.offloaded is not None:
+            (lse,) = ctx.saved_tensors
+            x, o = (model._reload(h) for h in ctx.offloaded)
+        else:
+            x, o, lse = ctx.saved_tensors
         with torch.enable_grad():
             x1 = x.detach().requires_grad_()
             q, k, v = model._seg_qkv(x1, li)                    # recomputed (cheap)
@@ -156,10 +168,40 @@ class LlamaModel:
     """Parameters live in one flat bf16 buffer (fp32 on CPU) so that the optimizer and the
     gradient collectives work on a single tensor."""
 
+    # ---- activation checkpoints in pinned host memory (optional) --------------------------------
+    def _offload(self, t: torch.Tensor, li: int, slot: int):
+        """Start copying a checkpoint to its pinned host buffer on the copy stream; returns the
+        handle ``_reload`` takes. The device tensor may be freed as soon as the copy has run."""
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=t.device)
+        key = (li, slot)
+        h = self._host_ckpt.get(key)
+        if h is None or h.shape != t.shape or h.dtype != t.dtype:
+            h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+            self._host_ckpt[key] = h
+        cur = torch.cuda.current_stream(t.device)
+        self._copy_stream.wait_stream(cur)
+        with torch.cuda.stream(self._copy_stream):
+            h.copy_(t, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self._copy_stream)
+        t.record_stream(self._copy_stream)
+        return h, ev
+
+    def _reload(self, handle) -> torch.Tensor:
+        h, ev = handle
+        cur = torch.cuda.current_stream(self.device)
+        cur.wait_event(ev)
+        return h.to(self.device, non_blocking=True)
+
     def __init__(self, cfg: LlamaConfig, device=None, pattern: Optional[BSA_Repr] = None,
                  runtime=None, group=None, dtype=None, seed: int = 0, lr: float = 1e-4,
-                 betas=(0.9, 0.95), weight_decay: float = 0.0, max_pos: int = 1 << 20):
+                 betas=(0.9, 0.95), weight_decay: float = 0.0, max_pos: int = 1 << 20,
+                 offload_checkpoints: bool = False):
         self.cfg = cfg
+        self.offload_checkpoints = offload_checkpoints
+        self._host_ckpt: dict = {}          # (layer, slot) -> pinned host buffer, reused every step
+        self._copy_stream = None
         self.device = torch.device(device) if device is not None else torch.device("cpu")
         self.dtype = dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
         self.pattern = pattern
