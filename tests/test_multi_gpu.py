@@ -172,6 +172,64 @@ def test_nvls_primitives_2gpu():
     assert res[0]["reduce"] < 1e-5 and res[0]["reduce_bf16"] < 1e-2, res
 
 
+def _llama_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    try:
+        import math
+        from ultraattn_b200 import patterns as P
+        from ultraattn_b200.models.llama import LlamaConfig, LlamaModel
+        from ultraattn_b200.ops import attention as A
+        from ultraattn_b200.runtime import ContextParallelAttention
+        cfg = LlamaConfig(n_layers=2, hidden=256, n_heads=2, head_dim=128, ffn=512, vocab=1000)
+        pat = P.global_local(4, 1, 2)
+        S = 2048
+        rt = ContextParallelAttention(pat, S, cfg.n_heads, 128, device=dev, path="fused", plan_time_limit=5.0)
+        par_d = rt.table.shape[0]
+        blk = S // par_d
+        pos = torch.cat([torch.arange(b * blk, (b + 1) * blk) for b in range(par_d) if rt.cmap[b] == rank])
+        g = torch.Generator().manual_seed(3)
+        ids_all = torch.randint(0, cfg.vocab, (S + 1,), generator=g)
+        ids, tgt, posd = ids_all[pos].to(dev), ids_all[pos + 1].to(dev), pos.to(dev)
+        out = {}
+        for name, nvls in (("nccl", False), ("nvls", None)):
+            m = LlamaModel(cfg, device=dev, pattern=pat, runtime=rt, group=dist.group.WORLD, seed=0,
+                           nvls_optimizer=nvls)
+            out[name] = [m.train_step(ids, tgt, posd, n_total_tokens=S) for _ in range(3)]
+            out[name + "_used_nvls"] = m.space is not None
+        torch.cuda.synchronize()
+        A.check_status(dev)
+        out["lnV"] = math.log(cfg.vocab)
+        ret[rank] = out
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = {"error": f"{type(e).__name__}: {e}\n{traceback.format_exc()}"}
+    finally:
+        dist.destroy_process_group()
+
+
+def test_llama_context_parallel_training_2gpu():
+    """Three training steps of a small Llama over two GPUs (fused context-parallel attention,
+    sharded Adam): the first loss is ln(vocab), the losses fall, and the optimizer that sums
+    gradients inside the switch (when the machine has multicast) tracks the NCCL one."""
+    _need(2)
+    port = 29350 + os.getpid() % 100
+    ret = mp.Manager().dict()
+    mp.spawn(_llama_worker, args=(2, port, ret), nprocs=2, join=True)
+    res = dict(ret)
+    for r in range(2):
+        assert "error" not in res[r], res[r].get("error")
+        a, b = res[r]["nccl"], res[r]["nvls"]
+        assert abs(a[0] - res[r]["lnV"]) < 0.3 and a[2] < a[0], res
+        assert all(abs(x - y) < 2e-2 for x, y in zip(a, b)), res
+    assert res[0]["nccl"] == res[1]["nccl"]
+
+
 def test_context_parallel_4gpu_fused():
     _need(4)
     res = _run(4, {"pattern": "strided", "args": (8, 4, 2), "S": 4096, "H": 2, "path": "fused"})

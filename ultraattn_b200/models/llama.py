@@ -197,7 +197,7 @@ class LlamaModel:
     def __init__(self, cfg: LlamaConfig, device=None, pattern: Optional[BSA_Repr] = None,
                  runtime=None, group=None, dtype=None, seed: int = 0, lr: float = 1e-4,
                  betas=(0.9, 0.95), weight_decay: float = 0.0, max_pos: int = 1 << 20,
-                 offload_checkpoints: bool = False):
+                 offload_checkpoints: bool = False, nvls_optimizer: Optional[bool] = None):
         self.cfg = cfg
         self.offload_checkpoints = offload_checkpoints
         self._host_ckpt: dict = {}          # (layer, slot) -> pinned host buffer, reused every step
@@ -220,8 +220,30 @@ class LlamaModel:
         shapes += [("norm_f", (H,)), ("lm_head", (V, H))]
         total = sum(math.prod(s) for _, s in shapes)
         pad = (-total) % (8 * max(self.world, 1))
-        self.flat = torch.zeros(total + pad, dtype=self.dtype, device=self.device)
-        self.flat_grad = torch.zeros_like(self.flat)
+        # Parameters and gradients of a multi-GPU job live in symmetric memory when the machine has
+        # NVSwitch multicast: the sharded optimizer then sums the gradients of its shard inside
+        # the switch (multimem.ld_reduce) and stores the updated shard into every rank's copy with
+        # one multimem.st, instead of NCCL reduce-scatter + all-gather.
+        self.space = None
+        want_nvls = nvls_optimizer if nvls_optimizer is not None else True
+        if want_nvls and self.world > 1 and self.device.type == "cuda" and self.dtype == torch.bfloat16:
+            from ..runtime.fused import SymmMemSpace
+            sp = SymmMemSpace(group, self.device)
+            sp.alloc("params", (total + pad,), self.dtype)
+            sp.alloc("grads", (total + pad,), self.dtype)
+            sp.finalize()
+            if sp.has_multicast():
+                self.space = sp
+            elif nvls_optimizer:
+                raise RuntimeError("nvls_optimizer requested but symmetric memory has no multicast address")
+        if self.space is not None:
+            self.flat = self.space.local("params")
+            self.flat_grad = self.space.local("grads")
+            self.flat.zero_()
+            self.flat_grad.zero_()
+        else:
+            self.flat = torch.zeros(total + pad, dtype=self.dtype, device=self.device)
+            self.flat_grad = torch.zeros_like(self.flat)
         self.p: dict = {}
         gen = torch.Generator(device=self.device).manual_seed(seed)
         off = 0
@@ -317,16 +339,27 @@ class LlamaModel:
     # ------------------------------- optimizer --------------------------------------------------
     def optimizer_step(self) -> None:
         self.step_no += 1
-        if self.world > 1:
+        sl = slice(self.rank * self.shard, (self.rank + 1) * self.shard)
+        es = self.flat.element_size()
+        if self.space is not None:
+            # every rank's gradients are complete -> in-switch sum of this rank's shard
+            self.space.barrier(0)
+            shard_grad = torch.empty(self.shard, dtype=self.dtype, device=self.device)
+            E.multimem_reduce(self.space.multicast_ptr("grads") + sl.start * es, shard_grad, self.shard * es,
+                              self.dtype, self.device)
+        elif self.world > 1:
             shard_grad = torch.empty(self.shard, dtype=self.dtype, device=self.device)
             dist.reduce_scatter_tensor(shard_grad, self.flat_grad, group=self.group)
         else:
             shard_grad = self.flat_grad
-        sl = slice(self.rank * self.shard, (self.rank + 1) * self.shard)
         with torch.no_grad():
             E.adam_step(self.master, self.m, self.v, shard_grad, self.flat[sl], self.lr, self.betas[0],
                         self.betas[1], 1e-8, self.wd, self.step_no)
-            if self.world > 1:
+            if self.space is not None:
+                # the updated shard goes into every rank's parameter buffer with one multicast store
+                E.multimem_bcast_(self.space.multicast_ptr("params") + sl.start * es, self.flat[sl])
+                self.space.barrier(1)      # all shards have landed; all ranks have read my gradients
+            elif self.world > 1:
                 dist.all_gather_into_tensor(self.flat, self.flat[sl].clone(), group=self.group)
             self.flat_grad.zero_()
 
