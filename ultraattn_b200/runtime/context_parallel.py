@@ -79,7 +79,9 @@ class ContextParallelAttention:
                  group=None, device: Optional[torch.device] = None, path: str = "fused",
                  n_kv_heads: Optional[int] = None, batch: int = 1, allocation: str = "ilp",
                  plan_time_limit: float = 20.0, dtype=torch.bfloat16, cmap=None,
-                 nvls_min_consumers: int = 2):
+                 nvls_min_consumers: int = 2, plan=None):
+        """``plan``: an earlier runtime's ``(table, cmap)`` to reuse instead of solving the
+        allocation again (fused path; e.g. a second runtime for a different number of heads)."""
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
@@ -88,7 +90,8 @@ class ContextParallelAttention:
         self.pattern = pattern
         if path == "fused":
             from .fused import FusedContextParallel, SymmMemSpace
-            box = [plan_allocation(pattern, self.world, 1, allocation, plan_time_limit, cmap)
+            box = [(plan if plan is not None else
+                    plan_allocation(pattern, self.world, 1, allocation, plan_time_limit, cmap))
                    if self.rank == 0 else None]
             dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, 0), group=self.group)
             table, cm = box[0]
