@@ -188,6 +188,8 @@ def main() -> None:
     ms, launches = timed(step_kernels, args.steps, max(args.warmup, 3))
     A.check_status(dev)
     clocks = sampler.stop() if rank == 0 else None
+    # NVLink bytes rank 0 moves per step on the fused path (from the tables its kernels execute)
+    traffic = dict(runtime.impl.traffic) if (runtime is not None and args.path == "fused") else None
 
     # ---- end-to-end arm: public API, H2D of the inputs and D2H of the result every step ---------
     # The heads are independent, so the step runs as `--e2e-head-chunks` calls of the public
@@ -265,6 +267,7 @@ def main() -> None:
                        "global_batch": 1, "seq_len": S, "parallelism": parallelism,
                        "l2": "inputs (4 GiB per tensor in total) far exceed the 126 MB L2; no flush needed"},
             "model_tflops_per_gpu": tflops, "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "nvlink_bytes_rank0": traffic,
         }))
     if world > 1:
         dist.destroy_process_group()

@@ -84,3 +84,24 @@ def test_fused_host_logic_with_multicast_blocks(name, pattern, world, alloc, min
     instead of being pulled by every consumer; results must not change."""
     err, table = _run_all_ranks(pattern(), world, 512, 2, 16, alloc, multicast=True, min_consumers=minc)
     assert err < 2e-4, (err, table)
+
+
+def test_traffic_accounting_causal_two_ranks():
+    """Dense causal on two ranks, one block each, row-owner allocation: rank 1 computes tile (1, 0)
+    and pulls K/V of block 0; its dK/dV for that block go back; rank 0 moves nothing itself."""
+    pat = P.causal(1)
+    table = np.array([[0, -1], [1, 1]])
+    cmap = np.array([0, 1])
+    S, H, D = 256, 2, 16
+    registry = {}
+    ranks = [FusedContextParallel(table, cmap, pat, S, H, D, FakeSpace(r, 2, registry), dtype=torch.float32,
+                                  defer_build=True) for r in range(2)]
+    for rk in ranks:
+        rk.build()
+    blk_elems = (S // 2) * H * D
+    t0, t1 = ranks[0].traffic, ranks[1].traffic
+    assert all(v == 0 for v in t0.values()), t0
+    assert t1["fwd_pull_bytes"] == 2 * blk_elems * 4            # K and V of block 0 (fp32 in this test)
+    assert t1["fwd_push_bytes"] == 0 and t1["bwd_pull_bytes"] == 0
+    assert t1["bwd_push_bytes"] == 2 * blk_elems * 4            # dK and dV partials (fp32)
+    assert ranks[1].metrics()["phases_ms"] == {}

@@ -43,7 +43,9 @@ from ..ops import elementwise as E
 from ..patterns.blocks import BSA_Config, BSA_Repr, CAUSAL
 
 CHUNK_BYTES = 1 << 20       # staging granularity: one copy task moves at most this much
-MAX_COPY_CTAS = 148
+# CTAs that share the staging copies at the start of a launch (UA_COPY_CTAS overrides): all SMs
+# by default; fewer leave SMs free to start on tiles whose inputs are local while the copies run
+MAX_COPY_CTAS = int(os.environ.get("UA_COPY_CTAS", "148"))
 
 
 # =================================================================================================
@@ -226,6 +228,54 @@ class FusedContextParallel:
         """Build the launch tables (needs every rank's buffers to exist)."""
         self._build_fwd()
         self._build_bwd()
+        self._account_traffic()
+
+    # ------------------------------- observability ----------------------------------------------
+    def _account_traffic(self) -> None:
+        """Bytes this rank moves over NVLink per call, by direction and purpose (what the fused
+        kernels do no longer shows up as separate communication kernels, so it is accounted for
+        here from the same tables the kernels execute)."""
+        es = torch.empty((), dtype=self.dtype).element_size()
+        nbytes = lambda pieces: sum(src.numel() * src.element_size() for _, src, _ in pieces)
+        row_o = self.B * self.blk * self.H * self.D * es + self.B * self.H * self.blk * 4
+        kv_blk = self.B * self.blk * self.Hk * self.D
+        bc_in = sum(1 for c in self.remote_cols if c in self.bc_slot) * 2 * kv_blk * es
+        bc_out = sum(1 for c in self.bc_cols if int(self.cmap[c]) == self.rank) * 2 * kv_blk * es
+        self.traffic = {
+            "fwd_pull_bytes": nbytes(self.f_pieces),                    # staged Q / K / V blocks (peer loads)
+            "fwd_multicast_in_bytes": bc_in,                            # blocks received by multicast
+            "fwd_multicast_out_bytes": bc_out,                          # blocks this rank broadcasts (leave once)
+            "fwd_push_bytes": len(self.remote_rows) * row_o,            # partial (O, lse) into mailboxes
+            "bwd_pull_bytes": nbytes(self.b_pieces),                    # dO / lse / D of foreign rows
+            "bwd_pull_bytes_no_reuse": nbytes(self.b_pieces_full),
+            "bwd_push_bytes": (len(self.remote_rows) * self.B * self.blk * self.H * self.D * 4      # dQ
+                               + len(self.remote_cols) * 2 * kv_blk * 4),                             # dK, dV
+        }
+
+    def enable_trace(self, on: bool = True) -> None:
+        """Record CUDA events around every phase of the following calls (see :meth:`metrics`)."""
+        self._trace = [] if on else None
+
+    def _mark(self, name: str) -> None:
+        tr = getattr(self, "_trace", None)
+        if tr is not None and self.cuda:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream(self.device))
+            tr.append((name, ev))
+
+    def metrics(self) -> dict:
+        """Phase durations (ms, this rank) of the calls since :meth:`enable_trace`, plus the
+        per-call NVLink byte counts; synchronises the device."""
+        out = {"traffic": dict(self.traffic), "phases_ms": {}}
+        tr = getattr(self, "_trace", None)
+        if tr and self.cuda:
+            torch.cuda.synchronize(self.device)
+            for (n0, e0), (n1, e1) in zip(tr[:-1], tr[1:]):
+                if n1.endswith(":begin"):
+                    continue
+                out["phases_ms"][n1] = out["phases_ms"].get(n1, 0.0) + e0.elapsed_time(e1)
+            self._trace = []
+        return out
 
     # ------------------------------- buffers ----------------------------------------------------
     def _alloc(self) -> None:
@@ -482,13 +532,19 @@ class FusedContextParallel:
                     E.lse_merge(parts, (o[b, tok], lse[b, :, tok]))
 
     def forward(self, q, k, v, softmax_scale=None):
+        self._mark("fwd:begin")
         self.fwd_prepare(q, k, v)
+        self._mark("fwd_prepare")
         self.space.barrier(0)
+        self._mark("fwd_barrier_in")
         if not self.cuda:
             self.stage_on_host(self.f_pieces)
         o, lse = self.fwd_compute(softmax_scale)
+        self._mark("fwd_compute")
         self.space.barrier(1)
+        self._mark("fwd_barrier_out")
         self.fwd_finish(o, lse)
+        self._mark("fwd_finish")
         self._staged_inputs = True
         return o, lse
 
@@ -557,12 +613,18 @@ class FusedContextParallel:
 
     def backward(self, d_o, q, k, v, o, lse, softmax_scale=None, reuse_inputs: Optional[bool] = None):
         reuse = bool(getattr(self, "_staged_inputs", False)) if reuse_inputs is None else reuse_inputs
+        self._mark("bwd:begin")
         self.bwd_prepare(d_o, q, k, v, o, lse, reuse)
+        self._mark("bwd_prepare")
         self.space.barrier(2)
+        self._mark("bwd_barrier_in")
         if not self.cuda:
             self.stage_on_host(self.b_pieces if reuse else self.b_pieces_full)
         self.bwd_compute(reuse, softmax_scale)
+        self._mark("bwd_compute")
         self.space.barrier(3)
+        self._mark("bwd_barrier_out")
         res = self.bwd_finish()
+        self._mark("bwd_finish")
         self._staged_inputs = False
         return res
