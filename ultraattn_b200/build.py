@@ -60,6 +60,21 @@ def build_all(force: bool = False, verbose: bool = False) -> Path:
         return LIB_PATH
     nvcc = _nvcc()
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    # several ranks may arrive here at once on a machine where the library is missing: one builds,
+    # the others wait for the lock and then find the library up to date
+    import fcntl
+    lock = open(LIB_DIR / ".build.lock", "w")
+    fcntl.flock(lock, fcntl.LOCK_EX)
+    try:
+        if not force and not needs_build():
+            return LIB_PATH
+        return _build_locked(nvcc, force, verbose)
+    finally:
+        fcntl.flock(lock, fcntl.LOCK_UN)
+        lock.close()
+
+
+def _build_locked(nvcc: str, force: bool, verbose: bool) -> Path:
     hdr = _newest_header_mtime()
 
     def compile_one(src: Path) -> Path:
@@ -80,11 +95,13 @@ def build_all(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
         objs = list(ex.map(compile_one, sources()))
-    cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs),
+    tmp = LIB_PATH.with_suffix(".so.tmp")
+    cmd = [nvcc, "-shared", "-o", str(tmp), *map(str, objs),
            "-gencode", "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, LIB_PATH)          # a reader never sees a half-written library
     return LIB_PATH
 
 

@@ -95,6 +95,16 @@ __device__ __forceinline__ int seg_tiles(const AttnSeg& sg, int r0, int rows_her
   return n;
 }
 
+// Optional pipeline trace (compile with -DUA_FWD_PROF): CTA (0, 0) records clock64() at the
+// hand-over points of one key tile of every role into g_fwd_prof; ua_fwd_prof_read copies it out.
+#ifdef UA_FWD_PROF
+__device__ long long g_fwd_prof[64];
+#define FWD_PROF(cond, slot) do { if ((cond) && blockIdx.x == 0 && blockIdx.y == 0) g_fwd_prof[slot] = clock64(); } while (0)
+#else
+#define FWD_PROF(cond, slot) do { } while (0)
+#endif
+constexpr int FWD_PROF_TILE = 8;
+
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -229,8 +239,10 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           const int stn = (j + 1) % FWD_KV_STAGES;
           const uint32_t phn = ((j + 1) / FWD_KV_STAGES) & 1;
           const bool more = (j + 1 < n_total);
+          FWD_PROF(j == FWD_PROF_TILE, 0);
           if (!mbar_wait(&s.v_full[st], ph, wc, 203)) { ok = false; break; }
           if (!mbar_wait(&s.p_full[0], j & 1, wc, 204)) { ok = false; break; }
+          FWD_PROF(j == FWD_PROF_TILE, 1);
           tc_fence_after_sync();
           issue_pv(0, st, j > 0);
           if (more) {
@@ -239,7 +251,9 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             issue_s(0, stn);
             tc_commit(&s.s_full[0]);
           }
+          FWD_PROF(j == FWD_PROF_TILE, 2);
           if (!mbar_wait(&s.p_full[1], j & 1, wc, 206)) { ok = false; break; }
+          FWD_PROF(j == FWD_PROF_TILE, 3);
           tc_fence_after_sync();
           issue_pv(1, st, j > 0);
           tc_commit(&s.v_empty[st]);
@@ -248,6 +262,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             tc_commit(&s.s_full[1]);
             tc_commit(&s.k_empty[stn]);
           }
+          FWD_PROF(j == FWD_PROF_TILE, 4);
         }
         if (ok) tc_commit(&s.o_full);
       } while (false);
@@ -272,7 +287,12 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       const AttnSeg sg = p.segs[e];
       const int nt = seg_tiles(sg, r0, rows_here);
       for (int t = 0; t < nt; ++t, ++j) {
+        const bool prof = (j == FWD_PROF_TILE || j == FWD_PROF_TILE + 1) && quad == 0 && lane == 0;
+        const int pslot = 8 + w * 24 + (static_cast<int>(j) - FWD_PROF_TILE) * 8;
+        (void)prof; (void)pslot;
+        FWD_PROF(prof, pslot + 0);
         if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.s_full[w], j & 1, wc, 300 + w))) { ok = false; break; }
+        FWD_PROF(prof, pslot + 1);
         tc_fence_after_sync();
         float sv[128];
         {
@@ -283,6 +303,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           tmem_ld_x32(tS + 96, reinterpret_cast<uint32_t(&)[32]>(raw[96]));
           tmem_wait_ld();
         }
+        FWD_PROF(prof, pslot + 2);
         // masking: key index c (segment-relative) allowed iff c < len and (c <= r + diag)
         const int c0 = t * ATTN_TILE;
         int limit = sg.len - c0;                               // columns < limit are in range
@@ -323,6 +344,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             tmem_st_x32(tO + c * 32, ov);
           }
         }
+        FWD_PROF(prof, pslot + 3);
         const float m_eff = (m_use == NEG_INF) ? 0.f : m_use;
         // multiply-add and row sum on packed pairs; four independent partial sums
         const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2);
@@ -355,9 +377,11 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           ls4[k] = a + b;
         }
         l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+        FWD_PROF(prof, pslot + 4);
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(&s.p_full[w]);
+        FWD_PROF(prof, pslot + 5);
       }
     }
 
@@ -443,6 +467,13 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
 }  // namespace ua
 
 using namespace ua;
+
+#ifdef UA_FWD_PROF
+extern "C" int ua_fwd_prof_read(long long* host64) {
+  UA_CUDA(cudaMemcpyFromSymbol(host64, g_fwd_prof, sizeof(long long) * 64));
+  return 0;
+}
+#endif
 
 // Host-side description of one tensor source: [batch, tokens, heads, 128] bf16 with the given
 // strides (elements).
