@@ -32,6 +32,8 @@ def _run_all_ranks(pattern, world, S, H, D, allocation, seed=0, multicast=False,
     shard = lambda t, r: t[:, idx[r]].contiguous()
     # forward, phase by phase in lock step (a barrier separates the phases on real hardware)
     for r, rk in enumerate(ranks):
+        if rk.debug_poison:
+            rk._poison(("q", "k", "v", "do", "lse", "dvec"))
         rk.fwd_prepare(shard(q, r), shard(k, r), shard(v, r))
     outs = []
     for rk in ranks:
@@ -105,3 +107,11 @@ def test_traffic_accounting_causal_two_ranks():
     assert t1["fwd_push_bytes"] == 0 and t1["bwd_pull_bytes"] == 0
     assert t1["bwd_push_bytes"] == 2 * blk_elems * 4            # dK and dV partials (fp32)
     assert ranks[1].metrics()["phases_ms"] == {}
+
+
+def test_poisoned_mirrors_are_fully_overwritten(monkeypatch):
+    """With UA_DEBUG_POISON=1 every staging mirror starts as NaN: a correct result proves that the
+    staging lists deliver every block a tile reads."""
+    monkeypatch.setenv("UA_DEBUG_POISON", "1")
+    err, table = _run_all_ranks(P.strided(8, 4, 2), 4, 512, 2, 16, "ilp")
+    assert err < 2e-4, (err, table)

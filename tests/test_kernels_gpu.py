@@ -290,3 +290,24 @@ def test_llama_offloaded_checkpoints_match(dev):
             assert len(m._host_ckpt) == 2 * cfg.n_layers and all(h.is_pinned() for h in m._host_ckpt.values())
     A.check_status(dev)
     assert out[0] == out[1], out
+
+
+def test_forward_and_dkdv_are_bitwise_reproducible(dev):
+    """The forward and dK / dV have a fixed reduction order (one CTA owns each output tile), so
+    two runs must agree bit for bit; dQ is summed by memory-side reductions in arrival order and
+    is only required to agree to rounding."""
+    import ultraattn_b200 as ua
+    from ultraattn_b200 import patterns as P
+    torch.manual_seed(11)
+    S, H = 2048, 4
+    pat = P.strided(8, 4, 2)
+    q, k, v, d_o = (torch.randn(1, S, H, 128, device=dev, dtype=torch.bfloat16) for _ in range(4))
+    runs = []
+    for _ in range(2):
+        qq, kk, vv = (t.clone().requires_grad_() for t in (q, k, v))
+        o = ua.attention(qq, kk, vv, pat)
+        o.backward(d_o)
+        runs.append((o.detach().clone(), qq.grad.clone(), kk.grad.clone(), vv.grad.clone()))
+    assert torch.equal(runs[0][0], runs[1][0])
+    assert torch.equal(runs[0][2], runs[1][2]) and torch.equal(runs[0][3], runs[1][3])
+    _close(runs[0][1], runs[1][1], 1e-2)

@@ -220,6 +220,10 @@ class FusedContextParallel:
         self.bc_slot = {c: i for i, c in enumerate(self.bc_cols)}
         self.fwd_calls = 0
         self.bwd_calls = 0
+        # UA_DEBUG_POISON=1: the staging mirrors are filled with NaN before every call, so a tile
+        # that reads a block the staging plan did not deliver (or a stale copy from an earlier
+        # call) shows up as NaN in the result instead of going unnoticed
+        self.debug_poison = os.environ.get("UA_DEBUG_POISON") == "1"
         self._alloc()
         if not defer_build:
             self.build()
@@ -531,8 +535,15 @@ class FusedContextParallel:
                 if parts:
                     E.lse_merge(parts, (o[b, tok], lse[b, :, tok]))
 
+    def _poison(self, kinds) -> None:
+        for (kind, _), t in self.mir.items():
+            if kind in kinds and t.is_floating_point():
+                t.fill_(float("nan"))
+
     def forward(self, q, k, v, softmax_scale=None):
         self._mark("fwd:begin")
+        if self.debug_poison:
+            self._poison(("q", "k", "v"))
         self.fwd_prepare(q, k, v)
         self._mark("fwd_prepare")
         self.space.barrier(0)
@@ -614,6 +625,8 @@ class FusedContextParallel:
     def backward(self, d_o, q, k, v, o, lse, softmax_scale=None, reuse_inputs: Optional[bool] = None):
         reuse = bool(getattr(self, "_staged_inputs", False)) if reuse_inputs is None else reuse_inputs
         self._mark("bwd:begin")
+        if self.debug_poison:
+            self._poison(("do", "lse", "dvec") if reuse else ("q", "k", "v", "do", "lse", "dvec"))
         self.bwd_prepare(d_o, q, k, v, o, lse, reuse)
         self._mark("bwd_prepare")
         self.space.barrier(2)
