@@ -359,11 +359,18 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           for (int i = 0; i < 16; ++i) {
             float x0, x1;
             f2_unpack(f2_fma(f2_pack(sv[c * 32 + 2 * i], sv[c * 32 + 2 * i + 1]), sc2, nm2), x0, x1);
-            // optionally one pair in every FWD_POLY_EXP_PERIOD runs on the FMA pipe; measured slower
-            // (1.10 vs 1.19 PFLOP/s: the loop is bound by instruction issue), so the default is none
-            const bool poly = FWD_POLY_EXP_PERIOD > 0 && (i % (FWD_POLY_EXP_PERIOD > 0 ? FWD_POLY_EXP_PERIOD : 1)) == 0;
-            const float p0 = poly ? poly_exp2(x0) : fast_exp2(x0);
-            const float p1 = poly ? poly_exp2(x1) : fast_exp2(x1);
+            // optionally one pair in every FWD_POLY_EXP_PERIOD runs on the FMA pipe (packed cubic);
+            // measured neutral at one in eight and slower beyond (1.19 / 1.14 vs 1.21 PFLOP/s at one
+            // in four / two: the loop is bound by instruction issue, not by the special-function
+            // unit), so the default is none
+            const bool poly = FWD_POLY_EXP_PERIOD > 0 && (i % (FWD_POLY_EXP_PERIOD > 0 ? FWD_POLY_EXP_PERIOD : 1)) == (FWD_POLY_EXP_PERIOD > 0 ? FWD_POLY_EXP_PERIOD : 1) - 1;
+            float p0, p1;
+            if (poly) {
+              f2_unpack(poly_exp2_x2(x0, x1), p0, p1);
+            } else {
+              p0 = fast_exp2(x0);
+              p1 = fast_exp2(x1);
+            }
             ls2[i & 3] = f2_add(ls2[i & 3], f2_pack(p0, p1));
             pk[i] = pack_bf16x2(p0, p1);
           }

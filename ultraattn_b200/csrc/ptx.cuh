@@ -412,6 +412,29 @@ __device__ __forceinline__ float poly_exp2(float x) {
   p = fmaf(p, f, 0.9999280571937561f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
+// poly_exp2 for two values at once on packed fp32 pairs (the clamps and the exponent insertion stay scalar).
+__device__ __forceinline__ uint64_t poly_exp2_x2(float x0, float x1) {
+  x0 = fmaxf(x0, -126.0f);
+  x1 = fmaxf(x1, -126.0f);
+  const uint64_t x = f2_pack(x0, x1);
+  const uint64_t magic = f2_pack(12582912.0f, 12582912.0f);
+  const uint64_t nmagic = f2_pack(-12582912.0f, -12582912.0f);
+  const uint64_t neg1 = f2_pack(-1.0f, -1.0f);
+  const uint64_t t = f2_add(x, magic);
+  const uint64_t fl = f2_add(t, nmagic);
+  const uint64_t f = f2_fma(fl, neg1, x);                      // x - round(x), in [-0.5, 0.5]
+  uint64_t p = f2_fma(f, f2_pack(0.05517164617776871f, 0.05517164617776871f),
+                      f2_pack(0.2426111251115799f, 0.2426111251115799f));
+  p = f2_fma(p, f, f2_pack(0.6932609677314758f, 0.6932609677314758f));
+  p = f2_fma(p, f, f2_pack(0.9999280571937561f, 0.9999280571937561f));
+  float t0, t1, p0, p1;
+  f2_unpack(t, t0, t1);
+  f2_unpack(p, p0, p1);
+  p0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  p1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+  return f2_pack(p0, p1);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
