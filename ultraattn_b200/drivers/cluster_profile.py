@@ -118,18 +118,71 @@ def profile_comm(out_dir: Path, quick: bool) -> None:
     dist.destroy_process_group()
 
 
+def _profile_memory_bound_ops(rows: int, iters: int) -> None:
+    """Time the memory-bound kernels of the model on tensors larger than L2 (``rows`` x 4096 bf16 and
+    relatives) and print achieved GB/s (algorithmic bytes / device time) next to the measured copy
+    bandwidth from ``MEASURED_PEAKS.json`` when present."""
+    from ..ops import elementwise as E
+    dev = torch.device("cuda")
+    peak = None
+    for base in (Path.cwd(), Path(__file__).resolve().parents[2]):
+        f = base / "MEASURED_PEAKS.json"
+        if f.exists():
+            peak = float(json.loads(f.read_text()).get("hbm_gbs", 0.0)) or None
+            break
+    Hd, F, H = 4096, 11008, 32
+    bf = torch.bfloat16
+    x = torch.randn(rows, Hd, device=dev, dtype=bf)
+    w = torch.ones(Hd, device=dev, dtype=bf)
+    g = torch.randn(rows, Hd, device=dev, dtype=bf)
+    y, rstd = E.rmsnorm_fwd(x, w, 1e-5)
+    gu = torch.randn(rows, 2 * F, device=dev, dtype=bf)
+    dy = torch.randn(rows, F, device=dev, dtype=bf)
+    q = torch.randn(rows, H, 128, device=dev, dtype=bf)
+    cos, sin = E.rope_tables(rows, 128, device=dev)
+    pos = torch.arange(rows, device=dev, dtype=torch.int32)
+    o1, o2 = torch.randn(2, rows, H, 128, device=dev, dtype=bf)
+    l1, l2 = torch.randn(2, H, rows, device=dev, dtype=torch.float32)
+    oo, lo = torch.empty_like(o1), torch.empty_like(l1)
+    acc = torch.randn(rows, Hd, device=dev, dtype=torch.float32)
+    n = rows * Hd
+    master, m, v = (torch.zeros(n, device=dev, dtype=torch.float32) for _ in range(3))
+    grad, par = torch.randn(n, device=dev, dtype=bf), torch.zeros(n, device=dev, dtype=bf)
+    b2, b4 = 2, 4
+    ops = [
+        ("rmsnorm_fwd", lambda: E.rmsnorm_fwd(x, w, 1e-5), 2 * n * b2),
+        ("rmsnorm_bwd", lambda: E.rmsnorm_bwd(x, w, g, rstd), 3 * n * b2 + n * b2),
+        ("rope", lambda: E.rope(q, cos, sin, pos), 2 * q.numel() * b2),
+        ("swiglu_fwd", lambda: E.swiglu_fwd(gu), 3 * rows * F * b2),
+        ("swiglu_bwd", lambda: E.swiglu_bwd(gu, dy), 5 * rows * F * b2),
+        ("lse_merge_2way", lambda: E.lse_merge([(o1, l1), (o2, l2)], (oo, lo)), 3 * o1.numel() * b2),
+        ("rowdot", lambda: E.rowdot(o1, o2), 2 * o1.numel() * b2),
+        ("cast_scale", lambda: E.cast_scale(acc, g), n * (b4 + b2)),
+        ("adam", lambda: E.adam_step(master, m, v, grad, par, 1e-4, 0.9, 0.95, 1e-8, 0.0, 1), n * (6 * b4 + 2 * b2)),
+    ]
+    for name, fn, nbytes in ops:
+        t = _time(fn, iters, 2)
+        rec = {"op": name, "rows": rows, "ms": t * 1e3, "gbs": nbytes / t / 1e9}
+        if peak:
+            rec["of_measured_copy_bandwidth"] = rec["gbs"] / peak
+        print(json.dumps(rec))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernels", action="store_true")
     ap.add_argument("--comm", action="store_true")
     ap.add_argument("--out", default="logs/m_configs")
     ap.add_argument("--quick", action="store_true")
-    ap.add_argument("--one", choices=["fwd", "bwd", "gemm"], default=None)
+    ap.add_argument("--one", choices=["fwd", "bwd", "gemm", "ops"], default=None)
     ap.add_argument("--S", type=int, default=16384)
     ap.add_argument("--Nh", type=int, default=32)
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
+    if a.one == "ops":
+        _profile_memory_bound_ops(a.S, a.iters)
+        return
     if a.one:
         dev = torch.device("cuda")
         if a.one == "gemm":
