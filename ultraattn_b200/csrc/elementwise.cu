@@ -43,38 +43,35 @@ struct MergeParams {
   int heads;
 };
 
+// Block = one token x 16 heads x 16 lanes (16 bytes of the 256-byte head row each); K sources.
+template <int K>
 __global__ void __launch_bounds__(256) lse_merge_kernel(const __grid_constant__ MergeParams p) {
   const int sub = threadIdx.x & 15;                       // 16-byte chunk inside the 256 B row
-  const long rid = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
-  if (rid >= static_cast<long>(p.tokens) * p.heads) return;
-  const int tok = static_cast<int>(rid / p.heads);
-  const int head = static_cast<int>(rid % p.heads);
-  float lses[MERGE_MAX];
+  const int tok = blockIdx.x;
+  const int head = blockIdx.y * 16 + (threadIdx.x >> 4);
+  if (head >= p.heads) return;
+  float lses[K];
   float mx = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < MERGE_MAX; ++i) {
-    if (i < p.k) {
-      lses[i] = p.lse_src[i][head * p.lse_hstride[i] + tok];
-      mx = fmaxf(mx, lses[i]);
-    }
+  for (int i = 0; i < K; ++i) {
+    lses[i] = p.lse_src[i][head * p.lse_hstride[i] + tok];
+    mx = fmaxf(mx, lses[i]);
   }
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   float tot = 0.f;
   if (mx > -INFINITY) {
 #pragma unroll
-    for (int i = 0; i < MERGE_MAX; ++i) {
-      if (i < p.k) {
-        const float w = __expf(lses[i] - mx);
-        tot += w;
-        if (w != 0.f) {
-          const uint4 v = *reinterpret_cast<const uint4*>(
-              p.o_src[i] + static_cast<long>(tok) * p.o_stride[i] + head * 128 + sub * 8);
-          const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
+    for (int i = 0; i < K; ++i) {
+      const float w = __expf(lses[i] - mx);
+      tot += w;
+      if (w != 0.f) {
+        const uint4 v = *reinterpret_cast<const uint4*>(
+            p.o_src[i] + static_cast<long>(tok) * p.o_stride[i] + head * 128 + sub * 8);
+        const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            acc[2 * q] += w * bf_lo(ws[q]);
-            acc[2 * q + 1] += w * bf_hi(ws[q]);
-          }
+        for (int q = 0; q < 4; ++q) {
+          acc[2 * q] += w * bf_lo(ws[q]);
+          acc[2 * q + 1] += w * bf_hi(ws[q]);
         }
       }
     }
@@ -248,10 +245,7 @@ rmsnorm_bwd_dw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   const int r0 = blockIdx.y * rows_per_slice;
   const int r1 = min(rows, r0 + rows_per_slice);
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int row = r0; row < r1; ++row) {
-    const float r = rstd[row];
-    const uint4 xv = *reinterpret_cast<const uint4*>(x + static_cast<long>(row) * H + c);
-    const uint4 gv = *reinterpret_cast<const uint4*>(g + static_cast<long>(row) * H + c);
+  auto add_row = [&](const uint4& xv, const uint4& gv, float r) {
     const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w};
     const uint32_t gs[4] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
@@ -259,7 +253,23 @@ rmsnorm_bwd_dw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
       acc[2 * q] += bf_lo(gs[q]) * bf_lo(xs[q]) * r;
       acc[2 * q + 1] += bf_hi(gs[q]) * bf_hi(xs[q]) * r;
     }
+  };
+  int row = r0;
+  for (; row + 4 <= r1; row += 4) {          // four rows (eight 16-byte loads) in flight per thread
+    uint4 xv[4], gv[4];
+    float rr[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      xv[u] = *reinterpret_cast<const uint4*>(x + static_cast<long>(row + u) * H + c);
+      gv[u] = *reinterpret_cast<const uint4*>(g + static_cast<long>(row + u) * H + c);
+      rr[u] = rstd[row + u];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) add_row(xv[u], gv[u], rr[u]);
   }
+  for (; row < r1; ++row)
+    add_row(*reinterpret_cast<const uint4*>(x + static_cast<long>(row) * H + c),
+            *reinterpret_cast<const uint4*>(g + static_cast<long>(row) * H + c), rstd[row]);
 #pragma unroll
   for (int q = 0; q < 8; ++q) atomicAdd(dw + c + q, acc[q]);
 }
@@ -438,9 +448,15 @@ extern "C" int ua_lse_merge(const void* const* o_srcs, const float* const* lse_s
   p.o_dst_stride = o_dst_stride;
   p.lse_dst_hstride = lse_dst_hstride;
   p.k = k; p.tokens = tokens; p.heads = heads;
-  const long threads = static_cast<long>(tokens) * heads * 16;
-  if (threads == 0) return 0;
-  lse_merge_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(p);
+  if (tokens == 0 || heads == 0) return 0;
+  const dim3 grid(static_cast<unsigned>(tokens), static_cast<unsigned>((heads + 15) / 16), 1);
+  switch (k) {
+#define UA_MERGE_CASE(K) case K: lse_merge_kernel<K><<<grid, 256, 0, stream>>>(p); break;
+    UA_MERGE_CASE(1) UA_MERGE_CASE(2) UA_MERGE_CASE(3) UA_MERGE_CASE(4) UA_MERGE_CASE(5)
+    UA_MERGE_CASE(6) UA_MERGE_CASE(7) UA_MERGE_CASE(8) UA_MERGE_CASE(9)
+#undef UA_MERGE_CASE
+    default: UA_FAIL("ua_lse_merge: k must be in [1, 9]");
+  }
   UA_CUDA(cudaGetLastError());
   return 0;
 }
@@ -490,7 +506,7 @@ extern "C" int ua_rmsnorm_bwd(const void* x, const void* w, const void* g, const
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
       static_cast<const __nv_bfloat16*>(g), rstd, static_cast<__nv_bfloat16*>(dx), rows, H);
   UA_CUDA(cudaGetLastError());
-  const int rows_per_slice = 256;
+  const int rows_per_slice = 64;
   dim3 grid((H / 8 + 255) / 256, (rows + rows_per_slice - 1) / rows_per_slice);
   rmsnorm_bwd_dw_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
                                                   static_cast<const __nv_bfloat16*>(g), rstd, dw,
