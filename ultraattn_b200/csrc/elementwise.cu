@@ -274,6 +274,94 @@ rmsnorm_bwd_dw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   for (int q = 0; q < 8; ++q) atomicAdd(dw + c + q, acc[q]);
 }
 
+// Fused form of the two kernels above for H a multiple of 2048: x and g are read once. A block of
+// eight warps walks groups of R rows; warp w owns the column slice [w H/8, (w+1) H/8) of every
+// row, so its dw partial sums stay in registers for the whole walk (one atomicAdd per column and
+// block at the end). The row-wide dot product that dx needs is assembled through shared memory.
+template <int NCH, int R>     // NCH: 16-byte chunks per lane and row (H / 2048); R: rows per group
+__global__ void __launch_bounds__(256, 2)
+rmsnorm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                         const __nv_bfloat16* __restrict__ g, const float* __restrict__ rstd,
+                         __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, int rows, int H) {
+  __shared__ float part[2][R][8];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int col0 = warp * (H / 8) + lane * 8;       // chunk j sits at col0 + j * 256
+  uint4 wv[NCH];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) wv[j] = *reinterpret_cast<const uint4*>(w + col0 + j * 256);
+  float acc[NCH][8];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[j][q] = 0.f;
+  int buf = 0;
+  for (int r0 = blockIdx.x * R; r0 < rows; r0 += static_cast<int>(gridDim.x) * R, buf ^= 1) {
+    uint4 xv[R][NCH], gv[R][NCH];
+    float rs[R], dot[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int row = min(r0 + r, rows - 1);          // rows past the end repeat the last one
+      rs[r] = rstd[row];
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        xv[r][j] = *reinterpret_cast<const uint4*>(x + static_cast<long>(row) * H + col0 + j * 256);
+        gv[r][j] = *reinterpret_cast<const uint4*>(g + static_cast<long>(row) * H + col0 + j * 256);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float d = 0.f;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const uint32_t xs[4] = {xv[r][j].x, xv[r][j].y, xv[r][j].z, xv[r][j].w};
+        const uint32_t gs[4] = {gv[r][j].x, gv[r][j].y, gv[r][j].z, gv[r][j].w};
+        const uint32_t ws[4] = {wv[j].x, wv[j].y, wv[j].z, wv[j].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          d += bf_lo(gs[q]) * bf_lo(ws[q]) * bf_lo(xs[q]) + bf_hi(gs[q]) * bf_hi(ws[q]) * bf_hi(xs[q]);
+      }
+      d = warp_sum(d);
+      if (lane == 0) part[buf][r][warp] = d;
+    }
+    __syncthreads();          // the other buffer is free again: its readers passed this barrier
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float d = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) d += part[buf][r][k];
+      dot[r] = d;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const bool live = r0 + r < rows;
+      const float rr = live ? rs[r] : 0.f;            // a repeated tail row adds nothing to dw
+      const float cc = dot[r] * rr * rr / H;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const uint32_t xs[4] = {xv[r][j].x, xv[r][j].y, xv[r][j].z, xv[r][j].w};
+        const uint32_t gs[4] = {gv[r][j].x, gv[r][j].y, gv[r][j].z, gv[r][j].w};
+        const uint32_t ws[4] = {wv[j].x, wv[j].y, wv[j].z, wv[j].w};
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float xl = bf_lo(xs[q]), xh = bf_hi(xs[q]), gl = bf_lo(gs[q]), gh = bf_hi(gs[q]);
+          o[q] = pack_bf16x2(rr * (gl * bf_lo(ws[q]) - xl * cc), rr * (gh * bf_hi(ws[q]) - xh * cc));
+          acc[j][2 * q] += gl * xl * rr;
+          acc[j][2 * q + 1] += gh * xh * rr;
+        }
+        if (live)
+          *reinterpret_cast<uint4*>(dx + static_cast<long>(r0 + r) * H + col0 + j * 256) =
+              make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NCH; ++j)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) atomicAdd(dw + col0 + j * 256 + q, acc[j][q]);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Rotary embedding (rotate-half convention of Llama): for pair (i, i+64) of a 128-wide head,
 //   y[i] = x[i] cos - x[i+64] sin ; y[i+64] = x[i+64] cos + x[i] sin.
@@ -501,6 +589,27 @@ extern "C" int ua_rmsnorm_bwd(const void* x, const void* w, const void* g, const
                               void* dx, float* dw, int rows, int H, cudaStream_t stream) {
   if (H % 256 != 0) UA_FAIL("ua_rmsnorm_bwd: H must be a multiple of 256");
   if (rows == 0) return 0;
+  if (H % 2048 == 0 && H <= 8192) {
+    // fused single-pass kernel: a few persistent blocks per SM, each walking its share of the rows
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int R = H <= 2048 ? 4 : 2;
+    long want = (static_cast<long>(rows) + R - 1) / R;
+    const unsigned nb = static_cast<unsigned>(want < 6L * sms ? want : 6L * sms);
+    auto xx = static_cast<const __nv_bfloat16*>(x);
+    auto ww = static_cast<const __nv_bfloat16*>(w);
+    auto gg = static_cast<const __nv_bfloat16*>(g);
+    auto dd = static_cast<__nv_bfloat16*>(dx);
+    switch (H / 2048) {
+      case 1: rmsnorm_bwd_fused_kernel<1, 4><<<nb, 256, 0, stream>>>(xx, ww, gg, rstd, dd, dw, rows, H); break;
+      case 2: rmsnorm_bwd_fused_kernel<2, 2><<<nb, 256, 0, stream>>>(xx, ww, gg, rstd, dd, dw, rows, H); break;
+      case 3: rmsnorm_bwd_fused_kernel<3, 2><<<nb, 256, 0, stream>>>(xx, ww, gg, rstd, dd, dw, rows, H); break;
+      default: rmsnorm_bwd_fused_kernel<4, 2><<<nb, 256, 0, stream>>>(xx, ww, gg, rstd, dd, dw, rows, H); break;
+    }
+    UA_CUDA(cudaGetLastError());
+    return 0;
+  }
   const unsigned blocks = (static_cast<long>(rows) * 32 + 255) / 256;
   rmsnorm_bwd_dx_kernel<<<blocks, 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
