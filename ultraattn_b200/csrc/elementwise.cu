@@ -192,6 +192,67 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
+// Same block organisation as the fused backward below for H a multiple of 2048: eight warps own one
+// column slice each of R rows at a time, the row-wide sum of squares goes through shared memory.
+template <int NCH, int R>
+__global__ void __launch_bounds__(256, 2)
+rmsnorm_fwd_sliced_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                          __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int H,
+                          float eps) {
+  __shared__ float part[2][R][8];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int col0 = warp * (H / 8) + lane * 8;
+  uint4 wv[NCH];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) wv[j] = *reinterpret_cast<const uint4*>(w + col0 + j * 256);
+  int buf = 0;
+  for (int r0 = blockIdx.x * R; r0 < rows; r0 += static_cast<int>(gridDim.x) * R, buf ^= 1) {
+    uint4 xv[R][NCH];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int row = min(r0 + r, rows - 1);
+#pragma unroll
+      for (int j = 0; j < NCH; ++j)
+        xv[r][j] = *reinterpret_cast<const uint4*>(x + static_cast<long>(row) * H + col0 + j * 256);
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const uint32_t xs[4] = {xv[r][j].x, xv[r][j].y, xv[r][j].z, xv[r][j].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) ss += bf_lo(xs[q]) * bf_lo(xs[q]) + bf_hi(xs[q]) * bf_hi(xs[q]);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) part[buf][r][warp] = ss;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss += part[buf][r][k];
+      const float rr = rsqrtf(ss / H + eps);
+      const bool live = r0 + r < rows;
+      if (live && threadIdx.x == 0 && rstd != nullptr) rstd[r0 + r] = rr;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const uint32_t xs[4] = {xv[r][j].x, xv[r][j].y, xv[r][j].z, xv[r][j].w};
+        const uint32_t ws[4] = {wv[j].x, wv[j].y, wv[j].z, wv[j].w};
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          o[q] = pack_bf16x2(bf_lo(xs[q]) * rr * bf_lo(ws[q]), bf_hi(xs[q]) * rr * bf_hi(ws[q]));
+        if (live)
+          *reinterpret_cast<uint4*>(y + static_cast<long>(r0 + r) * H + col0 + j * 256) =
+              make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+}
+
 // dx = rstd * (g*w - x * rstd^2 * mean(g*w*x)). One warp per row, two passes over the row (the
 // second one hits L1/L2) so that nothing but the running dot product is kept in registers.
 __global__ void __launch_bounds__(256)
@@ -578,6 +639,21 @@ extern "C" int ua_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
   auto xx = static_cast<const __nv_bfloat16*>(x);
   auto ww = static_cast<const __nv_bfloat16*>(w);
   auto yy = static_cast<__nv_bfloat16*>(y);
+  if (H % 2048 == 0) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long want = (static_cast<long>(rows) + 3) / 4;
+    const unsigned nb = static_cast<unsigned>(want < 8L * sms ? want : 8L * sms);
+    switch (H / 2048) {
+      case 1: rmsnorm_fwd_sliced_kernel<1, 4><<<nb, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps); break;
+      case 2: rmsnorm_fwd_sliced_kernel<2, 4><<<nb, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps); break;
+      case 3: rmsnorm_fwd_sliced_kernel<3, 4><<<nb, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps); break;
+      default: rmsnorm_fwd_sliced_kernel<4, 4><<<nb, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps); break;
+    }
+    UA_CUDA(cudaGetLastError());
+    return 0;
+  }
   if (H <= 4096) rmsnorm_fwd_kernel<16><<<blocks, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps);
   else rmsnorm_fwd_kernel<32><<<blocks, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps);
   UA_CUDA(cudaGetLastError());
