@@ -6,10 +6,14 @@
 // stored K-contiguous ([N,K] row-major, the torch `linear` weight) or N-contiguous ([K,N]
 // row-major). That covers y = x W^T, dx = dy W and dW = dy^T x without any transpose copy.
 //
-// One persistent CTA per SM walks output tiles of 128 x 256. Warp 0 feeds a 4-stage shared
-// memory ring with TMA, warp 1 issues tcgen05.mma, warps 2..5 drain the accumulator from TMEM.
-// The accumulator is double-buffered (2 x 256 TMEM columns) so the epilogue of tile i overlaps
-// the main loop of tile i+1.
+// One persistent CTA per SM walks output tiles. Warp 0 feeds a shared-memory ring with TMA, warp 1
+// issues tcgen05.mma, the remaining warps drain the accumulator from TMEM. Two tile shapes:
+//  * 128 x 256 (MH = 1): 4 stages, two 256-column TMEM accumulators so the epilogue of tile i
+//    overlaps the main loop of tile i+1; used when there are few tiles.
+//  * 256 x 256 (MH = 2): two M = 128 instructions per k-step share the B tile in shared memory
+//    (acc 0 | acc 1 = all 512 TMEM columns, 3 stages, 8 epilogue warps). The shared-memory port
+//    bounds this kernel (TMA writes + operand reads), and the taller tile needs 160 B per tensor
+//    clock instead of 192; used when the problem has at least four waves of such tiles.
 //
 // Two optional fusions serve the head-parallel (Ulysses) attention path, where an all-to-all
 // normally sits next to a projection GEMM (reference: comm_lib/comm_utils.py:32-45 A2AComm and
@@ -25,12 +29,16 @@
 
 namespace ua {
 
-constexpr int GEMM_BM = 128;
 constexpr int GEMM_BN = 256;
 constexpr int GEMM_BK = 64;
-constexpr int GEMM_STAGES = 4;
 constexpr int GEMM_MAX_PEERS = 8;
-constexpr int GEMM_THREADS = 192;
+template <int MH> struct GemmCfg {
+  static constexpr int BM = 128 * MH;
+  static constexpr int STAGES = MH == 1 ? 4 : 3;
+  static constexpr int ACC_BUFS = MH == 1 ? 2 : 1;
+  static constexpr int EPI_WARPS = 4 * MH;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+};
 
 struct GemmParams {
   CUtensorMap tmA[GEMM_MAX_PEERS];
@@ -49,21 +57,26 @@ struct GemmParams {
   int* status;
 };
 
+template <int MH>
 struct __align__(1024) GemmSmem {
-  uint8_t a[GEMM_STAGES][GEMM_BM * GEMM_BK * 2];   // 16 KB per stage
-  uint8_t b[GEMM_STAGES][GEMM_BN * GEMM_BK * 2];   // 32 KB per stage
-  uint64_t full[GEMM_STAGES];
-  uint64_t empty[GEMM_STAGES];
+  uint8_t a[GemmCfg<MH>::STAGES][GemmCfg<MH>::BM * GEMM_BK * 2];   // 16 KB per 128 rows and stage
+  uint8_t b[GemmCfg<MH>::STAGES][GEMM_BN * GEMM_BK * 2];           // 32 KB per stage
+  uint64_t full[GemmCfg<MH>::STAGES];
+  uint64_t empty[GemmCfg<MH>::STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <int MH>
+__global__ void __launch_bounds__(GemmCfg<MH>::THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
+  constexpr int GEMM_STAGES = GemmCfg<MH>::STAGES;
+  constexpr int ACC_BUFS = GemmCfg<MH>::ACC_BUFS;
+  constexpr int TILE_M = GemmCfg<MH>::BM;
   extern __shared__ uint8_t smem_raw[];
-  GemmSmem& s = *reinterpret_cast<GemmSmem*>(
+  GemmSmem<MH>& s = *reinterpret_cast<GemmSmem<MH>*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -75,7 +88,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.acc_full[i], 1);
-      mbar_init(&s.acc_empty[i], 128);
+      mbar_init(&s.acc_empty[i], 32 * GemmCfg<MH>::EPI_WARPS);
     }
     s.abort_flag = 0;
     fence_mbar_init();
@@ -90,7 +103,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t tmem_base = s.tmem_base;
   WaitCtx wc{&s.abort_flag, p.status, 4000000000ull};
 
-  const int m_tiles = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int m_tiles = (p.M + TILE_M - 1) / TILE_M;
   const int n_tiles = (p.N + GEMM_BN - 1) / GEMM_BN;
   const int total = m_tiles * n_tiles;
   const int k_blocks = (p.K + GEMM_BK - 1) / GEMM_BK;
@@ -102,22 +115,23 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       tma_prefetch_desc(&p.tmB);
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * GEMM_BM;
+        const int m0 = (tile % m_tiles) * TILE_M;
         const int n0 = (tile / m_tiles) * GEMM_BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int st = it % GEMM_STAGES;
           const uint32_t ph = (it / GEMM_STAGES) & 1;
           if (!mbar_wait(&s.empty[st], ph ^ 1, wc, 10)) break;
-          mbar_arrive_expect_tx(&s.full[st], (GEMM_BM + GEMM_BN) * GEMM_BK * 2);
+          mbar_arrive_expect_tx(&s.full[st], (TILE_M + GEMM_BN) * GEMM_BK * 2);
           const int k0 = kb * GEMM_BK;
           const int src = k0 / p.k_per_src;
           const int ksrc = k0 - src * p.k_per_src;
           if (!p.a_mn_major) {
+            // one box of TILE_M rows x 64 k (rows of 128 B; the second 128 rows start at +16 KB)
             tma_load_2d(s.a[st], &p.tmA[src], &s.full[st], ksrc, p.a_row_off + m0);
           } else {
-            // [K,M] storage: two 64-wide M panels of 64 k-rows each
-            tma_load_2d(s.a[st], &p.tmA[src], &s.full[st], m0, p.a_row_off + ksrc);
-            tma_load_2d(s.a[st] + 8192, &p.tmA[src], &s.full[st], m0 + 64, p.a_row_off + ksrc);
+            // [K,M] storage: 64-wide M panels of 64 k-rows each, two per 128 rows
+            for (int pm = 0; pm < 2 * MH; ++pm)
+              tma_load_2d(s.a[st] + pm * 8192, &p.tmA[src], &s.full[st], m0 + pm * 64, p.a_row_off + ksrc);
           }
           if (!p.b_mn_major) {
             tma_load_2d(s.b[st], &p.tmB, &s.full[st], k0, n0);
@@ -131,7 +145,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ---------------------------------------------
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(GEMM_BM, GEMM_BN, p.a_mn_major, p.b_mn_major);
+      const uint32_t idesc = make_idesc_bf16(128, GEMM_BN, p.a_mn_major, p.b_mn_major);
       // K-major tile: rows of 128 B, 8-row groups 1024 B apart; 16 k-elements = 32 B.
       // MN-major tile: 64-element panels 8192 B apart (LBO), 8 k-rows = 1024 B (SBO);
       //                16 k-rows = 2048 B.
@@ -142,11 +156,11 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       uint32_t it = 0;
       uint32_t tcount = 0;
       for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++tcount) {
-        const int buf = tcount & 1;
-        const uint32_t aph = (tcount >> 1) & 1;
+        const int buf = ACC_BUFS == 2 ? (tcount & 1) : 0;
+        const uint32_t aph = ACC_BUFS == 2 ? ((tcount >> 1) & 1) : (tcount & 1);
         if (!mbar_wait(&s.acc_empty[buf], aph ^ 1, wc, 20)) break;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * GEMM_BN;
+        const uint32_t d_tmem = tmem_base + buf * GEMM_BN;      // MH = 2: halves at columns 0 and 256
         bool ok = true;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int st = it % GEMM_STAGES;
@@ -157,9 +171,12 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
           const uint32_t b_addr = smem_u32(s.b[st]);
 #pragma unroll
           for (int k = 0; k < GEMM_BK / 16; ++k) {
-            const uint64_t ad = make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
             const uint64_t bd = make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
-            umma_ss(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+            for (int h = 0; h < MH; ++h) {
+              const uint64_t ad = make_smem_desc_sw128(a_addr + h * 16384 + k * a_kstep, a_lbo, 1024);
+              umma_ss(d_tmem + h * GEMM_BN, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
           }
           tc_commit(&s.empty[st]);
         }
@@ -170,17 +187,18 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   } else {
     // ------------------------------- epilogue (4 warps) -------------------------------------
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
-    const int row_in_tile = quad * 32 + lane;
+    const int half = (warp - 2) >> 2;                 // which 128 rows of the tile (MH = 2: warps 6-9 take the second)
+    const int row_in_tile = half * 128 + quad * 32 + lane;
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++tcount) {
-      const int buf = tcount & 1;
-      const uint32_t aph = (tcount >> 1) & 1;
-      const int m0 = (tile % m_tiles) * GEMM_BM;
+      const int buf = ACC_BUFS == 2 ? (tcount & 1) : 0;
+      const uint32_t aph = ACC_BUFS == 2 ? ((tcount >> 1) & 1) : (tcount & 1);
+      const int m0 = (tile % m_tiles) * TILE_M;
       const int n0 = (tile / m_tiles) * GEMM_BN;
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.acc_full[buf], aph, wc, 30))) break;
       tc_fence_after_sync();
       const int row = m0 + row_in_tile;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * GEMM_BN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + (buf + half) * GEMM_BN;
 #pragma unroll 1
       for (int c = 0; c < GEMM_BN / 32; ++c) {
         uint32_t v[32];
@@ -225,7 +243,22 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
 
 using namespace ua;
 
-static int g_gemm_smem_set[64] = {0};
+static int g_gemm_smem_set[2][64] = {{0}};
+
+template <int MH>
+static int launch_gemm(const GemmParams& p, int grid, cudaStream_t stream) {
+  const int smem_bytes = sizeof(GemmSmem<MH>) + 1024;
+  int dev = 0;
+  UA_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !g_gemm_smem_set[MH - 1][dev]) {
+    UA_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<MH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 smem_bytes));
+    g_gemm_smem_set[MH - 1][dev] = 1;
+  }
+  gemm_bf16_kernel<MH><<<grid, GemmCfg<MH>::THREADS, smem_bytes, stream>>>(p);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}
 
 // a_ptrs / c_ptrs: arrays of n_src / n_dst device pointers (host arrays).
 // lda / ldb / ldc in elements. Requirements: K % 8 == 0, lda % 8 == 0, ldb % 8 == 0,
@@ -249,12 +282,15 @@ extern "C" int ua_gemm_bf16(const void* const* a_ptrs, int n_src, long a_rows_to
   p.n_dst = n_dst; p.cols_per_dst = N / n_dst; p.dst_row_off = dst_row_off;
   p.status = status;
   for (int i = 0; i < n_dst; ++i) p.c_dst[i] = static_cast<__nv_bfloat16*>(c_ptrs[i]);
+  // tile height: 256 rows when that still leaves at least four waves of tiles (UA_GEMM_MH forces)
+  int mh = (static_cast<long>((M + 255) / 256) * ((N + GEMM_BN - 1) / GEMM_BN) >= 4L * num_sms) ? 2 : 1;
+  if (const char* e = getenv("UA_GEMM_MH")) mh = atoi(e) == 2 ? 2 : 1;
   for (int i = 0; i < n_src; ++i) {
     if (!a_mn_major) {
       // [rows, k_per_src] K contiguous
       uint64_t dims[2] = {static_cast<uint64_t>(p.k_per_src), static_cast<uint64_t>(a_rows_total)};
       uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
-      uint32_t box[2] = {GEMM_BK, GEMM_BM};
+      uint32_t box[2] = {GEMM_BK, static_cast<uint32_t>(128 * mh)};
       if (make_tmap_2byte(&p.tmA[i], a_ptrs[i], 2, dims, str, box)) return -1;
     } else {
       // [k rows, M] M contiguous; a_rows_total counts k rows
@@ -275,20 +311,12 @@ extern "C" int ua_gemm_bf16(const void* const* a_ptrs, int n_src, long a_rows_to
     uint32_t box[2] = {64, GEMM_BK};
     if (make_tmap_2byte(&p.tmB, b, 2, dims, str, box)) return -1;
   }
-  const int smem_bytes = sizeof(GemmSmem) + 1024;
-  int dev = 0;
-  UA_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !g_gemm_smem_set[dev]) {
-    UA_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 smem_bytes));
-    g_gemm_smem_set[dev] = 1;
-  }
-  const int m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
+  const int m_tiles = (M + 128 * mh - 1) / (128 * mh);
   const int n_tiles = (N + GEMM_BN - 1) / GEMM_BN;
   int grid = m_tiles * n_tiles;
   if (grid > num_sms) grid = num_sms;
   if (grid < 1) return 0;
-  gemm_bf16_kernel<<<grid, GEMM_THREADS, smem_bytes, stream>>>(p);
-  UA_CUDA(cudaGetLastError());
+  if (mh == 2) return launch_gemm<2>(p, grid, stream);
+  return launch_gemm<1>(p, grid, stream);
   return 0;
 }
