@@ -230,6 +230,55 @@ def test_llama_context_parallel_training_2gpu():
     assert res[0]["nccl"] == res[1]["nccl"]
 
 
+def _campaign_worker(rank, world, port, root, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    try:
+        from ultraattn_b200 import patterns as P
+        from ultraattn_b200.drivers import report, task1
+        from ultraattn_b200.drivers.exp_configs import ExpSpace
+        from ultraattn_b200.ops import attention as A
+        from ultraattn_b200.patterns.blocks import BSA_Config
+        from ultraattn_b200.plandb import ABLATION_SUFFIXES, Prof_DB, plan_key_prefix
+        cfg = BSA_Config(None, None, {"bsa_repr": P.star(4, 1), "CP": (2, 1)})
+        space = ExpSpace("bsa_infer", [0], [cfg], [cfg], [8192], [4], D=128, S_per_gpu_bounds=(1, 1 << 20))
+        db = Prof_DB("unit", "B200", root=root)
+        work = task1.step1_generate_intra_bsa_exe_plans(space, db, time_limit=2.0)
+        task1.step2_profile_intra_bsa_exe_plans(work, db, dev, world)
+        dist.barrier()
+        torch.cuda.synchronize()
+        A.check_status(dev)
+        shape = {"S": (8192, 8192), "Nh": (4, 4), "bs": 1, "D": 128}
+        prefix = plan_key_prefix(0, (2, 1), shape, cfg)
+        prof = [Prof_DB("unit", "B200", root=root).get_profile(prefix + s) for s in ABLATION_SUFFIXES]
+        ok = all(p is not None and float(p["time"]) > 0 and float(p["hfu"]) > 0 for p in prof)
+        rows = report.build_rows({prefix + s: p for s, p in zip(ABLATION_SUFFIXES, prof)})
+        ret[rank] = {"ok": ok, "ultra": rows[0]["ultraattn"], "n_rows": len(rows)}
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = {"error": f"{type(e).__name__}: {e}\n{traceback.format_exc()}"}
+    finally:
+        dist.destroy_process_group()
+
+
+def test_planning_campaign_profiles_on_2gpu(tmp_path):
+    """Plan generation, measurement of every plan variant with the NCCL executor on two GPUs, the
+    profile database and the report table, end to end on a small star-attention prefill."""
+    _need(2)
+    port = 29250 + os.getpid() % 100
+    ret = mp.Manager().dict()
+    mp.spawn(_campaign_worker, args=(2, port, str(tmp_path), ret), nprocs=2, join=True)
+    res = dict(ret)
+    for r in range(2):
+        assert "error" not in res[r], res[r].get("error")
+        assert res[r]["ok"] and res[r]["n_rows"] == 1 and res[r]["ultra"] > 0, res
+
+
 def test_context_parallel_4gpu_fused():
     _need(4)
     res = _run(4, {"pattern": "strided", "args": (8, 4, 2), "S": 4096, "H": 2, "path": "fused"})
