@@ -193,6 +193,10 @@ __device__ __forceinline__ void tma_store_wait_all() {
 __device__ __forceinline__ void tma_store_wait_read_all() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+// all but the most recent group have finished reading their shared-memory source
+__device__ __forceinline__ void tma_store_wait_read_all_but_one() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
 
 // ----------------------------------------------------------------------------------------------
 // tcgen05: tensor memory management
