@@ -1,0 +1,31 @@
+# Convenience targets (the reference drives its campaigns from scripts/Makefile; same names here).
+PY ?= python
+GPUS ?= 8
+CLUSTER_NAME ?= local
+PLATFORM ?= B200
+export CLUSTER_NAME PLATFORM
+
+.PHONY: build test test-gpu bench cluster_profile bsa_train dense_train bsa_infer report
+
+build:            ## compile the sm_100a kernel library in-tree (nvcc; works without a GPU)
+	$(PY) -c "import __graft_entry__ as g; g.build()"
+
+test:             ## CPU tests (planner, gloo executors, host logic of the fused path, model parity)
+	$(PY) -m pytest tests -q -m "not gpu"
+
+test-gpu:         ## kernel and multi-GPU tests (multi-GPU ones skip on a single GPU)
+	$(PY) -m pytest tests -q -m gpu
+
+bench:            ## headline benchmark on $(GPUS) GPUs
+	$(PY) -m ultraattn_b200.drivers.launch --gpus $(GPUS) -- bench.py --gpus $(GPUS)
+
+cluster_profile:  ## kernel grid + link curves -> logs/m_configs (inputs of the cost model)
+	$(PY) -m ultraattn_b200.drivers.cluster_profile --kernels --out logs/m_configs
+	$(PY) -m ultraattn_b200.drivers.launch --gpus 2 -- -m ultraattn_b200.drivers.cluster_profile --comm --out logs/m_configs
+
+bsa_train dense_train bsa_infer:   ## planning + profiling campaign of one experiment class
+	$(PY) -m ultraattn_b200.drivers.launch --gpus $(GPUS) -- search_algo/task1_bsa.py --exp-class $@
+	$(PY) -m ultraattn_b200.drivers.launch --gpus $(GPUS) -- search_algo/task2_bsa.py --exp-class $@
+
+report:           ## figure tables from the profile database
+	$(PY) -m ultraattn_b200.drivers.report --db database/$(CLUSTER_NAME)/$(PLATFORM)
