@@ -31,10 +31,10 @@
 //   warps 0-7 : two softmax warpgroups; thread (key, half) handles 64 of the 128 query columns of
 //               its key row; in the epilogue one warpgroup stores dK, the other dV
 //   warps 8-11: dQ drain warpgroup (one thread per head-dim element): each warp reads its whole
-//               32 x 128 slice into registers (handing tensor memory back at once), transposes it
-//               through two alternating 16-query staging tiles and issues
-//               cp.reduce.async.bulk.tensor (fp32 add at the memory side) into the dQ accumulator;
-//               one reduce is in flight while the next tile is staged
+//               32 x 128 slice into registers (handing tensor memory back at once); the four warps
+//               transpose it into two alternating [16 queries][128] staging tiles and one thread
+//               issues cp.reduce.async.bulk.tensor (fp32 add at the memory side, 512-byte rows)
+//               into the dQ accumulator; one reduce is in flight while the next tile is staged
 //   warp  12  : TMA producer (K, V once; Q double-buffered; dO single-buffered)
 //   warp  13  : tcgen05.mma issuer, TMEM allocation
 // dK/dV leave the CTA either as bf16 stores (the CTA is their only producer) or as fp32
@@ -87,7 +87,7 @@ struct BwdParams {
   long lse_head_stride[ATTN_MAX_SRC];
   long lse_batch_stride[ATTN_MAX_SRC];
   int q_tokens[ATTN_MAX_SRC];       // tokens in each query-side source (bounds for lse / D)
-  CUtensorMap tmdQ[ATTN_MAX_SRC];   // fp32 [batch, tokens, q heads, 128] accumulators, box 32x1x16
+  CUtensorMap tmdQ[ATTN_MAX_SRC];   // fp32 [batch, tokens, q heads, 128] accumulators, box 128x1x16
   float* dq_ptr[ATTN_MAX_SRC];      // the same accumulators as plain pointers
   long dq_row_stride[ATTN_MAX_SRC];     // elements between tokens
   long dq_batch_stride[ATTN_MAX_SRC];
@@ -114,7 +114,7 @@ struct __align__(1024) BwdSmem {
   uint8_t q[2][BWD_TILE_BYTES];
   uint8_t d_o[BWD_TILE_BYTES];
   uint8_t ds[BWD_TILE_BYTES];              // dS^T: two 64-query panels of [128 keys][128 B], swizzled
-  float dq_stage[4][2][16 * 32];           // per drain warp: two tiles of [16 queries][32 head-dim] fp32
+  float dq_stage[2][16 * 128];             // two tiles of [16 queries][128 head-dim] fp32 shared by the drain warps
   // One extra 16-wide reduction step folds the row terms into the products: S^T and dP^T come out
   // of the tensor core as S^T - lse / scale and dP^T - D. aug[stage]: per query 16 bf16 (columns 0-2:
   // three bf16 parts of -lse * log2(e) / scale_log2, columns 4-6: parts of -D, rest 0); ones_lse /
@@ -664,7 +664,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     const int quad = warp & 3;                       // TMEM lanes quad*32.. = head-dim slice
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t t_dq = tmem_base + lane_base + 384;
-    float* stage = s.dq_stage[quad][0];        // two 16-query tiles, 512 floats apart
+    float* stage = s.dq_stage[0];              // two 16-query tiles, 2048 floats apart
     bool ok = true;
     uint32_t i = 0;
     for (int g = 0; g < p.kv_group && ok; ++g) {
@@ -715,20 +715,21 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
           } else {
 #pragma unroll
             for (int h = 0; h < 8; ++h) {              // 16 queries at a time, two staging tiles in turn
-              // the reduce issued two chunks ago (same tile) must have finished reading it; the
-              // one issued last may still be in flight while this chunk is staged
-              if (lane == 0) tma_store_wait_read_all_but_one();
-              __syncwarp();
+              // The four warps fill one [16 queries][128 head-dim] tile (a 32-wide slice each) and one
+              // thread issues a single reduce with 512-byte rows. The reduce issued two chunks
+              // ago (same tile) must have finished reading it; the last one may still be in flight.
+              if (quad == 0 && lane == 0) tma_store_wait_read_all_but_one();
+              asm volatile("bar.sync 1, 128;" ::: "memory");
               BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0 && (h & 1) == 0, 52 + (h >> 1) * 3);
-              float* tile = stage + (h & 1) * 512;
+              float* tile = stage + (h & 1) * 2048;
 #pragma unroll
               for (int c = 0; c < 16; ++c)
-                tile[c * 32 + lane] = __uint_as_float(dv[h >> 1][(h & 1) * 16 + c]) * p.scale;
+                tile[c * 128 + quad * 32 + lane] = __uint_as_float(dv[h >> 1][(h & 1) * 16 + c]) * p.scale;
               fence_proxy_async_smem();
-              __syncwarp();
+              asm volatile("bar.sync 1, 128;" ::: "memory");
               BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0 && (h & 1) == 0, 53 + (h >> 1) * 3);
-              if (lane == 0) {
-                tma_reduce_add_4d(tdq, tile, quad * 32, head, qrow + h * 16, batch);
+              if (quad == 0 && lane == 0) {
+                tma_reduce_add_4d(tdq, tile, 0, head, qrow + h * 16, batch);
                 tma_store_commit();
               }
               BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0 && (h & 1) == 0, 54 + (h >> 1) * 3);
@@ -830,7 +831,7 @@ extern "C" int ua_attn_bwd(const UaTensorSrc* q_src, const UaTensorSrc* do_src,
                                                       : q_side[i].dq_row_stride * t.tokens;
       uint64_t str[3] = {ATTN_D * 4ull, static_cast<uint64_t>(q_side[i].dq_row_stride) * 4,
                          static_cast<uint64_t>(bstr) * 4};
-      uint32_t box[4] = {32, 1, 16, 1};
+      uint32_t box[4] = {128, 1, 16, 1};
       if (make_tmap_f32(&p.tmdQ[i], q_side[i].dq, 4, dims, str, box)) return -1;
       p.dq_ptr[i] = q_side[i].dq;
       p.dq_row_stride[i] = q_side[i].dq_row_stride;
@@ -981,7 +982,7 @@ extern "C" int ua_attn_bwd_dense_noalloc(const void* q, const void* k, const voi
     uint64_t dims[4] = {ATTN_D, static_cast<uint64_t>(n_heads), static_cast<uint64_t>(tokens), 1};
     uint64_t str[3] = {ATTN_D * 4ull, static_cast<uint64_t>(n_heads) * ATTN_D * 4,
                        static_cast<uint64_t>(n_dq) * 4};
-    uint32_t box[4] = {32, 1, 16, 1};
+    uint32_t box[4] = {128, 1, 16, 1};
     if (make_tmap_f32(&p.tmdQ[0], dq32, 4, dims, str, box)) return -1;
     p.dq_ptr[0] = dq32;
     p.dq_row_stride[0] = static_cast<long>(n_heads) * ATTN_D;
