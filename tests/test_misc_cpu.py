@@ -118,3 +118,13 @@ def test_launcher_command_and_env():
     assert env["CLUSTER_NAME"] == "pool" and env["PLATFORM"] == "B200"
     assert env["NCCL_NVLS_ENABLE"] == "0" and env["UA_NVLS"] == "0"
     assert launch.main(["--gpus", "2", "--dry-run", "--", "-m", "x"]) == 0
+
+
+def test_cluster_probe_local_and_sinfo_parsing():
+    from ultraattn_b200.drivers import cluster_probe as cp
+    res = cp.fan_out(["localhost", "127.0.0.1"], ["echo", "hello"])
+    assert [r["rc"] for r in res] == [0, 0] and all(r["stdout"].strip() == "hello" for r in res)
+    assert cp.run_on_host("localhost", ["definitely-not-a-command-xyz"])["rc"] == -1
+    rows = cp.parse_sinfo("gpu* up 4 idle\ngpu* up 12 alloc\ncpu up 3 idle~\n")
+    assert rows[0] == {"partition": "gpu", "avail": "up", "nodes": 4, "state": "idle"} and len(rows) == 3
+    assert cp.main(["--hosts", "localhost", "--", "true"]) == 0
