@@ -32,9 +32,9 @@
 //               its key row; in the epilogue one warpgroup stores dK, the other dV
 //   warps 8-11: dQ drain warpgroup (one thread per head-dim element): each warp reads its whole
 //               32 x 128 slice into registers (handing tensor memory back at once); the four warps
-//               transpose it into two alternating [16 queries][128] staging tiles and one thread
+//               transpose it into three rotating [16 queries][128] staging tiles and one thread
 //               issues cp.reduce.async.bulk.tensor (fp32 add at the memory side, 512-byte rows)
-//               into the dQ accumulator; one reduce is in flight while the next tile is staged
+//               into the dQ accumulator; two reduces are in flight while the next tile is staged
 //   warp  12  : TMA producer (K, V once; Q double-buffered; dO single-buffered)
 //   warp  13  : tcgen05.mma issuer, TMEM allocation
 // dK/dV leave the CTA either as bf16 stores (the CTA is their only producer) or as fp32
@@ -114,15 +114,19 @@ struct __align__(1024) BwdSmem {
   uint8_t q[2][BWD_TILE_BYTES];
   uint8_t d_o[BWD_TILE_BYTES];
   uint8_t ds[BWD_TILE_BYTES];              // dS^T: two 64-query panels of [128 keys][128 B], swizzled
-  float dq_stage[2][16 * 128];             // two tiles of [16 queries][128 head-dim] fp32 shared by the drain warps
+  float dq_stage[3][16 * 128];             // three tiles of [16 queries][128 head-dim] fp32 shared by the drain warps
   // One extra 16-wide reduction step folds the row terms into the products: S^T and dP^T come out
   // of the tensor core as S^T - lse / scale and dP^T - D. aug[stage]: per query 16 bf16 (columns 0-2:
   // three bf16 parts of -lse * log2(e) / scale_log2, columns 4-6: parts of -D, rest 0); ones_lse /
-  // ones_d: per key 16 bf16 with ones in columns 0-2 resp. 4-6. Layout: K-major without swizzle,
+  // ones_d: per key 16 bf16 with ones in columns 0-2 resp. 4-6. Only the first 8 columns of each
+  // operand are stored: the second 8 columns of both row-term stages are one shared block of zeros,
+  // so what the ones operands present there (whatever finite data follows them) multiplies zero.
+  // Layout: K-major without swizzle,
   // row r's first 8 columns at r * 16, the other 8 at 2048 + r * 16.
-  uint8_t aug[2][4096];
-  uint8_t ones_lse[4096];
-  uint8_t ones_d[4096];
+  uint8_t ones_lse[2048];     // first 8 columns only; the second chunk of a ones operand may alias any finite data
+  uint8_t ones_d[2048];
+  uint8_t aug[2][2048];       // first 8 columns of each stage; both share aug_zero as their second chunk
+  uint8_t aug_zero[2048];
   uint64_t kv_full;
   uint64_t q_full[2];
   uint64_t q_empty[2];
@@ -229,8 +233,16 @@ __device__ __forceinline__ void bwd_phase_a(uint32_t t_st, float scale_log2, boo
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
-  BwdSmem& s = *reinterpret_cast<BwdSmem*>(
-      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  // The operand tiles need 1 KB alignment and the CTA uses all 227 KB, so there is no room to align
+  // by hand: the dynamic shared memory window itself has to start on a 1 KB boundary (it does on
+  // sm_100 with no static shared memory). If it ever does not, fail loudly instead of computing
+  // with misplaced swizzle atoms.
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0 && p.status != nullptr && atomicCAS(p.status, 0, UA_ERR_SMEM_ALIGN) == 0)
+      p.status[1] = 999;
+    return;
+  }
+  BwdSmem& s = *reinterpret_cast<BwdSmem*>(smem_raw);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -271,12 +283,11 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     if (r < 128) {
       *reinterpret_cast<uint4*>(s.ones_lse + row * 16) = make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u);
-      *reinterpret_cast<uint4*>(s.ones_lse + 2048 + row * 16) = zero;
-      *reinterpret_cast<uint4*>(s.aug[0] + 2048 + row * 16) = zero;
+      *reinterpret_cast<uint4*>(s.aug_zero + row * 16) = zero;
+      *reinterpret_cast<uint4*>(s.aug[0] + row * 16) = zero;
     } else {
       *reinterpret_cast<uint4*>(s.ones_d + row * 16) = make_uint4(0u, 0u, 0x3F803F80u, 0x00003F80u);
-      *reinterpret_cast<uint4*>(s.ones_d + 2048 + row * 16) = zero;
-      *reinterpret_cast<uint4*>(s.aug[1] + 2048 + row * 16) = zero;
+      *reinterpret_cast<uint4*>(s.aug[1] + row * 16) = zero;
     }
   }
   fence_proxy_async_smem();
@@ -363,8 +374,9 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       const uint64_t q_nmaj0 = make_smem_desc_sw128(smem_u32(s.q[0]), 16384, 1024); // B of dK
       const uint64_t ones_lse_d = make_smem_desc_noswz(smem_u32(s.ones_lse), 2048, 128);
       const uint64_t ones_d_d = make_smem_desc_noswz(smem_u32(s.ones_d), 2048, 128);
-      const uint64_t aug_d0 = make_smem_desc_noswz(smem_u32(s.aug[0]), 2048, 128);
-      constexpr uint64_t AUG_STAGE = 4096 >> 4;
+      // stage 0: chunks at aug[0] and aug_zero (4096 apart); stage 1: at aug[1] and aug_zero (2048 apart)
+      const uint64_t aug_desc[2] = {make_smem_desc_noswz(smem_u32(s.aug[0]), 4096, 128),
+                                    make_smem_desc_noswz(smem_u32(s.aug[1]), 2048, 128)};
       constexpr uint64_t Q_STAGE = BWD_TILE_BYTES >> 4;
       // K-major operands: 16 elements of the reduction = 32 B, the two 64-element halves 16384 B apart
       auto koff = [](int kk) -> uint64_t { return static_cast<uint64_t>(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4); };
@@ -375,13 +387,13 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_ss(t_st, k_kmaj + koff(kk), qd + koff(kk), idesc_kk, kk > 0 ? 1u : 0u);
-        umma_ss(t_st, ones_lse_d, aug_d0 + st * AUG_STAGE, idesc_kk, 1u);     // - lse / scale
+        umma_ss(t_st, ones_lse_d, aug_desc[st], idesc_kk, 1u);     // - lse / scale
       };
       auto issue_dp = [&](int st) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_ss(t_dp, v_kmaj + koff(kk), do_kmaj + koff(kk), idesc_kk, kk > 0 ? 1u : 0u);
-        umma_ss(t_dp, ones_d_d, aug_d0 + st * AUG_STAGE, idesc_kk, 1u);       // - D
+        umma_ss(t_dp, ones_d_d, aug_desc[st], idesc_kk, 1u);       // - D
       };
       bool ok = true;
       do {
@@ -664,9 +676,10 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     const int quad = warp & 3;                       // TMEM lanes quad*32.. = head-dim slice
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t t_dq = tmem_base + lane_base + 384;
-    float* stage = s.dq_stage[0];              // two 16-query tiles, 2048 floats apart
+    float* stage = s.dq_stage[0];
     bool ok = true;
     uint32_t i = 0;
+    uint32_t n_chunk = 0;
     for (int g = 0; g < p.kv_group && ok; ++g) {
       const int head = kv_head * p.kv_group + g;
       for (int e = col.seg_begin; e < col.seg_end && ok; ++e) {
@@ -714,14 +727,14 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
             }
           } else {
 #pragma unroll
-            for (int h = 0; h < 8; ++h) {              // 16 queries at a time, two staging tiles in turn
+            for (int h = 0; h < 8; ++h) {              // 16 queries at a time, three staging tiles in turn
               // The four warps fill one [16 queries][128 head-dim] tile (a 32-wide slice each) and one
-              // thread issues a single reduce with 512-byte rows. The reduce issued two chunks
-              // ago (same tile) must have finished reading it; the last one may still be in flight.
-              if (quad == 0 && lane == 0) tma_store_wait_read_all_but_one();
+              // thread issues a single reduce with 512-byte rows. The reduce issued three chunks
+              // ago (same tile) must have finished reading it; the last two may still be in flight.
+              if (quad == 0 && lane == 0) tma_store_wait_read_all_but<2>();
               asm volatile("bar.sync 1, 128;" ::: "memory");
               BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0 && (h & 1) == 0, 52 + (h >> 1) * 3);
-              float* tile = stage + (h & 1) * 2048;
+              float* tile = stage + ((n_chunk + h) % 3) * 2048;
 #pragma unroll
               for (int c = 0; c < 16; ++c)
                 tile[c * 128 + quad * 32 + lane] = __uint_as_float(dv[h >> 1][(h & 1) * 16 + c]) * p.scale;
@@ -735,6 +748,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
               BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0 && (h & 1) == 0, 54 + (h >> 1) * 3);
             }
           }
+          n_chunk += 8;
           BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0, 51);
         }
       }
@@ -868,7 +882,7 @@ extern "C" int ua_attn_bwd(const UaTensorSrc* q_src, const UaTensorSrc* do_src,
   }
   p.stage.flags = stage_flags;
   p.stage.epoch = stage_epoch;
-  const int smem_bytes = sizeof(BwdSmem) + 1024;
+  const int smem_bytes = sizeof(BwdSmem);
   int dev = 0;
   UA_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !g_bwd_smem_set[dev]) {
@@ -1013,7 +1027,7 @@ extern "C" int ua_attn_bwd_dense_noalloc(const void* q, const void* k, const voi
   p.stage.flags = nullptr;
   p.stage.epoch = 1;
 
-  const int smem_bytes = sizeof(BwdSmem) + 1024;
+  const int smem_bytes = sizeof(BwdSmem);
   if (!g_bwd_smem_set[dev]) {
     UA_CUDA(cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     g_bwd_smem_set[dev] = 1;

@@ -19,6 +19,7 @@ enum : int {
   UA_ERR_MBAR_TIMEOUT = 1,   // an mbarrier wait inside a kernel ran out
   UA_ERR_FLAG_TIMEOUT = 2,   // a global-memory flag wait (peer / staging) ran out
   UA_ERR_BAD_ARG = 3,
+  UA_ERR_SMEM_ALIGN = 4,     // the dynamic shared memory window does not start on a 1 KB boundary
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -193,9 +194,10 @@ __device__ __forceinline__ void tma_store_wait_all() {
 __device__ __forceinline__ void tma_store_wait_read_all() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
-// all but the most recent group have finished reading their shared-memory source
-__device__ __forceinline__ void tma_store_wait_read_all_but_one() {
-  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+// all but the N most recent groups have finished reading their shared-memory source
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read_all_but() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 
 // ----------------------------------------------------------------------------------------------
