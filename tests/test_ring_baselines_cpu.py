@@ -45,3 +45,88 @@ def test_baselines_world4(kind, causal):
     for r in range(4):
         assert isinstance(ret[r], float), ret[r]
         assert ret[r] < 2e-4, (r, ret[r])
+
+
+def _dense_packed(q, k, v, d_o, cu, causal):
+    """Dense oracle of a packed batch: every sequence on its own."""
+    from ultraattn_b200 import patterns as P
+    pat = P.causal(1) if causal else P.full(1)
+    outs = [P.dense_attention_with_grads(*(t[None, a:b] for t in (q, k, v, d_o)), pat)
+            for a, b in zip(cu[:-1], cu[1:])]
+    return [torch.cat([o[i][0] for o in outs], dim=0) for i in (0, 2, 3, 4)]
+
+
+def _varlen_worker(rank, world, port, kind, causal, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ultraattn_b200 import parallel as PL
+        H, D = 2, 16
+        cu = [0, 64, 64, 192, 224]          # lengths 64, 0, 128, 32
+        g = torch.Generator().manual_seed(3)
+        q, k, v, d_o = (torch.randn(cu[-1], H, D, generator=g) for _ in range(4))
+        sh = lambda t: PL.shard_packed(t, cu, rank, world, kind)[0]
+        local_cu = PL.shard_packed(q, cu, rank, world, kind)[1]
+        ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
+        fn = {"ring": PL.ring_flash_attn_varlen_func, "zigzag": PL.zigzag_ring_flash_attn_varlen_func}[kind]
+        o = fn(ql, kl, vl, local_cu, max(b - a for a, b in zip(local_cu[:-1], local_cu[1:])), causal=causal)
+        o.backward(sh(d_o))
+        # the kv-packed form must give the same output
+        kvp = getattr(PL, fn.__name__.replace("_func", "_kvpacked_func"))
+        o2 = kvp(ql.detach(), torch.stack([kl.detach(), vl.detach()], dim=1), local_cu, None, causal=causal)
+        o_ref, dq, dk, dv = _dense_packed(q, k, v, d_o, cu, causal)
+        ret[rank] = max((o - sh(o_ref)).abs().max().item(), (ql.grad - sh(dq)).abs().max().item(),
+                        (kl.grad - sh(dk)).abs().max().item(), (vl.grad - sh(dv)).abs().max().item(),
+                        (o2 - o.detach()).abs().max().item())
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("kind,causal", [("ring", True), ("ring", False), ("zigzag", True)])
+def test_varlen_baselines_world2(kind, causal):
+    port = 29700 + (os.getpid() + hash(kind)) % 90
+    ret = mp.Manager().dict()
+    mp.spawn(_varlen_worker, args=(2, port, kind, causal, ret), nprocs=2, join=True)
+    for r in range(2):
+        assert isinstance(ret[r], float), ret[r]
+        assert ret[r] < 2e-4, (r, ret[r])
+
+
+def _hierarchy_worker(rank, world, port, causal, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ultraattn_b200 import parallel as PL, patterns as P
+        S, H, D = 256, 2, 16
+        g = torch.Generator().manual_seed(4)
+        q, k, v, d_o = (torch.randn(1, S, H, D, generator=g) for _ in range(4))
+        kind = "zigzag" if causal else "ring"
+        sh = lambda t: PL.shard_sequence(t, rank, world, kind)
+        groups = PL.create_hierarchy_groups(tasks_per_node=2)          # 2 nodes x 2 devices
+        ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
+        o = PL.hierarchy_attn_func(ql, kl, vl, causal=causal, groups=groups)
+        o.backward(sh(d_o))
+        pat = P.causal(1) if causal else P.full(1)
+        o_ref, _, dq, dk, dv = P.dense_attention_with_grads(q, k, v, d_o, pat)
+        ret[rank] = max((o - sh(o_ref)).abs().max().item(), (ql.grad - sh(dq)).abs().max().item(),
+                        (kl.grad - sh(dk)).abs().max().item(), (vl.grad - sh(dv)).abs().max().item())
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_two_level_ring_2x2(causal):
+    port = 29600 + (os.getpid() + int(causal)) % 90
+    ret = mp.Manager().dict()
+    mp.spawn(_hierarchy_worker, args=(4, port, causal, ret), nprocs=4, join=True)
+    for r in range(4):
+        assert isinstance(ret[r], float), ret[r]
+        assert ret[r] < 2e-4, (r, ret[r])

@@ -1,6 +1,11 @@
 from .comm import A2AComm, PROC_INFO, RingComm, get_proc_info, initialize_distribution
+from .hierarchy import create_hierarchy_groups, hierarchy_attn_func
 from .ring import (deepspeed_ulysses_attn_func, ring_backward, ring_flash_attn_func,
-                   ring_flash_attn_kvpacked_func, ring_flash_attn_qkvpacked_func, ring_forward,
-                   shard_sequence, stripe_flash_attn_func, stripe_flash_attn_kvpacked_func,
+                   ring_flash_attn_kvpacked_func, ring_flash_attn_qkvpacked_func,
+                   ring_flash_attn_varlen_func, ring_flash_attn_varlen_kvpacked_func,
+                   ring_flash_attn_varlen_qkvpacked_func, ring_forward, shard_packed, shard_sequence,
+                   stripe_flash_attn_func, stripe_flash_attn_kvpacked_func,
                    stripe_flash_attn_qkvpacked_func, zigzag_ring_flash_attn_func,
-                   zigzag_ring_flash_attn_kvpacked_func, zigzag_ring_flash_attn_qkvpacked_func)
+                   zigzag_ring_flash_attn_kvpacked_func, zigzag_ring_flash_attn_qkvpacked_func,
+                   zigzag_ring_flash_attn_varlen_func, zigzag_ring_flash_attn_varlen_kvpacked_func,
+                   zigzag_ring_flash_attn_varlen_qkvpacked_func)

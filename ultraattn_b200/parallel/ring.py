@@ -11,7 +11,7 @@ slicing of Q / K: the kernels take the diagonal offset of the causal mask as a p
 """
 from __future__ import annotations
 
-from typing import Optional
+import math
 
 import torch
 import torch.distributed as dist
@@ -21,35 +21,51 @@ from ..ops import elementwise as E
 from .comm import A2AComm, RingComm
 
 
-# per-step work: list of (q_start, q_len, [(k_start, k_len, causal, diag), ...]) or None to skip
-def _ring_rule(step, rank, world, S, causal):
+# A rule maps (ring position of the rank whose K/V block is held, own ring position, shard length)
+# to this step's work: a list of (q_start, q_len, [(k_start, k_len, causal, diag), ...]), or None
+# when the block is invisible. Rules depend on positions only, never on the step number, so the
+# same rules serve the flat ring and the two-level ring (which visits the blocks in another order).
+def _ring_rule(src, rank, S, causal):
     if not causal:
         return [(0, S, [(0, S, False, 0)])]
-    if step == 0:
+    if src == rank:
         return [(0, S, [(0, S, True, 0)])]
-    if step <= rank:
+    if src < rank:
         return [(0, S, [(0, S, False, 0)])]
     return None
 
 
-def _zigzag_rule(step, rank, world, S, causal):
+def _zigzag_rule(src, rank, S, causal):
     assert causal, "zigzag sharding is defined for causal attention"
     c = S // 2
-    if step == 0:
+    if src == rank:
         return [(0, c, [(0, c, True, 0)]), (c, c, [(0, c, False, 0), (c, c, True, 0)])]
-    if step <= rank:
+    if src < rank:
         return [(0, S, [(0, c, False, 0)])]
     return [(c, c, [(0, S, False, 0)])]
 
 
-def _stripe_rule(step, rank, world, S, causal):
+def _stripe_rule(src, rank, S, causal):
     assert causal, "striped sharding is defined for causal attention"
-    # token t of the shard is global token t * world + rank; the K/V at this step come from rank
-    # (rank - step) % world: visible iff k_global <= q_global
-    return [(0, S, [(0, S, True, 0 if step <= rank else -1)])]
+    # token t of a shard is global token t * world + position: a key of rank src is visible to
+    # the query with the same index iff src <= rank, otherwise only to later queries
+    return [(0, S, [(0, S, True, 0 if src <= rank else -1)])]
 
 
 _RULES = {"ring": _ring_rule, "zigzag": _zigzag_rule, "stripe": _stripe_rule}
+_NAMES = {"ring": "ring_flash_attn", "zigzag": "zigzag_ring_flash_attn", "stripe": "stripe_flash_attn"}
+
+
+def _work(kind, src, rank, bounds, causal):
+    """The rule applied to every packed sequence ((start, end) pairs of this rank's shard)."""
+    out = []
+    for a, b in bounds:
+        w = _RULES[kind](src, rank, b - a, causal) if b > a else None
+        for qs, ql, segs in w or []:
+            segs = [(a + ks, kl, c, d) for ks, kl, c, d in segs if kl > 0]
+            if ql > 0 and segs:
+                out.append((a + qs, ql, segs))
+    return out
 
 
 def _fwd_rows(work, started):
@@ -57,7 +73,7 @@ def _fwd_rows(work, started):
             for qs, ql, segs in work]
 
 
-def _bwd_cols(work, S):
+def _bwd_cols(work):
     """Transpose a step's work into key-major form."""
     by_kv = {}
     for qs, ql, segs in work:
@@ -66,31 +82,109 @@ def _bwd_cols(work, S):
     return [A.Col(0, ks, kl, tuple(segs), 0, ks) for (ks, kl), segs in sorted(by_kv.items())]
 
 
-def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None):
-    rule = _RULES[kind]
-    comm = RingComm(group)
+class _Route:
+    """The order in which the K/V blocks of all ranks visit this rank.
+
+    One level: a ring over ``group``. Two levels (``intra``, ``inter``): the block makes a full
+    tour of the intra-node ring, then one hop on the inter-node ring (to the same local rank of
+    the next node), and so on; only every ``len(intra)``-th hop crosses nodes. The ring position
+    ``inter_rank * len(intra) + intra_rank`` orders the sequence shards.
+    """
+
+    def __init__(self, group=None, intra=None, inter=None):
+        self.levels = [group] if intra is None else [intra, inter]
+        self.sizes = [dist.get_world_size(g) for g in self.levels]
+        self.pos = [dist.get_rank(g) for g in self.levels]
+        self.world = math.prod(self.sizes)
+        self.rank = self._flat(self.pos)
+        self.shift = [0] * len(self.levels)
+
+    def _flat(self, pos):
+        r, mul = 0, 1
+        for p, n in zip(pos, self.sizes):
+            r, mul = r + p * mul, mul * n
+        return r
+
+    def comms(self):
+        return [RingComm(g) for g in self.levels]
+
+    @property
+    def src(self) -> int:
+        """Ring position of the rank whose block is held now."""
+        return self._flat([(p - s) % n for p, s, n in zip(self.pos, self.shift, self.sizes)])
+
+    def level_after(self, step: int) -> int:
+        """The ring that the block takes after compute step ``step``."""
+        lvl, n = 0, step + 1
+        while lvl + 1 < len(self.sizes) and n % self.sizes[lvl] == 0:
+            n //= self.sizes[lvl]
+            lvl += 1
+        return lvl
+
+    def advance(self, lvl: int) -> None:
+        self.shift[lvl] = (self.shift[lvl] + 1) % self.sizes[lvl]
+
+    def send_home(self, tensors):
+        """Return travelling buffers to the ranks whose blocks they belong to: one exchange per
+        level, to the position ``shift`` places back."""
+        for lvl, g in enumerate(self.levels):
+            s, n, p = self.shift[lvl], self.sizes[lvl], self.pos[lvl]
+            if s == 0:
+                continue
+            glob = (lambda r: dist.get_global_rank(g, r)) if g is not None else (lambda r: r)
+            recv = [torch.empty_like(t) for t in tensors]
+            ops = []
+            for t, r in zip(tensors, recv):
+                ops.append(dist.P2POp(dist.isend, t, glob((p - s) % n), group=g))
+                ops.append(dist.P2POp(dist.irecv, r, glob((p + s) % n), group=g))
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+            tensors = recv
+        return tensors
+
+
+def _route(group):
+    if isinstance(group, _Route):
+        return group
+    if isinstance(group, dict):
+        return _Route(intra=group["intra"], inter=group["inter"])
+    return _Route(group)
+
+
+def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None, bounds=None):
+    """``group``: a process group (flat ring) or ``{'intra': pg, 'inter': pg}`` (two-level ring).
+    ``bounds``: (start, end) of every packed sequence in this rank's shard; default one sequence."""
+    route = _route(group)
+    comms = route.comms()
+    k, v = k.contiguous(), v.contiguous()        # they are sent as whole messages
     S = q.shape[1]
+    bounds = bounds or [(0, S)]
     o = torch.zeros_like(q)
     lse = torch.full((q.shape[0], q.shape[2], S), float("-inf"), dtype=torch.float32, device=q.device)
     started = False
-    for step in range(comm.world):
-        if step + 1 != comm.world:
-            nk, nv = comm.send_recv(k), comm.send_recv(v)
-            comm.commit()
-        work = rule(step, comm.rank, comm.world, S, causal)
+    for step in range(route.world):
+        last = step + 1 == route.world
+        if not last:
+            lvl = route.level_after(step)
+            nk, nv = comms[lvl].send_recv(k), comms[lvl].send_recv(v)
+            comms[lvl].commit()
+        work = _work(kind, route.src, route.rank, bounds, causal)
         if work:
             A.attn_fwd([q], [k], [v], [(o, lse)], A.FwdPlan(_fwd_rows(work, started), q.device), softmax_scale)
             started = True
-        if step + 1 != comm.world:
-            comm.wait()
+        if not last:
+            comms[lvl].wait()
+            route.advance(lvl)
             k, v = nk, nv
     return o, lse
 
 
-def ring_backward(d_o, q, k, v, o, lse, group, kind: str, causal: bool, softmax_scale=None):
-    rule = _RULES[kind]
-    kv_comm, g_comm = RingComm(group), RingComm(group)
+def ring_backward(d_o, q, k, v, o, lse, group, kind: str, causal: bool, softmax_scale=None, bounds=None):
+    route = _route(group)
+    kv_comms, g_comms = route.comms(), route.comms()
+    k, v = k.contiguous(), v.contiguous()
     B, S, H, D = q.shape
+    bounds = bounds or [(0, S)]
     dvec = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
     for b in range(B):
         E.rowdot(o[b], d_o[b], dvec[b])
@@ -98,91 +192,119 @@ def ring_backward(d_o, q, k, v, o, lse, group, kind: str, causal: bool, softmax_
     dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
     dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
     side = A.BwdQSide(q, d_o, lse, dvec, dq)
-    for step in range(kv_comm.world):
-        last = step + 1 == kv_comm.world
+    for step in range(route.world):
+        last = step + 1 == route.world
         if not last:
-            nk, nv = kv_comm.send_recv(k), kv_comm.send_recv(v)
-            kv_comm.commit()
-        work = rule(step, kv_comm.rank, kv_comm.world, S, causal)
+            lvl = route.level_after(step)
+            nk, nv = kv_comms[lvl].send_recv(k), kv_comms[lvl].send_recv(v)
+            kv_comms[lvl].commit()
+        work = _work(kind, route.src, route.rank, bounds, causal)
         if work:
-            A.attn_bwd([side], [k], [v], [A.BwdKvOut(dk, dv)], A.BwdPlan(_bwd_cols(work, S), q.device),
+            A.attn_bwd([side], [k], [v], [A.BwdKvOut(dk, dv)], A.BwdPlan(_bwd_cols(work), q.device),
                        softmax_scale)
-        # the gradient buffers travel with their K/V block; after the last step one more hop
-        # brings them home
-        ndk, ndv = g_comm.send_recv(dk), g_comm.send_recv(dv)
-        g_comm.commit()
         if not last:
-            kv_comm.wait()
-            k, v = nk, nv
-        g_comm.wait()
-        dk, dv = ndk, ndv
+            # the gradient buffers travel with their K/V block
+            ndk, ndv = g_comms[lvl].send_recv(dk), g_comms[lvl].send_recv(dv)
+            g_comms[lvl].commit()
+            kv_comms[lvl].wait()
+            g_comms[lvl].wait()
+            route.advance(lvl)
+            k, v, dk, dv = nk, nv, ndk, ndv
+    dk, dv = route.send_home([dk, dv])
     return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
 
 
 class _RingFunc(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, softmax_scale, causal, group, kind):
-        o, lse = ring_forward(q, k, v, group, kind, causal, softmax_scale)
+    def forward(ctx, q, k, v, softmax_scale, causal, group, kind, bounds=None):
+        o, lse = ring_forward(q, k, v, group, kind, causal, softmax_scale, bounds)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.args = (softmax_scale, causal, group, kind)
+        ctx.args = (softmax_scale, causal, group, kind, bounds)
         return o, lse
 
     @staticmethod
     def backward(ctx, d_o, _dlse):
         q, k, v, o, lse = ctx.saved_tensors
-        scale, causal, group, kind = ctx.args
-        dq, dk, dv = ring_backward(d_o.contiguous(), q, k, v, o, lse, group, kind, causal, scale)
-        return dq, dk, dv, None, None, None, None
+        scale, causal, group, kind, bounds = ctx.args
+        dq, dk, dv = ring_backward(d_o.contiguous(), q, k, v, o, lse, group, kind, causal, scale, bounds)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def _check_unsupported(dropout_p, alibi_slopes, window_size):
+    assert dropout_p == 0.0 and alibi_slopes is None and tuple(window_size) == (-1, -1), \
+        "dropout, alibi and sliding windows are not part of these baselines"
 
 
 def _make_func(kind: str):
     def func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
              alibi_slopes=None, deterministic=False, return_attn_probs=False, group=None,
              PROC_INFO=None, opt=False):
-        assert dropout_p == 0.0 and alibi_slopes is None and tuple(window_size) == (-1, -1), \
-            "dropout, alibi and sliding windows are not part of these baselines"
+        _check_unsupported(dropout_p, alibi_slopes, window_size)
         o, lse = _RingFunc.apply(q, k, v, softmax_scale, causal, group, kind)
         return (o, lse, None) if return_attn_probs else o
-    func.__name__ = f"{kind}_flash_attn_func"
+    func.__name__ = _NAMES[kind] + "_func"
     func.__doc__ = (f"{kind} context-parallel attention: q, k, v are this rank's shard "
-                    "[batch, tokens, heads, head_dim]; same signature as the reference's function.")
+                    "[batch, tokens, heads, head_dim]; same signature as the reference's function. "
+                    "``group`` may also be {'intra': pg, 'inter': pg} for the two-level ring.")
     return func
+
+
+def _make_varlen_func(kind: str):
+    def func(q, k, v, cu_seqlens, max_seqlen=None, dropout_p=0.0, softmax_scale=None, causal=False,
+             window_size=(-1, -1), alibi_slopes=None, deterministic=False, return_attn_probs=False,
+             group=None):
+        _check_unsupported(dropout_p, alibi_slopes, window_size)
+        cu = [int(x) for x in cu_seqlens]
+        bounds = list(zip(cu[:-1], cu[1:]))
+        o, lse = _RingFunc.apply(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), softmax_scale, causal,
+                                 group, kind, bounds)
+        o = o.squeeze(0)
+        return (o, lse.squeeze(0), None) if return_attn_probs else o
+    func.__name__ = _NAMES[kind] + "_varlen_func"
+    func.__doc__ = (
+        f"{kind} context-parallel attention over a packed batch. q, k, v: ``[tokens, heads, head_dim]``, "
+        "this rank's shard of every sequence one after the other; ``cu_seqlens`` are the boundaries "
+        "of those shards (the same on every rank: each sequence is cut evenly, "
+        "ring_flash_attn/ring_flash_attn_varlen.py:24-79; zigzag shards hold chunks r and 2W-1-r of "
+        "each sequence, zigzag_ring_flash_attn_varlen.py:23-56). Tokens attend only their own "
+        "sequence. ``max_seqlen`` is accepted for signature parity and not needed: the kernels take "
+        "(query block, key segment) lists, so the returned lse is already packed ``[heads, tokens]`` "
+        "and no flatten / unflatten pass exists.")
+    return func
+
+
+def _packed_variants(func, varlen: bool = False):
+    """The (qkv-packed, kv-packed) forms of an attention function: q, k, v stacked along a new
+    dimension right after the token dimension."""
+    dim = 1 if varlen else 2
+
+    def qkvpacked(qkv, *a, **kw):
+        q, k, v = qkv.unbind(dim)
+        return func(q, k, v, *a, **kw)
+
+    def kvpacked(q, kv, *a, **kw):
+        k, v = kv.unbind(dim)
+        return func(q, k, v, *a, **kw)
+
+    base = func.__name__[:-len("_func")]
+    qkvpacked.__name__, kvpacked.__name__ = base + "_qkvpacked_func", base + "_kvpacked_func"
+    return qkvpacked, kvpacked
 
 
 ring_flash_attn_func = _make_func("ring")
 zigzag_ring_flash_attn_func = _make_func("zigzag")
 stripe_flash_attn_func = _make_func("stripe")
+ring_flash_attn_varlen_func = _make_varlen_func("ring")
+zigzag_ring_flash_attn_varlen_func = _make_varlen_func("zigzag")
 
-
-def _packed(func, n):
-    def f(packed, *a, **kw):
-        parts = packed.unbind(dim=2)
-        return func(*parts, *a, **kw) if n == 3 else None
-    return f
-
-
-def ring_flash_attn_qkvpacked_func(qkv, *a, **kw):
-    return ring_flash_attn_func(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], *a, **kw)
-
-
-def ring_flash_attn_kvpacked_func(q, kv, *a, **kw):
-    return ring_flash_attn_func(q, kv[:, :, 0], kv[:, :, 1], *a, **kw)
-
-
-def zigzag_ring_flash_attn_qkvpacked_func(qkv, *a, **kw):
-    return zigzag_ring_flash_attn_func(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], *a, **kw)
-
-
-def zigzag_ring_flash_attn_kvpacked_func(q, kv, *a, **kw):
-    return zigzag_ring_flash_attn_func(q, kv[:, :, 0], kv[:, :, 1], *a, **kw)
-
-
-def stripe_flash_attn_qkvpacked_func(qkv, *a, **kw):
-    return stripe_flash_attn_func(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], *a, **kw)
-
-
-def stripe_flash_attn_kvpacked_func(q, kv, *a, **kw):
-    return stripe_flash_attn_func(q, kv[:, :, 0], kv[:, :, 1], *a, **kw)
+ring_flash_attn_qkvpacked_func, ring_flash_attn_kvpacked_func = _packed_variants(ring_flash_attn_func)
+zigzag_ring_flash_attn_qkvpacked_func, zigzag_ring_flash_attn_kvpacked_func = \
+    _packed_variants(zigzag_ring_flash_attn_func)
+stripe_flash_attn_qkvpacked_func, stripe_flash_attn_kvpacked_func = _packed_variants(stripe_flash_attn_func)
+ring_flash_attn_varlen_qkvpacked_func, ring_flash_attn_varlen_kvpacked_func = \
+    _packed_variants(ring_flash_attn_varlen_func, varlen=True)
+zigzag_ring_flash_attn_varlen_qkvpacked_func, zigzag_ring_flash_attn_varlen_kvpacked_func = \
+    _packed_variants(zigzag_ring_flash_attn_varlen_func, varlen=True)
 
 
 # -------------------------------------------------------------------------------------------------
@@ -199,6 +321,18 @@ def shard_sequence(x: torch.Tensor, rank: int, world: int, kind: str, dim: int =
         idx = torch.arange(rank, x.shape[dim], world, device=x.device)
         return x.index_select(dim, idx).contiguous()
     raise ValueError(kind)
+
+
+def shard_packed(x: torch.Tensor, cu_seqlens, rank: int, world: int, kind: str):
+    """Shard a packed batch ``[tokens, ...]`` sequence by sequence; returns this rank's shard and
+    the boundaries of the sequences inside it (every sequence length must divide evenly: by
+    ``world`` for the ring, by ``2 * world`` for zigzag)."""
+    cu = [int(c) for c in cu_seqlens]
+    parts = [shard_sequence(x[a:b], rank, world, kind, dim=0) for a, b in zip(cu[:-1], cu[1:])]
+    local = [0]
+    for p in parts:
+        local.append(local[-1] + p.shape[0])
+    return torch.cat(parts, dim=0).contiguous(), local
 
 
 # -------------------------------------------------------------------------------------------------
