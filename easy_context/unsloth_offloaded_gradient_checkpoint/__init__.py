@@ -1,0 +1,3 @@
+"""Reference: easy_context/unsloth_offloaded_gradient_checkpoint/monkey_patch.py."""
+from ultraattn_b200.models.glue import (OffloadedCheckpoint,  # noqa: F401
+                                        apply_unsloth_offloaded_gradient_checkpoint_monkey_patch)

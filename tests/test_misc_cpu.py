@@ -128,3 +128,51 @@ def test_cluster_probe_local_and_sinfo_parsing():
     rows = cp.parse_sinfo("gpu* up 4 idle\ngpu* up 12 alloc\ncpu up 3 idle~\n")
     assert rows[0] == {"partition": "gpu", "avail": "up", "nodes": 4, "state": "idle"} and len(rows) == 3
     assert cp.main(["--hosts", "localhost", "--", "true"]) == 0
+
+
+def test_offloaded_checkpoint_matches_plain_backward():
+    """A layer run through OffloadedCheckpoint gives the gradients of the plain call."""
+    from easy_context.unsloth_offloaded_gradient_checkpoint import OffloadedCheckpoint
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(8, 8)
+    layer = lambda h, scale: torch.tanh(lin(h)) * scale
+    x = torch.randn(4, 8, requires_grad=True)
+    layer(x, 2.0).sum().backward()
+    gx, gw = x.grad.clone(), lin.weight.grad.clone()
+    x.grad = None
+    lin.weight.grad = None
+    OffloadedCheckpoint.apply(layer, x, 2.0).sum().backward()
+    assert torch.allclose(x.grad, gx) and torch.allclose(lin.weight.grad, gw)
+
+
+def test_hf_llama_with_offloaded_checkpoints_and_registered_attention():
+    """The reference's glue names on a tiny HuggingFace Llama: offloaded gradient checkpointing
+    reproduces the plain gradients; the family-name form of the monkey patch registers an
+    attention function."""
+    import easy_context
+    from transformers import AttentionInterface, LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=64)
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg).train()
+    ids = torch.randint(0, 64, (1, 16))
+    model(input_ids=ids, labels=ids).loss.backward()
+    ref = {n: p.grad.clone() for n, p in model.named_parameters()}
+    model.zero_grad()
+    from ultraattn_b200.models import glue
+    calls = []
+    orig = glue.OffloadedCheckpoint.forward
+    glue.OffloadedCheckpoint.forward = staticmethod(lambda ctx, *a: (calls.append(1), orig(ctx, *a))[1])
+    try:
+        easy_context.apply_unsloth_offloaded_gradient_checkpoint_monkey_patch(model)
+        model(input_ids=ids, labels=ids).loss.backward()
+    finally:
+        glue.OffloadedCheckpoint.forward = orig
+    assert len(calls) == cfg.num_hidden_layers
+    for n, p in model.named_parameters():
+        assert torch.allclose(p.grad, ref[n], atol=1e-6), n
+    name = easy_context.apply_seq_parallel_monkey_patch("zigzag_ring_attn", "llama")
+    assert name == "ultraattn_zigzag_ring_attn" and name in AttentionInterface().valid_keys()
+    assert easy_context.prepare_dataloader("zigzag_ring_attn", [1, 2]) == [1, 2]
+    d = easy_context.prepare_zigzag_ring_attn_inputs(torch.arange(8)[None], torch.arange(8)[None], None, 1, 2)
+    assert d["local_input_ids"].tolist() == [[2, 3, 4, 5]] and d["local_target_ids"] is None

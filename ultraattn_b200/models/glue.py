@@ -75,13 +75,130 @@ def make_attention_interface(seq_algo: str, group=None, runtime=None):
 
 
 def apply_seq_parallel_monkey_patch(seq_algo: str, model, group=None, runtime=None):
-    """Make ``model`` (a HuggingFace causal LM) use context-parallel attention. Returns the name
-    under which the attention function was registered."""
+    """Make ``model`` use context-parallel attention. ``model`` is a HuggingFace causal LM (or
+    its config), which is switched to the new attention function, or, as in the reference, the
+    family name ``"llama"`` / ``"mistral"``: the function is then only registered and models are
+    built with ``attn_implementation=<returned name>``. Returns the registered name."""
     if _KIND.get(seq_algo, seq_algo) is None:
         return None
     from transformers import AttentionInterface
     name = f"ultraattn_{seq_algo}"
     AttentionInterface.register(name, make_attention_interface(seq_algo, group, runtime))
+    if isinstance(model, str):
+        assert model in ("llama", "mistral"), f"Invalid model: {model}"
+        return name
     cfg = model if not hasattr(model, "config") else model.config
     cfg._attn_implementation = name
     return name
+
+
+# -------------------------------------------------------------------------------------------------
+# the reference's per-strategy names (easy_context/__init__.py:1-6)
+# -------------------------------------------------------------------------------------------------
+def prepare_zigzag_ring_attn_inputs(input_ids, position_ids, target_ids, rank, world_size, device=None):
+    """Reference: easy_context/zigzag_ring_attn/prepare_inputs.py:4-40 (rank r holds chunks r and
+    2W-1-r of the 2W chunks of the sequence)."""
+    return prepare_seq_parallel_inputs("zigzag_ring_attn", input_ids, position_ids, target_ids, rank,
+                                       world_size, device)
+
+
+def prepare_dist_flash_attn_inputs(input_ids, position_ids, target_ids, rank, world_size, device=None):
+    """Reference: easy_context/dist_flash_attn/prepare_input.py (contiguous chunks)."""
+    return prepare_seq_parallel_inputs("dist_flash_attn", input_ids, position_ids, target_ids, rank,
+                                       world_size, device)
+
+
+def prepare_dataloader(seq_algo: str, dataloader, accelerator=None):
+    """Reference: easy_context/__init__.py:44-48. Under data parallelism every rank reads its own
+    samples (``accelerator.prepare`` shards the loader); under sequence parallelism all ranks of
+    the group read the same sample and shard it with :func:`prepare_seq_parallel_inputs`."""
+    if _KIND.get(seq_algo, seq_algo) is None and accelerator is not None:
+        return accelerator.prepare(dataloader)
+    return dataloader
+
+
+def apply_zigzag_ring_attn_monkey_patch_llama(group=None):
+    return apply_seq_parallel_monkey_patch("zigzag_ring_attn", "llama", group)
+
+
+def apply_zigzag_ring_attn_monkey_patch_mistral(group=None):
+    return apply_seq_parallel_monkey_patch("zigzag_ring_attn", "mistral", group)
+
+
+def apply_dist_flash_attn_monkey_patch_llama(group=None):
+    return apply_seq_parallel_monkey_patch("dist_flash_attn", "llama", group)
+
+
+class OffloadedCheckpoint(torch.autograd.Function):
+    """Activation checkpoint whose saved input lives in pinned host memory (reference:
+    easy_context/unsloth_offloaded_gradient_checkpoint/monkey_patch.py:20-60). The copy out runs
+    on a side stream so the layer's forward does not wait for it; the backward brings the
+    input back, re-runs the layer with gradients enabled and back-propagates through it."""
+
+    @staticmethod
+    def forward(ctx, forward_function, hidden_states, *args):
+        if hidden_states.is_cuda:
+            host = torch.empty(hidden_states.shape, dtype=hidden_states.dtype, device="cpu", pin_memory=True)
+            side = _offload_stream(hidden_states.device)
+            side.wait_stream(torch.cuda.current_stream(hidden_states.device))
+            with torch.cuda.stream(side):
+                host.copy_(hidden_states, non_blocking=True)
+            hidden_states.record_stream(side)
+            ctx.copied = torch.cuda.Event()
+            ctx.copied.record(side)
+        else:
+            host, ctx.copied = hidden_states.detach().clone(), None
+        with torch.no_grad():
+            output = forward_function(hidden_states, *args)
+        ctx.host, ctx.device = host, hidden_states.device
+        ctx.forward_function, ctx.args = forward_function, args
+        return output
+
+    @staticmethod
+    def backward(ctx, *d_out):
+        if ctx.copied is not None:
+            ctx.copied.synchronize()
+        x = ctx.host.to(ctx.device, non_blocking=True).detach().requires_grad_(True)
+        with torch.enable_grad():
+            out = ctx.forward_function(x, *ctx.args)
+        outs = out if isinstance(out, (tuple, list)) else (out,)
+        pairs = [(o, g) for o, g in zip(outs, d_out) if isinstance(o, torch.Tensor) and o.requires_grad]
+        torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        return (None, x.grad) + (None,) * len(ctx.args)
+
+
+_offload_streams: dict = {}
+
+
+def _offload_stream(device):
+    if device not in _offload_streams:
+        _offload_streams[device] = torch.cuda.Stream(device)
+    return _offload_streams[device]
+
+
+def apply_unsloth_offloaded_gradient_checkpoint_monkey_patch(model=None):
+    """Make gradient checkpointing of HuggingFace models keep the checkpoints in host memory
+    (reference: easy_context/unsloth_offloaded_gradient_checkpoint/monkey_patch.py:63-94). With a
+    model, only that model is switched; without, every ``PreTrainedModel`` that enables gradient
+    checkpointing afterwards."""
+    def checkpoint(function, *args, **kwargs):
+        hidden, rest = args[0], args[1:]
+        fn = (lambda h, *a: function(h, *a, **kwargs)) if kwargs else function
+        return OffloadedCheckpoint.apply(fn, hidden, *rest)
+
+    if model is not None:
+        model.gradient_checkpointing_enable()
+        for m in model.modules():
+            if hasattr(m, "_gradient_checkpointing_func"):
+                m._gradient_checkpointing_func = checkpoint
+        return checkpoint
+    import transformers
+
+    def enable(self, gradient_checkpointing_kwargs=None):
+        if not self.supports_gradient_checkpointing:
+            raise ValueError(f"{type(self).__name__} does not support gradient checkpointing")
+        self._set_gradient_checkpointing(enable=True, gradient_checkpointing_func=checkpoint)
+        if getattr(self, "_hf_peft_config_loaded", False):
+            self.enable_input_require_grads()
+    transformers.modeling_utils.PreTrainedModel.gradient_checkpointing_enable = enable
+    return checkpoint
