@@ -1,8 +1,10 @@
 """Reference: orchestrated_attn/global_vars.py:1-17."""
 import torch
 
+from ultraattn_b200.parallel.communicator import CommRegistry
+
 FULL_DTYPE = torch.float32
-ncclcomm_dict: dict = {}
+ncclcomm_dict: CommRegistry = CommRegistry()      # communicators by tuple(ranks)
 cpu_group_dict: dict = {}
 streams: dict = {}
 _vars: dict = {}

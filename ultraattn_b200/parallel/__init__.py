@@ -1,4 +1,6 @@
 from .comm import A2AComm, PROC_INFO, RingComm, get_proc_info, initialize_distribution
+from .communicator import (CommRegistry, InterComm, InterComm_fused, IntraComm, IntraComm_fused,
+                           PyNcclCommunicator, StreamCommunicator)
 from .hierarchy import create_hierarchy_groups, hierarchy_attn_func
 from .ring import (deepspeed_ulysses_attn_func, ring_backward, ring_flash_attn_func,
                    ring_flash_attn_kvpacked_func, ring_flash_attn_qkvpacked_func,
