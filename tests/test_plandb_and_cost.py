@@ -83,3 +83,45 @@ def test_report_tables_from_profile_db(tmp_path):
     assert abs(r["speedup_vs_ring"] - 2.0) < 1e-9 and abs(r["speedup_vs_best_baseline"] - 0.8) < 1e-9
     assert report.main(["--db", str(tmp_path), "--csv", str(tmp_path / "out.csv")]) == 0
     assert (tmp_path / "out.csv").read_text().count("\n") == 2
+
+
+def test_sim_accuracy_and_e2e_rows(tmp_path, capsys):
+    """Predicted-vs-measured statistics (outlier share, R^2) and the layers x attention + constant
+    end-to-end table."""
+    import json
+    from ultraattn_b200.drivers import report
+    shape = "_shape_config={S=(524288, 524288)_Nh=(32, 32)_bs=1_D=128}_bsa_config={CP=(8, 1)_repr=[[2]]}"
+    prof = {}
+    for fob, (t_u, t_r) in {0: (0.10, 0.30), 1: (0.25, 0.50)}.items():
+        pre = f"fob={fob}_CP=(8, 1)" + shape
+        prof[pre + "_ablation=(w/o_kernel_tile,ILP)"] = {"hfu": 1.0, "time": f"{t_u:.3e}", "sim_time": f"{t_u * 1.1:.3e}"}
+        prof[pre + "_ring"] = {"hfu": 1.0, "time": f"{t_r:.3e}", "sim_time": f"{t_r * 2:.3e}"}
+    acc = report.sim_accuracy(prof, tolerance=0.3)
+    assert acc["n"] == 4 and acc["outlier_pct"] == 50.0 and acc["r2"] < 1.0
+    perfect = {k: dict(v, sim_time=v["time"]) for k, v in prof.items()}
+    assert report.sim_accuracy(perfect)["r2"] == 1.0 and report.sim_accuracy(perfect)["outlier_pct"] == 0.0
+    rows = report.e2e_rows(report.build_rows(prof), n_layers=4, time_wo_attn=0.1)
+    assert len(rows) == 1
+    assert abs(rows[0]["ultraattn"] - (4 * 0.35 + 0.1)) < 1e-9 and abs(rows[0]["ring"] - (4 * 0.8 + 0.1)) < 1e-9
+    assert abs(rows[0]["speedup_vs_best_baseline"] - 3.3 / 1.5) < 1e-9
+    (tmp_path / "inter_bsa_exe_plans_profile.json").write_text(json.dumps(prof))
+    assert report.main(["--db", str(tmp_path), "--sim-accuracy"]) == 0
+    assert json.loads(capsys.readouterr().out)["n"] == 4
+    assert report.main(["--db", str(tmp_path), "--e2e-layers", "4", "--e2e-const", "0.1"]) == 0
+
+
+def test_metrics_jsonl_and_roofline(tmp_path):
+    from ultraattn_b200.utils import metrics as M
+    peaks = {"bf16_tflops": 1000.0, "bf16_tflops_sustained": 500.0, "hbm_gbs": 6000.0}
+    r = M.roofline(flops_per_gpu=1e15, nvlink_bytes_per_gpu=77e9, seconds=4.0, peaks=peaks)
+    assert r["bound"] == "compute" and abs(r["target_s"] - 2.0) < 1e-9 and abs(r["fraction"] - 0.5) < 1e-9
+    r = M.roofline(1e12, 770e9, 2.0, peaks=peaks)
+    assert r["bound"] == "nvlink" and abs(r["fraction"] - 0.5) < 1e-9
+    (tmp_path / "p.json").write_text('{"bf16_tflops": 1600, "bf16_tflops_sustained": 1400, "hbm_gbs": 6400}')
+    assert M.load_peaks(str(tmp_path / "p.json"))["source"] == "measured"
+    log = M.MetricsLogger(str(tmp_path / "m" / "calls.jsonl"), config="strided", n_gpus=2)
+    log.log("fwd", 0.5, flops_per_gpu=3e14, pull_bytes=10, push_bytes=20)
+    log.log("barrier", 1e-5)
+    recs = M.read_jsonl(tmp_path / "m" / "calls.jsonl")
+    assert [x["name"] for x in recs] == ["fwd", "barrier"] and recs[0]["config"] == "strided"
+    assert recs[0]["nvlink_push_bytes"] == 20 and 0 < recs[0]["fraction"] < 1 and "fraction" not in recs[1]

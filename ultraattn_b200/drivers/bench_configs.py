@@ -73,7 +73,10 @@ def main() -> None:
     ap.add_argument("--paths", default="fused,nccl")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--scale", type=int, default=1, help="divide every sequence length (smoke runs)")
+    ap.add_argument("--metrics-jsonl", default=None, help="append one JSON object per measured call to this file")
     a = ap.parse_args()
+    from ..utils.metrics import MetricsLogger
+    metrics = MetricsLogger(a.metrics_jsonl) if a.metrics_jsonl else None
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
@@ -144,6 +147,9 @@ def main() -> None:
                                       "roofline_bound": "compute" if t_comp >= t_link else "nvlink",
                                       "fraction_of_roofline": round(max(t_comp, t_link) * 1e3 / ms, 3),
                                       "peak_tflops_of_measured": peak}), flush=True)
+                    if metrics is not None:
+                        metrics.log(name, ms * 1e-3, flops_per_gpu=flops / world, pull_bytes=int(nvl_bytes),
+                                    path=path if world > 1 else "local", n_gpus=world, S=S)
             except Exception as e:  # noqa: BLE001
                 if rank == 0:
                     print(json.dumps({"config": name, "path": path, "n_gpus": world, "error": f"{type(e).__name__}: {e}"}),

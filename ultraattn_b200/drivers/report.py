@@ -74,6 +74,54 @@ def build_rows(profile: dict) -> list:
     return rows
 
 
+def sim_accuracy(profile: dict, tolerance: float = 0.3) -> dict:
+    """How well the planner's predicted time (``sim_time``) matches the measured ``time`` over all
+    entries that carry both: share of outliers beyond ``tolerance`` relative error (the reference
+    uses 0.3 at the intra level and 0.5 at the inter level) and R^2 of predicted against measured
+    (reference: plot/sim_accuracy.py:26-66)."""
+    pairs = []
+    for entry in profile.values():
+        if isinstance(entry, dict) and "sim_time" in entry and "time" in entry:
+            t, s = float(entry["time"]), float(entry["sim_time"])
+            if t > 0 and s > 0:
+                pairs.append((t, s))
+    if not pairs:
+        return {"n": 0, "outlier_pct": 0.0, "r2": float("nan"), "mean_abs_rel_err": float("nan")}
+    rel = [abs(s - t) / t for t, s in pairs]
+    mean_t = sum(t for t, _ in pairs) / len(pairs)
+    ss_res = sum((t - s) ** 2 for t, s in pairs)
+    ss_tot = sum((t - mean_t) ** 2 for t, _ in pairs)
+    return {"n": len(pairs), "outlier_pct": 100.0 * sum(r > tolerance for r in rel) / len(pairs),
+            "r2": 1.0 - ss_res / ss_tot if ss_tot > 0 else float("nan"),
+            "mean_abs_rel_err": sum(rel) / len(rel)}
+
+
+def e2e_rows(rows: list, n_layers: int, time_wo_attn: float) -> list:
+    """End-to-end step time the way the reference's figure derives it (plot/e2e_pick.py:144-177):
+    forward + backward attention time of one layer times ``n_layers`` plus a constant for
+    everything else. Rows are joined on (CP, shape, pattern); returns one row per configuration
+    with the baselines' and UltraAttn's step time and the speed-up over the best baseline."""
+    by_cfg: dict = {}
+    for r in rows:
+        cfg = re.sub(r"^fob=\d_", "", r["key"])
+        by_cfg.setdefault(cfg, {})[r["fob"]] = r
+    out = []
+    for cfg, fobs in sorted(by_cfg.items()):
+        if "0" not in fobs:
+            continue
+        def total(col):
+            ts = [fobs[f].get(col) for f in sorted(fobs)]
+            return None if any(t is None for t in ts) else n_layers * sum(ts) + time_wo_attn
+        row = {"key": cfg, "CP": fobs["0"]["CP"], "shape": fobs["0"]["shape"]}
+        for col in ("ring", "zigzag", "stripe", "ultraattn"):
+            row[col] = total(col)
+        base = [row[c] for c in ("ring", "zigzag", "stripe") if row[c] is not None]
+        if base and row["ultraattn"]:
+            row["speedup_vs_best_baseline"] = min(base) / row["ultraattn"]
+        out.append(row)
+    return out
+
+
 COLS = ["fob", "CP", "shape", "ring", "zigzag", "stripe", "node_tile", "node_device_tile", "kernel_tile",
         "ultraattn", "speedup_vs_ring", "speedup_vs_best_baseline"]
 
@@ -91,12 +139,28 @@ def main(argv=None) -> int:
     ap.add_argument("--db", required=True, help="database/<cluster>/<platform> directory")
     ap.add_argument("--level", default="inter", choices=["intra", "inter"])
     ap.add_argument("--csv", default=None)
+    ap.add_argument("--sim-accuracy", action="store_true",
+                    help="print predicted-vs-measured statistics instead of the table")
+    ap.add_argument("--e2e-layers", type=int, default=0,
+                    help="print end-to-end step times: layers x (fwd + bwd) + --e2e-const")
+    ap.add_argument("--e2e-const", type=float, default=0.0, help="seconds per step outside attention")
     a = ap.parse_args(argv)
     path = Path(a.db) / f"{a.level}_bsa_exe_plans_profile.json"
     if not path.exists():
         print(f"no profile file {path}", file=sys.stderr)
         return 1
-    rows = build_rows(json.loads(path.read_text()))
+    profile = json.loads(path.read_text())
+    if a.sim_accuracy:
+        print(json.dumps(sim_accuracy(profile, 0.3 if a.level == "intra" else 0.5)))
+        return 0
+    rows = build_rows(profile)
+    if a.e2e_layers:
+        cols = ["CP", "shape", "ring", "zigzag", "stripe", "ultraattn", "speedup_vs_best_baseline"]
+        print("| " + " | ".join(cols) + " |")
+        print("|" + "---|" * len(cols))
+        for r in e2e_rows(rows, a.e2e_layers, a.e2e_const):
+            print("| " + " | ".join(_fmt(r.get(c)) for c in cols) + " |")
+        return 0
     print("| " + " | ".join(COLS) + " |")
     print("|" + "---|" * len(COLS))
     for r in rows:
