@@ -79,9 +79,14 @@ class ContextParallelAttention:
                  group=None, device: Optional[torch.device] = None, path: str = "fused",
                  n_kv_heads: Optional[int] = None, batch: int = 1, allocation: str = "ilp",
                  plan_time_limit: float = 20.0, dtype=torch.bfloat16, cmap=None,
-                 nvls_min_consumers: int = 2, plan=None):
+                 nvls_min_consumers: int = 2, plan=None, local_groups: bool = False):
         """``plan``: an earlier runtime's ``(table, cmap)`` to reuse instead of solving the
-        allocation again (fused path; e.g. a second runtime for a different number of heads)."""
+        allocation again (fused path; e.g. a second runtime for a different number of heads).
+        ``local_groups``: create the internal process groups with only the members of ``group``
+        taking part (needed when ``group`` is a strict subset of the job, as after a rank left)."""
+        self._ctor = dict(seq_len=seq_len, n_heads=n_heads, head_dim=head_dim, device=device, path=path,
+                          n_kv_heads=n_kv_heads, batch=batch, allocation=allocation,
+                          plan_time_limit=plan_time_limit, dtype=dtype, nvls_min_consumers=nvls_min_consumers)
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
@@ -112,12 +117,21 @@ class ContextParallelAttention:
             dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, 0), group=self.group)
             pf, pb = box[0]
             ranks = [dist.get_global_rank(self.group, r) for r in range(self.world)]
-            duplex = (dist.new_group(ranks), dist.new_group(ranks))
+            duplex = tuple(dist.new_group(ranks, use_local_synchronization=local_groups) for _ in range(2))
             self.impl = PlanExecutor(pf, pb, group=self.group, device=self.device, p2p_groups=duplex)
             self.table = np.asarray(pf.allocation.table)
             self.cmap = np.asarray(pf.allocation.cmap)
         else:
             raise ValueError(f"unknown path {path!r}")
+
+    def replan(self, group, **overrides) -> "ContextParallelAttention":
+        """A runtime for the same problem over another set of ranks, e.g. the survivors after a
+        rank left between two steps: the allocation is solved again for the new world size (plans
+        are cheap at these sizes) and every member then passes its new, larger shard. Collective
+        over ``group`` only. The reference has no recovery path (a failed task ends the job,
+        scripts/runtime/wrapper_bx.sh:19); this is the building block for one."""
+        kw = dict(self._ctor, **overrides)
+        return ContextParallelAttention(self.pattern, group=group, local_groups=True, **kw)
 
     def forward(self, q, k, v, softmax_scale=None):
         return self.impl.forward(q, k, v, softmax_scale)
