@@ -1,7 +1,12 @@
 """Block types and small utilities (reference: search_algo/utils.py)."""
 from ultraattn_b200.patterns.blocks import Block_Comp_Volume, Block_Table_Type, Block_Type  # noqa: F401
-from ultraattn_b200.planner.cost import (convert_profile_data_to_comm_map,  # noqa: F401
-                                         convert_profile_data_to_map)
+from ultraattn_b200.drivers.arguments import parse_args  # noqa: F401
+from ultraattn_b200.planner.cost import (convert_node_profile_data_to_comp_map,  # noqa: F401
+                                         convert_profile_data_to_comm_map, convert_profile_data_to_map)
+from ultraattn_b200.utils.misc import (Block_Attention_Config, all_wait_main_stream,  # noqa: F401
+                                       closest_fraction, combine_list_to_0,
+                                       convert_block_table_to_value, filter_kwargs,
+                                       find_file_with_regex, get_factors, main_stream_wait_all)
 from ultraattn_b200.utils.misc import (FinitePriorityQueue, calc_flops, calc_table_comp_relative_time,  # noqa: F401
                                        get_block_table_type, print_rank_0, report_memory,
                                        unique_list, use_all_cpus)

@@ -1,5 +1,6 @@
 """Utilities, configuration, data carriers and model glue (CPU)."""
 import numpy as np
+import pytest
 import torch
 
 from ultraattn_b200 import patterns as P
@@ -176,3 +177,67 @@ def test_hf_llama_with_offloaded_checkpoints_and_registered_attention():
     assert easy_context.prepare_dataloader("zigzag_ring_attn", [1, 2]) == [1, 2]
     d = easy_context.prepare_zigzag_ring_attn_inputs(torch.arange(8)[None], torch.arange(8)[None], None, 1, 2)
     assert d["local_input_ids"].tolist() == [[2, 3, 4, 5]] and d["local_target_ids"] is None
+
+
+def test_reference_helper_names_and_legacy_log_roundtrip(tmp_path):
+    """Helper names of the reference's search_algo modules, and the legacy node-profile log:
+    written by format_node_profile_lines, parsed back by convert_node_profile_data_to_comp_map."""
+    import search_algo.bsa_utils as BU
+    import search_algo.exp_configs as EC
+    import search_algo.utils as U
+    import search_algo.workload_partition as WP
+    from ultraattn_b200.planner.cost import format_node_profile_lines
+    assert U.get_factors(12) == [1, 2, 3, 4, 6, 12] and str(U.closest_fraction(0.3333, 8)) == "1/3"
+    assert U.combine_list_to_0([1, 2], [2, 3]) == [1, 2, 3]
+    assert U.filter_kwargs(lambda a, b=1: 0, {"a": 1, "c": 2}) == {"a": 1}
+    bac = U.Block_Attention_Config.from_causal(2, 4, [0, 0, 1, 1])
+    assert bac.block_table_value.tolist() == [[2, 0, 0, 0], [1, 2, 0, 0], [1, 1, 2, 0], [1, 1, 1, 2]]
+    al = WP.Quad_LP_GUROBI_from_block_config(bac, fob=0, hierarchy=1, ParD=4, time_limit=3.0)
+    assert al["table"].shape == (4, 4) and (al["table"][np.tril_indices(4)] >= 0).all()
+    assert [c.fob for c in EC.get_exp_train_configs()] == [0, 1] and EC.get_exp_configs()[0].plan_type == "manual"
+    # compute-balanced allocation of dense causal on 4 ranks: perfectly even, unlike the row owner
+    from ultraattn_b200 import patterns as P
+    from ultraattn_b200.patterns.blocks import BSA_Config
+    cfg = BSA_Config(None, None, {"bsa_repr": P.causal(1), "CP": (4, 1)})
+    bal, naive = WP.comp_balance_allocate_strategy(cfg, fob=0), WP.naive_allocate_strategy(cfg, fob=0, ParD=8)
+    assert bal.comp_max < naive.comp_max and bal.comp_max == (28 + 8 * 0.5) / 4
+    # FULL node tiles: profile key -> plan key / kernel-tile plan
+    pre = "fob=1_CP=(8, 1)_shape_config={S=(4096, 16384)_Nh=(1, 1)_bs=1_D=128}_bsa_config={CP=(8, 1)_repr=[[1]]}"
+    assert BU.convert_intra_profile_key_to_exe_key_or_plan(pre + "_ablation=(w/o_kernel_tile,Y=2,X=4,dim=0)") == \
+        "fob=1_CP=(8, 1)_shape_config=full_ablation=(Y=2,X=4,dim=0)"
+    fp = BU.convert_intra_profile_key_to_exe_key_or_plan(pre + "_ablation=(w_kernel_tile,Y=4,X=2,dim=0)")
+    assert (fp.Y, fp.X, fp.fob) == (4, 2, 1)
+    assert BU.convert_intra_profile_key_to_exe_key_or_plan(pre + "_ablation=(w_kernel_tile,ILP)").endswith("ILP)")
+    # legacy log
+    lines = []
+    for fob in (0, 1):
+        lines += format_node_profile_lines(fob, (1, 8), (2048, 2048), (1, 1), 1, 128, False, {
+            "orchestrated_attn_func": [(1.0, 3e-4 * (fob + 1)), (1.2, 2e-4 * (fob + 1))],
+            "orchestrated_attn_func fused": [(3.0, 1e-4 * (fob + 1))],
+            "ring_flash_attn_func": [(9.0, 1e-6)]})
+    log = tmp_path / "node.log"
+    log.write_text("\n".join(lines) + "\n")
+    m = U.convert_node_profile_data_to_comp_map(str(log), 8)
+    key = ((1, 8), (256, 256), (1, 1), 1, 128, False)
+    assert np.allclose(m["level0"][key], [2e-4, 4e-4]) and np.allclose(m["level1"][key], [1e-4, 2e-4])
+    assert m["level2"] is m["level1"]
+
+
+def test_create_buf_dict_regions_do_not_overlap():
+    import search_algo.benchmark as B
+    from ultraattn_b200 import patterns as P
+    from ultraattn_b200.planner import make_plan
+    from ultraattn_b200.planner.schedule import Fused_Execution_Plan
+    plan = make_plan(pattern=P.causal(1), cp=2, seq_len=256, n_heads=2, head_dim=16, fob=1,
+                     allocation="naive", plan_type="Flexflow")
+    d = B.create_buf_dict(plan.da_config, 1, plan, level_rank=0, dtype=torch.float32, device="cpu")
+    carriers = [v for k, v in d.items() if isinstance(k, tuple)]
+    spans = sorted((c.data.data_ptr(), c.data.data_ptr() + c.nbytes()) for c in carriers if c.nbytes())
+    assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
+    assert d["inp_row"].Q.shape == (1, 128, 2, 16) and d["out_col"].dV.dtype == torch.float32
+    with pytest.raises(ValueError):
+        B.create_buf_dict(plan.da_config, 1, plan, tensor_buf=torch.zeros(64, dtype=torch.uint8), dtype=torch.float32)
+    f = B.create_buf_dict(plan.da_config, 0, Fused_Execution_Plan(2, 2, None, 0), level_rank=3, fused=True,
+                          dtype=torch.float32, device="cpu")
+    assert f["graph_type"] == "fused" and len(f["ir_slots"]) == 2 and f["inp_row"] is f[("ir", 1)]
+    assert f["ir"].numel() >= 2 * f["inp_row"].nbytes()

@@ -79,6 +79,23 @@ def get_bsa_infer_configs(max_intra=8, max_nodes=1, quick=False) -> ExpSpace:
     return _space("bsa_infer", [0], reprs, Ss, [1, 32], max_intra, max_nodes, quick)
 
 
+def get_exp_configs(fobs=(0,), plan_type: str = "manual", transform_mode: str = "greedy",
+                    MAX_QUEUE_SIZE: int = 100) -> list:
+    """One :class:`Evaluation_Configs` per pass (reference: search_algo/exp_configs.py:13-67; the
+    hierarchy is set later, per experiment)."""
+    from ..planner.cost import Evaluation_Configs
+    return [Evaluation_Configs(plan_type, MAX_QUEUE_SIZE, fob, hierarchy=None, transform_mode=transform_mode)
+            for fob in fobs]
+
+
+def get_exp_train_configs(**kw) -> list:
+    return get_exp_configs(fobs=(0, 1), **kw)
+
+
+def get_exp_infer_configs(**kw) -> list:
+    return get_exp_configs(fobs=(0,), **kw)
+
+
 def step0_top_down_decompose(exp_class: str, max_intra: int = 8, max_nodes: int = 1, quick: bool = False) -> ExpSpace:
     fn = {"bsa_train": get_bsa_train_configs, "dense_train": get_dense_train_configs,
           "bsa_infer": get_bsa_infer_configs}.get(exp_class)

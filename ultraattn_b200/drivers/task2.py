@@ -18,11 +18,41 @@ from .arguments import parse_args
 from .exp_configs import step0_top_down_decompose
 
 
-def prepare_inter_comp_plans(inter_plan, prof_db) -> None:
-    """Attach to every inter-level compute kernel the intra-level plan that implements it."""
-    for k in inter_plan.valid_kernels:
+def prepare_inter_comp_plans(inter_plan, prof_db, da_config=None, node_id: int = 0) -> dict:
+    """Attach to every inter-level compute kernel of ``node_id`` the intra-level plan that
+    implements it; returns ``{(batch degrees, profile key): intra plan}`` so that kernels with the
+    same workload share one plan object. A kernel-tile inter plan (``Fused_Execution_Plan``) has
+    one compute kernel per node and gets ``kernel_execution_plan``."""
+    from ..planner.schedule import Fused_Execution_Plan
+    from ..utils.bsa_helpers import convert_intra_profile_key_to_exe_key_or_plan
+    if da_config is not None and hasattr(inter_plan, "materialize") and (
+            isinstance(inter_plan, Fused_Execution_Plan)
+            or getattr(getattr(inter_plan, "d_graph", None), "seqlen_variable_graph", False)):
+        inter_plan.materialize(da_config)
+    plans: dict = {}
+
+    def resolve(key, degrees):
+        ident = (degrees, key)
+        if ident not in plans:
+            what = convert_intra_profile_key_to_exe_key_or_plan(key, prof_db)
+            plans[ident] = prof_db.get_plan(what, 1) if isinstance(what, str) else what
+            if plans[ident] is None:
+                raise KeyError(f"no intra-level plan is stored under {what!r}")
+        return plans[ident]
+
+    if isinstance(inter_plan, Fused_Execution_Plan):
+        key = getattr(inter_plan, "comp_map_key", None)
+        if isinstance(key, str):
+            inter_plan.kernel_execution_plan = resolve(key, (inter_plan.X, inter_plan.Y))
+        return plans
+    lists = inter_plan.gpu_kernel_lists
+    kernels = lists.get(node_id, []) if isinstance(lists, dict) else lists[node_id]
+    for k in kernels:
         if k.type == "comp" and isinstance(k.comp_map_key, str):
-            k.execution_plan = prof_db.get_plan(k.comp_map_key, 1)
+            r, c = k.key[2], k.key[3]
+            degrees = (len(r) if isinstance(r, tuple) else 1, len(c) if isinstance(c, tuple) else 1)
+            k.execution_plan = resolve(k.comp_map_key, degrees)
+    return plans
 
 
 def step4_profile_inter_bsa_exe_plans(space, prof_db, world: int) -> None:

@@ -113,6 +113,40 @@ def naive_allocate_strategy(bsa_config: BSA_Config, fob: int = 0, hierarchy: int
                       float(comp_volumes(table, vol, cp).max()), "naive")
 
 
+def comp_balance_allocate_strategy(bsa_config: BSA_Config, fob: int = 0, hierarchy: int = 1,
+                                   ParD: Optional[int] = None) -> Allocation:
+    """Compute-balanced allocation that ignores traffic ("like zigzag"; a stub that raises in the
+    reference, workload_partition.py:589-591): diagonal tiles stay with their owners, the other
+    tiles go, heaviest first, to the least loaded rank, preferring the owner of the tile's
+    queries, then of its keys, on ties. An upper bound on what balancing alone can achieve; the
+    ILP trades some of it for traffic."""
+    cp = bsa_config.CP[0] if hierarchy == 1 else bsa_config.CP[1]
+    par_d = ParD or max(2 * cp, bsa_config.table.shape[0])
+    vol = tile_volumes(bsa_config.bsa_repr, par_d)
+    cmap = _default_cmap(bsa_config, par_d, cp)
+    table = np.full((par_d, par_d), EMPTY_TILE, dtype=np.int64)
+    load = np.zeros(cp)
+    rest = []
+    for i in range(par_d):
+        for j in range(par_d):
+            if vol[i, j] <= 0:
+                continue
+            if i == j:
+                table[i, j] = cmap[i]
+                load[cmap[i]] += vol[i, j]
+            else:
+                rest.append((i, j))
+    rest.sort(key=lambda t: (-vol[t], t))
+    for i, j in rest:
+        low = load.min()
+        cands = [g for g in range(cp) if load[g] <= low + 1e-9]
+        g = cmap[i] if cmap[i] in cands else cmap[j] if cmap[j] in cands else cands[0]
+        table[i, j] = g
+        load[g] += vol[i, j]
+    cin, cout = comm_volumes(table, cmap, cp, fob)
+    return Allocation(par_d, cmap, table, float(max(cin.max(), cout.max())), float(load.max()), "comp_balance")
+
+
 def _default_cmap(bsa_config: BSA_Config, par_d: int, cp: int) -> np.ndarray:
     if bsa_config.cmap is not None and len(bsa_config.cmap) == par_d:
         return np.asarray(bsa_config.cmap)

@@ -381,3 +381,78 @@ def get_cc_optimal_schedule_from_table(da_config: Dist_Attn_Config, m_config: Ma
     split = (par_d, par_d, 1, 1)
     s_map = np.tile(cmap[None, :], (1, 1))
     return Dist_Attn_Schedule(da_config, m_config, split, s_map, table[None, None])
+
+
+# -------------------------------------------------------------------------------------------------
+# legacy node-profile logs
+# -------------------------------------------------------------------------------------------------
+_LEGACY_BASELINES = ("ring_flash_attn_func", "zigzag_ring_flash_attn_func", "stripe_flash_attn_func")
+
+
+def format_node_profile_lines(fob: int, SP, S, Nh, bs: int, D: int, causal: bool, results: dict) -> list:
+    """Log lines of one measured configuration in the format the reference's benchmark prints and
+    its cost model parses back (search_algo/utils.py:274-363). ``results`` maps a section name
+    (``orchestrated_attn_func``, ``orchestrated_attn_func fused`` or a baseline function name) to
+    a list of ``(tflops, seconds_per_iter)`` measurements."""
+    lines = [f"fob={fob}",
+             f"da_config: SP=({SP[0]},{SP[1]}),Sg=({S[0] // (SP[0] * SP[1])},{S[1] // (SP[0] * SP[1])}),"
+             f"S=({S[0]},{S[1]}),Nh=({Nh[0]},{Nh[1]}),bs={bs},D={D},causal={causal},hierarchy=1"]
+    for name, runs in results.items():
+        lines.append(f"# {name}")
+        for tflops, sec in runs:
+            lines.append(f"mfu: {tflops:.3f} Tflops/s, hfu: {tflops:.3f} Tflops/s, {1.0 / sec:.3f} iter/s, "
+                         f"{sec:.3e} s/iter, (0.000, 0.000, 0.000) sec")
+    return lines
+
+
+def convert_node_profile_data_to_comp_map(file_name, local_size: int = 8) -> dict:
+    """Parse a node-profile log into ``{'level0' | 'level1' | 'level2': {key: [fwd_s, bwd_s]}}``
+    with ``key = (SP, S_per_gpu, Nh, bs, D, causal)``.
+
+    The log is a sequence of ``fob=<0|1>`` lines, configuration lines (``SP=(a,b),...S=(..),Nh=(..),
+    bs=..,D=..,causal=..``), section headers naming the function that was timed and timing lines
+    (``... iter/s, <t> s/iter, ...``). Level 0 keeps the best time of the plain orchestrated
+    sections, level 1 (and its alias level 2) the best over plain and kernel-tile ("fused")
+    sections. Sections of the ring-family baselines are skipped, as in the reference, whose
+    authors did not trust those numbers (search_algo/utils.py:311)."""
+    import re
+    out = {"level0": {}, "level1": {}}
+    if file_name is None:
+        return out
+    rx_fob = re.compile(r"^fob=(\d)")
+    rx_cfg = re.compile(r"SP=\((\d+),(\d+)\),.*S=\((\d+),(\d+)\),Nh=\((\d+),(\d+)\),bs=(\d+),D=(\d+),causal=(True|False)")
+    rx_time = re.compile(r"iter/s, (-?\d+(?:\.\d+)?(?:e[+-]\d+)?) s/iter")
+    fob = key = None
+    level = 0
+    in_baseline = False
+    with open(file_name) as f:
+        for line in f:
+            if any(b in line for b in _LEGACY_BASELINES):
+                in_baseline = True
+                continue
+            if "orchestrated_attn_func" in line:
+                in_baseline = False
+                level = 1 if "fused" in line else 0
+                continue
+            m = rx_time.search(line)
+            if m:
+                if in_baseline or key is None or fob is None:
+                    continue
+                t = float(m.group(1))
+                for lv in range(level, 2):
+                    slot = out[f"level{lv}"].setdefault(key, np.full(2, np.inf, dtype=np.float32))
+                    slot[fob] = min(slot[fob], t)
+                out["level0"].setdefault(key, np.full(2, np.inf, dtype=np.float32))
+                continue
+            m = rx_cfg.search(line)
+            if m:
+                g = [int(x) for x in m.groups()[:8]]
+                tot = g[0] * g[1]
+                key = ((g[0], g[1]), (g[2] // tot, g[3] // tot), (g[4], g[5]), g[6], g[7], m.group(9) == "True")
+                in_baseline = False
+                continue
+            m = rx_fob.match(line)
+            if m:
+                fob = int(m.group(1))
+    out["level2"] = out["level1"]
+    return out

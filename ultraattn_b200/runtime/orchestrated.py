@@ -144,3 +144,92 @@ def orchestrated_attn_backward(inp_row, inp_col, out_fwd=None, dropout_p: float 
     c.dK.copy_(dk)
     c.dV.copy_(dv)
     return r, c
+
+
+# -------------------------------------------------------------------------------------------------
+# one buffer for every carrier of a plan
+# -------------------------------------------------------------------------------------------------
+def _carrier_types(fob: int) -> dict:
+    return {("i", "r"): Input_Row_Fwd if fob == 0 else Input_Row_Bwd,
+            ("i", "c"): Input_Col_Fwd if fob == 0 else Input_Col_Bwd,
+            ("o", "r"): Output_Row_Fwd if fob == 0 else Output_Row_Bwd,
+            ("o", "c"): Output_Col_Fwd if fob == 0 else Output_Col_Bwd}
+
+
+def _fusion_degrees(execution_plan, level_rank: int) -> tuple:
+    """(row degrees, column degrees) of the compute kernels of one rank: a fused kernel spans
+    several Q rows / KV columns, a plain one spans one of each."""
+    rows, cols = {1}, {1}
+    lists = getattr(execution_plan, "gpu_kernel_lists", None) or {}
+    for k in (lists.get(level_rank, []) if isinstance(lists, dict) else lists[level_rank]):
+        if getattr(k, "type", None) == "comp":
+            r, c = k.key[2], k.key[3]
+            rows.add(len(r) if isinstance(r, tuple) else 1)
+            cols.add(len(c) if isinstance(c, tuple) else 1)
+    return sorted(rows), sorted(cols)
+
+
+def create_buf_dict(da_config, fob: int, execution_plan=None, batch_degrees=(1, 1), tensor_buf=None,
+                    level_rank: int = 0, fused: bool = False, dtype=torch.bfloat16, device=None) -> dict:
+    """Carve the data carriers of a plan out of ONE byte buffer (reference: search_algo/benchmark.py:
+    231-334, where every carrier aliases offset 0 of the buffer because results are discarded;
+    here every carrier has its own 256-byte aligned region, so the buffers hold real data).
+
+    General plans: ``buf_dict[((io, rc), degree)]`` for ``io`` in 'i'/'o', ``rc`` in 'r'/'c' and
+    every fusion degree of the rank's compute kernels, plus the aliases ``inp_row``, ``inp_col``,
+    ``out_row``, ``out_col`` (degree 1). Kernel-tile plans (``fused=True``, a
+    ``Fused_Execution_Plan``): regions ``ir`` / ``or`` with X slots and ``ic`` / ``oc`` with Y slots
+    (the gather / reduce-scatter operands), ``inp_row`` / ``inp_col`` being this rank's own slot.
+    ``tensor_buf=None`` allocates exactly what is needed; a buffer that is too small is an error.
+    """
+    types = _carrier_types(fob)
+    cursor = 0
+    pending = []            # (key, cls, batch_degree, offset, nbytes)
+
+    def reserve(key, cls, degree):
+        nonlocal cursor
+        probe = cls.from_da_config_with_buf(da_config, None, degree, dtype, "meta")
+        n = probe.nbytes()
+        pending.append((key, cls, degree, cursor, n))
+        cursor += (n + 255) // 256 * 256
+
+    out: dict = {"graph_type": "fused" if fused else "general"}
+    if not fused:
+        row_deg, col_deg = _fusion_degrees(execution_plan, level_rank) if execution_plan is not None else ([1], [1])
+        for io in ("i", "o"):
+            for deg in row_deg:
+                reserve(((io, "r"), deg), types[(io, "r")], batch_degrees[0] * deg)
+            for deg in col_deg:
+                reserve(((io, "c"), deg), types[(io, "c")], batch_degrees[1] * deg)
+    else:
+        X, Y = execution_plan.X, execution_plan.Y
+        for name, rc, n_slots in (("ir", "r", X), ("ic", "c", Y), ("or", "r", X), ("oc", "c", Y)):
+            io = name[0]
+            for slot in range(n_slots):
+                reserve((name, slot), types[(io, rc)], batch_degrees[0 if rc == "r" else 1])
+    if tensor_buf is None:
+        tensor_buf = torch.zeros(max(cursor, 1), dtype=torch.uint8, device=device)
+    buf = tensor_buf.view(torch.uint8).view(-1) if tensor_buf.dtype != torch.uint8 else tensor_buf.view(-1)
+    if buf.numel() < cursor:
+        raise ValueError(f"tensor_buf holds {buf.numel()} bytes, the plan's carriers need {cursor}")
+    for key, cls, degree, off, n in pending:
+        out[key] = cls.from_da_config_with_buf(da_config, buf[off:off + max(n, 0)], degree, dtype)
+    out["tensor_buf"], out["nbytes"] = tensor_buf, cursor
+    if not fused:
+        out["inp_row"], out["inp_col"] = out[(("i", "r"), 1)], out[(("i", "c"), 1)]
+        out["out_row"], out["out_col"] = out[(("o", "r"), 1)], out[(("o", "c"), 1)]
+    else:
+        x_id, y_id = level_rank % X, level_rank // X
+        for name, n_slots in (("ir", X), ("ic", Y), ("or", X), ("oc", Y)):
+            first, last = pending_offsets(pending, name)
+            out[name] = buf[first:last]
+            out[name + "_slots"] = [out[(name, s)] for s in range(n_slots)]
+        out["inp_row"], out["inp_col"] = out[("ir", x_id)], out[("ic", y_id)]
+        out["out_row"], out["out_col"] = out[("or", x_id)], out[("oc", y_id)]
+    return out
+
+
+def pending_offsets(pending, name: str) -> tuple:
+    """Byte range [first, last) that the slots of region ``name`` cover."""
+    spans = [(off, off + n) for key, _, _, off, n in pending if key[0] == name]
+    return min(s for s, _ in spans), max(e for _, e in spans)

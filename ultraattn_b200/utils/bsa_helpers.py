@@ -67,6 +67,27 @@ def select_best_profile_comp_key(key_prefix: str, suffixes, comp_profile_map, fo
     return best
 
 
+def convert_intra_profile_key_to_exe_key_or_plan(comp_map_key: str, prof_db=None):
+    """What implements an inter-level compute kernel whose cost was looked up under
+    ``comp_map_key`` (reference: search_algo/bsa_utils.py:27-51). Block-sparse keys name their plan
+    directly. FULL node tiles are profiled per (Y, X) grid: the variant without kernel tile maps to
+    the shape-free plan key ``..._shape_config=full_ablation=(Y=..,X=..,dim=0)``, the variant with
+    kernel tile to a ``Fused_Execution_Plan(Y, X)`` built on the spot."""
+    import re
+    if "Y=" not in comp_map_key:
+        return comp_map_key
+    if "w/o_kernel_tile" in comp_map_key:
+        return re.sub(r"shape_config=.*_ablation=\(w/o_kernel_tile,", "shape_config=full_ablation=(", comp_map_key)
+    if "w_kernel_tile" in comp_map_key:
+        m = re.match(r"^fob=(\d+)_.*Y=(\d+),X=(\d+),", comp_map_key)
+        if m is None:
+            raise ValueError(f"cannot read (fob, Y, X) from {comp_map_key!r}")
+        from ..planner.schedule import Fused_Execution_Plan
+        fob, Y, X = (int(g) for g in m.groups())
+        return Fused_Execution_Plan(Y, X, None, fob=fob, m_config=getattr(prof_db, "m_config", None))
+    raise ValueError(f"unsupported profile key {comp_map_key!r}")
+
+
 def create_block_sparse_pattern(CP: int, ParD: int, pattern_type: str, pattern_sparsity: float,
                                 local_blocks=(1, 1), global_blocks=(0, 0), replicate: int = 1) -> BSA_Repr:
     """Parametric generator: ``star`` / ``stream`` = sink columns + causal local band sized from the

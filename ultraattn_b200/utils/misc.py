@@ -118,3 +118,92 @@ class _Neg:
     def __lt__(self, o): return self.k > o.k
     def __gt__(self, o): return self.k < o.k
     def __eq__(self, o): return self.k == o.k
+
+
+# -------------------------------------------------------------------------------------------------
+# small helpers of the reference's search_algo/utils.py that scripts written against it import
+# -------------------------------------------------------------------------------------------------
+def all_wait_main_stream(stream_list, main_stream) -> None:
+    """Every stream of the list waits for the work queued so far on ``main_stream``
+    (reference: search_algo/utils.py:105-108)."""
+    for s in stream_list:
+        if s.cuda_stream != main_stream.cuda_stream:
+            s.wait_stream(main_stream)
+
+
+def main_stream_wait_all(stream_list, main_stream) -> None:
+    """``main_stream`` waits for every stream of the list (reference: search_algo/utils.py:110-113)."""
+    for s in stream_list:
+        if s.cuda_stream != main_stream.cuda_stream:
+            main_stream.wait_stream(s)
+
+
+def convert_block_table_to_value(block_table):
+    """Integer table (0 empty, 1 full, 2 causal) of a table of :class:`Block_Type` members."""
+    import numpy as np
+    flat = [getattr(v, "value", v) for v in np.asarray(block_table, dtype=object).flatten()]
+    return np.array(flat, dtype=np.int64).reshape(np.asarray(block_table).shape)
+
+
+def combine_list_to_0(l0: list, l1: list) -> list:
+    """Append to ``l0`` the items of ``l1`` that it lacks (order kept); returns ``l0``."""
+    for x in l1:
+        if x not in l0:
+            l0.append(x)
+    return l0
+
+
+def closest_fraction(x: float, max_denominator: int = 1000):
+    from fractions import Fraction
+    return Fraction(x).limit_denominator(max_denominator)
+
+
+def get_factors(n: int) -> list:
+    """All divisors of ``n`` in increasing order."""
+    small = [d for d in range(1, int(n ** 0.5) + 1) if n % d == 0]
+    return sorted(set(small + [n // d for d in small]))
+
+
+def find_file_with_regex(directory: str, pattern: str) -> list:
+    """Names of the files in ``directory`` that match the regular expression."""
+    import os
+    import re
+    rx = re.compile(pattern)
+    return sorted(f for f in os.listdir(directory) if rx.match(f))
+
+
+def filter_kwargs(func, kwargs: dict) -> dict:
+    """The entries of ``kwargs`` that ``func`` accepts."""
+    import inspect
+    names = inspect.signature(func).parameters
+    return {k: v for k, v in kwargs.items() if k in names}
+
+
+class Block_Attention_Config:
+    """Pattern plus partition in the pre-``BSA_Config`` form of the reference
+    (search_algo/utils.py:151-178): ``CP`` ranks, ``ParD`` x ``ParD`` table of
+    :class:`Block_Type`, ``cmap`` chunk -> rank. ``to_bsa_config`` gives the current form."""
+
+    def __init__(self, CP: int, ParD: int, cmap, block_table):
+        import numpy as np
+        self.CP, self.ParD = CP, ParD
+        self.cmap = np.asarray(cmap)
+        self.block_table = block_table
+
+    @classmethod
+    def from_causal(cls, CP: int, ParD: int, cmap):
+        import numpy as np
+        from ..patterns.blocks import Block_Type
+        table = np.empty((ParD, ParD), dtype=object)
+        for i in range(ParD):
+            for j in range(ParD):
+                table[i, j] = Block_Type.FULL if j < i else Block_Type.CAUSAL if j == i else Block_Type.EMPTY
+        return cls(CP, ParD, cmap, table)
+
+    @property
+    def block_table_value(self):
+        return convert_block_table_to_value(self.block_table)
+
+    def to_bsa_config(self):
+        from ..patterns.blocks import BSA_Config, BSA_Repr
+        return BSA_Config(None, None, {"bsa_repr": BSA_Repr(self.block_table_value, self.cmap), "CP": (self.CP, 1)})
