@@ -98,7 +98,18 @@ class Output_Col_Bwd(Integrated_Data):
 _executors: dict = {}
 
 
-def _executor(execution_plan_dict: dict, PROC_INFO, device) -> PlanExecutor:
+def _executor(execution_plan_dict: dict, PROC_INFO, device):
+    """The object that runs the plans of ``execution_plan_dict``: a :class:`PlanExecutor` for
+    launch plans ('fwd' / 'bwd', or 'intra'), a grid executor for a kernel-tile plan ('fused': a
+    ``Fused_Execution_Plan``). Cached per plan object."""
+    fused = execution_plan_dict.get("fused")
+    if fused is not None:
+        key = ("fused", id(fused))
+        if key not in _executors:
+            from .grid import GridExecutor
+            _executors[key] = GridExecutor.from_plan(fused, execution_plan_dict.get("group"), device,
+                                                     execution_plan_dict.get("registry"))
+        return _executors[key]
     key = (id(execution_plan_dict.get("fwd") or execution_plan_dict.get("intra")), id(execution_plan_dict.get("bwd")))
     if key not in _executors:
         pf = execution_plan_dict.get("fwd") or execution_plan_dict.get("intra")
@@ -106,6 +117,27 @@ def _executor(execution_plan_dict: dict, PROC_INFO, device) -> PlanExecutor:
         _executors[key] = PlanExecutor(pf, pb, group=execution_plan_dict.get("group"), device=device,
                                        p2p_groups=execution_plan_dict.get("p2p_groups"))
     return _executors[key]
+
+
+class OrchestratedAttnFunc(torch.autograd.Function):
+    """Differentiable form on plain tensors (the reference's class of this name has a forward that
+    returns nothing and a backward that asserts, orchestrated_attn_impl.py:688-761):
+    ``OrchestratedAttnFunc.apply(q, k, v, softmax_scale, execution_plan_dict)`` -> O of this
+    rank's shard; gradients flow to q, k, v."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, softmax_scale, execution_plan_dict):
+        ex = _executor(execution_plan_dict, None, q.device)
+        o, lse = ex.forward(q, k, v, softmax_scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.ex, ctx.scale = ex, softmax_scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = ctx.ex.backward(d_o.contiguous(), q, k, v, o, lse, ctx.scale)
+        return dq, dk, dv, None, None
 
 
 def orchestrated_attn_func(inp_row, inp_col, dropout_p: float = 0.0, softmax_scale=None, causal: bool = False,
