@@ -1,4 +1,6 @@
 """Utilities, configuration, data carriers and model glue (CPU)."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -241,3 +243,38 @@ def test_create_buf_dict_regions_do_not_overlap():
                           dtype=torch.float32, device="cpu")
     assert f["graph_type"] == "fused" and len(f["ir_slots"]) == 2 and f["inp_row"] is f[("ir", 1)]
     assert f["ir"].numel() >= 2 * f["inp_row"].nbytes()
+
+
+def test_cluster_launchers_and_rank_setup(tmp_path, capsys):
+    """SLURM / OpenMPI command lines, scheduler variables -> rank variables, NUMA core lists, and a
+    real per-rank exec that runs a child with the derived environment."""
+    import subprocess
+    import sys
+    from ultraattn_b200.drivers import launch
+    assert launch.main(["--launcher", "slurm", "--nodes", "2", "--gpus", "8", "--partition", "H800",
+                        "--ib-hca", "mlx5_0,mlx5_1", "--dry-run", "--", "bench.py"]) == 0
+    line = capsys.readouterr().out
+    assert line.startswith("srun -N 2 --ntasks-per-node=8 --gres=gpu:8 -K") and "--rank-exec --ib-hca mlx5_0,mlx5_1 -- bench.py" in line
+    assert launch.main(["--launcher", "mpirun", "--hosts", "g1:8,g2:4", "--dry-run", "--", "bench.py"]) == 0
+    assert capsys.readouterr().out.startswith("mpirun -np 12 --host g1:8,g2:4")
+    e = launch.rank_env({"SLURM_PROCID": "9", "SLURM_NTASKS": "16", "SLURM_LOCALID": "1",
+                         "SLURM_NTASKS_PER_NODE": "8", "SLURM_JOB_NODELIST": "g1,g2"})
+    assert (e["RANK"], e["WORLD_SIZE"], e["LOCAL_RANK"], e["LOCAL_WORLD_SIZE"], e["MASTER_ADDR"]) == ("9", "16", "1", "8", "g1")
+    e = launch.rank_env({"OMPI_COMM_WORLD_RANK": "3", "OMPI_COMM_WORLD_SIZE": "4", "OMPI_COMM_WORLD_LOCAL_RANK": "3",
+                         "MASTER_ADDR": "10.0.0.1"})
+    assert e["RANK"] == "3" and "MASTER_ADDR" not in e and e["MASTER_PORT"] == "12215"
+    assert launch.parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    for n, cpus in enumerate(["0-3", "4-7"]):
+        (tmp_path / f"node{n}").mkdir()
+        (tmp_path / f"node{n}" / "cpulist").write_text(cpus + "\n")
+    nodes = launch.numa_nodes(str(tmp_path))
+    assert nodes == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    assert launch.cpus_for_local_rank(1, 8, nodes) == [0, 1, 2, 3] and launch.cpus_for_local_rank(6, 8, nodes) == [4, 5, 6, 7]
+    assert launch.cpus_for_local_rank(0, 8, []) == []
+    env = dict(os.environ, SLURM_PROCID="5", SLURM_NTASKS="8", SLURM_LOCALID="5", SLURM_NTASKS_PER_NODE="8")
+    env.pop("RANK", None)
+    out = subprocess.run([sys.executable, "-m", "ultraattn_b200.drivers.launch", "--rank-exec", "--ib-hca", "mlx5_9",
+                          "--", "-c", "import os; print(os.environ['RANK'], os.environ['WORLD_SIZE'], "
+                          "os.environ['NCCL_IB_HCA'], os.environ['CUDA_DEVICE_MAX_CONNECTIONS'])"],
+                         env=env, capture_output=True, text=True, cwd=os.path.dirname(os.path.dirname(__file__)))
+    assert out.stdout.split() == ["5", "8", "mlx5_9", "32"], out.stderr
