@@ -31,7 +31,7 @@ GIB = 1024 ** 3
 
 # measured on B200 with this repository's kernels (bf16, D = 128): sustained tile throughput
 B200_FWD_TFLOPS = 1050.0
-B200_BWD_TFLOPS = 740.0
+B200_BWD_TFLOPS = 1100.0
 B200_NVLINK_GBS = 770.0          # peer copy, per direction
 B200_LINK_LATENCY_S = 4e-6
 B200_LAUNCH_S = 6e-6
