@@ -362,3 +362,71 @@ def test_flag_wait_times_out_cleanly():
                                   torch.cuda.current_stream(dev).cuda_stream)
     torch.cuda.synchronize()
     A.check_status(dev)
+
+
+def _grid_varlen_worker(rank, world, port, ret):
+    """Kernel-tile grid executor (NCCL collectives around one launch) and the packed
+    variable-length zigzag ring on real GPUs, against the dense oracle."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    try:
+        from ultraattn_b200 import parallel as PL, patterns as P
+        from ultraattn_b200.ops import attention as A
+        from ultraattn_b200.runtime import GridExecutor
+        S, H = 2048, 2
+        g = torch.Generator().manual_seed(21)
+        q, k, v, d_o = (torch.randn(1, S, H, 128, generator=g).to(torch.bfloat16) for _ in range(4))
+        sl = slice(rank * S // world, (rank + 1) * S // world)
+        ql, kl, vl, dol = (t[:, sl].contiguous().to(dev) for t in (q, k, v, d_o))
+        out = {}
+        for name, (Y, X, causal) in {"grid_1x2_causal": (1, 2, True), "grid_2x1_full": (2, 1, False)}.items():
+            ex = GridExecutor(Y, X, device=dev, causal=causal)
+            o, lse = ex.forward(ql, kl, vl)
+            dq, dk, dv = ex.backward(dol, ql, kl, vl, o, lse)
+            torch.cuda.synchronize()
+            A.check_status(dev)
+            ref = P.dense_attention_with_grads(q.float(), k.float(), v.float(), d_o.float(),
+                                               P.causal(1) if causal else P.full(1))
+            worst = 0.0
+            for got, r in ((o, ref[0]), (dq, ref[2]), (dk, ref[3]), (dv, ref[4])):
+                worst = max(worst, (got.float().cpu() - r[:, sl]).abs().max().item() / (r.abs().max().item() + 1e-6))
+            out[name] = worst
+        # packed batch of two sequences, zigzag shards, causal
+        cu = [0, 1024, 1536]
+        qp, kp, vp, dop = (t[0, :cu[-1]] for t in (q, k, v, d_o))
+        sh = lambda t: PL.shard_packed(t, cu, rank, world, "zigzag")[0]
+        local_cu = PL.shard_packed(qp, cu, rank, world, "zigzag")[1]
+        qz, kz, vz = (sh(t).to(dev).requires_grad_() for t in (qp, kp, vp))
+        oz = PL.zigzag_ring_flash_attn_varlen_func(qz, kz, vz, local_cu, None, causal=True)
+        oz.backward(sh(dop).to(dev))
+        torch.cuda.synchronize()
+        A.check_status(dev)
+        worst = 0.0
+        refs = [P.dense_attention_with_grads(*(t[None, a:b].float() for t in (qp, kp, vp, dop)), P.causal(1))
+                for a, b in zip(cu[:-1], cu[1:])]
+        for got, i in ((oz, 0), (qz.grad, 2), (kz.grad, 3), (vz.grad, 4)):
+            r = torch.cat([x[i][0] for x in refs], dim=0)
+            worst = max(worst, (got.float().cpu() - sh(r)).abs().max().item() / (r.abs().max().item() + 1e-6))
+        out["zigzag_varlen"] = worst
+        ret[rank] = out
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = {"error": f"{type(e).__name__}: {e}\n{traceback.format_exc()}"}
+    finally:
+        dist.destroy_process_group()
+
+
+def test_grid_executor_and_varlen_ring_2gpu():
+    _need(2)
+    port = 29300 + os.getpid() % 200
+    ret = mp.Manager().dict()
+    mp.spawn(_grid_varlen_worker, args=(2, port, ret), nprocs=2, join=True)
+    for r in range(2):
+        assert "error" not in ret[r], ret[r].get("error")
+        for name, err in ret[r].items():
+            assert err < 2e-2, (r, name, err)

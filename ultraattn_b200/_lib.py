@@ -81,7 +81,6 @@ def load():
         return _lib
     path = _build.LIB_PATH
     if os.environ.get("UA_LIB_PATH"):           # explicit library file (development builds)
-        from pathlib import Path
         _lib = _declare(ctypes.CDLL(os.environ["UA_LIB_PATH"]))
         return _lib
     if not path.exists() or os.environ.get("UA_REBUILD") == "1":

@@ -8,10 +8,8 @@ with a forward that returns nothing and a backward that asserts
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
-import numpy as np
 import torch
 
 from .ops import attention as A

@@ -7,7 +7,8 @@ Configurations: ``causal128k`` (dense causal, S = 128k, forward + backward), ``s
 (32 blocks of 16k, stride 4, window 2, forward + backward), ``gl512k`` (global+local, block 0
 global, causal window 2, forward + backward), ``star512k`` and ``streaming512k`` (prefill, forward
 only); all with 32 heads of 128, batch 1, bf16. Paths: ``fused`` (peer-memory kernels), ``nccl``
-(plan executed with NCCL messages), ``ring`` / ``zigzag`` (ring baselines; dense patterns only).
+(plan executed with NCCL messages), ``ring`` / ``zigzag`` (ring baselines; dense patterns only),
+``grid<Y>x<X>`` (kernel-tile form: gathers, one launch, merge / reduce-scatter; dense patterns only).
 
 Every line carries the device time (max over ranks), the model TFLOP/s per GPU and the achieved
 fraction of the roofline = max(FLOPs / measured bf16 peak, bytes that must cross NVLink per GPU /
@@ -17,6 +18,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 from pathlib import Path
 
@@ -100,7 +102,9 @@ def main() -> None:
         for path in a.paths.split(","):
             if world == 1 and path != "fused":
                 continue
-            if path in ("ring", "zigzag") and not (pat.check_causal() and n == 1 or pat.check_full()):
+            if (path in ("ring", "zigzag") or path.startswith("grid")) and not (pat.check_causal() and n == 1 or pat.check_full()):
+                continue
+            if path.startswith("grid") and math.prod(int(t) for t in path[4:].split("x")) != world:
                 continue
             try:
                 nvl_bytes = 0.0
@@ -127,6 +131,16 @@ def main() -> None:
                         o_, l_ = rt.forward(q, k, v)
                         if train:
                             rt.backward(d_o, q, k, v, o_, l_)
+                elif path.startswith("grid"):
+                    # kernel-tile form with NCCL collectives, e.g. grid1x2 = Y 1, X 2 (dense patterns)
+                    from ..runtime.grid import GridExecutor
+                    Y, X = (int(t) for t in path[4:].split("x"))
+                    gx = GridExecutor(Y, X, device=dev, causal=pat.check_causal())
+
+                    def step():
+                        o_, l_ = gx.forward(q, k, v)
+                        if train:
+                            gx.backward(d_o, q, k, v, o_, l_)
                 else:
                     kind = path
                     qs, ks, vs = (t.clone().requires_grad_() for t in (q, k, v))

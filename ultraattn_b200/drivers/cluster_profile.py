@@ -15,11 +15,8 @@ from __future__ import annotations
 
 import argparse
 import json
-import os
-import time
 from pathlib import Path
 
-import numpy as np
 import torch
 
 

@@ -16,9 +16,8 @@ input of the backward (orchestrated_attn/utils.py:148-188).
 """
 from __future__ import annotations
 
-import ctypes
 import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Sequence
 
 import numpy as np

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import enum
 import math
-from typing import Iterable, Optional, Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 

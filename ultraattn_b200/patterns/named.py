@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import numpy as np
 
-from .blocks import BSA_Repr, Block_Type, CAUSAL, EMPTY, FULL, _to_enum
+from .blocks import BSA_Repr, CAUSAL, EMPTY, FULL, _to_enum
 
 
 def full(n_blocks: int = 1) -> BSA_Repr:

@@ -35,7 +35,7 @@ from typing import Optional, Sequence
 
 import numpy as np
 
-from ..patterns.blocks import BSA_Config, BSA_Repr, CAUSAL, EMPTY, FULL, _VOLUME
+from ..patterns.blocks import BSA_Config, BSA_Repr, _VOLUME
 from .solver import Model
 
 EMPTY_TILE = -1       # schedule_table value for a tile nobody computes

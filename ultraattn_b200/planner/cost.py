@@ -18,7 +18,6 @@ from __future__ import annotations
 import json
 import math
 import re
-from dataclasses import dataclass, field
 from functools import reduce
 from pathlib import Path
 from typing import Optional, Sequence

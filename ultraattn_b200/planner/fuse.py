@@ -16,7 +16,6 @@ from __future__ import annotations
 import copy
 import itertools
 import math
-from typing import Optional
 
 import numpy as np
 

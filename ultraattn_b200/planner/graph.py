@@ -14,11 +14,11 @@ Kernel keys (kept identical to the reference, search_algo/dependent_graph.py:15-
 from __future__ import annotations
 
 import copy
-from typing import Iterable, Optional
+from typing import Optional
 
 import numpy as np
 
-from ..patterns.blocks import BSA_Config, CAUSAL, EMPTY, FULL, _VOLUME
+from ..patterns.blocks import BSA_Config, CAUSAL, FULL
 from .cost import (Dist_Attn_Config, Dist_Attn_Schedule, Machine_Config, analytic_tile_time,
                    convert_shape_config_to_str)
 

@@ -20,7 +20,6 @@ Data bundles per message (one flat buffer each, like the reference's carriers):
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import numpy as np
@@ -29,7 +28,7 @@ import torch.distributed as dist
 
 from ..ops import attention as A
 from ..ops import elementwise as E
-from ..patterns.blocks import CAUSAL, FULL
+from ..patterns.blocks import CAUSAL
 
 
 class FaultInjector:

@@ -29,7 +29,6 @@ staging lists, merge lists) also runs on CPU with all ranks simulated in one pro
 """
 from __future__ import annotations
 
-import math
 import os
 from typing import Optional, Sequence
 
@@ -40,7 +39,7 @@ import torch.distributed as dist
 from .. import _lib
 from ..ops import attention as A
 from ..ops import elementwise as E
-from ..patterns.blocks import BSA_Config, BSA_Repr, CAUSAL
+from ..patterns.blocks import BSA_Repr, CAUSAL
 
 CHUNK_BYTES = 1 << 20       # staging granularity: one copy task moves at most this much
 # CTAs that share the staging copies at the start of a launch (UA_COPY_CTAS overrides): all SMs
