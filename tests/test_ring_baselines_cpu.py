@@ -130,3 +130,71 @@ def test_two_level_ring_2x2(causal):
     for r in range(4):
         assert isinstance(ret[r], float), ret[r]
         assert ret[r] < 2e-4, (r, ret[r])
+
+
+def test_lightseq_time_steps_match_the_allocation_table():
+    """The worker / helper time-step view restates the balanced allocation table: every causal
+    tile is computed exactly once, by the rank the table names."""
+    from ultraattn_b200.parallel import lightseq as LS
+    from ultraattn_b200.planner.dense import get_lightseq_schedule_table
+    for w in (2, 4, 5, 8):
+        table = get_lightseq_schedule_table(w)
+        seen = {}
+        for r in range(w):
+            for t in range(LS.num_time_steps(w)):
+                kind, other = LS.time_step_work(t, r, w)
+                tile = (r, other) if kind == "local" else (other, r) if kind == "help" else None
+                if tile is not None:
+                    assert tile not in seen and table[tile] == r, (w, r, t, tile)
+                    seen[tile] = r
+        assert len(seen) == w * (w + 1) // 2
+    # the reference's predicates on its 8-rank example
+    assert [t for t in range(5) if LS.is_last_time(t, 5, 8)] == [4] and LS.is_last_time(2, 2, 8)
+    assert [t for t in range(5) if LS.is_compute_for_local_query(t, 1, 8)] == [0, 1]
+    assert [r for r in range(8) if LS.is_idle(4, r, 8)] == [0, 1, 2, 3]
+    assert [t for t in range(5) if LS.is_sync_from_remote(t, 7, 8)] == [2, 3, 4]
+    assert not any(LS.is_sync_from_remote(t, 4, 8) for t in range(5))
+
+
+def _lightseq_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    try:
+        from easy_context.dist_flash_attn import async_communication as AC
+        from easy_context.dist_flash_attn.lightseq_async_attn import attention
+        from easy_context.dist_flash_attn.prepare_input import extract_local
+        from ultraattn_b200 import patterns as P
+        from ultraattn_b200.parallel.comm import comm_stats
+        AC.initialize_distributed("gloo")
+        assert AC.get_sequence_parallel_size() == world and AC.get_sequence_parallel_rank() == rank
+        S, H, Hk, D = 256, 4, 2, 16
+        g = torch.Generator().manual_seed(9)
+        q, d_o = (torch.randn(1, H, S, D, generator=g) for _ in range(2))      # [batch, heads, tokens, dim]
+        k, v = (torch.randn(1, Hk, S, D, generator=g) for _ in range(2))
+        loc = lambda t: extract_local(t, rank, world, dim=2).contiguous()
+        ql, kl, vl = (loc(t).requires_grad_() for t in (q, k, v))
+        comm_stats(reset=True)
+        o = attention(ql, kl, vl, True, None)
+        o.backward(loc(d_o))
+        st = comm_stats()
+        assert st["fwd_send"] > 0 and st["bwd_recv"] > 0
+        tr = lambda t: t.transpose(1, 2)
+        o_ref, _, dq, dk, dv = P.dense_attention_with_grads(tr(q), tr(k), tr(v), tr(d_o), P.causal(1))
+        ret[rank] = max((o - loc(tr(o_ref))).abs().max().item(), (ql.grad - loc(tr(dq))).abs().max().item(),
+                        (kl.grad - loc(tr(dk))).abs().max().item(), (vl.grad - loc(tr(dv))).abs().max().item())
+        AC.destroy_sequence_parallel()
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_lightseq_attention_world4():
+    port = 29100 + os.getpid() % 90
+    ret = mp.Manager().dict()
+    mp.spawn(_lightseq_worker, args=(4, port, ret), nprocs=4, join=True)
+    for r in range(4):
+        assert isinstance(ret[r], float), ret[r]
+        assert ret[r] < 2e-4, (r, ret[r])

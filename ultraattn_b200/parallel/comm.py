@@ -18,6 +18,39 @@ import torch.distributed as dist
 PROC_INFO: dict = {}
 _groups: dict = {}
 
+# bytes this process handed to / asked from torch.distributed point-to-point and all-to-all calls,
+# by phase (reference: the per-step byte counters of LightSeq's communication layer,
+# easy_context/dist_flash_attn/async_communication.py:499-512)
+_comm_stats = {"fwd_send": 0, "fwd_recv": 0, "bwd_send": 0, "bwd_recv": 0}
+_comm_phase = ["fwd"]
+
+
+def set_comm_phase(phase: str) -> None:
+    assert phase in ("fwd", "bwd")
+    _comm_phase[0] = phase
+
+
+def count_comm(send_bytes: int = 0, recv_bytes: int = 0) -> None:
+    _comm_stats[_comm_phase[0] + "_send"] += int(send_bytes)
+    _comm_stats[_comm_phase[0] + "_recv"] += int(recv_bytes)
+
+
+def comm_stats(reset: bool = False) -> dict:
+    out = dict(_comm_stats)
+    if reset:
+        for k in _comm_stats:
+            _comm_stats[k] = 0
+    return out
+
+
+def print_and_reset_comm_stats(rank: Optional[int] = None) -> dict:
+    """Print this rank's communicated volume in GB per phase and direction, then clear it."""
+    st = comm_stats(reset=True)
+    r = rank if rank is not None else (dist.get_rank() if dist.is_initialized() else 0)
+    print(f"R={r} fwd send: {st['fwd_send'] * 1e-9} fwd recv: {st['fwd_recv'] * 1e-9}; "
+          f"bwd send: {st['bwd_send'] * 1e-9}, bwd recv: {st['bwd_recv'] * 1e-9} GB.", flush=True)
+    return st
+
 
 def get_proc_info() -> dict:
     env = os.environ
@@ -104,6 +137,8 @@ class RingComm:
 
     def send_recv(self, to_send: torch.Tensor, recv_tensor: Optional[torch.Tensor] = None) -> torch.Tensor:
         res = torch.empty_like(to_send) if recv_tensor is None else recv_tensor
+        nbytes = to_send.numel() * to_send.element_size()
+        count_comm(nbytes, nbytes)
         self._ops.append(dist.P2POp(dist.isend, to_send, self.send_rank, group=self.group))
         self._ops.append(dist.P2POp(dist.irecv, res, self.recv_rank, group=self.group))
         return res
@@ -133,6 +168,8 @@ class A2AComm:
         if self.world == 1:
             return x
         ins = [t.contiguous() for t in x.chunk(self.world, dim=scatter_dim)]
+        moved = (self.world - 1) * ins[0].numel() * ins[0].element_size()
+        count_comm(moved, moved)
         outs = [torch.empty_like(ins[0]) for _ in range(self.world)]
         dist.all_to_all(outs, ins, group=self.group) if x.is_cuda else _a2a_p2p(outs, ins, self.group)
         return torch.cat(outs, dim=gather_dim)

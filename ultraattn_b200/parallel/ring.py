@@ -18,7 +18,7 @@ import torch.distributed as dist
 
 from ..ops import attention as A
 from ..ops import elementwise as E
-from .comm import A2AComm, RingComm
+from .comm import A2AComm, RingComm, set_comm_phase
 
 
 # A rule maps (ring position of the rank whose K/V block is held, own ring position, shard length)
@@ -154,6 +154,7 @@ def _route(group):
 def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None, bounds=None):
     """``group``: a process group (flat ring) or ``{'intra': pg, 'inter': pg}`` (two-level ring).
     ``bounds``: (start, end) of every packed sequence in this rank's shard; default one sequence."""
+    set_comm_phase("fwd")
     route = _route(group)
     comms = route.comms()
     k, v = k.contiguous(), v.contiguous()        # they are sent as whole messages
@@ -180,6 +181,7 @@ def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None, bo
 
 
 def ring_backward(d_o, q, k, v, o, lse, group, kind: str, causal: bool, softmax_scale=None, bounds=None):
+    set_comm_phase("bwd")
     route = _route(group)
     kv_comms, g_comms = route.comms(), route.comms()
     k, v = k.contiguous(), v.contiguous()

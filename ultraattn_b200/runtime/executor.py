@@ -28,6 +28,7 @@ import torch.distributed as dist
 
 from ..ops import attention as A
 from ..ops import elementwise as E
+from ..parallel.comm import count_comm, set_comm_phase
 from ..patterns.blocks import CAUSAL
 
 
@@ -125,6 +126,7 @@ class PlanExecutor:
     def _send(self, buf: torch.Tensor, kernel, stream_idx: int, deps):
         dst = self._global_rank(kernel.key[4])
         self.bytes_sent += buf.numel() * buf.element_size()
+        count_comm(send_bytes=buf.numel() * buf.element_size())
         if self.cuda:
             st = self.streams[stream_idx]
             for e in deps:
@@ -139,6 +141,7 @@ class PlanExecutor:
     def _recv(self, buf: torch.Tensor, kernel, stream_idx: int, deps):
         src = self._global_rank(kernel.key[3])
         self.bytes_recv += buf.numel() * buf.element_size()
+        count_comm(recv_bytes=buf.numel() * buf.element_size())
         if self.cuda:
             st = self.streams[stream_idx]
             for e in deps:
@@ -172,6 +175,7 @@ class PlanExecutor:
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale=None):
         """q/k/v: this rank's shard ``[B, S/CP, H, D]`` (blocks in ``my_blocks`` order).
         Returns (O ``[B, S/CP, H, D]``, lse ``[B, H, S/CP]`` fp32)."""
+        set_comm_phase("fwd")
         plan, g = self.plan_fwd, self.rank
         B, _, H, D = q.shape
         Hk = k.shape[2]
@@ -293,6 +297,7 @@ class PlanExecutor:
     # =============================== backward ===================================================
     def backward(self, d_o, q, k, v, o, lse, softmax_scale=None):
         """Returns (dQ, dK, dV) shards in the dtype of q. ``o`` and ``lse`` are the forward's."""
+        set_comm_phase("bwd")
         plan, g = self.plan_bwd, self.rank
         assert plan is not None, "no backward plan was given"
         B, S_loc, H, D = q.shape
