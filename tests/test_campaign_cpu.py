@@ -70,3 +70,26 @@ def test_inter_node_plan_uses_intra_costs():
                                 {"hfu": 1.0, "time": "5.000e-01", "sim_time": "5.000e-01"}})
     g2 = Dependent_Graph(sch, 0, bsa_comp_key_suffixes=["_ablation=(w/o_kernel_tile,ILP)"])
     assert any(abs(k.time[0] - 0.5) < 1e-12 for k in g2.kernel_dict.values() if k.type == "comp")
+
+
+def test_fusion_table_and_full_plan_generation(tmp_path, capsys):
+    """The tile-fusion table (small tiles gain from fusing, big ones do not) and the generator of
+    the Y x X plans of FULL attention into the plan database."""
+    from ultraattn_b200.drivers import fusion_evaluate, intra_attn_gen
+    from ultraattn_b200.plandb import Prof_DB
+    from ultraattn_b200.planner.cost import FlashAttn_Profile_Map
+    rows = fusion_evaluate.fusion_table(FlashAttn_Profile_Map({}), [1], [256, 16384], degrees=[(2, 2)])
+    small = next(r for r in rows if r["S"] == 256 and r["fob"] == 0)
+    big = next(r for r in rows if r["S"] == 16384 and r["fob"] == 0)
+    assert small["speedup"] > 1.5 and big["speedup"] < small["speedup"]
+    measured = FlashAttn_Profile_Map({(256, 1, 1, 128, "1/1", False): [1e-5, 3e-5],
+                                      (256, 1, 1, 128, "2/1", False): [1.2e-5, 3.3e-5]})
+    r = fusion_evaluate.fusion_table(measured, [1], [256], degrees=[(2, 1)])
+    assert abs(r[0]["speedup"] - 2 / 1.2) < 1e-9 and abs(r[1]["speedup"] - 2 * 3 / 3.3) < 1e-9
+    assert fusion_evaluate.main(["--nh", "1", "--smin", "256", "--smax", "512"]) == 0
+    assert "speed-up" in capsys.readouterr().out
+    db = Prof_DB("t", "B200", root=str(tmp_path))
+    keys = intra_attn_gen.generate(db, 4, (0, 1))
+    assert len(keys) == 6 and "fob=1_CP=(4, 1)_shape_config=full_ablation=(Y=2,X=2,dim=0)" in keys
+    plan = db.get_plan(keys[0], 1)
+    assert plan.verify() == [] and intra_attn_gen.generate(db, 4, (0, 1)) == keys
