@@ -115,3 +115,51 @@ def test_poisoned_mirrors_are_fully_overwritten(monkeypatch):
     monkeypatch.setenv("UA_DEBUG_POISON", "1")
     err, table = _run_all_ranks(P.strided(8, 4, 2), 4, 512, 2, 16, "ilp")
     assert err < 2e-4, (err, table)
+
+
+def _build_ranks(pattern, world, S=1024, H=2, D=16, allocation="ilp", multicast=False, min_consumers=2):
+    table, cmap = plan_allocation(pattern, world, 1, allocation, time_limit=5.0)
+    registry = {}
+    ranks = [FusedContextParallel(table, cmap, pattern, S, H, D, FakeSpace(r, world, registry, multicast=multicast),
+                                  dtype=torch.float32, defer_build=True, nvls_min_consumers=min_consumers)
+             for r in range(world)]
+    for rk in ranks:
+        rk.build()
+    return ranks
+
+
+@pytest.mark.parametrize("name,world,multicast", [("strided", 4, False), ("global_local", 4, True), ("causal", 2, False)])
+def test_static_verifier_accepts_the_tables_and_catches_damage(name, world, multicast):
+    """The memory-level plan check: the tables every rank builds pass; a doubled mailbox writer, a
+    dropped wait and a tile moved to another rank are each reported."""
+    import dataclasses
+    from ultraattn_b200.ops import attention as A
+    from ultraattn_b200.runtime.verify import verify_fused_tables
+    pattern = {"strided": P.strided(8, 4, 2), "global_local": P.global_local(8, 1, 2), "causal": P.causal(1)}[name]
+    ranks = _build_ranks(pattern, world, allocation="naive" if multicast else "ilp", multicast=multicast,
+                         min_consumers=1 if multicast else 2)
+    assert verify_fused_tables(ranks) == []
+    # 1. a foreign row written into somebody else's slot
+    victim = next((rk for rk in ranks if any(r.o_slot != 0 for r in rk.f_rows)), None)
+    if victim is not None:
+        i = next(i for i, r in enumerate(victim.f_rows) if r.o_slot != 0)
+        good = victim.f_rows[i]
+        victim.f_rows[i] = dataclasses.replace(good, o_start=good.o_start + victim.blk)
+        assert any("mailbox" in p for p in verify_fused_tables(ranks))
+        victim.f_rows[i] = good
+    # 2. a remote key block read without waiting for its staging flag
+    victim = next((rk for rk in ranks if any(s.wait_flag for r in rk.f_rows for s in r.segs)), None)
+    if victim is not None:
+        i = next(i for i, r in enumerate(victim.f_rows) if any(s.wait_flag for s in r.segs))
+        good = victim.f_rows[i]
+        segs = tuple(dataclasses.replace(s, wait_flag=0, wait_count=0) for s in good.segs)
+        victim.f_rows[i] = dataclasses.replace(good, segs=segs)
+        assert any("without a matching wait" in p for p in verify_fused_tables(ranks))
+        victim.f_rows[i] = good
+    # 3. a tile dropped from one rank's work list
+    rk = ranks[-1]
+    good = rk.f_rows[-1]
+    rk.f_rows[-1] = dataclasses.replace(good, segs=good.segs[:-1])
+    assert any("computed by []" in p for p in verify_fused_tables(ranks))
+    rk.f_rows[-1] = good
+    assert verify_fused_tables(ranks) == []
