@@ -278,3 +278,41 @@ def test_cluster_launchers_and_rank_setup(tmp_path, capsys):
                           "os.environ['NCCL_IB_HCA'], os.environ['CUDA_DEVICE_MAX_CONNECTIONS'])"],
                          env=env, capture_output=True, text=True, cwd=os.path.dirname(os.path.dirname(__file__)))
     assert out.stdout.split() == ["5", "8", "mlx5_9", "32"], out.stderr
+
+
+def test_ring_utils_and_dense_helpers(tmp_path):
+    """update_out_and_lse equals one softmax over both blocks; flatten / unflatten of packed lse;
+    write_plan round trip; the causal-only allocation names."""
+    import math
+    import search_algo.dense_utils as DU
+    import search_algo.workload_partition as WP
+    from ring_flash_attn.utils import flatten_varlen_lse, unflatten_varlen_lse, update_out_and_lse
+    torch.manual_seed(0)
+    B, S, H, D = 1, 8, 2, 4
+    q, k1, k2, v1, v2 = (torch.randn(B, S, H, D) for _ in range(5))
+
+    def block(k, v):
+        s = torch.einsum("bqhd,bkhd->bhqk", q, k) / math.sqrt(D)
+        return torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), v), torch.logsumexp(s, -1)
+    o1, l1 = block(k1, v1)
+    o2, l2 = block(k2, v2)
+    out, lse = update_out_and_lse(None, None, o1, l1)
+    out, lse = update_out_and_lse(out, lse, o2, l2)
+    o_ref, l_ref = block(torch.cat([k1, k2], 1), torch.cat([v1, v2], 1))
+    assert torch.allclose(out, o_ref, atol=1e-5) and torch.allclose(lse.squeeze(-1).transpose(1, 2), l_ref, atol=1e-5)
+    half = (slice(None), slice(0, 4))
+    out2, lse2 = update_out_and_lse(o1.clone(), l1.transpose(1, 2).unsqueeze(-1).clone(), o2[:, :4], l2[:, :, :4], slice_=half)
+    assert torch.allclose(out2[:, :4], o_ref[:, :4], atol=1e-5) and torch.allclose(out2[:, 4:], o1[:, 4:])
+    cu = [0, 3, 8]
+    padded = torch.randn(2, H, 5)
+    flat = flatten_varlen_lse(padded, cu)
+    assert flat.shape == (H, 8) and torch.equal(flat[:, :3], padded[0, :, :3])
+    back = unflatten_varlen_lse(flat.t().unsqueeze(-1), cu, 5)
+    assert torch.equal(back[0, :, :3], padded[0, :, :3]) and torch.equal(back[1], padded[1])
+    plan = DU.create_plan_for_full(4, 2, 0)
+    path = DU.write_plan(plan, str(tmp_path))
+    assert os.path.exists(path) and os.path.exists(path[:-4] + ".json")
+    full, causal = DU.split_dense_configs([WP._causal_config(2), P.BSA_Config.create_full((2, 1))])
+    assert len(full) == 1 and len(causal) == 1
+    al = WP.ILP(2)
+    assert al["table"].tolist()[0][0] == 0 and al["table"][1, 1] == 1

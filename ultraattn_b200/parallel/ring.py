@@ -376,3 +376,48 @@ def deepspeed_ulysses_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, caus
     missing, head_parallel_attn/deepspeed_ulysses_attn.py:43-47.)"""
     assert dropout_p == 0.0 and alibi_slopes is None
     return _UlyssesFunc.apply(q, k, v, softmax_scale, causal, group)
+
+
+# -------------------------------------------------------------------------------------------------
+# helper functions with the reference's names (ring_flash_attn/utils.py:38-121). The strategies
+# above do not need them (the kernels merge in their epilogue and work on packed layouts); they
+# serve code written against the reference.
+# -------------------------------------------------------------------------------------------------
+def update_out_and_lse(out, lse, block_out, block_lse, slice_=None):
+    """Merge a block's ``(block_out [B, S, H, D], block_lse [B, H, S])`` into the running
+    ``(out [B, S, H, D], lse [B, S, H, 1])`` with the log-sum-exp rule; the first call (``out`` is
+    None) adopts the block. ``slice_`` restricts the update to part of the running state. Unlike
+    the reference's formula, rows where either side is empty (lse = -inf) stay finite."""
+    blse = block_lse.transpose(-2, -1).unsqueeze(-1).float()
+    if out is None:
+        if slice_ is not None:
+            raise RuntimeError("first update_out_and_lse should not pass slice_ args")
+        return block_out, blse
+    o_run, l_run = (out, lse) if slice_ is None else (out[slice_], lse[slice_])
+    new = torch.logaddexp(l_run, blse)
+    safe = new.masked_fill(new == float("-inf"), 0.0)
+    w_old = torch.where(torch.isfinite(l_run), torch.exp(l_run - safe), torch.zeros_like(new))
+    w_new = torch.where(torch.isfinite(blse), torch.exp(blse - safe), torch.zeros_like(new))
+    merged = (w_old * o_run.float() + w_new * block_out.float()).to(o_run.dtype)
+    if slice_ is None:
+        return merged, new
+    out[slice_], lse[slice_] = merged, new
+    return out, lse
+
+
+def flatten_varlen_lse(lse: torch.Tensor, cu_seqlens) -> torch.Tensor:
+    """Padded ``[n_seq, heads, max_len]`` -> packed ``[heads, total_tokens]``."""
+    cu = [int(c) for c in cu_seqlens]
+    return torch.cat([lse[i, :, :b - a] for i, (a, b) in enumerate(zip(cu[:-1], cu[1:]))], dim=1)
+
+
+def unflatten_varlen_lse(lse: torch.Tensor, cu_seqlens, max_seqlen: int) -> torch.Tensor:
+    """Packed ``[total_tokens, heads, 1]`` (or ``[total_tokens, heads]``) -> padded
+    ``[n_seq, heads, max_seqlen]``; the padding is zero."""
+    cu = [int(c) for c in cu_seqlens]
+    if lse.dim() == 3:
+        lse = lse.squeeze(-1)
+    out = torch.zeros(len(cu) - 1, max_seqlen, lse.shape[1], dtype=torch.float32, device=lse.device)
+    for i, (a, b) in enumerate(zip(cu[:-1], cu[1:])):
+        out[i, :b - a] = lse[a:b]
+    return out.transpose(1, 2).contiguous()

@@ -95,3 +95,33 @@ def create_plan_for_full(CP: int, X: int, fob: int, m_config: Machine_Config = N
     sched = Dist_Attn_Schedule(da, m_config, (CP, CP, 1, 1), np.arange(CP)[None, :], table[None, None])
     g = Dependent_Graph(sched, fob, seqlen_variable_graph=svg)
     return Execution_Plan(g, fob, "manual", X=X, first_dim=first_dim)
+
+
+def write_plan(execute_plan: Execution_Plan, prefix: str) -> str:
+    """Store a plan as ``<prefix>/<plan name>.pkl`` with its JSON side-car next to it and read it
+    back as a check (reference: search_algo/dense_utils.py:53-62). Returns the pickle's path."""
+    import os
+    import pickle
+    os.makedirs(prefix, exist_ok=True)
+    path = os.path.join(prefix, execute_plan.get_plan_name() + ".pkl")
+    with open(path, "wb") as f:
+        pickle.dump(execute_plan, f)
+    execute_plan.to_json(path[:-4] + ".json")
+    with open(path, "rb") as f:
+        assert pickle.load(f).get_plan_name() == execute_plan.get_plan_name()
+    return path
+
+
+def split_dense_configs(dense_configs: list) -> tuple:
+    """(full configs, causal configs) of a list of dense one-block patterns."""
+    full, causal = [], []
+    for c in dense_configs:
+        tab = c.bsa_repr.table
+        assert tab.shape == (1, 1), "dense patterns coarsen to a single block"
+        if tab[0, 0] == 1:
+            full.append(c)
+        elif tab[0, 0] == 2:
+            causal.append(c)
+        else:
+            raise ValueError("an empty pattern is not a dense configuration")
+    return full, causal
