@@ -96,20 +96,20 @@ def test_varlen_baselines_world2(kind, causal):
         assert ret[r] < 2e-4, (r, ret[r])
 
 
-def _hierarchy_worker(rank, world, port, causal, ret):
+def _hierarchy_worker(rank, world, port, causal, ret, mode="kv", per_node=2, S=256):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         from ultraattn_b200 import parallel as PL, patterns as P
-        S, H, D = 256, 2, 16
+        H, D = 2, 16
         g = torch.Generator().manual_seed(4)
         q, k, v, d_o = (torch.randn(1, S, H, D, generator=g) for _ in range(4))
         kind = "zigzag" if causal else "ring"
         sh = lambda t: PL.shard_sequence(t, rank, world, kind)
-        groups = PL.create_hierarchy_groups(tasks_per_node=2)          # 2 nodes x 2 devices
+        groups = PL.create_hierarchy_groups(tasks_per_node=per_node)
         ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
-        o = PL.hierarchy_attn_func(ql, kl, vl, causal=causal, groups=groups)
+        o = PL.hierarchy_attn_func(ql, kl, vl, causal=causal, groups=groups, mode=mode)
         o.backward(sh(d_o))
         pat = P.causal(1) if causal else P.full(1)
         o_ref, _, dq, dk, dv = P.dense_attention_with_grads(q, k, v, d_o, pat)
@@ -122,11 +122,11 @@ def _hierarchy_worker(rank, world, port, causal, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("causal", [True, False])
-def test_two_level_ring_2x2(causal):
-    port = 29600 + (os.getpid() + int(causal)) % 90
+@pytest.mark.parametrize("causal,mode", [(True, "kv"), (False, "kv"), (True, "qo"), (False, "qo")])
+def test_two_level_ring_2x2(causal, mode):
+    port = 29600 + (os.getpid() + int(causal) + 2 * (mode == "qo")) % 90
     ret = mp.Manager().dict()
-    mp.spawn(_hierarchy_worker, args=(4, port, causal, ret), nprocs=4, join=True)
+    mp.spawn(_hierarchy_worker, args=(4, port, causal, ret, mode), nprocs=4, join=True)
     for r in range(4):
         assert isinstance(ret[r], float), ret[r]
         assert ret[r] < 2e-4, (r, ret[r])
@@ -196,5 +196,17 @@ def test_lightseq_attention_world4():
     ret = mp.Manager().dict()
     mp.spawn(_lightseq_worker, args=(4, port, ret), nprocs=4, join=True)
     for r in range(4):
+        assert isinstance(ret[r], float), ret[r]
+        assert ret[r] < 2e-4, (r, ret[r])
+
+
+@pytest.mark.parametrize("mode", ["kv", "qo"])
+def test_two_level_ring_3_nodes(mode):
+    """Three nodes of two ranks: the query / output exchange visits two other nodes (the second
+    visitor is requested while the first is computed)."""
+    port = 29500 + (os.getpid() + (mode == "qo")) % 90
+    ret = mp.Manager().dict()
+    mp.spawn(_hierarchy_worker, args=(6, port, True, ret, mode, 2, 240), nprocs=6, join=True)
+    for r in range(6):
         assert isinstance(ret[r], float), ret[r]
         assert ret[r] < 2e-4, (r, ret[r])

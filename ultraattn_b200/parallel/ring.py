@@ -91,16 +91,19 @@ class _Route:
     ``inter_rank * len(intra) + intra_rank`` orders the sequence shards.
     """
 
-    def __init__(self, group=None, intra=None, inter=None):
+    def __init__(self, group=None, intra=None, inter=None, offset: int = 0):
+        """``offset`` is added to every ring position (a ring that is one node of a larger job
+        reports job-wide positions to the mask rules)."""
         self.levels = [group] if intra is None else [intra, inter]
         self.sizes = [dist.get_world_size(g) for g in self.levels]
         self.pos = [dist.get_rank(g) for g in self.levels]
         self.world = math.prod(self.sizes)
+        self.offset = offset
         self.rank = self._flat(self.pos)
         self.shift = [0] * len(self.levels)
 
     def _flat(self, pos):
-        r, mul = 0, 1
+        r, mul = self.offset, 1
         for p, n in zip(pos, self.sizes):
             r, mul = r + p * mul, mul * n
         return r
@@ -145,17 +148,20 @@ class _Route:
 
 def _route(group):
     if isinstance(group, _Route):
+        group.shift = [0] * len(group.levels)
         return group
     if isinstance(group, dict):
         return _Route(intra=group["intra"], inter=group["inter"])
     return _Route(group)
 
 
-def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None, bounds=None):
+def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None, bounds=None, q_rank=None):
     """``group``: a process group (flat ring) or ``{'intra': pg, 'inter': pg}`` (two-level ring).
-    ``bounds``: (start, end) of every packed sequence in this rank's shard; default one sequence."""
+    ``bounds``: (start, end) of every packed sequence in this rank's shard; default one sequence.
+    ``q_rank``: ring position of the rank that owns the queries, when they are a visitor's."""
     set_comm_phase("fwd")
     route = _route(group)
+    q_rank = route.rank if q_rank is None else q_rank
     comms = route.comms()
     k, v = k.contiguous(), v.contiguous()        # they are sent as whole messages
     S = q.shape[1]
@@ -169,7 +175,7 @@ def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None, bo
             lvl = route.level_after(step)
             nk, nv = comms[lvl].send_recv(k), comms[lvl].send_recv(v)
             comms[lvl].commit()
-        work = _work(kind, route.src, route.rank, bounds, causal)
+        work = _work(kind, route.src, q_rank, bounds, causal)
         if work:
             A.attn_fwd([q], [k], [v], [(o, lse)], A.FwdPlan(_fwd_rows(work, started), q.device), softmax_scale)
             started = True
@@ -180,9 +186,12 @@ def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None, bo
     return o, lse
 
 
-def ring_backward(d_o, q, k, v, o, lse, group, kind: str, causal: bool, softmax_scale=None, bounds=None):
+def ring_backward(d_o, q, k, v, o, lse, group, kind: str, causal: bool, softmax_scale=None, bounds=None,
+                  q_rank=None, keep_f32: bool = False):
+    """``keep_f32``: return the fp32 accumulators instead of casting to the input dtype."""
     set_comm_phase("bwd")
     route = _route(group)
+    q_rank = route.rank if q_rank is None else q_rank
     kv_comms, g_comms = route.comms(), route.comms()
     k, v = k.contiguous(), v.contiguous()
     B, S, H, D = q.shape
@@ -200,7 +209,7 @@ def ring_backward(d_o, q, k, v, o, lse, group, kind: str, causal: bool, softmax_
             lvl = route.level_after(step)
             nk, nv = kv_comms[lvl].send_recv(k), kv_comms[lvl].send_recv(v)
             kv_comms[lvl].commit()
-        work = _work(kind, route.src, route.rank, bounds, causal)
+        work = _work(kind, route.src, q_rank, bounds, causal)
         if work:
             A.attn_bwd([side], [k], [v], [A.BwdKvOut(dk, dv)], A.BwdPlan(_bwd_cols(work), q.device),
                        softmax_scale)
@@ -213,6 +222,8 @@ def ring_backward(d_o, q, k, v, o, lse, group, kind: str, causal: bool, softmax_
             route.advance(lvl)
             k, v, dk, dv = nk, nv, ndk, ndv
     dk, dv = route.send_home([dk, dv])
+    if keep_f32:
+        return dq, dk, dv
     return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
 
 
