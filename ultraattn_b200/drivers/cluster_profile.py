@@ -53,14 +53,24 @@ def _setup(sq, skv, nh, causal, dev):
     return fwd, bwd
 
 
-def profile_kernels(out_dir: Path, quick: bool) -> Path:
+def profile_kernels(out_dir: Path, quick: bool, max_seconds: float = 0.0) -> Path:
     """Tile grid: Smin in 256..64k, Sq/Skv ratios p/q with max(p, q) <= 8, full and causal,
-    Nh in {1, 32}. Writes ``time_b200_flash_all.json``."""
+    Nh in {1, 32}. Writes ``time_b200_flash_all.json`` (rewritten after every few shapes, so an
+    interrupted run keeps what it measured; ``max_seconds`` > 0 stops the sweep cleanly). Shapes
+    run smallest first within each head count, and 32 heads before 1 (the planner's configs)."""
+    import time
     dev = torch.device("cuda")
     sizes = [256, 1024, 4096, 16384] if quick else [256 << i for i in range(9)]
     ratios = ["1/1", "2/1", "1/2"] if quick else ["1/1", "2/1", "1/2", "4/1", "1/4", "8/1", "1/8", "3/1", "1/3"]
     rows = []
-    for nh in ([32] if quick else [1, 32]):
+    out_dir.mkdir(parents=True, exist_ok=True)
+    path = out_dir / "time_b200_flash_all.json"
+    t_start = time.time()
+
+    def flush():
+        path.write_text(json.dumps({"flash_attn": rows}, indent=1))
+
+    for nh in ([32] if quick else [32, 1]):
         for smin in sizes:
             for ratio in ratios:
                 p, q_ = (int(x) for x in ratio.split("/"))
@@ -68,15 +78,19 @@ def profile_kernels(out_dir: Path, quick: bool) -> Path:
                 if max(sq, skv) > 131072 or sq * skv * nh > (1 << 38):
                     continue
                 for causal in ([False, True] if ratio == "1/1" else [False]):
+                    if max_seconds and time.time() - t_start > max_seconds:
+                        flush()
+                        return path
                     fwd, bwd = _setup(sq, skv, nh, causal, dev)
-                    tf, tb = _time(fwd), _time(bwd)
+                    big = sq * skv * nh >= (1 << 34)
+                    tf, tb = _time(fwd, 3 if big else 5, 1 if big else 2), _time(bwd, 3 if big else 5, 1 if big else 2)
                     fl = 4.0 * sq * skv * 128 * nh * (0.5 if causal else 1.0)
                     rows.append([[smin, 1, nh, 128, ratio, causal],
                                  [tf * 1e6, tb * 1e6, fl / tf / 1e12, 2.5 * fl / tb / 1e12]])
                     print(rows[-1], flush=True)
-    out_dir.mkdir(parents=True, exist_ok=True)
-    path = out_dir / "time_b200_flash_all.json"
-    path.write_text(json.dumps({"flash_attn": rows}, indent=1))
+                    if len(rows) % 8 == 0:
+                        flush()
+    flush()
     return path
 
 
@@ -171,6 +185,7 @@ def main() -> None:
     ap.add_argument("--comm", action="store_true")
     ap.add_argument("--out", default="logs/m_configs")
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--max-seconds", type=float, default=0.0, help="(--kernels) stop the sweep after this long")
     ap.add_argument("--one", choices=["fwd", "bwd", "gemm", "ops"], default=None)
     ap.add_argument("--S", type=int, default=16384)
     ap.add_argument("--Nh", type=int, default=32)
@@ -197,7 +212,7 @@ def main() -> None:
                           "tflops": fl / t / 1e12}))
         return
     if a.kernels:
-        print(profile_kernels(Path(a.out), a.quick))
+        print(profile_kernels(Path(a.out), a.quick, a.max_seconds))
     if a.comm:
         profile_comm(Path(a.out), a.quick)
 
