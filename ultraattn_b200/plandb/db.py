@@ -32,9 +32,7 @@ from typing import Optional
 
 import numpy as np
 
-from ..planner.cost import (Comm_Profile_Map, FlashAttn_Profile_Map, Inter_Comp_Profile_Map,
-                            Machine_Config, convert_profile_data_to_comm_map,
-                            convert_shape_config_to_str, load_flash_profile)
+from ..planner.cost import Machine_Config, convert_shape_config_to_str
 
 ABLATION_SUFFIXES = [
     "_ablation=(w/o_gpu_tile,w/o_kernel_tile,Flexflow)",
@@ -109,13 +107,9 @@ class Prof_DB:
         """Read ``time*.json`` / ``cb_8_*.log`` / ``cb_16_*.log`` if present; parts that are missing
         fall back to the analytic B200 model."""
         mdir = Path(self.M_CONFIG_DIR)
-        flash = sorted(mdir.glob("time*.json"))
-        cb8 = sorted(mdir.glob("cb_8_*.log"))
-        cb16 = sorted(mdir.glob("cb_16_*.log"))
-        comp_intra = FlashAttn_Profile_Map(load_flash_profile(flash[0]) if flash else None)
-        comm_intra = Comm_Profile_Map(convert_profile_data_to_comm_map(cb8[0]) if cb8 else None)
-        comm_inter = Comm_Profile_Map(convert_profile_data_to_comm_map(cb16[0]) if cb16 else None)
-        return Machine_Config(None, [Inter_Comp_Profile_Map(), comp_intra], [comm_inter, comm_intra])
+        if not any(mdir.glob("time*.json")) and not any(mdir.glob("cb_*.log")):
+            return Machine_Config.b200_default()        # nothing profiled here: the packaged profile
+        return Machine_Config.from_dir(mdir)
 
     def m_config_update_inter_bsa_profile(self) -> None:
         self.m_config.update_inter_bsa_profile(self._load(self.INTRA_BSA_EXE_PLANS_PROFILE))

@@ -34,6 +34,7 @@ B200_BWD_TFLOPS = 1100.0
 B200_NVLINK_GBS = 770.0          # peer copy, per direction
 B200_LINK_LATENCY_S = 4e-6
 B200_LAUNCH_S = 6e-6
+PACKAGED_M_CONFIG_DIR = Path(__file__).resolve().parents[1] / "data" / "m_configs" / "B200"
 
 
 def convert_shape_config_to_str(shape_config: dict) -> str:
@@ -279,7 +280,24 @@ class Machine_Config:
 
     @classmethod
     def b200_default(cls) -> "Machine_Config":
-        return cls()
+        """The machine profile shipped with the package (``data/m_configs/B200``: the kernel grid
+        measured on a B200 with this repository's kernels, in the reference's ``time*.json``
+        format, and link curves when present); shapes outside the measured grid use the analytic
+        model."""
+        return cls.from_dir(PACKAGED_M_CONFIG_DIR)
+
+    @classmethod
+    def from_dir(cls, m_config_dir) -> "Machine_Config":
+        """Read ``time*.json`` / ``cb_8_*.log`` / ``cb_16_*.log`` of a directory; what is missing
+        falls back to the analytic B200 model."""
+        mdir = Path(m_config_dir)
+        flash = sorted(mdir.glob("time*.json")) if mdir.is_dir() else []
+        cb8 = sorted(mdir.glob("cb_8_*.log")) if mdir.is_dir() else []
+        cb16 = sorted(mdir.glob("cb_16_*.log")) if mdir.is_dir() else []
+        comp_intra = FlashAttn_Profile_Map(load_flash_profile(flash[0]) if flash else None)
+        comm_intra = Comm_Profile_Map(convert_profile_data_to_comm_map(cb8[0]) if cb8 else None)
+        comm_inter = Comm_Profile_Map(convert_profile_data_to_comm_map(cb16[0]) if cb16 else None)
+        return cls(None, [Inter_Comp_Profile_Map(), comp_intra], [comm_inter, comm_intra])
 
     def update_inter_bsa_profile(self, profile: dict) -> None:
         self.comp_profile_maps[0].update(profile)
