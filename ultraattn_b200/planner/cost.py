@@ -33,7 +33,7 @@ B200_FWD_TFLOPS = 1050.0
 B200_BWD_TFLOPS = 1100.0
 B200_NVLINK_GBS = 770.0          # peer copy, per direction
 B200_LINK_LATENCY_S = 4e-6
-B200_LAUNCH_S = 6e-6
+B200_LAUNCH_S = 3e-5            # per-launch floor seen when tiles are tiny (host launch path included)
 PACKAGED_M_CONFIG_DIR = Path(__file__).resolve().parents[1] / "data" / "m_configs" / "B200"
 
 
