@@ -93,3 +93,44 @@ def test_fusion_table_and_full_plan_generation(tmp_path, capsys):
     assert len(keys) == 6 and "fob=1_CP=(4, 1)_shape_config=full_ablation=(Y=2,X=2,dim=0)" in keys
     plan = db.get_plan(keys[0], 1)
     assert plan.verify() == [] and intra_attn_gen.generate(db, 4, (0, 1)) == keys
+
+
+_YAML = """
+Parallel:
+  SP: [1, 2]
+Shape: {Sq: 512, Skv: 512, Nhq: 2, Nhkv: 2, BS: 1, D: 16}
+Pattern: {pattern_type: stream, n_blocks: 4, global_blocks: 1, local_blocks: 2}
+Experiment: {transform_mode: greedy, lowering_mode: ILP}
+"""
+
+
+def _main_worker(rank, world, port, cfg_path, out_dir):
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    from ultraattn_b200.drivers import main as M
+    sys.stdout = open(os.path.join(out_dir, f"rank{rank}.out"), "w")
+    rc = M.main(["--config", cfg_path, "--iters", "1", "--time-limit", "3"])
+    sys.stdout.flush()
+    assert rc == 0
+
+
+def test_single_configuration_driver(tmp_path, capsys):
+    """YAML -> plan -> description (plan only), and the same configuration executed and timed on
+    two gloo ranks."""
+    import json
+    import os
+    import torch.multiprocessing as mp
+    from ultraattn_b200.drivers import main as M
+    cfg = tmp_path / "stream.yaml"
+    cfg.write_text(_YAML)
+    assert M.main(["--config", str(cfg), "--plan-only", "--time-limit", "3", "--save-plan", str(tmp_path / "plans")]) == 0
+    recs = [json.loads(line) for line in capsys.readouterr().out.strip().splitlines()]
+    assert [r["fob"] for r in recs] == [0, 1] and all(r["problems"] == [] and r["sim_time_ms"] > 0 for r in recs)
+    assert all(os.path.exists(r["plan_file"]) for r in recs)
+    mp.spawn(_main_worker, args=(2, 29150 + os.getpid() % 40, str(cfg), str(tmp_path)), nprocs=2, join=True)
+    lines = [json.loads(line) for line in (tmp_path / "rank0.out").read_text().strip().splitlines()]
+    timed = [r for r in lines if "time_ms" in r]
+    assert [r["fob"] for r in timed] == [0, 1] and all(r["time_ms"] > 0 and r["n_ranks"] == 2 for r in timed)
