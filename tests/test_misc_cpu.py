@@ -316,3 +316,13 @@ def test_ring_utils_and_dense_helpers(tmp_path):
     assert len(full) == 1 and len(causal) == 1
     al = WP.ILP(2)
     assert al["table"].tolist()[0][0] == 0 and al["table"][1, 1] == 1
+
+
+def test_start_gate_is_a_no_op_on_cpu():
+    from ultraattn_b200.drivers.benchmark import benchmark_ops
+    from ultraattn_b200.ops.gate import StartGate
+    g = StartGate("cpu")
+    g.close()
+    g.open()
+    assert g.check() and g.epoch == 1 and int(g.flag[0]) == 1
+    assert benchmark_ops(lambda: None, warmup=1, num_iter=2, repeats=1, device=torch.device("cpu"), start_gate=True) >= 0

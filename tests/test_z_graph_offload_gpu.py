@@ -90,3 +90,35 @@ def test_offloaded_checkpoint_on_gpu(dev):
     lin.weight.grad = None
     OffloadedCheckpoint.apply(layer, x, 2.0).sum().backward()
     assert torch.allclose(x.grad, gx, atol=1e-5) and torch.allclose(lin.weight.grad, gw, atol=1e-3, rtol=1e-4)
+
+
+def test_start_gate_holds_and_releases_the_stream(dev):
+    """Work queued behind a closed gate does not run until the host opens it; the timing harness
+    with the gate gives a sane number; a gate that is never opened gives up after its budget."""
+    import time
+    from ultraattn_b200.drivers.benchmark import benchmark_ops
+    from ultraattn_b200.ops import attention as A
+    from ultraattn_b200.ops.gate import StartGate
+    A.status_buffer(dev).zero_()
+    gate = StartGate(dev, budget_s=3.0)
+    x = torch.zeros(1024, device=dev)
+    torch.cuda.synchronize(dev)
+    gate.close()
+    x.add_(1)
+    done = torch.cuda.Event()
+    done.record()
+    time.sleep(0.05)
+    assert not done.query(), "the kernel behind the gate ran before the gate was opened"
+    gate.open()
+    torch.cuda.synchronize(dev)
+    assert gate.check() and x.sum().item() == 1024
+    A.check_status(dev)
+    y = torch.randn(1 << 20, device=dev)
+    t = benchmark_ops(lambda: y.mul_(1.0001), warmup=2, num_iter=20, repeats=2, device=dev, start_gate=True)
+    assert 0 < t < 1e-2
+    A.check_status(dev)
+    short = StartGate(dev, budget_s=0.1)
+    short.close()
+    torch.cuda.synchronize(dev)                       # never opened: returns after its budget
+    assert not short.check() and short.timed_out
+    A.check_status(dev)                               # and leaves no error behind

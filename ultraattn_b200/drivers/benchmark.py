@@ -3,7 +3,11 @@
 ``benchmark_ops`` times a callable: warm-up, then ``num_iter`` calls bracketed by CUDA events on the
 launching stream (wall clock on CPU ranks), repeated ``repeats`` times, last value kept, MAX over
 ranks. The reference lines the ranks up with an 8 GiB NCCL all-reduce before each timing
-(benchmark.py:593-594); a barrier plus device synchronisation does the same job here.
+(benchmark.py:593-594) so that the CPU can queue the kernels ahead of the GPU; a barrier plus
+device synchronisation lines the ranks up here, and ``start_gate=True`` adds the run-ahead: the
+stream is held at a bounded device-side wait (:class:`ultraattn_b200.ops.gate.StartGate`) while
+the calls are queued, then released, so launch latency stays out of the measurement of short
+kernels.
 Optional torch.profiler -> TensorBoard traces follow the reference's schedule (wait 4, warm-up 4,
 active 12).
 """
@@ -20,9 +24,13 @@ from ..utils.misc import calc_flops
 
 def benchmark_ops(fn: Callable[[], object], warmup: int = 3, num_iter: int = 4, repeats: int = 3,
                   device: Optional[torch.device] = None, group=None, tb_dir: Optional[str] = None,
-                  trace_name: str = "trace") -> float:
+                  trace_name: str = "trace", start_gate: bool = False) -> float:
     """Seconds per call, max over the ranks of ``group``."""
     cuda = device is not None and device.type == "cuda"
+    gate = None
+    if start_gate and cuda:
+        from ..ops.gate import StartGate
+        gate = StartGate(device)
 
     def sync():
         if dist.is_initialized():
@@ -48,11 +56,17 @@ def benchmark_ops(fn: Callable[[], object], warmup: int = 3, num_iter: int = 4, 
         sync()
         if cuda:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if gate is not None:
+                gate.close()
             e0.record()
             for _ in range(num_iter):
                 fn()
             e1.record()
+            if gate is not None:
+                gate.open()
             sync()
+            if gate is not None:
+                gate.check()
             td = e0.elapsed_time(e1) / 1e3 / num_iter
         else:
             t0 = time.perf_counter()
