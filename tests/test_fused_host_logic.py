@@ -12,19 +12,33 @@ from ultraattn_b200 import patterns as P
 from ultraattn_b200.runtime import FakeSpace, FusedContextParallel, plan_allocation
 
 
-def _run_all_ranks(pattern, world, S, H, D, allocation, seed=0, multicast=False, min_consumers=2):
+def _run_all_ranks(pattern, world, S, H, D, allocation, seed=0, multicast=False, min_consumers=2,
+                   nvls_reduce=False, steps=1):
     table, cmap = plan_allocation(pattern, world, 1, allocation, time_limit=5.0)
     if allocation == "lightseq":
         tiles = [int((table == r).sum()) for r in range(world)]
         assert max(tiles) - min(tiles) <= 1, tiles          # the point of the schedule: balance
     registry = {}
     ranks = [FusedContextParallel(table, cmap, pattern, S, H, D, FakeSpace(r, world, registry, multicast=multicast),
-                                  dtype=torch.float32, defer_build=True, nvls_min_consumers=min_consumers)
+                                  dtype=torch.float32, defer_build=True, nvls_min_consumers=min_consumers,
+                                  nvls_reduce=nvls_reduce)
              for r in range(world)]
     if multicast:
         assert ranks[0].bc_cols, "the pattern was chosen to have one-to-many blocks"
     for rk in ranks:
         rk.build()
+    if nvls_reduce:
+        from ultraattn_b200.runtime.verify import verify_fused_tables
+        assert all(rk.nvls_reduce for rk in ranks) and verify_fused_tables(ranks) == []
+        # the owners' dK/dV of broadcast blocks no longer arrive as per-consumer reductions
+        assert sum(rk.traffic["bwd_reduce_in_bytes"] for rk in ranks) > 0
+    worst = 0.0
+    for step in range(steps):
+        worst = max(worst, _one_step(ranks, pattern, world, S, H, D, seed + step))
+    return worst, table
+
+
+def _one_step(ranks, pattern, world, S, H, D, seed):
     g = torch.Generator().manual_seed(seed)
     q, k, v, d_o = (torch.randn(1, S, H, D, generator=g) for _ in range(4))
     blk = S // ranks[0].par_d
@@ -58,7 +72,7 @@ def _run_all_ranks(pattern, world, S, H, D, allocation, seed=0, multicast=False,
                     (grads[r][2] - dv_ref[:, idx[r]]).abs().max().item())
         fin = torch.isfinite(lse_ref[:, :, idx[r]])
         worst = max(worst, (outs[r][1][fin] - lse_ref[:, :, idx[r]][fin]).abs().max().item())
-    return worst, table
+    return worst
 
 
 @pytest.mark.parametrize("name,pattern,world,alloc", [
@@ -85,6 +99,20 @@ def test_fused_host_logic_with_multicast_blocks(name, pattern, world, alloc, min
     """Blocks that several ranks need are broadcast by their owner (emulated multicast store)
     instead of being pulled by every consumer; results must not change."""
     err, table = _run_all_ranks(pattern(), world, 512, 2, 16, alloc, multicast=True, min_consumers=minc)
+    assert err < 2e-4, (err, table)
+
+
+@pytest.mark.parametrize("name,pattern,world,alloc,minc", [
+    ("global-local-4", lambda: P.global_local(8, 1, 2), 4, "ilp", 2),
+    ("star-4", lambda: P.star(8, 1), 4, "naive", 2),
+    ("causal-2-forced", lambda: P.causal(1), 2, "naive", 1),
+], ids=lambda x: x if isinstance(x, str) else None)
+def test_fused_host_logic_with_in_switch_gradient_sum(name, pattern, world, alloc, minc):
+    """dK/dV of broadcast blocks: every rank adds into its own replica of the reduction buffer and
+    the owner takes the sum over replicas (emulated multimem.ld_reduce). Two steps, so that stale
+    contents of the replicas would show."""
+    err, table = _run_all_ranks(pattern(), world, 512, 2, 16, alloc, multicast=True, min_consumers=minc,
+                                nvls_reduce=True, steps=2)
     assert err < 2e-4, (err, table)
 
 

@@ -79,14 +79,16 @@ class ContextParallelAttention:
                  group=None, device: Optional[torch.device] = None, path: str = "fused",
                  n_kv_heads: Optional[int] = None, batch: int = 1, allocation: str = "ilp",
                  plan_time_limit: float = 20.0, dtype=torch.bfloat16, cmap=None,
-                 nvls_min_consumers: int = 2, plan=None, local_groups: bool = False):
+                 nvls_min_consumers: int = 2, plan=None, local_groups: bool = False,
+                 nvls_reduce: Optional[bool] = None):
         """``plan``: an earlier runtime's ``(table, cmap)`` to reuse instead of solving the
         allocation again (fused path; e.g. a second runtime for a different number of heads).
         ``local_groups``: create the internal process groups with only the members of ``group``
         taking part (needed when ``group`` is a strict subset of the job, as after a rank left)."""
         self._ctor = dict(seq_len=seq_len, n_heads=n_heads, head_dim=head_dim, device=device, path=path,
                           n_kv_heads=n_kv_heads, batch=batch, allocation=allocation,
-                          plan_time_limit=plan_time_limit, dtype=dtype, nvls_min_consumers=nvls_min_consumers)
+                          plan_time_limit=plan_time_limit, dtype=dtype, nvls_min_consumers=nvls_min_consumers,
+                          nvls_reduce=nvls_reduce)
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
@@ -104,7 +106,7 @@ class ContextParallelAttention:
             space = SymmMemSpace(self.group, self.device)
             self.impl = FusedContextParallel(table, cm, pattern, seq_len, n_heads, head_dim, space,
                                              n_kv_heads, batch, dtype, self.device,
-                                             nvls_min_consumers=nvls_min_consumers)
+                                             nvls_min_consumers=nvls_min_consumers, nvls_reduce=nvls_reduce)
         elif path == "nccl":
             from .executor import PlanExecutor
             kw = dict(pattern=pattern, cp=self.world, seq_len=seq_len, n_heads=n_heads, head_dim=head_dim,

@@ -69,6 +69,12 @@ class PeerSpace:
         indices / slices selecting a contiguous piece)."""
         raise NotImplementedError
 
+    def multicast_reduce(self, name: str, index, dst: torch.Tensor) -> None:
+        """dst = sum over all ranks of replica[index] of buffer ``name`` (fp32), computed inside
+        the switch (``multimem.ld_reduce``): the owner receives one block however many ranks
+        contributed."""
+        raise NotImplementedError
+
 
 class FakeSpace(PeerSpace):
     """All ranks in one process on CPU; ``peer`` hands out the other rank's tensor itself."""
@@ -82,6 +88,9 @@ class FakeSpace(PeerSpace):
     def multicast_store(self, name, index, src):
         for r in range(self.world):
             self.registry[(r, name)][index].copy_(src)
+
+    def multicast_reduce(self, name, index, dst):
+        dst.copy_(sum(self.registry[(r, name)][index].to(torch.float32) for r in range(self.world)))
 
     def alloc(self, name, shape, dtype):
         t = torch.zeros(*shape, dtype=dtype, device=self.device)
@@ -156,6 +165,12 @@ class SymmMemSpace(PeerSpace):
         off = dst.data_ptr() - self.local(name).data_ptr()
         E.multimem_bcast_(self.multicast_ptr(name) + off, src.contiguous())
 
+    def multicast_reduce(self, name, index, dst):
+        src = self.local(name)[index]
+        assert src.is_contiguous() and dst.is_contiguous() and src.dtype == dst.dtype == torch.float32
+        off = src.data_ptr() - self.local(name).data_ptr()
+        E.multimem_reduce(self.multicast_ptr(name) + off, dst, src.numel() * 4, torch.float32, self.device)
+
     def barrier(self, channel: int) -> None:
         """Device barrier on the current stream (bounded wait; errors land in the status word)."""
         ep = self.epochs.get(channel, 0) + 1
@@ -175,9 +190,14 @@ class FusedContextParallel:
     def __init__(self, table: np.ndarray, cmap: np.ndarray, pattern: BSA_Repr, seq_len: int,
                  n_heads: int, head_dim: int, space: PeerSpace, n_kv_heads: Optional[int] = None,
                  batch: int = 1, dtype=torch.bfloat16, device=None, defer_build: bool = False,
-                 nvls_min_consumers: int = 2):
+                 nvls_min_consumers: int = 2, nvls_reduce: Optional[bool] = None):
+        """``nvls_reduce``: deliver dK/dV of the broadcast (one-to-many) key/value blocks by an
+        in-switch sum instead of one peer reduction per consumer: every rank adds its share into
+        its own replica of a symmetric buffer and the block's owner reads the sum of all replicas
+        with ``multimem.ld_reduce``. Default: the ``UA_NVLS_REDUCE=1`` environment switch (off)."""
         self.space = space
         self.nvls_min_consumers = nvls_min_consumers
+        self.nvls_reduce = (os.environ.get("UA_NVLS_REDUCE") == "1") if nvls_reduce is None else bool(nvls_reduce)
         self.rank, self.world = space.rank, space.world
         self.table = np.asarray(table)
         self.cmap = np.asarray(cmap)
@@ -252,7 +272,11 @@ class FusedContextParallel:
             "bwd_pull_bytes": nbytes(self.b_pieces),                    # dO / lse / D of foreign rows
             "bwd_pull_bytes_no_reuse": nbytes(self.b_pieces_full),
             "bwd_push_bytes": (len(self.remote_rows) * self.B * self.blk * self.H * self.D * 4      # dQ
-                               + len(self.remote_cols) * 2 * kv_blk * 4),                             # dK, dV
+                               + sum(1 for c in self.remote_cols
+                                     if not (self.nvls_reduce and c in self.bc_slot)) * 2 * kv_blk * 4),  # dK, dV
+            # dK / dV of broadcast blocks that this rank owns, summed in the switch: one block in
+            "bwd_reduce_in_bytes": (sum(1 for c in self.bc_cols if int(self.cmap[c]) == self.rank)
+                                    * 2 * kv_blk * 4 if self.nvls_reduce else 0),
         }
 
     def enable_trace(self, on: bool = True) -> None:
@@ -291,11 +315,15 @@ class FusedContextParallel:
             ("dq_acc", (B, S, H, D), torch.float32), ("dk_acc", (B, S, Hk, D), torch.float32),
             ("dv_acc", (B, S, Hk, D), torch.float32),
         ] + ([("bc_k", (B, len(self.bc_cols) * self.blk, Hk, D), dt),
-              ("bc_v", (B, len(self.bc_cols) * self.blk, Hk, D), dt)] if self.bc_cols else []):
+              ("bc_v", (B, len(self.bc_cols) * self.blk, Hk, D), dt)] if self.bc_cols else []) \
+          + ([("bc_dk", (B, len(self.bc_cols) * self.blk, Hk, D), torch.float32),
+              ("bc_dv", (B, len(self.bc_cols) * self.blk, Hk, D), torch.float32)]
+             if self.bc_cols and self.nvls_reduce else []):
             sp.alloc(name, shape, dtype)
         sp.finalize()
         if self.bc_cols and not sp.has_multicast():
             self.bc_cols, self.bc_slot = [], {}
+        self.nvls_reduce = self.nvls_reduce and bool(self.bc_cols)
         dev = self.device
         peers_rows = sorted({int(self.cmap[r]) for r in self.remote_rows})
         peers_cols = sorted({int(self.cmap[c]) for c in self.remote_cols})
@@ -444,7 +472,10 @@ class FusedContextParallel:
             kv_src[p] = len(kv_src)
         if self.bc_cols:
             kv_src["bc"] = len(kv_src)
+        if self.nvls_reduce:
+            kv_src["bcg"] = len(kv_src)         # gradient slot only: this rank's replica of bc_dk / bc_dv
         self.b_q_src, self.b_kv_src = q_src, kv_src
+        assert len(kv_src) <= 10 and len(q_src) <= 10, "too many source tensors for one launch"
         self.b_plans = []
         for cnt in (counts, counts_full):
             cols = []
@@ -461,6 +492,14 @@ class FusedContextParallel:
                                       (r + 1) if remote else 0, cnt.get(r, 0) if remote else 0))
                 kv_remote = pc != g
                 kv_cnt = cnt.get(self.par_d + c, 0)
+                if self.nvls_reduce and c in self.bc_slot:
+                    # gradients of a broadcast block go into this rank's own replica of the
+                    # reduction buffer (the owner's share too); the owner sums the replicas
+                    src = kv_src["bc"] if kv_remote else kv_src[pc]
+                    start = self.bc_slot[c] * self.blk if kv_remote else self.lidx[c] * self.blk
+                    cols.append(A.Col(src, start, self.blk, tuple(segs), kv_src["bcg"],
+                                      self.bc_slot[c] * self.blk, 0, 0))
+                    continue
                 if kv_remote and c in self.bc_slot:
                     # keys / values from the broadcast buffer, gradients into the owner's accumulators
                     cols.append(A.Col(kv_src["bc"], self.bc_slot[c] * self.blk, self.blk, tuple(segs),
@@ -590,6 +629,14 @@ class FusedContextParallel:
                 k_srcs[i], v_srcs[i] = sp.local("bc_k"), sp.local("bc_v")
                 outs[i] = A.BwdKvOut(sp.local("dk_acc"), sp.local("dv_acc"))     # never written through
                 continue
+            if p == "bcg":
+                k_srcs[i], v_srcs[i] = sp.local("bc_k"), sp.local("bc_v")        # never read through
+                # cleared here, after the barrier: the owner's read of the previous call precedes
+                # its arrival at that barrier
+                sp.local("bc_dk").zero_()
+                sp.local("bc_dv").zero_()
+                outs[i] = A.BwdKvOut(sp.local("bc_dk"), sp.local("bc_dv"))
+                continue
             k_srcs[i] = sp.local("k") if p == g else self.mir[("k", p)]
             v_srcs[i] = sp.local("v") if p == g else self.mir[("v", p)]
             outs[i] = A.BwdKvOut(sp.local("dk_acc") if p == g else sp.peer("dk_acc", p),
@@ -610,6 +657,14 @@ class FusedContextParallel:
 
     def bwd_finish(self):
         sp = self.space
+        if self.nvls_reduce:
+            for c in self.bc_cols:
+                if int(self.cmap[c]) != self.rank:
+                    continue
+                bs = slice(self.bc_slot[c] * self.blk, (self.bc_slot[c] + 1) * self.blk)
+                for b in range(self.B):
+                    sp.multicast_reduce("bc_dk", (b, bs), sp.local("dk_acc")[b, self._tok(c)])
+                    sp.multicast_reduce("bc_dv", (b, bs), sp.local("dv_acc")[b, self._tok(c)])
         outs = []
         for name, like in (("dq_acc", (self.B, self.S_loc, self.H, self.D)),
                            ("dk_acc", (self.B, self.S_loc, self.Hk, self.D)),

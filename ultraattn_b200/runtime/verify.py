@@ -90,8 +90,13 @@ def verify_fused_tables(ranks: Sequence) -> list:
                 src = bkv_of[col.kv_src]
                 owner = bkv_of[col.g_slot]
                 c = bc_block[col.kv_start // blk] if src == "bc" else rk.owned[src][col.kv_start // blk]
-                if owner != int(rk.cmap[c]) or col.g_start != rk.lidx[c] * blk:
+                if owner == "bcg":          # in-switch reduction: own replica, at the block's broadcast slot
+                    if c not in rk.bc_slot or col.g_start != rk.bc_slot[c] * blk:
+                        problems.append(f"rank {g}: dK/dV of block {c} go to reduction slot {col.g_start // blk}")
+                elif owner != int(rk.cmap[c]) or col.g_start != rk.lidx[c] * blk:
                     problems.append(f"rank {g}: dK/dV of block {c} go to rank {owner} at {col.g_start}")
+                elif rk.nvls_reduce and c in rk.bc_slot:
+                    problems.append(f"rank {g}: dK/dV of broadcast block {c} bypass the reduction buffer")
                 staged_kv = cnt.get(par_d + c, 0)
                 if src not in ("bc", g) and staged_kv and (col.kv_wait_flag != par_d + c + 1 or col.kv_wait_count != staged_kv):
                     problems.append(f"rank {g}: backward key block {c} is read without a matching wait")
