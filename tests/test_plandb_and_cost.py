@@ -125,3 +125,24 @@ def test_metrics_jsonl_and_roofline(tmp_path):
     recs = M.read_jsonl(tmp_path / "m" / "calls.jsonl")
     assert [x["name"] for x in recs] == ["fwd", "barrier"] and recs[0]["config"] == "strided"
     assert recs[0]["nvlink_push_bytes"] == 20 and 0 < recs[0]["fraction"] < 1 and "fraction" not in recs[1]
+
+
+def test_report_bar_chart_svg(tmp_path):
+    """The figure output: a well-formed SVG with one bar per measured variant and the speed-ups
+    over the ring baseline as labels."""
+    import json
+    import xml.etree.ElementTree as ET
+    from ultraattn_b200.drivers import report
+    pre = ("fob=0_CP=(8, 1)_shape_config={S=(524288, 524288)_Nh=(32, 32)_bs=1_D=128}"
+           "_bsa_config={CP=(8, 1)_repr=[[2]]}")
+    prof = {pre + "_ablation=(w/o_kernel_tile,Flexflow)": {"hfu": 1.0, "time": "2.500e-01", "sim_time": "0"},
+            pre + "_ring": {"hfu": 1.0, "time": "5.000e-01", "sim_time": "0"},
+            pre + "_zigzag": {"hfu": 1.0, "time": "2.000e-01", "sim_time": "0"}}
+    (tmp_path / "inter_bsa_exe_plans_profile.json").write_text(json.dumps(prof))
+    assert report.main(["--db", str(tmp_path), "--svg", str(tmp_path / "fig.svg")]) == 0
+    root = ET.fromstring((tmp_path / "fig.svg").read_text())
+    ns = "{http://www.w3.org/2000/svg}"
+    bars = [e for e in root.iter(ns + "rect") if e.get("class") == "bar"]
+    assert len(bars) == 4                               # ring, zigzag, node+device tile, UltraAttn
+    labels = [e.text for e in root.iter(ns + "text")]
+    assert "1.00" in labels and "2.50" in labels and "2.00" in labels and any("S=512k" in (t or "") for t in labels)

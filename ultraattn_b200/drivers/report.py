@@ -12,8 +12,8 @@ over the ring baseline and over the best baseline. The label mapping is the refe
 "+Kernel Tile" = min with ``(w_kernel_tile,Flexflow)``, "UltraAttn" = min over the four
 ``w/o|w_kernel_tile`` x ``Flexflow|ILP`` variants; baselines carry the suffixes ``_ring``,
 ``_zigzag``, ``_stripe``. Unlike the reference's plot scripts nothing is substituted when a
-baseline wins: the ratio is printed as measured. Figures need matplotlib, which this image does
-not ship; ``--csv`` gives the same numbers to any plotting tool.
+baseline wins: the ratio is printed as measured. ``--svg`` draws the speed-ups as a grouped bar chart without any plotting library (this image
+has no matplotlib); ``--csv`` gives the same numbers to any plotting tool.
 """
 from __future__ import annotations
 
@@ -122,6 +122,60 @@ def e2e_rows(rows: list, n_layers: int, time_wo_attn: float) -> list:
     return out
 
 
+SERIES = [("ring", "#9e9e9e"), ("zigzag", "#64b5f6"), ("stripe", "#4db6ac"), ("node_tile", "#ffcc80"),
+          ("node_device_tile", "#ffa726"), ("ultraattn", "#e53935")]
+
+
+def bar_chart_svg(rows: list, title: str = "", baseline: str = "ring", width_per_group: int = 150,
+                  height: int = 260) -> str:
+    """Grouped bar chart of speed-ups over ``baseline`` (one group per configuration, one bar per
+    variant that was measured), as a self-contained SVG string. The reference draws its figures
+    with matplotlib (plot/*.py), which this image does not have; the chart carries the same
+    content as its per-configuration panels: bars labelled with the speed-up, baselines in cool
+    colours, the tiling ablations in orange, the full system in red."""
+    groups = []
+    for r in rows:
+        base = r.get(baseline) or next((r[k] for k, _ in SERIES if r.get(k)), None)
+        if not base:
+            continue
+        bars = [(k, colour, base / r[k]) for k, colour in SERIES if r.get(k)]
+        label = f"fob={r.get('fob', '')} CP={r.get('CP', '')}"
+        m = re.search(r"S=\((\d+)", r.get("shape", "") or "")
+        if m:
+            label += f" S={int(m.group(1)) // 1024}k"
+        groups.append((label, bars))
+    top = max([v for _, bars in groups for _, _, v in bars] + [1.0]) * 1.15
+    left, bottom, head = 46, 46, 30
+    plot_h = height - bottom - head
+    total_w = left + max(1, len(groups)) * width_per_group + 10
+    out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{total_w}" height="{height}" '
+           f'font-family="sans-serif" font-size="10">',
+           f'<rect width="{total_w}" height="{height}" fill="white"/>',
+           f'<text x="{total_w / 2:.0f}" y="16" text-anchor="middle" font-size="12">{title}</text>']
+    y_of = lambda v: head + plot_h * (1 - v / top)
+    for tick in range(0, int(top) + 1):
+        y = y_of(tick)
+        out.append(f'<line x1="{left}" y1="{y:.1f}" x2="{total_w - 10}" y2="{y:.1f}" stroke="#ddd"/>')
+        out.append(f'<text x="{left - 6}" y="{y + 3:.1f}" text-anchor="end">{tick}x</text>')
+    for gi, (label, bars) in enumerate(groups):
+        x0 = left + gi * width_per_group + 8
+        bw = (width_per_group - 16) / max(1, len(bars))
+        for bi, (name, colour, v) in enumerate(bars):
+            x, y = x0 + bi * bw, y_of(v)
+            out.append(f'<rect class="bar" x="{x:.1f}" y="{y:.1f}" width="{bw - 2:.1f}" '
+                       f'height="{head + plot_h - y:.1f}" fill="{colour}"><title>{name}</title></rect>')
+            out.append(f'<text x="{x + bw / 2 - 1:.1f}" y="{y - 2:.1f}" text-anchor="middle" font-size="8">{v:.2f}</text>')
+        out.append(f'<text x="{x0 + (width_per_group - 16) / 2:.1f}" y="{height - bottom + 14}" '
+                   f'text-anchor="middle">{label}</text>')
+    lx = left
+    for name, colour in SERIES:
+        out.append(f'<rect x="{lx}" y="{height - 14}" width="9" height="9" fill="{colour}"/>')
+        out.append(f'<text x="{lx + 12}" y="{height - 6}">{name}</text>')
+        lx += 16 + 6 * len(name) + 10
+    out.append("</svg>")
+    return "\n".join(out)
+
+
 COLS = ["fob", "CP", "shape", "ring", "zigzag", "stripe", "node_tile", "node_device_tile", "kernel_tile",
         "ultraattn", "speedup_vs_ring", "speedup_vs_best_baseline"]
 
@@ -139,6 +193,7 @@ def main(argv=None) -> int:
     ap.add_argument("--db", required=True, help="database/<cluster>/<platform> directory")
     ap.add_argument("--level", default="inter", choices=["intra", "inter"])
     ap.add_argument("--csv", default=None)
+    ap.add_argument("--svg", default=None, help="also draw the speed-ups over the ring baseline as a bar chart")
     ap.add_argument("--sim-accuracy", action="store_true",
                     help="print predicted-vs-measured statistics instead of the table")
     ap.add_argument("--e2e-layers", type=int, default=0,
@@ -165,6 +220,8 @@ def main(argv=None) -> int:
     print("|" + "---|" * len(COLS))
     for r in rows:
         print("| " + " | ".join(_fmt(r.get(c)) for c in COLS) + " |")
+    if a.svg:
+        Path(a.svg).write_text(bar_chart_svg(rows, title=f"{a.level}-level plans, speed-up over ring"))
     if a.csv:
         with open(a.csv, "w", newline="") as f:
             w = csv.DictWriter(f, fieldnames=["key"] + COLS, extrasaction="ignore")
