@@ -186,7 +186,7 @@ def main() -> None:
     ap.add_argument("--out", default="logs/m_configs")
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--max-seconds", type=float, default=0.0, help="(--kernels) stop the sweep after this long")
-    ap.add_argument("--one", choices=["fwd", "bwd", "gemm", "ops"], default=None)
+    ap.add_argument("--one", choices=["fwd", "bwd", "gemm", "ops", "gate"], default=None)
     ap.add_argument("--S", type=int, default=16384)
     ap.add_argument("--Nh", type=int, default=32)
     ap.add_argument("--causal", action="store_true")
@@ -194,6 +194,18 @@ def main() -> None:
     a = ap.parse_args()
     if a.one == "ops":
         _profile_memory_bound_ops(a.S, a.iters)
+        return
+    if a.one == "gate":
+        # small tiles with and without the start gate: what the host launch path adds to a timing
+        from .benchmark import benchmark_ops
+        dev = torch.device("cuda")
+        for S in (256, 512, 1024, 2048, 4096):
+            fwd, bwd = _setup(S, S, a.Nh, a.causal, dev)
+            for name, fn in (("fwd", fwd), ("bwd", bwd)):
+                plain = benchmark_ops(fn, warmup=3, num_iter=50, repeats=2, device=dev)
+                gated = benchmark_ops(fn, warmup=3, num_iter=50, repeats=2, device=dev, start_gate=True)
+                print(json.dumps({"op": name, "S": S, "Nh": a.Nh, "us_per_launch": round(plain * 1e6, 2),
+                                  "us_per_launch_behind_gate": round(gated * 1e6, 2)}), flush=True)
         return
     if a.one:
         dev = torch.device("cuda")
