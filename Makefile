@@ -5,7 +5,8 @@ CLUSTER_NAME ?= local
 PLATFORM ?= B200
 export CLUSTER_NAME PLATFORM
 
-.PHONY: build test test-gpu bench cluster_profile bsa_train dense_train bsa_infer report
+.PHONY: build test test-gpu bench cluster_profile bsa_train dense_train bsa_infer report plan fusion_table full_plans
+CONFIG ?= configs/stride.yaml
 
 build:            ## compile the sm_100a kernel library in-tree (nvcc; works without a GPU)
 	$(PY) -c "import __graft_entry__ as g; g.build()"
@@ -29,3 +30,12 @@ bsa_train dense_train bsa_infer:   ## planning + profiling campaign of one exper
 
 report:           ## figure tables from the profile database
 	$(PY) -m ultraattn_b200.drivers.report --db database/$(CLUSTER_NAME)/$(PLATFORM)
+
+plan:             ## one configuration from a YAML file: plan, predicted time (add a launcher to run it)
+	$(PY) -m ultraattn_b200.drivers.main --config $(CONFIG) --plan-only
+
+fusion_table:     ## speed-up of fused x-by-y tiles over single tiles, from the machine profile
+	$(PY) -m ultraattn_b200.drivers.fusion_evaluate --m-config ultraattn_b200/data/m_configs/$(PLATFORM)
+
+full_plans:       ## all Y x X plans of full attention for $(GPUS) ranks into the plan database
+	$(PY) -m ultraattn_b200.drivers.intra_attn_gen --cp $(GPUS)

@@ -42,6 +42,27 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
+def probe_sources() -> list[Path]:
+    """Stand-alone measurement programs (not linked into the library)."""
+    return sorted((CSRC / "microbench").glob("*.cu"))
+
+
+def build_probes(force: bool = False) -> list[Path]:
+    """Compile the stand-alone probes to objects, so that a build checks every CUDA source of the
+    tree. Returns the object paths."""
+    nvcc = _nvcc()
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    objs = []
+    for src in probe_sources():
+        obj = OBJ_DIR / ("probe_" + src.stem + ".o")
+        if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, _newest_header_mtime()):
+            r = subprocess.run([nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)], capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
+        objs.append(obj)
+    return objs
+
+
 def _newest_header_mtime() -> float:
     return max((p.stat().st_mtime for p in CSRC.glob("*.cuh")), default=0.0)
 
