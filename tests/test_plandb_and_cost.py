@@ -146,3 +146,35 @@ def test_report_bar_chart_svg(tmp_path):
     assert len(bars) == 4                               # ring, zigzag, node+device tile, UltraAttn
     labels = [e.text for e in root.iter(ns + "text")]
     assert "1.00" in labels and "2.50" in labels and "2.00" in labels and any("S=512k" in (t or "") for t in labels)
+
+
+def test_pickled_plans_use_the_reference_class_paths(tmp_path):
+    """A stored plan's pickle names ``search_algo.*`` classes (the paths the reference's pickles
+    are bound to) and loads in a fresh interpreter through those modules; whatever was imported
+    first."""
+    import pickletools
+    import subprocess
+    import sys
+    import search_algo.execute_plan  # noqa: F401  (imported before the planner on purpose)
+    from ultraattn_b200 import patterns as P
+    from ultraattn_b200.plandb import Prof_DB
+    from ultraattn_b200.planner import make_plan
+    plan = make_plan(pattern=P.global_local(4, 1, 2), cp=2, seq_len=256, n_heads=2, head_dim=16, fob=1,
+                     allocation="naive", plan_type="Flexflow")
+    db = Prof_DB("t", "B200", root=str(tmp_path))
+    pid = db.put_plan("some_key", plan, 1)
+    blob = (tmp_path / "t" / "B200" / "intra_bsa_exe_plans" / f"{pid}.pkl").read_bytes()
+    names = {arg for _, arg, _ in pickletools.genops(blob) if isinstance(arg, str)}
+    for mod in ("search_algo.execute_plan", "search_algo.dependent_graph", "search_algo.search_engine",
+                "search_algo.bsa_config"):
+        assert mod in names, mod
+    assert not any(n.startswith("ultraattn_b200.planner.schedule") or n.startswith("ultraattn_b200.planner.graph")
+                   for n in names)
+    code = ("import pickle, sys; p = pickle.load(open(sys.argv[1], 'rb')); "
+            "from search_algo.execute_plan import Execution_Plan; "
+            "print(isinstance(p, Execution_Plan), p.fob, len(p.gpu_kernel_lists), p.verify() == [])")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", code, str(tmp_path / "t" / "B200" / "intra_bsa_exe_plans" / f"{pid}.pkl")],
+                         capture_output=True, text=True, cwd=root)
+    assert out.stdout.split() == ["True", "1", "2", "True"], out.stderr
+    assert db.get_plan("some_key", 1).verify() == []

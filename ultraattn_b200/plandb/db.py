@@ -149,6 +149,8 @@ class Prof_DB:
         kv = self._load(kv_path)
         pid = kv[key] if key in kv else (max(kv.values()) + 1 if kv else 0)
         d = Path(getattr(self, f"{lvl}_BSA_EXE_PLANS_DIR"))
+        from ..planner import bind_reference_class_paths
+        bind_reference_class_paths()        # pickles name the reference's module paths when possible
         with open(d / f"{pid}.pkl", "wb") as f:
             pickle.dump(plan, f)
         if hasattr(plan, "to_plain") and getattr(plan, "d_graph", None) is not None:

@@ -102,6 +102,8 @@ def write_plan(execute_plan: Execution_Plan, prefix: str) -> str:
     back as a check (reference: search_algo/dense_utils.py:53-62). Returns the pickle's path."""
     import os
     import pickle
+    from . import bind_reference_class_paths
+    bind_reference_class_paths()
     os.makedirs(prefix, exist_ok=True)
     path = os.path.join(prefix, execute_plan.get_plan_name() + ".pkl")
     with open(path, "wb") as f:
