@@ -1,0 +1,69 @@
+"""The reference's kernel-level calls (forked flash-attention signatures) on the fp32 restatement."""
+import math
+
+import torch
+
+from ultraattn_b200.ops.flash_compat import (_flash_attn_backward, _flash_attn_forward,
+                                             _flash_attn_varlen_backward, _flash_attn_varlen_forward)
+
+
+def _dense(q, k, v, d_o, causal):
+    """[S, H, D] tensors; grouped-query heads repeated; bottom-right aligned causal mask."""
+    q, k, v = (t.detach().clone().requires_grad_() for t in (q, k, v))
+    g = q.shape[1] // k.shape[1]
+    kk, vv = k.repeat_interleave(g, 1), v.repeat_interleave(g, 1)
+    s = torch.einsum("qhd,khd->hqk", q, kk) / math.sqrt(q.shape[-1])
+    if causal:
+        sq, sk = q.shape[0], k.shape[0]
+        mask = torch.arange(sk)[None, :] <= torch.arange(sq)[:, None] + (sk - sq)
+        s = s.masked_fill(~mask[None], float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    o = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vv)
+    o.backward(d_o)
+    return o.detach(), lse.detach(), q.grad, k.grad, v.grad
+
+
+def test_dense_calls_with_out_and_softmax_d():
+    torch.manual_seed(0)
+    Sq, Skv, H, Hk, D = 48, 80, 4, 2, 16
+    q, d_o = torch.randn(1, Sq, H, D), torch.randn(1, Sq, H, D)
+    k, v = torch.randn(1, Skv, Hk, D), torch.randn(1, Skv, Hk, D)
+    for causal in (False, True):
+        o_ref, lse_ref, dq_ref, dk_ref, dv_ref = _dense(q[0], k[0], v[0], d_o[0], causal)
+        buf = torch.full_like(q, 7.0)
+        ret = _flash_attn_forward(q, k, v, 0.0, None, causal, window_size=(-1, -1), alibi_slopes=None,
+                                  return_softmax=False, out=buf)
+        assert len(ret) == 8 and ret[0] is buf and ret[6] is None
+        assert torch.allclose(buf[0], o_ref, atol=1e-5) and torch.allclose(ret[5][0], lse_ref, atol=1e-5)
+        # the fork's way: D precomputed, a dummy tensor in place of O
+        dvec = (o_ref * d_o[0]).sum(-1).t()[None].contiguous()
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _flash_attn_backward(d_o, q, k, v, q, ret[5], dq, dk, dv, 0.0, None, causal, (-1, -1), None, False,
+                             rng_state=None, softmax_d=dvec)
+        assert torch.allclose(dq[0], dq_ref, atol=1e-5) and torch.allclose(dk[0], dk_ref, atol=1e-5)
+        assert torch.allclose(dv[0], dv_ref, atol=1e-5)
+        # the stock way: D derived from O
+        dq2, dk2, dv2 = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _flash_attn_backward(d_o, q, k, v, buf, ret[5], dq2, dk2, dv2, 0.0, None, causal)
+        assert torch.allclose(dq2, dq, atol=1e-6) and torch.allclose(dk2, dk, atol=1e-6)
+
+
+def test_varlen_calls():
+    torch.manual_seed(1)
+    H, D = 2, 16
+    cu = [0, 24, 24, 64, 72]
+    T = cu[-1]
+    q, k, v, d_o = (torch.randn(T, H, D) for _ in range(4))
+    max_len = max(b - a for a, b in zip(cu[:-1], cu[1:]))
+    ret = _flash_attn_varlen_forward(q, k, v, cu, cu, max_len, max_len, 0.0, None, True)
+    o, lse = ret[0], ret[5]
+    assert lse.shape == (len(cu) - 1, H, max_len)
+    dq, dk, dv = torch.empty_like(q), torch.full_like(k, 3.0), torch.full_like(v, 3.0)
+    _flash_attn_varlen_backward(d_o, q, k, v, o, lse, dq, dk, dv, cu, cu, max_len, max_len, 0.0, None, True)
+    for i, (a, b) in enumerate(zip(cu[:-1], cu[1:])):
+        if b == a:
+            continue
+        o_ref, lse_ref, dq_ref, dk_ref, dv_ref = _dense(q[a:b], k[a:b], v[a:b], d_o[a:b], True)
+        assert torch.allclose(o[a:b], o_ref, atol=1e-5) and torch.allclose(lse[i, :, :b - a], lse_ref, atol=1e-5)
+        assert torch.allclose(dq[a:b], dq_ref, atol=1e-5) and torch.allclose(dk[a:b], dk_ref, atol=1e-5)
+        assert torch.allclose(dv[a:b], dv_ref, atol=1e-5)
