@@ -122,3 +122,57 @@ def test_start_gate_holds_and_releases_the_stream(dev):
     torch.cuda.synchronize(dev)                       # never opened: returns after its budget
     assert not short.check() and short.timed_out
     A.check_status(dev)                               # and leaves no error behind
+
+
+def test_reference_kernel_calls_on_gpu(dev):
+    """The forked-flash-attention signatures on the sm_100a kernels: rectangular causal (mask
+    aligned bottom-right), caller-named output, precomputed D with a dummy O, packed batch."""
+    import math
+    from ultraattn_b200.ops import attention as A
+    from ultraattn_b200.ops.flash_compat import (_flash_attn_backward, _flash_attn_forward,
+                                                 _flash_attn_varlen_backward, _flash_attn_varlen_forward)
+
+    def dense(q, k, v, d_o, causal):            # [S, H, D] fp32 on the CPU
+        q, k, v = (t.detach().float().cpu().clone().requires_grad_() for t in (q, k, v))
+        g = q.shape[1] // k.shape[1]
+        s = torch.einsum("qhd,khd->hqk", q, k.repeat_interleave(g, 1)) / math.sqrt(q.shape[-1])
+        if causal:
+            sq, sk = q.shape[0], k.shape[0]
+            s = s.masked_fill(~(torch.arange(sk)[None, :] <= torch.arange(sq)[:, None] + (sk - sq))[None], float("-inf"))
+        o = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v.repeat_interleave(g, 1))
+        o.backward(d_o.float().cpu())
+        return o.detach(), q.grad, k.grad, v.grad
+
+    torch.manual_seed(15)
+    Sq, Skv, H, Hk = 256, 384, 4, 2
+    mk = lambda s, h: torch.randn(1, s, h, 128, device=dev, dtype=torch.bfloat16)
+    q, d_o, k, v = mk(Sq, H), mk(Sq, H), mk(Skv, Hk), mk(Skv, Hk)
+    o_ref, dq_ref, dk_ref, dv_ref = dense(q[0], k[0], v[0], d_o[0], True)
+    buf = torch.empty_like(q)
+    ret = _flash_attn_forward(q, k, v, 0.0, None, True, (-1, -1), None, False, out=buf)
+    assert ret[0] is buf
+    _close(buf[0].cpu(), o_ref, 1e-2)
+    dvec = (buf.float() * d_o.float()).sum(-1).permute(0, 2, 1).contiguous()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    _flash_attn_backward(d_o, q, k, v, q, ret[5], dq, dk, dv, 0.0, None, True, (-1, -1), None, False, None,
+                         softmax_d=dvec)
+    torch.cuda.synchronize(dev)
+    A.check_status(dev)
+    _close(dq[0].cpu(), dq_ref, 2e-2)
+    _close(dk[0].cpu(), dk_ref, 2e-2)
+    _close(dv[0].cpu(), dv_ref, 2e-2)
+    cu = [0, 256, 256, 640, 768]
+    T = cu[-1]
+    qp, kp, vp, dop = (torch.randn(T, H, 128, device=dev, dtype=torch.bfloat16) for _ in range(4))
+    r = _flash_attn_varlen_forward(qp, kp, vp, cu, cu, 384, 384, 0.0, None, True)
+    dq, dk, dv = torch.empty_like(qp), torch.empty_like(kp), torch.empty_like(vp)
+    _flash_attn_varlen_backward(dop, qp, kp, vp, r[0], r[5], dq, dk, dv, cu, cu, 384, 384, 0.0, None, True)
+    torch.cuda.synchronize(dev)
+    A.check_status(dev)
+    for a, b in zip(cu[:-1], cu[1:]):
+        if b > a:
+            o_ref, dq_ref, dk_ref, dv_ref = dense(qp[a:b], kp[a:b], vp[a:b], dop[a:b], True)
+            _close(r[0][a:b].cpu(), o_ref, 1e-2)
+            _close(dq[a:b].cpu(), dq_ref, 2e-2)
+            _close(dk[a:b].cpu(), dk_ref, 2e-2)
+            _close(dv[a:b].cpu(), dv_ref, 2e-2)
