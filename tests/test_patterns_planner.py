@@ -144,3 +144,27 @@ def test_make_plan_and_remap():
     a = solve_sparse_from_bsa(cfg, fob=0, time_limit=3.0)
     b = solve_sparse_from_bsa(cfg, fob=0, time_limit=3.0, cmap=cm)
     assert b.comm_volume <= a.comm_volume + 2
+
+
+def test_causal8_not_worse_than_the_published_table():
+    """The reference ships a hand-kept answer of its allocation ILP for dense causal attention on
+    8 ranks (a literal 8 x 8 table, search_algo/manual_schedules.py:495-504). Ours must be at
+    least as good on the ILP's own objective (worst rank's traffic) under the same load bound."""
+    from ultraattn_b200.planner.allocate import comm_volumes, comp_volumes, tile_volumes
+    published = np.array([[0, -1, -1, -1, -1, -1, -1, -1],
+                          [0, 1, -1, -1, -1, -1, -1, -1],
+                          [1, 1, 2, -1, -1, -1, -1, -1],
+                          [1, 1, 3, 3, -1, -1, -1, -1],
+                          [0, 4, 0, 0, 4, -1, -1, -1],
+                          [2, 4, 2, 5, 4, 5, -1, -1],
+                          [2, 6, 2, 5, 7, 5, 6, -1],
+                          [7, 6, 3, 3, 7, 3, 6, 7]])
+    cfg = BSA_Config.create_causal((8, 1))
+    cmap = np.arange(8)
+    vol = tile_volumes(cfg.bsa_repr, 8)
+    for fob in (0, 1):
+        cin, cout = comm_volumes(published, cmap, 8, fob)
+        theirs = max(cin.max(), cout.max())
+        ours = solve_sparse_from_bsa(cfg, fob=fob, ParD=8, time_limit=5.0)
+        assert ours.comm_volume <= theirs + 1e-9, (fob, ours.comm_volume, theirs)
+        assert ours.comp_max <= comp_volumes(published, vol, 8).max() + 1e-9
