@@ -178,3 +178,25 @@ def test_pickled_plans_use_the_reference_class_paths(tmp_path):
                          capture_output=True, text=True, cwd=root)
     assert out.stdout.split() == ["True", "1", "2", "True"], out.stderr
     assert db.get_plan("some_key", 1).verify() == []
+
+
+def test_report_reads_the_published_profile_entries():
+    """Seven entries of the reference's published profile database (dense causal, S = 512k, 32
+    heads, 8 x A800, forward; plot/results_exp/inter_dense_exe_plans_profile.json:478-502), read
+    as data: the table reproduces 'UltraAttn = min over its four variants' and shows the
+    measured ratio to the best baseline (0.69, not the figure's substituted value)."""
+    from ultraattn_b200.drivers import report
+    pre = ("fob=0_CP=(8, 1)_shape_config={S=(524288, 524288)_Nh=(32, 32)_bs=1_D=128}"
+           "_bsa_config={CP=(8, 1)_repr=[[2]]}")
+    published = {"_ring": (114.458, "2.459e+00"), "_zigzag": (219.121, "1.285e+00"), "_stripe": (200.497, "1.404e+00"),
+                 "_ablation=(w/o_kernel_tile,ILP)": (151.927, "1.853e+00"),
+                 "_ablation=(w_kernel_tile,ILP)": (107.276, "2.624e+00"),
+                 "_ablation=(w/o_kernel_tile,Flexflow)": (150.884, "1.866e+00"),
+                 "_ablation=(w_kernel_tile,Flexflow)": (134.258, "2.097e+00")}
+    rows = report.build_rows({pre + s: {"hfu": h, "time": t} for s, (h, t) in published.items()})
+    assert len(rows) == 1
+    r = rows[0]
+    assert (r["ring"], r["zigzag"], r["stripe"]) == (2.459, 1.285, 1.404)
+    assert r["ultraattn"] == 1.853 and r["node_device_tile"] == 1.866 and r["kernel_tile"] == 1.866
+    assert abs(r["speedup_vs_ring"] - 2.459 / 1.853) < 1e-9
+    assert abs(r["speedup_vs_best_baseline"] - 1.285 / 1.853) < 1e-9 and r["speedup_vs_best_baseline"] < 0.7
