@@ -11,29 +11,12 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, Y, X, causal, ret):
+def _worker(rank, world, port, cases, ret):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from ultraattn_b200 import patterns as P
-        from ultraattn_b200.planner import Fused_Execution_Plan
-        from ultraattn_b200.runtime.grid import GridExecutor
-        S, H, Hk, D = 256, 4, 2, 16
-        g = torch.Generator().manual_seed(7)
-        q, d_o = (torch.randn(1, S, H, D, generator=g) for _ in range(2))
-        k, v = (torch.randn(1, S, Hk, D, generator=g) for _ in range(2))
-        sl = slice(rank * S // world, (rank + 1) * S // world)
-        ex = GridExecutor.from_plan(Fused_Execution_Plan(Y, X, None, 0, causal=causal), device=torch.device("cpu"))
-        assert ex.row_chunks == list(range(rank // X * X, rank // X * X + X))
-        o, lse = ex.forward(q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous())
-        dq, dk, dv = ex.backward(d_o[:, sl].contiguous(), q[:, sl].contiguous(), k[:, sl].contiguous(),
-                                 v[:, sl].contiguous(), o, lse)
-        pat = P.causal(1) if causal else P.full(1)
-        o_ref, lse_ref, dq_ref, dk_ref, dv_ref = P.dense_attention_with_grads(q, k, v, d_o, pat)
-        ret[rank] = max((o - o_ref[:, sl]).abs().max().item(), (lse - lse_ref[:, :, sl]).abs().max().item(),
-                        (dq - dq_ref[:, sl]).abs().max().item(), (dk - dk_ref[:, sl]).abs().max().item(),
-                        (dv - dv_ref[:, sl]).abs().max().item())
+        ret[rank] = {f"{Y}x{X}-{causal}": _one_grid(rank, world, Y, X, causal) for Y, X, causal in cases}
     except Exception as e:  # noqa: BLE001
         import traceback
         ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
@@ -41,14 +24,36 @@ def _worker(rank, world, port, Y, X, causal, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("Y,X,causal", [(2, 2, False), (2, 2, True), (4, 1, False), (1, 4, True)])
-def test_grid_executor_world4(Y, X, causal):
-    port = 29300 + (os.getpid() + 7 * Y + X + int(causal)) % 90
+def _one_grid(rank, world, Y, X, causal):
+    from ultraattn_b200 import patterns as P
+    from ultraattn_b200.planner import Fused_Execution_Plan
+    from ultraattn_b200.runtime.grid import GridExecutor
+    S, H, Hk, D = 256, 4, 2, 16
+    g = torch.Generator().manual_seed(7)
+    q, d_o = (torch.randn(1, S, H, D, generator=g) for _ in range(2))
+    k, v = (torch.randn(1, S, Hk, D, generator=g) for _ in range(2))
+    sl = slice(rank * S // world, (rank + 1) * S // world)
+    ex = GridExecutor.from_plan(Fused_Execution_Plan(Y, X, None, 0, causal=causal), device=torch.device("cpu"))
+    assert ex.row_chunks == list(range(rank // X * X, rank // X * X + X))
+    o, lse = ex.forward(q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous())
+    dq, dk, dv = ex.backward(d_o[:, sl].contiguous(), q[:, sl].contiguous(), k[:, sl].contiguous(),
+                             v[:, sl].contiguous(), o, lse)
+    pat = P.causal(1) if causal else P.full(1)
+    o_ref, lse_ref, dq_ref, dk_ref, dv_ref = P.dense_attention_with_grads(q, k, v, d_o, pat)
+    return max((o - o_ref[:, sl]).abs().max().item(), (lse - lse_ref[:, :, sl]).abs().max().item(),
+               (dq - dq_ref[:, sl]).abs().max().item(), (dk - dk_ref[:, sl]).abs().max().item(),
+               (dv - dv_ref[:, sl]).abs().max().item())
+
+
+def test_grid_executor_world4():
+    """2 x 2 (full and causal), 4 x 1 (keys / values move) and 1 x 4 (queries move, causal)."""
+    cases = [(2, 2, False), (2, 2, True), (4, 1, False), (1, 4, True)]
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(4, port, Y, X, causal, ret), nprocs=4, join=True)
+    mp.spawn(_worker, args=(4, 29300 + os.getpid() % 90, cases, ret), nprocs=4, join=True)
     for r in range(4):
-        assert isinstance(ret[r], float), ret[r]
-        assert ret[r] < 2e-4, (r, ret[r])
+        assert isinstance(ret[r], dict), ret[r]
+        for name, err in ret[r].items():
+            assert err < 2e-4, (r, name, err)
 
 
 def _api_worker(rank, world, port, ret):

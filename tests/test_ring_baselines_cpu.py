@@ -10,25 +10,15 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, kind, causal, ret):
+def _worker(rank, world, port, cases, ret):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from ultraattn_b200 import parallel as PL, patterns as P
-        S, H, D = 256, 4, 16
-        g = torch.Generator().manual_seed(0)
-        q, k, v, d_o = (torch.randn(1, S, H, D, generator=g) for _ in range(4))
-        sh = lambda t: PL.shard_sequence(t, rank, world, kind)
-        ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
-        fn = {"ring": PL.ring_flash_attn_func, "zigzag": PL.zigzag_ring_flash_attn_func,
-              "stripe": PL.stripe_flash_attn_func, "ulysses": PL.deepspeed_ulysses_attn_func}[kind]
-        o = fn(ql, kl, vl, causal=causal)
-        o.backward(sh(d_o))
-        pat = P.causal(1) if causal else P.full(1)
-        o_ref, _, dq, dk, dv = P.dense_attention_with_grads(q, k, v, d_o, pat)
-        ret[rank] = max((o - sh(o_ref)).abs().max().item(), (ql.grad - sh(dq)).abs().max().item(),
-                        (kl.grad - sh(dk)).abs().max().item(), (vl.grad - sh(dv)).abs().max().item())
+        out = {}
+        for kind, causal in cases:
+            out[f"{kind}-{causal}"] = _one_baseline(rank, world, kind, causal)
+        ret[rank] = out
     except Exception as e:  # noqa: BLE001
         import traceback
         ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
@@ -36,15 +26,36 @@ def _worker(rank, world, port, kind, causal, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("kind,causal", [("ring", True), ("ring", False), ("zigzag", True),
-                                         ("stripe", True), ("ulysses", True)])
-def test_baselines_world4(kind, causal):
-    port = 29900 + (os.getpid() + hash(kind)) % 90
+def _one_baseline(rank, world, kind, causal):
+    from ultraattn_b200 import parallel as PL, patterns as P
+    S, H, D = 256, 4, 16
+    g = torch.Generator().manual_seed(0)
+    q, k, v, d_o = (torch.randn(1, S, H, D, generator=g) for _ in range(4))
+    sh = lambda t: PL.shard_sequence(t, rank, world, kind)
+    ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
+    fn = {"ring": PL.ring_flash_attn_func, "zigzag": PL.zigzag_ring_flash_attn_func,
+          "stripe": PL.stripe_flash_attn_func, "ulysses": PL.deepspeed_ulysses_attn_func}[kind]
+    o = fn(ql, kl, vl, causal=causal)
+    o.backward(sh(d_o))
+    pat = P.causal(1) if causal else P.full(1)
+    o_ref, _, dq, dk, dv = P.dense_attention_with_grads(q, k, v, d_o, pat)
+    return max((o - sh(o_ref)).abs().max().item(), (ql.grad - sh(dq)).abs().max().item(),
+               (kl.grad - sh(dk)).abs().max().item(), (vl.grad - sh(dv)).abs().max().item())
+
+
+def _check(ret, world):
+    for r in range(world):
+        assert isinstance(ret[r], dict), ret[r]
+        for name, err in ret[r].items():
+            assert err < 2e-4, (r, name, err)
+
+
+def test_baselines_world4():
+    """Ring (causal and full), zigzag, stripe and Ulysses on four ranks, one process group."""
+    cases = [("ring", True), ("ring", False), ("zigzag", True), ("stripe", True), ("ulysses", True)]
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(4, port, kind, causal, ret), nprocs=4, join=True)
-    for r in range(4):
-        assert isinstance(ret[r], float), ret[r]
-        assert ret[r] < 2e-4, (r, ret[r])
+    mp.spawn(_worker, args=(4, 29900 + os.getpid() % 90, cases, ret), nprocs=4, join=True)
+    _check(ret, 4)
 
 
 def _dense_packed(q, k, v, d_o, cu, causal):
@@ -56,29 +67,12 @@ def _dense_packed(q, k, v, d_o, cu, causal):
     return [torch.cat([o[i][0] for o in outs], dim=0) for i in (0, 2, 3, 4)]
 
 
-def _varlen_worker(rank, world, port, kind, causal, ret):
+def _varlen_worker(rank, world, port, cases, ret):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from ultraattn_b200 import parallel as PL
-        H, D = 2, 16
-        cu = [0, 64, 64, 192, 224]          # lengths 64, 0, 128, 32
-        g = torch.Generator().manual_seed(3)
-        q, k, v, d_o = (torch.randn(cu[-1], H, D, generator=g) for _ in range(4))
-        sh = lambda t: PL.shard_packed(t, cu, rank, world, kind)[0]
-        local_cu = PL.shard_packed(q, cu, rank, world, kind)[1]
-        ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
-        fn = {"ring": PL.ring_flash_attn_varlen_func, "zigzag": PL.zigzag_ring_flash_attn_varlen_func}[kind]
-        o = fn(ql, kl, vl, local_cu, max(b - a for a, b in zip(local_cu[:-1], local_cu[1:])), causal=causal)
-        o.backward(sh(d_o))
-        # the kv-packed form must give the same output
-        kvp = getattr(PL, fn.__name__.replace("_func", "_kvpacked_func"))
-        o2 = kvp(ql.detach(), torch.stack([kl.detach(), vl.detach()], dim=1), local_cu, None, causal=causal)
-        o_ref, dq, dk, dv = _dense_packed(q, k, v, d_o, cu, causal)
-        ret[rank] = max((o - sh(o_ref)).abs().max().item(), (ql.grad - sh(dq)).abs().max().item(),
-                        (kl.grad - sh(dk)).abs().max().item(), (vl.grad - sh(dv)).abs().max().item(),
-                        (o2 - o.detach()).abs().max().item())
+        ret[rank] = {f"{kind}-{causal}": _one_varlen(rank, world, kind, causal) for kind, causal in cases}
     except Exception as e:  # noqa: BLE001
         import traceback
         ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
@@ -86,35 +80,41 @@ def _varlen_worker(rank, world, port, kind, causal, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("kind,causal", [("ring", True), ("ring", False), ("zigzag", True)])
-def test_varlen_baselines_world2(kind, causal):
-    port = 29700 + (os.getpid() + hash(kind)) % 90
+def _one_varlen(rank, world, kind, causal):
+    from ultraattn_b200 import parallel as PL
+    H, D = 2, 16
+    cu = [0, 64, 64, 192, 224]          # lengths 64, 0, 128, 32
+    g = torch.Generator().manual_seed(3)
+    q, k, v, d_o = (torch.randn(cu[-1], H, D, generator=g) for _ in range(4))
+    sh = lambda t: PL.shard_packed(t, cu, rank, world, kind)[0]
+    local_cu = PL.shard_packed(q, cu, rank, world, kind)[1]
+    ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
+    fn = {"ring": PL.ring_flash_attn_varlen_func, "zigzag": PL.zigzag_ring_flash_attn_varlen_func}[kind]
+    o = fn(ql, kl, vl, local_cu, max(b - a for a, b in zip(local_cu[:-1], local_cu[1:])), causal=causal)
+    o.backward(sh(d_o))
+    # the kv-packed form must give the same output
+    kvp = getattr(PL, fn.__name__.replace("_func", "_kvpacked_func"))
+    o2 = kvp(ql.detach(), torch.stack([kl.detach(), vl.detach()], dim=1), local_cu, None, causal=causal)
+    o_ref, dq, dk, dv = _dense_packed(q, k, v, d_o, cu, causal)
+    return max((o - sh(o_ref)).abs().max().item(), (ql.grad - sh(dq)).abs().max().item(),
+               (kl.grad - sh(dk)).abs().max().item(), (vl.grad - sh(dv)).abs().max().item(),
+               (o2 - o.detach()).abs().max().item())
+
+
+def test_varlen_baselines_world2():
+    """Packed batches through the ring (causal and full) and the zigzag ring on two ranks."""
+    cases = [("ring", True), ("ring", False), ("zigzag", True)]
     ret = mp.Manager().dict()
-    mp.spawn(_varlen_worker, args=(2, port, kind, causal, ret), nprocs=2, join=True)
-    for r in range(2):
-        assert isinstance(ret[r], float), ret[r]
-        assert ret[r] < 2e-4, (r, ret[r])
+    mp.spawn(_varlen_worker, args=(2, 29700 + os.getpid() % 90, cases, ret), nprocs=2, join=True)
+    _check(ret, 2)
 
 
-def _hierarchy_worker(rank, world, port, causal, ret, mode="kv", per_node=2, S=256):
+def _hierarchy_worker(rank, world, port, cases, ret, per_node=2, S=256):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from ultraattn_b200 import parallel as PL, patterns as P
-        H, D = 2, 16
-        g = torch.Generator().manual_seed(4)
-        q, k, v, d_o = (torch.randn(1, S, H, D, generator=g) for _ in range(4))
-        kind = "zigzag" if causal else "ring"
-        sh = lambda t: PL.shard_sequence(t, rank, world, kind)
-        groups = PL.create_hierarchy_groups(tasks_per_node=per_node)
-        ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
-        o = PL.hierarchy_attn_func(ql, kl, vl, causal=causal, groups=groups, mode=mode)
-        o.backward(sh(d_o))
-        pat = P.causal(1) if causal else P.full(1)
-        o_ref, _, dq, dk, dv = P.dense_attention_with_grads(q, k, v, d_o, pat)
-        ret[rank] = max((o - sh(o_ref)).abs().max().item(), (ql.grad - sh(dq)).abs().max().item(),
-                        (kl.grad - sh(dk)).abs().max().item(), (vl.grad - sh(dv)).abs().max().item())
+        ret[rank] = {f"{mode}-{causal}": _one_hierarchy(rank, world, causal, mode, per_node, S) for causal, mode in cases}
     except Exception as e:  # noqa: BLE001
         import traceback
         ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
@@ -122,14 +122,38 @@ def _hierarchy_worker(rank, world, port, causal, ret, mode="kv", per_node=2, S=2
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("causal,mode", [(True, "kv"), (False, "kv"), (True, "qo"), (False, "qo")])
-def test_two_level_ring_2x2(causal, mode):
-    port = 29600 + (os.getpid() + int(causal) + 2 * (mode == "qo")) % 90
+def _one_hierarchy(rank, world, causal, mode, per_node, S):
+    from ultraattn_b200 import parallel as PL, patterns as P
+    H, D = 2, 16
+    g = torch.Generator().manual_seed(4)
+    q, k, v, d_o = (torch.randn(1, S, H, D, generator=g) for _ in range(4))
+    kind = "zigzag" if causal else "ring"
+    sh = lambda t: PL.shard_sequence(t, rank, world, kind)
+    groups = PL.create_hierarchy_groups(tasks_per_node=per_node)
+    ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
+    o = PL.hierarchy_attn_func(ql, kl, vl, causal=causal, groups=groups, mode=mode)
+    o.backward(sh(d_o))
+    pat = P.causal(1) if causal else P.full(1)
+    o_ref, _, dq, dk, dv = P.dense_attention_with_grads(q, k, v, d_o, pat)
+    return max((o - sh(o_ref)).abs().max().item(), (ql.grad - sh(dq)).abs().max().item(),
+               (kl.grad - sh(dk)).abs().max().item(), (vl.grad - sh(dv)).abs().max().item())
+
+
+def test_two_level_ring_2x2():
+    """Two nodes of two ranks: both modes, causal (zigzag shards) and full."""
+    cases = [(True, "kv"), (False, "kv"), (True, "qo"), (False, "qo")]
     ret = mp.Manager().dict()
-    mp.spawn(_hierarchy_worker, args=(4, port, causal, ret, mode), nprocs=4, join=True)
-    for r in range(4):
-        assert isinstance(ret[r], float), ret[r]
-        assert ret[r] < 2e-4, (r, ret[r])
+    mp.spawn(_hierarchy_worker, args=(4, 29600 + os.getpid() % 90, cases, ret), nprocs=4, join=True)
+    _check(ret, 4)
+
+
+def test_two_level_ring_3_nodes():
+    """Three nodes of two ranks: the query / output exchange visits two other nodes (the second
+    visitor is requested while the first is computed)."""
+    ret = mp.Manager().dict()
+    mp.spawn(_hierarchy_worker, args=(6, 29500 + os.getpid() % 90, [(True, "kv"), (True, "qo")], ret, 2, 240),
+             nprocs=6, join=True)
+    _check(ret, 6)
 
 
 def test_lightseq_time_steps_match_the_allocation_table():
@@ -196,17 +220,5 @@ def test_lightseq_attention_world4():
     ret = mp.Manager().dict()
     mp.spawn(_lightseq_worker, args=(4, port, ret), nprocs=4, join=True)
     for r in range(4):
-        assert isinstance(ret[r], float), ret[r]
-        assert ret[r] < 2e-4, (r, ret[r])
-
-
-@pytest.mark.parametrize("mode", ["kv", "qo"])
-def test_two_level_ring_3_nodes(mode):
-    """Three nodes of two ranks: the query / output exchange visits two other nodes (the second
-    visitor is requested while the first is computed)."""
-    port = 29500 + (os.getpid() + (mode == "qo")) % 90
-    ret = mp.Manager().dict()
-    mp.spawn(_hierarchy_worker, args=(6, port, True, ret, mode, 2, 240), nprocs=6, join=True)
-    for r in range(6):
         assert isinstance(ret[r], float), ret[r]
         assert ret[r] < 2e-4, (r, ret[r])
