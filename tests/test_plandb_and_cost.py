@@ -200,3 +200,26 @@ def test_report_reads_the_published_profile_entries():
     assert r["ultraattn"] == 1.853 and r["node_device_tile"] == 1.866 and r["kernel_tile"] == 1.866
     assert abs(r["speedup_vs_ring"] - 2.459 / 1.853) < 1e-9
     assert abs(r["speedup_vs_best_baseline"] - 1.285 / 1.853) < 1e-9 and r["speedup_vs_best_baseline"] < 0.7
+
+
+def test_fused_step_time_model():
+    """The time model of the fused runtime: one rank = the sum of its tile times; a balanced
+    allocation is predicted faster than the row-owner one; eight ranks take about an eighth."""
+    from ultraattn_b200.planner.allocate import naive_allocate_strategy
+    from ultraattn_b200.planner.cost import Machine_Config, fused_step_time
+    from ultraattn_b200.runtime.context_parallel import plan_allocation
+    pat = P.strided(32, 4, 2)
+    S, H = 524288, 32
+    one = fused_step_time(np.where(pat.refined(32) > 0, 0, -1), np.zeros(32, dtype=int), pat, S, H)
+    comp = Machine_Config.b200_default().comp_profile_maps[1]
+    full = comp.get_comp_time_from_map_key((16384, 1, 32, 128, "1/1", False))
+    causal = comp.get_comp_time_from_map_key((16384, 1, 32, 128, "1/1", True))
+    assert abs(sum(one["per_rank"][0]["compute_s"]) - (143 * full.sum() + 32 * causal.sum())) / one["step_s"] < 0.01
+    table, cmap = plan_allocation(pat, 8, 1, "ilp", time_limit=5.0)
+    ilp = fused_step_time(table, cmap, pat, S, H)
+    cfg = BSA_Config(None, None, {"bsa_repr": pat, "CP": (8, 1)})
+    nv = naive_allocate_strategy(cfg, fob=1)
+    naive = fused_step_time(np.asarray(nv.table), np.asarray(nv.cmap), pat, S, H)
+    assert ilp["step_s"] < naive["step_s"]
+    assert 0.9 < one["step_s"] / (8 * ilp["step_s"]) <= 1.02          # near-linear strong scaling predicted
+    assert all(r["link_s"][1] < r["compute_s"][1] for r in ilp["per_rank"])   # compute-bound on NVLink 5

@@ -473,3 +473,70 @@ def convert_node_profile_data_to_comp_map(file_name, local_size: int = 8) -> dic
                 fob = int(m.group(1))
     out["level2"] = out["level1"]
     return out
+
+
+# -------------------------------------------------------------------------------------------------
+# time model of the fused runtime
+# -------------------------------------------------------------------------------------------------
+def fused_step_time(table, cmap, pattern, seq_len: int, n_heads: int, head_dim: int = 128,
+                    m_config: Optional["Machine_Config"] = None, n_kv_heads: Optional[int] = None,
+                    batch: int = 1, hbm_gbs: float = 6400.0) -> dict:
+    """Predicted time of one forward and one backward call of the fused context-parallel runtime
+    for an allocation ``table`` (tile -> rank) and ownership ``cmap``.
+
+    Unlike a launch plan's ``end_time`` (one launch and one message per tile, scheduled on three
+    streams) the fused runtime runs ONE kernel per pass and rank that walks all of the rank's
+    tiles, pulls remote blocks while the first tiles compute and pushes results from its epilogue.
+    Its time per rank is therefore modelled as: the sum of the rank's tile times (from the kernel
+    grid of the machine profile, at the tile's shape and mask type, minus the per-launch floor that
+    a fused launch pays only once) + what the transfers cannot hide (the larger of inbound and
+    outbound NVLink bytes over the link curve, overlapped with compute: only the excess counts)
+    + the memory-bound passes around the kernels (copy-in of the shards, D = rowsum(dO * O),
+    merge of mailbox slots, fp32 -> bf16 cast and clearing of the accumulators). The step ends
+    when the slowest rank ends. Returns per-pass times in seconds and the per-rank breakdown."""
+    import numpy as _np
+    m = m_config or Machine_Config.b200_default()
+    table = _np.asarray(table)
+    cmap = _np.asarray(cmap)
+    par_d = table.shape[0]
+    cp = int(cmap.max()) + 1
+    blk = seq_len // par_d
+    hk = n_kv_heads or n_heads
+    types = pattern.refined(par_d)
+    comp = m.comp_profile_maps[1]
+    comm = m.comm_profile_maps[1]
+    t_tile = {c: _np.maximum(comp.get_comp_time_from_map_key((blk, batch, n_heads, head_dim, "1/1", c))
+                             - B200_LAUNCH_S, 1e-7) for c in (False, True)}
+    es = 2
+    q_blk = batch * blk * n_heads * head_dim * es
+    kv_blk = batch * blk * hk * head_dim * es
+    shard = seq_len // cp
+    out = {"per_rank": []}
+    for g in range(cp):
+        tiles = [(r, c) for r in range(par_d) for c in range(par_d) if table[r, c] == g]
+        comp_t = _np.zeros(2)
+        for r, c in tiles:
+            comp_t += t_tile[bool(types[r, c] == 2)]
+        rows = {r for r, _ in tiles if cmap[r] != g}
+        cols = {c for _, c in tiles if cmap[c] != g}
+        # forward: pull Q rows and K, V columns; push (O, lse) of foreign rows
+        f_in = len(rows) * q_blk + len(cols) * 2 * kv_blk
+        f_out = len(rows) * (q_blk + batch * n_heads * blk * 4)
+        # backward (inputs staged by the forward are reused): pull dO, lse, D; push dQ (fp32), dK, dV (fp32)
+        b_in = len(rows) * (q_blk + 2 * batch * n_heads * blk * 4)
+        b_out = len(rows) * 2 * q_blk + len(cols) * 2 * 2 * kv_blk
+        link = [max(comm.get_comm_time_from_map_key((x,)) if x else 0.0 for x in pair)
+                for pair in ((f_in, f_out), (b_in, b_out))]
+        own_q = batch * shard * n_heads * head_dim
+        own_kv = batch * shard * hk * head_dim
+        mem_f = (2 * (own_q + 2 * own_kv) * es + len(rows) * 0 + 3 * own_q * es) / (hbm_gbs * 1e9)
+        mem_b = (2 * own_q * es + 2 * own_q * es            # copy-in of dO, D pre-pass reads O and dO
+                 + (own_q + 2 * own_kv) * (4 + es + 4)) / (hbm_gbs * 1e9)   # cast + clear of the accumulators
+        launch = _np.array([B200_LAUNCH_S * 3, B200_LAUNCH_S * 5])
+        total = _np.array([max(comp_t[0], link[0]) + mem_f, max(comp_t[1], link[1]) + mem_b]) + launch
+        out["per_rank"].append({"rank": g, "tiles": len(tiles), "compute_s": comp_t.tolist(), "link_s": link,
+                                "memory_s": [mem_f, mem_b], "total_s": total.tolist()})
+    out["fwd_s"] = max(r["total_s"][0] for r in out["per_rank"])
+    out["bwd_s"] = max(r["total_s"][1] for r in out["per_rank"])
+    out["step_s"] = out["fwd_s"] + out["bwd_s"]
+    return out
