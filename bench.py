@@ -257,6 +257,19 @@ def main() -> None:
     if rank == 0:
         vol = pattern.volume * (S / N_BLOCKS) ** 2 * 4 * HEAD_DIM * N_HEADS      # forward model FLOPs
         tflops = vol * 3.5 / (ms * 1e-3) / 1e12 / world
+        roof = None
+        try:        # achieved fraction of max(FLOPs at the measured GEMM peak, NVLink bytes at link bandwidth)
+            from ultraattn_b200.utils.metrics import load_peaks, roofline
+            tr = traffic if isinstance(traffic, dict) else {}
+            pull = sum(tr.get(k, 0) or 0 for k in ("fwd_pull_bytes", "fwd_multicast_in_bytes", "bwd_pull_bytes"))
+            push = sum(tr.get(k, 0) or 0 for k in ("fwd_push_bytes", "fwd_multicast_out_bytes", "bwd_push_bytes"))
+            peaks = load_peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
+            r = roofline(vol * 3.5 / world, max(pull, push), ms * 1e-3, peaks, sustained=True)
+            roof = {"bound": r["bound"], "target_ms": r["target_s"] * 1e3, "fraction": r["fraction"],
+                    "of": f"{peaks.get('source', 'measured')} sustained bf16 peak {peaks['bf16_tflops_sustained']} TFLOP/s, "
+                          "770 GB/s per NVLink direction"}
+        except Exception as e:  # noqa: BLE001  (never let the report break the benchmark line)
+            roof = {"error": f"{type(e).__name__}: {e}"}
         print(json.dumps({
             "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False,
@@ -266,7 +279,7 @@ def main() -> None:
                        "global_batch": 1, "seq_len": S, "parallelism": parallelism,
                        "l2": "inputs (4 GiB per tensor in total) far exceed the 126 MB L2; no flush needed"},
             "model_tflops_per_gpu": tflops, "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
-            "nvlink_bytes_rank0": traffic,
+            "nvlink_bytes_rank0": traffic, "roofline": roof,
         }))
     if world > 1:
         dist.destroy_process_group()
