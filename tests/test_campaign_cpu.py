@@ -32,6 +32,22 @@ def _worker(rank, world, port, root, ret):
         # a second pass is a no-op: everything is keyed in the database
         work2 = task1.step1_generate_intra_bsa_exe_plans(space, db, time_limit=2.0)
         assert len(work2) == len(work)
+        # dense_train: every (Y, X) grid of FULL attention, without and with kernel tile
+        from ultraattn_b200.plandb import full_plan_key, full_profile_suffix
+        full = BSA_Config.create_full((2, 1))
+        fspace = ExpSpace("dense_train", [0, 1], [full], [full], [256], [2], D=16, S_per_gpu_bounds=(1, 1 << 20))
+        keys = task1.step1_generate_intra_full_exe_plans(fspace, db)
+        if rank == 0:
+            assert full_plan_key(1, (2, 1), 1, 2) in keys and len(keys) == 4
+        task1.step2_profile_intra_full_exe_plans(fspace, db, torch.device("cpu"), world)
+        dist.barrier()
+        fresh = Prof_DB("unit", "cpu", root=root)
+        for fob in (0, 1):
+            fprefix = plan_key_prefix(fob, (2, 1), shape, full)
+            for Y, X in ((2, 1), (1, 2)):
+                for kt in (False, True):
+                    p = fresh.get_profile(fprefix + full_profile_suffix(kt, Y, X))
+                    assert p is not None and float(p["time"]) > 0 and float(p["sim_time"]) > 0, (fob, Y, X, kt)
     except Exception as e:  # noqa: BLE001
         import traceback
         ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"

@@ -14,7 +14,8 @@ import torch
 import torch.distributed as dist
 
 from ..parallel.comm import initialize_distribution
-from ..plandb import ABLATION_SUFFIXES, Prof_DB, allocation_key, plan_key_prefix
+from ..plandb import (ABLATION_SUFFIXES, Prof_DB, allocation_key, full_plan_key, full_profile_suffix,
+                      plan_key_prefix)
 from ..planner.allocate import naive_allocate_strategy, solve_sparse_from_bsa
 from ..planner.cost import Dist_Attn_Config, get_cc_optimal_schedule_from_table
 from ..planner.fuse import Graph_Transformation_Engine
@@ -106,6 +107,71 @@ def step2_profile_intra_bsa_exe_plans(work, prof_db, device, world: int) -> None
                 dist.barrier()
 
 
+def _full_configs(space) -> list:
+    from ..utils.bsa_helpers import bsa_is_full
+    return [c for c in space.intra_bsa_configs if bsa_is_full(c)]
+
+
+def step1_generate_intra_full_exe_plans(space, prof_db) -> list:
+    """FULL attention gets one shape-free manual plan per grid (Y, X) with Y * X = CP (reference:
+    search_algo/task1_bsa.py:672-697); returns the plan keys."""
+    from .intra_attn_gen import generate
+    keys = []
+    if not dist.is_initialized() or dist.get_rank() == 0:
+        for cp in sorted({c.CP[0] for c in _full_configs(space)}):
+            keys += generate(prof_db, cp, space.fobs)
+    if dist.is_initialized():
+        dist.barrier()
+    return keys
+
+
+def step2_profile_intra_full_exe_plans(space, prof_db, device, world: int) -> None:
+    """Measure every grid (Y, X) of FULL attention on the ranks running now, without kernel tile
+    (the manual launch plan: one launch and one message per tile) and with it (gathers, one
+    launch, merge / reduce-scatter), under the keys the inter-level planner looks up
+    (``..._ablation=({w/o_kernel_tile|w_kernel_tile},Y=..,X=..,dim=0)``; reference:
+    search_algo/task1_bsa.py:404-470)."""
+    from ..planner.dense import create_ablation_configs_for_full, create_plan_for_full
+    from ..runtime.grid import GridExecutor
+    from ..utils.misc import calc_flops
+    from .benchmark import benchmark_ops
+    for cfg in _full_configs(space):
+        if cfg.CP[0] != world:
+            continue
+        for shape in space.shape_configs(world):
+            for fob in space.fobs:
+                prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
+                for Y, X in create_ablation_configs_for_full(world):
+                    for kernel_tile in (False, True):
+                        key = prefix + full_profile_suffix(kernel_tile, Y, X)
+                        if prof_db.get_profile(key, 1) is not None:
+                            continue
+                        if not kernel_tile:
+                            pf = create_plan_for_full(world, X, 0, prof_db.m_config, shape_config=shape)
+                            pb = create_plan_for_full(world, X, 1, prof_db.m_config, shape_config=shape) if fob else None
+                            res = benchmark_orchestrate_bsa(pf, pb, fob, device)
+                        else:
+                            dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+                            gx = GridExecutor(Y, X, device=device)
+                            g = torch.Generator().manual_seed(dist.get_rank() if dist.is_initialized() else 0)
+                            S_loc = shape["S"][0] // world
+                            mk = lambda h: torch.randn(shape["bs"], S_loc, h, shape["D"], generator=g).to(dtype).to(device)
+                            q, k, v, d_o = mk(shape["Nh"][0]), mk(shape["Nh"][1]), mk(shape["Nh"][1]), mk(shape["Nh"][0])
+                            o, lse = gx.forward(q, k, v)
+                            fn = (lambda: gx.forward(q, k, v)) if fob == 0 else (lambda: gx.backward(d_o, q, k, v, o, lse))
+                            t = benchmark_ops(fn, 2, 2, 2, device)
+                            _, hw = calc_flops(shape["bs"], shape["S"], shape["Nh"][0], shape["D"], False, fob, 1.0)
+                            from ..planner.schedule import Fused_Execution_Plan
+                            sim = Fused_Execution_Plan(Y, X, None, fob, prof_db.m_config)
+                            from ..planner.cost import Dist_Attn_Config as _DA
+                            sim_t = sim.materialize(_DA.from_bsa_config(cfg, shape, 1))
+                            res = {"time": t, "hfu": hw / t / world / 1e12, "sim_time": float(sim_t)}
+                        if not dist.is_initialized() or dist.get_rank() == 0:
+                            prof_db.put_profile(key, res["hfu"], res["time"], res["sim_time"], 1)
+                        if dist.is_initialized():
+                            dist.barrier()
+
+
 def step3_generate_inter_bsa_exe_plans(space, prof_db, time_limit=20.0) -> list:
     prof_db.m_config_update_inter_bsa_profile()
     work = []
@@ -139,6 +205,9 @@ def main(argv=None) -> None:
     work = step1_generate_intra_bsa_exe_plans(space, prof_db)
     device = torch.device("cuda", info["local_rank"]) if torch.cuda.is_available() else torch.device("cpu")
     step2_profile_intra_bsa_exe_plans(work, prof_db, device, info["world_size"])
+    if _full_configs(space):                        # dense_train: the (Y, X) grids of FULL attention
+        step1_generate_intra_full_exe_plans(space, prof_db)
+        step2_profile_intra_full_exe_plans(space, prof_db, device, info["world_size"])
     step3_generate_inter_bsa_exe_plans(space, prof_db)
     print_rank_0("task1 done")
     if dist.is_initialized():
