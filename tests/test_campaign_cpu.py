@@ -150,3 +150,27 @@ def test_single_configuration_driver(tmp_path, capsys):
     lines = [json.loads(line) for line in (tmp_path / "rank0.out").read_text().strip().splitlines()]
     timed = [r for r in lines if "time_ms" in r]
     assert [r["fob"] for r in timed] == [0, 1] and all(r["time_ms"] > 0 and r["n_ranks"] == 2 for r in timed)
+
+
+def test_step4_full_attention_takes_the_best_grid(tmp_path):
+    """Single node, FULL attention: every ablation level of the inter profile is the best (Y, X)
+    grid measurement that level may use."""
+    from ultraattn_b200.drivers import task2
+    from ultraattn_b200.drivers.exp_configs import ExpSpace
+    from ultraattn_b200.patterns.blocks import BSA_Config
+    from ultraattn_b200.plandb import Prof_DB, full_profile_suffix, plan_key_prefix
+    full = BSA_Config.create_full((2, 1))
+    space = ExpSpace("dense_train", [0], [full], [full], [256], [2], D=16, S_per_gpu_bounds=(1, 1 << 20))
+    db = Prof_DB("unit", "cpu", root=str(tmp_path))
+    shape = {"S": (256, 256), "Nh": (2, 2), "bs": 1, "D": 16}
+    prefix = plan_key_prefix(0, (2, 1), shape, full)
+    times = {(False, 2, 1): 4e-3, (False, 1, 2): 3e-3, (True, 2, 1): 2e-3, (True, 1, 2): 5e-3}
+    for (kt, Y, X), t in times.items():
+        db.put_profile(prefix + full_profile_suffix(kt, Y, X), 1.0, t, t, 1)
+    task2.step4_profile_inter_bsa_exe_plans(space, db, world=2)
+    got = {s: float(db.get_profile(prefix + s, 0)["time"]) for s in
+           ("_ablation=(w/o_gpu_tile,w/o_kernel_tile,Flexflow)", "_ablation=(w/o_kernel_tile,ILP)",
+            "_ablation=(w_kernel_tile,ILP)")}
+    assert got["_ablation=(w/o_gpu_tile,w/o_kernel_tile,Flexflow)"] == 4e-3      # Y = CP, X = 1 only
+    assert got["_ablation=(w/o_kernel_tile,ILP)"] == 3e-3                         # best grid without kernel tile
+    assert got["_ablation=(w_kernel_tile,ILP)"] == 2e-3                           # best of all

@@ -66,6 +66,13 @@ def step4_profile_inter_bsa_exe_plans(space, prof_db, world: int) -> None:
                 prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
                 for suf in ABLATION_SUFFIXES:
                     intra = prof_db.get_profile(prefix + suf, 1)
+                    if intra is None and cfg.CP[1] == 1 and cfg.bsa_repr.check_full():
+                        # FULL attention is measured per (Y, X) grid: an ablation level stands for
+                        # the best grid it may use (reference: search_algo/bsa_utils.py:53-70)
+                        from ..utils.bsa_helpers import get_b2f_suf_map
+                        cands = [prof_db.get_profile(prefix + s, 1) for s in get_b2f_suf_map(cfg.CP[0])[suf]]
+                        cands = [c for c in cands if c is not None]
+                        intra = min(cands, key=lambda c: float(c["time"])) if cands else None
                     if intra is not None and cfg.CP[1] == 1:
                         prof_db.put_profile(prefix + suf, intra["hfu"], float(intra["time"]),
                                             float(intra["sim_time"]), 0)
