@@ -48,6 +48,23 @@ def _worker(rank, world, port, root, ret):
                 for kt in (False, True):
                     p = fresh.get_profile(fprefix + full_profile_suffix(kt, Y, X))
                     assert p is not None and float(p["time"]) > 0 and float(p["sim_time"]) > 0, (fob, Y, X, kt)
+        # step 4 + baselines: the figure table gets its ring / zigzag / stripe columns
+        from ultraattn_b200.drivers import report, task2
+        causal = BSA_Config.create_causal((2, 1))
+        cspace = ExpSpace("dense_train", [0], [causal], [causal], [256], [2], D=16, S_per_gpu_bounds=(1, 1 << 20))
+        task2.step4_profile_inter_bsa_exe_plans(space, db, world)
+        keys = task2.step5_profile_baselines(space, db, torch.device("cpu"), world, iters=1)
+        keys += task2.step5_profile_baselines(cspace, db, torch.device("cpu"), world, iters=1)
+        assert [k.rsplit("_", 1)[1] for k in keys] == ["ring", "ring", "zigzag", "stripe"]
+        dist.barrier()
+        if rank == 0:
+            import json
+            prof = json.loads(open(db.INTER_BSA_EXE_PLANS_PROFILE).read())
+            rows = {r["key"]: r for r in report.build_rows(prof)}
+            star_row = rows[plan_key_prefix(0, (2, 1), shape, cfg)]
+            assert star_row["ring"] > 0 and star_row["ultraattn"] > 0 and star_row["speedup_vs_ring"] > 0
+            causal_row = rows[plan_key_prefix(0, (2, 1), shape, causal)]
+            assert causal_row["zigzag"] > 0 and causal_row["stripe"] > 0
     except Exception as e:  # noqa: BLE001
         import traceback
         ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"

@@ -31,6 +31,15 @@ def _one_baseline(rank, world, kind, causal):
     S, H, D = 256, 4, 16
     g = torch.Generator().manual_seed(0)
     q, k, v, d_o = (torch.randn(1, S, H, D, generator=g) for _ in range(4))
+    if kind.startswith("bsa:"):                     # the ring under a block-sparse pattern
+        pat = {"strided": P.strided(8, 4, 2), "global_local": P.global_local(8, 1, 2), "star": P.star(4, 1)}[kind[4:]]
+        sh = lambda t: PL.shard_sequence(t, rank, world, "ring")
+        ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
+        o = PL.block_sparse_ring_attn_func(ql, kl, vl, pat)
+        o.backward(sh(d_o))
+        o_ref, _, dq, dk, dv = P.dense_attention_with_grads(q, k, v, d_o, pat)
+        return max((o - sh(o_ref)).abs().max().item(), (ql.grad - sh(dq)).abs().max().item(),
+                   (kl.grad - sh(dk)).abs().max().item(), (vl.grad - sh(dv)).abs().max().item())
     sh = lambda t: PL.shard_sequence(t, rank, world, kind)
     ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
     fn = {"ring": PL.ring_flash_attn_func, "zigzag": PL.zigzag_ring_flash_attn_func,
@@ -51,8 +60,10 @@ def _check(ret, world):
 
 
 def test_baselines_world4():
-    """Ring (causal and full), zigzag, stripe and Ulysses on four ranks, one process group."""
-    cases = [("ring", True), ("ring", False), ("zigzag", True), ("stripe", True), ("ulysses", True)]
+    """Ring (causal and full), zigzag, stripe, Ulysses and the ring under three block-sparse
+    patterns on four ranks, one process group."""
+    cases = [("ring", True), ("ring", False), ("zigzag", True), ("stripe", True), ("ulysses", True),
+             ("bsa:strided", False), ("bsa:global_local", False), ("bsa:star", False)]
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(4, 29900 + os.getpid() % 90, cases, ret), nprocs=4, join=True)
     _check(ret, 4)

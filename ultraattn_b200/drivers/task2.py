@@ -78,6 +78,60 @@ def step4_profile_inter_bsa_exe_plans(space, prof_db, world: int) -> None:
                                             float(intra["sim_time"]), 0)
 
 
+def step5_profile_baselines(space, prof_db, device, world: int, iters: int = 2) -> list:
+    """Measure the ring-family baselines of every configuration that fits the ranks running now and
+    store them beside the plans' profiles under the suffixes the figure tables read (``_ring``,
+    ``_zigzag``, ``_stripe``; reference: plot/common.py:48-53, whose baseline rows come from a
+    separate repository). Dense causal gets all three, dense full the ring; block-sparse patterns
+    get the ring that skips the block pairs the pattern leaves out. Returns the keys written."""
+    import torch
+    from ..parallel import ring as R
+    from ..utils.bsa_helpers import bsa_is_causal, bsa_is_full
+    from ..utils.misc import calc_flops
+    from .benchmark import benchmark_ops
+    written = []
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    for fob in space.fobs:
+        for cfg in space.inter_bsa_configs:
+            if cfg.CP[0] * cfg.CP[1] != world:
+                continue
+            kinds = ["ring", "zigzag", "stripe"] if bsa_is_causal(cfg) else ["ring"]
+            dense = bsa_is_causal(cfg) or bsa_is_full(cfg)
+            types = None
+            if not dense:
+                import math
+                n = cfg.bsa_repr.table.shape[0]
+                types = cfg.bsa_repr.refined(n * world // math.gcd(n, world))
+            for shape in space.shape_configs(world):
+                prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
+                S_loc = shape["S"][0] // world
+                if types is not None and S_loc % (types.shape[0] // world):
+                    continue
+                g = torch.Generator().manual_seed(rank)
+                mk = lambda h: torch.randn(shape["bs"], S_loc, h, shape["D"], generator=g).to(dtype).to(device)
+                q, k, v, d_o = mk(shape["Nh"][0]), mk(shape["Nh"][1]), mk(shape["Nh"][1]), mk(shape["Nh"][0])
+                for kind in kinds:
+                    key = prefix + "_" + kind
+                    if prof_db.get_profile(key, 0) is not None:
+                        continue
+                    causal = bsa_is_causal(cfg)
+                    o, lse = R.ring_forward(q, k, v, None, kind, causal, block_types=types)
+                    if fob == 0:
+                        fn = lambda: R.ring_forward(q, k, v, None, kind, causal, block_types=types)
+                    else:
+                        fn = lambda: R.ring_backward(d_o, q, k, v, o, lse, None, kind, causal, block_types=types)
+                    t = benchmark_ops(fn, 2, iters, 2, device)
+                    _, hw = calc_flops(shape["bs"], shape["S"], shape["Nh"][0], shape["D"], False, fob,
+                                       cfg.total_sparsity)
+                    if rank == 0:
+                        prof_db.put_profile(key, hw / t / world / 1e12, t, 0.0, 0)
+                    written.append(key)
+                    if dist.is_initialized():
+                        dist.barrier()
+    return written
+
+
 def main(argv=None) -> None:
     args = parse_args(argv)
     info = initialize_distribution()
@@ -85,6 +139,10 @@ def main(argv=None) -> None:
     space = step0_top_down_decompose(args.exp_class or "bsa_train", max_intra=info["tasks_per_node"],
                                      max_nodes=info["node_num"], quick=bool(args.extra.get("quick")))
     step4_profile_inter_bsa_exe_plans(space, prof_db, info["world_size"])
+    import torch
+    device = torch.device("cuda", info["local_rank"]) if torch.cuda.is_available() else torch.device("cpu")
+    if info["world_size"] > 1:
+        step5_profile_baselines(space, prof_db, device, info["world_size"])
     print_rank_0("task2 done")
     if dist.is_initialized():
         dist.barrier()

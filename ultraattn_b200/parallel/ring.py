@@ -56,8 +56,27 @@ _RULES = {"ring": _ring_rule, "zigzag": _zigzag_rule, "stripe": _stripe_rule}
 _NAMES = {"ring": "ring_flash_attn", "zigzag": "zigzag_ring_flash_attn", "stripe": "stripe_flash_attn"}
 
 
-def _work(kind, src, rank, bounds, causal):
+def _table_work(types, world, src, rank, S):
+    """Work of one ring step under a block table: ``types`` is the pattern refined to a multiple of
+    the ring size (0 empty, 1 full, 2 causal) and every rank owns ``len(types) / world``
+    consecutive blocks of ``S / that`` tokens. Query block i of ``rank`` meets key block j of
+    ``src`` iff the table says so; empty pairs are skipped, which is all the block sparsity a ring
+    can exploit (the blocks still travel)."""
+    per = types.shape[0] // world
+    blk = S // per
+    out = []
+    for i in range(per):
+        segs = [(j * blk, blk, int(types[rank * per + i, src * per + j]) == 2, 0)
+                for j in range(per) if int(types[rank * per + i, src * per + j])]
+        if segs:
+            out.append((i * blk, blk, segs))
+    return out
+
+
+def _work(kind, src, rank, bounds, causal, types=None, world=None):
     """The rule applied to every packed sequence ((start, end) pairs of this rank's shard)."""
+    if types is not None:
+        return _table_work(types, world, src, rank, bounds[0][1] - bounds[0][0])
     out = []
     for a, b in bounds:
         w = _RULES[kind](src, rank, b - a, causal) if b > a else None
@@ -155,10 +174,13 @@ def _route(group):
     return _Route(group)
 
 
-def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None, bounds=None, q_rank=None):
+def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None, bounds=None, q_rank=None,
+                 block_types=None):
     """``group``: a process group (flat ring) or ``{'intra': pg, 'inter': pg}`` (two-level ring).
     ``bounds``: (start, end) of every packed sequence in this rank's shard; default one sequence.
-    ``q_rank``: ring position of the rank that owns the queries, when they are a visitor's."""
+    ``q_rank``: ring position of the rank that owns the queries, when they are a visitor's.
+    ``block_types``: a block table (pattern refined to a multiple of the ring size) that replaces
+    the dense rule of ``kind``: the ring baseline for block-sparse patterns."""
     set_comm_phase("fwd")
     route = _route(group)
     q_rank = route.rank if q_rank is None else q_rank
@@ -175,7 +197,7 @@ def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None, bo
             lvl = route.level_after(step)
             nk, nv = comms[lvl].send_recv(k), comms[lvl].send_recv(v)
             comms[lvl].commit()
-        work = _work(kind, route.src, q_rank, bounds, causal)
+        work = _work(kind, route.src, q_rank, bounds, causal, block_types, route.world)
         if work:
             A.attn_fwd([q], [k], [v], [(o, lse)], A.FwdPlan(_fwd_rows(work, started), q.device), softmax_scale)
             started = True
@@ -187,7 +209,7 @@ def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None, bo
 
 
 def ring_backward(d_o, q, k, v, o, lse, group, kind: str, causal: bool, softmax_scale=None, bounds=None,
-                  q_rank=None, keep_f32: bool = False):
+                  q_rank=None, keep_f32: bool = False, block_types=None):
     """``keep_f32``: return the fp32 accumulators instead of casting to the input dtype."""
     set_comm_phase("bwd")
     route = _route(group)
@@ -209,7 +231,7 @@ def ring_backward(d_o, q, k, v, o, lse, group, kind: str, causal: bool, softmax_
             lvl = route.level_after(step)
             nk, nv = kv_comms[lvl].send_recv(k), kv_comms[lvl].send_recv(v)
             kv_comms[lvl].commit()
-        work = _work(kind, route.src, q_rank, bounds, causal)
+        work = _work(kind, route.src, q_rank, bounds, causal, block_types, route.world)
         if work:
             A.attn_bwd([side], [k], [v], [A.BwdKvOut(dk, dv)], A.BwdPlan(_bwd_cols(work), q.device),
                        softmax_scale)
@@ -229,18 +251,32 @@ def ring_backward(d_o, q, k, v, o, lse, group, kind: str, causal: bool, softmax_
 
 class _RingFunc(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, softmax_scale, causal, group, kind, bounds=None):
-        o, lse = ring_forward(q, k, v, group, kind, causal, softmax_scale, bounds)
+    def forward(ctx, q, k, v, softmax_scale, causal, group, kind, bounds=None, block_types=None):
+        o, lse = ring_forward(q, k, v, group, kind, causal, softmax_scale, bounds, block_types=block_types)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.args = (softmax_scale, causal, group, kind, bounds)
+        ctx.args = (softmax_scale, causal, group, kind, bounds, block_types)
         return o, lse
 
     @staticmethod
     def backward(ctx, d_o, _dlse):
         q, k, v, o, lse = ctx.saved_tensors
-        scale, causal, group, kind, bounds = ctx.args
-        dq, dk, dv = ring_backward(d_o.contiguous(), q, k, v, o, lse, group, kind, causal, scale, bounds)
-        return dq, dk, dv, None, None, None, None, None
+        scale, causal, group, kind, bounds, block_types = ctx.args
+        dq, dk, dv = ring_backward(d_o.contiguous(), q, k, v, o, lse, group, kind, causal, scale, bounds,
+                                   block_types=block_types)
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+def block_sparse_ring_attn_func(q, k, v, pattern, softmax_scale=None, group=None, return_lse: bool = False):
+    """Ring attention under a block-sparse pattern: the K/V ring of :func:`ring_flash_attn_func`
+    with contiguous shards, where every step computes only the block pairs that the pattern
+    allows. This is what a ring-based context-parallel system can do with block sparsity (skip
+    compute, still move every block), i.e. the "Ring" baseline of the block-sparse comparisons."""
+    world = dist.get_world_size(group)
+    n = pattern.table.shape[0]
+    par_d = n * world // math.gcd(n, world)
+    types = pattern.refined(par_d)
+    o, lse = _RingFunc.apply(q, k, v, softmax_scale, False, group, "ring", None, types)
+    return (o, lse) if return_lse else o
 
 
 def _check_unsupported(dropout_p, alibi_slopes, window_size):
