@@ -7,7 +7,7 @@ Configurations: ``causal128k`` (dense causal, S = 128k, forward + backward), ``s
 (32 blocks of 16k, stride 4, window 2, forward + backward), ``gl512k`` (global+local, block 0
 global, causal window 2, forward + backward), ``star512k`` and ``streaming512k`` (prefill, forward
 only); all with 32 heads of 128, batch 1, bf16. Paths: ``fused`` (peer-memory kernels), ``nccl``
-(plan executed with NCCL messages), ``ring`` / ``zigzag`` (ring baselines; dense patterns only),
+(plan executed with NCCL messages), ``ring`` (K/V ring; under a block-sparse pattern it skips the excluded block pairs) / ``zigzag`` (dense causal),
 ``grid<Y>x<X>`` (kernel-tile form: gathers, one launch, merge / reduce-scatter; dense patterns only).
 
 Every line carries the device time (max over ranks), the model TFLOP/s per GPU and the achieved
@@ -102,7 +102,8 @@ def main() -> None:
         for path in a.paths.split(","):
             if world == 1 and path != "fused":
                 continue
-            if (path in ("ring", "zigzag") or path.startswith("grid")) and not (pat.check_causal() and n == 1 or pat.check_full()):
+            dense = pat.check_causal() and n == 1 or pat.check_full()
+            if (path == "zigzag" or path.startswith("grid")) and not dense:
                 continue
             if path.startswith("grid") and math.prod(int(t) for t in path[4:].split("x")) != world:
                 continue
@@ -144,12 +145,15 @@ def main() -> None:
                 else:
                     kind = path
                     qs, ks, vs = (t.clone().requires_grad_() for t in (q, k, v))
+                    # block-sparse patterns: the ring that skips the block pairs the pattern excludes
+                    types = None if dense else pat.refined(n * world // math.gcd(n, world))
 
                     def step():
-                        o_, l_ = R.ring_forward(qs.detach(), ks.detach(), vs.detach(), None, kind, pat.check_causal())
+                        o_, l_ = R.ring_forward(qs.detach(), ks.detach(), vs.detach(), None, kind, pat.check_causal(),
+                                                block_types=types)
                         if train:
                             R.ring_backward(d_o, qs.detach(), ks.detach(), vs.detach(), o_, l_, None, kind,
-                                            pat.check_causal())
+                                            pat.check_causal(), block_types=types)
                 ms = _timed(step, a.iters, dev, world)
                 A.check_status(dev)
                 t_comp = flops / world / (peak * 1e12)
