@@ -79,12 +79,21 @@ def _replan_worker(rank, world, port, ret):
             return max((o - o_ref[:, sl]).abs().max().item(), (ql.grad - dq_ref[:, sl]).abs().max().item(),
                        (kl.grad - dk_ref[:, sl]).abs().max().item(), (vl.grad - dv_ref[:, sl]).abs().max().item())
 
+        from ultraattn_b200.runtime.heartbeat import StepHeartbeat
+        hb = StepHeartbeat()
         rt = ContextParallelAttention(pat, S, H, D, device=torch.device("cpu"), path="nccl", dtype=torch.float32,
                                       plan_time_limit=3.0)
+        hb.beat(0)
+        assert hb.missing(0, timeout_s=20.0) == []
         err = run(rt, rank, world)
-        # ranks 2 and 3 leave between two steps; the survivors re-plan for two ranks and go on
+        # between two steps rank 2 says good-bye and rank 3 just stops announcing; the survivors
+        # notice on the host before launching anything, re-plan for two ranks and go on
+        if rank == 2:
+            hb.leave()
         if rank < 2:
-            sub = dist.new_group([0, 1], use_local_synchronization=True)
+            hb.beat(1)
+            assert hb.missing(1, timeout_s=1.5) == [2, 3] and hb.alive == [0, 1]
+            sub = dist.new_group(hb.alive, use_local_synchronization=True)
             rt2 = rt.replan(sub)
             assert rt2.world == 2 and rt2.table.shape[0] >= 2
             err = max(err, run(rt2, rank, 2))

@@ -3,3 +3,4 @@ from .executor import FaultInjector, PlanExecutor
 from .fused import FakeSpace, FusedContextParallel, PeerSpace, SymmMemSpace
 from .grid import GridExecutor
 from .verify import verify_fused_tables
+from .heartbeat import StepHeartbeat
