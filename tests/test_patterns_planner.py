@@ -168,3 +168,30 @@ def test_causal8_not_worse_than_the_published_table():
         ours = solve_sparse_from_bsa(cfg, fob=fob, ParD=8, time_limit=5.0)
         assert ours.comm_volume <= theirs + 1e-9, (fob, ours.comm_volume, theirs)
         assert ours.comp_max <= comp_volumes(published, vol, 8).max() + 1e-9
+
+
+def test_document_mask_pattern_matches_packed_attention_and_plans():
+    """A packed batch of documents as a block table: same result as the packed (cu_seqlens)
+    operator, and it goes through allocation and scheduling like any other pattern."""
+    import torch
+    from ultraattn_b200 import patterns as P
+    from ultraattn_b200.api import varlen_attention
+    from ultraattn_b200.planner import make_plan
+    pat = P.document([2, 1, 3, 2])
+    assert str(pat) == "[[20000000][12000000][00200000][00020000][00012000][00011200][00000020][00000012]]"
+    blk, H, D = 16, 2, 8
+    T = 8 * blk
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(1, T, H, D) for _ in range(3))
+    o_pat, _ = P.dense_attention(q, k, v, pat.token_mask(T, T))
+    cu = [0, 2 * blk, 3 * blk, 6 * blk, 8 * blk]
+    o_var = varlen_attention(q[0], k[0], v[0], cu, causal=True)
+    assert (o_pat[0] - o_var).abs().max().item() < 1e-5
+    full_docs = P.document([1, 3], causal_docs=False)
+    assert full_docs.block_table_int.tolist() == [[1, 0, 0, 0], [0, 1, 1, 1], [0, 1, 1, 1], [0, 1, 1, 1]]
+    for fob in (0, 1):
+        plan = make_plan(pattern=pat, cp=4, seq_len=T, n_heads=H, head_dim=D, fob=fob, allocation="ilp",
+                         plan_type="Flexflow", time_limit=3.0)
+        assert plan.verify() == []
+        # documents that fit one rank's blocks need no traffic at all for that rank's rows
+        assert plan.allocation.comm_volume <= 4

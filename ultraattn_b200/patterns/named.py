@@ -79,10 +79,27 @@ def streaming(n_blocks: int, n_sink: int = 1, window: int = 1) -> BSA_Repr:
     return BSA_Repr(t)
 
 
+def document(doc_blocks, causal_docs: bool = True) -> BSA_Repr:
+    """Document mask for a packed batch whose documents are whole numbers of blocks long:
+    ``doc_blocks[i]`` blocks for document i. Tokens attend only their own document (causally, or
+    fully with ``causal_docs=False``), so the table is block-diagonal. The reference lists this
+    mask as future work (README.md:71); as a block table it goes through the same planner and
+    runtimes as every other pattern, which gives context parallelism over packed documents."""
+    n = int(sum(doc_blocks))
+    t = np.zeros((n, n), dtype=np.int8)
+    a = 0
+    for d in doc_blocks:
+        for i in range(a, a + d):
+            for j in range(a, (i if causal_docs else a + d - 1) + 1):
+                t[i, j] = (CAUSAL if i == j else FULL) if causal_docs else FULL
+        a += d
+    return BSA_Repr(t)
+
+
 def by_name(name: str, **kw) -> BSA_Repr:
     table = {"full": full, "causal": causal, "strided": strided, "stride": strided,
              "global_local": global_local, "local_global": global_local, "lg": global_local,
-             "star": star, "streaming": streaming, "stream": streaming}
+             "star": star, "streaming": streaming, "stream": streaming, "document": document}
     if name not in table:
         raise KeyError(f"unknown pattern {name!r}; choose from {sorted(set(table))}")
     return table[name](**kw)
