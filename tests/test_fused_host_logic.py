@@ -82,6 +82,7 @@ def _one_step(ranks, pattern, world, S, H, D, seed):
     ("global-local-ilp", lambda: P.global_local(8, 1, 2), 2, "ilp"),
     ("star-naive", lambda: P.star(4, 1), 2, "naive"),
     ("full-ilp", lambda: P.full(1), 4, "ilp"),
+    ("documents-ilp", lambda: P.document([2, 1, 3, 2]), 4, "ilp"),
     ("causal-lightseq-4", lambda: P.causal(1), 4, "lightseq"),
     ("causal-lightseq-8", lambda: P.causal(1), 8, "lightseq"),
 ], ids=lambda x: x if isinstance(x, str) else None)
