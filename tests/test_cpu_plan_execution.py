@@ -6,7 +6,6 @@ causal local window of 2 blocks), 4 heads, D=64, fp32, world size 2; ILP plan, f
 import os
 import sys
 
-import numpy as np
 import pytest
 import torch
 import torch.distributed as dist

@@ -162,7 +162,6 @@ def test_static_verifier_accepts_the_tables_and_catches_damage(name, world, mult
     """The memory-level plan check: the tables every rank builds pass; a doubled mailbox writer, a
     dropped wait and a tile moved to another rank are each reported."""
     import dataclasses
-    from ultraattn_b200.ops import attention as A
     from ultraattn_b200.runtime.verify import verify_fused_tables
     pattern = {"strided": P.strided(8, 4, 2), "global_local": P.global_local(8, 1, 2), "causal": P.causal(1)}[name]
     ranks = _build_ranks(pattern, world, allocation="naive" if multicast else "ilp", multicast=multicast,

@@ -3,7 +3,6 @@ CPU ranks against dense attention."""
 import os
 import sys
 
-import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp

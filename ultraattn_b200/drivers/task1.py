@@ -14,8 +14,7 @@ import torch
 import torch.distributed as dist
 
 from ..parallel.comm import initialize_distribution
-from ..plandb import (ABLATION_SUFFIXES, Prof_DB, allocation_key, full_plan_key, full_profile_suffix,
-                      plan_key_prefix)
+from ..plandb import ABLATION_SUFFIXES, Prof_DB, allocation_key, full_profile_suffix, plan_key_prefix
 from ..planner.allocate import naive_allocate_strategy, solve_sparse_from_bsa
 from ..planner.cost import Dist_Attn_Config, get_cc_optimal_schedule_from_table
 from ..planner.fuse import Graph_Transformation_Engine
