@@ -223,3 +223,21 @@ def test_fused_step_time_model():
     assert ilp["step_s"] < naive["step_s"]
     assert 0.9 < one["step_s"] / (8 * ilp["step_s"]) <= 1.02          # near-linear strong scaling predicted
     assert all(r["link_s"][1] < r["compute_s"][1] for r in ilp["per_rank"])   # compute-bound on NVLink 5
+
+
+def test_ring_time_model_and_predictions():
+    """The ring model: contiguous causal shards are bound by the last rank, zigzag is not; a
+    block-sparse pattern saves the ring compute but not transfers; the fused runtime is predicted
+    ahead of the ring on the sparse configs."""
+    from ultraattn_b200.drivers.predict import predict
+    from ultraattn_b200.planner.cost import ring_step_time
+    ring = ring_step_time(P.causal(1), 8, 131072, 32)
+    zig = ring_step_time(P.causal(1), 8, 131072, 32, kind="zigzag")
+    assert 1.6 < ring["step_s"] / zig["step_s"] < 2.0            # (CP) / (CP + 1) / 2 of the work per step
+    dense = ring_step_time(P.full(1), 8, 524288, 32)
+    sparse = ring_step_time(P.star(32, 1), 8, 524288, 32)
+    assert sparse["fwd_s"] < dense["fwd_s"]
+    rec = predict("star512k", 4, time_limit=3.0)
+    assert rec["speedup_fwd"] > 1.5 and "fused_bwd_ms" not in rec
+    rec = predict("causal128k", 2, time_limit=3.0)
+    assert abs(rec["zigzag_fwd_ms"] + rec["zigzag_bwd_ms"] - 242.6) / 242.6 < 0.1     # measured on 2 B200: 242.6 ms

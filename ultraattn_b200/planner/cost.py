@@ -540,3 +540,48 @@ def fused_step_time(table, cmap, pattern, seq_len: int, n_heads: int, head_dim: 
     out["bwd_s"] = max(r["total_s"][1] for r in out["per_rank"])
     out["step_s"] = out["fwd_s"] + out["bwd_s"]
     return out
+
+
+def ring_step_time(pattern, cp: int, seq_len: int, n_heads: int, head_dim: int = 128,
+                   m_config: Optional["Machine_Config"] = None, n_kv_heads: Optional[int] = None,
+                   batch: int = 1, kind: str = "ring") -> dict:
+    """Predicted forward and backward time of the ring baselines (``parallel/ring.py``) with
+    contiguous shards: ``cp`` steps; in every step a rank computes the block pairs that the
+    pattern allows between its queries and the visiting K/V shard (one launch) while the next
+    shard travels (K and V forward; in the backward also the fp32 dK, dV that ride along), and a
+    step ends when both are done, on the slowest rank. ``kind="zigzag"`` models the balanced
+    causal layout (every rank does the same share of every step). A block-sparse pattern lets the
+    ring skip compute but not transfers, which is why its advantage shrinks with sparsity."""
+    import numpy as _np
+    m = m_config or Machine_Config.b200_default()
+    comp, comm = m.comp_profile_maps[1], m.comm_profile_maps[1]
+    hk = n_kv_heads or n_heads
+    n = pattern.table.shape[0]
+    par_d = n * cp // math.gcd(n, cp)
+    types = pattern.refined(par_d)
+    per = par_d // cp
+    blk = seq_len // par_d
+    t_tile = {c: _np.maximum(comp.get_comp_time_from_map_key((blk, batch, n_heads, head_dim, "1/1", c))
+                             - B200_LAUNCH_S, 1e-7) for c in (False, True)}
+    kv_bytes = 2 * batch * (seq_len // cp) * hk * head_dim * 2
+    t_kv = comm.get_comm_time_from_map_key((kv_bytes,))
+    t_dkv = comm.get_comm_time_from_map_key((2 * kv_bytes,))          # fp32 dK, dV
+    fwd = bwd = 0.0
+    for step in range(cp):
+        worst = _np.zeros(2)
+        total = _np.zeros(2)
+        for rank in range(cp):
+            src = (rank - step) % cp
+            t = _np.zeros(2)
+            for i in range(per):
+                for j in range(per):
+                    ty = int(types[rank * per + i, src * per + j])
+                    if ty:
+                        t += t_tile[ty == 2]
+            worst = _np.maximum(worst, t)
+            total += t
+        work = total / cp if kind == "zigzag" else worst
+        last = step + 1 == cp
+        fwd += max(work[0] + B200_LAUNCH_S, 0.0 if last else t_kv)
+        bwd += max(work[1] + B200_LAUNCH_S, t_dkv + (0.0 if last else t_kv))
+    return {"fwd_s": fwd, "bwd_s": bwd, "step_s": fwd + bwd}
