@@ -5,7 +5,7 @@ CLUSTER_NAME ?= local
 PLATFORM ?= B200
 export CLUSTER_NAME PLATFORM
 
-.PHONY: build test test-gpu bench cluster_profile bsa_train dense_train bsa_infer report plan fusion_table full_plans
+.PHONY: build test test-gpu bench cluster_profile bsa_train dense_train bsa_infer report plan fusion_table full_plans predict
 CONFIG ?= configs/stride.yaml
 
 build:            ## compile the sm_100a kernel library in-tree (nvcc; works without a GPU)
@@ -39,3 +39,6 @@ fusion_table:     ## speed-up of fused x-by-y tiles over single tiles, from the 
 
 full_plans:       ## all Y x X plans of full attention for $(GPUS) ranks into the plan database
 	$(PY) -m ultraattn_b200.drivers.intra_attn_gen --cp $(GPUS)
+
+predict:          ## cost-model predictions: fused runtime against the ring baselines for the named configs
+	$(PY) -m ultraattn_b200.drivers.predict
