@@ -124,8 +124,12 @@ def step5_profile_baselines(space, prof_db, device, world: int, iters: int = 2) 
                     t = benchmark_ops(fn, 2, iters, 2, device)
                     _, hw = calc_flops(shape["bs"], shape["S"], shape["Nh"][0], shape["D"], False, fob,
                                        cfg.total_sparsity)
+                    from ..planner.cost import ring_step_time
+                    model = ring_step_time(cfg.bsa_repr, world, shape["S"][0], shape["Nh"][0], shape["D"],
+                                           prof_db.m_config, shape["Nh"][1], shape["bs"],
+                                           "ring" if kind == "ring" else "zigzag")
                     if rank == 0:
-                        prof_db.put_profile(key, hw / t / world / 1e12, t, 0.0, 0)
+                        prof_db.put_profile(key, hw / t / world / 1e12, t, model["fwd_s" if fob == 0 else "bwd_s"], 0)
                     written.append(key)
                     if dist.is_initialized():
                         dist.barrier()
