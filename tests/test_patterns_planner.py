@@ -195,3 +195,30 @@ def test_document_mask_pattern_matches_packed_attention_and_plans():
         assert plan.verify() == []
         # documents that fit one rank's blocks need no traffic at all for that rank's rows
         assert plan.allocation.comm_volume <= 4
+
+
+def test_context_remap_search_and_execution():
+    """The remap stage: for the strided pattern an ownership map other than contiguous chunks is
+    at least as cheap and is found; attention over the permuted sequence with the permuted
+    pattern equals the original attention, token for token."""
+    import torch
+    from ultraattn_b200.planner.allocate import apply_block_permutation, search_context_remap
+    pat = P.strided(8, 4, 2)
+    cfg = BSA_Config(None, None, {"bsa_repr": pat, "CP": (4, 1)})
+    res = search_context_remap(cfg, fob=0, time_limit=3.0)
+    assert set(res["scores"]) == {"contiguous", "strided", "zigzag"}
+    assert res["scores"][res["name"]] == min(res["scores"].values())
+    assert res["scores"][res["name"]] <= res["scores"]["contiguous"]
+    perm = res["permutation"]
+    assert sorted(perm.tolist()) == list(range(8))
+    # rank r owns blocks perm[2r], perm[2r + 1]: contiguous in the permuted order
+    assert all(res["cmap"][perm[2 * r]] == r and res["cmap"][perm[2 * r + 1]] == r for r in range(4))
+    torch.manual_seed(0)
+    S, H, D = 128, 2, 8
+    q, k, v = (torch.randn(1, S, H, D) for _ in range(3))
+    o, _ = P.dense_attention(q, k, v, pat.token_mask(S, S))
+    qp, kp, vp = (apply_block_permutation(t, perm) for t in (q, k, v))
+    mask_p = apply_block_permutation(apply_block_permutation(pat.token_mask(S, S), perm, 0), perm, 1)
+    op, _ = P.dense_attention(qp, kp, vp, mask_p)
+    inv = np.argsort(perm)
+    assert torch.allclose(apply_block_permutation(op, inv), o, atol=1e-6)

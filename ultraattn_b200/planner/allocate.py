@@ -398,3 +398,49 @@ def brute_force_allocate(bsa_config: BSA_Config, fob: int = 0, ParD: Optional[in
         comp_ub += 0.5
     return Allocation(par_d, cm, best[1], float(best[0]), float(comp_volumes(best[1], vol, cp).max()),
                       "optimal")
+
+
+def search_context_remap(bsa_config: BSA_Config, fob: int = 0, ParD: Optional[int] = None,
+                         candidates=("contiguous", "strided", "zigzag"), time_limit: float = 10.0) -> dict:
+    """Context remap as a planner stage: try a small set of ownership maps (which rank owns which
+    block of the sequence) and keep the one whose best allocation is cheapest, i.e. lowest
+    worst-rank traffic, ties broken by the busiest rank's compute.
+
+    The reference draws this stage in its overview (strided attention -> remapped context -> node
+    / device / kernel tiles) but only ships its hand-made result for one pattern and the hook
+    (``cmap``; "[TODO]: Explore the best cmap", search_algo/bsa_config.py:417-418). Returns
+    ``{"name", "cmap", "allocation", "permutation", "scores"}``; ``permutation`` (block order that
+    makes every rank's blocks contiguous) is what the data loader applies to token / position ids
+    (``apply_block_permutation``) so that rank r simply holds the r-th chunk of the permuted
+    sequence."""
+    from ..patterns.named import cmap_contiguous, cmap_strided, cmap_zigzag, remap_permutation
+    cp = bsa_config.CP[0]
+    par_d = ParD or max(cp, bsa_config.table.shape[0])
+    makers = {"contiguous": cmap_contiguous, "strided": cmap_strided, "zigzag": cmap_zigzag}
+    scores, best = {}, None
+    for name in candidates:
+        if name == "zigzag" and par_d % (2 * cp):
+            continue
+        if par_d % cp:
+            continue
+        cmap = makers[name](par_d, cp)
+        al = solve_sparse_from_bsa(bsa_config, fob=fob, ParD=par_d, time_limit=time_limit, cmap=cmap)
+        scores[name] = (float(al.comm_volume), float(al.comp_max))
+        if best is None or scores[name] < scores[best[0]]:
+            best = (name, cmap, al)
+    if best is None:
+        raise ValueError(f"no ownership map fits {par_d} blocks on {cp} ranks")
+    name, cmap, al = best
+    return {"name": name, "cmap": cmap, "allocation": al, "permutation": remap_permutation(cmap), "scores": scores}
+
+
+def apply_block_permutation(x, permutation, dim: int = 1):
+    """Reorder the blocks of a ``[..., tokens, ...]`` tensor along ``dim``: block ``permutation[i]``
+    of the input becomes block i of the output (token ids, position ids, targets at data-loading
+    time; the inverse permutation restores the order)."""
+    import torch
+    n = len(permutation)
+    blk = x.shape[dim] // n
+    assert blk * n == x.shape[dim], "the token count is not a multiple of the number of blocks"
+    idx = torch.cat([torch.arange(int(p) * blk, (int(p) + 1) * blk) for p in permutation]).to(x.device)
+    return x.index_select(dim, idx)
