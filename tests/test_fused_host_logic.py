@@ -13,8 +13,8 @@ from ultraattn_b200.runtime import FakeSpace, FusedContextParallel, plan_allocat
 
 
 def _run_all_ranks(pattern, world, S, H, D, allocation, seed=0, multicast=False, min_consumers=2,
-                   nvls_reduce=False, steps=1):
-    table, cmap = plan_allocation(pattern, world, 1, allocation, time_limit=5.0)
+                   nvls_reduce=False, steps=1, cmap=None):
+    table, cmap = plan_allocation(pattern, world, 1, allocation, time_limit=5.0, cmap=cmap)
     if allocation == "lightseq":
         tiles = [int((table == r).sum()) for r in range(world)]
         assert max(tiles) - min(tiles) <= 1, tiles          # the point of the schedule: balance
@@ -114,6 +114,15 @@ def test_fused_host_logic_with_in_switch_gradient_sum(name, pattern, world, allo
     contents of the replicas would show."""
     err, table = _run_all_ranks(pattern(), world, 512, 2, 16, alloc, multicast=True, min_consumers=minc,
                                 nvls_reduce=True, steps=2)
+    assert err < 2e-4, (err, table)
+
+
+@pytest.mark.parametrize("name,pattern", [("strided", lambda: P.strided(8, 4, 2)), ("causal", lambda: P.causal(1))],
+                         ids=lambda x: x if isinstance(x, str) else None)
+def test_fused_host_logic_with_searched_ownership(name, pattern):
+    """Context remap chosen by the planner (residue classes for the strided pattern, zigzag for
+    dense causal): ranks own non-adjacent blocks; results must not change."""
+    err, table = _run_all_ranks(pattern(), 4, 512, 2, 16, "ilp", cmap="search")
     assert err < 2e-4, (err, table)
 
 

@@ -19,8 +19,19 @@ from ..planner.pipeline import make_plan
 
 def plan_allocation(pattern: BSA_Repr, cp: int, fob: int = 1, allocation: str = "ilp",
                     time_limit: float = 20.0, cmap=None):
-    """(table, cmap) of the tile allocation for ``cp`` ranks."""
+    """(table, cmap) of the tile allocation for ``cp`` ranks. ``cmap``: an ownership map (block ->
+    rank), None for contiguous chunks, or ``"search"`` to let the planner pick among contiguous /
+    residue-class / zigzag ownership (context remap; every rank then passes the blocks it owns
+    under the returned map, in increasing block order)."""
     cfg = BSA_Config(None, None, {"bsa_repr": pattern, "CP": (cp, 1)})
+    if isinstance(cmap, str):
+        assert cmap == "search", f"unknown cmap option {cmap!r}"
+        from ..planner.allocate import search_context_remap
+        import math
+        n = cfg.table.shape[0]
+        par_d = n if n % (2 * cp) == 0 else math.lcm(n, 2 * cp)      # every candidate map must fit
+        res = search_context_remap(cfg, fob=fob, ParD=par_d, time_limit=time_limit)
+        return np.asarray(res["allocation"].table), np.asarray(res["cmap"])
     if allocation == "naive":
         al = naive_allocate_strategy(cfg, fob=fob)
         return np.asarray(al.table), np.asarray(al.cmap)
