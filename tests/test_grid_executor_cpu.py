@@ -94,6 +94,19 @@ def _api_worker(rank, world, port, ret):
         o_c, _, dq_c, dk_c, dv_c = P.dense_attention_with_grads(q, k, v, d_o, P.causal(1))
         err += [(o - o_c[:, sl]).abs().max().item(), (ql.grad - dq_c[:, sl]).abs().max().item(),
                 (kl.grad - dk_c[:, sl]).abs().max().item(), (vl.grad - dv_c[:, sl]).abs().max().item()]
+        # context-parallel runtime with the ownership chosen by the remap stage
+        from ultraattn_b200.runtime import ContextParallelAttention
+        pat = P.strided(8, 4, 2)
+        rt = ContextParallelAttention(pat, S, H, D, device=torch.device("cpu"), path="nccl", dtype=torch.float32,
+                                      plan_time_limit=3.0, cmap="search")
+        blk = S // rt.table.shape[0]
+        idx = torch.cat([torch.arange(b * blk, (b + 1) * blk) for b in range(rt.table.shape[0]) if rt.cmap[b] == rank])
+        ql, kl, vl = (t[:, idx].clone().requires_grad_() for t in (q, k, v))
+        o = rt(ql, kl, vl)
+        o.backward(d_o[:, idx])
+        o_s, _, dq_s, dk_s, dv_s = P.dense_attention_with_grads(q, k, v, d_o, pat)
+        err += [(o - o_s[:, idx]).abs().max().item(), (ql.grad - dq_s[:, idx]).abs().max().item(),
+                (kl.grad - dk_s[:, idx]).abs().max().item(), (vl.grad - dv_s[:, idx]).abs().max().item()]
         ret[rank] = max(err)
     except Exception as e:  # noqa: BLE001
         import traceback

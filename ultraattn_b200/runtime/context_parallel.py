@@ -124,8 +124,11 @@ class ContextParallelAttention:
                       n_kv_heads=n_kv_heads, batch=batch, allocation=allocation, plan_type="Flexflow",
                       time_limit=plan_time_limit, cmap=cmap)
             if self.rank == 0 and allocation not in ("naive", "lightseq"):
-                # same partition granularity as the fused path (refined until balanced)
-                kw["ParD"] = plan_allocation(pattern, self.world, 1, allocation, plan_time_limit, cmap)[0].shape[0]
+                # same partition granularity (and, with cmap="search", ownership) as the fused path
+                table0, cmap0 = plan_allocation(pattern, self.world, 1, allocation, plan_time_limit, cmap)
+                kw["ParD"] = table0.shape[0]
+                if isinstance(cmap, str):
+                    kw["cmap"] = cmap0
             box = [(make_plan(fob=0, **kw), make_plan(fob=1, **kw)) if self.rank == 0 else None]
             dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, 0), group=self.group)
             pf, pb = box[0]
