@@ -326,3 +326,12 @@ def test_start_gate_is_a_no_op_on_cpu():
     g.open()
     assert g.check() and g.epoch == 1 and int(g.flag[0]) == 1
     assert benchmark_ops(lambda: None, warmup=1, num_iter=2, repeats=1, device=torch.device("cpu"), start_gate=True) >= 0
+
+
+def test_inputs_sharded_by_remapped_ownership():
+    from ultraattn_b200.models.glue import prepare_seq_parallel_inputs, shard_by_ownership
+    ids = torch.arange(16)[None]
+    cmap = P.cmap_strided(8, 4)                       # rank r owns blocks r and r + 4 (2 tokens each)
+    out = prepare_seq_parallel_inputs("ultra_attn", ids, ids, None, rank=1, world_size=4, cmap=cmap)
+    assert out["local_input_ids"].tolist() == [[2, 3, 10, 11]] and out["local_target_ids"] is None
+    assert shard_by_ownership(torch.arange(8), P.cmap_zigzag(4, 2), 0, dim=0).tolist() == [0, 1, 6, 7]

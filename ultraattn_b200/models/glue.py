@@ -19,10 +19,25 @@ _KIND = {"zigzag_ring_attn": "zigzag", "zigzag": "zigzag", "ring_attn": "ring", 
          "dist_flash_attn": "lightseq", "lightseq": "lightseq", "data_parallel": None, "ultra_attn": "ring", "ultraattn": "ring"}
 
 
+def shard_by_ownership(x: torch.Tensor, cmap, rank: int, dim: int = 1) -> torch.Tensor:
+    """The blocks of ``x`` (along ``dim``) that ``cmap`` (block -> rank) gives to ``rank``, in
+    increasing block order: the shard a context-parallel runtime expects under a remapped
+    ownership (``ContextParallelAttention(cmap=...)``, ``plan_allocation(cmap="search")``)."""
+    n = len(cmap)
+    blk = x.shape[dim] // n
+    assert blk * n == x.shape[dim], "the token count is not a multiple of the number of blocks"
+    idx = torch.cat([torch.arange(b * blk, (b + 1) * blk) for b in range(n) if int(cmap[b]) == rank])
+    return x.index_select(dim, idx.to(x.device)).contiguous()
+
+
 def prepare_seq_parallel_inputs(seq_algo: str, input_ids, position_ids, target_ids, rank: int, world_size: int,
-                                device=None) -> dict:
+                                device=None, cmap=None) -> dict:
+    """Shard token / position / target ids the way ``seq_algo`` expects. ``cmap`` (block -> rank,
+    e.g. a runtime's ``.cmap``) overrides the layout for the planner-driven runtime."""
     kind = _KIND.get(seq_algo, seq_algo)
-    if kind is None:
+    if cmap is not None:
+        sh = lambda t: None if t is None else shard_by_ownership(t, cmap, rank, dim=1)
+    elif kind is None:
         sh = lambda t: t
     elif kind == "lightseq":        # contiguous chunks, like the plain ring
         sh = lambda t: None if t is None else R.shard_sequence(t, rank, world_size, "ring", dim=1)
