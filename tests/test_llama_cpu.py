@@ -69,3 +69,19 @@ def test_llama_matches_plain_pytorch():
     for name, p in model.p.items():
         assert (p.detach() - ref_params[name].detach()).abs().max().item() < 1e-4, name
     assert model.flat_grad.abs().max().item() == 0
+
+
+def test_memory_plan_of_the_headline_training_config():
+    """Llama-2-7B, S = 512k, CP = 8: parameter count, and the per-GPU plan fits a 180 GB GPU with
+    the checkpoints on the device; offloading moves exactly the checkpoints to the host."""
+    from ultraattn_b200.models.llama import LlamaConfig, estimate_memory
+    cfg = LlamaConfig.llama2_7b()
+    m = estimate_memory(cfg, 524288, 8)
+    assert m["n_params"] == 6738415616
+    assert abs(m["parameters"] - 12.55) < 0.01 and abs(m["optimizer_shard"] - 3 * 4 * m["n_params"] / 8 / 2**30) < 1e-9
+    assert 80 < m["device_total"] < 140
+    off = estimate_memory(cfg, 524288, 8, offload_checkpoints=True)
+    assert off["checkpoints_device"] == 0 and abs(off["checkpoints_host"] - m["checkpoints_device"]) < 1e-9
+    assert abs((m["device_total"] - off["device_total"]) - m["checkpoints_device"]) < 1e-9
+    small = estimate_memory(LlamaConfig(n_layers=4), 65536, 2)
+    assert 15 < small["device_total"] < 30                     # a run of this size peaked at 18.4 GiB per GPU

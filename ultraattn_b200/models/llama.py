@@ -394,3 +394,44 @@ class _ChunkLoss(torch.autograd.Function):
         dh = G.gemm(dl, w, b_is_kn=True)
         dw = G.gemm(dl, h, a_is_km=True, b_is_kn=True)
         return dh, dw, None
+
+
+def estimate_memory(cfg: LlamaConfig, seq_len: int, cp: int = 1, offload_checkpoints: bool = False,
+                    loss_chunk_tokens: int = 4096, staged_peer_ranks: Optional[int] = None) -> dict:
+    """Per-GPU memory plan of a training step (GiB), by what holds it: replicated bf16 parameters
+    and gradients, the 1/cp shard of the fp32 optimizer state (master, m, v), the activation
+    checkpoints (layer input and attention output of every layer, plus lse; in pinned host memory
+    with ``offload_checkpoints``), the context-parallel runtime's buffers (symmetric shards of
+    Q/K/V/dO, mailboxes, fp32 gradient accumulators, mirrors of the peers it reads from), the
+    working set of one layer's backward and one chunk of logits. A planning aid: it tells whether
+    a (model, sequence, CP) fits 180 GB before anything is launched."""
+    GiB = float(1 << 30)
+    H, D, Hk, Fd, V, L = cfg.hidden, cfg.head_dim, cfg.kv_heads, cfg.ffn, cfg.vocab, cfg.n_layers
+    per_layer = 2 * H + (cfg.n_heads + 2 * Hk) * D * H + H * cfg.n_heads * D + 2 * Fd * H + H * Fd
+    n_params = 2 * V * H + H + L * per_layer
+    s_loc = seq_len // cp
+    q_bytes = s_loc * cfg.n_heads * D * 2
+    kv_bytes = s_loc * Hk * D * 2
+    lse_bytes = cfg.n_heads * s_loc * 4
+    ckpt_per_layer = s_loc * H * 2 + q_bytes + lse_bytes
+    peers = (cp - 1) if staged_peer_ranks is None else staged_peer_ranks
+    runtime = 0.0
+    if cp > 1:
+        runtime = (2 * q_bytes + 2 * kv_bytes + 2 * lse_bytes           # symmetric q, do, k, v, lse, dvec
+                   + q_bytes + lse_bytes                                # mailboxes (one slot per foreign row block: bounded by a shard)
+                   + 2 * q_bytes + 2 * 2 * kv_bytes                     # fp32 dq / dk / dv accumulators
+                   + peers * (2 * q_bytes + 2 * lse_bytes + 2 * q_bytes + 2 * kv_bytes))  # mirrors: q, do, lse, dvec, fp32 dq, k, v
+    layer_work = (s_loc * ((cfg.n_heads + 2 * Hk) * D + 2 * Fd + Fd + 3 * H) * 2) * 2     # activations + their gradients of one layer
+    out = {
+        "parameters": n_params * 2 / GiB,
+        "gradients": n_params * 2 / GiB,
+        "optimizer_shard": n_params * 12 / cp / GiB,
+        "checkpoints_device": 0.0 if offload_checkpoints else L * ckpt_per_layer / GiB,
+        "checkpoints_host": L * ckpt_per_layer / GiB if offload_checkpoints else 0.0,
+        "attention_runtime": runtime / GiB,
+        "layer_working_set": layer_work / GiB,
+        "logits_chunk": loss_chunk_tokens * V * (2 + 4) / GiB,
+        "n_params": n_params,
+    }
+    out["device_total"] = sum(v for k, v in out.items() if k not in ("checkpoints_host", "n_params"))
+    return out
