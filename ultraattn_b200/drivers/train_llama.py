@@ -38,7 +38,15 @@ def main() -> None:
     ap.add_argument("--path", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--offload-checkpoints", action="store_true",
                     help="keep the per-layer activation checkpoints in pinned host memory")
+    ap.add_argument("--estimate-memory", type=int, default=0, metavar="CP",
+                    help="print the per-GPU memory plan for CP ranks and exit (needs no GPU)")
     a = ap.parse_args()
+    if a.estimate_memory:
+        from ..models.llama import estimate_memory
+        plan = estimate_memory(LlamaConfig(n_layers=a.layers, hidden=a.hidden, n_heads=a.heads, head_dim=128,
+                                           ffn=a.ffn, vocab=a.vocab), a.seq, a.estimate_memory, a.offload_checkpoints)
+        print(json.dumps({k: round(v, 2) if isinstance(v, float) else v for k, v in plan.items()}))
+        return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
