@@ -335,3 +335,78 @@ def test_inputs_sharded_by_remapped_ownership():
     out = prepare_seq_parallel_inputs("ultra_attn", ids, ids, None, rank=1, world_size=4, cmap=cmap)
     assert out["local_input_ids"].tolist() == [[2, 3, 10, 11]] and out["local_target_ids"] is None
     assert shard_by_ownership(torch.arange(8), P.cmap_zigzag(4, 2), 0, dim=0).tolist() == [0, 1, 6, 7]
+
+
+def test_every_reference_module_path_imports_and_exports():
+    """Every module path of the reference that this distribution mirrors imports, and exports the
+    names code written against the reference uses."""
+    import importlib
+    surface = {
+        "search_algo.bsa_config": ["BSA_Repr", "BSA_Config"],
+        "search_algo.bsa_utils": ["create_bsa_block_table", "split_to_node_configs", "get_b2f_suf_map",
+                                  "select_best_profile_comp_key", "convert_intra_profile_key_to_exe_key_or_plan",
+                                  "convert_shape_config_to_str", "bsa_is_full", "bsa_is_causal", "bsa_is_dense"],
+        "search_algo.custom_sparse_pattern": ["create_block_sparse_pattern"],
+        "search_algo.utils": ["Block_Type", "Block_Table_Type", "Block_Comp_Volume", "Block_Attention_Config",
+                              "FinitePriorityQueue", "calc_flops", "report_memory", "print_rank_0", "parse_args",
+                              "all_wait_main_stream", "main_stream_wait_all", "convert_profile_data_to_map",
+                              "convert_profile_data_to_comm_map", "convert_node_profile_data_to_comp_map",
+                              "get_factors", "closest_fraction", "unique_list", "use_all_cpus"],
+        "search_algo.workload_partition": ["solve_sparse_from_bsa", "naive_allocate_strategy",
+                                           "Quad_LP_GUROBI_from_block_config", "comp_balance_allocate_strategy",
+                                           "Quad_LP_GUROBI", "ILP", "solve_global_causal"],
+        "search_algo.manual_schedules": ["get_qo_schedule_table", "get_kv_schedule_table", "get_cc_optimal_schedule_table"],
+        "search_algo.dense_utils": ["CP2ParD_map", "get_block_schedule_table_for_full", "create_plan_for_full",
+                                    "create_ablation_configs_for_full", "write_plan", "split_dense_configs"],
+        "search_algo.search_engine": ["Evaluation_Configs", "Dist_Attn_Config", "Dist_Attn_Schedule", "Machine_Config",
+                                      "FlashAttn_Profile_Map", "Inter_Comp_Profile_Map", "Comm_Profile_Map",
+                                      "get_cc_optimal_schedule_from_table"],
+        "search_algo.dependent_graph": ["Dependent_Graph", "Cuda_Kernel", "Comp_Kernel", "Comm_Kernel"],
+        "search_algo.graph_transformation_engine": ["Graph_Transformation_Engine", "Comp_Fusion_Substitution",
+                                                    "Comp_Fusion_Transformation"],
+        "search_algo.execute_plan": ["Execution_Plan", "Fused_Execution_Plan"],
+        "search_algo.database": ["Prof_DB"],
+        "search_algo.initialize": ["get_proc_info", "initialize_distribution"],
+        "search_algo.exp_configs": ["get_exp_configs", "get_exp_train_configs", "get_exp_infer_configs",
+                                    "get_bsa_train_configs", "get_dense_train_configs", "get_bsa_infer_configs",
+                                    "step0_top_down_decompose"],
+        "search_algo.benchmark": ["benchmark_ops", "benchmark_orchestrate_bsa", "prepare_inter_comp_plans", "create_buf_dict"],
+        "search_algo.arguments": ["parse_args", "get_args"],
+        "search_algo.global_vars": ["get_global_var", "set_global_var"],
+        "search_algo.task1_bsa": ["main"], "search_algo.task2_bsa": ["main"], "search_algo.main": ["main"],
+        "search_algo.fusion_evaluate": ["main"], "search_algo.intra_attn_gen": ["main"],
+        "orchestrated_attn": ["orchestrated_attn_func", "orchestrated_attn_backward", "OrchestratedAttnFunc",
+                              "Input_Row_Fwd", "Input_Col_Fwd", "Output_Row_Fwd", "Output_Col_Fwd",
+                              "Input_Row_Bwd", "Input_Col_Bwd", "Output_Row_Bwd", "Output_Col_Bwd"],
+        "orchestrated_attn.orchestrated_attn_impl": ["orchestrated_attn_forward", "orchestrated_attn_backward",
+                                                     "fused_attn_forward", "fused_attn_backward",
+                                                     "intra_attn_forward", "intra_attn_backward"],
+        "orchestrated_attn.utils": ["IntraComm", "InterComm", "IntraComm_fused", "InterComm_fused", "Integrated_Data"],
+        "orchestrated_attn.global_vars": ["FULL_DTYPE", "ncclcomm_dict", "cpu_group_dict", "streams"],
+        "ring_flash_attn": ["ring_flash_attn_func", "ring_flash_attn_kvpacked_func", "ring_flash_attn_qkvpacked_func",
+                            "ring_flash_attn_backward", "ring_flash_attn_varlen_func",
+                            "zigzag_ring_flash_attn_func", "zigzag_ring_flash_attn_varlen_func",
+                            "zigzag_ring_flash_attn_varlen_qkvpacked_func", "stripe_flash_attn_func",
+                            "stripe_flash_attn_kvpacked_func"],
+        "ring_flash_attn.utils": ["update_out_and_lse", "flatten_varlen_lse", "unflatten_varlen_lse"],
+        "hierarchy_attn": ["hierarchy_attn_func"], "head_parallel_attn": ["deepspeed_ulysses_attn_func"],
+        "comm_lib.comm_utils": ["RingComm", "RingCommOld", "RingCommNew", "A2AComm"],
+        "easy_context": ["prepare_seq_parallel_inputs", "apply_seq_parallel_monkey_patch", "prepare_dataloader",
+                         "prepare_zigzag_ring_attn_inputs", "prepare_dist_flash_attn_inputs",
+                         "apply_zigzag_ring_attn_monkey_patch_llama", "apply_zigzag_ring_attn_monkey_patch_mistral",
+                         "apply_dist_flash_attn_monkey_patch_llama",
+                         "apply_unsloth_offloaded_gradient_checkpoint_monkey_patch"],
+        "easy_context.dist_flash_attn.lightseq_async_attn": ["attention"],
+        "easy_context.dist_flash_attn.async_communication": ["initialize_distributed", "get_sequence_parallel_group",
+                                                            "get_sequence_parallel_rank", "get_sequence_parallel_size",
+                                                            "is_last_time", "is_compute_for_local_query", "is_idle",
+                                                            "is_sync_from_remote", "print_and_reset_comm_stats"],
+        "easy_context.dist_flash_attn.prepare_input": ["extract_local", "prepare_dist_flash_attn_inputs"],
+        "easy_context.zigzag_ring_attn": ["prepare_zigzag_ring_attn_inputs"],
+        "easy_context.unsloth_offloaded_gradient_checkpoint": ["apply_unsloth_offloaded_gradient_checkpoint_monkey_patch"],
+    }
+    missing = []
+    for mod, names in surface.items():
+        m = importlib.import_module(mod)
+        missing += [f"{mod}.{n}" for n in names if not hasattr(m, n)]
+    assert not missing, missing
