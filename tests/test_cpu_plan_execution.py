@@ -107,3 +107,51 @@ def test_patterns_world4(case):
         assert "error" not in res[r], res[r].get("error")
         for name, e in res[r].items():
             assert e < 2e-4, (r, name, e)
+
+
+def _json_worker(rank, world, port, path_f, path_b, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ultraattn_b200 import patterns as P
+        from ultraattn_b200.planner import Execution_Plan
+        from ultraattn_b200.runtime import PlanExecutor
+        plan_f, plan_b = Execution_Plan.from_json(path_f), Execution_Plan.from_json(path_b)
+        assert plan_f.sanity_check_stream_exclusive()
+        pattern = plan_f.da_config.bsa_config.bsa_repr
+        S, (H, _), D = plan_f.da_config.S[0], plan_f.da_config.Nh, plan_f.da_config.D
+        g = torch.Generator().manual_seed(2)
+        q, k, v, d_o = (torch.randn(1, S, H, D, generator=g) for _ in range(4))
+        ex = PlanExecutor(plan_f, plan_b, group=None, device=torch.device("cpu"), recv_timeout_s=30)
+        blk = S // ex.par_d
+        idx = torch.cat([torch.arange(b * blk, (b + 1) * blk) for b in ex.my_blocks])
+        o, lse = ex.forward(*(t[:, idx].contiguous() for t in (q, k, v)))
+        dq, dk, dv = ex.backward(d_o[:, idx].contiguous(), *(t[:, idx].contiguous() for t in (q, k, v)), o, lse)
+        o_ref, _, dq_ref, dk_ref, dv_ref = P.dense_attention_with_grads(q, k, v, d_o, pattern)
+        ret[rank] = max((o - o_ref[:, idx]).abs().max().item(), (dq - dq_ref[:, idx]).abs().max().item(),
+                        (dk - dk_ref[:, idx]).abs().max().item(), (dv - dv_ref[:, idx]).abs().max().item())
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = f"{type(e).__name__}: {e}\\n{traceback.format_exc()}"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_plans_execute_from_their_json_form(tmp_path):
+    """A plan written as JSON (no pickle) is read back by other processes and executed on two
+    ranks: same results as the dense oracle."""
+    from ultraattn_b200 import patterns as P
+    from ultraattn_b200.planner import make_plan
+    kw = dict(pattern=P.global_local(4, 1, 2), cp=2, seq_len=256, n_heads=2, head_dim=16, allocation="ilp",
+              plan_type="ILP", time_limit=3.0, kernel_tile=True)
+    paths = []
+    for fob in (0, 1):
+        plan = make_plan(fob=fob, **kw)
+        paths.append(str(tmp_path / f"plan{fob}.json"))
+        plan.to_json(paths[-1])
+    ret = mp.Manager().dict()
+    mp.spawn(_json_worker, args=(2, 29480 + os.getpid() % 15, paths[0], paths[1], ret), nprocs=2, join=True)
+    for r in range(2):
+        assert isinstance(ret[r], float), ret[r]
+        assert ret[r] < 2e-4, (r, ret[r])

@@ -178,6 +178,9 @@ def test_pickled_plans_use_the_reference_class_paths(tmp_path):
                          capture_output=True, text=True, cwd=root)
     assert out.stdout.split() == ["True", "1", "2", "True"], out.stderr
     assert db.get_plan("some_key", 1).verify() == []
+    from_json = db.get_plan_from_json("some_key", 1)
+    assert [k.key for k in from_json.gpu_kernel_lists[1]] == [k.key for k in plan.gpu_kernel_lists[1]]
+    assert from_json.end_time == plan.end_time and from_json.sanity_check_stream_exclusive()
 
 
 def test_report_reads_the_published_profile_entries():

@@ -173,6 +173,14 @@ class Prof_DB:
         p = Path(getattr(self, f"{lvl}_BSA_EXE_PLANS_DIR")) / f"{kv.get(key, -1)}.json"
         return json.loads(p.read_text()) if p.exists() else None
 
+    def get_plan_from_json(self, key: str, hierarchy: int = 1):
+        """The stored plan rebuilt from its JSON side-car (nothing is unpickled); None if absent."""
+        plain = self.get_plan_plain(key, hierarchy)
+        if plain is None:
+            return None
+        from ..planner.schedule import Execution_Plan
+        return Execution_Plan.from_plain(plain)
+
     # profiles
     def get_profile(self, key: str, hierarchy: int = 1) -> Optional[dict]:
         return self._load(getattr(self, f"{self._lvl(hierarchy)}_BSA_EXE_PLANS_PROFILE")).get(key)

@@ -398,6 +398,71 @@ class Execution_Plan:
         with open(path, "w") as f:
             json.dump(self.to_plain(), f)
 
+    @classmethod
+    def from_plain(cls, d: dict) -> "Execution_Plan":
+        """Rebuild an executable plan from its plain-data form (the JSON side-car), without
+        unpickling anything: kernels with their keys, times, start times and precursor /
+        successor links, the per-rank launch lists, the per-stream lists, and the problem
+        description the executors read (shape, pattern, partition, ownership)."""
+        import re
+        from ..patterns.blocks import BSA_Config, BSA_Repr
+        from .cost import Dist_Attn_Config
+        assert d.get("format") == "ultraattn-plan/1", f"unknown plan format {d.get('format')!r}"
+        dc = d["da_config"]
+        m = re.match(r"CP=\((\d+), (\d+)\)_repr=(.*)$", dc["bsa_config"])
+        bsa = BSA_Config(None, None, {"bsa_repr": BSA_Repr.from_string(m.group(3)),
+                                      "CP": (int(m.group(1)), int(m.group(2)))})
+        da = Dist_Attn_Config.from_bsa_config(bsa, {"S": tuple(dc["S"]), "Nh": tuple(dc["Nh"]), "bs": dc["bs"],
+                                                    "D": dc["D"]}, dc["hierarchy"])
+        plan = cls(None, d["fob"], d["plan_type"])
+        kernels = {}
+        for k in d["kernels"]:
+            key = tuple(tuple(x) if isinstance(x, list) else x for x in k["key"])
+            if k["type"] == "comp":
+                v = Comp_Kernel(key, None, None, 0, time=np.array(k["time"]))
+            else:
+                v = Comm_Kernel(key, None, None, np.array(k["units"] or [0.0, 0.0]), 0, seqlen_variable_graph=True)
+                v.time = np.array(k["time"], dtype=float)
+                del v.is_empty_kernel               # emptiness follows from the stored times again
+            v.id, v._start_time = k["id"], k["start"]
+            kernels[k["id"]] = v
+        for k in d["kernels"]:
+            v = kernels[k["id"]]
+            for pid in k["precursors"]:
+                v.precursors.add(kernels[pid])
+                kernels[pid].successors.add(v)
+        plan.valid_kernels = [kernels[k["id"]] for k in d["kernels"]]
+        plan.gpu_kernel_lists = [[kernels[i] for i in lst] for lst in d["gpu_kernel_lists"]]
+        plan.stream_kernel_lists = {}
+        for v in plan.valid_kernels:
+            for slot in cls._streams_of(v):
+                plan.stream_kernel_lists.setdefault(slot, []).append(v)
+        for lst in plan.stream_kernel_lists.values():
+            lst.sort(key=lambda v: v._start_time)
+        plan.end_time = d["end_time"]
+
+        class _Schedule:            # what executors and tools read from ``plan.d_graph.schedule``
+            pass
+        sch = _Schedule()
+        sch.da_config, sch.m_config = da, None
+        sch.split_degrees = tuple(d["split_degrees"])
+        sch.S_map, sch.schedule_table = np.asarray(d["S_map"]), np.asarray(d["schedule_table"])
+
+        class _Graph:
+            pass
+        g = _Graph()
+        g.schedule, g.fob, g.da_config, g.m_config = sch, d["fob"], da, None
+        g.split_degrees, g.hierarchy, g.hierarchy_sp, g.tot_sp = sch.split_degrees, da.hierarchy, da.hierarchy_sp, da.tot_sp
+        g.kernel_dict = {v.key: v for v in plan.valid_kernels}
+        g.seqlen_variable_graph = False
+        plan.d_graph = g
+        return plan
+
+    @classmethod
+    def from_json(cls, path) -> "Execution_Plan":
+        with open(path) as f:
+            return cls.from_plain(json.load(f))
+
     def print_lp_result(self) -> None:
         for (g, s), lst in self.stream_kernel_lists.items():
             print(f"rank {g} stream {s}: " + " ".join(
