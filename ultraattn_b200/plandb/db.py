@@ -153,7 +153,7 @@ class Prof_DB:
         bind_reference_class_paths()        # pickles name the reference's module paths when possible
         with open(d / f"{pid}.pkl", "wb") as f:
             pickle.dump(plan, f)
-        if hasattr(plan, "to_plain") and getattr(plan, "d_graph", None) is not None:
+        if hasattr(plan, "to_plain") and (getattr(plan, "d_graph", None) is not None or hasattr(plan, "Y")):
             _atomic_write_json(d / f"{pid}.json", plan.to_plain())
         kv[key] = pid
         _atomic_write_json(kv_path, kv)
@@ -178,7 +178,9 @@ class Prof_DB:
         plain = self.get_plan_plain(key, hierarchy)
         if plain is None:
             return None
-        from ..planner.schedule import Execution_Plan
+        from ..planner.schedule import Execution_Plan, Fused_Execution_Plan
+        if plain.get("format", "").startswith("ultraattn-fused-plan"):
+            return Fused_Execution_Plan.from_plain(plain, self.m_config)
         return Execution_Plan.from_plain(plain)
 
     # profiles

@@ -533,3 +533,12 @@ class Fused_Execution_Plan:
 
     def get_plan_name(self) -> str:
         return f"fused_Y={self.Y}_X={self.X}_fob={self.fob}"
+
+    def to_plain(self) -> dict:
+        return {"format": "ultraattn-fused-plan/1", "Y": self.Y, "X": self.X, "fob": self.fob,
+                "causal": bool(self.causal), "end_time": None if self.end_time is None else float(self.end_time)}
+
+    @classmethod
+    def from_plain(cls, d: dict, m_config=None) -> "Fused_Execution_Plan":
+        assert d.get("format") == "ultraattn-fused-plan/1", f"unknown plan format {d.get('format')!r}"
+        return cls(d["Y"], d["X"], d.get("end_time"), d["fob"], m_config, d.get("causal", False))
