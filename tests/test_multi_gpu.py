@@ -29,7 +29,8 @@ def _worker(rank, world, port, case, ret):
         S, H = case["S"], case["H"]
         rt = ContextParallelAttention(pattern, S, H, 128, device=dev, path=case["path"],
                                       allocation=case.get("allocation", "ilp"), plan_time_limit=5.0,
-                                      nvls_min_consumers=case.get("nvls_min_consumers", 2))
+                                      nvls_min_consumers=case.get("nvls_min_consumers", 2),
+                                      nvls_reduce=case.get("nvls_reduce"))
         if case.get("nvls_min_consumers", 2) == 1 and not rt.impl.bc_cols:
             ret[rank] = {"skip": "no NVSwitch multicast address for symmetric memory on this machine"}
             return
@@ -89,6 +90,21 @@ def test_context_parallel_2gpu_multicast_blocks():
     _need(2)
     res = _run(2, {"pattern": "global_local", "args": (8, 1, 2), "S": 2048, "H": 2, "path": "fused",
                    "allocation": "naive", "nvls_min_consumers": 1})
+    if any("skip" in res[r] for r in range(2)):
+        pytest.skip(res[0].get("skip") or res[1].get("skip"))
+    for r in range(2):
+        assert "error" not in res[r], res[r].get("error")
+        assert res[r]["rel_err"] < 2e-2, res
+
+
+@pytest.mark.skipif(os.environ.get("UA_TEST_NVLS_REDUCE") != "1",
+                    reason="opt-in (UA_TEST_NVLS_REDUCE=1): the in-switch gradient sum is off by default")
+def test_context_parallel_2gpu_in_switch_gradient_sum():
+    """dK/dV of broadcast blocks summed by multimem.ld_reduce (own-replica accumulation): same
+    results as the default delivery by peer reductions."""
+    _need(2)
+    res = _run(2, {"pattern": "global_local", "args": (8, 1, 2), "S": 2048, "H": 2, "path": "fused",
+                   "allocation": "naive", "nvls_min_consumers": 1, "nvls_reduce": True})
     if any("skip" in res[r] for r in range(2)):
         pytest.skip(res[0].get("skip") or res[1].get("skip"))
     for r in range(2):
