@@ -8,7 +8,7 @@ Per configuration and rank count: forward / backward time of the fused runtime u
 allocation (``planner.cost.fused_step_time``), of the K/V ring with contiguous shards that skips
 excluded block pairs (``ring_step_time``), of the zigzag ring for dense causal attention, and the
 ratios. The reference publishes such ratios as its headline (speed-up over ring attention,
-README.md:31-67); these are the model's values for one NVSwitch box of B200s.
+its README.md:31-67); these are the model's values for one NVSwitch box of B200s.
 """
 from __future__ import annotations
 

@@ -83,7 +83,7 @@ def document(doc_blocks, causal_docs: bool = True) -> BSA_Repr:
     """Document mask for a packed batch whose documents are whole numbers of blocks long:
     ``doc_blocks[i]`` blocks for document i. Tokens attend only their own document (causally, or
     fully with ``causal_docs=False``), so the table is block-diagonal. The reference lists this
-    mask as future work (README.md:71); as a block table it goes through the same planner and
+    mask as future work (its README.md:71); as a block table it goes through the same planner and
     runtimes as every other pattern, which gives context parallelism over packed documents."""
     n = int(sum(doc_blocks))
     t = np.zeros((n, n), dtype=np.int8)
