@@ -222,3 +222,31 @@ def test_context_remap_search_and_execution():
     op, _ = P.dense_attention(qp, kp, vp, mask_p)
     inv = np.argsort(perm)
     assert torch.allclose(apply_block_permutation(op, inv), o, atol=1e-6)
+
+
+def test_refinement_preserves_the_token_mask_property():
+    """Property test over random block tables: refining a table (a CAUSAL block becomes a
+    lower-triangular arrangement of CAUSAL / FULL / EMPTY blocks) never changes the token-level
+    mask, coarsening undoes refinement up to the irreducible form, and the string form parses
+    back to the same table."""
+    from hypothesis import given, settings, strategies as st
+    from ultraattn_b200.patterns.blocks import BSA_Repr
+
+    @st.composite
+    def tables(draw):
+        n = draw(st.integers(min_value=1, max_value=5))
+        rows = [[draw(st.sampled_from([0, 1, 2] if i == j else [0, 1])) for j in range(n)] for i in range(n)]
+        return np.array(rows, dtype=np.int8)
+
+    @settings(max_examples=60, deadline=None)
+    @given(tables(), st.sampled_from([2, 3, 4]))
+    def check(table, rate):
+        rep = BSA_Repr(table)
+        n = rep.table.shape[0]
+        fine = rep.refined(n * rate)
+        S = table.shape[0] * n * rate * 2             # divisible by the given and by the refined block count
+        assert bool((rep.token_mask(S, S) == BSA_Repr(fine).token_mask(S, S)).all())
+        assert BSA_Repr(fine).table.tolist() == rep.table.tolist()          # same irreducible form
+        assert BSA_Repr.from_string(str(rep)).table.tolist() == rep.table.tolist()      # the string is the irreducible form
+
+    check()
