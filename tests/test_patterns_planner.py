@@ -250,3 +250,34 @@ def test_refinement_preserves_the_token_mask_property():
         assert BSA_Repr.from_string(str(rep)).table.tolist() == rep.table.tolist()      # the string is the irreducible form
 
     check()
+
+
+def test_random_patterns_plan_and_verify_property():
+    """Property test: for random causal-type block tables, ranks and passes, the whole pipeline
+    (allocation, dependent graph, kernel tiling, list schedule) yields a plan that passes every
+    static check, computes every non-empty tile exactly once and never an empty one."""
+    from hypothesis import given, settings, strategies as st
+    from ultraattn_b200.patterns.blocks import BSA_Repr
+
+    @st.composite
+    def causal_tables(draw):
+        n = draw(st.sampled_from([4, 8]))
+        t = np.zeros((n, n), dtype=np.int8)
+        for i in range(n):
+            t[i, i] = 2
+            for j in range(i):
+                t[i, j] = draw(st.sampled_from([0, 1]))
+        return t
+
+    @settings(max_examples=12, deadline=None)
+    @given(causal_tables(), st.sampled_from([2, 4]), st.sampled_from([0, 1]), st.booleans())
+    def check(table, cp, fob, kernel_tile):
+        pat = BSA_Repr(table)
+        plan = make_plan(pattern=pat, cp=cp, seq_len=1024, n_heads=2, head_dim=32, fob=fob, allocation="ilp",
+                         plan_type="Flexflow", kernel_tile=kernel_tile, time_limit=1.5)
+        assert plan.verify() == []
+        al = np.asarray(plan.allocation.table)
+        fine = pat.refined(al.shape[0])
+        assert ((al >= 0) == (fine > 0)).all() and al.max() < cp
+
+    check()
