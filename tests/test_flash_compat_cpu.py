@@ -67,3 +67,72 @@ def test_varlen_calls():
         assert torch.allclose(o[a:b], o_ref, atol=1e-5) and torch.allclose(lse[i, :, :b - a], lse_ref, atol=1e-5)
         assert torch.allclose(dq[a:b], dq_ref, atol=1e-5) and torch.allclose(dk[a:b], dk_ref, atol=1e-5)
         assert torch.allclose(dv[a:b], dv_ref, atol=1e-5)
+
+
+def test_plan_restatement_matches_explicit_masks_property():
+    """Property test of the fp32 restatement of the launch plans (the oracle of the GPU kernels):
+    random query blocks with random key segments (offsets, lengths, causal diagonals) against an
+    explicit token mask, forward and backward."""
+    from hypothesis import given, settings, strategies as st
+    from ultraattn_b200.ops import attention as A
+
+    @st.composite
+    def rows(draw):
+        T = 48
+        out, used = [], 0
+        for _ in range(draw(st.integers(1, 3))):
+            q_len = draw(st.integers(1, 12))
+            if used + q_len > T:
+                break
+            segs = []
+            for _ in range(draw(st.integers(1, 3))):
+                start = draw(st.integers(0, T - 1))
+                length = draw(st.integers(1, T - start))
+                segs.append(A.Seg(0, start, length, draw(st.booleans()), draw(st.integers(-3, 3))))
+            out.append(A.Row(0, used, q_len, tuple(segs), 0, used, False))
+            used += q_len
+        return out
+
+    @settings(max_examples=40, deadline=None)
+    @given(rows())
+    def check(rws):
+        if not rws:
+            return
+        torch.manual_seed(0)
+        T, H, D = 48, 2, 8
+        q, k, v, d_o = (torch.randn(1, T, H, D) for _ in range(4))
+        o = torch.zeros(1, T, H, D)
+        lse = torch.full((1, H, T), float("-inf"))
+        A.attn_fwd_reference([q], [k], [v], [(o, lse)], rws)
+        # explicit: every row attends the concatenation of its segments (a key may appear twice)
+        q_, k_, v_ = (t.clone().requires_grad_() for t in (q, k, v))
+        o_ref = torch.zeros(1, T, H, D)
+        for r in rws:
+            idx, keep = [], []
+            for s in r.segs:
+                for c in range(s.length):
+                    idx.append(s.start + c)
+                    keep.append([(not s.causal) or c <= rr + s.diag for rr in range(r.q_len)])
+            ks, vs = k_[0, idx], v_[0, idx]
+            sc = torch.einsum("qhd,khd->hqk", q_[0, r.q_start:r.q_start + r.q_len], ks) / math.sqrt(D)
+            mask = torch.tensor(keep).t()
+            sc = sc.masked_fill(~mask[None], float("-inf"))
+            p = torch.softmax(sc, -1)
+            p = torch.where(torch.isnan(p), torch.zeros_like(p), p)
+            o_ref[0, r.q_start:r.q_start + r.q_len] = torch.einsum("hqk,khd->qhd", p, vs)
+        assert torch.allclose(o, o_ref.detach(), atol=1e-5)
+        # backward of the restatement against autograd of the explicit form
+        o_ref.backward(d_o)
+        dvec = (o * d_o).sum(-1).permute(0, 2, 1).contiguous()
+        dq = torch.zeros(1, T, H, D)
+        by_kv = {}
+        for r in rws:
+            for s in r.segs:
+                by_kv.setdefault((s.start, s.length), []).append(A.Seg(0, r.q_start, r.q_len, s.causal, s.diag))
+        cols = [A.Col(0, ks_, kl_, tuple(sg), 0, ks_) for (ks_, kl_), sg in by_kv.items()]
+        dk, dv = torch.zeros(1, T, H, D), torch.zeros(1, T, H, D)
+        A.attn_bwd_reference([A.BwdQSide(q, d_o, lse, dvec, dq)], [k], [v], [A.BwdKvOut(dk, dv)], cols)
+        assert torch.allclose(dq, q_.grad, atol=1e-4) and torch.allclose(dk, k_.grad, atol=1e-4)
+        assert torch.allclose(dv, v_.grad, atol=1e-4)
+
+    check()
