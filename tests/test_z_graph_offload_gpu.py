@@ -176,3 +176,39 @@ def test_reference_kernel_calls_on_gpu(dev):
             _close(dq[a:b].cpu(), dq_ref, 2e-2)
             _close(dk[a:b].cpu(), dk_ref, 2e-2)
             _close(dv[a:b].cpu(), dv_ref, 2e-2)
+
+
+@pytest.mark.skipif(__import__("os").environ.get("UA_TEST_RANDOM_PLANS") != "1",
+                    reason="opt-in (UA_TEST_RANDOM_PLANS=1): randomised launch plans against the fp32 restatement")
+def test_random_launch_plans_against_the_restatement(dev):
+    """Seeded random forward plans (several query blocks, several key segments each, arbitrary
+    offsets and lengths inside the tensors, causal diagonals) on the sm_100a kernel against the
+    fp32 restatement of the same plan."""
+    import random
+    from ultraattn_b200.ops import attention as A
+    T, H = 2048, 2
+    torch.manual_seed(16)
+    q, k, v = (torch.randn(1, T, H, 128, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    for seed in range(6):
+        rng = random.Random(seed)
+        rows, used = [], 0
+        while used < T and len(rows) < 5:
+            q_len = min(T - used, rng.choice([64, 128, 200, 256, 512]))
+            segs = []
+            for _ in range(rng.randint(1, 3)):
+                start = rng.randrange(0, T - 64)
+                length = rng.randint(32, min(768, T - start))
+                segs.append(A.Seg(0, start, length, rng.random() < 0.5, rng.choice([-1, 0, 0, 64])))
+            rows.append(A.Row(0, used, q_len, tuple(segs), 0, used, False))
+            used += q_len
+        o = torch.zeros_like(q)
+        lse = torch.full((1, H, T), float("-inf"), device=dev)
+        A.attn_fwd_cuda([q], [k], [v], [(o, lse)], A.FwdPlan(rows, dev))
+        o_ref = torch.zeros(1, T, H, 128, device=dev)
+        lse_ref = torch.full((1, H, T), float("-inf"), device=dev)
+        A.attn_fwd_reference([q], [k], [v], [(o_ref, lse_ref)], rows)
+        torch.cuda.synchronize(dev)
+        A.check_status(dev)
+        _close(o[:, :used], o_ref[:, :used], 1.5e-2)
+        fin = torch.isfinite(lse_ref)
+        assert (lse[fin] - lse_ref[fin]).abs().max().item() < 3e-3, seed
