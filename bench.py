@@ -280,6 +280,8 @@ def main() -> None:
                        "l2": "inputs (4 GiB per tensor in total) far exceed the 126 MB L2; no flush needed"},
             "model_tflops_per_gpu": tflops, "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "nvlink_bytes_rank0": traffic, "roofline": roof,
+            "tokens_per_s": S / (ms * 1e-3) if ms else None,
+            "e2e_tokens_per_s": (S / (e2e["value"] * 1e-3)) if isinstance(e2e, dict) and e2e.get("value") else None,
         }))
     if world > 1:
         dist.destroy_process_group()
