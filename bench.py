@@ -30,11 +30,22 @@ S_TOTAL, N_BLOCKS, N_HEADS, HEAD_DIM = 512 * 1024, 32, 32, 128
 
 
 def reference_arm(args) -> None:
-    why = ("reference is not installable offline: pip reports neither setup.py nor pyproject.toml; its "
-           "runtime also needs the forked flash-attention v2.5.7_burst submodule (empty in this checkout), "
-           "NCCL 2.21.5 at a hard-coded path and a Gurobi licence")
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
+    """Hands this process over to ``baseline/run_reference.py``: the unmodified reference under
+    ``baseline/_ref`` on the same config, N, steps and warm-up, in an interpreter state that cannot
+    import this repository's package. That script prints the JSON line (or an ``unavailable`` line
+    carrying the exception of the step that failed) and exits 0."""
+    runner = os.path.join(ROOT, "baseline", "run_reference.py")
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "search_algo")):
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "baseline/_ref is missing: run `python baseline/install_reference.py <reference checkout>`"}))
+        return
+    cmd = [sys.executable, runner, "--gpus", str(args.gpus), "--steps", str(args.steps),
+           "--warmup", str(args.warmup), "--seq", str(args.seq)]
+    if args.no_e2e:
+        cmd.append("--no-e2e")
+    sys.stdout.flush()
+    os.execv(sys.executable, cmd)
 
 
 class ClockSampler:

@@ -230,3 +230,56 @@ def test_fused_host_logic_on_random_patterns_property():
         assert err < 2e-4, (table.tolist(), world, err)
 
     check()
+
+
+def _lock_step(gens):
+    """Drive one generator per simulated rank to completion, all of them one barrier at a time."""
+    done = [None] * len(gens)
+    live = list(range(len(gens)))
+    while live:
+        channels = set()
+        for r in list(live):
+            try:
+                channels.add(next(gens[r]))
+            except StopIteration as fin:
+                done[r] = fin.value
+                live.remove(r)
+        assert len(channels) <= 1, f"ranks met at different barriers: {channels}"
+    return done
+
+
+def test_backward_restages_when_another_forward_ran_in_between():
+    """fwd(A); fwd(B); bwd(A); bwd(B): the mirrors hold B's inputs when A's backward runs, so A's
+    backward must restage Q / K / V instead of reusing what "the last forward" left there. Only a
+    backward that directly follows its own forward may skip the restaging."""
+    pattern, world, S, H, D = P.strided(8, 4, 2), 4, 512, 2, 16
+    table, cmap = plan_allocation(pattern, world, 1, "ilp", time_limit=5.0)
+    registry = {}
+    ranks = [FusedContextParallel(table, cmap, pattern, S, H, D, FakeSpace(r, world, registry),
+                                  dtype=torch.float32, defer_build=True) for r in range(world)]
+    for rk in ranks:
+        rk.build()
+    assert any(rk.remote_cols or rk.remote_rows for rk in ranks)
+    blk = S // ranks[0].par_d
+    idx = [torch.cat([torch.arange(b * blk, (b + 1) * blk) for b in rk.owned[rk.rank]]) for rk in ranks]
+    shard = lambda t, r: t[:, idx[r]].contiguous()
+    data, outs = {}, {}
+    for name, seed in (("A", 11), ("B", 12)):
+        g = torch.Generator().manual_seed(seed)
+        data[name] = tuple(torch.randn(1, S, H, D, generator=g) for _ in range(4))
+        q, k, v, _ = data[name]
+        outs[name] = _lock_step([rk.forward_steps(shard(q, r), shard(k, r), shard(v, r)) for r, rk in enumerate(ranks)])
+    assert all(rk.staged_inputs_match(outs["B"][r][0]) for r, rk in enumerate(ranks))
+    assert not any(rk.staged_inputs_match(outs["A"][r][0]) for r, rk in enumerate(ranks))
+    for name in ("A", "B"):
+        q, k, v, d_o = data[name]
+        grads = _lock_step([rk.backward_steps(shard(d_o, r), shard(q, r), shard(k, r), shard(v, r),
+                                              outs[name][r][0], outs[name][r][1]) for r, rk in enumerate(ranks)])
+        _, _, dq_ref, dk_ref, dv_ref = P.dense_attention_with_grads(q, k, v, d_o, pattern)
+        for r in range(world):
+            for got, ref in zip(grads[r], (dq_ref, dk_ref, dv_ref)):
+                assert (got - ref[:, idx[r]]).abs().max().item() < 2e-4, (name, r)
+    # the fast path still exists: a backward right after its own forward reuses the staged inputs
+    q, k, v, d_o = data["A"]
+    out = _lock_step([rk.forward_steps(shard(q, r), shard(k, r), shard(v, r)) for r, rk in enumerate(ranks)])
+    assert all(rk.staged_inputs_match(out[r][0]) for r, rk in enumerate(ranks))

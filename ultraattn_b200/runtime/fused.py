@@ -578,24 +578,46 @@ class FusedContextParallel:
             if kind in kinds and t.is_floating_point():
                 t.fill_(float("nan"))
 
-    def forward(self, q, k, v, softmax_scale=None):
+    def forward_steps(self, q, k, v, softmax_scale=None):
+        """The forward call as a generator that yields the barrier channel wherever all ranks have
+        to meet; :meth:`forward` drives it with the device barrier, the single-process tests drive
+        all simulated ranks in lock step."""
         self._mark("fwd:begin")
         if self.debug_poison:
             self._poison(("q", "k", "v"))
         self.fwd_prepare(q, k, v)
         self._mark("fwd_prepare")
-        self.space.barrier(0)
+        yield 0
         self._mark("fwd_barrier_in")
         if not self.cuda:
             self.stage_on_host(self.f_pieces)
         o, lse = self.fwd_compute(softmax_scale)
         self._mark("fwd_compute")
-        self.space.barrier(1)
+        yield 1
         self._mark("fwd_barrier_out")
         self.fwd_finish(o, lse)
         self._mark("fwd_finish")
-        self._staged_inputs = True
+        # the peers' Q / K / V now sit in the mirrors: remember WHICH forward put them there (the
+        # output tensor it returned), so that only the backward of that very call skips restaging
+        self._staged_for = (o.data_ptr(), tuple(o.shape), self.fwd_calls)
         return o, lse
+
+    def _drive(self, steps):
+        try:
+            while True:
+                self.space.barrier(next(steps))
+        except StopIteration as done:
+            return done.value
+
+    def forward(self, q, k, v, softmax_scale=None):
+        return self._drive(self.forward_steps(q, k, v, softmax_scale))
+
+    def staged_inputs_match(self, o: torch.Tensor) -> bool:
+        """True when the mirrors still hold the inputs of the forward call that returned ``o``
+        (no other forward or full-restage backward ran on this runtime since). Every rank runs the
+        same sequence of calls, so every rank reaches the same answer."""
+        st = getattr(self, "_staged_for", None)
+        return st is not None and st[0] == o.data_ptr() and st[1] == tuple(o.shape)
 
     # =============================== backward ===================================================
     def bwd_prepare(self, d_o, q, k, v, o, lse, reuse_inputs: bool) -> None:
@@ -676,22 +698,29 @@ class FusedContextParallel:
             outs.append(out)
         return tuple(outs)
 
-    def backward(self, d_o, q, k, v, o, lse, softmax_scale=None, reuse_inputs: Optional[bool] = None):
-        reuse = bool(getattr(self, "_staged_inputs", False)) if reuse_inputs is None else reuse_inputs
+    def backward_steps(self, d_o, q, k, v, o, lse, softmax_scale=None, reuse_inputs: Optional[bool] = None):
+        """The backward call as a generator of barrier channels (see :meth:`forward_steps`)."""
+        # the forward's staged Q / K / V are reused only by the backward of that same forward call;
+        # after fwd(A), fwd(B) the backward of A restages everything (its inputs were overwritten)
+        reuse = self.staged_inputs_match(o) if reuse_inputs is None else reuse_inputs
         self._mark("bwd:begin")
         if self.debug_poison:
             self._poison(("do", "lse", "dvec") if reuse else ("q", "k", "v", "do", "lse", "dvec"))
         self.bwd_prepare(d_o, q, k, v, o, lse, reuse)
         self._mark("bwd_prepare")
-        self.space.barrier(2)
+        yield 2
         self._mark("bwd_barrier_in")
         if not self.cuda:
             self.stage_on_host(self.b_pieces if reuse else self.b_pieces_full)
         self.bwd_compute(reuse, softmax_scale)
         self._mark("bwd_compute")
-        self.space.barrier(3)
+        yield 3
         self._mark("bwd_barrier_out")
         res = self.bwd_finish()
         self._mark("bwd_finish")
-        self._staged_inputs = False
+        if not reuse:
+            self._staged_for = None     # the mirrors now hold this backward's inputs, owned by no forward
         return res
+
+    def backward(self, d_o, q, k, v, o, lse, softmax_scale=None, reuse_inputs: Optional[bool] = None):
+        return self._drive(self.backward_steps(d_o, q, k, v, o, lse, softmax_scale, reuse_inputs))
