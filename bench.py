@@ -104,6 +104,9 @@ def main() -> None:
                     help="multi-GPU execution path: fused peer-memory kernels or the NCCL baseline")
     ap.add_argument("--seq", type=int, default=S_TOTAL, help="(debug) total sequence length")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--check", action="store_true",
+                    help="before timing, compare sampled rows of O / lse / dQ / dK / dV at the benchmark shape with an fp32 oracle")
+    ap.add_argument("--check-rows", type=int, default=64, help="query rows sampled by --check (whole job)")
     ap.add_argument("--e2e-head-chunks", type=int, default=4,
                     help="end-to-end arm: head groups whose host-to-device copies overlap the compute")
     args = ap.parse_args()
@@ -132,21 +135,34 @@ def main() -> None:
     S = args.seq
     pattern = P.strided(N_BLOCKS, 4, 2)
     S_loc = S // world
-    gen = torch.Generator(device=dev).manual_seed(1 + rank)
+    blk = S // N_BLOCKS
+    assert N_BLOCKS % world == 0
+    owned = list(range(rank * N_BLOCKS // world, (rank + 1) * N_BLOCKS // world))   # contiguous chunks
+    KINDS = {"q": 0, "k": 1, "v": 2, "do": 3}
 
-    # ---- inputs: generated once on the device, kept as pinned host copies (for the end-to-end
-    # arm) and as device copies (kernel arm) ----------------------------------------------------
-    def make_pair():
-        d = torch.empty(1, S_loc, N_HEADS, HEAD_DIM, dtype=torch.bfloat16, device=dev)
-        flat = d.view(-1)
-        chunk = 1 << 26
+    def gen_block(kind: str, b: int) -> torch.Tensor:
+        """Block ``b`` (16k tokens) of one input tensor, N(0,1) in bf16. Every block has its own
+        random stream derived from seed 1, so the global tensors are the same for every N and
+        any rank can regenerate any block (the sampled check below needs other ranks' keys)."""
+        gen = torch.Generator(device=dev).manual_seed(1 + 7919 * KINDS[kind] + 104729 * b)
+        out = torch.empty(blk, N_HEADS, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        flat = out.view(-1)
+        chunk = 1 << 25
         for off in range(0, flat.numel(), chunk):        # bounded temporary fp32 memory
             n = min(chunk, flat.numel() - off)
             flat[off:off + n] = torch.randn(n, generator=gen, dtype=torch.float32, device=dev).to(torch.bfloat16)
+        return out
+
+    # ---- inputs: generated once on the device, kept as pinned host copies (for the end-to-end
+    # arm) and as device copies (kernel arm) ----------------------------------------------------
+    def make_pair(kind):
+        d = torch.empty(1, S_loc, N_HEADS, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        for i, b in enumerate(owned):
+            d[0, i * blk:(i + 1) * blk] = gen_block(kind, b)
         h = torch.empty(d.shape, dtype=torch.bfloat16, pin_memory=True)
         h.copy_(d)
         return h, d
-    (h_q, q), (h_k, k), (h_v, v), (h_do, d_o) = (make_pair() for _ in range(4))
+    (h_q, q), (h_k, k), (h_v, v), (h_do, d_o) = (make_pair(kd) for kd in ("q", "k", "v", "do"))
     torch.cuda.synchronize()
 
     if world == 1:
@@ -191,6 +207,62 @@ def main() -> None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = t.item()
         return ms, _lib.LAUNCHES[0] - n0
+
+    # ---- correctness at the benchmark shape: sampled rows against an fp32 oracle --------------
+    check = None
+    if args.check:
+        from ultraattn_b200.utils.sampled_check import SampledCheck, pick_rows
+        if world == 1:
+            A.attn_fwd([q], [k], [v], [(o, lse)], fplan)
+            o_c, lse_c = o, lse
+            dq_c, dk_c, dv_c = ua.api.local_backward(q, k, v, o, lse, d_o, bplan)
+        else:
+            o_c, lse_c = runtime.forward(q, k, v)
+            dq_c, dk_c, dv_c = runtime.backward(d_o, q, k, v, o_c, lse_c)
+        A.check_status(dev)
+        from ultraattn_b200.ops import elementwise as E
+        dvec_c = torch.empty(1, N_HEADS, S_loc, dtype=torch.float32, device=dev)         # D = rowsum(dO * O)
+        E.rowdot(o_c[0], d_o[0], dvec_c[0])
+        if world > 1:       # lse / D of the other ranks' rows (needed by the key-row oracle)
+            lse_all = [torch.empty_like(lse_c) for _ in range(world)]
+            dvec_all = [torch.empty_like(dvec_c) for _ in range(world)]
+            dist.all_gather(lse_all, lse_c.contiguous())
+            dist.all_gather(dvec_all, dvec_c)
+        else:
+            lse_all, dvec_all = [lse_c], [dvec_c]
+        local = {"q": q, "k": k, "v": v, "do": d_o}
+        per_rank = N_BLOCKS // world
+
+        def get_block(kind, b):
+            if b in owned:
+                i = owned.index(b)
+                return local[kind][0, i * blk:(i + 1) * blk]
+            return gen_block(kind, b)
+
+        def stat_block(parts):
+            return lambda b: parts[b // per_rank][0, :, (b % per_rank) * blk:(b % per_rank + 1) * blk]
+
+        loc = lambda t: (t // blk - owned[0]) * blk + t % blk            # global token -> index in the shard
+        chk = SampledCheck(pattern, S, get_block, head_dim=HEAD_DIM)
+        rows = pick_rows(pattern, S, owned, max(8, args.check_rows // world), seed=rank)
+        res = chk.check_query_rows(rows, lambda t: (o_c[0, loc(t)], lse_c[0, :, loc(t)], dq_c[0, loc(t)]))
+        res.update(chk.check_key_rows(rows[::4], lambda u: (dk_c[0, loc(u)], dv_c[0, loc(u)]),
+                                      stat_block(lse_all), stat_block(dvec_all)))
+        flat = torch.tensor([res[kk][m] for kk in sorted(res) for m in ("max_abs_over_max_ref", "max_row_relative")],
+                            device=dev, dtype=torch.float64)
+        cks = torch.stack([o_c.sum(dtype=torch.float64), dq_c.sum(dtype=torch.float64)])
+        if world > 1:
+            dist.all_reduce(flat, op=dist.ReduceOp.MAX)
+            dist.all_reduce(cks)
+        it = iter(flat.tolist())
+        check = {kk: {"max_abs_over_max_ref": next(it), "max_row_relative": next(it)} for kk in sorted(res)}
+        check["rows_per_rank"] = len(rows)
+        check["includes_last_token"] = (S - 1) in rows if rank == world - 1 else None
+        check["sum_o"], check["sum_dq"] = cks.tolist()          # same data for every N: comparable across N
+        worst = max(vv["max_row_relative"] for vv in check.values() if isinstance(vv, dict) and "max_row_relative" in vv)
+        check["ok"] = bool(worst < 0.05)
+        del o_c, lse_c, dq_c, dk_c, dv_c, dvec_c, lse_all, dvec_all
+        torch.cuda.empty_cache()
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -267,7 +339,10 @@ def main() -> None:
 
     if rank == 0:
         vol = pattern.volume * (S / N_BLOCKS) ** 2 * 4 * HEAD_DIM * N_HEADS      # forward model FLOPs
-        tflops = vol * 3.5 / (ms * 1e-3) / 1e12 / world
+        # the backward runs five GEMMs for the forward's two (2.5x, recomputing S) but the model
+        # needs only 2x: hardware FLOPs (what the tensor cores did) vs model FLOPs
+        hw_tflops = vol * 3.5 / (ms * 1e-3) / 1e12 / world
+        model_tflops = vol * 3.0 / (ms * 1e-3) / 1e12 / world
         roof = None
         try:        # achieved fraction of max(FLOPs at the measured GEMM peak, NVLink bytes at link bandwidth)
             from ultraattn_b200.utils.metrics import load_peaks, roofline
@@ -284,12 +359,12 @@ def main() -> None:
         print(json.dumps({
             "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic N(0,1), seed 1",
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic N(0,1), seed 1 (one stream per 16k block: the same tensors for every N)",
             "config": {"model": "attention-only (Llama2-7B attention shape: 32 heads x 128)",
                        "pattern": "strided: 32 blocks of 16k, j<=i and (i-j<=1 or (i-j)%4==0)",
                        "global_batch": 1, "seq_len": S, "parallelism": parallelism,
                        "l2": "inputs (4 GiB per tensor in total) far exceed the 126 MB L2; no flush needed"},
-            "model_tflops_per_gpu": tflops, "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "hw_tflops_per_gpu": hw_tflops, "model_tflops_per_gpu": model_tflops, "check": check, "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "nvlink_bytes_rank0": traffic, "roofline": roof,
             "tokens_per_s": S / (ms * 1e-3) if ms else None,
             "e2e_tokens_per_s": (S / (e2e["value"] * 1e-3)) if isinstance(e2e, dict) and e2e.get("value") else None,

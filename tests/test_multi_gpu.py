@@ -303,6 +303,70 @@ def test_context_parallel_4gpu_fused():
         assert res[r]["rel_err"] < 2e-2, res
 
 
+@pytest.mark.parametrize("path", ["fused", "nccl"])
+@pytest.mark.parametrize("pattern,args", [("strided", (32, 4, 2)), ("global_local", (32, 1, 2))],
+                         ids=["strided", "global_local"])
+def test_context_parallel_8gpu(path, pattern, args):
+    """The benchmark's block tables (32 blocks) on all eight GPUs of a box, two iterations."""
+    _need(8)
+    res = _run(8, {"pattern": pattern, "args": args, "S": 8192, "H": 2, "path": path})
+    for r in range(8):
+        assert "error" not in res[r], res[r].get("error")
+        assert res[r]["rel_err"] < 2e-2, res
+
+
+def _interleaved_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    try:
+        from ultraattn_b200 import patterns as P
+        from ultraattn_b200.ops import attention as A
+        from ultraattn_b200.runtime import ContextParallelAttention
+        pattern = P.strided(8, 4, 2)
+        S, H = 2048, 2
+        rt = ContextParallelAttention(pattern, S, H, 128, device=dev, path="fused", plan_time_limit=5.0)
+        blk = S // rt.table.shape[0]
+        idx = torch.cat([torch.arange(b * blk, (b + 1) * blk) for b in range(rt.table.shape[0]) if rt.cmap[b] == rank])
+        data, outs, worst = {}, {}, 0.0
+        for name, seed in (("A", 1), ("B", 2)):
+            g = torch.Generator().manual_seed(seed)
+            data[name] = [torch.randn(1, S, H, 128, generator=g).to(torch.bfloat16) for _ in range(4)]
+            ql, kl, vl, _ = (t[:, idx].contiguous().to(dev) for t in data[name])
+            outs[name] = (ql, kl, vl) + tuple(rt.forward(ql, kl, vl))
+        for name in ("A", "B"):             # A's backward comes after B's forward
+            ql, kl, vl, o, lse = outs[name]
+            q, k, v, d_o = data[name]
+            dq, dk, dv = rt.backward(d_o[:, idx].contiguous().to(dev), ql, kl, vl, o, lse)
+            torch.cuda.synchronize()
+            A.check_status(dev)
+            _, _, dq_ref, dk_ref, dv_ref = P.dense_attention_with_grads(q.float(), k.float(), v.float(), d_o.float(), pattern)
+            for got, ref in ((dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+                worst = max(worst, (got.float().cpu() - ref[:, idx]).abs().max().item() / (ref.abs().max().item() + 1e-6))
+        ret[rank] = {"rel_err": worst}
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = {"error": f"{type(e).__name__}: {e}\n{traceback.format_exc()}"}
+    finally:
+        dist.destroy_process_group()
+
+
+def test_backward_after_another_forward_2gpu():
+    """fwd(A); fwd(B); bwd(A); bwd(B) on the fused path: A's backward must not reuse the peers'
+    Q / K / V that B's forward left in the staging mirrors."""
+    _need(2)
+    port = 29700 + os.getpid() % 200
+    ret = mp.Manager().dict()
+    mp.spawn(_interleaved_worker, args=(2, port, ret), nprocs=2, join=True)
+    for r in range(2):
+        assert "error" not in ret[r], ret[r].get("error")
+        assert ret[r]["rel_err"] < 2e-2, dict(ret)
+
+
 def _ulysses_worker(rank, world, port, ret):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")

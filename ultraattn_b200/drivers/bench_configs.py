@@ -7,7 +7,8 @@ Configurations: ``causal128k`` (dense causal, S = 128k, forward + backward), ``s
 (32 blocks of 16k, stride 4, window 2, forward + backward), ``gl512k`` (global+local, block 0
 global, causal window 2, forward + backward), ``star512k`` and ``streaming512k`` (prefill, forward
 only); all with 32 heads of 128, batch 1, bf16. Paths: ``fused`` (peer-memory kernels), ``nccl``
-(plan executed with NCCL messages), ``ring`` (K/V ring; under a block-sparse pattern it skips the excluded block pairs) / ``zigzag`` (dense causal),
+(plan executed with NCCL messages, launch order by list scheduling; ``nccl-ilp``: by the
+kernel-schedule integer program), ``ring`` (K/V ring; under a block-sparse pattern it skips the excluded block pairs) / ``zigzag`` (dense causal),
 ``grid<Y>x<X>`` (kernel-tile form: gathers, one launch, merge / reduce-scatter; dense patterns only).
 
 Every line carries the device time (max over ranks), the model TFLOP/s per GPU and the achieved
@@ -75,6 +76,8 @@ def main() -> None:
     ap.add_argument("--paths", default="fused,nccl")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--scale", type=int, default=1, help="divide every sequence length (smoke runs)")
+    ap.add_argument("--trace", action="store_true",
+                    help="fused path: also print the device time of every phase of a step (slowest rank per phase)")
     ap.add_argument("--metrics-jsonl", default=None, help="append one JSON object per measured call to this file")
     a = ap.parse_args()
     from ..utils.metrics import MetricsLogger
@@ -119,8 +122,9 @@ def main() -> None:
                         A.attn_fwd([q], [k], [v], [(o, lse)], fplan)
                         if train:
                             api.local_backward(q, k, v, o, lse, d_o, bplan)
-                elif path in ("fused", "nccl"):
-                    rt = ContextParallelAttention(pat, S, H, D, device=dev, path=path, plan_time_limit=15.0)
+                elif path in ("fused", "nccl", "nccl-ilp"):
+                    rt = ContextParallelAttention(pat, S, H, D, device=dev, path=path.split("-")[0], plan_time_limit=15.0,
+                                                  plan_type="ILP" if path.endswith("-ilp") else "Flexflow")
                     if path == "fused":
                         im = rt.impl
                         blk_q = im.blk * H * D * 2
@@ -156,6 +160,18 @@ def main() -> None:
                                             pat.check_causal(), block_types=types)
                 ms = _timed(step, a.iters, dev, world)
                 A.check_status(dev)
+                phases = None
+                if a.trace and world > 1 and path == "fused":
+                    rt.impl.enable_trace()
+                    step()
+                    ph = rt.impl.metrics()["phases_ms"]
+                    rt.impl.enable_trace(False)
+                    names = sorted(ph)
+                    t = torch.tensor([ph[n] for n in names], device=dev)
+                    tmax, tmin = t.clone(), t.clone()
+                    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+                    dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+                    phases = {n: [round(lo, 3), round(hi, 3)] for n, lo, hi in zip(names, tmin.tolist(), tmax.tolist())}
                 t_comp = flops / world / (peak * 1e12)
                 t_link = nvl_bytes / (NVLINK_GBS * 1e9)
                 if rank == 0:
@@ -164,7 +180,8 @@ def main() -> None:
                                       "roofline_ms": round(max(t_comp, t_link) * 1e3, 3),
                                       "roofline_bound": "compute" if t_comp >= t_link else "nvlink",
                                       "fraction_of_roofline": round(max(t_comp, t_link) * 1e3 / ms, 3),
-                                      "peak_tflops_of_measured": peak}), flush=True)
+                                      "peak_tflops_of_measured": peak,
+                                      **({"phases_ms_min_max_over_ranks": phases} if phases else {})}), flush=True)
                     if metrics is not None:
                         metrics.log(name, ms * 1e-3, flops_per_gpu=flops / world, pull_bytes=int(nvl_bytes),
                                     path=path if world > 1 else "local", n_gpus=world, S=S)

@@ -91,15 +91,18 @@ class ContextParallelAttention:
                  n_kv_heads: Optional[int] = None, batch: int = 1, allocation: str = "ilp",
                  plan_time_limit: float = 20.0, dtype=torch.bfloat16, cmap=None,
                  nvls_min_consumers: int = 2, plan=None, local_groups: bool = False,
-                 nvls_reduce: Optional[bool] = None):
-        """``plan``: an earlier runtime's ``(table, cmap)`` to reuse instead of solving the
+                 nvls_reduce: Optional[bool] = None, plan_type: str = "Flexflow"):
+        """``plan_type`` (NCCL path): how the launch order on the compute / send / receive streams
+        is chosen, ``"Flexflow"`` (list scheduling) or ``"ILP"`` (the kernel-schedule integer
+        program, reference search_algo/execute_plan.py:209-275).
+        ``plan``: an earlier runtime's ``(table, cmap)`` to reuse instead of solving the
         allocation again (fused path; e.g. a second runtime for a different number of heads).
         ``local_groups``: create the internal process groups with only the members of ``group``
         taking part (needed when ``group`` is a strict subset of the job, as after a rank left)."""
         self._ctor = dict(seq_len=seq_len, n_heads=n_heads, head_dim=head_dim, device=device, path=path,
                           n_kv_heads=n_kv_heads, batch=batch, allocation=allocation,
                           plan_time_limit=plan_time_limit, dtype=dtype, nvls_min_consumers=nvls_min_consumers,
-                          nvls_reduce=nvls_reduce)
+                          nvls_reduce=nvls_reduce, plan_type=plan_type)
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
@@ -121,7 +124,7 @@ class ContextParallelAttention:
         elif path == "nccl":
             from .executor import PlanExecutor
             kw = dict(pattern=pattern, cp=self.world, seq_len=seq_len, n_heads=n_heads, head_dim=head_dim,
-                      n_kv_heads=n_kv_heads, batch=batch, allocation=allocation, plan_type="Flexflow",
+                      n_kv_heads=n_kv_heads, batch=batch, allocation=allocation, plan_type=plan_type,
                       time_limit=plan_time_limit, cmap=cmap)
             if self.rank == 0 and allocation not in ("naive", "lightseq"):
                 # same partition granularity (and, with cmap="search", ownership) as the fused path
