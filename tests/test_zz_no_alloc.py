@@ -25,11 +25,21 @@ def _close(got, ref, tol):
     assert err <= tol * scale, f"max err {err} vs scale {scale}"
 
 
+# each case is a series of (tokens, heads, kv heads) calls made one after the other on the shared scratch
+CASES = {
+    "same-shape-twice": [(2048, 4, 2), (2048, 4, 2)],
+    "large-then-small-ragged": [(4096, 4, 4), (1000, 4, 2)],     # stale tails of the first call must not leak
+    "at-the-size-limit": [(32768, 4, 4), (2048, 2, 1)],          # tokens * heads == 131072 exactly
+}
+
+
 @pytest.mark.parametrize("causal", [True, False])
-def test_noalloc_backward_matches_regular_entry_point(causal):
+@pytest.mark.parametrize("case", list(CASES), ids=list(CASES))
+def test_noalloc_backward_matches_regular_entry_point(case, causal):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA GPU")
     from ultraattn_b200 import _lib
+    from ultraattn_b200 import patterns as P
     from ultraattn_b200.ops import attention as A, elementwise as E
     lib = _lib.load()
     fn = lib.ua_attn_bwd_dense_noalloc              # the exported C symbol itself
@@ -37,8 +47,7 @@ def test_noalloc_backward_matches_regular_entry_point(causal):
     fn.restype = ctypes.c_int
     fn.argtypes = [vp] * 9 + [ctypes.c_int] * 4 + [ctypes.c_float, vp, vp]
     dev = torch.device("cuda", 0)
-    S, H, Hk = 2048, 4, 2
-    for call in range(2):                           # two calls in a row on the shared scratch
+    for call, (S, H, Hk) in enumerate(CASES[case]):  # calls in a row on the shared scratch
         torch.manual_seed(10 + call)
         q = torch.randn(1, S, H, 128, device=dev, dtype=torch.bfloat16)
         k = torch.randn(1, S, Hk, 128, device=dev, dtype=torch.bfloat16)
@@ -68,6 +77,14 @@ def test_noalloc_backward_matches_regular_entry_point(causal):
         _close(dq, dq_ref, 2e-2)
         _close(dk, dk_ref, 2e-2)
         _close(dv, dv_ref, 2e-2)
+        if S <= 1024:
+            # and once against plain fp32 attention with autograd, so the test also stands alone
+            pat = P.causal(1) if causal else P.full(1)
+            _, _, dq_o, dk_o, dv_o = P.dense_attention_with_grads(q.cpu().float(), k.cpu().float(), v.cpu().float(),
+                                                                  d_o.cpu().float(), pat)
+            _close(dq.cpu(), dq_o, 2e-2)
+            _close(dk.cpu(), dk_o, 2e-2)
+            _close(dv.cpu(), dv_o, 2e-2)
     # beyond the built-in scratch: refused, nothing launched
     rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr(), lse.data_ptr(), dvec.data_ptr(),
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), 1 << 20, H, Hk, int(causal), 0.1, None,

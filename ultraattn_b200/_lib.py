@@ -65,6 +65,7 @@ def _declare(lib):
         "ua_swiglu_fwd": [vp, vp, l, i, vp],
         "ua_swiglu_bwd": [vp, vp, vp, l, i, vp],
         "ua_adam": [vp, vp, vp, vp, vp, l, f, f, f, f, f, i, f, vp],
+        "ua_mma_rate": [i, i, i, i, vp, vp, vp],
     }
     for name, args in sigs.items():
         if hasattr(lib, name):
@@ -75,7 +76,9 @@ def _declare(lib):
 
 
 def load():
-    """Return the loaded library (building it first if the .so is missing)."""
+    """Return the loaded library, (re)building it first when it is missing or older than any of
+    its sources or headers: the ctypes structures of this module mirror structs of those headers,
+    so a stale binary must never be loaded."""
     global _lib
     if _lib is not None:
         return _lib
@@ -83,11 +86,13 @@ def load():
     if os.environ.get("UA_LIB_PATH"):           # explicit library file (development builds)
         _lib = _declare(ctypes.CDLL(os.environ["UA_LIB_PATH"]))
         return _lib
-    if not path.exists() or os.environ.get("UA_REBUILD") == "1":
-        try:
-            _build.build_all(force=os.environ.get("UA_REBUILD") == "1")
-        except Exception as e:  # noqa: BLE001
+    try:
+        # cheap when the library is up to date (a few stat calls); takes a lock when it builds
+        _build.build_all(force=os.environ.get("UA_REBUILD") == "1")
+    except Exception as e:  # noqa: BLE001
+        if not path.exists():
             raise ImportError(f"ultraattn_b200: kernel library missing and build failed: {e}") from e
+        raise ImportError(f"ultraattn_b200: kernel library is older than its sources and the rebuild failed: {e}") from e
     _lib = _declare(ctypes.CDLL(str(path)))
     return _lib
 

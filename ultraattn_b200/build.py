@@ -42,37 +42,30 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
-def probe_sources() -> list[Path]:
-    """Stand-alone measurement programs (not linked into the library)."""
-    return sorted((CSRC / "microbench").glob("*.cu"))
-
-
-def build_probes(force: bool = False) -> list[Path]:
-    """Compile the stand-alone probes to objects, so that a build checks every CUDA source of the
-    tree. Returns the object paths."""
-    nvcc = _nvcc()
-    OBJ_DIR.mkdir(parents=True, exist_ok=True)
-    objs = []
-    for src in probe_sources():
-        obj = OBJ_DIR / ("probe_" + src.stem + ".o")
-        if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, _newest_header_mtime()):
-            r = subprocess.run([nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)], capture_output=True, text=True)
-            if r.returncode != 0:
-                raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
-        objs.append(obj)
-    return objs
-
-
 def _newest_header_mtime() -> float:
-    return max((p.stat().st_mtime for p in CSRC.glob("*.cuh")), default=0.0)
+    hdrs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
+    return max((p.stat().st_mtime for p in hdrs), default=0.0)
+
+
+STAMP_PATH = LIB_DIR / "build_stamp.txt"
+
+
+def source_digest() -> str:
+    """Hash of everything the library is built from (sources, headers, compiler flags). File times
+    do not survive every way of copying a tree to another machine; contents do."""
+    import hashlib
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    for f in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    return h.hexdigest()
 
 
 def needs_build() -> bool:
-    if not LIB_PATH.exists():
+    """True when the library is missing or was built from other sources than the present ones."""
+    if not LIB_PATH.exists() or not STAMP_PATH.exists():
         return True
-    t = LIB_PATH.stat().st_mtime
-    hdr = _newest_header_mtime()
-    return any(s.stat().st_mtime > t for s in sources()) or hdr > t
+    return STAMP_PATH.read_text().strip() != source_digest()
 
 
 def build_all(force: bool = False, verbose: bool = False) -> Path:
@@ -123,6 +116,7 @@ def _build_locked(nvcc: str, force: bool, verbose: bool) -> Path:
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     os.replace(tmp, LIB_PATH)          # a reader never sees a half-written library
+    STAMP_PATH.write_text(source_digest() + "\n")
     return LIB_PATH
 
 

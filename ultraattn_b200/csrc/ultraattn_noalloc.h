@@ -15,7 +15,7 @@
  * fp32 -> bf16 conversion of dQ.
  *
  * Where its scratch lives: the fp32 dQ accumulator and the launch tables sit in a fixed device
- * array inside the library (64 MiB + 8 KiB, held by every GPU that loads the library until the
+ * array inside the library (64 MiB + 4.5 KiB, held by every GPU that loads the library until the
  * process ends). Hence the limits  tokens <= 65536  and  tokens * n_heads <= 131072;  larger
  * problems are rejected with a non-zero return code and a message from ua_last_error().
  * The call itself performs no cudaMalloc / cudaFree and calls no allocating library routine.

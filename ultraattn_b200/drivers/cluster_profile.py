@@ -179,6 +179,27 @@ def _profile_memory_bound_ops(rows: int, iters: int) -> None:
         print(json.dumps(rec))
 
 
+def _profile_mma_rate(iters: int = 200) -> None:
+    """Clocks per ``tcgen05.mma`` (M = 128, K = 16, bf16) for N = 64 / 128 / 256, operands from
+    shared memory (SS) or A from tensor memory (TS), four ways of issuing; one JSON line each."""
+    from .. import _lib
+    from ..ops import attention as A
+    dev = torch.device("cuda")
+    out = torch.zeros(2, dtype=torch.int64, device=dev)
+    st = A.status_buffer(dev)
+    for n in (64, 128, 256):
+        for mode in (0, 1):
+            for variant in range(4):
+                rc = _lib.load().ua_mma_rate(variant, mode, n, iters, out.data_ptr(), st.data_ptr(),
+                                             torch.cuda.current_stream(dev).cuda_stream)
+                _lib.check(rc, "ua_mma_rate")
+                torch.cuda.synchronize()
+                A.check_status(dev)
+                issue, complete = (x / (8.0 * iters) for x in out.tolist())
+                print(json.dumps({"op": "tcgen05.mma", "operands": "TS" if mode else "SS", "N": n, "variant": variant,
+                                  "clk_per_mma_issue": round(issue, 1), "clk_per_mma_complete": round(complete, 1)}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernels", action="store_true")
@@ -186,7 +207,7 @@ def main() -> None:
     ap.add_argument("--out", default="logs/m_configs")
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--max-seconds", type=float, default=0.0, help="(--kernels) stop the sweep after this long")
-    ap.add_argument("--one", choices=["fwd", "bwd", "gemm", "ops", "gate"], default=None)
+    ap.add_argument("--one", choices=["fwd", "bwd", "gemm", "ops", "gate", "mma_rate"], default=None)
     ap.add_argument("--S", type=int, default=16384)
     ap.add_argument("--Nh", type=int, default=32)
     ap.add_argument("--causal", action="store_true")
@@ -194,6 +215,9 @@ def main() -> None:
     a = ap.parse_args()
     if a.one == "ops":
         _profile_memory_bound_ops(a.S, a.iters)
+        return
+    if a.one == "mma_rate":
+        _profile_mma_rate()
         return
     if a.one == "gate":
         # small tiles with and without the start gate: what the host launch path adds to a timing
