@@ -23,7 +23,8 @@ What runs is the reference's own stack, through its own entry points:
 
 Environment stand-ins, all outside the reference's files: OpenMPI-style rank variables derived
 from torchrun's, a loop-back fallback for host-name resolution, ``gurobipy`` / ``pulp`` import-only
-modules, the machine-profile directory ``logs/m_configs`` the reference copies into its database
+modules, an ``int()`` around the peer index the reference passes to ``ncclSend`` / ``ncclRecv`` as a
+``numpy.bool`` (NumPy 2 no longer lets ctypes read one as an integer), the machine-profile directory ``logs/m_configs`` the reference copies into its database
 (filled with the reference's own H800 kernel profile and link curves).
 """
 from __future__ import annotations
@@ -84,6 +85,22 @@ def _patch_hostname_resolution() -> None:
         except OSError:
             return "127.0.0.1"
     socket.gethostbyname = gethostbyname
+
+
+def _numpy2_peer_index_compat() -> None:
+    """The reference computes the peer index of a two-rank communicator as ``self.rank <
+    global_dst`` on numpy integers (orchestrated_attn/utils.py:308-334), i.e. a ``numpy.bool``, and
+    hands it to a ctypes ``c_int`` parameter. NumPy 1.x let ctypes read that through ``__index__``;
+    NumPy 2 (installed here) removed it. Convert at the call boundary, outside the reference's files."""
+    from tests.distributed.device_communicators.pynccl import PyNcclCommunicator
+    send, recv = PyNcclCommunicator.send, PyNcclCommunicator.recv
+
+    def send_int(self, tensor, dst, stream=None):
+        return send(self, tensor, int(dst), stream)
+
+    def recv_int(self, tensor, src, stream=None):
+        return recv(self, tensor, int(src), stream)
+    PyNcclCommunicator.send, PyNcclCommunicator.recv = send_int, recv_int
 
 
 def _provide_libnccl() -> str:
@@ -243,6 +260,7 @@ def run(args) -> dict:
     from orchestrated_attn.global_vars import get_global_var as get_global_var_orch
     from orchestrated_attn.orchestrated_attn_impl import orchestrated_attn_func, orchestrated_attn_backward
 
+    _numpy2_peer_index_compat()
     ncclcomm_global, gloo_group = initialize_distribution()
     if rank == 0 and os.path.exists(marker):
         os.remove(marker)

@@ -68,6 +68,49 @@ def test_gemm_scatter_gather_single_gpu(dev):
     A.check_status(dev)
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (1000, 520, 264), (4096, 2048, 1024), (320, 256, 64)])
+def test_gemm_cta_pair_all_layouts(dev, monkeypatch, M, N, K):
+    """The 256 x 256 tile computed by a pair of CTAs (cta_group::2), forced on for shapes the
+    heuristic would give to the single-CTA kernel: x W^T, dy W and dy^T x storage orders, ragged
+    edges, and the scatter / gather fusions."""
+    from ultraattn_b200.ops import attention as A, gemm as G
+    monkeypatch.setenv("UA_GEMM_PAIR", "1")
+    torch.manual_seed(3)
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+    _close(G.gemm(a, b), a.float() @ b.float().t(), 1e-2)
+    bkn = torch.randn(K, N, device=dev, dtype=torch.bfloat16)
+    _close(G.gemm(a, bkn, b_is_kn=True), a.float() @ bkn.float(), 1e-2)
+    akm = torch.randn(K, M, device=dev, dtype=torch.bfloat16)
+    _close(G.gemm(akm, bkn, a_is_km=True, b_is_kn=True), akm.float().t() @ bkn.float(), 1e-2)
+    _close(G.gemm(akm, b, a_is_km=True), akm.float().t() @ b.float().t(), 1e-2)
+    A.check_status(dev)
+    if N % 128 == 0 and K % 128 == 0:
+        P = 2
+        ref = a.float() @ b.float().t()
+        dsts = [torch.zeros(2 * M, N // P, device=dev, dtype=torch.bfloat16) for _ in range(P)]
+        G.gemm_scatter(a, b, [d.data_ptr() for d in dsts], N // P, M)
+        for g, d in enumerate(dsts):
+            _close(d[M:], ref[:, g * (N // P):(g + 1) * (N // P)], 1e-2)
+            assert d[:M].abs().max().item() == 0
+        srcs = [torch.randn(3 * M, K // P, device=dev, dtype=torch.bfloat16) for _ in range(P)]
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        G.gemm_gather([t.data_ptr() for t in srcs], 3 * M, K // P, M, M, K // P, b, out)
+        _close(out, torch.cat([t[M:2 * M] for t in srcs], dim=1).float() @ b.float().t(), 1e-2)
+        A.check_status(dev)
+
+
+def test_gemm_large_uses_pair_kernel_and_matches(dev):
+    """A projection-sized problem (the heuristic picks the CTA-pair kernel) against torch."""
+    from ultraattn_b200.ops import attention as A, gemm as G
+    torch.manual_seed(4)
+    a = torch.randn(8192, 4096, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(4096, 4096, device=dev, dtype=torch.bfloat16)
+    c = G.gemm(a, b)
+    A.check_status(dev)
+    _close(c, (a @ b.t()).float(), 1e-2)
+
+
 CASES = [
     ("full", 256, 1, 1, [[1]], 256),
     ("causal", 256, 2, 2, [[2]], 256),

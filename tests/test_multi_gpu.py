@@ -246,6 +246,66 @@ def test_llama_context_parallel_training_2gpu():
     assert res[0]["nccl"] == res[1]["nccl"]
 
 
+def _llama_ulysses_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    try:
+        from ultraattn_b200 import patterns as P
+        from ultraattn_b200.models.llama import LlamaConfig, LlamaModel
+        from ultraattn_b200.ops import attention as A
+        from ultraattn_b200.parallel.ulysses_fused import unpermute_qkv_weight
+        from ultraattn_b200.runtime import ContextParallelAttention
+        cfg = LlamaConfig(n_layers=2, hidden=256, n_heads=2, head_dim=128, ffn=512, vocab=1000)
+        pat = P.global_local(4, 1, 2)
+        S = 2048
+        S_loc = S // world
+        g = torch.Generator().manual_seed(3)
+        ids_all = torch.randint(0, cfg.vocab, (S + 1,), generator=g)
+        # head-parallel model: contiguous token ranges
+        pos_u = torch.arange(rank * S_loc, (rank + 1) * S_loc)
+        mu = LlamaModel(cfg, device=dev, pattern=pat, group=dist.group.WORLD, seed=0, nvls_optimizer=False,
+                        seq_algo="ulysses", seq_len=S)
+        assert mu.ulysses is not None
+        # context-parallel model with the same weights (its wqkv rows in [q | k | v] order)
+        rt = ContextParallelAttention(pat, S, cfg.n_heads, 128, device=dev, path="fused", plan_time_limit=5.0)
+        blk = S // rt.table.shape[0]
+        pos_c = torch.cat([torch.arange(b * blk, (b + 1) * blk) for b in range(rt.table.shape[0]) if rt.cmap[b] == rank])
+        mc = LlamaModel(cfg, device=dev, pattern=pat, runtime=rt, group=dist.group.WORLD, seed=0, nvls_optimizer=False)
+        with torch.no_grad():
+            for li in range(cfg.n_layers):
+                mc.p[f"l{li}.wqkv"].copy_(unpermute_qkv_weight(mu.p[f"l{li}.wqkv"], cfg.n_heads, cfg.kv_heads, 128, world))
+            mc.master.copy_(mc.flat[rank * mc.shard:(rank + 1) * mc.shard].float())
+        lu = [mu.train_step(ids_all[pos_u].to(dev), ids_all[pos_u + 1].to(dev), pos_u.to(dev), n_total_tokens=S) for _ in range(3)]
+        lc = [mc.train_step(ids_all[pos_c].to(dev), ids_all[pos_c + 1].to(dev), pos_c.to(dev), n_total_tokens=S) for _ in range(3)]
+        torch.cuda.synchronize()
+        A.check_status(dev)
+        ret[rank] = {"ulysses": lu, "cp": lc}
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = {"error": f"{type(e).__name__}: {e}\n{traceback.format_exc()}"}
+    finally:
+        dist.destroy_process_group()
+
+
+def test_llama_ulysses_training_matches_context_parallel_2gpu():
+    """Three training steps with head-parallel attention (all-to-alls fused into the projection
+    GEMMs, forward and backward) follow the context-parallel model started from the same weights."""
+    _need(2)
+    port = 29450 + os.getpid() % 100
+    ret = mp.Manager().dict()
+    mp.spawn(_llama_ulysses_worker, args=(2, port, ret), nprocs=2, join=True)
+    res = dict(ret)
+    for r in range(2):
+        assert "error" not in res[r], res[r].get("error")
+        u, c = res[r]["ulysses"], res[r]["cp"]
+        assert u[2] < u[0] and all(abs(a - b) < 3e-2 for a, b in zip(u, c)), res
+
+
 def _campaign_worker(rank, world, port, root, ret):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -416,6 +476,87 @@ def test_fused_ulysses_projections_2gpu():
     for r in range(2):
         assert "error" not in ret[r], ret[r].get("error")
         assert ret[r]["rel_err"] < 3e-2, dict(ret)
+
+
+def _ulysses_grad_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    try:
+        from ultraattn_b200 import patterns as P
+        from ultraattn_b200.ops import attention as A, elementwise as E
+        from ultraattn_b200.parallel.ulysses_fused import (FusedUlyssesAttention, permute_qkv_weight,
+                                                            unpermute_qkv_weight, unfused_reference)
+        S, hidden, H = 1024, 512, 4
+        pattern = P.strided(8, 4, 2)
+        g = torch.Generator().manual_seed(0)
+        x = (torch.randn(S, hidden, generator=g) * 0.5).to(torch.bfloat16)
+        wqkv = (torch.randn(3 * H * 128, hidden, generator=g) * 0.05).to(torch.bfloat16)
+        wo = (torch.randn(hidden, H * 128, generator=g) * 0.05).to(torch.bfloat16)
+        dy = (torch.randn(S, hidden, generator=g) * 0.5).to(torch.bfloat16)
+        cos, sin = E.rope_tables(S, 128, 10000.0, dev)
+        mod = FusedUlyssesAttention(dist.group.WORLD, dev, S, hidden, H, pattern=pattern)
+        S_loc = S // world
+        sl = slice(rank * S_loc, (rank + 1) * S_loc)
+        wp = permute_qkv_weight(wqkv, H, H, 128, world)
+        assert torch.equal(unpermute_qkv_weight(wp, H, H, 128, world), wqkv)
+        res = {}
+        for name in ("fused", "unfused"):
+            xl = x[sl].contiguous().to(dev).requires_grad_()
+            w1 = wp.to(dev).requires_grad_()
+            w2 = wo.to(dev).requires_grad_()
+            for _ in range(2):                    # twice: buffers and barriers must survive reuse
+                for t in (xl, w1, w2):
+                    t.grad = None
+                if name == "fused":
+                    y = mod(xl, w1, w2, cos, sin)
+                else:
+                    y = unfused_reference(xl, w1, w2, dist.group.WORLD, H, H, 128, pattern, cos, sin)
+                y.backward(dy[sl].to(dev))
+                torch.cuda.synchronize()
+                A.check_status(dev)
+            # weight gradients of the ranks add up (every rank saw its own tokens)
+            gw1, gw2 = w1.grad.float(), w2.grad.float()
+            dist.all_reduce(gw1)
+            dist.all_reduce(gw2)
+            res[name] = (y.detach().float().cpu(), xl.grad.float().cpu(), gw1.cpu(), gw2.cpu())
+        # CPU fp32 autograd of the same block on the whole sequence
+        xf = x.float().requires_grad_()
+        wq = wqkv.float().requires_grad_()
+        wof = wo.float().requires_grad_()
+        qkv = xf @ wq.t()
+        q, k, v = (qkv[:, i * H * 128:(i + 1) * H * 128].reshape(S, H, 128) for i in range(3))
+        pos = torch.arange(S)
+        rot = lambda t: torch.cat([t[..., :64] * cos.cpu()[pos][:, None] - t[..., 64:] * sin.cpu()[pos][:, None],
+                                   t[..., 64:] * cos.cpu()[pos][:, None] + t[..., :64] * sin.cpu()[pos][:, None]], -1)
+        o, _ = P.dense_attention(rot(q)[None], rot(k)[None], v[None], pattern.token_mask(S))
+        yf = o[0].reshape(S, H * 128) @ wof.t()
+        yf.backward(dy.float())
+        oracle = (yf.detach()[sl], xf.grad[sl], permute_qkv_weight(wq.grad, H, H, 128, world), wof.grad)
+        rel = lambda a, b: (a - b).abs().max().item() / (b.abs().max().item() + 1e-6)
+        ret[rank] = {"fused_vs_unfused": max(rel(a, b) for a, b in zip(res["fused"], res["unfused"])),
+                     "fused_vs_oracle": max(rel(a, b) for a, b in zip(res["fused"], oracle))}
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = {"error": f"{type(e).__name__}: {e}\n{traceback.format_exc()}"}
+    finally:
+        dist.destroy_process_group()
+
+
+def test_fused_ulysses_backward_2gpu():
+    """Gradients of the head-parallel block through the fused projections (dO scattered by the
+    dy @ Wo GEMM, dQKV gathered by the dx GEMM, weight gradients from peer operands) against the
+    same block with plain GEMMs + all_to_all, and against fp32 autograd on the whole sequence."""
+    _need(2)
+    ret = mp.Manager().dict()
+    mp.spawn(_ulysses_grad_worker, args=(2, 29880 + os.getpid() % 50, ret), nprocs=2, join=True)
+    for r in range(2):
+        assert "error" not in ret[r], ret[r].get("error")
+        assert ret[r]["fused_vs_unfused"] < 3e-2 and ret[r]["fused_vs_oracle"] < 4e-2, dict(ret)
 
 
 def test_flag_wait_times_out_cleanly():

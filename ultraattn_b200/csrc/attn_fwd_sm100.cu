@@ -17,7 +17,17 @@
 //   warp  8   : TMA producer (Q once, then the K and V rings)
 //   warp  9   : tcgen05.mma issuer (one elected thread), TMEM allocation
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P (bf16) overwrites the first
-// 64 columns of its S region and is consumed from TMEM as the A operand of the PV product.
+// columns of its S region and is consumed from TMEM as the A operand of the PV product.
+//
+// Two forms of the inner loop (template parameter SPLIT):
+//  * whole tiles: S of a sub-tile covers 128 keys; a warpgroup's softmax and the tensor-core work
+//    on its own sub-tile (P V of this tile, Q K^T of the next) cannot overlap, because P
+//    overwrites S in place; with two sub-tiles the tensor pipe is busy about half the time.
+//  * half tiles (default): every 128-key tile is handled as two 64-key halves with their own S
+//    regions (S0a | S0b | S1a | S1b, 64 columns each). While a warpgroup works on one half, the
+//    tensor core runs P V of the other half and Q K^T of the next tile's half into the region just
+//    vacated, so a warpgroup never waits for its own products. The price is N = 64 for Q K^T (48
+//    instead of 32 clocks per instruction: operand reads from shared memory bound it).
 #include "attn_common.cuh"
 #include "host_common.cuh"
 #include "ptx.cuh"
@@ -75,8 +85,9 @@ struct __align__(1024) FwdSmem {
   uint64_t k_empty[FWD_KV_STAGES];
   uint64_t v_full[FWD_KV_STAGES];
   uint64_t v_empty[FWD_KV_STAGES];
-  uint64_t s_full[2];
-  uint64_t p_full[2];
+  uint64_t s_full[2][2];     // [sub-tile][half]; the whole-tile form uses half 0 only
+  uint64_t p_full[2][2];
+  uint64_t pv_done[2];       // one arrival per P V product of the sub-tile (half-tile form, rescale path)
   uint64_t o_full;
   uint32_t tmem_base;
   int abort_flag;
@@ -105,6 +116,7 @@ __device__ long long g_fwd_prof[64];
 #endif
 constexpr int FWD_PROF_TILE = 8;
 
+template <bool SPLIT>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -126,8 +138,11 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.q_full[i], 1);
-      mbar_init(&s.s_full[i], 1);
-      mbar_init(&s.p_full[i], 128);
+      mbar_init(&s.pv_done[i], 1);
+      for (int h = 0; h < 2; ++h) {
+        mbar_init(&s.s_full[i][h], 1);
+        mbar_init(&s.p_full[i][h], 128);
+      }
     }
     for (int i = 0; i < FWD_KV_STAGES; ++i) {
       mbar_init(&s.k_full[i], 1);
@@ -222,16 +237,17 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         }
       };
       bool ok = true;
+      if constexpr (!SPLIT) {
       do {
         if (!mbar_wait(&s.q_full[0], 0, wc, 200)) { ok = false; break; }
         if (!mbar_wait(&s.k_full[0], 0, wc, 201)) { ok = false; break; }
         tc_fence_after_sync();
         issue_s(0, 0);
-        tc_commit(&s.s_full[0]);
+        tc_commit(&s.s_full[0][0]);
         if (!mbar_wait(&s.q_full[1], 0, wc, 202)) { ok = false; break; }
         tc_fence_after_sync();
         issue_s(1, 0);
-        tc_commit(&s.s_full[1]);
+        tc_commit(&s.s_full[1][0]);
         tc_commit(&s.k_empty[0]);
         for (int j = 0; j < n_total; ++j) {
           const int st = j % FWD_KV_STAGES;
@@ -241,7 +257,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           const bool more = (j + 1 < n_total);
           FWD_PROF(j == FWD_PROF_TILE, 0);
           if (!mbar_wait(&s.v_full[st], ph, wc, 203)) { ok = false; break; }
-          if (!mbar_wait(&s.p_full[0], j & 1, wc, 204)) { ok = false; break; }
+          if (!mbar_wait(&s.p_full[0][0], j & 1, wc, 204)) { ok = false; break; }
           FWD_PROF(j == FWD_PROF_TILE, 1);
           tc_fence_after_sync();
           issue_pv(0, st, j > 0);
@@ -249,23 +265,88 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             if (!mbar_wait(&s.k_full[stn], phn, wc, 205)) { ok = false; break; }
             tc_fence_after_sync();
             issue_s(0, stn);
-            tc_commit(&s.s_full[0]);
+            tc_commit(&s.s_full[0][0]);
           }
           FWD_PROF(j == FWD_PROF_TILE, 2);
-          if (!mbar_wait(&s.p_full[1], j & 1, wc, 206)) { ok = false; break; }
+          if (!mbar_wait(&s.p_full[1][0], j & 1, wc, 206)) { ok = false; break; }
           FWD_PROF(j == FWD_PROF_TILE, 3);
           tc_fence_after_sync();
           issue_pv(1, st, j > 0);
           tc_commit(&s.v_empty[st]);
           if (more) {
             issue_s(1, stn);
-            tc_commit(&s.s_full[1]);
+            tc_commit(&s.s_full[1][0]);
             tc_commit(&s.k_empty[stn]);
           }
           FWD_PROF(j == FWD_PROF_TILE, 4);
         }
         if (ok) tc_commit(&s.o_full);
       } while (false);
+      } else {
+      // ---- half tiles: S regions [w][h] of 64 columns; issue order per tile: (h, w) = a0 a1 b0 b1
+      const uint32_t idesc_s64 = make_idesc_bf16(128, 64, 0, 0);
+      auto issue_s_half = [&](int w, int h, int st) {
+        const uint32_t qa = smem_u32(s.q[w]);
+        const uint32_t ka = smem_u32(s.k[st]) + h * 8192;          // keys h*64 .. h*64+63 (rows of 128 B)
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_ss(tS[w] + h * 64, make_smem_desc_sw128(qa + off, 16, 1024),
+                  make_smem_desc_sw128(ka + off, 16, 1024), idesc_s64, kk > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv_half = [&](int w, int h, int st, bool acc) {
+        const uint32_t va = smem_u32(s.v[st]);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          umma_ts(tO[w], tS[w] + h * 64 + kk * 8, make_smem_desc_sw128(va + (h * 4 + kk) * 2048, 16384, 1024),
+                  idesc_o, (acc || kk > 0) ? 1u : 0u);
+        }
+      };
+      do {
+        if (!mbar_wait(&s.q_full[0], 0, wc, 200)) { ok = false; break; }
+        if (!mbar_wait(&s.k_full[0], 0, wc, 201)) { ok = false; break; }
+        tc_fence_after_sync();
+        issue_s_half(0, 0, 0);
+        tc_commit(&s.s_full[0][0]);
+        if (!mbar_wait(&s.q_full[1], 0, wc, 202)) { ok = false; break; }
+        tc_fence_after_sync();
+        issue_s_half(1, 0, 0);
+        tc_commit(&s.s_full[1][0]);
+        issue_s_half(0, 1, 0);
+        tc_commit(&s.s_full[0][1]);
+        issue_s_half(1, 1, 0);
+        tc_commit(&s.s_full[1][1]);
+        tc_commit(&s.k_empty[0]);
+        for (int j = 0; j < n_total && ok; ++j) {
+          const int st = j % FWD_KV_STAGES;
+          const uint32_t ph = (j / FWD_KV_STAGES) & 1;
+          const int stn = (j + 1) % FWD_KV_STAGES;
+          const uint32_t phn = ((j + 1) / FWD_KV_STAGES) & 1;
+          const bool more = (j + 1 < n_total);
+          if (!mbar_wait(&s.v_full[st], ph, wc, 203)) { ok = false; break; }
+#pragma unroll
+          for (int hw = 0; hw < 4; ++hw) {
+            const int h = hw >> 1, w = hw & 1;
+            if (!mbar_wait(&s.p_full[w][h], j & 1, wc, 204 + hw)) { ok = false; break; }
+            tc_fence_after_sync();
+            issue_pv_half(w, h, st, j > 0 || h > 0);
+            tc_commit(&s.pv_done[w]);
+            if (hw == 3) tc_commit(&s.v_empty[st]);
+            if (more) {
+              if (hw == 0) {
+                if (!mbar_wait(&s.k_full[stn], phn, wc, 208)) { ok = false; break; }
+                tc_fence_after_sync();
+              }
+              issue_s_half(w, h, stn);
+              tc_commit(&s.s_full[w][h]);
+              if (hw == 3) tc_commit(&s.k_empty[stn]);
+            }
+          }
+        }
+        if (ok) tc_commit(&s.o_full);
+      } while (false);
+      }
       (void)ok;
     }
   } else {
@@ -283,42 +364,47 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     float l = 0.f;
     bool ok = true;
     uint32_t j = 0;
+    constexpr int NH = SPLIT ? 2 : 1;          // passes per 128-key tile
+    constexpr int NC = ATTN_TILE / NH;         // S columns per pass
+    uint32_t n_half = 0;                       // passes done so far (= P V products issued for this sub-tile)
     for (int e = row.seg_begin; e < row.seg_end && ok; ++e) {
       const AttnSeg sg = p.segs[e];
       const int nt = seg_tiles(sg, r0, rows_here);
-      for (int t = 0; t < nt; ++t, ++j) {
-        const bool prof = (j == FWD_PROF_TILE || j == FWD_PROF_TILE + 1) && quad == 0 && lane == 0;
+      for (int t = 0; t < nt && ok; ++t, ++j) {
+#pragma unroll
+        for (int h = 0; h < NH; ++h, ++n_half) {
+        const bool prof = (j == FWD_PROF_TILE || j == FWD_PROF_TILE + 1) && quad == 0 && lane == 0 && h == 0;
         const int pslot = 8 + w * 24 + (static_cast<int>(j) - FWD_PROF_TILE) * 8;
         (void)prof; (void)pslot;
+        const uint32_t tSh = tS + h * NC;
         FWD_PROF(prof, pslot + 0);
-        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.s_full[w], j & 1, wc, 300 + w))) { ok = false; break; }
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.s_full[w][h], j & 1, wc, 300 + w))) { ok = false; break; }
         FWD_PROF(prof, pslot + 1);
         tc_fence_after_sync();
-        float sv[128];
+        float sv[NC];
         {
-          uint32_t(&raw)[128] = reinterpret_cast<uint32_t(&)[128]>(sv);
-          tmem_ld_x32(tS + 0, reinterpret_cast<uint32_t(&)[32]>(raw[0]));
-          tmem_ld_x32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(raw[32]));
-          tmem_ld_x32(tS + 64, reinterpret_cast<uint32_t(&)[32]>(raw[64]));
-          tmem_ld_x32(tS + 96, reinterpret_cast<uint32_t(&)[32]>(raw[96]));
+          uint32_t(&raw)[NC] = reinterpret_cast<uint32_t(&)[NC]>(sv);
+#pragma unroll
+          for (int c = 0; c < NC / 32; ++c)
+            tmem_ld_x32(tSh + c * 32, reinterpret_cast<uint32_t(&)[32]>(raw[c * 32]));
           tmem_wait_ld();
         }
         FWD_PROF(prof, pslot + 2);
         // masking: key index c (segment-relative) allowed iff c < len and (c <= r + diag)
-        const int c0 = t * ATTN_TILE;
+        const int c0 = t * ATTN_TILE + h * NC;
         int limit = sg.len - c0;                               // columns < limit are in range
         if (sg.causal) limit = min(limit, r_blk + sg.diag - c0 + 1);
-        if (limit < ATTN_TILE) {
+        if (limit < NC) {
 #pragma unroll
-          for (int i = 0; i < 128; ++i) sv[i] = (i < limit) ? sv[i] : NEG_INF;
+          for (int i = 0; i < NC; ++i) sv[i] = (i < limit) ? sv[i] : NEG_INF;
         }
         // eight independent running maxima, two new values per instruction: one dependent chain of
-        // 127 compares would cost more than the exponentials
+        // compares would cost more than the exponentials
         float mx8[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(sv[i], sv[8 + i]);
 #pragma unroll
-        for (int i = 16; i < 128; i += 16)
+        for (int i = 16; i < NC; i += 16)
 #pragma unroll
           for (int k = 0; k < 8; ++k) mx8[k] = fmax3(mx8[k], sv[i + k], sv[i + 8 + k]);
         float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]));
@@ -328,9 +414,15 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         // lazy rescale: only when the running max grew by more than 2^8 (warp-uniform branch,
         // because the TMEM accesses below are warp-collective)
         const bool need = (m_new - m_use > 8.0f) || (m_use == NEG_INF && m_new > NEG_INF);
-        if (j == 0) {
+        if (n_half == 0) {
           m_use = m_new;
         } else if (__any_sync(0xFFFFFFFFu, need)) {
+          if constexpr (SPLIT) {
+            // O may still be the target of the P V product of the previous pass (issued after the
+            // Q K^T this pass waited for): all n_half products issued so far must have completed
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.pv_done[w], (n_half - 1) & 1, wc, 320 + w))) { ok = false; break; }
+            tc_fence_after_sync();
+          }
           const float alpha = need ? fast_exp2(m_use - m_new) : 1.0f;
           if (need) m_use = m_new;
           l *= alpha;
@@ -353,16 +445,13 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) ls2[k] = f2_pack(0.f, 0.f);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < NC / 32; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             float x0, x1;
             f2_unpack(f2_fma(f2_pack(sv[c * 32 + 2 * i], sv[c * 32 + 2 * i + 1]), sc2, nm2), x0, x1);
-            // optionally one pair in every FWD_POLY_EXP_PERIOD runs on the FMA pipe (packed cubic);
-            // measured neutral at one in eight and slower beyond (1.19 / 1.14 vs 1.21 PFLOP/s at one
-            // in four / two: the loop is bound by instruction issue, not by the special-function
-            // unit), so the default is none
+            // optionally one pair in every FWD_POLY_EXP_PERIOD runs on the FMA pipe (packed cubic)
             const bool poly = FWD_POLY_EXP_PERIOD > 0 && (i % (FWD_POLY_EXP_PERIOD > 0 ? FWD_POLY_EXP_PERIOD : 1)) == (FWD_POLY_EXP_PERIOD > 0 ? FWD_POLY_EXP_PERIOD : 1) - 1;
             float p0, p1;
             if (poly) {
@@ -374,7 +463,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             ls2[i & 3] = f2_add(ls2[i & 3], f2_pack(p0, p1));
             pk[i] = pack_bf16x2(p0, p1);
           }
-          tmem_st_x16(tS + c * 16, pk);
+          tmem_st_x16(tSh + c * 16, pk);
         }
         float ls4[4];
 #pragma unroll
@@ -387,8 +476,9 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         FWD_PROF(prof, pslot + 4);
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&s.p_full[w]);
+        mbar_arrive(&s.p_full[w][h]);
         FWD_PROF(prof, pslot + 5);
+        }
       }
     }
 
@@ -512,7 +602,7 @@ static int encode_src(CUtensorMap* tm, const UaTensorSrc& t) {
   return make_tmap_2byte(tm, t.ptr, 4, dims, str, box);
 }
 
-static int g_fwd_smem_set[64] = {0};
+static int g_fwd_smem_set[2][64] = {{0}};
 
 // rows / segs / tiles are device pointers (prepared once per plan); q/k/v/out tables are host
 // arrays of n_q / n_kv / n_out entries.
@@ -563,13 +653,21 @@ extern "C" int ua_attn_fwd(const UaTensorSrc* q_src, int n_q, const UaTensorSrc*
   const int smem_bytes = sizeof(FwdSmem) + 1024;
   int dev = 0;
   UA_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !g_fwd_smem_set[dev]) {
-    UA_CUDA(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 smem_bytes));
-    g_fwd_smem_set[dev] = 1;
+  // UA_FWD_SPLIT=0 selects the whole-tile form of the inner loop (see the top of this file)
+  const char* env = getenv("UA_FWD_SPLIT");
+  const int split = (env == nullptr || atoi(env) != 0) ? 1 : 0;
+  if (dev < 64 && !g_fwd_smem_set[split][dev]) {
+    if (split)
+      UA_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    else
+      UA_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    g_fwd_smem_set[split][dev] = 1;
   }
   dim3 grid(n_tiles * n_heads, batch, 1);
-  attn_fwd_kernel<<<grid, FWD_THREADS, smem_bytes, stream>>>(p);
+  if (split)
+    attn_fwd_kernel<true><<<grid, FWD_THREADS, smem_bytes, stream>>>(p);
+  else
+    attn_fwd_kernel<false><<<grid, FWD_THREADS, smem_bytes, stream>>>(p);
   UA_CUDA(cudaGetLastError());
   return 0;
 }

@@ -57,6 +57,23 @@ struct GemmParams {
   int* status;
 };
 
+// Tile order of the persistent kernels: tiles are walked in bands of GEMM_GROUP_M tile rows, down
+// the band first, so that the tiles in flight at any moment (one per SM or SM pair) cover a
+// compact block of the output: a few row panels of A and a few column panels of B, which then
+// stay in L2 between the tiles that share them. With the plain "all tile rows of one tile column"
+// order a wave touches 148 different A panels (more than the L2 holds for large M) and every A
+// panel is fetched from HBM again for every tile column.
+constexpr int GEMM_GROUP_M = 8;
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
+  const int per_group = GEMM_GROUP_M * n_tiles;
+  const int group = tile / per_group;
+  const int first_m = group * GEMM_GROUP_M;
+  const int rows = min(GEMM_GROUP_M, m_tiles - first_m);
+  const int in_group = tile - group * per_group;
+  mt = first_m + in_group % rows;
+  nt = in_group / rows;
+}
+
 template <int MH>
 struct __align__(1024) GemmSmem {
   uint8_t a[GemmCfg<MH>::STAGES][GemmCfg<MH>::BM * GEMM_BK * 2];   // 16 KB per 128 rows and stage
@@ -115,8 +132,10 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       tma_prefetch_desc(&p.tmB);
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * TILE_M;
-        const int n0 = (tile / m_tiles) * GEMM_BN;
+        int mt, nt;
+        tile_coords(tile, m_tiles, n_tiles, mt, nt);
+        const int m0 = mt * TILE_M;
+        const int n0 = nt * GEMM_BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int st = it % GEMM_STAGES;
           const uint32_t ph = (it / GEMM_STAGES) & 1;
@@ -193,8 +212,10 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++tcount) {
       const int buf = ACC_BUFS == 2 ? (tcount & 1) : 0;
       const uint32_t aph = ACC_BUFS == 2 ? ((tcount >> 1) & 1) : (tcount & 1);
-      const int m0 = (tile % m_tiles) * TILE_M;
-      const int n0 = (tile / m_tiles) * GEMM_BN;
+      int mt, nt;
+      tile_coords(tile, m_tiles, n_tiles, mt, nt);
+      const int m0 = mt * TILE_M;
+      const int n0 = nt * GEMM_BN;
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.acc_full[buf], aph, wc, 30))) break;
       tc_fence_after_sync();
       const int row = m0 + row_in_tile;
@@ -239,6 +260,205 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// CTA-pair form (cta_group::2): a cluster of two CTAs on two SMs computes one 256 x 256 tile.
+// Each CTA loads its own 128 rows of A and its own half (128 of 256) of the B tile; the tensor
+// cores of both SMs read both halves, so every B byte is written to shared memory once and read
+// by two SMs. That halves the shared-memory traffic per FLOP of the B operand, which is what
+// bounds the single-CTA kernel above (TMA writes + operand reads exceed the 128 B/clk port).
+// The even CTA (leader) issues the MMAs for the pair and owns the "full" and "accumulator empty"
+// barriers; every TMA load of either CTA signals the leader's barrier (plain unicast loads: no
+// cluster-multicast load anywhere), tcgen05.commit arrives on the per-stage "empty" barrier and on
+// the "accumulator full" barrier of both CTAs.
+// ------------------------------------------------------------------------------------------------
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_BM = 256;            // rows per cluster tile (128 per CTA)
+constexpr int PAIR_THREADS = 64 + 32 * 4;
+
+struct __align__(1024) PairSmem {
+  uint8_t a[PAIR_STAGES][128 * GEMM_BK * 2];   // this CTA's 128 rows: 16 KB per stage
+  uint8_t b[PAIR_STAGES][128 * GEMM_BK * 2];   // this CTA's half of the B tile: 16 KB per stage
+  uint64_t full[PAIR_STAGES];                  // used in the leader only
+  uint64_t empty[PAIR_STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];                       // used in the leader only (both CTAs' epilogues arrive)
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  PairSmem& s = *reinterpret_cast<PairSmem*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();        // 0 = leader, 1 = peer
+  const bool leader = cta == 0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < PAIR_STAGES; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.acc_full[i], 1);
+      mbar_init(&s.acc_empty[i], 2 * 4);         // one arrival per epilogue warp of both CTAs
+    }
+    s.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&s.tmem_base, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                            // the peer's barriers exist before anyone signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = s.tmem_base;
+  WaitCtx wc{&s.abort_flag, p.status, 4000000000ull};
+
+  const int m_tiles = (p.M + PAIR_BM - 1) / PAIR_BM;
+  const int n_tiles = (p.N + GEMM_BN - 1) / GEMM_BN;
+  const int total = m_tiles * n_tiles;
+  const int k_blocks = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int cluster_id = blockIdx.x >> 1;
+  const int n_clusters = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) -------------------------------
+    if (lane == 0) {
+      for (int i = 0; i < p.n_src; ++i) tma_prefetch_desc(&p.tmA[i]);
+      tma_prefetch_desc(&p.tmB);
+      uint32_t it = 0;
+      for (int tile = cluster_id; tile < total; tile += n_clusters) {
+        int mt, nt;
+        tile_coords(tile, m_tiles, n_tiles, mt, nt);
+        const int m0 = mt * PAIR_BM + static_cast<int>(cta) * 128;
+        const int n0 = nt * GEMM_BN + static_cast<int>(cta) * 128;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int st = it % PAIR_STAGES;
+          const uint32_t ph = (it / PAIR_STAGES) & 1;
+          if (!mbar_wait(&s.empty[st], ph ^ 1, wc, 40)) { ok = false; break; }
+          // the leader announces the bytes of both CTAs; the peer's loads complete on the same barrier
+          if (leader) mbar_arrive_expect_tx(&s.full[st], 2 * (128 + 128) * GEMM_BK * 2);
+          const uint32_t bar = mapa_shared(smem_u32(&s.full[st]), 0);
+          const int k0 = kb * GEMM_BK;
+          const int src = k0 / p.k_per_src;
+          const int ksrc = k0 - src * p.k_per_src;
+          if (!p.a_mn_major) {
+            tma_load_2d_pair(s.a[st], &p.tmA[src], bar, ksrc, p.a_row_off + m0);
+          } else {
+            for (int pm = 0; pm < 2; ++pm)
+              tma_load_2d_pair(s.a[st] + pm * 8192, &p.tmA[src], bar, m0 + pm * 64, p.a_row_off + ksrc);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d_pair(s.b[st], &p.tmB, bar, k0, n0);
+          } else {
+            for (int pn = 0; pn < 2; ++pn)
+              tma_load_2d_pair(s.b[st] + pn * 8192, &p.tmB, bar, n0 + pn * 64, k0);
+          }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader only) -------------------------------
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc_bf16(256, GEMM_BN, p.a_mn_major, p.b_mn_major);
+      const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u;
+      const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u;
+      const uint32_t a_kstep = p.a_mn_major ? 2048u : 32u;
+      const uint32_t b_kstep = p.b_mn_major ? 2048u : 32u;
+      uint32_t it = 0;
+      uint32_t tcount = 0;
+      for (int tile = cluster_id; tile < total; tile += n_clusters, ++tcount) {
+        const int buf = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbar_wait(&s.acc_empty[buf], aph ^ 1, wc, 50)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * GEMM_BN;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int st = it % PAIR_STAGES;
+          const uint32_t ph = (it / PAIR_STAGES) & 1;
+          if (!mbar_wait(&s.full[st], ph, wc, 51)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(s.a[st]);
+          const uint32_t b_addr = smem_u32(s.b[st]);
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            const uint64_t ad = make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
+            const uint64_t bd = make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
+            umma_ss_pair(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          // the stage is free again in both CTAs once these MMAs have read it
+          tc_commit_pair(&s.empty[st], 3);
+        }
+        if (!ok) break;
+        tc_commit_pair(&s.acc_full[buf], 3);
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (4 warps per CTA) -----------------------------
+    const int quad = warp & 3;
+    const int row_in_tile = static_cast<int>(cta) * 128 + quad * 32 + lane;
+    uint32_t tcount = 0;
+    for (int tile = cluster_id; tile < total; tile += n_clusters, ++tcount) {
+      const int buf = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      int mt, nt;
+      tile_coords(tile, m_tiles, n_tiles, mt, nt);
+      const int m0 = mt * PAIR_BM;
+      const int n0 = nt * GEMM_BN;
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.acc_full[buf], aph, wc, 60))) break;
+      tc_fence_after_sync();
+      const int row = m0 + row_in_tile;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * GEMM_BN;
+#pragma unroll 1
+      for (int c = 0; c < GEMM_BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(taddr + c * 32, v);
+        tmem_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          const int g = col0 / p.cols_per_dst;
+          const int cin = col0 - g * p.cols_per_dst;
+          __nv_bfloat16* dst = p.c_dst[g] + static_cast<size_t>(p.dst_row_off + row) * p.ldc + cin;
+          if (col0 + 32 <= p.N) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+              d4[q] = o;
+            }
+          } else {
+            for (int q = 0; q < 32 && col0 + q < p.N; ++q)
+              dst[q] = __float2bfloat16(__uint_as_float(v[q]));
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&s.acc_empty[buf]), 0));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();      // nobody leaves while the other CTA may still read its shared memory or signal its barriers
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
 }  // namespace ua
 
 using namespace ua;
@@ -256,6 +476,27 @@ static int launch_gemm(const GemmParams& p, int grid, cudaStream_t stream) {
     g_gemm_smem_set[MH - 1][dev] = 1;
   }
   gemm_bf16_kernel<MH><<<grid, GemmCfg<MH>::THREADS, smem_bytes, stream>>>(p);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}
+
+
+static int g_pair_smem_set[64] = {0};
+
+static int launch_gemm_pair(const GemmParams& p, int num_sms, cudaStream_t stream) {
+  const int smem_bytes = sizeof(PairSmem) + 1024;
+  int dev = 0;
+  UA_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !g_pair_smem_set[dev]) {
+    UA_CUDA(cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    g_pair_smem_set[dev] = 1;
+  }
+  const int m_tiles = (p.M + PAIR_BM - 1) / PAIR_BM;
+  const int n_tiles = (p.N + GEMM_BN - 1) / GEMM_BN;
+  int clusters = m_tiles * n_tiles;
+  if (clusters > num_sms / 2) clusters = num_sms / 2;
+  if (clusters < 1) return 0;
+  gemm_bf16_pair_kernel<<<2 * clusters, PAIR_THREADS, smem_bytes, stream>>>(p);
   UA_CUDA(cudaGetLastError());
   return 0;
 }
@@ -285,6 +526,11 @@ extern "C" int ua_gemm_bf16(const void* const* a_ptrs, int n_src, long a_rows_to
   // tile height: 256 rows when that still leaves at least four waves of tiles (UA_GEMM_MH forces)
   int mh = (static_cast<long>((M + 255) / 256) * ((N + GEMM_BN - 1) / GEMM_BN) >= 4L * num_sms) ? 2 : 1;
   if (const char* e = getenv("UA_GEMM_MH")) mh = atoi(e) == 2 ? 2 : 1;
+  // CTA pairs (256 x 256 tile over two SMs) when there are at least two waves of such tiles for
+  // the 74 pairs; UA_GEMM_PAIR=0 / 1 forces the choice
+  bool pair = static_cast<long>((M + 255) / 256) * ((N + GEMM_BN - 1) / GEMM_BN) >= static_cast<long>(num_sms);
+  if (const char* e = getenv("UA_GEMM_PAIR")) pair = atoi(e) != 0;
+  if (pair) mh = 1;        // per-CTA boxes of the pair kernel are those of the 128-row kernel
   for (int i = 0; i < n_src; ++i) {
     if (!a_mn_major) {
       // [rows, k_per_src] K contiguous
@@ -303,7 +549,7 @@ extern "C" int ua_gemm_bf16(const void* const* a_ptrs, int n_src, long a_rows_to
   if (!b_mn_major) {
     uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
     uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
-    uint32_t box[2] = {GEMM_BK, GEMM_BN};
+    uint32_t box[2] = {GEMM_BK, static_cast<uint32_t>(pair ? 128 : GEMM_BN)};   // a pair loads half a tile per CTA
     if (make_tmap_2byte(&p.tmB, b, 2, dims, str, box)) return -1;
   } else {
     uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
@@ -311,6 +557,7 @@ extern "C" int ua_gemm_bf16(const void* const* a_ptrs, int n_src, long a_rows_to
     uint32_t box[2] = {64, GEMM_BK};
     if (make_tmap_2byte(&p.tmB, b, 2, dims, str, box)) return -1;
   }
+  if (pair) return launch_gemm_pair(p, num_sms, stream);
   const int m_tiles = (M + 128 * mh - 1) / (128 * mh);
   const int n_tiles = (N + GEMM_BN - 1) / GEMM_BN;
   int grid = m_tiles * n_tiles;

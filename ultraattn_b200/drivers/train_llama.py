@@ -24,6 +24,44 @@ from ..ops import attention as A
 from ..runtime import ContextParallelAttention
 
 
+def _breakdown(model, step, dev) -> dict:
+    """One instrumented step: device time inside the attention calls (context-parallel runtime or
+    head-parallel block, forward and backward), inside the GEMM kernel, and the rest."""
+    from ..ops import gemm as G
+    spans = {"attention": [], "gemm": []}
+
+    def timed(kind, fn):
+        def wrapper(*args, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*args, **kw)
+            e1.record()
+            spans[kind].append((e0, e1))
+            return out
+        return wrapper
+
+    saved = (model._attn_fwd, model._attn_bwd, G.gemm, G.gemm_scatter, G.gemm_gather)
+    model._attn_fwd, model._attn_bwd = timed("attention", saved[0]), timed("attention", saved[1])
+    G.gemm, G.gemm_scatter, G.gemm_gather = (timed("gemm", f) for f in saved[2:])
+    if model.ulysses is not None:       # head-parallel: the attention kernels are called inside the block
+        from ..ops import attention as Aops
+        saved_a = (Aops.attn_fwd, Aops.attn_bwd)
+        Aops.attn_fwd, Aops.attn_bwd = timed("attention", saved_a[0]), timed("attention", saved_a[1])
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    step()
+    t1.record()
+    torch.cuda.synchronize(dev)
+    model._attn_fwd, model._attn_bwd, G.gemm, G.gemm_scatter, G.gemm_gather = saved
+    if model.ulysses is not None:
+        Aops.attn_fwd, Aops.attn_bwd = saved_a
+    total = t0.elapsed_time(t1)
+    out = {k: sum(a.elapsed_time(b) for a, b in v) for k, v in spans.items()}
+    out["other"] = total - out["attention"] - out["gemm"]
+    out["step"] = total
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--seq", type=int, default=524288)
@@ -36,6 +74,12 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--path", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--seq-algo", default="cp", choices=["cp", "ulysses"],
+                    help="cp: context-parallel attention; ulysses: head-parallel attention with the all-to-alls "
+                         "fused into the projection GEMMs")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="after the timed steps, run one more step with CUDA events around the attention calls "
+                         "and the GEMMs and report the attention / GEMM / other split")
     ap.add_argument("--offload-checkpoints", action="store_true",
                     help="keep the per-layer activation checkpoints in pinned host memory")
     ap.add_argument("--estimate-memory", type=int, default=0, metavar="CP",
@@ -60,7 +104,10 @@ def main() -> None:
     cfg = LlamaConfig(n_layers=a.layers, hidden=a.hidden, n_heads=a.heads, head_dim=128, ffn=a.ffn, vocab=a.vocab)
     pattern = P.global_local(a.blocks, 1, 2)
     runtime = None
-    if world > 1:
+    if world > 1 and a.seq_algo == "ulysses":
+        s_loc = a.seq // world
+        pos = torch.arange(rank * s_loc, (rank + 1) * s_loc)
+    elif world > 1:
         runtime = ContextParallelAttention(pattern, a.seq, a.heads, 128, group=group, device=dev, path=a.path)
         cmap = runtime.cmap
         par_d = runtime.table.shape[0]
@@ -70,7 +117,7 @@ def main() -> None:
     else:
         pos = torch.arange(a.seq)
     model = LlamaModel(cfg, device=dev, pattern=pattern, runtime=runtime, group=group, seed=0,
-                       offload_checkpoints=a.offload_checkpoints)
+                       offload_checkpoints=a.offload_checkpoints, seq_algo=a.seq_algo, seq_len=a.seq)
     g = torch.Generator().manual_seed(3)
     ids_all = torch.randint(0, a.vocab, (a.seq + 1,), generator=g)
     ids = ids_all[pos].to(dev)
@@ -98,12 +145,20 @@ def main() -> None:
     ms = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    split = None
+    if a.breakdown:
+        split = _breakdown(model, step, dev)
+        if world > 1:
+            t = torch.tensor([split[k] for k in sorted(split)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            split = dict(zip(sorted(split), [round(x, 2) for x in t.tolist()]))
     if rank == 0:
         n_params = model.flat.numel()
         print(json.dumps({"metric": "e2e_tokens_per_s", "value": a.seq / (ms.item() / 1e3), "ms_per_step": ms.item(),
                           "n_gpus": world, "seq_len": a.seq, "layers": a.layers, "params": n_params, "loss": loss,
-                          "path": a.path if world > 1 else "local", "dtype": "bf16",
-                          "max_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30}), flush=True)
+                          "path": (a.path if a.seq_algo == "cp" else "ulysses-fused") if world > 1 else "local", "dtype": "bf16",
+                          "max_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
+                          **({"split_ms_max_over_ranks": split} if split else {})}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

@@ -131,6 +131,18 @@ class _Layer(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, model, li):
+        ctx.model, ctx.li = model, li
+        if model.ulysses is not None:
+            # head-parallel attention: both all-to-alls live inside the projection GEMMs
+            c, p = model.cfg, model.p
+            with torch.no_grad():
+                h = _RMSNorm.apply(x, p[f"l{li}.norm1"], c.eps)
+                cos, sin = model._tables(model.ulysses.S)
+                a, o, lse = model.ulysses.forward(h, p[f"l{li}.wqkv"], p[f"l{li}.wo"], cos, sin, return_state=True)
+                y = model._seg_ffn(x + a, li)
+            ctx.offloaded = None
+            ctx.save_for_backward(x, o, lse)
+            return y
         with torch.no_grad():
             q, k, v = model._seg_qkv(x, li)
             o, lse = model._attn_fwd(q, k, v)
@@ -141,7 +153,6 @@ class _Layer(torch.autograd.Function):
         else:
             ctx.offloaded = None
             ctx.save_for_backward(x, o, lse)
-        ctx.model, ctx.li = model, li
         return y
 
     @staticmethod
@@ -152,6 +163,25 @@ class _Layer(torch.autograd.Function):
             x, o = (model._reload(h) for h in ctx.offloaded)
         else:
             x, o, lse = ctx.saved_tensors
+        if model.ulysses is not None:
+            c, p, ul = model.cfg, model.p, model.ulysses
+            wqkv, wo = p[f"l{li}.wqkv"], p[f"l{li}.wo"]
+            cos, sin = model._tables(ul.S)
+            with torch.enable_grad():
+                x1 = x.detach().requires_grad_()
+                h = _RMSNorm.apply(x1, p[f"l{li}.norm1"], c.eps)            # recomputed
+                with torch.no_grad():
+                    a = ul.recompute_out(o, wo)                              # projection only, attention is NOT recomputed
+                a2 = a.requires_grad_()
+                x2 = x.detach().requires_grad_()
+                y = model._seg_ffn(x2 + a2, li)
+                torch.autograd.backward([y], [dy])
+                with torch.no_grad():
+                    dh, dwqkv, dwo = ul.backward(a2.grad, h.detach(), wqkv, wo, o, lse, cos, sin, attn_in_place=True)
+                    wqkv.grad.add_(dwqkv)
+                    wo.grad.add_(dwo)
+                torch.autograd.backward([h], [dh])
+            return x1.grad + x2.grad, None, None
         with torch.enable_grad():
             x1 = x.detach().requires_grad_()
             q, k, v = model._seg_qkv(x1, li)                    # recomputed (cheap)
@@ -197,8 +227,17 @@ class LlamaModel:
     def __init__(self, cfg: LlamaConfig, device=None, pattern: Optional[BSA_Repr] = None,
                  runtime=None, group=None, dtype=None, seed: int = 0, lr: float = 1e-4,
                  betas=(0.9, 0.95), weight_decay: float = 0.0, max_pos: int = 1 << 20,
-                 offload_checkpoints: bool = False, nvls_optimizer: Optional[bool] = None):
+                 offload_checkpoints: bool = False, nvls_optimizer: Optional[bool] = None,
+                 seq_algo: str = "cp", seq_len: Optional[int] = None):
+        """``seq_algo``: how the sequence is parallelised over ``group``. ``"cp"``: context-parallel
+        attention through ``runtime`` (tokens stay sharded inside the attention). ``"ulysses"``:
+        head-parallel attention (``parallel/ulysses_fused.py``: the four all-to-alls fused into the
+        projection GEMMs); needs ``seq_len`` (whole sequence), every rank then passes the
+        contiguous token range ``[rank * S/world, (rank + 1) * S/world)``, and the rows of every
+        ``wqkv`` are stored in destination-rank order (``permute_qkv_weight``)."""
         self.cfg = cfg
+        self.seq_algo = seq_algo
+        self.ulysses = None
         self.offload_checkpoints = offload_checkpoints
         self._host_ckpt: dict = {}          # (layer, slot) -> pinned host buffer, reused every step
         self._copy_stream = None
@@ -270,6 +309,13 @@ class LlamaModel:
         self.v = torch.zeros_like(self.master)
         self.cos, self.sin = None, None
         self.max_pos = max_pos
+        if seq_algo == "ulysses" and self.world > 1:
+            from ..parallel.ulysses_fused import FusedUlyssesAttention
+            assert seq_len is not None, "seq_algo='ulysses' needs seq_len"
+            self.ulysses = FusedUlyssesAttention(group, self.device, seq_len, cfg.hidden, cfg.n_heads, cfg.kv_heads,
+                                                 cfg.head_dim, pattern=pattern)
+        elif seq_algo not in ("cp", "ulysses"):
+            raise ValueError(f"unknown seq_algo {seq_algo!r}")
 
     # ------------------------------- segments of a layer ---------------------------------------
     def _tables(self, n_pos: int):
@@ -294,7 +340,11 @@ class LlamaModel:
     def _seg_out(self, x, o, li):
         c, p = self.cfg, self.p
         a = _Linear.apply(o.reshape(x.shape[0], c.n_heads * c.head_dim), p[f"l{li}.wo"])
-        x = x + a
+        return self._seg_ffn(x + a, li)
+
+    def _seg_ffn(self, x, li):
+        """Second half of a layer: x + W_down(SwiGLU(W_gate,up(RMSNorm(x))))."""
+        c, p = self.cfg, self.p
         h = _RMSNorm.apply(x, p[f"l{li}.norm2"], c.eps)
         gu = _Linear.apply(h, p[f"l{li}.wgu"])
         return x + _Linear.apply(_Swiglu.apply(gu), p[f"l{li}.wdown"])

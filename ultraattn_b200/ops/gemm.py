@@ -73,16 +73,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) ->
 
 
 def gemm_scatter(a: torch.Tensor, b: torch.Tensor, dst_ptrs: Sequence[int], ldc: int,
-                 dst_row_off: int) -> None:
-    """``A[M,K] @ B[N,K].T`` with the all-to-all fused into the epilogue: output columns are split
-    into ``len(dst_ptrs)`` equal groups; group g is written to the buffer at ``dst_ptrs[g]``
-    (typically peer GPU g's receive buffer) at rows ``dst_row_off .. dst_row_off + M``."""
+                 dst_row_off: int, b_is_kn: bool = False) -> None:
+    """``A[M,K] @ B`` (``b`` stored ``[N,K]``, or ``[K,N]`` with ``b_is_kn``) with the all-to-all
+    fused into the epilogue: output columns are split into ``len(dst_ptrs)`` equal groups; group g
+    is written to the buffer at ``dst_ptrs[g]`` (typically peer GPU g's receive buffer) at rows
+    ``dst_row_off .. dst_row_off + M``."""
     M, K = a.shape
-    N = b.shape[0]
+    N = b.shape[1] if b_is_kn else b.shape[0]
+    assert (b.shape[0] if b_is_kn else b.shape[1]) == K
     lib = _lib.load()
     a_ptrs = (ctypes.c_void_p * 1)(a.data_ptr())
     c_ptrs = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
-    rc = lib.ua_gemm_bf16(a_ptrs, 1, M, a.stride(0), 0, 0, b.data_ptr(), b.stride(0), 0, c_ptrs,
+    rc = lib.ua_gemm_bf16(a_ptrs, 1, M, a.stride(0), 0, 0, b.data_ptr(), b.stride(0), int(b_is_kn), c_ptrs,
                           len(dst_ptrs), ldc, dst_row_off, M, N, K,
                           status_buffer(a.device).data_ptr(), _sms(a.device),
                           torch.cuda.current_stream(a.device).cuda_stream)
@@ -90,18 +92,18 @@ def gemm_scatter(a: torch.Tensor, b: torch.Tensor, dst_ptrs: Sequence[int], ldc:
 
 
 def gemm_gather(src_ptrs: Sequence[int], src_rows_total: int, lda: int, a_row_off: int, M: int,
-                k_per_src: int, b: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """``A @ B[N,K].T`` with the all-to-all fused into the operand load: the K dimension of A is
-    the concatenation of ``len(src_ptrs)`` buffers (typically one per peer GPU, each
-    ``[src_rows_total, k_per_src]`` bf16 with row stride ``lda``); rows ``a_row_off .. +M`` of
-    every buffer are read directly by TMA."""
-    N, K = b.shape
+                k_per_src: int, b: torch.Tensor, out: torch.Tensor, b_is_kn: bool = False) -> torch.Tensor:
+    """``A @ B`` (``b`` stored ``[N,K]``, or ``[K,N]`` with ``b_is_kn``) with the all-to-all fused
+    into the operand load: the K dimension of A is the concatenation of ``len(src_ptrs)`` buffers
+    (typically one per peer GPU, each ``[src_rows_total, k_per_src]`` bf16 with row stride
+    ``lda``); rows ``a_row_off .. +M`` of every buffer are read directly by TMA."""
+    K, N = b.shape if b_is_kn else (b.shape[1], b.shape[0])
     assert K == k_per_src * len(src_ptrs)
     lib = _lib.load()
     a_ptrs = (ctypes.c_void_p * len(src_ptrs))(*src_ptrs)
     c_ptrs = (ctypes.c_void_p * 1)(out.data_ptr())
     rc = lib.ua_gemm_bf16(a_ptrs, len(src_ptrs), src_rows_total, lda, a_row_off, 0, b.data_ptr(),
-                          b.stride(0), 0, c_ptrs, 1, out.stride(0), 0, M, N, K,
+                          b.stride(0), int(b_is_kn), c_ptrs, 1, out.stride(0), 0, M, N, K,
                           status_buffer(out.device).data_ptr(), _sms(out.device),
                           torch.cuda.current_stream(out.device).cuda_stream)
     _lib.check(rc, "ua_gemm_bf16(gather)")
