@@ -7,6 +7,7 @@ head dim 128, batch 1, bf16, Q/K/V/dO ~ N(0,1) seed 1, context-parallel over N G
 
     python bench.py --gpus N --steps K --warmup W            (N > 1: launched under torchrun)
     python bench.py --impl reference ...                      (the reference arm)
+    python bench.py --gpus N --e2e-model [--seq-algo ulysses]  (Llama-2-7B training step, tokens/s)
 
 Prints one JSON line on rank 0. ``value`` = milliseconds per forward+backward, device-timed with
 CUDA events around exactly K steps, max over ranks. ``e2e`` = the same step through the public
@@ -104,6 +105,11 @@ def main() -> None:
                     help="multi-GPU execution path: fused peer-memory kernels or the NCCL baseline")
     ap.add_argument("--seq", type=int, default=S_TOTAL, help="(debug) total sequence length")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-model", action="store_true",
+                    help="run the other half of the headline metric instead: one Llama-2-7B training step "
+                         "(32 layers, global+local mask, S = --seq) over the N GPUs, tokens per second")
+    ap.add_argument("--seq-algo", default="cp", choices=["cp", "ulysses"], help="(--e2e-model) sequence parallelism")
+    ap.add_argument("--layers", type=int, default=32, help="(--e2e-model) decoder layers")
     ap.add_argument("--check", action="store_true",
                     help="before timing, compare sampled rows of O / lse / dQ / dK / dV at the benchmark shape with an fp32 oracle")
     ap.add_argument("--check-rows", type=int, default=64, help="query rows sampled by --check (whole job)")
@@ -112,6 +118,14 @@ def main() -> None:
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
+        return
+    if args.e2e_model:
+        # config 5 of the baseline: end-to-end training step, tokens per second over the whole job
+        from ultraattn_b200.drivers import train_llama
+        sys.argv = [sys.argv[0], "--seq", str(args.seq), "--steps", str(max(1, args.steps)),
+                    "--warmup", str(max(1, min(args.warmup, 2))), "--path", args.path, "--seq-algo", args.seq_algo,
+                    "--layers", str(args.layers), "--breakdown"]
+        train_llama.main()
         return
 
     import torch

@@ -1,6 +1,8 @@
 """Failure detection, exercised on the host only: a dropped message and a rank that raises make
 the other rank's step fail with a clear error within its deadline instead of hanging."""
 import os
+
+import pytest
 import sys
 
 import torch
@@ -113,3 +115,21 @@ def test_survivors_replan_after_ranks_leave():
     for r in range(4):
         assert isinstance(ret[r], float), ret[r]
         assert ret[r] < 2e-4, (r, ret[r])
+
+
+def test_heartbeat_survivors_adopt_one_member_list():
+    """A rank whose announcement lands between two survivors' scans must not split them: the first
+    survivor to finish publishes its member list, the others adopt it, and the late rank learns
+    that it is out."""
+    from ultraattn_b200.runtime.heartbeat import ExcludedFromGroup, StepHeartbeat
+    store = dist.HashStore()
+    hbs = [StepHeartbeat(store, rank=r, world=4, prefix="t") for r in range(4)]
+    for hb in hbs[:3]:
+        hb.beat(7)
+    assert hbs[0].missing(7, timeout_s=0.2) == [3] and hbs[0].alive == [0, 1, 2]     # rank 3 is late
+    hbs[3].beat(7)                                  # ... and announces just now
+    # rank 1's own scan sees all four, but it adopts the list rank 0 published
+    assert hbs[1].missing(7, timeout_s=0.2) == [3] and hbs[1].alive == [0, 1, 2]
+    assert hbs[2].missing(7, timeout_s=0.2) == [3] and hbs[2].alive == [0, 1, 2]
+    with pytest.raises(ExcludedFromGroup):
+        hbs[3].missing(7, timeout_s=0.2)

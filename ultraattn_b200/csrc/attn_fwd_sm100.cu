@@ -23,7 +23,7 @@
 //  * whole tiles: S of a sub-tile covers 128 keys; a warpgroup's softmax and the tensor-core work
 //    on its own sub-tile (P V of this tile, Q K^T of the next) cannot overlap, because P
 //    overwrites S in place; with two sub-tiles the tensor pipe is busy about half the time.
-//  * half tiles (default): every 128-key tile is handled as two 64-key halves with their own S
+//  * half tiles (UA_FWD_SPLIT=1): every 128-key tile is handled as two 64-key halves with their own S
 //    regions (S0a | S0b | S1a | S1b, 64 columns each). While a warpgroup works on one half, the
 //    tensor core runs P V of the other half and Q K^T of the next tile's half into the region just
 //    vacated, so a warpgroup never waits for its own products. The price is N = 64 for Q K^T (48
@@ -329,6 +329,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           for (int hw = 0; hw < 4; ++hw) {
             const int h = hw >> 1, w = hw & 1;
             if (!mbar_wait(&s.p_full[w][h], j & 1, wc, 204 + hw)) { ok = false; break; }
+            FWD_PROF(j == FWD_PROF_TILE, hw * 2);
             tc_fence_after_sync();
             issue_pv_half(w, h, st, j > 0 || h > 0);
             tc_commit(&s.pv_done[w]);
@@ -342,6 +343,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
               tc_commit(&s.s_full[w][h]);
               if (hw == 3) tc_commit(&s.k_empty[stn]);
             }
+            FWD_PROF(j == FWD_PROF_TILE, hw * 2 + 1);
           }
         }
         if (ok) tc_commit(&s.o_full);
@@ -373,8 +375,8 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       for (int t = 0; t < nt && ok; ++t, ++j) {
 #pragma unroll
         for (int h = 0; h < NH; ++h, ++n_half) {
-        const bool prof = (j == FWD_PROF_TILE || j == FWD_PROF_TILE + 1) && quad == 0 && lane == 0 && h == 0;
-        const int pslot = 8 + w * 24 + (static_cast<int>(j) - FWD_PROF_TILE) * 8;
+        const bool prof = (j == FWD_PROF_TILE || j == FWD_PROF_TILE + 1) && quad == 0 && lane == 0;
+        const int pslot = 8 + w * 24 + (static_cast<int>(j) - FWD_PROF_TILE) * (SPLIT ? 12 : 8) + h * 6;
         (void)prof; (void)pslot;
         const uint32_t tSh = tS + h * NC;
         FWD_PROF(prof, pslot + 0);
@@ -653,9 +655,9 @@ extern "C" int ua_attn_fwd(const UaTensorSrc* q_src, int n_q, const UaTensorSrc*
   const int smem_bytes = sizeof(FwdSmem) + 1024;
   int dev = 0;
   UA_CUDA(cudaGetDevice(&dev));
-  // UA_FWD_SPLIT=0 selects the whole-tile form of the inner loop (see the top of this file)
+  // UA_FWD_SPLIT=1 selects the half-tile form of the inner loop (see the top of this file)
   const char* env = getenv("UA_FWD_SPLIT");
-  const int split = (env == nullptr || atoi(env) != 0) ? 1 : 0;
+  const int split = (env != nullptr && atoi(env) != 0) ? 1 : 0;
   if (dev < 64 && !g_fwd_smem_set[split][dev]) {
     if (split)
       UA_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));

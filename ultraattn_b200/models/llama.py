@@ -447,7 +447,8 @@ class _ChunkLoss(torch.autograd.Function):
 
 
 def estimate_memory(cfg: LlamaConfig, seq_len: int, cp: int = 1, offload_checkpoints: bool = False,
-                    loss_chunk_tokens: int = 4096, staged_peer_ranks: Optional[int] = None) -> dict:
+                    loss_chunk_tokens: int = 4096, staged_row_tokens: Optional[int] = None,
+                    staged_col_tokens: Optional[int] = None) -> dict:
     """Per-GPU memory plan of a training step (GiB), by what holds it: replicated bf16 parameters
     and gradients, the 1/cp shard of the fp32 optimizer state (master, m, v), the activation
     checkpoints (layer input and attention output of every layer, plus lse; in pinned host memory
@@ -464,13 +465,17 @@ def estimate_memory(cfg: LlamaConfig, seq_len: int, cp: int = 1, offload_checkpo
     kv_bytes = s_loc * Hk * D * 2
     lse_bytes = cfg.n_heads * s_loc * 4
     ckpt_per_layer = s_loc * H * 2 + q_bytes + lse_bytes
-    peers = (cp - 1) if staged_peer_ranks is None else staged_peer_ranks
+    # staging mirrors hold only the foreign blocks a rank's tiles read (``FusedContextParallel.
+    # mirror_bytes`` is the exact figure of a plan); default: as many foreign tokens as own ones
+    row_tok = s_loc if staged_row_tokens is None else staged_row_tokens
+    col_tok = s_loc if staged_col_tokens is None else staged_col_tokens
     runtime = 0.0
     if cp > 1:
         runtime = (2 * q_bytes + 2 * kv_bytes + 2 * lse_bytes           # symmetric q, do, k, v, lse, dvec
                    + q_bytes + lse_bytes                                # mailboxes (one slot per foreign row block: bounded by a shard)
                    + 2 * q_bytes + 2 * 2 * kv_bytes                     # fp32 dq / dk / dv accumulators
-                   + peers * (2 * q_bytes + 2 * lse_bytes + 2 * q_bytes + 2 * kv_bytes))  # mirrors: q, do, lse, dvec, fp32 dq, k, v
+                   + row_tok * cfg.n_heads * (D * (2 + 2 + 4) + 8)      # mirrors of foreign rows: q, do, fp32 dq, lse, dvec
+                   + col_tok * Hk * D * 4)                              # mirrors of foreign columns: k, v
     layer_work = (s_loc * ((cfg.n_heads + 2 * Hk) * D + 2 * Fd + Fd + 3 * H) * 2) * 2     # activations + their gradients of one layer
     out = {
         "parameters": n_params * 2 / GiB,

@@ -327,23 +327,44 @@ class FusedContextParallel:
         dev = self.device
         peers_rows = sorted({int(self.cmap[r]) for r in self.remote_rows})
         peers_cols = sorted({int(self.cmap[c]) for c in self.remote_cols})
+        # Mirrors hold only the blocks this rank's tiles need from a peer (not the peer's whole
+        # shard): mir_rows[p] / mir_cols[p] list those blocks in mirror order. Key/value blocks
+        # that arrive through the broadcast buffer need no mirror.
+        self.mir_rows = {p: [r for r in self.remote_rows if int(self.cmap[r]) == p] for p in peers_rows}
+        self.mir_cols = {p: [c for c in self.remote_cols if int(self.cmap[c]) == p and c not in self.bc_slot]
+                         for p in peers_cols}
+        self.mslot = {}                  # ("r" | "c", block) -> index of the block inside its mirror
+        for p, blocks in self.mir_rows.items():
+            self.mslot.update({("r", r): i for i, r in enumerate(blocks)})
+        for p, blocks in self.mir_cols.items():
+            self.mslot.update({("c", c): i for i, c in enumerate(blocks)})
         self.mir = {}
+        blk = self.blk
         for p in peers_rows:
-            self.mir[("q", p)] = torch.zeros(B, S, H, D, dtype=dt, device=dev)
-            self.mir[("do", p)] = torch.zeros(B, S, H, D, dtype=dt, device=dev)
-            self.mir[("lse", p)] = torch.zeros(B, H, S, dtype=torch.float32, device=dev)
-            self.mir[("dvec", p)] = torch.zeros(B, H, S, dtype=torch.float32, device=dev)
+            n = len(self.mir_rows[p]) * blk
+            self.mir[("q", p)] = torch.zeros(B, n, H, D, dtype=dt, device=dev)
+            self.mir[("do", p)] = torch.zeros(B, n, H, D, dtype=dt, device=dev)
+            self.mir[("lse", p)] = torch.zeros(B, H, n, dtype=torch.float32, device=dev)
+            self.mir[("dvec", p)] = torch.zeros(B, H, n, dtype=torch.float32, device=dev)
             # dQ of foreign rows is accumulated here (every key tile adds into it) and pushed to
             # the owner once per step; adding straight into the owner's memory would send every
             # partial sum over NVLink
-            self.mir[("dq", p)] = torch.zeros(B, S, H, D, dtype=torch.float32, device=dev)
+            self.mir[("dq", p)] = torch.zeros(B, n, H, D, dtype=torch.float32, device=dev)
         for p in peers_cols:
-            self.mir[("k", p)] = torch.zeros(B, S, Hk, D, dtype=dt, device=dev)
-            self.mir[("v", p)] = torch.zeros(B, S, Hk, D, dtype=dt, device=dev)
+            n = max(1, len(self.mir_cols[p])) * blk      # (a peer whose blocks all come by broadcast keeps a stub)
+            self.mir[("k", p)] = torch.zeros(B, n, Hk, D, dtype=dt, device=dev)
+            self.mir[("v", p)] = torch.zeros(B, n, Hk, D, dtype=dt, device=dev)
         self.peers_rows, self.peers_cols = peers_rows, peers_cols
+        self.mirror_bytes = sum(t.numel() * t.element_size() for t in self.mir.values())
 
     def _tok(self, blk_id: int) -> slice:
+        """Tokens of a block inside its owner's shard."""
         i = self.lidx[blk_id]
+        return slice(i * self.blk, (i + 1) * self.blk)
+
+    def _mtok(self, side: str, blk_id: int) -> slice:
+        """Tokens of a foreign block inside this rank's mirror of its owner (side "r" or "c")."""
+        i = self.mslot[(side, blk_id)]
         return slice(i * self.blk, (i + 1) * self.blk)
 
     # ------------------------------- staging lists ----------------------------------------------
@@ -357,10 +378,10 @@ class FusedContextParallel:
                 if kind in ("lse", "dvec"):
                     for b in range(self.B):
                         for h in range(self.H):
-                            pieces.append((r, src[b, h, self._tok(r)], dst[b, h, self._tok(r)]))
+                            pieces.append((r, src[b, h, self._tok(r)], dst[b, h, self._mtok("r", r)]))
                 else:
                     for b in range(self.B):
-                        pieces.append((r, src[b, self._tok(r)], dst[b, self._tok(r)]))
+                        pieces.append((r, src[b, self._tok(r)], dst[b, self._mtok("r", r)]))
         for c in self.remote_cols:
             if c in self.bc_slot:
                 continue                  # arrives by multicast before the barrier
@@ -368,7 +389,7 @@ class FusedContextParallel:
             for kind in kinds_cols:
                 src, dst = self.space.peer(kind, p), self.mir[(kind, p)]
                 for b in range(self.B):
-                    pieces.append((self.par_d + c, src[b, self._tok(c)], dst[b, self._tok(c)]))
+                    pieces.append((self.par_d + c, src[b, self._tok(c)], dst[b, self._mtok("c", c)]))
         return pieces
 
     def _device_tasks(self, pieces):
@@ -434,7 +455,7 @@ class FusedContextParallel:
                     segs.append(A.Seg(kv_src["bc"], self.bc_slot[c] * self.blk, self.blk,
                                       self.types[r, c] == CAUSAL, 0, 0, 0))
                     continue
-                segs.append(A.Seg(kv_src[pc], self.lidx[c] * self.blk, self.blk,
+                segs.append(A.Seg(kv_src[pc], (self.mslot[("c", c)] if remote else self.lidx[c]) * self.blk, self.blk,
                                   self.types[r, c] == CAUSAL, 0,
                                   (self.par_d + c + 1) if remote else 0,
                                   counts.get(self.par_d + c, 0) if remote else 0))
@@ -442,7 +463,8 @@ class FusedContextParallel:
                 o_start = self.lidx[r] * self.blk
             else:
                 o_start = self.slots[p].index((r, g)) * self.blk
-            rows.append(A.Row(q_src[p], self.lidx[r] * self.blk, self.blk, tuple(segs), out_slot[p],
+            rows.append(A.Row(q_src[p], (self.lidx[r] if p == g else self.mslot[("r", r)]) * self.blk, self.blk,
+                              tuple(segs), out_slot[p],
                               o_start, False, (r + 1) if p != g else 0, counts.get(r, 0) if p != g else 0))
         # rows whose inputs are all local first: they can start while the staging runs
         rows.sort(key=lambda row: (row.q_wait_flag != 0) + sum(s.wait_flag != 0 for s in row.segs))
@@ -487,7 +509,7 @@ class FusedContextParallel:
                 for r in rows:
                     pr = int(self.cmap[r])
                     remote = pr != g
-                    segs.append(A.Seg(q_src[pr], self.lidx[r] * self.blk, self.blk,
+                    segs.append(A.Seg(q_src[pr], (self.mslot[("r", r)] if remote else self.lidx[r]) * self.blk, self.blk,
                                       self.types[r, c] == CAUSAL, 0,
                                       (r + 1) if remote else 0, cnt.get(r, 0) if remote else 0))
                 kv_remote = pc != g
@@ -505,8 +527,9 @@ class FusedContextParallel:
                     cols.append(A.Col(kv_src["bc"], self.bc_slot[c] * self.blk, self.blk, tuple(segs),
                                       kv_src[pc], self.lidx[c] * self.blk, 0, 0))
                     continue
-                cols.append(A.Col(kv_src[pc], self.lidx[c] * self.blk, self.blk, tuple(segs), kv_src[pc],
-                                  self.lidx[c] * self.blk,
+                # keys / values: own shard or the compact mirror; gradients: the owner's accumulator
+                cols.append(A.Col(kv_src[pc], (self.mslot[("c", c)] if kv_remote else self.lidx[c]) * self.blk,
+                                  self.blk, tuple(segs), kv_src[pc], self.lidx[c] * self.blk,
                                   (self.par_d + c + 1) if (kv_remote and kv_cnt) else 0, kv_cnt if kv_remote else 0))
             self.b_plans.append(A.BwdPlan(cols, self.device))
             self.b_cols = cols
@@ -675,7 +698,7 @@ class FusedContextParallel:
             p = int(self.cmap[r])
             tok = self._tok(r)
             for b in range(self.B):
-                E.peer_add_(sp.peer("dq_acc", p)[b, tok], self.mir[("dq", p)][b, tok], zero_src=True)
+                E.peer_add_(sp.peer("dq_acc", p)[b, tok], self.mir[("dq", p)][b, self._mtok("r", r)], zero_src=True)
 
     def bwd_finish(self):
         sp = self.space

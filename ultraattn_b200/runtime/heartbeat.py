@@ -19,6 +19,11 @@ import torch.distributed as dist
 LEFT = "left"
 
 
+class ExcludedFromGroup(RuntimeError):
+    """The survivors agreed on a member list for a step that does not contain this rank (its
+    announcement came too late for the rank whose view was adopted): it must not take part."""
+
+
 class StepHeartbeat:
     def __init__(self, store=None, rank: Optional[int] = None, world: Optional[int] = None, prefix: str = "ua_hb"):
         if store is None:
@@ -49,9 +54,15 @@ class StepHeartbeat:
         return LEFT if val == LEFT else int(val)
 
     def missing(self, step: int, timeout_s: float = 1.0, poll_s: float = 0.02) -> list:
-        """Ranks (of those still counted alive) that have not announced ``step`` within the time
-        limit or have left. They are dropped from ``alive``; the result is the same on every
-        survivor as long as the time limit exceeds the skew between ranks."""
+        """Ranks (of those still counted alive) that do not take part in ``step``: they have not
+        announced it within the time limit, or have left. They are dropped from ``alive``.
+
+        Every survivor scans the store against its own deadline, so two survivors can see
+        different things (a slow rank's announcement may land between their last polls). The scan
+        is therefore only a proposal: the first survivor to finish publishes its member list for
+        the step with an atomic compare-and-set, and everybody adopts that list, so that all
+        survivors build the same sub-group afterwards. A rank that finds itself outside the
+        adopted list raises :class:`ExcludedFromGroup`."""
         deadline = time.monotonic() + timeout_s
         behind = [r for r in self.alive if r != self.rank]
         while True:
@@ -59,6 +70,22 @@ class StepHeartbeat:
             behind = [r for r, st in states.items() if st == LEFT or st is None or st < step]
             only_leavers = all(states[r] == LEFT for r in behind)       # nobody left to wait for
             if not behind or only_leavers or time.monotonic() >= deadline:
-                self.alive = [r for r in self.alive if r not in behind]
-                return behind
+                break
             time.sleep(poll_s)
+        proposal = [r for r in self.alive if r not in behind]
+        agreed = self._agree(step, proposal)
+        gone = [r for r in self.alive if r not in agreed]
+        self.alive = [r for r in self.alive if r in agreed]
+        if self.rank not in agreed:
+            raise ExcludedFromGroup(f"rank {self.rank} is not among the members agreed for step {step}: {agreed}")
+        return gone
+
+    def _agree(self, step: int, proposal: list) -> list:
+        key = f"{self.prefix}/members/{int(step)}"
+        mine = ",".join(str(r) for r in proposal)
+        try:
+            got = self.store.compare_set(key, "", mine)         # first writer wins; returns what is stored
+            got = got.decode() if isinstance(got, bytes) else str(got)
+        except (RuntimeError, NotImplementedError, AttributeError):
+            return proposal                                     # a store without compare-and-set: local view
+        return [int(x) for x in got.split(",") if x != ""] if got else proposal

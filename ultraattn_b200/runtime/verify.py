@@ -54,8 +54,7 @@ def verify_fused_tables(ranks: Sequence) -> list:
         # ---- forward rows
         for row in rk.f_rows:
             p = q_of[row.q_src]
-            own_blocks = rk.owned[p]
-            r = own_blocks[row.q_start // blk]
+            r = (rk.owned[p] if p == g else rk.mir_rows[p])[row.q_start // blk]
             if p != g:
                 if row.q_wait_flag != r + 1 or row.q_wait_count != f_counts.get(r, -1):
                     problems.append(f"rank {g}: row {r} of rank {p} is read without a matching wait")
@@ -74,7 +73,7 @@ def verify_fused_tables(ranks: Sequence) -> list:
                     if s.wait_flag:
                         problems.append(f"rank {g}: broadcast block {c} must not be waited for")
                 else:
-                    c = rk.owned[src][s.start // blk]
+                    c = (rk.owned[src] if src == g else rk.mir_cols[src])[s.start // blk]
                     if src != g and (s.wait_flag != par_d + c + 1 or s.wait_count != f_counts.get(par_d + c, -1)):
                         problems.append(f"rank {g}: key block {c} of rank {src} is read without a matching wait")
                     if src == g and s.wait_flag:
@@ -89,7 +88,8 @@ def verify_fused_tables(ranks: Sequence) -> list:
             for col in plan.cols:
                 src = bkv_of[col.kv_src]
                 owner = bkv_of[col.g_slot]
-                c = bc_block[col.kv_start // blk] if src == "bc" else rk.owned[src][col.kv_start // blk]
+                c = bc_block[col.kv_start // blk] if src == "bc" else \
+                    (rk.owned[src] if src == g else rk.mir_cols[src])[col.kv_start // blk]
                 if owner == "bcg":          # in-switch reduction: own replica, at the block's broadcast slot
                     if c not in rk.bc_slot or col.g_start != rk.bc_slot[c] * blk:
                         problems.append(f"rank {g}: dK/dV of block {c} go to reduction slot {col.g_start // blk}")
@@ -102,7 +102,7 @@ def verify_fused_tables(ranks: Sequence) -> list:
                     problems.append(f"rank {g}: backward key block {c} is read without a matching wait")
                 for s in col.segs:
                     p = bq_of[s.src]
-                    r = rk.owned[p][s.start // blk]
+                    r = (rk.owned[p] if p == g else rk.mir_rows[p])[s.start // blk]
                     if p != g and (s.wait_flag != r + 1 or s.wait_count != cnt.get(r, -1)):
                         problems.append(f"rank {g}: backward row {r} of rank {p} is read without a matching wait")
                     if variant == 0:
