@@ -283,3 +283,27 @@ def test_backward_restages_when_another_forward_ran_in_between():
     q, k, v, d_o = data["A"]
     out = _lock_step([rk.forward_steps(shard(q, r), shard(k, r), shard(v, r)) for r, rk in enumerate(ranks)])
     assert all(rk.staged_inputs_match(out[r][0]) for r, rk in enumerate(ranks))
+
+
+def test_debug_bounds_mode_checks_every_table_entry(monkeypatch):
+    """UA_DEBUG_BOUNDS=1: every launch first checks its tables against the tensors it was given
+    (the kernels are table driven, so this covers every address they form). A correct fused run
+    passes; a table entry that points past a staging mirror is refused before anything runs."""
+    from ultraattn_b200.ops import attention as A
+    monkeypatch.setenv("UA_DEBUG_BOUNDS", "1")
+    err, _ = _run_all_ranks(P.strided(8, 4, 2), 4, 512, 2, 16, "ilp")
+    assert err < 2e-4
+    q = torch.randn(1, 256, 2, 16)
+    k = torch.randn(1, 128, 2, 16)
+    o, lse = torch.zeros_like(q), torch.zeros(1, 2, 256)
+    good = A.FwdPlan([A.Row(0, 0, 256, (A.Seg(0, 0, 128),), 0, 0, False)])
+    A.attn_fwd([q], [k], [k], [(o, lse)], good)
+    bad = A.FwdPlan([A.Row(0, 0, 256, (A.Seg(0, 64, 128),), 0, 0, False)])          # keys 64..191 of 128
+    with pytest.raises(IndexError, match="exceed 128 tokens"):
+        A.attn_fwd([q], [k], [k], [(o, lse)], bad)
+    dq = torch.zeros(1, 256, 2, 16)
+    side = A.BwdQSide(q, torch.randn_like(q), lse, torch.zeros_like(lse), dq)
+    dk, dv = torch.zeros(1, 128, 2, 16), torch.zeros(1, 128, 2, 16)
+    badc = A.BwdPlan([A.Col(0, 0, 128, (A.Seg(0, 192, 128),), 0, 0)])                 # queries 192..319 of 256
+    with pytest.raises(IndexError, match="rows 192\\+128 exceed 256"):
+        A.attn_bwd([side], [k], [k], [A.BwdKvOut(dk, dv)], badc)

@@ -264,6 +264,26 @@ def test_model_ops(dev):
     _close(param, ref[4].to(dev), 1e-2)
 
 
+@pytest.mark.parametrize("Hd", [4096, 768])       # the sliced single-pass kernels (H % 2048 == 0) and the warp-per-row ones
+def test_rmsnorm_with_fused_residual(dev, Hd):
+    """x + res and RMSNorm(x + res) from one kernel, and the backward that adds the residual
+    branch's gradient inside the norm's backward kernel, against the fp32 restatement."""
+    from ultraattn_b200.ops import elementwise as E
+    torch.manual_seed(7)
+    rows = 259
+    x, res, g, dres = (torch.randn(rows, Hd, device=dev, dtype=torch.bfloat16) for _ in range(4))
+    w = (1 + 0.1 * torch.randn(Hd, device=dev)).to(torch.bfloat16)
+    xsum, y, rstd = E.add_rmsnorm_fwd(x, res, w, 1e-5)
+    xsum_ref, y_ref, rstd_ref = E.add_rmsnorm_fwd(x.cpu(), res.cpu(), w.cpu(), 1e-5)
+    assert torch.equal(xsum.cpu(), xsum_ref)                       # one bf16 rounding of the sum on both sides
+    _close(y, y_ref.to(dev), 1e-2)
+    _close(rstd, rstd_ref.to(dev), 1e-3)
+    dx, dw = E.rmsnorm_bwd(xsum, w, g, rstd, dres=dres)
+    dx_ref, dw_ref = E.rmsnorm_bwd(xsum_ref, w.cpu(), g.cpu(), rstd_ref, dres=dres.cpu())
+    _close(dx, dx_ref.to(dev), 1e-2)
+    _close(dw, dw_ref.to(dev), 1e-2)
+
+
 def test_varlen_packed_attention(dev):
     """Packed sequences of ragged lengths (document mask) through the same kernels."""
     from ultraattn_b200.api import varlen_attention

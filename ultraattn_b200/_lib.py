@@ -46,10 +46,10 @@ def _declare(lib):
         "ua_gemm_bf16": [POINTER(vp), i, l, i, i, i, vp, i, i, POINTER(vp), i, i, i, i, i, i, vp, i,
                          vp],
         "ua_attn_fwd": [POINTER(UaTensorSrc), i, POINTER(UaTensorSrc), POINTER(UaTensorSrc), i,
-                        POINTER(UaOutDst), i, vp, vp, vp, i, i, i, i, f, vp, vp, i, i, vp, i, vp],
+                        POINTER(UaOutDst), i, vp, vp, vp, i, i, i, i, f, vp, vp, i, i, vp, i, vp, vp],
         "ua_attn_bwd": [POINTER(UaTensorSrc), POINTER(UaTensorSrc), POINTER(UaBwdQSide), i,
                         POINTER(UaTensorSrc), POINTER(UaTensorSrc), i, POINTER(UaBwdKvOut), i,
-                        vp, vp, vp, i, i, i, i, f, vp, vp, i, i, vp, i, vp],
+                        vp, vp, vp, i, i, i, i, f, vp, vp, i, i, vp, i, vp, vp],
         "ua_barrier": [POINTER(vp), i, i, i, ctypes.c_uint, ctypes.c_double, vp, vp],
         "ua_peer_add_f32": [vp, vp, l, i, i, vp],
         "ua_multimem_bcast": [vp, vp, l, i, vp],
@@ -61,12 +61,17 @@ def _declare(lib):
         "ua_cast_scale": [vp, vp, l, f, i, vp],
         "ua_rmsnorm_fwd": [vp, vp, vp, vp, i, i, f, vp],
         "ua_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, i, i, vp],
+        "ua_add_rmsnorm_fwd": [vp, vp, vp, vp, vp, vp, i, i, f, vp],
+        "ua_rmsnorm_bwd_res": [vp, vp, vp, vp, vp, vp, vp, i, i, vp],
         "ua_rope": [vp, vp, vp, vp, vp, l, i, l, l, i, vp],
         "ua_swiglu_fwd": [vp, vp, l, i, vp],
         "ua_swiglu_bwd": [vp, vp, vp, l, i, vp],
         "ua_adam": [vp, vp, vp, vp, vp, l, f, f, f, f, f, i, f, vp],
         "ua_mma_rate": [i, i, i, i, vp, vp, vp],
     }
+    if hasattr(lib, "ua_gemm_pair_mode"):
+        lib.ua_gemm_pair_mode.restype = None
+        lib.ua_gemm_pair_mode.argtypes = [c_int]
     for name, args in sigs.items():
         if hasattr(lib, name):
             fn = getattr(lib, name)

@@ -106,6 +106,7 @@ struct BwdParams {
   float scale_log2;
   int* status;
   StageParams stage;                // optional in-kernel staging of remote blocks
+  KernelTrace trace;                // optional per-CTA time stamps
 };
 
 struct __align__(1024) BwdSmem {
@@ -142,7 +143,10 @@ struct __align__(1024) BwdSmem {
   uint64_t aug0_ready;   // the first step's row terms are in shared memory (256 softmax threads)
   uint32_t tmem_base;
   int abort_flag;
+  int stage_slot;
 };
+
+static_assert(sizeof(BwdSmem) <= 232448, "BwdSmem exceeds the 227 KB a CTA may use");
 
 // First 128-query tile of a segment that can see the key tile starting at column c0.
 __device__ __forceinline__ int seg_first_qt(const AttnSeg& sg, int c0) {
@@ -246,12 +250,20 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  run_stage_prologue(p.stage, blockIdx.y * gridDim.x + blockIdx.x);
-
   const int kv_head = blockIdx.x / p.n_tiles;
   const int2 tl = p.tiles[blockIdx.x % p.n_tiles];
   const int batch = blockIdx.y;
   const BwdCol col = p.cols[tl.x];
+  const int cta_linear = blockIdx.y * gridDim.x + blockIdx.x;
+  trace_stamp(p.trace, cta_linear, 0);
+  trace_ident(p.trace, cta_linear, tl.x);
+  {
+    // does this CTA read a staged block? then it first helps to empty the copy queue
+    bool waits = col.kv_wait_flag != 0;
+    for (int e = col.seg_begin; e < col.seg_end && !waits; ++e) waits = p.segs[e].wait_flag != 0;
+    drain_stage_queue(p.stage, waits, cta_linear, &s.stage_slot);
+  }
+  trace_stamp(p.trace, cta_linear, 1);
   const int c0 = tl.y * ATTN_TILE;              // column-relative first key of this CTA
 
   if (threadIdx.x == 0) {
@@ -759,6 +771,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
 
   tc_fence_before_sync();
   __syncthreads();
+  trace_stamp(p.trace, cta_linear, 2);
   if (warp == BWD_MMA_WARP) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
@@ -823,7 +836,7 @@ extern "C" int ua_attn_bwd(const UaTensorSrc* q_src, const UaTensorSrc* do_src,
                            int n_tiles, int n_heads, int n_kv_heads, int batch,
                            float softmax_scale, int* status, const void* copy_tasks_dev,
                            int n_copy_tasks, int n_copy_ctas, unsigned int* stage_flags,
-                           int stage_epoch, cudaStream_t stream) {
+                           int stage_epoch, unsigned int* stage_ticket, cudaStream_t stream) {
   if (n_q > ATTN_MAX_SRC || n_kv > ATTN_MAX_SRC || n_out > ATTN_MAX_SRC)
     UA_FAIL("ua_attn_bwd: too many sources (max %d)", ATTN_MAX_SRC);
   if (n_tiles <= 0) return 0;
@@ -874,14 +887,24 @@ extern "C" int ua_attn_bwd(const UaTensorSrc* q_src, const UaTensorSrc* do_src,
   p.status = status;
   p.stage.tasks = static_cast<const CopyTask*>(copy_tasks_dev);
   p.stage.n_tasks = n_copy_tasks;
-  // the copy tasks are shared by the first n_copy_ctas CTAs: never more than the grid has, or the
-  // tasks of the missing CTAs would never run and their consumers would time out
   {
     const long grid_ctas = static_cast<long>(n_tiles) * n_kv_heads * batch;
     p.stage.n_copy_ctas = static_cast<int>(n_copy_ctas < grid_ctas ? n_copy_ctas : grid_ctas);
   }
   p.stage.flags = stage_flags;
   p.stage.epoch = stage_epoch;
+  p.stage.ticket = stage_ticket;
+  {
+    int tdev = 0;
+    UA_CUDA(cudaGetDevice(&tdev));
+    const TraceSlot ts = tdev < 64 ? trace_registry()[1 * 64 + tdev] : TraceSlot{nullptr, 0};
+    p.trace.buf = ts.buf;
+    p.trace.cap = ts.cap;
+  }
+  if (n_copy_tasks > 0) {
+    if (stage_ticket == nullptr) UA_FAIL("ua_attn_bwd: copy tasks need a ticket counter");
+    UA_CUDA(cudaMemsetAsync(stage_ticket, 0, sizeof(unsigned int), stream));
+  }
   const int smem_bytes = sizeof(BwdSmem);
   int dev = 0;
   UA_CUDA(cudaGetDevice(&dev));
@@ -1026,6 +1049,9 @@ extern "C" int ua_attn_bwd_dense_noalloc(const void* q, const void* k, const voi
   p.stage.n_copy_ctas = 0;
   p.stage.flags = nullptr;
   p.stage.epoch = 1;
+  p.stage.ticket = nullptr;
+  p.trace.buf = nullptr;
+  p.trace.cap = 0;
 
   const int smem_bytes = sizeof(BwdSmem);
   if (!g_bwd_smem_set[dev]) {

@@ -47,18 +47,57 @@ struct CopyTask {
 struct StageParams {
   const CopyTask* tasks;
   int n_tasks;
-  int n_copy_ctas;         // the first n_copy_ctas CTAs (linear id) share the tasks round-robin
+  int n_copy_ctas;         // the first n_copy_ctas CTAs (linear id) help with the copies even if they wait for nothing
   unsigned int* flags;     // monotonically increasing counters, never reset
   int epoch;               // call number (1, 2, ...): a block is ready at wait_count * epoch
+  unsigned int* ticket;    // next unclaimed copy task of this launch (zeroed by the host before the launch)
+};
+
+// Optional per-CTA time stamps of a launch, available in the normal build (set through
+// ua_set_kernel_trace): CTA i of the grid writes four 64-bit words at buf[4 * i]: globaltimer at
+// its start, after its share of the staging copies, at its end, and (SM id << 32 | work item).
+// The fused kernels do their transfers themselves, so a timeline shows them as one launch; these
+// stamps keep staging, compute and idle tails attributable.
+struct KernelTrace {
+  unsigned long long* buf;
+  int cap;                 // CTAs that fit
 };
 
 #ifdef __CUDACC__
-// Staging prologue, executed by every thread of the first n_copy_ctas CTAs before they take up
-// their own tile. The copy never waits on anything, so a CTA that later waits for a staged block
-// only ever waits on work that is unconditionally in progress.
-__device__ __forceinline__ void run_stage_prologue(const StageParams& sp, int cta_linear) {
-  if (sp.n_tasks == 0 || cta_linear >= sp.n_copy_ctas) return;
-  for (int t = cta_linear; t < sp.n_tasks; t += sp.n_copy_ctas) {
+__device__ __forceinline__ void trace_stamp(const KernelTrace& kt, int cta_linear, int slot) {
+  if (kt.buf != nullptr && cta_linear < kt.cap && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    kt.buf[4 * static_cast<long>(cta_linear) + slot] = t;
+  }
+}
+__device__ __forceinline__ void trace_ident(const KernelTrace& kt, int cta_linear, int item) {
+  if (kt.buf != nullptr && cta_linear < kt.cap && threadIdx.x == 0) {
+    unsigned int smid;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    kt.buf[4 * static_cast<long>(cta_linear) + 3] = (static_cast<unsigned long long>(smid) << 32) |
+                                                   static_cast<unsigned int>(item);
+  }
+}
+#endif
+
+#ifdef __CUDACC__
+// Staging prologue. The copy tasks of a launch form a queue; a CTA takes tasks from it (one atomic
+// ticket per task) until the queue is empty. Every CTA that is going to wait for a staged block
+// does this BEFORE its first wait (`take_part`), and so do the first n_copy_ctas CTAs of the grid.
+// A copy never waits on anything. So whenever a CTA waits, every task has already been claimed
+// by a CTA that is running and will finish it: the wait can only be for work that is in progress,
+// whatever order the hardware dispatches the CTAs in. `slot`: one int of shared memory.
+__device__ __forceinline__ void drain_stage_queue(const StageParams& sp, bool take_part, int cta_linear,
+                                                  int* slot) {
+  if (sp.n_tasks == 0 || sp.ticket == nullptr) return;
+  if (!take_part && cta_linear >= sp.n_copy_ctas) return;      // (uniform over the CTA)
+  for (;;) {
+    __syncthreads();
+    if (threadIdx.x == 0) *slot = static_cast<int>(atomicAdd(sp.ticket, 1u));
+    __syncthreads();
+    const int t = *slot;
+    if (t >= sp.n_tasks) break;
     const CopyTask task = sp.tasks[t];
     const long n = task.n_vec16;
     long i = threadIdx.x;

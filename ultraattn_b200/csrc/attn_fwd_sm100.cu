@@ -11,31 +11,36 @@
 // an existing partial (O, lse) — possibly a mailbox in a peer GPU's memory.
 //
 // CTA = 256 query rows x 1 head: two 128-row sub-tiles processed ping-pong so that the tensor
-// core works on one sub-tile while the softmax warps work on the other.
-//   warps 0-3 : softmax / correction / epilogue for sub-tile 0 (one thread per query row)
-//   warps 4-7 : same for sub-tile 1
-//   warp  8   : TMA producer (Q once, then the K and V rings)
-//   warp  9   : tcgen05.mma issuer (one elected thread), TMEM allocation
+// core works on one sub-tile while the softmax warps work on the other. TPR = threads per query
+// row (template parameter):
+//   TPR = 1 (320 threads): warps 0-3 softmax / correction / epilogue for sub-tile 0 (one thread per
+//            query row, 128 score columns each), warps 4-7 the same for sub-tile 1
+//   TPR = 2 (640 threads, default): two warpgroups per sub-tile; the two threads of a row take 64
+//            score columns each (both can reach the row's TMEM lane), exchange their row maxima
+//            through shared memory once per tile and each keep a partial row sum. The softmax of
+//            a 128 x 128 tile is a chain of dependent latencies (TMEM load, max, exp2, pack, TMEM
+//            store) that one warp per scheduler cannot hide; four warps per scheduler can, which
+//            shortens the softmax phase that the tensor pipe has to wait for.
+//   then one TMA producer warp (Q once, then the K and V rings) and one tcgen05.mma issuer warp
+//   (one elected thread; it also owns the TMEM allocation)
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P (bf16) overwrites the first
-// columns of its S region and is consumed from TMEM as the A operand of the PV product.
-//
-// Two forms of the inner loop (template parameter SPLIT):
-//  * whole tiles: S of a sub-tile covers 128 keys; a warpgroup's softmax and the tensor-core work
-//    on its own sub-tile (P V of this tile, Q K^T of the next) cannot overlap, because P
-//    overwrites S in place; with two sub-tiles the tensor pipe is busy about half the time.
-//  * half tiles (UA_FWD_SPLIT=1): every 128-key tile is handled as two 64-key halves with their own S
-//    regions (S0a | S0b | S1a | S1b, 64 columns each). While a warpgroup works on one half, the
-//    tensor core runs P V of the other half and Q K^T of the next tile's half into the region just
-//    vacated, so a warpgroup never waits for its own products. The price is N = 64 for Q K^T (48
-//    instead of 32 clocks per instruction: operand reads from shared memory bound it).
+// 64 columns of its S region and is consumed from TMEM as the A operand of the PV product.
 #include "attn_common.cuh"
 #include "host_common.cuh"
 #include "ptx.cuh"
 
 namespace ua {
 
-constexpr int FWD_THREADS = 320;
 constexpr int FWD_KV_STAGES = 2;
+template <int TPR> struct FwdCfg {
+  static constexpr int SOFTMAX_WARPS = 8 * TPR;
+  static constexpr int TMA_WARP = SOFTMAX_WARPS;
+  static constexpr int MMA_WARP = SOFTMAX_WARPS + 1;
+  // TPR = 2: five warpgroups (the last one: TMA, MMA and two idle warps), so that every scheduler
+  // hosts the same number of warps and the register file can be re-balanced by warpgroup
+  static constexpr int THREADS = TPR == 2 ? 640 : 32 * (SOFTMAX_WARPS + 2);
+  static constexpr int NC = ATTN_TILE / TPR;      // score columns per thread
+};
 #ifndef UA_FWD_POLY_EXP_PERIOD
 #define UA_FWD_POLY_EXP_PERIOD 0
 #endif
@@ -74,6 +79,7 @@ struct FwdParams {
   float scale_log2;    // softmax scale * log2(e)
   int* status;
   StageParams stage;   // optional in-kernel staging of remote K/V (and Q) blocks
+  KernelTrace trace;   // optional per-CTA time stamps
 };
 
 struct __align__(1024) FwdSmem {
@@ -85,13 +91,16 @@ struct __align__(1024) FwdSmem {
   uint64_t k_empty[FWD_KV_STAGES];
   uint64_t v_full[FWD_KV_STAGES];
   uint64_t v_empty[FWD_KV_STAGES];
-  uint64_t s_full[2][2];     // [sub-tile][half]; the whole-tile form uses half 0 only
-  uint64_t p_full[2][2];
-  uint64_t pv_done[2];       // one arrival per P V product of the sub-tile (half-tile form, rescale path)
+  uint64_t s_full[2];
+  uint64_t p_full[2];
   uint64_t o_full;
   uint32_t tmem_base;
   int abort_flag;
+  int stage_slot;
+  float xchg[2][2][ATTN_TILE];    // [sub-tile][column half][row]: row maxima / row sums exchanged between the two threads of a row
+  uint64_t xbar[2];               // the 256 threads of a sub-tile meet here (an mbarrier, so that the wait is bounded)
 };
+static_assert(sizeof(FwdSmem) + 1024 <= 232448, "FwdSmem exceeds the 227 KB a CTA may use");
 
 // Number of 128-key tiles of a segment that the 256-row tile starting at block-relative row r0
 // has to visit (tiles entirely above the causal diagonal for both sub-tiles are skipped).
@@ -116,21 +125,32 @@ __device__ long long g_fwd_prof[64];
 #endif
 constexpr int FWD_PROF_TILE = 8;
 
-template <bool SPLIT>
-__global__ void __launch_bounds__(FWD_THREADS, 1)
+
+template <int TPR>
+__global__ void __launch_bounds__(FwdCfg<TPR>::THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ FwdParams p) {
+  using Cfg = FwdCfg<TPR>;
+  constexpr int NC = Cfg::NC;
   extern __shared__ uint8_t smem_raw[];
   FwdSmem& s = *reinterpret_cast<FwdSmem*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  run_stage_prologue(p.stage, blockIdx.y * gridDim.x + blockIdx.x);
-
   const int head = blockIdx.x / p.n_tiles;
   const int2 tl = p.tiles[blockIdx.x % p.n_tiles];
   const int batch = blockIdx.y;
   const FwdRow row = p.rows[tl.x];
+  const int cta_linear = blockIdx.y * gridDim.x + blockIdx.x;
+  trace_stamp(p.trace, cta_linear, 0);
+  trace_ident(p.trace, cta_linear, tl.x);
+  {
+    // does this CTA read a staged block? then it first helps to empty the copy queue
+    bool waits = row.q_wait_flag != 0;
+    for (int e = row.seg_begin; e < row.seg_end && !waits; ++e) waits = p.segs[e].wait_flag != 0;
+    drain_stage_queue(p.stage, waits, cta_linear, &s.stage_slot);
+  }
+  trace_stamp(p.trace, cta_linear, 1);
   const int r0 = tl.y * 256;                                    // block-relative first row
   const int rows_here = min(256, row.q_len - r0);               // valid query rows of this CTA
   const int kv_head = head / p.kv_group;
@@ -138,11 +158,9 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.q_full[i], 1);
-      mbar_init(&s.pv_done[i], 1);
-      for (int h = 0; h < 2; ++h) {
-        mbar_init(&s.s_full[i][h], 1);
-        mbar_init(&s.p_full[i][h], 128);
-      }
+      mbar_init(&s.s_full[i], 1);
+      mbar_init(&s.p_full[i], 128 * TPR);
+      mbar_init(&s.xbar[i], 256);
     }
     for (int i = 0; i < FWD_KV_STAGES; ++i) {
       mbar_init(&s.k_full[i], 1);
@@ -154,7 +172,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     s.abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 9) {
+  if (warp == Cfg::MMA_WARP) {
     tmem_alloc(&s.tmem_base, 512);
     tmem_relinquish();
   }
@@ -168,7 +186,13 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
   int n_total = 0;
   for (int e = row.seg_begin; e < row.seg_end; ++e) n_total += seg_tiles(p.segs[e], r0, rows_here);
 
-  if (warp == 8) {
+  if (warp >= Cfg::SOFTMAX_WARPS) {
+  // 20 warps leave 96 registers per thread (five warps share a scheduler's 16K registers). The last
+  // warpgroup (TMA, MMA, two idle warps) needs few; the softmax warpgroups, which hold 64 scores per
+  // thread, take what it gives back. (The instruction sits inside the role's branch so that the
+  // compiler budgets each role separately.)
+  if constexpr (TPR == 2) reg_dealloc<56>();
+  if (warp == Cfg::TMA_WARP) {
     // =============================== TMA producer ===========================================
     if (lane == 0 && n_total > 0) {
       const CUtensorMap* tq = &p.tmQ[row.q_src];
@@ -210,7 +234,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == Cfg::MMA_WARP) {
     // =============================== MMA issuer =============================================
     if (lane == 0 && n_total > 0) {
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // S = Q K^T, both K-major
@@ -237,17 +261,16 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         }
       };
       bool ok = true;
-      if constexpr (!SPLIT) {
       do {
         if (!mbar_wait(&s.q_full[0], 0, wc, 200)) { ok = false; break; }
         if (!mbar_wait(&s.k_full[0], 0, wc, 201)) { ok = false; break; }
         tc_fence_after_sync();
         issue_s(0, 0);
-        tc_commit(&s.s_full[0][0]);
+        tc_commit(&s.s_full[0]);
         if (!mbar_wait(&s.q_full[1], 0, wc, 202)) { ok = false; break; }
         tc_fence_after_sync();
         issue_s(1, 0);
-        tc_commit(&s.s_full[1][0]);
+        tc_commit(&s.s_full[1]);
         tc_commit(&s.k_empty[0]);
         for (int j = 0; j < n_total; ++j) {
           const int st = j % FWD_KV_STAGES;
@@ -257,7 +280,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           const bool more = (j + 1 < n_total);
           FWD_PROF(j == FWD_PROF_TILE, 0);
           if (!mbar_wait(&s.v_full[st], ph, wc, 203)) { ok = false; break; }
-          if (!mbar_wait(&s.p_full[0][0], j & 1, wc, 204)) { ok = false; break; }
+          if (!mbar_wait(&s.p_full[0], j & 1, wc, 204)) { ok = false; break; }
           FWD_PROF(j == FWD_PROF_TILE, 1);
           tc_fence_after_sync();
           issue_pv(0, st, j > 0);
@@ -265,122 +288,62 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             if (!mbar_wait(&s.k_full[stn], phn, wc, 205)) { ok = false; break; }
             tc_fence_after_sync();
             issue_s(0, stn);
-            tc_commit(&s.s_full[0][0]);
+            tc_commit(&s.s_full[0]);
           }
           FWD_PROF(j == FWD_PROF_TILE, 2);
-          if (!mbar_wait(&s.p_full[1][0], j & 1, wc, 206)) { ok = false; break; }
+          if (!mbar_wait(&s.p_full[1], j & 1, wc, 206)) { ok = false; break; }
           FWD_PROF(j == FWD_PROF_TILE, 3);
           tc_fence_after_sync();
           issue_pv(1, st, j > 0);
           tc_commit(&s.v_empty[st]);
           if (more) {
             issue_s(1, stn);
-            tc_commit(&s.s_full[1][0]);
+            tc_commit(&s.s_full[1]);
             tc_commit(&s.k_empty[stn]);
           }
           FWD_PROF(j == FWD_PROF_TILE, 4);
         }
         if (ok) tc_commit(&s.o_full);
       } while (false);
-      } else {
-      // ---- half tiles: S regions [w][h] of 64 columns; issue order per tile: (h, w) = a0 a1 b0 b1
-      const uint32_t idesc_s64 = make_idesc_bf16(128, 64, 0, 0);
-      auto issue_s_half = [&](int w, int h, int st) {
-        const uint32_t qa = smem_u32(s.q[w]);
-        const uint32_t ka = smem_u32(s.k[st]) + h * 8192;          // keys h*64 .. h*64+63 (rows of 128 B)
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_ss(tS[w] + h * 64, make_smem_desc_sw128(qa + off, 16, 1024),
-                  make_smem_desc_sw128(ka + off, 16, 1024), idesc_s64, kk > 0 ? 1u : 0u);
-        }
-      };
-      auto issue_pv_half = [&](int w, int h, int st, bool acc) {
-        const uint32_t va = smem_u32(s.v[st]);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          umma_ts(tO[w], tS[w] + h * 64 + kk * 8, make_smem_desc_sw128(va + (h * 4 + kk) * 2048, 16384, 1024),
-                  idesc_o, (acc || kk > 0) ? 1u : 0u);
-        }
-      };
-      do {
-        if (!mbar_wait(&s.q_full[0], 0, wc, 200)) { ok = false; break; }
-        if (!mbar_wait(&s.k_full[0], 0, wc, 201)) { ok = false; break; }
-        tc_fence_after_sync();
-        issue_s_half(0, 0, 0);
-        tc_commit(&s.s_full[0][0]);
-        if (!mbar_wait(&s.q_full[1], 0, wc, 202)) { ok = false; break; }
-        tc_fence_after_sync();
-        issue_s_half(1, 0, 0);
-        tc_commit(&s.s_full[1][0]);
-        issue_s_half(0, 1, 0);
-        tc_commit(&s.s_full[0][1]);
-        issue_s_half(1, 1, 0);
-        tc_commit(&s.s_full[1][1]);
-        tc_commit(&s.k_empty[0]);
-        for (int j = 0; j < n_total && ok; ++j) {
-          const int st = j % FWD_KV_STAGES;
-          const uint32_t ph = (j / FWD_KV_STAGES) & 1;
-          const int stn = (j + 1) % FWD_KV_STAGES;
-          const uint32_t phn = ((j + 1) / FWD_KV_STAGES) & 1;
-          const bool more = (j + 1 < n_total);
-          if (!mbar_wait(&s.v_full[st], ph, wc, 203)) { ok = false; break; }
-#pragma unroll
-          for (int hw = 0; hw < 4; ++hw) {
-            const int h = hw >> 1, w = hw & 1;
-            if (!mbar_wait(&s.p_full[w][h], j & 1, wc, 204 + hw)) { ok = false; break; }
-            FWD_PROF(j == FWD_PROF_TILE, hw * 2);
-            tc_fence_after_sync();
-            issue_pv_half(w, h, st, j > 0 || h > 0);
-            tc_commit(&s.pv_done[w]);
-            if (hw == 3) tc_commit(&s.v_empty[st]);
-            if (more) {
-              if (hw == 0) {
-                if (!mbar_wait(&s.k_full[stn], phn, wc, 208)) { ok = false; break; }
-                tc_fence_after_sync();
-              }
-              issue_s_half(w, h, stn);
-              tc_commit(&s.s_full[w][h]);
-              if (hw == 3) tc_commit(&s.k_empty[stn]);
-            }
-            FWD_PROF(j == FWD_PROF_TILE, hw * 2 + 1);
-          }
-        }
-        if (ok) tc_commit(&s.o_full);
-      } while (false);
-      }
       (void)ok;
     }
+  }
   } else {
     // =============================== softmax + epilogue =====================================
-    const int w = warp >> 2;                 // sub-tile
+    if constexpr (TPR == 2) reg_alloc<112>();
+    const int w = warp / (4 * TPR);          // sub-tile
+    const int part = (warp >> 2) % TPR;      // which NC-column slice of the row this thread handles
     const int quad = warp & 3;               // TMEM lane quadrant of this warp
     const int r_tile = quad * 32 + lane;     // row inside the 128-row sub-tile
     const int r_blk = r0 + w * ATTN_TILE + r_tile;   // row inside the query block
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + w * 128;
+    const uint32_t tSp = tS + part * NC;             // this thread's score columns
+    const uint32_t tPp = tS + part * (NC / 2);       // ... and where its packed probabilities go
     const uint32_t tO = tmem_base + lane_base + 256 + w * 128;
     const float NEG_INF = -INFINITY;
 
-    float m_use = NEG_INF;   // running reference max, log2 units (already scaled)
-    float l = 0.f;
+    uint32_t xph = 0;        // phase of the sub-tile's exchange barrier
+    // all 256 threads of the sub-tile have passed this point (bounded like every other wait)
+    auto subtile_sync = [&]() -> bool {
+      mbar_arrive(&s.xbar[w]);
+      const bool good = mbar_wait(&s.xbar[w], xph & 1, wc, 330 + w);
+      ++xph;
+      return good;
+    };
+    float m_use = NEG_INF;   // running reference max, log2 units (already scaled); identical in both threads of a row
+    float l = 0.f;           // row sum over this thread's columns
     bool ok = true;
     uint32_t j = 0;
-    constexpr int NH = SPLIT ? 2 : 1;          // passes per 128-key tile
-    constexpr int NC = ATTN_TILE / NH;         // S columns per pass
-    uint32_t n_half = 0;                       // passes done so far (= P V products issued for this sub-tile)
     for (int e = row.seg_begin; e < row.seg_end && ok; ++e) {
       const AttnSeg sg = p.segs[e];
       const int nt = seg_tiles(sg, r0, rows_here);
-      for (int t = 0; t < nt && ok; ++t, ++j) {
-#pragma unroll
-        for (int h = 0; h < NH; ++h, ++n_half) {
-        const bool prof = (j == FWD_PROF_TILE || j == FWD_PROF_TILE + 1) && quad == 0 && lane == 0;
-        const int pslot = 8 + w * 24 + (static_cast<int>(j) - FWD_PROF_TILE) * (SPLIT ? 12 : 8) + h * 6;
+      for (int t = 0; t < nt; ++t, ++j) {
+        const bool prof = (j == FWD_PROF_TILE || j == FWD_PROF_TILE + 1) && quad == 0 && lane == 0 && part == 0;
+        const int pslot = 8 + w * 24 + (static_cast<int>(j) - FWD_PROF_TILE) * 8;
         (void)prof; (void)pslot;
-        const uint32_t tSh = tS + h * NC;
         FWD_PROF(prof, pslot + 0);
-        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.s_full[w][h], j & 1, wc, 300 + w))) { ok = false; break; }
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.s_full[w], j & 1, wc, 300 + w))) { ok = false; break; }
         FWD_PROF(prof, pslot + 1);
         tc_fence_after_sync();
         float sv[NC];
@@ -388,12 +351,12 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           uint32_t(&raw)[NC] = reinterpret_cast<uint32_t(&)[NC]>(sv);
 #pragma unroll
           for (int c = 0; c < NC / 32; ++c)
-            tmem_ld_x32(tSh + c * 32, reinterpret_cast<uint32_t(&)[32]>(raw[c * 32]));
+            tmem_ld_x32(tSp + c * 32, reinterpret_cast<uint32_t(&)[32]>(raw[c * 32]));
           tmem_wait_ld();
         }
         FWD_PROF(prof, pslot + 2);
         // masking: key index c (segment-relative) allowed iff c < len and (c <= r + diag)
-        const int c0 = t * ATTN_TILE + h * NC;
+        const int c0 = t * ATTN_TILE + part * NC;
         int limit = sg.len - c0;                               // columns < limit are in range
         if (sg.causal) limit = min(limit, r_blk + sg.diag - c0 + 1);
         if (limit < NC) {
@@ -411,25 +374,28 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
           for (int k = 0; k < 8; ++k) mx8[k] = fmax3(mx8[k], sv[i + k], sv[i + 8 + k]);
         float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]));
         mx = fmax3(mx, mx8[6], mx8[7]);
+        if constexpr (TPR == 2) {
+          // the row maximum over all 128 columns: exchange with the thread that holds the other half.
+          // (The slot is free again: its reader of the previous tile arrived at p_full before the
+          // products this tile's scores waited for could be issued.)
+          s.xchg[w][part][r_tile] = mx;
+          if (!__all_sync(0xFFFFFFFFu, subtile_sync())) { ok = false; break; }
+          mx = fmaxf(mx, s.xchg[w][part ^ 1][r_tile]);
+        }
         mx *= p.scale_log2;
         const float m_new = fmaxf(m_use, mx);
         // lazy rescale: only when the running max grew by more than 2^8 (warp-uniform branch,
         // because the TMEM accesses below are warp-collective)
         const bool need = (m_new - m_use > 8.0f) || (m_use == NEG_INF && m_new > NEG_INF);
-        if (n_half == 0) {
+        if (j == 0) {
           m_use = m_new;
         } else if (__any_sync(0xFFFFFFFFu, need)) {
-          if constexpr (SPLIT) {
-            // O may still be the target of the P V product of the previous pass (issued after the
-            // Q K^T this pass waited for): all n_half products issued so far must have completed
-            if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s.pv_done[w], (n_half - 1) & 1, wc, 320 + w))) { ok = false; break; }
-            tc_fence_after_sync();
-          }
           const float alpha = need ? fast_exp2(m_use - m_new) : 1.0f;
           if (need) m_use = m_new;
           l *= alpha;
+          // each thread of the row rescales its share of the 128 output columns
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = part * (4 / TPR); c < (part + 1) * (4 / TPR); ++c) {
             uint32_t ov[32];
             tmem_ld_x32(tO + c * 32, ov);
             tmem_wait_ld();
@@ -465,7 +431,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
             ls2[i & 3] = f2_add(ls2[i & 3], f2_pack(p0, p1));
             pk[i] = pack_bf16x2(p0, p1);
           }
-          tmem_st_x16(tSh + c * 16, pk);
+          tmem_st_x16(tPp + c * 16, pk);
         }
         float ls4[4];
 #pragma unroll
@@ -478,10 +444,16 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         FWD_PROF(prof, pslot + 4);
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&s.p_full[w][h]);
+        mbar_arrive(&s.p_full[w]);
         FWD_PROF(prof, pslot + 5);
-        }
       }
+    }
+    if constexpr (TPR == 2) {
+      // the row sum over all columns (m_use is the same in both threads)
+      if (ok) ok = __all_sync(0xFFFFFFFFu, subtile_sync());      // the last exchange of maxima has been read
+      s.xchg[w][part][r_tile] = l;
+      if (ok) ok = __all_sync(0xFFFFFFFFu, subtile_sync());
+      l += s.xchg[w][part ^ 1][r_tile];
     }
 
     // ---------------------------------- epilogue --------------------------------------------
@@ -502,8 +474,13 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
       inv = 1.0f / l;
     }
     float w_old = 0.f, w_new = 1.f;
+    float lse_old = NEG_INF;
+    if (row.accumulate) {
+      if (valid_row) lse_old = *lptr;
+      // (both threads of a row have read the old lse before one of them overwrites it below)
+      if constexpr (TPR == 2) { if (ok) ok = __all_sync(0xFFFFFFFFu, subtile_sync()); }
+    }
     if (row.accumulate && valid_row) {
-      const float lse_old = *lptr;
       const float mx = fmaxf(lse_old, lse);
       if (mx == NEG_INF) {
         w_old = 0.f; w_new = 0.f;
@@ -516,7 +493,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     }
     const float fnew = inv * w_new;
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = part * (4 / TPR); c < (part + 1) * (4 / TPR); ++c) {
       uint32_t ov[32];
       if (n_total > 0) {
         tmem_ld_x32(tO + c * 32, ov);
@@ -552,12 +529,13 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         }
       }
     }
-    if (valid_row) *lptr = lse;
+    if (valid_row && part == 0) *lptr = lse;
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 9) {
+  trace_stamp(p.trace, cta_linear, 2);
+  if (warp == Cfg::MMA_WARP) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
@@ -566,6 +544,16 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
 }  // namespace ua
 
 using namespace ua;
+
+// Register (or, with buf = NULL, remove) the per-CTA trace buffer of the current device:
+// which = 0 forward, 1 backward; buf = 4 * cap 64-bit words of device memory (see KernelTrace).
+extern "C" int ua_set_kernel_trace(int which, unsigned long long* buf, int cap) {
+  int dev = 0;
+  UA_CUDA(cudaGetDevice(&dev));
+  if (which < 0 || which > 1 || dev >= 64) UA_FAIL("ua_set_kernel_trace: bad kernel or device index");
+  trace_registry()[which * 64 + dev] = TraceSlot{buf, buf != nullptr ? cap : 0};
+  return 0;
+}
 
 #ifdef UA_FWD_PROF
 extern "C" int ua_fwd_prof_read(long long* host64) {
@@ -614,7 +602,7 @@ extern "C" int ua_attn_fwd(const UaTensorSrc* q_src, int n_q, const UaTensorSrc*
                            int n_tiles, int n_heads, int n_kv_heads, int batch,
                            float softmax_scale, int* status, const void* copy_tasks_dev,
                            int n_copy_tasks, int n_copy_ctas, unsigned int* stage_flags,
-                           int stage_epoch, cudaStream_t stream) {
+                           int stage_epoch, unsigned int* stage_ticket, cudaStream_t stream) {
   if (n_q > ATTN_MAX_SRC || n_kv > ATTN_MAX_SRC || n_out > ATTN_MAX_SRC)
     UA_FAIL("ua_attn_fwd: too many sources (max %d)", ATTN_MAX_SRC);
   if (n_tiles <= 0) return 0;
@@ -644,32 +632,42 @@ extern "C" int ua_attn_fwd(const UaTensorSrc* q_src, int n_q, const UaTensorSrc*
   p.status = status;
   p.stage.tasks = static_cast<const CopyTask*>(copy_tasks_dev);
   p.stage.n_tasks = n_copy_tasks;
-  // the copy tasks are shared by the first n_copy_ctas CTAs: never more than the grid has, or the
-  // tasks of the missing CTAs would never run and their consumers would time out
   {
     const long grid_ctas = static_cast<long>(n_tiles) * n_heads * batch;
     p.stage.n_copy_ctas = static_cast<int>(n_copy_ctas < grid_ctas ? n_copy_ctas : grid_ctas);
   }
   p.stage.flags = stage_flags;
   p.stage.epoch = stage_epoch;
+  p.stage.ticket = stage_ticket;
+  {
+    int tdev = 0;
+    UA_CUDA(cudaGetDevice(&tdev));
+    const TraceSlot ts = tdev < 64 ? trace_registry()[0 * 64 + tdev] : TraceSlot{nullptr, 0};
+    p.trace.buf = ts.buf;
+    p.trace.cap = ts.cap;
+  }
+  if (n_copy_tasks > 0) {
+    if (stage_ticket == nullptr) UA_FAIL("ua_attn_fwd: copy tasks need a ticket counter");
+    UA_CUDA(cudaMemsetAsync(stage_ticket, 0, sizeof(unsigned int), stream));
+  }
   const int smem_bytes = sizeof(FwdSmem) + 1024;
   int dev = 0;
   UA_CUDA(cudaGetDevice(&dev));
-  // UA_FWD_SPLIT=1 selects the half-tile form of the inner loop (see the top of this file)
-  const char* env = getenv("UA_FWD_SPLIT");
-  const int split = (env != nullptr && atoi(env) != 0) ? 1 : 0;
-  if (dev < 64 && !g_fwd_smem_set[split][dev]) {
-    if (split)
-      UA_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  // UA_FWD_TPR = 1 / 2: softmax threads per query row (see the top of this file)
+  const char* env = getenv("UA_FWD_TPR");
+  const int tpr = (env != nullptr && atoi(env) == 1) ? 1 : 2;
+  if (dev < 64 && !g_fwd_smem_set[tpr - 1][dev]) {
+    if (tpr == 2)
+      UA_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     else
-      UA_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-    g_fwd_smem_set[split][dev] = 1;
+      UA_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    g_fwd_smem_set[tpr - 1][dev] = 1;
   }
   dim3 grid(n_tiles * n_heads, batch, 1);
-  if (split)
-    attn_fwd_kernel<true><<<grid, FWD_THREADS, smem_bytes, stream>>>(p);
+  if (tpr == 2)
+    attn_fwd_kernel<2><<<grid, FwdCfg<2>::THREADS, smem_bytes, stream>>>(p);
   else
-    attn_fwd_kernel<false><<<grid, FWD_THREADS, smem_bytes, stream>>>(p);
+    attn_fwd_kernel<1><<<grid, FwdCfg<1>::THREADS, smem_bytes, stream>>>(p);
   UA_CUDA(cudaGetLastError());
   return 0;
 }

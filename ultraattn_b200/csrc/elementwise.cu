@@ -151,12 +151,24 @@ cast_scale_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst
 // ---------------------------------------------------------------------------------------------
 // RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w. One warp per row; row length H % 256 == 0.
 // rstd is saved for the backward.
+// Residual fusion: with `res` the kernels normalise xsum = x + res (rounded to bf16, which is what
+// the next layer sees) and also store xsum; in the backward `dres` (the gradient that reaches
+// xsum through the residual branch) is added to dx, so the two element-wise additions around a
+// norm in a transformer block cost no passes of their own.
 // ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 add_bf16x8(const uint4& a, const uint4& b) {
+  const uint32_t as[4] = {a.x, a.y, a.z, a.w};
+  const uint32_t bs[4] = {b.x, b.y, b.z, b.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) o[q] = pack_bf16x2(bf_lo(as[q]) + bf_lo(bs[q]), bf_hi(as[q]) + bf_hi(bs[q]));
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
 template <int MAXV>
 __global__ void __launch_bounds__(256)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int H,
-                   float eps) {
+                   float eps, const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ xsum) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= rows) return;
@@ -168,6 +180,11 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   for (int i = 0; i < MAXV; ++i) {
     if (i < nv) {
       v[i] = *reinterpret_cast<const uint4*>(xr + (i * 32 + lane) * 8);
+      if (res != nullptr) {
+        const long off = static_cast<long>(warp) * H + (i * 32 + lane) * 8;
+        v[i] = add_bf16x8(v[i], *reinterpret_cast<const uint4*>(res + off));
+        *reinterpret_cast<uint4*>(xsum + off) = v[i];
+      }
       const uint32_t ws[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
 #pragma unroll
       for (int q = 0; q < 4; ++q) ss += bf_lo(ws[q]) * bf_lo(ws[q]) + bf_hi(ws[q]) * bf_hi(ws[q]);
@@ -198,7 +215,7 @@ template <int NCH, int R>
 __global__ void __launch_bounds__(256, 2)
 rmsnorm_fwd_sliced_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                           __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int H,
-                          float eps) {
+                          float eps, const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ xsum) {
   __shared__ float part[2][R][8];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -213,8 +230,14 @@ rmsnorm_fwd_sliced_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
     for (int r = 0; r < R; ++r) {
       const int row = min(r0 + r, rows - 1);
 #pragma unroll
-      for (int j = 0; j < NCH; ++j)
-        xv[r][j] = *reinterpret_cast<const uint4*>(x + static_cast<long>(row) * H + col0 + j * 256);
+      for (int j = 0; j < NCH; ++j) {
+        const long off = static_cast<long>(row) * H + col0 + j * 256;
+        xv[r][j] = *reinterpret_cast<const uint4*>(x + off);
+        if (res != nullptr) {
+          xv[r][j] = add_bf16x8(xv[r][j], *reinterpret_cast<const uint4*>(res + off));
+          if (r0 + r < rows) *reinterpret_cast<uint4*>(xsum + off) = xv[r][j];
+        }
+      }
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -258,7 +281,8 @@ rmsnorm_fwd_sliced_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
 __global__ void __launch_bounds__(256)
 rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                       const __nv_bfloat16* __restrict__ g, const float* __restrict__ rstd,
-                      __nv_bfloat16* __restrict__ dx, int rows, int H) {
+                      __nv_bfloat16* __restrict__ dx, int rows, int H,
+                      const __nv_bfloat16* __restrict__ dres) {
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -287,11 +311,14 @@ rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
     const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w};
     const uint32_t gs[4] = {gv.x, gv.y, gv.z, gv.w};
     const uint32_t ws[4] = {wv.x, wv.y, wv.z, wv.w};
+    uint4 dr = make_uint4(0u, 0u, 0u, 0u);
+    if (dres != nullptr) dr = *reinterpret_cast<const uint4*>(dres + static_cast<long>(row) * H + c);
+    const uint32_t ds[4] = {dr.x, dr.y, dr.z, dr.w};
     uint32_t o[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q)
-      o[q] = pack_bf16x2(r * (bf_lo(gs[q]) * bf_lo(ws[q]) - bf_lo(xs[q]) * cc),
-                         r * (bf_hi(gs[q]) * bf_hi(ws[q]) - bf_hi(xs[q]) * cc));
+      o[q] = pack_bf16x2(r * (bf_lo(gs[q]) * bf_lo(ws[q]) - bf_lo(xs[q]) * cc) + bf_lo(ds[q]),
+                         r * (bf_hi(gs[q]) * bf_hi(ws[q]) - bf_hi(xs[q]) * cc) + bf_hi(ds[q]));
     *reinterpret_cast<uint4*>(dxr + c) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
@@ -343,7 +370,8 @@ template <int NCH, int R>     // NCH: 16-byte chunks per lane and row (H / 2048)
 __global__ void __launch_bounds__(256, 2)
 rmsnorm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                          const __nv_bfloat16* __restrict__ g, const float* __restrict__ rstd,
-                         __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, int rows, int H) {
+                         __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, int rows, int H,
+                         const __nv_bfloat16* __restrict__ dres) {
   __shared__ float part[2][R][8];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -403,11 +431,16 @@ rmsnorm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
         const uint32_t xs[4] = {xv[r][j].x, xv[r][j].y, xv[r][j].z, xv[r][j].w};
         const uint32_t gs[4] = {gv[r][j].x, gv[r][j].y, gv[r][j].z, gv[r][j].w};
         const uint32_t ws[4] = {wv[j].x, wv[j].y, wv[j].z, wv[j].w};
+        uint4 dr = make_uint4(0u, 0u, 0u, 0u);
+        if (dres != nullptr && live)
+          dr = *reinterpret_cast<const uint4*>(dres + static_cast<long>(r0 + r) * H + col0 + j * 256);
+        const uint32_t ds[4] = {dr.x, dr.y, dr.z, dr.w};
         uint32_t o[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const float xl = bf_lo(xs[q]), xh = bf_hi(xs[q]), gl = bf_lo(gs[q]), gh = bf_hi(gs[q]);
-          o[q] = pack_bf16x2(rr * (gl * bf_lo(ws[q]) - xl * cc), rr * (gh * bf_hi(ws[q]) - xh * cc));
+          o[q] = pack_bf16x2(rr * (gl * bf_lo(ws[q]) - xl * cc) + bf_lo(ds[q]),
+                             rr * (gh * bf_hi(ws[q]) - xh * cc) + bf_hi(ds[q]));
           acc[j][2 * q] += gl * xl * rr;
           acc[j][2 * q + 1] += gh * xh * rr;
         }
@@ -631,14 +664,16 @@ extern "C" int ua_cast_scale(const float* src, void* dst, long n, float scale, i
   return 0;
 }
 
-extern "C" int ua_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int H,
-                              float eps, cudaStream_t stream) {
+static int rmsnorm_fwd_launch(const void* x, const void* res, const void* w, void* xsum, void* y, float* rstd,
+                              int rows, int H, float eps, cudaStream_t stream) {
   if (H % 256 != 0 || H > 8192) UA_FAIL("ua_rmsnorm_fwd: H must be a multiple of 256, <= 8192");
   if (rows == 0) return 0;
   const unsigned blocks = (static_cast<long>(rows) * 32 + 255) / 256;
   auto xx = static_cast<const __nv_bfloat16*>(x);
   auto ww = static_cast<const __nv_bfloat16*>(w);
   auto yy = static_cast<__nv_bfloat16*>(y);
+  auto rr = static_cast<const __nv_bfloat16*>(res);
+  auto xs = static_cast<__nv_bfloat16*>(xsum);
   if (H % 2048 == 0) {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
@@ -646,23 +681,36 @@ extern "C" int ua_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
     const long want = (static_cast<long>(rows) + 3) / 4;
     const unsigned nb = static_cast<unsigned>(want < 8L * sms ? want : 8L * sms);
     switch (H / 2048) {
-      case 1: rmsnorm_fwd_sliced_kernel<1, 4><<<nb, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps); break;
-      case 2: rmsnorm_fwd_sliced_kernel<2, 4><<<nb, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps); break;
-      case 3: rmsnorm_fwd_sliced_kernel<3, 4><<<nb, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps); break;
-      default: rmsnorm_fwd_sliced_kernel<4, 4><<<nb, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps); break;
+      case 1: rmsnorm_fwd_sliced_kernel<1, 4><<<nb, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps, rr, xs); break;
+      case 2: rmsnorm_fwd_sliced_kernel<2, 4><<<nb, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps, rr, xs); break;
+      case 3: rmsnorm_fwd_sliced_kernel<3, 4><<<nb, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps, rr, xs); break;
+      default: rmsnorm_fwd_sliced_kernel<4, 4><<<nb, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps, rr, xs); break;
     }
     UA_CUDA(cudaGetLastError());
     return 0;
   }
-  if (H <= 4096) rmsnorm_fwd_kernel<16><<<blocks, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps);
-  else rmsnorm_fwd_kernel<32><<<blocks, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps);
+  if (H <= 4096) rmsnorm_fwd_kernel<16><<<blocks, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps, rr, xs);
+  else rmsnorm_fwd_kernel<32><<<blocks, 256, 0, stream>>>(xx, ww, yy, rstd, rows, H, eps, rr, xs);
   UA_CUDA(cudaGetLastError());
   return 0;
 }
 
+extern "C" int ua_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int H,
+                              float eps, cudaStream_t stream) {
+  return rmsnorm_fwd_launch(x, nullptr, w, nullptr, y, rstd, rows, H, eps, stream);
+}
+
+// xsum = x + res (bf16), y = RMSNorm(xsum) * w, in one pass.
+extern "C" int ua_add_rmsnorm_fwd(const void* x, const void* res, const void* w, void* xsum, void* y,
+                                  float* rstd, int rows, int H, float eps, cudaStream_t stream) {
+  if (res == nullptr || xsum == nullptr) UA_FAIL("ua_add_rmsnorm_fwd: res and xsum are required");
+  return rmsnorm_fwd_launch(x, res, w, xsum, y, rstd, rows, H, eps, stream);
+}
+
 // dw must be zeroed by the caller (fp32, H entries); it is accumulated into.
-extern "C" int ua_rmsnorm_bwd(const void* x, const void* w, const void* g, const float* rstd,
+static int rmsnorm_bwd_launch(const void* x, const void* w, const void* g, const float* rstd, const void* dres,
                               void* dx, float* dw, int rows, int H, cudaStream_t stream) {
+  auto dr = static_cast<const __nv_bfloat16*>(dres);
   if (H % 256 != 0) UA_FAIL("ua_rmsnorm_bwd: H must be a multiple of 256");
   if (rows == 0) return 0;
   if (H % 2048 == 0 && H <= 8192) {
@@ -678,10 +726,10 @@ extern "C" int ua_rmsnorm_bwd(const void* x, const void* w, const void* g, const
     auto gg = static_cast<const __nv_bfloat16*>(g);
     auto dd = static_cast<__nv_bfloat16*>(dx);
     switch (H / 2048) {
-      case 1: rmsnorm_bwd_fused_kernel<1, 4><<<nb, 256, 0, stream>>>(xx, ww, gg, rstd, dd, dw, rows, H); break;
-      case 2: rmsnorm_bwd_fused_kernel<2, 2><<<nb, 256, 0, stream>>>(xx, ww, gg, rstd, dd, dw, rows, H); break;
-      case 3: rmsnorm_bwd_fused_kernel<3, 2><<<nb, 256, 0, stream>>>(xx, ww, gg, rstd, dd, dw, rows, H); break;
-      default: rmsnorm_bwd_fused_kernel<4, 2><<<nb, 256, 0, stream>>>(xx, ww, gg, rstd, dd, dw, rows, H); break;
+      case 1: rmsnorm_bwd_fused_kernel<1, 4><<<nb, 256, 0, stream>>>(xx, ww, gg, rstd, dd, dw, rows, H, dr); break;
+      case 2: rmsnorm_bwd_fused_kernel<2, 2><<<nb, 256, 0, stream>>>(xx, ww, gg, rstd, dd, dw, rows, H, dr); break;
+      case 3: rmsnorm_bwd_fused_kernel<3, 2><<<nb, 256, 0, stream>>>(xx, ww, gg, rstd, dd, dw, rows, H, dr); break;
+      default: rmsnorm_bwd_fused_kernel<4, 2><<<nb, 256, 0, stream>>>(xx, ww, gg, rstd, dd, dw, rows, H, dr); break;
     }
     UA_CUDA(cudaGetLastError());
     return 0;
@@ -689,7 +737,7 @@ extern "C" int ua_rmsnorm_bwd(const void* x, const void* w, const void* g, const
   const unsigned blocks = (static_cast<long>(rows) * 32 + 255) / 256;
   rmsnorm_bwd_dx_kernel<<<blocks, 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-      static_cast<const __nv_bfloat16*>(g), rstd, static_cast<__nv_bfloat16*>(dx), rows, H);
+      static_cast<const __nv_bfloat16*>(g), rstd, static_cast<__nv_bfloat16*>(dx), rows, H, dr);
   UA_CUDA(cudaGetLastError());
   const int rows_per_slice = 64;
   dim3 grid((H / 8 + 255) / 256, (rows + rows_per_slice - 1) / rows_per_slice);
@@ -698,6 +746,18 @@ extern "C" int ua_rmsnorm_bwd(const void* x, const void* w, const void* g, const
                                                   rows, H, rows_per_slice);
   UA_CUDA(cudaGetLastError());
   return 0;
+}
+
+extern "C" int ua_rmsnorm_bwd(const void* x, const void* w, const void* g, const float* rstd,
+                              void* dx, float* dw, int rows, int H, cudaStream_t stream) {
+  return rmsnorm_bwd_launch(x, w, g, rstd, nullptr, dx, dw, rows, H, stream);
+}
+
+// dx = d RMSNorm / dx (g) + dres: the gradient of xsum when xsum also feeds a residual branch.
+extern "C" int ua_rmsnorm_bwd_res(const void* x, const void* w, const void* g, const float* rstd,
+                                  const void* dres, void* dx, float* dw, int rows, int H,
+                                  cudaStream_t stream) {
+  return rmsnorm_bwd_launch(x, w, g, rstd, dres, dx, dw, rows, H, stream);
 }
 
 extern "C" int ua_rope(const void* x, void* y, const float* cos_t, const float* sin_t,

@@ -482,6 +482,12 @@ static int launch_gemm(const GemmParams& p, int grid, cudaStream_t stream) {
 
 
 static int g_pair_smem_set[64] = {0};
+static int g_pair_mode = 0;      // 0: single-CTA tiles, 1: CTA pairs (set before a launch by ua_gemm_pair_mode)
+
+// Which form the following ua_gemm_bf16 calls of this process use: 0 = one CTA per tile, 1 = a pair
+// of CTAs per 256 x 256 tile. Neither is faster for every shape (measured on Llama-2-7B shapes at
+// 64k tokens: pairs win the 12288-wide QKV projection, single CTAs the others).
+extern "C" void ua_gemm_pair_mode(int mode) { g_pair_mode = mode; }
 
 static int launch_gemm_pair(const GemmParams& p, int num_sms, cudaStream_t stream) {
   const int smem_bytes = sizeof(PairSmem) + 1024;
@@ -526,9 +532,9 @@ extern "C" int ua_gemm_bf16(const void* const* a_ptrs, int n_src, long a_rows_to
   // tile height: 256 rows when that still leaves at least four waves of tiles (UA_GEMM_MH forces)
   int mh = (static_cast<long>((M + 255) / 256) * ((N + GEMM_BN - 1) / GEMM_BN) >= 4L * num_sms) ? 2 : 1;
   if (const char* e = getenv("UA_GEMM_MH")) mh = atoi(e) == 2 ? 2 : 1;
-  // CTA pairs (256 x 256 tile over two SMs) when there are at least two waves of such tiles for
-  // the 74 pairs; UA_GEMM_PAIR=0 / 1 forces the choice
-  bool pair = static_cast<long>((M + 255) / 256) * ((N + GEMM_BN - 1) / GEMM_BN) >= static_cast<long>(num_sms);
+  // CTA pairs (256 x 256 tile over two SMs): chosen per call by ua_gemm_pair_mode (the Python
+  // wrapper times both forms once per shape and keeps the faster), or forced by UA_GEMM_PAIR=0 / 1
+  bool pair = g_pair_mode > 0;
   if (const char* e = getenv("UA_GEMM_PAIR")) pair = atoi(e) != 0;
   if (pair) mh = 1;        // per-CTA boxes of the pair kernel are those of the 128-row kernel
   for (int i = 0; i < n_src; ++i) {

@@ -25,6 +25,16 @@ inline char* err_buf() {
     if (_e != cudaSuccess) UA_FAIL("%s failed: %s", #expr, cudaGetErrorString(_e));     \
   } while (0)
 
+// Trace buffers registered by ua_set_kernel_trace: [0 = forward, 1 = backward][device].
+struct TraceSlot {
+  unsigned long long* buf;
+  int cap;
+};
+inline TraceSlot* trace_registry() {
+  static TraceSlot slots[2][64] = {};
+  return &slots[0][0];
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,

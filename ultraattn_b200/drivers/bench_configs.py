@@ -162,9 +162,11 @@ def main() -> None:
                 A.check_status(dev)
                 phases = None
                 if a.trace and world > 1 and path == "fused":
-                    rt.impl.enable_trace()
+                    rt.impl.enable_trace(kernels=True)
                     step()
-                    ph = rt.impl.metrics()["phases_ms"]
+                    met = rt.impl.metrics()
+                    ph = met["phases_ms"]
+                    kernels_rank0 = met.get("kernels")
                     rt.impl.enable_trace(False)
                     names = sorted(ph)
                     t = torch.tensor([ph[n] for n in names], device=dev)
@@ -181,7 +183,8 @@ def main() -> None:
                                       "roofline_bound": "compute" if t_comp >= t_link else "nvlink",
                                       "fraction_of_roofline": round(max(t_comp, t_link) * 1e3 / ms, 3),
                                       "peak_tflops_of_measured": peak,
-                                      **({"phases_ms_min_max_over_ranks": phases} if phases else {})}), flush=True)
+                                      **({"phases_ms_min_max_over_ranks": phases,
+                                          "kernel_trace_rank0": kernels_rank0} if phases else {})}), flush=True)
                     if metrics is not None:
                         metrics.log(name, ms * 1e-3, flops_per_gpu=flops / world, pull_bytes=int(nvl_bytes),
                                     path=path if world > 1 else "local", n_gpus=world, S=S)

@@ -179,6 +179,36 @@ def _profile_memory_bound_ops(rows: int, iters: int) -> None:
         print(json.dumps(rec))
 
 
+def _profile_gemm_shapes(iters: int = 20) -> None:
+    """The GEMM kernel on the projection / FFN shapes of Llama-2-7B at 64k tokens per GPU (and
+    8192^3), single-CTA tiles and CTA pairs, next to the library GEMM PyTorch calls (cuBLAS) on
+    the same tensors; one JSON line per shape."""
+    import os
+    from ..ops import gemm as G
+    dev = torch.device("cuda")
+    for (M, N, K) in [(8192, 8192, 8192), (65536, 4096, 4096), (65536, 12288, 4096), (65536, 22016, 4096),
+                      (65536, 4096, 11008)]:
+        a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        fl = 2.0 * M * N * K
+        rec = {"op": "gemm", "M": M, "N": N, "K": K}
+        saved = os.environ.get("UA_GEMM_PAIR")
+        for pair in ("0", "1"):
+            os.environ["UA_GEMM_PAIR"] = pair
+            t = _time(lambda: G.gemm(a, b, out=out), iters, 3)
+            rec["single_cta_tflops" if pair == "0" else "cta_pair_tflops"] = round(fl / t / 1e12, 1)
+        if saved is None:
+            del os.environ["UA_GEMM_PAIR"]
+        else:
+            os.environ["UA_GEMM_PAIR"] = saved
+        t = _time(lambda: G.gemm(a, b, out=out), iters, 3)
+        rec["default_tflops"] = round(fl / t / 1e12, 1)
+        t = _time(lambda: torch.matmul(a, b.t(), out=out), iters, 3)
+        rec["library_tflops"] = round(fl / t / 1e12, 1)
+        print(json.dumps(rec), flush=True)
+
+
 def _profile_mma_rate(iters: int = 200) -> None:
     """Clocks per ``tcgen05.mma`` (M = 128, K = 16, bf16) for N = 64 / 128 / 256, operands from
     shared memory (SS) or A from tensor memory (TS), four ways of issuing; one JSON line each."""
@@ -207,7 +237,7 @@ def main() -> None:
     ap.add_argument("--out", default="logs/m_configs")
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--max-seconds", type=float, default=0.0, help="(--kernels) stop the sweep after this long")
-    ap.add_argument("--one", choices=["fwd", "bwd", "gemm", "ops", "gate", "mma_rate"], default=None)
+    ap.add_argument("--one", choices=["fwd", "bwd", "gemm", "gemm_shapes", "ops", "gate", "mma_rate"], default=None)
     ap.add_argument("--S", type=int, default=16384)
     ap.add_argument("--Nh", type=int, default=32)
     ap.add_argument("--causal", action="store_true")
@@ -218,6 +248,9 @@ def main() -> None:
         return
     if a.one == "mma_rate":
         _profile_mma_rate()
+        return
+    if a.one == "gemm_shapes":
+        _profile_gemm_shapes(a.iters)
         return
     if a.one == "gate":
         # small tiles with and without the start gate: what the host launch path adds to a timing

@@ -88,6 +88,23 @@ class _RMSNorm(torch.autograd.Function):
         return dx, dw.to(w.dtype), None
 
 
+class _AddRMSNorm(torch.autograd.Function):
+    """(x, a) -> (x + a, RMSNorm(x + a) * w) in one kernel; in the backward the gradient that
+    reaches x + a through the residual branch is added inside the norm's backward kernel."""
+
+    @staticmethod
+    def forward(ctx, x, a, w, eps):
+        xsum, y, rstd = E.add_rmsnorm_fwd(x, a.contiguous(), w, eps)
+        ctx.save_for_backward(xsum, w, rstd)
+        return xsum, y
+
+    @staticmethod
+    def backward(ctx, dxsum, dy):
+        xsum, w, rstd = ctx.saved_tensors
+        dx, dw = E.rmsnorm_bwd(xsum, w, dy.contiguous(), rstd, dres=dxsum.contiguous())
+        return dx, dx, dw.to(w.dtype), None
+
+
 class _Rope(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, cos, sin, pos):
@@ -98,6 +115,37 @@ class _Rope(torch.autograd.Function):
     def backward(ctx, g):
         cos, sin, pos = ctx.saved_tensors
         return E.rope(g.contiguous(), cos, sin, pos, inverse=True), None, None, None
+
+
+class _QkvRope(torch.autograd.Function):
+    """qkv [T, (H + 2 Hk) * 128] -> q [T, H, 128], k [T, Hk, 128] with rotary embedding applied and
+    v [T, Hk, 128]. The split is done by the RoPE kernel itself: it reads the q and k column
+    ranges of the projection's output through strided views (no copies, v stays a view), and in
+    the backward the inverse rotation writes dq and dk straight into their column ranges of one
+    dqkv buffer, next to a single copy of dv."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, pos, n_heads, n_kv_heads):
+        T, D = qkv.shape[0], 128
+        nq, nk = n_heads * D, n_kv_heads * D
+        ctx.save_for_backward(cos, sin, pos)
+        ctx.dims = (T, n_heads, n_kv_heads, qkv.dtype)
+        q = E.rope(qkv[:, :nq].unflatten(1, (n_heads, D)), cos, sin, pos)
+        k = E.rope(qkv[:, nq:nq + nk].unflatten(1, (n_kv_heads, D)), cos, sin, pos)
+        v = qkv[:, nq + nk:].unflatten(1, (n_kv_heads, D))
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        cos, sin, pos = ctx.saved_tensors
+        T, H, Hk, dtype = ctx.dims
+        D = 128
+        nq, nk = H * D, Hk * D
+        dqkv = torch.empty(T, nq + 2 * nk, dtype=dtype, device=dq.device)
+        E.rope(dq.contiguous(), cos, sin, pos, inverse=True, out=dqkv[:, :nq].unflatten(1, (H, D)))
+        E.rope(dk.contiguous(), cos, sin, pos, inverse=True, out=dqkv[:, nq:nq + nk].unflatten(1, (Hk, D)))
+        dqkv[:, nq + nk:].unflatten(1, (Hk, D)).copy_(dv)
+        return dqkv, None, None, None, None, None
 
 
 class _Swiglu(torch.autograd.Function):
@@ -139,7 +187,7 @@ class _Layer(torch.autograd.Function):
                 h = _RMSNorm.apply(x, p[f"l{li}.norm1"], c.eps)
                 cos, sin = model._tables(model.ulysses.S)
                 a, o, lse = model.ulysses.forward(h, p[f"l{li}.wqkv"], p[f"l{li}.wo"], cos, sin, return_state=True)
-                y = model._seg_ffn(x + a, li)
+                y = model._seg_ffn(x, li, a)
             ctx.offloaded = None
             ctx.save_for_backward(x, o, lse)
             return y
@@ -174,7 +222,7 @@ class _Layer(torch.autograd.Function):
                     a = ul.recompute_out(o, wo)                              # projection only, attention is NOT recomputed
                 a2 = a.requires_grad_()
                 x2 = x.detach().requires_grad_()
-                y = model._seg_ffn(x2 + a2, li)
+                y = model._seg_ffn(x2, li, a2)
                 torch.autograd.backward([y], [dy])
                 with torch.no_grad():
                     dh, dwqkv, dwo = ul.backward(a2.grad, h.detach(), wqkv, wo, o, lse, cos, sin, attn_in_place=True)
@@ -329,6 +377,10 @@ class LlamaModel:
         qkv = _Linear.apply(h, p[f"l{li}.wqkv"])
         T = x.shape[0]
         nq, nk = c.n_heads * c.head_dim, c.kv_heads * c.head_dim
+        if qkv.is_cuda and c.head_dim == 128:
+            cos, sin = self._tables(self._n_pos)
+            q, k, v = _QkvRope.apply(qkv, cos, sin, self._pos, c.n_heads, c.kv_heads)
+            return q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)
         q = qkv[:, :nq].reshape(T, c.n_heads, c.head_dim)
         k = qkv[:, nq:nq + nk].reshape(T, c.kv_heads, c.head_dim)
         v = qkv[:, nq + nk:].reshape(T, c.kv_heads, c.head_dim)
@@ -340,18 +392,24 @@ class LlamaModel:
     def _seg_out(self, x, o, li):
         c, p = self.cfg, self.p
         a = _Linear.apply(o.reshape(x.shape[0], c.n_heads * c.head_dim), p[f"l{li}.wo"])
-        return self._seg_ffn(x + a, li)
+        return self._seg_ffn(x, li, a)
 
-    def _seg_ffn(self, x, li):
-        """Second half of a layer: x + W_down(SwiGLU(W_gate,up(RMSNorm(x))))."""
+    def _seg_ffn(self, x, li, a=None):
+        """Second half of a layer on x (+ a, the attention block's output, added inside the norm
+        kernel): x' + W_down(SwiGLU(W_gate,up(RMSNorm(x')))) with x' = x + a."""
         c, p = self.cfg, self.p
-        h = _RMSNorm.apply(x, p[f"l{li}.norm2"], c.eps)
+        if a is not None:
+            x, h = _AddRMSNorm.apply(x, a, p[f"l{li}.norm2"], c.eps)
+        else:
+            h = _RMSNorm.apply(x, p[f"l{li}.norm2"], c.eps)
         gu = _Linear.apply(h, p[f"l{li}.wgu"])
         return x + _Linear.apply(_Swiglu.apply(gu), p[f"l{li}.wdown"])
 
     def _attn_fwd(self, q, k, v):
         if self.runtime is not None:
-            return self.runtime.forward(q.contiguous(), k.contiguous(), v.contiguous())
+            # the fused runtime copies into its symmetric buffers anyway (strided views are fine)
+            c = (lambda t: t) if getattr(self.runtime, "path", "") == "fused" else (lambda t: t.contiguous())
+            return self.runtime.forward(c(q), c(k), c(v))
         from ..ops import attention as A
         fplan, _ = api.local_plans(self.pattern, q.shape[1], q.device)
         o = torch.empty_like(q)
@@ -361,7 +419,8 @@ class LlamaModel:
 
     def _attn_bwd(self, d_o, q, k, v, o, lse):
         if self.runtime is not None:
-            return self.runtime.backward(d_o.contiguous(), q.contiguous(), k.contiguous(), v.contiguous(), o, lse)
+            c = (lambda t: t) if getattr(self.runtime, "path", "") == "fused" else (lambda t: t.contiguous())
+            return self.runtime.backward(d_o.contiguous(), c(q), c(k), c(v), o, lse)
         _, bplan = api.local_plans(self.pattern, q.shape[1], q.device)
         return api.local_backward(q, k, v, o, lse, d_o.contiguous(), bplan)
 

@@ -88,6 +88,7 @@ class StagePlan:
     n_copy_ctas: int
     flags: torch.Tensor
     epoch: int = 1
+    ticket: torch.Tensor | None = None      # one uint32: next unclaimed task of a launch (the launcher zeroes it)
 
 
 def _seg_tiles(seg: Seg, r0: int, rows_here: int) -> int:
@@ -131,6 +132,83 @@ class FwdPlan:
         self.tiles_t = torch.from_numpy(tile_arr).to(self.device)
 
 
+# ---------------------------------------------------------------------------------------------
+# Debug mode: bounds of the launch tables. The kernels are table driven: every address they form
+# is (source slot, first token, length) from a Row / Col / Seg, so checking the tables against the
+# tensors actually passed covers every index the device code will compute. ``UA_DEBUG_BOUNDS=1``
+# runs the check before every launch (also on the CPU restatements); it costs host time only.
+# ---------------------------------------------------------------------------------------------
+def debug_bounds_enabled() -> bool:
+    import os
+    return os.environ.get("UA_DEBUG_BOUNDS") == "1"
+
+
+def check_fwd_tables(rows: Sequence["Row"], q_srcs, k_srcs, v_srcs, outs, stage=None) -> list:
+    """Problems (strings) in a forward launch's tables; empty = every access is in range."""
+    bad = []
+    for i, r in enumerate(rows):
+        if not 0 <= r.q_src < len(q_srcs):
+            bad.append(f"row {i}: query slot {r.q_src} of {len(q_srcs)}")
+            continue
+        if r.q_start < 0 or r.q_len <= 0 or r.q_start + r.q_len > q_srcs[r.q_src].shape[1]:
+            bad.append(f"row {i}: queries {r.q_start}+{r.q_len} exceed {q_srcs[r.q_src].shape[1]} tokens of slot {r.q_src}")
+        if not 0 <= r.o_slot < len(outs):
+            bad.append(f"row {i}: output slot {r.o_slot} of {len(outs)}")
+        else:
+            o, lse = outs[r.o_slot]
+            if r.o_start < 0 or r.o_start + r.q_len > o.shape[1] or r.o_start + r.q_len > lse.shape[2]:
+                bad.append(f"row {i}: output rows {r.o_start}+{r.q_len} exceed slot {r.o_slot} ({o.shape[1]} rows)")
+        if stage is not None and r.q_wait_flag and not 0 < r.q_wait_flag <= stage.flags.numel():
+            bad.append(f"row {i}: wait flag {r.q_wait_flag} outside {stage.flags.numel()} counters")
+        for jx, sg in enumerate(r.segs):
+            if not 0 <= sg.src < len(k_srcs):
+                bad.append(f"row {i} segment {jx}: key slot {sg.src} of {len(k_srcs)}")
+                continue
+            for name, t in (("keys", k_srcs[sg.src]), ("values", v_srcs[sg.src])):
+                if sg.start < 0 or sg.length <= 0 or sg.start + sg.length > t.shape[1]:
+                    bad.append(f"row {i} segment {jx}: {name} {sg.start}+{sg.length} exceed {t.shape[1]} tokens of slot {sg.src}")
+            if stage is not None and sg.wait_flag and not 0 < sg.wait_flag <= stage.flags.numel():
+                bad.append(f"row {i} segment {jx}: wait flag {sg.wait_flag} outside {stage.flags.numel()} counters")
+    return bad
+
+
+def check_bwd_tables(cols: Sequence["Col"], q_sides, k_srcs, v_srcs, kv_outs, stage=None) -> list:
+    """Problems (strings) in a backward launch's tables; empty = every access is in range."""
+    bad = []
+    for i, c in enumerate(cols):
+        if not 0 <= c.kv_src < len(k_srcs):
+            bad.append(f"column {i}: key slot {c.kv_src} of {len(k_srcs)}")
+            continue
+        if c.kv_start < 0 or c.kv_len <= 0 or c.kv_start + c.kv_len > k_srcs[c.kv_src].shape[1] \
+                or c.kv_start + c.kv_len > v_srcs[c.kv_src].shape[1]:
+            bad.append(f"column {i}: keys {c.kv_start}+{c.kv_len} exceed slot {c.kv_src}")
+        if not 0 <= c.g_slot < len(kv_outs):
+            bad.append(f"column {i}: gradient slot {c.g_slot} of {len(kv_outs)}")
+        elif c.g_start < 0 or c.g_start + c.kv_len > kv_outs[c.g_slot].dk.shape[1]:
+            bad.append(f"column {i}: gradient rows {c.g_start}+{c.kv_len} exceed slot {c.g_slot} "
+                       f"({kv_outs[c.g_slot].dk.shape[1]} rows)")
+        if stage is not None and c.kv_wait_flag and not 0 < c.kv_wait_flag <= stage.flags.numel():
+            bad.append(f"column {i}: wait flag {c.kv_wait_flag} outside {stage.flags.numel()} counters")
+        for jx, sg in enumerate(c.segs):
+            if not 0 <= sg.src < len(q_sides):
+                bad.append(f"column {i} segment {jx}: query slot {sg.src} of {len(q_sides)}")
+                continue
+            side = q_sides[sg.src]
+            for name, n in (("q", side.q.shape[1]), ("dO", side.d_o.shape[1]), ("lse", side.lse.shape[2]),
+                            ("D", side.dvec.shape[2]), ("dQ", side.dq.shape[1])):
+                if sg.start < 0 or sg.length <= 0 or sg.start + sg.length > n:
+                    bad.append(f"column {i} segment {jx}: {name} rows {sg.start}+{sg.length} exceed {n} of slot {sg.src}")
+            if stage is not None and sg.wait_flag and not 0 < sg.wait_flag <= stage.flags.numel():
+                bad.append(f"column {i} segment {jx}: wait flag {sg.wait_flag} outside {stage.flags.numel()} counters")
+    return bad
+
+
+def _raise_if_bad(kind: str, problems: list) -> None:
+    if problems:
+        raise IndexError(f"{kind} launch tables address memory out of range: " + "; ".join(problems[:8])
+                         + (f" (+{len(problems) - 8} more)" if len(problems) > 8 else ""))
+
+
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -149,6 +227,50 @@ def check_status(device: torch.device | None = None) -> None:
     if st[0] != 0:
         status_buffer(device).zero_()
         raise RuntimeError(f"ultraattn kernel error code={st[0]} where={st[1]} block={st[2]} extra={st[3]}")
+
+
+# ---------------------------------------------------------------------------------------------
+# Per-CTA time stamps of the attention launches (normal build; see csrc/attn_common.cuh KernelTrace)
+# ---------------------------------------------------------------------------------------------
+_traces: dict = {}
+
+
+def enable_kernel_trace(device: torch.device, max_ctas: int = 1 << 18) -> None:
+    """From now on every forward / backward launch on ``device`` records, for each of its first
+    ``max_ctas`` CTAs: start, end of its staging copies, end (``globaltimer`` ns), SM id and work
+    item. A launch overwrites the record of the previous launch of the same kernel."""
+    import ctypes
+    lib = _lib.load()
+    lib.ua_set_kernel_trace.restype = ctypes.c_int
+    lib.ua_set_kernel_trace.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(idx):
+        for which in (0, 1):
+            buf = torch.zeros(max_ctas, 4, dtype=torch.int64, device=torch.device("cuda", idx))
+            _traces[(idx, which)] = buf
+            if lib.ua_set_kernel_trace(which, buf.data_ptr(), max_ctas) != 0:
+                raise RuntimeError(lib.ua_last_error().decode())
+
+
+def disable_kernel_trace(device: torch.device) -> None:
+    lib = _lib.load()
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(idx):
+        for which in (0, 1):
+            if _traces.pop((idx, which), None) is not None:
+                lib.ua_set_kernel_trace(which, None, 0)
+
+
+def read_kernel_trace(device: torch.device, kernel: str = "fwd") -> "np.ndarray":
+    """int64 [n_ctas, 4] of the last ``kernel`` ("fwd" / "bwd") launch: start, staged, end, (sm << 32 | item);
+    rows of CTAs that did not run are zero and dropped. Synchronises the device."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _traces[(idx, 0 if kernel == "fwd" else 1)]
+    torch.cuda.synchronize(idx)
+    arr = buf.cpu().numpy()
+    out = arr[arr[:, 0] != 0].copy()
+    buf.zero_()
+    return out
 
 
 def _src_struct(t: torch.Tensor) -> _lib.UaTensorSrc:
@@ -191,9 +313,11 @@ def attn_fwd_cuda(q_srcs: Sequence[torch.Tensor], k_srcs: Sequence[torch.Tensor]
 
 def _stage_args(stage):
     if stage is None:
-        return (None, 0, 0, None, 1)
+        return (None, 0, 0, None, 1, None)
+    if stage.ticket is None:
+        stage.ticket = torch.zeros(1, dtype=torch.int32, device=stage.flags.device)
     return (stage.tasks.data_ptr() if stage.n_tasks else None, stage.n_tasks, stage.n_copy_ctas,
-            stage.flags.data_ptr(), stage.epoch)
+            stage.flags.data_ptr(), stage.epoch, stage.ticket.data_ptr())
 
 
 def _mask_for(seg: Seg, q_len: int, device) -> torch.Tensor | None:
@@ -254,6 +378,8 @@ def attn_fwd_reference(q_srcs, k_srcs, v_srcs, outs, rows: Sequence[Row],
 def attn_fwd(q_srcs, k_srcs, v_srcs, outs, plan: FwdPlan, softmax_scale=None, stage=None) -> None:
     """Dispatch on the device of the inputs: CUDA tensors run the sm_100a kernel, CPU tensors the
     fp32 restatement (which expects staged data to be in place already)."""
+    if debug_bounds_enabled():
+        _raise_if_bad("forward", check_fwd_tables(plan.rows, q_srcs, k_srcs, v_srcs, outs, stage))
     if q_srcs[0].is_cuda:
         attn_fwd_cuda(q_srcs, k_srcs, v_srcs, outs, plan, softmax_scale, stage)
     else:
@@ -430,6 +556,8 @@ def attn_bwd_reference(q_sides: Sequence[BwdQSide], k_srcs, v_srcs, kv_outs: Seq
 
 
 def attn_bwd(q_sides, k_srcs, v_srcs, kv_outs, plan: BwdPlan, softmax_scale=None, stage=None) -> None:
+    if debug_bounds_enabled():
+        _raise_if_bad("backward", check_bwd_tables(plan.cols, q_sides, k_srcs, v_srcs, kv_outs, stage))
     if q_sides[0].q.is_cuda:
         attn_bwd_cuda(q_sides, k_srcs, v_srcs, kv_outs, plan, softmax_scale, stage)
     else:

@@ -95,20 +95,42 @@ def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5):
     return y, rstd
 
 
-def rmsnorm_bwd(x, w, g, rstd):
-    """-> (dx [rows, H] like x, dw fp32 [H])."""
+def add_rmsnorm_fwd(x: torch.Tensor, res: torch.Tensor, w: torch.Tensor, eps: float = 1e-5):
+    """xsum = x + res and y = RMSNorm(xsum) * w in one pass -> (xsum, y, rstd)."""
+    rows, H = x.shape
+    if not x.is_cuda:
+        xsum = (x.float() + res.float()).to(x.dtype)
+        y, rstd = rmsnorm_fwd(xsum, w, eps)
+        return xsum, y, rstd
+    xsum, y = torch.empty_like(x), torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rc = _lib.load().ua_add_rmsnorm_fwd(x.data_ptr(), res.data_ptr(), w.data_ptr(), xsum.data_ptr(),
+                                        y.data_ptr(), rstd.data_ptr(), rows, H, eps, _stream(x))
+    _lib.check(rc, "ua_add_rmsnorm_fwd")
+    return xsum, y, rstd
+
+
+def rmsnorm_bwd(x, w, g, rstd, dres=None):
+    """-> (dx [rows, H] like x, dw fp32 [H]). ``dres``: a gradient added to dx in the same pass
+    (what reaches x through a residual branch next to the norm)."""
     rows, H = x.shape
     if not x.is_cuda:
         xf, gf, wf = x.float(), g.float(), w.float()
         gw = gf * wf
         c = (gw * xf).sum(-1, keepdim=True) * (rstd[:, None] ** 2) / H
         dx = rstd[:, None] * (gw - xf * c)
+        if dres is not None:
+            dx = dx + dres.float()
         dw = (gf * xf * rstd[:, None]).sum(0)
         return dx.to(x.dtype), dw
     dx = torch.empty_like(x)
     dw = torch.zeros(H, dtype=torch.float32, device=x.device)
-    rc = _lib.load().ua_rmsnorm_bwd(x.data_ptr(), w.data_ptr(), g.data_ptr(), rstd.data_ptr(),
-                                    dx.data_ptr(), dw.data_ptr(), rows, H, _stream(x))
+    if dres is None:
+        rc = _lib.load().ua_rmsnorm_bwd(x.data_ptr(), w.data_ptr(), g.data_ptr(), rstd.data_ptr(),
+                                        dx.data_ptr(), dw.data_ptr(), rows, H, _stream(x))
+    else:
+        rc = _lib.load().ua_rmsnorm_bwd_res(x.data_ptr(), w.data_ptr(), g.data_ptr(), rstd.data_ptr(),
+                                            dres.data_ptr(), dx.data_ptr(), dw.data_ptr(), rows, H, _stream(x))
     _lib.check(rc, "ua_rmsnorm_bwd")
     return dx, dw
 

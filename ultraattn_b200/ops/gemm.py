@@ -16,6 +16,9 @@ from .. import _lib
 from .attention import status_buffer
 
 _sm_count: dict[int, int] = {}
+# (M, N, K, a_is_km, b_is_kn) -> 1 if the CTA-pair form of the kernel was faster when first timed
+_pair_choice: dict[tuple, int] = {}
+_TUNE_MIN_FLOPS = 2.0 * 4096 * 4096 * 4096       # below this a launch is too short for the choice to matter
 
 
 def _sms(device: torch.device) -> int:
@@ -57,12 +60,41 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_is_km: bool = False, b_is_kn: bo
     lib = _lib.load()
     a_ptrs = (ctypes.c_void_p * 1)(a.data_ptr())
     c_ptrs = (ctypes.c_void_p * 1)(out.data_ptr())
-    rc = lib.ua_gemm_bf16(a_ptrs, 1, a.shape[0], a.stride(0), 0, int(a_is_km), b.data_ptr(),
-                          b.stride(0), int(b_is_kn), c_ptrs, 1, out.stride(0), 0, M, N, K,
-                          status_buffer(a.device).data_ptr(), _sms(a.device),
-                          torch.cuda.current_stream(a.device).cuda_stream)
-    _lib.check(rc, "ua_gemm_bf16")
+
+    def launch():
+        rc = lib.ua_gemm_bf16(a_ptrs, 1, a.shape[0], a.stride(0), 0, int(a_is_km), b.data_ptr(),
+                              b.stride(0), int(b_is_kn), c_ptrs, 1, out.stride(0), 0, M, N, K,
+                              status_buffer(a.device).data_ptr(), _sms(a.device),
+                              torch.cuda.current_stream(a.device).cuda_stream)
+        _lib.check(rc, "ua_gemm_bf16")
+
+    lib.ua_gemm_pair_mode(_pick_form(lib, (M, N, K, bool(a_is_km), bool(b_is_kn)), launch, a.device))
+    launch()
     return out
+
+
+def _pick_form(lib, key: tuple, launch, device) -> int:
+    """0 = one CTA per output tile, 1 = a pair of CTAs per 256 x 256 tile. The first large call of
+    a shape times both forms (three launches each, CUDA events) and the choice is kept; nothing is
+    timed while a CUDA graph is being captured."""
+    if key in _pair_choice:
+        return _pair_choice[key]
+    M, N, K = key[:3]
+    if 2.0 * M * N * K < _TUNE_MIN_FLOPS or torch.cuda.is_current_stream_capturing():
+        return 0
+    times = []
+    for mode in (0, 1):
+        lib.ua_gemm_pair_mode(mode)
+        launch()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            launch()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    _pair_choice[key] = int(times[1] < 0.97 * times[0])
+    return _pair_choice[key]
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -84,6 +116,7 @@ def gemm_scatter(a: torch.Tensor, b: torch.Tensor, dst_ptrs: Sequence[int], ldc:
     lib = _lib.load()
     a_ptrs = (ctypes.c_void_p * 1)(a.data_ptr())
     c_ptrs = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    lib.ua_gemm_pair_mode(0)
     rc = lib.ua_gemm_bf16(a_ptrs, 1, M, a.stride(0), 0, 0, b.data_ptr(), b.stride(0), int(b_is_kn), c_ptrs,
                           len(dst_ptrs), ldc, dst_row_off, M, N, K,
                           status_buffer(a.device).data_ptr(), _sms(a.device),
@@ -102,6 +135,7 @@ def gemm_gather(src_ptrs: Sequence[int], src_rows_total: int, lda: int, a_row_of
     lib = _lib.load()
     a_ptrs = (ctypes.c_void_p * len(src_ptrs))(*src_ptrs)
     c_ptrs = (ctypes.c_void_p * 1)(out.data_ptr())
+    lib.ua_gemm_pair_mode(0)
     rc = lib.ua_gemm_bf16(a_ptrs, len(src_ptrs), src_rows_total, lda, a_row_off, 0, b.data_ptr(),
                           b.stride(0), int(b_is_kn), c_ptrs, 1, out.stride(0), 0, M, N, K,
                           status_buffer(out.device).data_ptr(), _sms(out.device),

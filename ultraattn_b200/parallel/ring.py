@@ -180,7 +180,13 @@ def ring_forward(q, k, v, group, kind: str, causal: bool, softmax_scale=None, bo
     ``bounds``: (start, end) of every packed sequence in this rank's shard; default one sequence.
     ``q_rank``: ring position of the rank that owns the queries, when they are a visitor's.
     ``block_types``: a block table (pattern refined to a multiple of the ring size) that replaces
-    the dense rule of ``kind``: the ring baseline for block-sparse patterns."""
+    the dense rule of ``kind``: the ring baseline for block-sparse patterns.
+
+    Accuracy: the running output is held in the input dtype and every ring step's kernel epilogue
+    merges into it (log-sum-exp weights in fp32, one rounding to the input dtype per step), so a
+    bf16 result carries up to ``world`` roundings of 2^-9 relative each instead of one; the
+    reference keeps out / lse in fp32 across steps and casts once
+    (ring_flash_attn/utils.py:38-52). lse itself is fp32 throughout."""
     set_comm_phase("fwd")
     route = _route(group)
     q_rank = route.rank if q_rank is None else q_rank

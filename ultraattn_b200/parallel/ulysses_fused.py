@@ -265,12 +265,14 @@ class _AllToAll(torch.autograd.Function):
     @staticmethod
     def forward(ctx, t, group):
         ctx.group = group
+        t = t.contiguous()
         out = torch.empty_like(t)
-        dist.all_to_all_single(out, t.contiguous(), group=group)
+        dist.all_to_all_single(out, t, group=group)
         return out
 
     @staticmethod
     def backward(ctx, g):
+        g = g.contiguous()
         out = torch.empty_like(g)
-        dist.all_to_all_single(out, g.contiguous(), group=ctx.group)
+        dist.all_to_all_single(out, g, group=ctx.group)
         return out, None

@@ -243,6 +243,86 @@ def solve_sparse_from_bsa(bsa_config: BSA_Config, fob: int = 0, ParD: Optional[i
     if cp == 1:
         table = np.where(vol > 0, 0, EMPTY_TILE)
         return Allocation(par_d, cm, table, 0.0, float(vol.sum()), "optimal")
+    key = None
+    if use_ilp and objective == "comm" and hierarchy == 1:
+        key = allocation_cache_key(bsa_config, fob, cp, par_d, cm)
+        hit = _cache_lookup(key, par_d, cp, vol)
+        if hit is not None:
+            table = hit
+            cin, cout = comm_volumes(table, cm, cp, fob)
+            return Allocation(par_d, cm, table, float(max(cin.max(), cout.max())),
+                              float(comp_volumes(table, vol, cp).max()), "cached")
+    alloc = _solve_uncached(bsa_config, fob, par_d, cp, cm, vol, objective, t_comp, t_comm, time_limit, backend,
+                            max_slack_steps, use_ilp, heuristic_iters)
+    if key is not None:
+        _cache_store(key, alloc)
+    return alloc
+
+
+# ---------------------------------------------------------------------------------------------
+# Cached answers. The reference keeps the results of this program in
+# ``{intra,inter}_bsa_allocation.json`` of its plan database ("Bypassed !!!",
+# search_algo/task1_bsa.py:106-143) and as literal tables (search_algo/manual_schedules.py:36-597).
+# Here: a read-only file shipped with the package (the named benchmark patterns on 2 / 4 / 8 ranks,
+# solved with a long time limit) plus an optional writable directory ``UA_PLAN_CACHE``. A cached
+# table is only used if it is a valid allocation of the present pattern. ``UA_PLAN_CACHE=0``
+# switches both off.
+# ---------------------------------------------------------------------------------------------
+_SHIPPED = None
+
+
+def allocation_cache_key(bsa_config: BSA_Config, fob: int, cp: int, par_d: int, cmap: np.ndarray) -> str:
+    contiguous = np.array_equal(cmap, np.arange(par_d) // (par_d // cp))
+    cm = "contiguous" if contiguous else "-".join(str(int(x)) for x in cmap)
+    return f"fob={int(fob)}_CP={cp}_ParD={par_d}_cmap={cm}_repr={bsa_config.bsa_repr}"
+
+
+def _cache_files():
+    import os
+    from pathlib import Path
+    env = os.environ.get("UA_PLAN_CACHE")
+    if env == "0":
+        return None, None
+    shipped = Path(__file__).resolve().parents[1] / "data" / "allocations.json"
+    user = Path(env) / "allocations.json" if env else None
+    return shipped, user
+
+
+def _cache_lookup(key: str, par_d: int, cp: int, vol: np.ndarray):
+    import json
+    global _SHIPPED
+    shipped, user = _cache_files()
+    if shipped is None:
+        return None
+    if _SHIPPED is None:
+        _SHIPPED = json.loads(shipped.read_text()) if shipped.exists() else {}
+    entry = _SHIPPED.get(key)
+    if entry is None and user is not None and user.exists():
+        entry = json.loads(user.read_text()).get(key)
+    if entry is None:
+        return None
+    table = np.asarray(entry["table"], dtype=np.int64)
+    ok = (table.shape == (par_d, par_d) and ((table >= 0) == (vol > 0)).all() and table.max() < cp)
+    return table if ok else None
+
+
+def _cache_store(key: str, alloc: "Allocation") -> None:
+    import json
+    import os
+    _, user = _cache_files()
+    if user is None:
+        return
+    user.parent.mkdir(parents=True, exist_ok=True)
+    data = json.loads(user.read_text()) if user.exists() else {}
+    data[key] = {"table": np.asarray(alloc.table).tolist(), "comm_volume": alloc.comm_volume,
+                 "comp_max": alloc.comp_max, "status": alloc.status}
+    tmp = user.with_suffix(f".tmp{os.getpid()}")
+    tmp.write_text(json.dumps(data))
+    os.replace(tmp, user)
+
+
+def _solve_uncached(bsa_config, fob, par_d, cp, cm, vol, objective, t_comp, t_comm, time_limit, backend,
+                    max_slack_steps, use_ilp, heuristic_iters) -> Allocation:
 
     diagonal_full = bool((np.diag(vol) > 0).all())
     tiles = [(i, j) for i in range(par_d) for j in range(par_d)

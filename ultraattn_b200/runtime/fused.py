@@ -42,8 +42,9 @@ from ..ops import elementwise as E
 from ..patterns.blocks import BSA_Repr, CAUSAL
 
 CHUNK_BYTES = 1 << 20       # staging granularity: one copy task moves at most this much
-# CTAs that share the staging copies at the start of a launch (UA_COPY_CTAS overrides): all SMs
-# by default; fewer leave SMs free to start on tiles whose inputs are local while the copies run
+# Every CTA that waits for a staged block first helps to empty the launch's queue of copy tasks;
+# in addition the first UA_COPY_CTAS CTAs of the grid help whether they wait or not (all SMs by
+# default; fewer leave SMs free to start on tiles whose inputs are local while the copies run)
 MAX_COPY_CTAS = int(os.environ.get("UA_COPY_CTAS", "148"))
 
 
@@ -279,9 +280,18 @@ class FusedContextParallel:
                                     * 2 * kv_blk * 4 if self.nvls_reduce else 0),
         }
 
-    def enable_trace(self, on: bool = True) -> None:
-        """Record CUDA events around every phase of the following calls (see :meth:`metrics`)."""
+    def enable_trace(self, on: bool = True, kernels: bool = False) -> None:
+        """Record CUDA events around every phase of the following calls (see :meth:`metrics`).
+        ``kernels``: also let the two attention kernels record per-CTA time stamps (start, end of
+        staging, end, SM): :meth:`metrics` then reports, for the last forward and backward launch,
+        how long SMs copied before computing, how busy they were and how long the tail ran."""
         self._trace = [] if on else None
+        self._ktrace = bool(on and kernels and self.cuda)
+        if self.cuda:
+            if self._ktrace:
+                A.enable_kernel_trace(self.device)
+            else:
+                A.disable_kernel_trace(self.device)
 
     def _mark(self, name: str) -> None:
         tr = getattr(self, "_trace", None)
@@ -302,6 +312,9 @@ class FusedContextParallel:
                     continue
                 out["phases_ms"][n1] = out["phases_ms"].get(n1, 0.0) + e0.elapsed_time(e1)
             self._trace = []
+        if getattr(self, "_ktrace", False):
+            from ..utils.kernel_trace import summarize
+            out["kernels"] = {k: summarize(A.read_kernel_trace(self.device, k)) for k in ("fwd", "bwd")}
         return out
 
     # ------------------------------- buffers ----------------------------------------------------
