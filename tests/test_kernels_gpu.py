@@ -193,6 +193,32 @@ def test_attention_accumulate_and_add_modes(dev):
     _close(dv, dv_r, 2e-2)
 
 
+def test_tensor_maps_are_encoded_once_per_buffer(dev):
+    """A repeated launch over the same buffers finds all of its TMA tensor maps in the library's
+    cache; a launch over other buffers of the same shape encodes new ones and computes from them."""
+    from ultraattn_b200.ops import attention as A
+    torch.manual_seed(11)
+    S, H = 512, 2
+    q, k, v = (torch.randn(1, S, H, 128, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    o, lse = torch.zeros_like(q), torch.zeros(1, H, S, device=dev)
+    rows = [A.Row(0, 0, S, (A.Seg(0, 0, S, True, 0),), 0, 0, False)]
+    plan = A.FwdPlan(rows, dev)
+    A.attn_fwd_cuda([q], [k], [v], [(o, lse)], plan)
+    h0, m0 = A.tensor_map_cache_stats()
+    A.attn_fwd_cuda([q], [k], [v], [(o, lse)], plan)
+    h1, m1 = A.tensor_map_cache_stats()
+    assert m1 == m0 and h1 - h0 >= 3
+    k2, v2 = torch.randn_like(k), torch.randn_like(v)
+    o2 = torch.zeros_like(q)
+    A.attn_fwd_cuda([q], [k2], [v2], [(o2, lse)], plan)
+    h2, m2 = A.tensor_map_cache_stats()
+    assert m2 - m1 == 2 and h2 > h1
+    o_ref, lse_ref = torch.zeros(1, S, H, 128, device=dev), torch.zeros(1, H, S, device=dev)
+    A.attn_fwd_reference([q], [k2], [v2], [(o_ref, lse_ref)], rows)
+    A.check_status(dev)
+    _close(o2, o_ref, 1.5e-2)
+
+
 def test_autograd_api(dev):
     import ultraattn_b200 as ua
     from ultraattn_b200 import patterns as P

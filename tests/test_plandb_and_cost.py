@@ -228,6 +228,39 @@ def test_fused_step_time_model():
     assert all(r["link_s"][1] < r["compute_s"][1] for r in ilp["per_rank"])   # compute-bound on NVLink 5
 
 
+def test_fused_transport_profile_feeds_the_model(tmp_path):
+    """A measured transport table in the machine directory replaces the point-to-point curve for
+    the fused runtime's inbound (staging pulls by n CTAs) and outbound (peer red.add) bytes."""
+    import json
+    import shutil
+    from ultraattn_b200.planner.cost import (PACKAGED_M_CONFIG_DIR, Fused_Transport_Profile, Machine_Config,
+                                              fused_step_time)
+    from ultraattn_b200.runtime.context_parallel import plan_allocation
+    recs = [{"transport": "peer_pull", "ranks": 8, "bytes": 1 << 28, "copy_ctas": c, "gbs_per_rank": g}
+            for c, g in ((8, 100.0), (32, 400.0), (148, 700.0))]
+    recs += [{"transport": "peer_red_add_f32", "ranks": 8, "bytes": b, "gbs_per_rank": g}
+             for b, g in ((1 << 22, 200.0), (1 << 28, 600.0))]
+    ft = Fused_Transport_Profile(recs)
+    assert ft.pull_gbs(8) == 100.0 and ft.pull_gbs(20) == 250.0 and ft.pull_gbs(1000) == 700.0
+    assert ft.gbs("peer_red_add_f32", 1 << 25) == 400.0 and ft.gbs("multimem_st_broadcast", 1 << 25) is None
+    assert abs(ft.time_s("peer_pull", 7e9, 8, copy_ctas=148) - 0.01) < 1e-12
+    for f in PACKAGED_M_CONFIG_DIR.glob("*"):
+        if not f.name.startswith("fused_comm_"):
+            shutil.copy(f, tmp_path / f.name)
+    (tmp_path / "fused_comm_test.json").write_text(json.dumps(recs))
+    m = Machine_Config.from_dir(tmp_path)
+    assert len(m.fused_transports.records) == len(recs)
+    pat = P.strided(32, 4, 2)
+    table, cmap = plan_allocation(pat, 8, 1, "ilp", time_limit=5.0)
+    few = fused_step_time(table, cmap, pat, 524288, 32, m_config=m, copy_ctas=8)
+    many = fused_step_time(table, cmap, pat, 524288, 32, m_config=m, copy_ctas=148)
+    r_few, r_many = few["per_rank"][1], many["per_rank"][1]
+    assert r_few["link_s"][0] > 5 * r_many["link_s"][0] > 0          # 100 vs 700 GB/s inbound
+    # staging takes SM time in proportion to the CTAs that copy
+    assert abs(r_many["stage_s"][0] - r_many["link_s"][0]) < 1e-12
+    assert abs(r_few["stage_s"][0] - r_few["link_s"][0] * 8 / 148) < 1e-12
+
+
 def test_ring_time_model_and_predictions():
     """The ring model: contiguous causal shards are bound by the last rank, zigzag is not; a
     block-sparse pattern saves the ring compute but not transfers; the fused runtime is predicted

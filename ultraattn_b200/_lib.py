@@ -52,6 +52,7 @@ def _declare(lib):
                         vp, vp, vp, i, i, i, i, f, vp, vp, i, i, vp, i, vp, vp],
         "ua_barrier": [POINTER(vp), i, i, i, ctypes.c_uint, ctypes.c_double, vp, vp],
         "ua_peer_add_f32": [vp, vp, l, i, i, vp],
+        "ua_peer_pull": [vp, vp, l, i, vp],
         "ua_multimem_bcast": [vp, vp, l, i, vp],
         "ua_multimem_reduce": [vp, vp, vp, l, i, i, vp],
         "ua_wait_flag": [vp, ctypes.c_uint, ctypes.c_double, vp, vp],

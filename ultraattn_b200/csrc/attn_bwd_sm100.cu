@@ -135,12 +135,12 @@ struct __align__(1024) BwdSmem {
   uint64_t do_empty;
   uint64_t s_full;       // S^T ready               (tcgen05.commit)
   uint64_t dp_full;      // dP^T ready              (tcgen05.commit)
-  uint64_t p_ready;      // P^T written to TMEM     (256 softmax threads)
-  uint64_t ds_ready;     // dS^T written to smem    (256 softmax threads)
+  uint64_t p_ready;      // P^T written to TMEM     (8 softmax warps, one arrival each)
+  uint64_t ds_ready;     // dS^T written to smem    (8 softmax warps, one arrival each)
   uint64_t dq_full;      // dQ^T ready              (tcgen05.commit)
-  uint64_t dq_free;      // dQ^T read out of TMEM   (128 drain threads)
+  uint64_t dq_free;      // dQ^T read out of TMEM   (4 drain warps, one arrival each)
   uint64_t dkv_full;
-  uint64_t aug0_ready;   // the first step's row terms are in shared memory (256 softmax threads)
+  uint64_t aug0_ready;   // the first step's row terms are in shared memory (8 softmax warps, one arrival each)
   uint32_t tmem_base;
   int abort_flag;
   int stage_slot;
@@ -276,12 +276,12 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
     mbar_init(&s.do_empty, 1);
     mbar_init(&s.s_full, 1);
     mbar_init(&s.dp_full, 1);
-    mbar_init(&s.p_ready, 256);
-    mbar_init(&s.ds_ready, 256);
+    mbar_init(&s.p_ready, 8);
+    mbar_init(&s.ds_ready, 8);
     mbar_init(&s.dq_full, 1);
-    mbar_init(&s.dq_free, 128);
+    mbar_init(&s.dq_free, 4);
     mbar_init(&s.dkv_full, 1);
-    mbar_init(&s.aug0_ready, 256);
+    mbar_init(&s.aug0_ready, 8);
     s.abort_flag = 0;
     fence_mbar_init();
   }
@@ -551,7 +551,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       ok = fetch(fut, lv, dv);
       if (ok) {
         write_aug(0, lv, dv);
-        mbar_arrive(&s.aug0_ready);
+        mbar_arrive_warp(&s.aug0_ready);
         if (n_steps > 1) {
           fut.next(p, col, c0);
           ok = fetch(fut, lv, dv);
@@ -593,7 +593,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       tmem_st_x32(t_st, pk);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&s.p_ready);
+      mbar_arrive_warp(&s.p_ready);
       BWD_PROF(prof, pslot + 4);
 
       // ---- phase B: dS^T = P^T * (dP^T - D) -> shared memory ------------------------------
@@ -628,7 +628,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
       BWD_PROF(prof, pslot + 9);
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(&s.ds_ready);
+      mbar_arrive_warp(&s.ds_ready);
       BWD_PROF(prof, pslot + 6);
       if (i + 1 < n_steps) cur.next(p, col, c0);
     }
@@ -714,7 +714,7 @@ attn_bwd_kernel(const __grid_constant__ BwdParams p) {
           for (int h = 0; h < 4; ++h) tmem_ld_x32(t_dq + h * 32, dv[h]);
           tmem_wait_ld();
           tc_fence_before_sync();
-          mbar_arrive(&s.dq_free);
+          mbar_arrive_warp(&s.dq_free);
           BWD_PROF(i == BWD_PROF_STEP && quad == 0 && lane == 0, 50);
           if (BWD_DQ_DIRECT) {
             // lane = head-dim element, register = query: the 32 lanes of one instruction cover 128

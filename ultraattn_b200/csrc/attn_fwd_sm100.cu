@@ -13,14 +13,16 @@
 // CTA = 256 query rows x 1 head: two 128-row sub-tiles processed ping-pong so that the tensor
 // core works on one sub-tile while the softmax warps work on the other. TPR = threads per query
 // row (template parameter):
-//   TPR = 1 (320 threads): warps 0-3 softmax / correction / epilogue for sub-tile 0 (one thread per
+//   TPR = 1 (320 threads, default): warps 0-3 softmax / correction / epilogue for sub-tile 0 (one thread per
 //            query row, 128 score columns each), warps 4-7 the same for sub-tile 1
-//   TPR = 2 (640 threads, default): two warpgroups per sub-tile; the two threads of a row take 64
+//   TPR = 2 (640 threads, UA_FWD_TPR=2): two warpgroups per sub-tile; the two threads of a row take 64
 //            score columns each (both can reach the row's TMEM lane), exchange their row maxima
 //            through shared memory once per tile and each keep a partial row sum. The softmax of
 //            a 128 x 128 tile is a chain of dependent latencies (TMEM load, max, exp2, pack, TMEM
-//            store) that one warp per scheduler cannot hide; four warps per scheduler can, which
-//            shortens the softmax phase that the tensor pipe has to wait for.
+//            store) that one warp per scheduler cannot hide; four warps per scheduler can. As
+//            measured (S = 16k, 32 heads) this form is slower than TPR = 1 all the same, 876 against
+//            1192 TFLOP/s: 104 registers per softmax thread leave spills in its inner loop and
+//            the exchange adds a barrier per tile. It is kept as a tested variant.
 //   then one TMA producer warp (Q once, then the K and V rings) and one tcgen05.mma issuer warp
 //   (one elected thread; it also owns the TMEM allocation)
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P (bf16) overwrites the first
@@ -40,6 +42,9 @@ template <int TPR> struct FwdCfg {
   // hosts the same number of warps and the register file can be re-balanced by warpgroup
   static constexpr int THREADS = TPR == 2 ? 640 : 32 * (SOFTMAX_WARPS + 2);
   static constexpr int NC = ATTN_TILE / TPR;      // score columns per thread
+  // register split of the TPR = 2 form (see the role dispatch in the kernel)
+  static constexpr int REGS_LAUNCH = 96, REGS_LOAD = 64, REGS_SOFTMAX = 104;
+  static_assert(4 * REGS_SOFTMAX + REGS_LOAD <= 5 * REGS_LAUNCH, "setmaxnreg may only redistribute the launch-time pool");
 };
 #ifndef UA_FWD_POLY_EXP_PERIOD
 #define UA_FWD_POLY_EXP_PERIOD 0
@@ -98,7 +103,7 @@ struct __align__(1024) FwdSmem {
   int abort_flag;
   int stage_slot;
   float xchg[2][2][ATTN_TILE];    // [sub-tile][column half][row]: row maxima / row sums exchanged between the two threads of a row
-  uint64_t xbar[2];               // the 256 threads of a sub-tile meet here (an mbarrier, so that the wait is bounded)
+  uint64_t xbar[2];               // the 8 warps of a sub-tile meet here (an mbarrier, so that the wait is bounded)
 };
 static_assert(sizeof(FwdSmem) + 1024 <= 232448, "FwdSmem exceeds the 227 KB a CTA may use");
 
@@ -159,8 +164,8 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.q_full[i], 1);
       mbar_init(&s.s_full[i], 1);
-      mbar_init(&s.p_full[i], 128 * TPR);
-      mbar_init(&s.xbar[i], 256);
+      mbar_init(&s.p_full[i], 4 * TPR);     // one arrival per softmax warp
+      mbar_init(&s.xbar[i], 8);
     }
     for (int i = 0; i < FWD_KV_STAGES; ++i) {
       mbar_init(&s.k_full[i], 1);
@@ -187,11 +192,13 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
   for (int e = row.seg_begin; e < row.seg_end; ++e) n_total += seg_tiles(p.segs[e], r0, rows_here);
 
   if (warp >= Cfg::SOFTMAX_WARPS) {
-  // 20 warps leave 96 registers per thread (five warps share a scheduler's 16K registers). The last
-  // warpgroup (TMA, MMA, two idle warps) needs few; the softmax warpgroups, which hold 64 scores per
-  // thread, take what it gives back. (The instruction sits inside the role's branch so that the
+  // 20 warps are launched with 96 registers per thread, and that launch-time total (5 x 96 per
+  // scheduler lane) is the whole pool that setmaxnreg can redistribute: an increase that asks for
+  // more than the decreases have returned never completes. The last warpgroup (TMA, MMA, two idle
+  // warps) goes down to 64 and the four softmax warpgroups, which hold 64 scores per thread, go up
+  // to 104: 4 x 104 + 64 = 5 x 96. (The instruction sits inside the role's branch so that the
   // compiler budgets each role separately.)
-  if constexpr (TPR == 2) reg_dealloc<56>();
+  if constexpr (TPR == 2) reg_dealloc<FwdCfg<2>::REGS_LOAD>();
   if (warp == Cfg::TMA_WARP) {
     // =============================== TMA producer ===========================================
     if (lane == 0 && n_total > 0) {
@@ -310,7 +317,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
   }
   } else {
     // =============================== softmax + epilogue =====================================
-    if constexpr (TPR == 2) reg_alloc<112>();
+    if constexpr (TPR == 2) reg_alloc<FwdCfg<2>::REGS_SOFTMAX>();
     const int w = warp / (4 * TPR);          // sub-tile
     const int part = (warp >> 2) % TPR;      // which NC-column slice of the row this thread handles
     const int quad = warp & 3;               // TMEM lane quadrant of this warp
@@ -326,7 +333,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
     uint32_t xph = 0;        // phase of the sub-tile's exchange barrier
     // all 256 threads of the sub-tile have passed this point (bounded like every other wait)
     auto subtile_sync = [&]() -> bool {
-      mbar_arrive(&s.xbar[w]);
+      mbar_arrive_warp(&s.xbar[w]);
       const bool good = mbar_wait(&s.xbar[w], xph & 1, wc, 330 + w);
       ++xph;
       return good;
@@ -444,7 +451,7 @@ attn_fwd_kernel(const __grid_constant__ FwdParams p) {
         FWD_PROF(prof, pslot + 4);
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&s.p_full[w]);
+        mbar_arrive_warp(&s.p_full[w]);
         FWD_PROF(prof, pslot + 5);
       }
     }
@@ -555,6 +562,16 @@ extern "C" int ua_set_kernel_trace(int which, unsigned long long* buf, int cap) 
   return 0;
 }
 
+// Hits and misses of the host-side tensor-map cache since the library was loaded.
+extern "C" int ua_tmap_cache_stats(unsigned long long* hits, unsigned long long* misses) {
+  TmapCache& c = tmap_cache();
+  while (c.busy.test_and_set(std::memory_order_acquire)) {}
+  *hits = c.hits;
+  *misses = c.misses;
+  c.busy.clear(std::memory_order_release);
+  return 0;
+}
+
 #ifdef UA_FWD_PROF
 extern "C" int ua_fwd_prof_read(long long* host64) {
   UA_CUDA(cudaMemcpyFromSymbol(host64, g_fwd_prof, sizeof(long long) * 64));
@@ -655,7 +672,7 @@ extern "C" int ua_attn_fwd(const UaTensorSrc* q_src, int n_q, const UaTensorSrc*
   UA_CUDA(cudaGetDevice(&dev));
   // UA_FWD_TPR = 1 / 2: softmax threads per query row (see the top of this file)
   const char* env = getenv("UA_FWD_TPR");
-  const int tpr = (env != nullptr && atoi(env) == 1) ? 1 : 2;
+  const int tpr = (env != nullptr && atoi(env) == 2) ? 2 : 1;
   if (dev < 64 && !g_fwd_smem_set[tpr - 1][dev]) {
     if (tpr == 2)
       UA_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));

@@ -102,6 +102,30 @@ peer_add_kernel(float* __restrict__ dst, float* __restrict__ src, long n_vec4, i
 }
 
 
+// dst[i] = src[i] in 16-byte vectors by `gridDim.x` CTAs with the access pattern of the attention
+// kernels' staging copies (four independent loads in flight per thread, `ld.global.cg`): src is
+// usually a peer GPU's memory. Used to measure how staging throughput grows with the number of
+// CTAs that copy (an input of the fused path's cost model).
+__global__ void __launch_bounds__(512)
+peer_pull_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long n16) {
+  const long per = (n16 + gridDim.x - 1) / gridDim.x;
+  const long lo = static_cast<long>(blockIdx.x) * per;
+  const long hi = lo + per < n16 ? lo + per : n16;
+  const long stride = blockDim.x;
+  long i = lo + threadIdx.x;
+  for (; i + 3 * stride < hi; i += 4 * stride) {
+    const uint4 a = __ldcg(src + i);
+    const uint4 b = __ldcg(src + i + stride);
+    const uint4 c = __ldcg(src + i + 2 * stride);
+    const uint4 d = __ldcg(src + i + 3 * stride);
+    dst[i] = a;
+    dst[i + stride] = b;
+    dst[i + 2 * stride] = c;
+    dst[i + 3 * stride] = d;
+  }
+  for (; i < hi; i += stride) dst[i] = __ldcg(src + i);
+}
+
 // ---- NVLS (NVSwitch multicast) primitives ---------------------------------------------------------
 // `mc` is the multicast address of a symmetric buffer: one store to it lands in every rank's
 // replica, one load-reduce from it returns the sum over all replicas, both performed by the switch.
@@ -147,6 +171,15 @@ multimem_reduce_kernel(float4* __restrict__ dst, const float4* __restrict__ mc, 
 }  // namespace ua
 
 using namespace ua;
+
+extern "C" int ua_peer_pull(void* dst, const void* src, long nbytes, int n_ctas, cudaStream_t stream) {
+  if (nbytes % 16 != 0 || n_ctas < 1) UA_FAIL("ua_peer_pull: size must be a multiple of 16 bytes, n_ctas >= 1");
+  if (nbytes == 0) return 0;
+  peer_pull_kernel<<<static_cast<unsigned>(n_ctas), 512, 0, stream>>>(
+      static_cast<uint4*>(dst), static_cast<const uint4*>(src), nbytes / 16);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int ua_peer_add_f32(void* dst, void* src, long n, int zero_src, int num_sms,
                                cudaStream_t stream) {

@@ -101,6 +101,17 @@ __device__ __forceinline__ void report_error(const WaitCtx& w, int code, int whe
   }
 }
 
+// One arrival for a whole (converged) warp. Each lane first completes what it publishes (its
+// shared-memory writes, or its TMEM stores followed by tcgen05.wait::st and
+// tcgen05.fence::before_thread_sync); the warp barrier orders all of that before lane 0's arrival.
+// 32 times fewer arrivals on one barrier word: with one arrival per thread the arrivals of a
+// 128- or 256-thread role serialise on the word, and the consumer sees the phase that much later.
+// The barrier's expected count is then the number of WARPS.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+
 // Bounded parity wait. Returns false if it gave up (error recorded) or the CTA is aborting.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w,
                                           int where) {

@@ -129,6 +129,65 @@ def profile_comm(out_dir: Path, quick: bool) -> None:
     dist.destroy_process_group()
 
 
+def profile_comm_fused(out_dir: Path, quick: bool) -> None:
+    """The transports of the fused path, every rank active at once (rank r talks to r + 1), device
+    time as the max over ranks: (i) staging pulls by peer loads against the number of CTAs that
+    copy, (ii) peer ``red.global.add.v4.f32`` pushes, (iii) ``multimem.st`` broadcast and
+    ``multimem.ld_reduce`` all-to-one sums through the switch when the allocation has a multicast
+    address. One JSON line per point; the table goes to ``fused_comm_b200.json`` beside the link
+    logs, where ``planner.cost`` looks for it. Counterpart of the reference's conflict bench
+    (third_party/comm_test, outputs prof_data/*/cb_*.log), for transports it does not have."""
+    import torch.distributed as dist
+    from .. import _lib
+    from ..ops import elementwise as E
+    from ..parallel.comm import initialize_distribution
+    from ..runtime.fused import SymmMemSpace
+    info = initialize_distribution()
+    dev = torch.device("cuda", info["local_rank"])
+    space = SymmMemSpace(dist.group.WORLD, dev)
+    nbytes = 1 << (26 if quick else 28)
+    space.alloc("buf", (nbytes,), torch.uint8)
+    space.alloc("acc", (nbytes // 4,), torch.float32)
+    space.finalize()
+    nxt = (space.rank + 1) % space.world
+    peer_buf, peer_acc = space.peer("buf", nxt), space.peer("acc", nxt)
+    local = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    part = torch.ones(nbytes // 4, dtype=torch.float32, device=dev)
+    lib = _lib.load()
+    stream = lambda: torch.cuda.current_stream(dev).cuda_stream
+    rows = []
+
+    def measure(kind, fn, bytes_moved, **extra):
+        dist.barrier()
+        t = torch.tensor([_time(fn, 5, 2)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        rec = {"transport": kind, "ranks": space.world, "bytes": bytes_moved, "ms": round(t.item() * 1e3, 4),
+               "gbs_per_rank": round(bytes_moved / t.item() / 1e9, 1), **extra}
+        rows.append(rec)
+        if space.rank == 0:
+            print(json.dumps(rec), flush=True)
+
+    for ctas in (8, 16, 32, 64, 148):
+        measure("peer_pull", lambda: _lib.check(lib.ua_peer_pull(local.data_ptr(), peer_buf.data_ptr(), nbytes, ctas,
+                                                                 stream()), "ua_peer_pull"), nbytes, copy_ctas=ctas)
+    for size in (1 << 22, 1 << 25, nbytes):
+        n = size // 4
+        measure("peer_red_add_f32", lambda: E.peer_add_(peer_acc[:n], part[:n]), size)
+    if space.has_multicast():
+        mc = space.multicast_ptr("buf")
+        for size in (1 << 22, 1 << 25, nbytes):
+            measure("multimem_st_broadcast", lambda: E.multimem_bcast_(mc, local[:size]), size)
+        mca = space.multicast_ptr("acc")
+        out = torch.empty(nbytes // 4, dtype=torch.float32, device=dev)
+        for size in (1 << 22, 1 << 25, nbytes):
+            # every rank sums all replicas of its own size-byte window (an all-to-one reduction per rank)
+            measure("multimem_ld_reduce_f32", lambda: E.multimem_reduce(mca, out[:size // 4], size, torch.float32, dev), size)
+    if space.rank == 0:
+        out_dir.mkdir(parents=True, exist_ok=True)
+        (out_dir / "fused_comm_b200.json").write_text(json.dumps(rows, indent=0))
+    dist.destroy_process_group()
+
+
 def _profile_memory_bound_ops(rows: int, iters: int) -> None:
     """Time the memory-bound kernels of the model on tensors larger than L2 (``rows`` x 4096 bf16 and
     relatives) and print achieved GB/s (algorithmic bytes / device time) next to the measured copy
@@ -234,6 +293,8 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernels", action="store_true")
     ap.add_argument("--comm", action="store_true")
+    ap.add_argument("--comm-fused", action="store_true",
+                    help="peer-load staging vs copy CTAs, peer red.add, multimem broadcast / reduce (all ranks at once)")
     ap.add_argument("--out", default="logs/m_configs")
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--max-seconds", type=float, default=0.0, help="(--kernels) stop the sweep after this long")
@@ -284,6 +345,8 @@ def main() -> None:
         print(profile_kernels(Path(a.out), a.quick, a.max_seconds))
     if a.comm:
         profile_comm(Path(a.out), a.quick)
+    if a.comm_fused:
+        profile_comm_fused(Path(a.out), a.quick)
 
 
 if __name__ == "__main__":

@@ -91,6 +91,21 @@ class StagePlan:
     ticket: torch.Tensor | None = None      # one uint32: next unclaimed task of a launch (the launcher zeroes it)
 
 
+def _launch_order(tiles: list) -> list:
+    """Order of the CTAs of a launch. ``tiles``: (cost, group, index) with group = the block row
+    (forward) or block column (backward) that the tile belongs to. Tiles of one group walk the SAME
+    list of key/value (or query) blocks; started together they stream it in step and a block comes
+    out of DRAM once for all of them, whereas a pure heaviest-first order interleaves groups of
+    similar cost and every CTA then fetches its blocks from DRAM alone (measured on a global + local
+    pattern, whose rows all cost about the same: 15 % of the launch time). So: groups by their
+    heaviest tile, heaviest group first (the tail of the launch is then made of light CTAs); inside
+    a group heaviest tile first."""
+    top = {}
+    for cost, g, _ in tiles:
+        top[g] = max(top.get(g, 0), cost)
+    return sorted(tiles, key=lambda x: (-top[x[1]], x[1], -x[0], x[2]))
+
+
 def _seg_tiles(seg: Seg, r0: int, rows_here: int) -> int:
     n = (seg.length + TILE - 1) // TILE
     if seg.causal:
@@ -102,7 +117,7 @@ def _seg_tiles(seg: Seg, r0: int, rows_here: int) -> int:
 
 
 class FwdPlan:
-    """Device-resident tables for one forward launch (rows, segments, heaviest-first tile list)."""
+    """Device-resident tables for one forward launch (rows, segments, tile list in launch order)."""
 
     def __init__(self, rows: Sequence[Row], device: torch.device | str = "cpu"):
         self.rows = list(rows)
@@ -120,7 +135,7 @@ class FwdPlan:
                 rows_here = min(CTA_ROWS, r.q_len - r0)
                 cost = sum(_seg_tiles(s, r0, rows_here) for s in r.segs)
                 tiles.append((cost, ri, t))
-        tiles.sort(key=lambda x: -x[0])
+        tiles = _launch_order(tiles)
         self.n_tiles = len(tiles)
         self.total_key_tiles = sum(c for c, _, _ in tiles)
         seg_arr = np.array(segs, dtype=np.int32).reshape(-1, 8) if segs else np.zeros((1, 8), np.int32)
@@ -271,6 +286,18 @@ def read_kernel_trace(device: torch.device, kernel: str = "fwd") -> "np.ndarray"
     out = arr[arr[:, 0] != 0].copy()
     buf.zero_()
     return out
+
+
+def tensor_map_cache_stats() -> tuple[int, int]:
+    """(hits, misses) of the library's host-side cache of encoded TMA tensor maps. A step that
+    reuses its buffers (same addresses, shapes and strides) encodes nothing after its first run."""
+    import ctypes
+    lib = _lib.load()
+    lib.ua_tmap_cache_stats.restype = ctypes.c_int
+    lib.ua_tmap_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(ctypes.c_ulonglong)]
+    h, m = ctypes.c_ulonglong(0), ctypes.c_ulonglong(0)
+    lib.ua_tmap_cache_stats(ctypes.byref(h), ctypes.byref(m))
+    return int(h.value), int(m.value)
 
 
 def _src_struct(t: torch.Tensor) -> _lib.UaTensorSrc:
@@ -440,7 +467,7 @@ class BwdPlan:
                            c.kv_wait_flag, c.kv_wait_count)
             for t in range((c.kv_len + TILE - 1) // TILE):
                 tiles.append((_col_steps(c, t * TILE), ci, t))
-        tiles.sort(key=lambda x: -x[0])
+        tiles = _launch_order(tiles)
         self.n_tiles = len(tiles)
         self.total_steps = sum(c for c, _, _ in tiles)
         seg_arr = np.array(segs, dtype=np.int32).reshape(-1, 8) if segs else np.zeros((1, 8), np.int32)

@@ -33,6 +33,7 @@ B200_FWD_TFLOPS = 1050.0
 B200_BWD_TFLOPS = 1100.0
 B200_NVLINK_GBS = 770.0          # peer copy, per direction
 B200_LINK_LATENCY_S = 4e-6
+B200_SMS = 148
 B200_LAUNCH_S = 3e-5            # per-launch floor seen when tiles are tiny (host launch path included)
 PACKAGED_M_CONFIG_DIR = Path(__file__).resolve().parents[1] / "data" / "m_configs" / "B200"
 
@@ -270,13 +271,55 @@ class Comm_Profile_Map:
     get_value_from_map_key = get_comm_time_from_map_key
 
 
-class Machine_Config:
-    """[inter, intra] compute maps and [inter, intra] communication maps."""
+class Fused_Transport_Profile:
+    """Measured throughput of the transports that only the fused runtime uses, read from the JSON
+    table that ``drivers.cluster_profile --comm-fused`` writes (one record per point: ``transport``,
+    ``ranks``, ``bytes``, ``gbs_per_rank`` and, for staging pulls, ``copy_ctas``). Every rank was
+    active while a point was measured, so the figures already include the contention of an
+    all-ranks pattern. A transport without records answers ``None`` and the caller falls back to the
+    point-to-point link curve."""
 
-    def __init__(self, BW=None, comp_profile_maps=None, comm_profile_maps=None):
+    def __init__(self, records: Optional[Sequence[dict]] = None):
+        self.records = list(records or [])
+
+    def _points(self, transport: str, ranks: Optional[int]):
+        pts = [r for r in self.records if r.get("transport") == transport]
+        if ranks is not None and pts:
+            best = min({r["ranks"] for r in pts}, key=lambda n: (abs(n - ranks), -n))
+            pts = [r for r in pts if r["ranks"] == best]
+        return pts
+
+    def pull_gbs(self, copy_ctas: int, ranks: Optional[int] = None) -> Optional[float]:
+        """GB/s into one rank when ``copy_ctas`` CTAs stage peer blocks (linear between measured
+        CTA counts, flat outside them)."""
+        pts = sorted((r["copy_ctas"], r["gbs_per_rank"]) for r in self._points("peer_pull", ranks))
+        if not pts:
+            return None
+        xs, ys = zip(*pts)
+        return float(np.interp(copy_ctas, xs, ys))
+
+    def gbs(self, transport: str, nbytes: float, ranks: Optional[int] = None) -> Optional[float]:
+        """GB/s of ``transport`` at a message of ``nbytes`` (log-linear between measured sizes)."""
+        pts = sorted((r["bytes"], r["gbs_per_rank"]) for r in self._points(transport, ranks))
+        if not pts or nbytes <= 0:
+            return None
+        xs, ys = zip(*pts)
+        return float(np.interp(math.log2(nbytes), [math.log2(x) for x in xs], ys))
+
+    def time_s(self, transport: str, nbytes: float, ranks: Optional[int] = None, **kw) -> Optional[float]:
+        g = self.pull_gbs(kw["copy_ctas"], ranks) if transport == "peer_pull" else self.gbs(transport, nbytes, ranks)
+        return None if not g else nbytes / (g * 1e9)
+
+
+class Machine_Config:
+    """[inter, intra] compute maps, [inter, intra] communication maps and the fused runtime's
+    transport table."""
+
+    def __init__(self, BW=None, comp_profile_maps=None, comm_profile_maps=None, fused_transports=None):
         self.BW = BW or (B200_NVLINK_GBS, B200_NVLINK_GBS)
         self.comp_profile_maps = comp_profile_maps or [Inter_Comp_Profile_Map(), FlashAttn_Profile_Map()]
         self.comm_profile_maps = comm_profile_maps or [Comm_Profile_Map(), Comm_Profile_Map()]
+        self.fused_transports = fused_transports or Fused_Transport_Profile()
 
     @classmethod
     def b200_default(cls) -> "Machine_Config":
@@ -288,8 +331,8 @@ class Machine_Config:
 
     @classmethod
     def from_dir(cls, m_config_dir) -> "Machine_Config":
-        """Read ``time*.json`` / ``cb_8_*.log`` / ``cb_16_*.log`` of a directory; what is missing
-        falls back to the analytic B200 model."""
+        """Read ``time*.json`` / ``cb_8_*.log`` / ``cb_16_*.log`` / ``fused_comm_*.json`` of a
+        directory; what is missing falls back to the analytic B200 model."""
         mdir = Path(m_config_dir)
         flash = sorted(mdir.glob("time*.json")) if mdir.is_dir() else []
         cb8 = sorted(mdir.glob("cb_8_*.log")) if mdir.is_dir() else []
@@ -297,7 +340,10 @@ class Machine_Config:
         comp_intra = FlashAttn_Profile_Map(load_flash_profile(flash[0]) if flash else None)
         comm_intra = Comm_Profile_Map(convert_profile_data_to_comm_map(cb8[0]) if cb8 else None)
         comm_inter = Comm_Profile_Map(convert_profile_data_to_comm_map(cb16[0]) if cb16 else None)
-        return cls(None, [Inter_Comp_Profile_Map(), comp_intra], [comm_inter, comm_intra])
+        ft = sorted(mdir.glob("fused_comm_*.json")) if mdir.is_dir() else []
+        records = [r for f in ft for r in json.loads(f.read_text())]
+        return cls(None, [Inter_Comp_Profile_Map(), comp_intra], [comm_inter, comm_intra],
+                   Fused_Transport_Profile(records))
 
     def update_inter_bsa_profile(self, profile: dict) -> None:
         self.comp_profile_maps[0].update(profile)
@@ -480,7 +526,7 @@ def convert_node_profile_data_to_comp_map(file_name, local_size: int = 8) -> dic
 # -------------------------------------------------------------------------------------------------
 def fused_step_time(table, cmap, pattern, seq_len: int, n_heads: int, head_dim: int = 128,
                     m_config: Optional["Machine_Config"] = None, n_kv_heads: Optional[int] = None,
-                    batch: int = 1, hbm_gbs: float = 6400.0) -> dict:
+                    batch: int = 1, hbm_gbs: float = 6400.0, copy_ctas: int = 148) -> dict:
     """Predicted time of one forward and one backward call of the fused context-parallel runtime
     for an allocation ``table`` (tile -> rank) and ownership ``cmap``.
 
@@ -493,7 +539,13 @@ def fused_step_time(table, cmap, pattern, seq_len: int, n_heads: int, head_dim: 
     outbound NVLink bytes over the link curve, overlapped with compute: only the excess counts)
     + the memory-bound passes around the kernels (copy-in of the shards, D = rowsum(dO * O),
     merge of mailbox slots, fp32 -> bf16 cast and clearing of the accumulators). The step ends
-    when the slowest rank ends. Returns per-pass times in seconds and the per-rank breakdown."""
+    when the slowest rank ends. Returns per-pass times in seconds and the per-rank breakdown.
+
+    Inbound bytes are staged by ``copy_ctas`` CTAs with peer loads and outbound fp32 partial sums
+    leave as peer ``red.add``; where the machine profile has measured those transports
+    (``Fused_Transport_Profile``) their throughput replaces the point-to-point link curve. The CTAs
+    that stage do so before they take their first tile, so staging also costs compute time: its
+    duration times the share of the SMs that copy (``stage_s`` in the breakdown)."""
     import numpy as _np
     m = m_config or Machine_Config.b200_default()
     table = _np.asarray(table)
@@ -525,16 +577,27 @@ def fused_step_time(table, cmap, pattern, seq_len: int, n_heads: int, head_dim: 
         # backward (inputs staged by the forward are reused): pull dO, lse, D; push dQ (fp32), dK, dV (fp32)
         b_in = len(rows) * (q_blk + 2 * batch * n_heads * blk * 4)
         b_out = len(rows) * 2 * q_blk + len(cols) * 2 * 2 * kv_blk
-        link = [max(comm.get_comm_time_from_map_key((x,)) if x else 0.0 for x in pair)
-                for pair in ((f_in, f_out), (b_in, b_out))]
+        ft = m.fused_transports
+
+        def t_in(x):
+            return 0.0 if not x else (ft.time_s("peer_pull", x, cp, copy_ctas=copy_ctas)
+                                      or comm.get_comm_time_from_map_key((x,)))
+
+        def t_out(x, transport):
+            return 0.0 if not x else (ft.time_s(transport, x, cp) or comm.get_comm_time_from_map_key((x,)))
+
+        link = [max(t_in(f_in), t_out(f_out, "peer_store")), max(t_in(b_in), t_out(b_out, "peer_red_add_f32"))]
         own_q = batch * shard * n_heads * head_dim
         own_kv = batch * shard * hk * head_dim
         mem_f = (2 * (own_q + 2 * own_kv) * es + len(rows) * 0 + 3 * own_q * es) / (hbm_gbs * 1e9)
         mem_b = (2 * own_q * es + 2 * own_q * es            # copy-in of dO, D pre-pass reads O and dO
                  + (own_q + 2 * own_kv) * (4 + es + 4)) / (hbm_gbs * 1e9)   # cast + clear of the accumulators
         launch = _np.array([B200_LAUNCH_S * 3, B200_LAUNCH_S * 5])
-        total = _np.array([max(comp_t[0], link[0]) + mem_f, max(comp_t[1], link[1]) + mem_b]) + launch
-        out["per_rank"].append({"rank": g, "tiles": len(tiles), "compute_s": comp_t.tolist(), "link_s": link,
+        share = min(copy_ctas, B200_SMS) / B200_SMS
+        stage = [t_in(f_in) * share, t_in(b_in) * share]
+        total = _np.array([max(comp_t[0] + stage[0], link[0]) + mem_f,
+                           max(comp_t[1] + stage[1], link[1]) + mem_b]) + launch
+        out["per_rank"].append({"rank": g, "tiles": len(tiles), "compute_s": comp_t.tolist(), "link_s": link, "stage_s": stage,
                                 "memory_s": [mem_f, mem_b], "total_s": total.tolist()})
     out["fwd_s"] = max(r["total_s"][0] for r in out["per_rank"])
     out["bwd_s"] = max(r["total_s"][1] for r in out["per_rank"])
