@@ -404,8 +404,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--seq", type=int, default=S_TOTAL)
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--time-limit", type=int, default=1500,
-                    help="seconds after which the arm gives up (a rank that failed leaves the others in a collective)")
+    ap.add_argument("--time-limit", type=int, default=int(os.environ.get("UA_REFERENCE_TIME_LIMIT", "1500")),
+                    help="seconds after which the arm gives up (a rank that failed leaves the others in a "
+                         "collective); default from UA_REFERENCE_TIME_LIMIT")
     args, _ = ap.parse_known_args()
     _clean_sys_path()
     rank = int(os.environ.get("RANK", "0"))
