@@ -116,6 +116,10 @@ def _worker(rank, world, port, ret, with_graph):
             torch.cuda.synchronize(dev)
             reached("replayed")
             ok = ok and bool((y == 10 + peer).all())
+            # NCCL keeps a communicator alive while a graph that captured its calls exists:
+            # ncclCommDestroy would wait for the graph to go away
+            del graph
+            torch.cuda.synchronize(dev)
         dist.barrier()
         comm.destroy()
         ret[rank] = {"ok": ok, "steps": list(steps)}

@@ -31,6 +31,8 @@ def main() -> None:
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--pattern", default="causal", choices=["causal", "full", "global_local"])
+    ap.add_argument("--with-peer-gather", action="store_true",
+                    help="also time the fused block whose gather GEMMs read the owners' buffers directly")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -49,28 +51,32 @@ def main() -> None:
     x, dy = rnd(S_loc, Hd, s=0.5), rnd(S_loc, Hd, s=0.5)
     wqkv, wo = rnd(3 * H * 128, Hd, s=0.02), rnd(Hd, H * 128, s=0.02)
     cos, sin = E.rope_tables(S, 128, 10000.0, dev)
-    block = FusedUlyssesAttention(group, dev, S, Hd, H, pattern=pattern)
+    blocks = {"fused": FusedUlyssesAttention(group, dev, S, Hd, H, pattern=pattern)}
+    if a.with_peer_gather:
+        blocks["fused, gathers read peer memory directly"] = FusedUlyssesAttention(
+            group, dev, S, Hd, H, pattern=pattern, gather="peer")
 
-    def step(fused: bool):
+    def step(variant: str):
         xl = x.detach().requires_grad_()
         w1 = wqkv.detach().requires_grad_()
         w2 = wo.detach().requires_grad_()
-        y = block(xl, w1, w2, cos, sin) if fused else \
+        y = blocks[variant](xl, w1, w2, cos, sin) if variant in blocks else \
             unfused_reference(xl, w1, w2, group, H, H, 128, pattern, cos, sin)
         y.backward(dy)
 
     n = pattern.table.shape[0]
     attn_flops = pattern.volume * (S / n) ** 2 * 4 * 128 * H * 3.5 / world
     gemm_flops = 2.0 * S_loc * Hd * (3 * H * 128 + H * 128) * 3
-    for name, fused in (("unfused", False), ("fused", True)):
+    for name in ["unfused"] + list(blocks):
+        fused = name in blocks
         for _ in range(2):
-            step(fused)
+            step(name)
         dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(a.iters):
-            step(fused)
+            step(name)
         e1.record()
         dist.barrier()
         torch.cuda.synchronize()
@@ -82,7 +88,7 @@ def main() -> None:
                    "heads": H, "pattern": a.pattern, "ms": round(t.item(), 3),
                    "hw_tflops_per_gpu": round((attn_flops + gemm_flops) / t.item() / 1e9, 1)}
             if fused:
-                rec["nvlink_bytes_per_rank"] = block.traffic
+                rec["nvlink_bytes_per_rank"] = blocks[name].traffic
             print(json.dumps(rec), flush=True)
     dist.destroy_process_group()
 

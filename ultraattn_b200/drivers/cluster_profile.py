@@ -241,30 +241,49 @@ def _profile_memory_bound_ops(rows: int, iters: int) -> None:
 def _profile_gemm_shapes(iters: int = 20) -> None:
     """The GEMM kernel on the projection / FFN shapes of Llama-2-7B at 64k tokens per GPU (and
     8192^3), single-CTA tiles and CTA pairs, next to the library GEMM PyTorch calls (cuBLAS) on
-    the same tensors; one JSON line per shape."""
+    the same tensors; one JSON line per shape. The variants take turns (five launches each per
+    round, ``iters`` launches in total), because under the power cap the clock sags within a few
+    hundred milliseconds of load: timed one after the other, whichever variant runs first would
+    look fastest."""
     import os
     from ..ops import gemm as G
     dev = torch.device("cuda")
+    saved = os.environ.get("UA_GEMM_PAIR")
+
+    def force(value):
+        if value is None:
+            os.environ.pop("UA_GEMM_PAIR", None)
+        else:
+            os.environ["UA_GEMM_PAIR"] = value
+
     for (M, N, K) in [(8192, 8192, 8192), (65536, 4096, 4096), (65536, 12288, 4096), (65536, 22016, 4096),
                       (65536, 4096, 11008)]:
         a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
         b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
         out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         fl = 2.0 * M * N * K
+        force(None)
+        G._pair_choice.clear()
+        G.gemm(a, b, out=out)                       # the wrapper picks its form for this shape here
+        form = "cta_pair" if G._pair_choice.get((M, N, K, False, False)) else "single_cta"
+        variants = {
+            "single_cta_tflops": ("0", lambda: G.gemm(a, b, out=out)),
+            "cta_pair_tflops": ("1", lambda: G.gemm(a, b, out=out)),
+            "library_tflops": (None, lambda: torch.matmul(a, b.t(), out=out)),
+        }
+        spent = {k: 0.0 for k in variants}
+        per_round = 5
+        rounds = max(1, iters // per_round)
+        for rnd in range(rounds + 1):               # round 0 warms up and is not counted
+            for name, (env, fn) in variants.items():
+                force(env)
+                t = _time(fn, per_round, 1 if rnd == 0 else 0)
+                if rnd:
+                    spent[name] += t
+        force(saved)
         rec = {"op": "gemm", "M": M, "N": N, "K": K}
-        saved = os.environ.get("UA_GEMM_PAIR")
-        for pair in ("0", "1"):
-            os.environ["UA_GEMM_PAIR"] = pair
-            t = _time(lambda: G.gemm(a, b, out=out), iters, 3)
-            rec["single_cta_tflops" if pair == "0" else "cta_pair_tflops"] = round(fl / t / 1e12, 1)
-        if saved is None:
-            del os.environ["UA_GEMM_PAIR"]
-        else:
-            os.environ["UA_GEMM_PAIR"] = saved
-        t = _time(lambda: G.gemm(a, b, out=out), iters, 3)
-        rec["default_tflops"] = round(fl / t / 1e12, 1)
-        t = _time(lambda: torch.matmul(a, b.t(), out=out), iters, 3)
-        rec["library_tflops"] = round(fl / t / 1e12, 1)
+        rec.update({k: round(fl / (v / rounds) / 1e12, 1) for k, v in spent.items()})
+        rec["default_form"] = form
         print(json.dumps(rec), flush=True)
 
 

@@ -225,6 +225,21 @@ def peer_add_(dst: torch.Tensor, src: torch.Tensor, zero_src: bool = False) -> N
     _lib.check(rc, "ua_peer_add_f32")
 
 
+def peer_pull_(dst: torch.Tensor, src: torch.Tensor, n_ctas: int = 0) -> None:
+    """dst = src for contiguous tensors of equal byte size (a multiple of 16); ``src`` is usually a
+    view of a peer GPU's memory, read with plain peer loads by this framework's copy kernel
+    (``n_ctas`` CTAs, default one per SM)."""
+    assert dst.is_contiguous() and src.is_contiguous()
+    nbytes = dst.numel() * dst.element_size()
+    assert nbytes == src.numel() * src.element_size()
+    if not dst.is_cuda:
+        dst.view(torch.uint8).copy_(src.view(torch.uint8))
+        return
+    n = n_ctas or torch.cuda.get_device_properties(dst.device).multi_processor_count
+    rc = _lib.load().ua_peer_pull(dst.data_ptr(), src.data_ptr(), nbytes, n, _stream(dst))
+    _lib.check(rc, "ua_peer_pull")
+
+
 def multimem_bcast_(mc_ptr: int, src: torch.Tensor) -> None:
     """Store ``src`` (contiguous, size a multiple of 16 bytes) into every rank's replica of a
     symmetric buffer through its NVSwitch multicast address ``mc_ptr`` (``multimem.st``): the

@@ -291,7 +291,8 @@ class NcclCommunicator:
 
     def destroy(self, abort: bool = False) -> None:
         """Free the communicator. ``abort=True`` does not wait for outstanding operations (the way
-        out after a peer failure)."""
+        out after a peer failure). CUDA graphs that captured calls of this communicator must be
+        destroyed first: ``ncclCommDestroy`` waits for them."""
         if self.comm:
             self._call("ncclCommAbort" if abort else "ncclCommDestroy", self.comm)
             self.comm = ncclComm_t()

@@ -7,16 +7,25 @@ Unfused (reference: head_parallel_attn/deepspeed_ulysses_attn.py:10-198, comm_li
 Fused (this module), forward:
     the QKV GEMM's epilogue stores every head group's output tile directly into the receive
     buffer of the rank that owns those heads (peer stores over NVLink, ``gemm_scatter``);
-    the output projection's TMA producer loads its A operand, K-group by K-group, directly from
-    the attention outputs held by the owning ranks (unicast TMA over peer mappings,
-    ``gemm_gather``).
+    the output projection's TMA producer loads its A operand K-group by K-group, one group per
+    owning rank (``gemm_gather``).
 Backward, through the same two fusions:
     dO of every head group:  dy @ Wo  with the scatter epilogue (rank g receives its heads' dO for
     all tokens);  block-sparse attention backward on the local heads over the whole sequence;
-    dx = dQKV @ Wqkv  with the gather prologue (this rank's tokens of every head group, read from
-    the owners' buffers).  The weight gradients are local GEMMs whose token-major operand is read
-    from the owning rank's buffer by unicast TMA (dWo: O of head group g, dWqkv: dQKV of group g).
+    dx = dQKV @ Wqkv  with the gather prologue (this rank's tokens of every head group).  The
+    weight gradients are per-group GEMMs on the same gathered operands (dWo: O of head group g,
+    dWqkv: dQKV of group g).
 No all-to-all kernel exists on this path.
+
+Where the gathered operand comes from (``gather="staged"``, default): a GEMM reads its A operand
+once per tile column, i.e. N / 256 times, and peer memory is not cached in the reader's L2, so a
+gather prologue that points TMA at the owners' buffers sends every byte over NVLink 16 times for a
+4096-wide output (measured on 8 GPUs, S = 256k: the block took 345 ms against 256 ms for the
+all-to-all form). So this rank's token rows of every peer's buffer are first pulled ONCE into a
+local staging buffer by this framework's copy kernel (plain peer loads, all SMs, about 640 GB/s)
+and the gather prologue and the weight-gradient GEMMs read the local copy. ``gather="peer"`` keeps
+the direct form (unicast TMA over the peer mappings), which is the right one when the output is
+narrow (one tile column).
 
 Weights: ``wqkv`` rows must be ordered by destination rank — for rank g the rows
 ``[q heads of g | k heads of g | v heads of g]`` — :func:`permute_qkv_weight` produces that order
@@ -65,7 +74,7 @@ class FusedUlyssesAttention:
     framework (default dense causal); rank r holds the tokens ``[r * S/sp, (r + 1) * S/sp)``."""
 
     def __init__(self, group, device, seq_len: int, hidden: int, n_heads: int, n_kv_heads: int = None,
-                 head_dim: int = 128, causal: bool = True, pattern=None):
+                 head_dim: int = 128, causal: bool = True, pattern=None, gather: str = "staged"):
         self.group, self.device = group, device
         self.sp = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -82,23 +91,49 @@ class FusedUlyssesAttention:
         self.space.alloc("dattn", (seq_len, self.hq * head_dim), torch.bfloat16)
         self.space.alloc("dqkv", (seq_len, self.cols), torch.bfloat16)
         self.space.finalize()
+        assert gather in ("staged", "peer")
+        self.gather = gather
+        # this rank's token rows of every peer's buffer, pulled once per use (attn: the first
+        # hq * D columns of a slot; dqkv: all of it)
+        self.stage = (torch.empty(self.sp, self.S_loc, self.cols, dtype=torch.bfloat16, device=device)
+                      if gather == "staged" and self.sp > 1 else None)
         from ..api import local_plans
         from ..patterns import named
         if pattern is None:
             pattern = named.causal(1) if causal else named.full(1)
         self.pattern = pattern
         self.fplan, self.bplan = local_plans(pattern, seq_len, device)
-        # NVLink bytes this rank moves per call (fused GEMM epilogues / prologues), for reports
+        # NVLink bytes this rank moves per call (scatter epilogues; gathers), for reports. Staged
+        # gathers move every byte once; the direct form re-reads a gathered operand once per tile
+        # column of the GEMM that consumes it (hidden / 256 for the projections).
         es, peers = 2, self.sp - 1
+        attn_b, qkv_b = self.S_loc * self.hq * head_dim * peers * es, self.S_loc * self.cols * peers * es
+        rereads = 1 if gather == "staged" else max(1, hidden // 256)
         self.traffic = {
-            "fwd_scatter_bytes": self.S_loc * self.cols * peers * es,
-            "fwd_gather_bytes": self.S_loc * self.hq * head_dim * peers * es,
-            "bwd_scatter_bytes": (self.S_loc * self.cols + self.S_loc * self.hq * head_dim) * peers * es,
-            "bwd_gather_bytes": (self.S_loc * self.cols + 2 * self.S_loc * self.hq * head_dim
-                                 + self.S_loc * self.cols) * peers * es,
+            "gather_form": gather,
+            "fwd_scatter_bytes": qkv_b,
+            "fwd_gather_bytes": attn_b * rereads,
+            "bwd_scatter_bytes": qkv_b + attn_b,                       # q/k/v again, dO
+            "bwd_gather_bytes": (attn_b + qkv_b) * (1 if gather == "staged" else rereads + 1),
         }
 
     # ------------------------------------------------------------------------------------------
+    def _gathered(self, name: str, width: int):
+        """This rank's rows ``[r0, r0 + S/sp)`` of buffer ``name`` on every rank, as a list of
+        ``[S/sp, width]`` tensors (one per owner). Staged form: remote ones are pulled into the
+        local staging buffer (one pass over NVLink); the own one is a view of the local buffer."""
+        sp, r0 = self.space, self.rank * self.S_loc
+        out = []
+        for g in range(self.sp):
+            src = sp.peer(name, g)[r0:r0 + self.S_loc]
+            if g == self.rank or self.stage is None:
+                out.append(src)
+                continue
+            dst = self.stage[g].view(-1)[:self.S_loc * width].view(self.S_loc, width)
+            E.peer_pull_(dst, src)
+            out.append(dst)
+        return out
+
     def _project_qkv(self, x, wqkv_perm, cos, sin):
         """x [S/sp, hidden] -> this rank's head group of q, k, v for all tokens (views of the
         symmetric receive buffer), RoPE applied."""
@@ -121,10 +156,10 @@ class FusedUlyssesAttention:
     def _project_out(self, wo):
         """y [S/sp, hidden] = attention outputs of this rank's tokens (all head groups, read from
         their owners) @ Wo^T."""
-        sp = self.space
         y = torch.empty(self.S_loc, wo.shape[0], dtype=torch.bfloat16, device=self.device)
-        src = [sp.peer("attn", r).data_ptr() for r in range(self.sp)]
-        G.gemm_gather(src, self.S, self.hq * self.D, self.rank * self.S_loc, self.S_loc, self.hq * self.D, wo, y)
+        hqD = self.hq * self.D
+        parts = self._gathered("attn", hqD)
+        G.gemm_gather([t.data_ptr() for t in parts], self.S_loc, hqD, 0, self.S_loc, hqD, wo, y)
         return y
 
     def forward(self, x: torch.Tensor, wqkv_perm: torch.Tensor, wo: torch.Tensor, cos=None, sin=None,
@@ -171,10 +206,9 @@ class FusedUlyssesAttention:
         dst = [sp.peer("dattn", r).data_ptr() for r in range(self.sp)]
         G.gemm_scatter(dy, wo, dst, hqD, r0, b_is_kn=True)
         sp.barrier(7)                       # dO of my heads has arrived from every rank; O is in place everywhere
-        # dWo[:, heads of g] = dy^T @ O_g[my tokens]   (O_g read from its owner)
+        # dWo[:, heads of g] = dy^T @ O_g[my tokens]
         dwo = torch.empty(wo.shape, dtype=torch.bfloat16, device=self.device)
-        for g in range(self.sp):
-            o_g = sp.peer("attn", g)[r0:r0 + S_loc]
+        for g, o_g in enumerate(self._gathered("attn", hqD)):
             G.gemm(dy, o_g, a_is_km=True, b_is_kn=True, out=dwo[:, g * hqD:(g + 1) * hqD])
         # attention backward on the local heads over the whole sequence
         d_o = sp.local("dattn").view(1, S, self.hq, D)
@@ -201,12 +235,12 @@ class FusedUlyssesAttention:
         sp.barrier(8)                       # every rank's dQ / dK / dV of its heads is complete
         # dx = dQKV[my tokens, every head group] @ Wqkv_perm   (A gathered from the owners)
         dx = torch.empty(S_loc, self.hidden, dtype=torch.bfloat16, device=self.device)
-        src = [sp.peer("dqkv", r).data_ptr() for r in range(self.sp)]
-        G.gemm_gather(src, S, self.cols, r0, S_loc, self.cols, wqkv_perm, dx, b_is_kn=True)
+        parts = self._gathered("dqkv", self.cols)
+        G.gemm_gather([t.data_ptr() for t in parts], S_loc, self.cols, 0, S_loc, self.cols, wqkv_perm, dx,
+                      b_is_kn=True)
         # dWqkv_perm[rows of g] = dQKV_g[my tokens]^T @ x
         dwqkv = torch.empty(wqkv_perm.shape, dtype=torch.bfloat16, device=self.device)
-        for g in range(self.sp):
-            d_g = sp.peer("dqkv", g)[r0:r0 + S_loc]
+        for g, d_g in enumerate(parts):
             G.gemm(d_g, x, a_is_km=True, b_is_kn=True, out=dwqkv[g * self.cols:(g + 1) * self.cols])
         return dx, dwqkv, dwo
 
