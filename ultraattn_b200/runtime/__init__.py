@@ -4,3 +4,4 @@ from .fused import FakeSpace, FusedContextParallel, PeerSpace, SymmMemSpace
 from .grid import GridExecutor
 from .verify import verify_fused_tables
 from .heartbeat import StepHeartbeat
+from .graphed import GraphedAttention
