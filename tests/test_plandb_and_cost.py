@@ -205,6 +205,28 @@ def test_report_reads_the_published_profile_entries():
     assert abs(r["speedup_vs_best_baseline"] - 1.285 / 1.853) < 1e-9 and r["speedup_vs_best_baseline"] < 0.7
 
 
+def test_report_from_bench_lines(tmp_path, capsys):
+    """The figure table and chart straight from bench_configs' JSON lines: baselines, the NCCL
+    path in its ablation column, UltraAttn = best of fused and NCCL, ratios as measured."""
+    import json
+    from ultraattn_b200.drivers import report
+    lines = [{"config": "gl512k", "S": 524288, "path": p, "n_gpus": 8, "ms": ms}
+             for p, ms in (("fused", 217.2), ("nccl", 282.8), ("ring", 626.1))]
+    lines += [{"config": "causal128k", "S": 131072, "path": p, "n_gpus": 8, "ms": ms}
+              for p, ms in (("fused", 64.2), ("nccl", 91.1), ("ring", 128.9), ("zigzag", 76.5))]
+    rows = report.rows_from_bench_lines([json.dumps(l) for l in lines] + ["{\"transport\": \"peer_pull\"}"])
+    by = {r["config"]: r for r in rows}
+    assert abs(by["gl512k"]["speedup_vs_ring"] - 626.1 / 217.2) < 1e-9 and by["gl512k"]["node_device_tile"] == 0.2828
+    assert abs(by["causal128k"]["speedup_vs_best_baseline"] - 76.5 / 64.2) < 1e-9 and by["causal128k"]["CP"] == "(8, 1)"
+    f = tmp_path / "lines.jsonl"
+    f.write_text("\n".join(json.dumps(l) for l in lines))
+    assert report.main(["--bench-jsonl", str(f), "--svg", str(tmp_path / "c.svg"), "--csv", str(tmp_path / "c.csv")]) == 0
+    out = capsys.readouterr().out
+    assert "| config |" in out and "gl512k" in out and "2.88" in out
+    svg = (tmp_path / "c.svg").read_text()
+    assert svg.count('class="bar"') == 3 + 4 and "gl512k CP=(8, 1)" in svg
+
+
 def test_fused_step_time_model():
     """The time model of the fused runtime: one rank = the sum of its tile times; a balanced
     allocation is predicted faster than the row-owner one; eight ranks take about an eighth."""

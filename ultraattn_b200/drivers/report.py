@@ -14,6 +14,13 @@ over the ring baseline and over the best baseline. The label mapping is the refe
 ``_zigzag``, ``_stripe``. Unlike the reference's plot scripts nothing is substituted when a
 baseline wins: the ratio is printed as measured. ``--svg`` draws the speed-ups as a grouped bar chart without any plotting library (this image
 has no matplotlib); ``--csv`` gives the same numbers to any plotting tool.
+
+    python -m ultraattn_b200.drivers.report --bench-jsonl lines.jsonl [--svg out.svg] [--csv out.csv]
+
+reads the JSON lines that ``drivers/bench_configs.py`` prints (one per configuration and path)
+instead of a database and prints the same table: ``ring`` / ``zigzag`` are the baselines, the
+``nccl`` path (the launch plan executed with NCCL messages) fills the "Node+Device Tile" column it
+corresponds to, and "UltraAttn" is the best of the fused path and the NCCL path.
 """
 from __future__ import annotations
 
@@ -122,6 +129,32 @@ def e2e_rows(rows: list, n_layers: int, time_wo_attn: float) -> list:
     return out
 
 
+def rows_from_bench_lines(lines) -> list:
+    """Figure rows from ``bench_configs`` JSON lines (dicts or strings); times become seconds."""
+    groups: dict = {}
+    for ln in lines:
+        rec = json.loads(ln) if isinstance(ln, str) else ln
+        if "config" not in rec or "path" not in rec:
+            continue
+        groups.setdefault((rec["config"], rec["n_gpus"], rec["S"]), {})[rec["path"]] = rec["ms"] / 1e3
+    rows = []
+    for (config, n, S), t in sorted(groups.items(), key=lambda kv: (kv[0][1], kv[0][0])):
+        ultra = [t[p] for p in ("fused", "nccl", "nccl-ilp") if p in t]
+        base = {b: t[b] for b in ("ring", "zigzag", "stripe") if b in t}
+        row = {"key": config, "config": config, "fob": "", "CP": f"({n}, 1)",
+               "shape": f"S=({S},{S})_Nh=(32,32)_bs=1_D=128",
+               "ring": t.get("ring"), "zigzag": t.get("zigzag"), "stripe": t.get("stripe"), "node_tile": None,
+               "node_device_tile": t.get("nccl"), "kernel_tile": None, "fused": t.get("fused"),
+               "ultraattn": min(ultra) if ultra else None}
+        if row["ultraattn"] is not None:
+            if row["ring"]:
+                row["speedup_vs_ring"] = row["ring"] / row["ultraattn"]
+            if base:
+                row["speedup_vs_best_baseline"] = min(base.values()) / row["ultraattn"]
+        rows.append(row)
+    return rows
+
+
 SERIES = [("ring", "#9e9e9e"), ("zigzag", "#64b5f6"), ("stripe", "#4db6ac"), ("node_tile", "#ffcc80"),
           ("node_device_tile", "#ffa726"), ("ultraattn", "#e53935")]
 
@@ -139,7 +172,7 @@ def bar_chart_svg(rows: list, title: str = "", baseline: str = "ring", width_per
         if not base:
             continue
         bars = [(k, colour, base / r[k]) for k, colour in SERIES if r.get(k)]
-        label = f"fob={r.get('fob', '')} CP={r.get('CP', '')}"
+        label = f"{r['config']} CP={r.get('CP', '')}" if r.get("config") else f"fob={r.get('fob', '')} CP={r.get('CP', '')}"
         m = re.search(r"S=\((\d+)", r.get("shape", "") or "")
         if m:
             label += f" S={int(m.group(1)) // 1024}k"
@@ -190,7 +223,9 @@ def _fmt(v):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--db", required=True, help="database/<cluster>/<platform> directory")
+    ap.add_argument("--db", default=None, help="database/<cluster>/<platform> directory")
+    ap.add_argument("--bench-jsonl", default=None,
+                    help="JSON lines printed by drivers/bench_configs.py, instead of a database")
     ap.add_argument("--level", default="inter", choices=["intra", "inter"])
     ap.add_argument("--csv", default=None)
     ap.add_argument("--svg", default=None, help="also draw the speed-ups over the ring baseline as a bar chart")
@@ -200,15 +235,22 @@ def main(argv=None) -> int:
                     help="print end-to-end step times: layers x (fwd + bwd) + --e2e-const")
     ap.add_argument("--e2e-const", type=float, default=0.0, help="seconds per step outside attention")
     a = ap.parse_args(argv)
-    path = Path(a.db) / f"{a.level}_bsa_exe_plans_profile.json"
-    if not path.exists():
-        print(f"no profile file {path}", file=sys.stderr)
-        return 1
-    profile = json.loads(path.read_text())
-    if a.sim_accuracy:
-        print(json.dumps(sim_accuracy(profile, 0.3 if a.level == "intra" else 0.5)))
-        return 0
-    rows = build_rows(profile)
+    if a.bench_jsonl:
+        rows = rows_from_bench_lines(l for l in Path(a.bench_jsonl).read_text().splitlines() if l.startswith("{"))
+        title = "measured paths, speed-up over the ring"
+    else:
+        if not a.db:
+            ap.error("one of --db / --bench-jsonl is needed")
+        path = Path(a.db) / f"{a.level}_bsa_exe_plans_profile.json"
+        if not path.exists():
+            print(f"no profile file {path}", file=sys.stderr)
+            return 1
+        profile = json.loads(path.read_text())
+        if a.sim_accuracy:
+            print(json.dumps(sim_accuracy(profile, 0.3 if a.level == "intra" else 0.5)))
+            return 0
+        rows = build_rows(profile)
+        title = f"{a.level}-level plans, speed-up over ring"
     if a.e2e_layers:
         cols = ["CP", "shape", "ring", "zigzag", "stripe", "ultraattn", "speedup_vs_best_baseline"]
         print("| " + " | ".join(cols) + " |")
@@ -216,15 +258,18 @@ def main(argv=None) -> int:
         for r in e2e_rows(rows, a.e2e_layers, a.e2e_const):
             print("| " + " | ".join(_fmt(r.get(c)) for c in cols) + " |")
         return 0
-    print("| " + " | ".join(COLS) + " |")
-    print("|" + "---|" * len(COLS))
+    cols = (["config"] if a.bench_jsonl else []) + [c for c in COLS if not (a.bench_jsonl and c == "fob")]
+    if a.bench_jsonl:
+        cols.insert(cols.index("ultraattn"), "fused")
+    print("| " + " | ".join(cols) + " |")
+    print("|" + "---|" * len(cols))
     for r in rows:
-        print("| " + " | ".join(_fmt(r.get(c)) for c in COLS) + " |")
+        print("| " + " | ".join(_fmt(r.get(c)) for c in cols) + " |")
     if a.svg:
-        Path(a.svg).write_text(bar_chart_svg(rows, title=f"{a.level}-level plans, speed-up over ring"))
+        Path(a.svg).write_text(bar_chart_svg(rows, title=title))
     if a.csv:
         with open(a.csv, "w", newline="") as f:
-            w = csv.DictWriter(f, fieldnames=["key"] + COLS, extrasaction="ignore")
+            w = csv.DictWriter(f, fieldnames=["key"] + COLS + (["fused"] if a.bench_jsonl else []), extrasaction="ignore")
             w.writeheader()
             w.writerows(rows)
     return 0
