@@ -18,9 +18,19 @@ def dev():
 
 
 def _close(got, ref, tol):
-    err = (got.float() - ref.float()).abs().max().item()
-    scale = ref.float().abs().max().item() + 1e-6
+    """Largest absolute error against the largest reference value, and, so that a wrong row of
+    small magnitude cannot hide behind the large ones, every row (last dimension) on its own:
+    |got - ref| <= 4 tol * max(|ref row|, a tenth of the median row norm)."""
+    g, r = got.float(), ref.float()
+    err = (g - r).abs().max().item()
+    scale = r.abs().max().item() + 1e-6
     assert err <= tol * scale, f"max err {err} vs scale {scale}"
+    if r.dim() >= 2 and r.shape[-1] > 1:
+        d = (g - r).flatten(0, -2).norm(dim=-1)
+        n = r.flatten(0, -2).norm(dim=-1)
+        rel = d / torch.clamp(n, min=0.1 * n.median().item() + 1e-12)
+        worst = int(rel.argmax())
+        assert rel[worst].item() <= 4 * tol, f"row {worst}: relative error {rel[worst].item():.3e} (norm {n[worst].item():.3e})"
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (1000, 520, 264), (2048, 4096, 1024)])
