@@ -290,7 +290,11 @@ def main() -> None:
     # ---- end-to-end arm: public API, H2D of the inputs and D2H of the result every step ---------
     # The heads are independent, so the step runs as `--e2e-head-chunks` calls of the public
     # attention function on head groups; a second stream copies the next group's Q/K/V/dO from
-    # pinned memory while the current group computes (only the first group's copy is exposed).
+    # pinned memory while the current group computes. Inside the timed region the first group of
+    # the NEXT step is fetched while the last group of this step computes (what a training loop's
+    # input prefetch does), so only the first timed step's first copy is exposed; nothing is
+    # fetched across the warm-up / timed boundary, so every timed step's bytes cross inside the
+    # timed region.
     e2e = None
     if not args.no_e2e:
         chunks = max(1, min(args.e2e_head_chunks, N_HEADS))
@@ -327,15 +331,24 @@ def main() -> None:
                 ev.record(copy_stream)
             return t, ev
 
+        e2e_steps, e2e_warmup = max(1, min(args.steps, 3)), 3
+        calls = {"n": 0, "ahead": None}
+
         def step_e2e():
             main = torch.cuda.current_stream(dev)
-            copy_stream.wait_stream(main)          # the previous step's tensors are released
-            nxt = fetch(0)
-            acc = 0.0
+            calls["n"] += 1
+            nxt, calls["ahead"] = calls["ahead"], None
+            if nxt is None:
+                copy_stream.wait_stream(main)      # the previous step's tensors are released
+                nxt = fetch(0)
+            # the next step's first group is fetched ahead only from one timed step to the next
+            ahead_ok = e2e_warmup < calls["n"] < e2e_warmup + e2e_steps
             for c in range(chunks):
                 (qd, kd, vd, wd), ev = nxt
                 if c + 1 < chunks:
                     nxt = fetch(c + 1)
+                elif ahead_ok:
+                    calls["ahead"] = fetch(0)
                 main.wait_event(ev)
                 for t in (qd, kd, vd, wd):
                     t.record_stream(main)
@@ -346,10 +359,11 @@ def main() -> None:
                     chk = qd.grad[0, :64].float().sum()
             # the step's scalar result: a checksum over a slice of dQ, read back to the host
             result["v"] = float(chk.cpu())
-        e2e_ms, _ = timed(step_e2e, max(1, min(args.steps, 3)), 3)
+        e2e_ms, _ = timed(step_e2e, e2e_steps, e2e_warmup)
         A.check_status(dev)
         e2e = {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": 4,
-               "checksum": result.get("v"), "head_chunks": chunks}
+               "checksum": result.get("v"), "head_chunks": chunks,
+               "prefetch": "next head group during compute; next step's first group during the last group (timed steps only)"}
 
     if rank == 0:
         vol = pattern.volume * (S / N_BLOCKS) ** 2 * 4 * HEAD_DIM * N_HEADS      # forward model FLOPs
