@@ -136,3 +136,23 @@ def test_plan_restatement_matches_explicit_masks_property():
         assert torch.allclose(dv, v_.grad, atol=1e-4)
 
     check()
+
+
+def test_launch_order_keeps_groups_together_heaviest_first():
+    """Launch order of a table-driven launch: a permutation of the tiles in which the tiles of one
+    block row (column) are adjacent, rows ordered by their heaviest tile, tiles inside a row by
+    weight. Global + local rows all weigh about the same: a pure weight sort would interleave them."""
+    from ultraattn_b200 import patterns as P
+    from ultraattn_b200.ops import attention as A
+    tab = P.global_local(8, 1, 2).block_table_int
+    blk = 1024
+    for plan, n_tiles_per_group in ((A.FwdPlan(A.rows_from_block_table(tab, blk)), blk // A.CTA_ROWS),
+                                    (A.BwdPlan(A.cols_from_block_table(tab, blk)), blk // A.TILE)):
+        tiles = plan.tiles_t.tolist()
+        assert len(tiles) == plan.n_tiles == 8 * n_tiles_per_group
+        assert len({tuple(t) for t in tiles}) == len(tiles)                     # every tile once
+        groups = [g for g, _ in tiles]
+        runs = [g for i, g in enumerate(groups) if i == 0 or groups[i - 1] != g]
+        assert len(runs) == len(set(runs)) == 8                                  # each group is one run
+    order = A._launch_order([(5, 0, 0), (9, 1, 0), (7, 1, 1), (6, 2, 0), (5, 0, 1)])
+    assert order == [(9, 1, 0), (7, 1, 1), (6, 2, 0), (5, 0, 0), (5, 0, 1)]
