@@ -203,6 +203,33 @@ def test_attention_accumulate_and_add_modes(dev):
     _close(dv, dv_r, 2e-2)
 
 
+@pytest.mark.parametrize("T,V,ld", [(300, 32000, 32000), (64, 1000, 1024)])
+def test_token_cross_entropy(dev, T, V, ld):
+    """Fused cross-entropy over bf16 logits (strided rows, an ignored target): log-sum-exp and loss
+    against fp32 PyTorch, and the in-place gradient g * (softmax - one-hot)."""
+    from ultraattn_b200.ops import elementwise as E
+    torch.manual_seed(5)
+    store = torch.randn(T, ld, device=dev) * 4
+    logits = store.to(torch.bfloat16)[:, :V]
+    targets = torch.randint(0, V, (T,), device=dev)
+    targets[3] = -100
+    ref = logits.float()
+    lse_r = torch.logsumexp(ref, dim=-1)
+    ok = targets >= 0
+    loss_r = torch.where(ok, lse_r - ref.gather(1, targets.clamp(min=0)[:, None]).squeeze(1), torch.zeros_like(lse_r))
+    lse, loss = E.xent_fwd(logits, targets)
+    assert (lse - lse_r).abs().max().item() < 1e-3 and (loss - loss_r).abs().max().item() < 1e-3
+    g = torch.tensor(0.37, device=dev)
+    p = torch.softmax(ref, dim=-1)
+    p[torch.arange(T, device=dev)[ok], targets[ok]] -= 1.0
+    want = p * 0.37 * ok[:, None]
+    work = logits.clone() if ld == V else logits       # the strided view is updated in place inside `store`'s copy
+    got = E.xent_bwd_(work, targets, lse, g)
+    assert got.data_ptr() == work.data_ptr()
+    _close(got, want, 1e-2)
+    assert got[3].abs().max().item() == 0.0
+
+
 def test_tensor_maps_are_encoded_once_per_buffer(dev):
     """A repeated launch over the same buffers finds all of its TMA tensor maps in the library's
     cache; a launch over other buffers of the same shape encodes new ones and computes from them."""

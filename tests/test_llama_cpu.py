@@ -85,3 +85,25 @@ def test_memory_plan_of_the_headline_training_config():
     assert abs((m["device_total"] - off["device_total"]) - m["checkpoints_device"]) < 1e-9
     small = estimate_memory(LlamaConfig(n_layers=4), 65536, 2)
     assert 15 < small["device_total"] < 30                     # a run of this size peaked at 18.4 GiB per GPU
+
+
+def test_token_cross_entropy_wrappers_match_pytorch():
+    """The loss head's two fused passes (CPU restatement of the CUDA kernels): loss and in-place
+    gradient against torch.nn.functional.cross_entropy, with an ignored target."""
+    import torch
+    import torch.nn.functional as F
+    from ultraattn_b200.ops import elementwise as E
+    torch.manual_seed(0)
+    T, V = 16, 40
+    logits = torch.randn(T, V)
+    tg = torch.randint(0, V, (T,))
+    tg[2] = -1
+    keep = tg >= 0
+    lse, loss = E.xent_fwd(logits, tg)
+    ref = F.cross_entropy(logits, tg.clamp(min=0), reduction="none") * keep
+    assert torch.allclose(loss, ref, atol=1e-5) and torch.allclose(lse, torch.logsumexp(logits, -1), atol=1e-6)
+    x = logits.clone().requires_grad_()
+    ((F.cross_entropy(x, tg.clamp(min=0), reduction="none") * keep).sum() * 0.5).backward()
+    work = logits.clone()
+    got = E.xent_bwd_(work, tg, lse, torch.tensor(0.5))
+    assert got is work and torch.allclose(got, x.grad, atol=1e-6) and got[2].abs().max() == 0

@@ -51,6 +51,8 @@ def _declare(lib):
                         POINTER(UaTensorSrc), POINTER(UaTensorSrc), i, POINTER(UaBwdKvOut), i,
                         vp, vp, vp, i, i, i, i, f, vp, vp, i, i, vp, i, vp, vp],
         "ua_barrier": [POINTER(vp), i, i, i, ctypes.c_uint, ctypes.c_double, vp, vp],
+        "ua_xent_fwd": [vp, vp, vp, vp, l, l, i, vp],
+        "ua_xent_bwd": [vp, vp, vp, vp, l, l, i, vp],
         "ua_peer_add_f32": [vp, vp, l, i, i, vp],
         "ua_peer_pull": [vp, vp, l, i, vp],
         "ua_multimem_bcast": [vp, vp, l, i, vp],

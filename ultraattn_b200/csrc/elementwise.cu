@@ -5,7 +5,9 @@
 //   * D = rowsum(dO * O), the "softmax_d" input of the backward
 //     (orchestrated_attn/utils.py:148-188 carries it inside Input_Row_Bwd),
 //   * fp32 -> bf16 conversion of gradient accumulators,
-//   * RMSNorm, rotary embedding, SwiGLU (forward and backward) and a fused Adam step.
+//   * RMSNorm, rotary embedding, SwiGLU (forward and backward), the token cross-entropy over bf16
+//     logits (forward: log-sum-exp and loss per token; backward: softmax minus one-hot, in place)
+//     and a fused Adam step.
 // All of them are one pass over HBM with 16-byte accesses.
 #include "host_common.cuh"
 #include "ptx.cuh"
@@ -608,6 +610,82 @@ adam_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Token cross-entropy over bf16 logits [T, V] (V a multiple of 8, rows 16-byte aligned). One block
+// per token. Forward: lse[t] = log sum_v exp(logit[t, v]) by an online (max, sum) pass with 16-byte
+// loads, loss[t] = lse[t] - logit[t, target[t]]. Backward, in place over the logits:
+// d[t, v] = g * (exp(logit[t, v] - lse[t]) - [v == target[t]]), rounded to bf16. The logits are
+// read once per pass and never exist in fp32 in memory.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+xent_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
+                float* __restrict__ lse, float* __restrict__ loss, long ld, int V) {
+  const long t = blockIdx.x;
+  const uint4* row = reinterpret_cast<const uint4*>(logits + t * ld);
+  float m = -INFINITY, sum = 0.f;
+  for (int i = threadIdx.x; i < V / 8; i += blockDim.x) {
+    const uint4 q = row[i];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    float x[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { x[2 * k] = bf_lo(w[k]); x[2 * k + 1] = bf_hi(w[k]); }
+    float mx = x[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) mx = fmaxf(mx, x[k]);
+    if (mx == -INFINITY) continue;                       // eight masked-out entries add nothing
+    if (mx > m) { sum *= __expf(m - mx); m = mx; }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sum += __expf(x[k] - m);
+  }
+  // combine the (max, sum) pairs: inside a warp by shuffles, across warps through shared memory
+  __shared__ float sm[8], ss[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xFFFFFFFFu, m, o);
+    const float s2 = __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    const float mn = fmaxf(m, m2);
+    sum = (mn == -INFINITY) ? 0.f : sum * __expf(m - mn) + s2 * __expf(m2 - mn);
+    m = mn;
+  }
+  if ((threadIdx.x & 31) == 0) { sm[threadIdx.x >> 5] = m; ss[threadIdx.x >> 5] = sum; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float mt = sm[0], st = ss[0];
+    for (int wv = 1; wv < static_cast<int>(blockDim.x >> 5); ++wv) {
+      const float mn = fmaxf(mt, sm[wv]);
+      st = (mn == -INFINITY) ? 0.f : st * __expf(mt - mn) + ss[wv] * __expf(sm[wv] - mn);
+      mt = mn;
+    }
+    const float l = mt + __logf(st);
+    lse[t] = l;
+    const int tg = targets[t];
+    loss[t] = (tg >= 0 && tg < V) ? l - __bfloat162float(logits[t * ld + tg]) : 0.f;   // ignored target: no loss
+  }
+}
+
+__global__ void __launch_bounds__(256)
+xent_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
+                const float* __restrict__ lse, const float* __restrict__ g, long ld, int V) {
+  const long t = blockIdx.x;
+  uint4* row = reinterpret_cast<uint4*>(logits + t * ld);
+  const float l = lse[t];
+  const int tg = targets[t];
+  const float scale = (tg >= 0 && tg < V) ? *g : 0.f;
+  for (int i = threadIdx.x; i < V / 8; i += blockDim.x) {
+    const uint4 q = row[i];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float a = __expf(bf_lo(w[k]) - l), b = __expf(bf_hi(w[k]) - l);
+      if (i * 8 + 2 * k == tg) a -= 1.f;
+      if (i * 8 + 2 * k + 1 == tg) b -= 1.f;
+      o[k] = pack_bf16x2(a * scale, b * scale);
+    }
+    row[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 }  // namespace ua
 
 using namespace ua;
@@ -804,6 +882,27 @@ extern "C" int ua_adam(float* master, float* m, float* v, const void* grad, void
   adam_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(
       master, m, v, static_cast<const __nv_bfloat16*>(grad), static_cast<__nv_bfloat16*>(param), n,
       lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ua_xent_fwd(const void* logits, const int* targets, float* lse, float* loss, long tokens,
+                           long ld, int V, cudaStream_t stream) {
+  if (V % 8 != 0 || ld % 8 != 0) UA_FAIL("ua_xent_fwd: vocabulary and row stride must be multiples of 8");
+  if (tokens == 0) return 0;
+  xent_fwd_kernel<<<static_cast<unsigned>(tokens), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(logits), targets, lse, loss, ld, V);
+  UA_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// In place: logits become g * (softmax - one-hot); g is a device scalar (the incoming gradient).
+extern "C" int ua_xent_bwd(void* logits, const int* targets, const float* lse, const float* g, long tokens,
+                           long ld, int V, cudaStream_t stream) {
+  if (V % 8 != 0 || ld % 8 != 0) UA_FAIL("ua_xent_bwd: vocabulary and row stride must be multiples of 8");
+  if (tokens == 0) return 0;
+  xent_bwd_kernel<<<static_cast<unsigned>(tokens), 256, 0, stream>>>(
+      static_cast<__nv_bfloat16*>(logits), targets, lse, g, ld, V);
   UA_CUDA(cudaGetLastError());
   return 0;
 }

@@ -487,19 +487,14 @@ class _ChunkLoss(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, h, w, targets):
-        logits = G.gemm(h, w).float()
-        lse = torch.logsumexp(logits, dim=-1)
-        loss = (lse - logits.gather(1, targets[:, None].long()).squeeze(1)).sum()
+        lse, rows = E.xent_fwd(G.gemm(h, w), targets)        # one pass over the bf16 logits
         ctx.save_for_backward(h, w, targets, lse)
-        return loss
+        return rows.sum()
 
     @staticmethod
     def backward(ctx, g):
         h, w, targets, lse = ctx.saved_tensors
-        logits = G.gemm(h, w).float()
-        p = torch.exp(logits - lse[:, None])
-        p.scatter_add_(1, targets[:, None].long(), -torch.ones_like(lse)[:, None])
-        dl = (p * g).to(h.dtype)
+        dl = E.xent_bwd_(G.gemm(h, w), targets, lse, g)     # logits again, turned into their gradient in place
         dh = G.gemm(dl, w, b_is_kn=True)
         dw = G.gemm(dl, h, a_is_km=True, b_is_kn=True)
         return dh, dw, None

@@ -209,6 +209,45 @@ def adam_step(master, m, v, grad, param, lr, beta1, beta2, eps, wd, step, grad_s
     _lib.check(rc, "ua_adam")
 
 
+def xent_fwd(logits: torch.Tensor, targets: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Token cross-entropy over ``logits [T, V]``: (lse [T], loss [T]) in fp32, loss =
+    lse - logit[target] (0 where the target is outside ``[0, V)``). bf16 logits on CUDA are read
+    once by this framework's kernel; anything else runs in PyTorch."""
+    T, V = logits.shape
+    if logits.is_cuda and logits.dtype == torch.bfloat16 and logits.stride(1) == 1:
+        tg = targets.to(torch.int32).contiguous()
+        lse = torch.empty(T, dtype=torch.float32, device=logits.device)
+        loss = torch.empty(T, dtype=torch.float32, device=logits.device)
+        rc = _lib.load().ua_xent_fwd(logits.data_ptr(), tg.data_ptr(), lse.data_ptr(), loss.data_ptr(), T,
+                                     logits.stride(0), V, _stream(logits))
+        _lib.check(rc, "ua_xent_fwd")
+        return lse, loss
+    lf = logits.float()
+    lse = torch.logsumexp(lf, dim=-1)
+    ok = (targets >= 0) & (targets < V)
+    picked = lf.gather(1, targets.clamp(0, V - 1)[:, None].long()).squeeze(1)
+    return lse, torch.where(ok, lse - picked, torch.zeros_like(lse))
+
+
+def xent_bwd_(logits: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """In place: ``logits`` becomes ``g * (softmax(logits) - one_hot(targets))`` (``g``: scalar
+    tensor, the gradient of the summed loss); rows with a target outside ``[0, V)`` become zero.
+    Returns ``logits``."""
+    T, V = logits.shape
+    if logits.is_cuda and logits.dtype == torch.bfloat16 and logits.stride(1) == 1:
+        tg = targets.to(torch.int32).contiguous()
+        gs = g.detach().to(torch.float32).reshape(1).contiguous()
+        rc = _lib.load().ua_xent_bwd(logits.data_ptr(), tg.data_ptr(), lse.data_ptr(), gs.data_ptr(), T,
+                                     logits.stride(0), V, _stream(logits))
+        _lib.check(rc, "ua_xent_bwd")
+        return logits
+    p = torch.exp(logits.float() - lse[:, None])
+    ok = (targets >= 0) & (targets < V)
+    p.scatter_add_(1, targets.clamp(0, V - 1)[:, None].long(), -torch.ones_like(lse)[:, None])
+    logits.copy_((p * g.float() * ok[:, None]).to(logits.dtype))
+    return logits
+
+
 def peer_add_(dst: torch.Tensor, src: torch.Tensor, zero_src: bool = False) -> None:
     """dst += src for contiguous fp32 tensors; ``dst`` may be a view of a peer GPU's memory
     (this framework's own kernel does the adds — library kernels never touch peer memory)."""
