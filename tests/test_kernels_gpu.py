@@ -273,6 +273,27 @@ def test_autograd_api(dev):
     _close(v.grad, dv, 2e-2)
 
 
+def test_head_dim_64_runs_zero_padded(dev):
+    """Head dim 64 on the GPU: the operator pads to the kernels' 128, keeps the scale of the true
+    head dim and returns outputs and gradients of the true shape."""
+    import ultraattn_b200 as ua
+    from ultraattn_b200 import patterns as P
+    torch.manual_seed(8)
+    S, H, D = 1024, 2, 64
+    pat = P.global_local(4, 1, 2)
+    q, k, v = (torch.randn(1, S, H, D, device=dev, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+    d_o = torch.randn(1, S, H, D, device=dev, dtype=torch.bfloat16)
+    o = ua.attention(q, k, v, pat)
+    assert o.shape == (1, S, H, D)
+    o.backward(d_o)
+    o_r, _, dq_r, dk_r, dv_r = P.dense_attention_with_grads(q.detach().float().cpu(), k.detach().float().cpu(),
+                                                            v.detach().float().cpu(), d_o.float().cpu(), pat)
+    _close(o.detach().cpu(), o_r, 1.5e-2)
+    for got, ref in ((q.grad, dq_r), (k.grad, dk_r), (v.grad, dv_r)):
+        assert got.shape == (1, S, H, D)
+        _close(got.cpu(), ref, 2e-2)
+
+
 def test_lse_merge(dev):
     from ultraattn_b200.ops import elementwise as E
     torch.manual_seed(5)

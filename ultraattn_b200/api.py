@@ -76,13 +76,23 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pattern: BSA_Re
               softmax_scale: Optional[float] = None, runtime=None) -> torch.Tensor:
     """Block-sparse attention ``softmax(mask(Q K^T) * scale) V`` with autograd.
 
-    ``q, k, v``: ``[batch, tokens, heads, head_dim]`` (bf16 with head_dim 128 on CUDA; any float
-    type and head dim on CPU). Without ``runtime`` the tensors hold the whole sequence and the call
+    ``q, k, v``: ``[batch, tokens, heads, head_dim]`` (bf16 on CUDA, head_dim 128 native and smaller
+    head dims zero-padded to it; any float type and head dim on CPU). Without ``runtime`` the tensors hold the whole sequence and the call
     runs on this device alone. With a :class:`ultraattn_b200.runtime.ContextParallelAttention`
     (``runtime=``) they hold this rank's shard and the call is context-parallel over its group.
     """
     if runtime is not None:
         return runtime(q, k, v, softmax_scale)
+    D = q.shape[-1]
+    if q.is_cuda and D < A.KERNEL_HEAD_DIM:
+        # The kernels are built for head dim 128. A smaller head dim runs zero-padded: the padding
+        # adds nothing to Q K^T, the padded output columns are zero and are cut off again, and
+        # autograd drops the padding's gradients (the scale stays that of the true head dim).
+        # Correct, at the cost of the 128-wide tiles.
+        pad = A.KERNEL_HEAD_DIM - D
+        scale = softmax_scale if softmax_scale is not None else D ** -0.5
+        qp, kp, vp = (torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v))
+        return _LocalAttention.apply(qp, kp, vp, pattern, scale)[..., :D]
     return _LocalAttention.apply(q, k, v, pattern, softmax_scale)
 
 

@@ -27,6 +27,7 @@ from .. import _lib
 
 TILE = 128
 CTA_ROWS = 256
+KERNEL_HEAD_DIM = 128          # head dim the sm_100a kernels are built for
 
 
 @dataclass(frozen=True)
