@@ -118,6 +118,54 @@ def test_plans_verify(plan_type, fob):
         assert p2.end_time == plan.end_time and len(p2.gpu_kernel_lists) == cp
         plain = plan.to_plain()
         assert len(plain["kernels"]) == len(plan.valid_kernels)
+        # the JSON side-car alone gives back a plan that passes the same static checks
+        import json
+        rebuilt = Execution_Plan.from_plain(json.loads(json.dumps(plain)))
+        assert rebuilt.verify() == [] and rebuilt.end_time == plan.end_time
+
+
+def test_objects_pickled_by_the_reference_load_into_these_classes():
+    """Plans pickled by the reference name ``search_algo.*`` classes, which resolve to this
+    framework's: its pattern object carries ``block_table`` / ``cmap`` (+ derived tables) under its
+    own attribute names and is rebuilt from those two; kernel keys carry NumPy integers, which the
+    JSON side-car turns into plain ones. (A whole plan pickled by the unmodified reference on the
+    headline config was loaded, verified, exported and rebuilt this way by hand.)"""
+    import json
+    from ultraattn_b200.patterns.blocks import BSA_Repr, Block_Type
+    from ultraattn_b200.planner.schedule import _plain
+    ours = P.strided(8, 4, 2)
+    enum_table = np.vectorize(Block_Type)(ours.block_table_int).astype(object)
+    state = {"block_table": enum_table, "block_table_raw": enum_table, "cmap": None, "cmap_raw": None,
+             "block_table_Par_D": None, "cmap_Par_D": None, "minimum_Par_D": 8}
+    loaded = BSA_Repr.__new__(BSA_Repr)
+    loaded.__setstate__(state)
+    assert str(loaded) == str(ours) and (loaded.table == ours.table).all() and loaded.minimum_Par_D == 8
+    again = pickle.loads(pickle.dumps(loaded))                       # own pickles keep working
+    assert str(again) == str(ours)
+    key = (0, 0, np.int32(3), (np.int64(1), 2), "i", "r")
+    assert json.loads(json.dumps(_plain(key))) == [0, 0, 3, [1, 2], "i", "r"]
+
+
+def test_plan_pickles_name_only_classes_the_reference_has():
+    """The other direction: a plan pickled here names ``search_algo.*`` classes only (nothing of
+    this package), its pattern travels in the reference's attribute layout, and what was attached
+    for this framework's own use (the allocation record, the machine profile's transport table)
+    comes back intact. (The unmodified reference loaded such a pickle and printed its schedule.)"""
+    from ultraattn_b200.planner import make_plan, bind_reference_class_paths
+    if not bind_reference_class_paths():
+        pytest.skip("the search_algo modules of this distribution are not importable")
+    plan = make_plan(P.strided(8, 4, 2), 4, 65536, 8, fob=0, plan_type="Flexflow", time_limit=5.0)
+    data = pickle.dumps(plan)
+    assert b"ultraattn_b200" not in data and b"search_algo.execute_plan" in data
+    state = plan.d_graph.schedule.da_config.bsa_config.bsa_repr.__getstate__()
+    assert set(state) == {"block_table", "cmap", "block_table_raw", "cmap_raw", "block_table_Par_D", "cmap_Par_D",
+                          "minimum_Par_D"}
+    assert state["block_table"].dtype == object and state["block_table"][0, 0].name == "CAUSAL"
+    back = pickle.loads(data)
+    assert back.verify() == [] and back.end_time == plan.end_time
+    assert type(back.allocation).__name__ == "Allocation" and (back.allocation.table == plan.allocation.table).all()
+    ft = back.d_graph.schedule.m_config.fused_transports
+    assert type(ft).__name__ == "Fused_Transport_Profile" and len(ft.records) == len(plan.d_graph.schedule.m_config.fused_transports.records)
 
 
 def test_kernel_tile_fusion():

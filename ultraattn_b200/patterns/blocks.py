@@ -128,6 +128,23 @@ class BSA_Repr:
         self.cmap_raw = self._coarsen_cmap()
         self.minimum_Par_D = self.table.shape[0]
 
+    def __getstate__(self) -> dict:
+        """Pickled with the attribute names and value types of the reference's class (tables of
+        ``Block_Type``, ``block_table_raw`` / ``cmap_raw``, the two ``*_Par_D`` slots), so that a
+        plan written here is usable after the reference loads it; :meth:`__setstate__` rebuilds
+        this class's own fields from ``block_table`` and ``cmap``."""
+        return {"block_table": self.block_table, "cmap": self.cmap, "block_table_raw": self.block_table_raw,
+                "cmap_raw": self.cmap_raw, "block_table_Par_D": None, "cmap_Par_D": None,
+                "minimum_Par_D": self.minimum_Par_D}
+
+    def __setstate__(self, state: dict) -> None:
+        """A pattern pickled here or by the reference (inside one of its plans): both carry
+        ``block_table`` / ``cmap``; everything else is derived again."""
+        if "block_table_int" not in state and "block_table" in state:
+            self.__init__(state["block_table"], state.get("cmap"))
+            return
+        self.__dict__.update(state)
+
     # -- reference-compatible views -------------------------------------------------------------
     @property
     def block_table(self) -> np.ndarray:

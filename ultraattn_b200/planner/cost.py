@@ -321,6 +321,18 @@ class Machine_Config:
         self.comm_profile_maps = comm_profile_maps or [Comm_Profile_Map(), Comm_Profile_Map()]
         self.fused_transports = fused_transports or Fused_Transport_Profile()
 
+    def __getstate__(self) -> dict:
+        """The transport table travels as its plain records: a pickled plan (which carries its
+        machine profile) then names no class that the reference does not have."""
+        state = dict(self.__dict__)
+        ft = state.pop("fused_transports", None)
+        state["fused_transport_records"] = list(ft.records) if ft is not None else []
+        return state
+
+    def __setstate__(self, state: dict) -> None:
+        self.__dict__.update(state)
+        self.fused_transports = Fused_Transport_Profile(self.__dict__.pop("fused_transport_records", []))
+
     @classmethod
     def b200_default(cls) -> "Machine_Config":
         """The machine profile shipped with the package (``data/m_configs/B200``: the kernel grid

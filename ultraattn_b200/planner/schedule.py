@@ -316,6 +316,26 @@ class Execution_Plan:
                     return False
         return True
 
+    # ------------------------------- pickling ----------------------------------------------------
+    def __getstate__(self) -> dict:
+        """Pickles name only classes the reference has too (``search_algo.*`` paths), so that it can
+        load plans written here: the allocation record attached by ``make_plan`` goes in as a plain
+        dict and comes back as an ``Allocation`` when this class loads it."""
+        state = dict(self.__dict__)
+        al = state.get("allocation")
+        if al is not None and not isinstance(al, dict):
+            state["allocation"] = {"Par_D": int(al.Par_D), "cmap": np.asarray(al.cmap), "table": np.asarray(al.table),
+                                   "comm_volume": float(al.comm_volume), "comp_max": float(al.comp_max),
+                                   "status": str(al.status)}
+        return state
+
+    def __setstate__(self, state: dict) -> None:
+        self.__dict__.update(state)
+        al = state.get("allocation")
+        if isinstance(al, dict):
+            from .allocate import Allocation
+            self.allocation = Allocation(**al)
+
     # ------------------------------- verification ------------------------------------------------
     def verify(self) -> list:
         """Static checks of a finished plan; returns a list of problems (empty = fine)."""
@@ -374,24 +394,24 @@ class Execution_Plan:
         kern = []
         for v in self.valid_kernels:
             kern.append({
-                "id": v.id, "key": _plain(v.key), "type": v.type,
+                "id": int(v.id), "key": _plain(v.key), "type": v.type,
                 "time": [float(v.time[0]), float(v.time[1])], "start": float(v._start_time),
-                "precursors": sorted(u.id for u in v.precursors),
+                "precursors": sorted(int(u.id) for u in v.precursors),
                 "units": [float(x) for x in v.units] if v.type == "comm" else None,
             })
         sch = self.d_graph.schedule
         return {
             "format": "ultraattn-plan/1", "fob": fob, "plan_type": self.plan_type,
             "end_time": float(self.end_time), "stream_num": 3,
-            "da_config": {"SP": list(self.da_config.SP), "S": list(self.da_config.S),
-                          "Nh": list(self.da_config.Nh), "bs": self.da_config.bs, "D": self.da_config.D,
-                          "hierarchy": self.da_config.hierarchy,
+            "da_config": {"SP": _plain(self.da_config.SP), "S": _plain(self.da_config.S),
+                          "Nh": _plain(self.da_config.Nh), "bs": int(self.da_config.bs), "D": int(self.da_config.D),
+                          "hierarchy": int(self.da_config.hierarchy),
                           "bsa_config": str(self.da_config.bsa_config)},
-            "split_degrees": list(sch.split_degrees),
+            "split_degrees": _plain(sch.split_degrees),
             "S_map": np.asarray(sch.S_map).tolist(),
             "schedule_table": np.asarray(sch.schedule_table).tolist(),
             "kernels": kern,
-            "gpu_kernel_lists": [[k.id for k in lst] for lst in self.gpu_kernel_lists],
+            "gpu_kernel_lists": [[int(k.id) for k in lst] for lst in self.gpu_kernel_lists],
         }
 
     def to_json(self, path) -> None:
@@ -448,8 +468,12 @@ class Execution_Plan:
         sch.split_degrees = tuple(d["split_degrees"])
         sch.S_map, sch.schedule_table = np.asarray(d["S_map"]), np.asarray(d["schedule_table"])
 
-        class _Graph:
-            pass
+        from .graph import Dependent_Graph
+
+        class _Graph:               # the graph as far as executors, the simulator and verify() use it
+            def valid_kernels(self):
+                return list(self.kernel_dict.values())
+            is_acyclic = Dependent_Graph.is_acyclic
         g = _Graph()
         g.schedule, g.fob, g.da_config, g.m_config = sch, d["fob"], da, None
         g.split_degrees, g.hierarchy, g.hierarchy_sp, g.tot_sp = sch.split_degrees, da.hierarchy, da.hierarchy_sp, da.tot_sp
@@ -470,7 +494,14 @@ class Execution_Plan:
 
 
 def _plain(key):
-    return [list(x) if isinstance(x, tuple) else x for x in key]
+    """A kernel key as plain JSON values (keys built by the reference carry NumPy integers)."""
+    def one(x):
+        if isinstance(x, (tuple, list)):
+            return [one(y) for y in x]
+        if isinstance(x, np.generic):
+            return x.item()
+        return x
+    return [one(x) for x in key]
 
 
 def create_one_node_exe_plan(fob: int, comp_time: float = 1.0) -> Execution_Plan:
