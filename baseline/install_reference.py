@@ -34,13 +34,20 @@ def _ignore(src_root: str):
 
 
 def main() -> None:
-    if len(sys.argv) != 2:
+    if len(sys.argv) != 2 or sys.argv[1].startswith("-"):
         raise SystemExit(__doc__)
     src = os.path.abspath(sys.argv[1])
+    if not os.path.isdir(os.path.join(src, "search_algo")) or not os.path.isdir(os.path.join(src, "orchestrated_attn")):
+        raise SystemExit(f"{src} is not a checkout of the reference (no search_algo/ and orchestrated_attn/ in it); "
+                         "nothing was changed")
     dst = os.path.join(HERE, "_ref")
+    tmp = dst + ".new"
+    if os.path.isdir(tmp):
+        shutil.rmtree(tmp)
+    shutil.copytree(src, tmp, ignore=_ignore(src), symlinks=False)     # the old copy goes only once the new one is complete
     if os.path.isdir(dst):
         shutil.rmtree(dst)
-    shutil.copytree(src, dst, ignore=_ignore(src), symlinks=False)
+    os.rename(tmp, dst)
     for root, dirs, files in os.walk(dst):          # the source may be read-only; the copy is not
         for d in dirs:
             os.chmod(os.path.join(root, d), 0o755)
