@@ -410,3 +410,23 @@ def test_every_reference_module_path_imports_and_exports():
         m = importlib.import_module(mod)
         missing += [f"{mod}.{n}" for n in names if not hasattr(m, n)]
     assert not missing, missing
+
+
+def test_kernel_trace_summary_on_a_synthetic_launch():
+    """`utils.kernel_trace.summarize` on a hand-made trace: 4 SMs, two waves of 1 ms CTAs, the first
+    wave spends 0.2 ms copying, one SM gets a third CTA (the tail)."""
+    import numpy as np
+    from ultraattn_b200.utils.kernel_trace import summarize
+    ms = 1_000_000
+    rows = []
+    for sm in range(4):
+        rows.append((0, int(0.2 * ms), 1 * ms, sm << 32 | sm))                 # first wave: copies, then computes
+        rows.append((1 * ms, 1 * ms + 500, 2 * ms, sm << 32 | (4 + sm)))       # second wave: no copying
+    rows.append((2 * ms, 2 * ms, 3 * ms, 0 << 32 | 8))                          # tail on SM 0
+    out = summarize(np.array(rows, dtype=np.int64), n_sms=4)
+    assert out["ctas"] == 9 and out["span_ms"] == 3.0
+    assert out["ctas_that_copied"] == 4 and out["staging_sm_ms_total"] == 0.8 and out["staging_done_ms_after_start"] == 0.2
+    assert out["longest_cta_ms"] == 1.0 and out["last_cta_start_ms"] == 2.0
+    assert out["tail_ms_under_half_sms"] == 1.0                               # three of four SMs are done at 2 ms
+    assert abs(out["sm_busy_fraction"] - 9 / 12) < 1e-4
+    assert summarize(np.zeros((0, 4), dtype=np.int64)) == {"ctas": 0}
