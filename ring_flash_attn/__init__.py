@@ -11,5 +11,8 @@ from ultraattn_b200.parallel.ring import (ring_flash_attn_func, ring_flash_attn_
                                           zigzag_ring_flash_attn_varlen_func,
                                           zigzag_ring_flash_attn_varlen_kvpacked_func,
                                           zigzag_ring_flash_attn_varlen_qkvpacked_func)
-from ultraattn_b200.parallel.ring import ring_backward as ring_flash_attn_backward  # noqa: F401
-from ultraattn_b200.parallel.ring import ring_forward as ring_flash_attn_forward  # noqa: F401
+from ultraattn_b200.parallel.ring import (RingFlashAttnFunc, RingFlashAttnVarlenFunc, StripeFlashAttnFunc,  # noqa: F401
+                                          ZigZagRingFlashAttnFunc, ZigZagRingFlashAttnVarlenFunc,
+                                          ring_flash_attn_backward, ring_flash_attn_forward,
+                                          stripe_flash_attn_backward, stripe_flash_attn_forward,
+                                          zigzag_ring_flash_attn_backward, zigzag_ring_flash_attn_forward)

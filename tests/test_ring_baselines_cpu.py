@@ -232,3 +232,89 @@ def test_lightseq_attention_world4():
     for r in range(4):
         assert isinstance(ret[r], float), ret[r]
         assert ret[r] < 2e-4, (r, ret[r])
+
+
+def _ref_names_worker(rank, world, port, ret):
+    """The strategies through the reference's module paths, function names and argument lists."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ultraattn_b200 import parallel as PL, patterns as P
+        from ring_flash_attn.ring_flash_attn import ring_flash_attn_backward, ring_flash_attn_forward
+        from ring_flash_attn.zigzag_ring_flash_attn import ZigZagRingFlashAttnFunc
+        from ring_flash_attn.stripe_flash_attn import StripeFlashAttnFunc
+        from ring_flash_attn.ring_flash_attn_varlen import RingFlashAttnVarlenFunc
+        from head_parallel_attn.deepspeed_ulysses_attn import DeepSpeedUlyssesAttnFunc
+        from hierarchy_attn.hierarchy_attn_impl import HierarchyAttnFunc
+        from hierarchy_attn.utils import InterComm, IntraComm
+        S, H, D = 256, 4, 16
+        g = torch.Generator().manual_seed(0)
+        q, k, v, d_o = (torch.randn(1, S, H, D, generator=g) for _ in range(4))
+        out = {}
+        o_ref, _, dq, dk, dv = P.dense_attention_with_grads(q, k, v, d_o, P.causal(1))
+
+        def err(kind, o, grads):
+            sh = lambda t: PL.shard_sequence(t, rank, world, kind)
+            return max([(o - sh(o_ref)).abs().max().item()] +
+                       [(a - sh(b)).abs().max().item() for a, b in zip(grads, (dq, dk, dv))])
+
+        # kernel-level pair: positional arguments as in the reference
+        sh = lambda t: PL.shard_sequence(t, rank, world, "ring")
+        o, lse = ring_flash_attn_forward(None, sh(q), sh(k), sh(v), D ** -0.5, 0, True)
+        out["ring fwd/bwd"] = err("ring", o, ring_flash_attn_backward(None, sh(d_o), sh(q), sh(k), sh(v), o, lse,
+                                                                    D ** -0.5, 0, True))
+        # autograd classes: apply(q, k, v, dropout_p, scale, causal, window, alibi, deterministic, return_softmax, group, ...)
+        for kind, cls, extra in (("zigzag", ZigZagRingFlashAttnFunc, (None, None, False)),
+                                 ("stripe", StripeFlashAttnFunc, (None,)),
+                                 ("ulysses", DeepSpeedUlyssesAttnFunc, (None,))):
+            sh = lambda t, kind=kind: PL.shard_sequence(t, rank, world, kind)
+            ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
+            res = cls.apply(ql, kl, vl, 0.0, None, True, (-1, -1), None, False, kind == "stripe", *extra)
+            o = res[0] if isinstance(res, tuple) else res
+            o.backward(sh(d_o))
+            out[cls.__name__] = err(kind, o, (ql.grad, kl.grad, vl.grad))
+        # two-level class on a 2 x 2 arrangement (queries visit the other node)
+        groups = PL.create_hierarchy_groups(tasks_per_node=2)
+        sh = lambda t: PL.shard_sequence(t, rank, world, "zigzag")
+        ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
+        o = HierarchyAttnFunc.apply(ql, kl, vl, 0.0, None, True, (-1, -1), None, False, False, groups, None, True)
+        o.backward(sh(d_o))
+        out["HierarchyAttnFunc"] = err("zigzag", o, (ql.grad, kl.grad, vl.grad))
+        # packed batch through the varlen class
+        full_cu = [0, 96, 256]
+        tq, tk, tv, tdo = (torch.randn(full_cu[-1], H, D, generator=g) for _ in range(4))
+        ref = _dense_packed(tq, tk, tv, tdo, full_cu, True)
+        shp = lambda t: PL.shard_packed(t, full_cu, rank, world, "ring")[0]
+        local_cu = PL.shard_packed(tq, full_cu, rank, world, "ring")[1]
+        ql, kl, vl = (shp(t).requires_grad_() for t in (tq, tk, tv))
+        o = RingFlashAttnVarlenFunc.apply(ql, kl, vl, torch.tensor(local_cu),
+                                          max(b - a for a, b in zip(local_cu, local_cu[1:])), 0.0, None, True,
+                                          (-1, -1), None, False, False, None)
+        o.backward(shp(tdo))
+        out["RingFlashAttnVarlenFunc"] = max((a - shp(b)).abs().max().item()
+                                             for a, b in zip((o, ql.grad, kl.grad, vl.grad), ref))
+        # communicator classes of hierarchy_attn.utils: one ring shift, one query visit
+        ring = IntraComm(groups)
+        t = torch.full((4,), float(rank))
+        got = ring.send_recv(t)
+        ring.commit(); ring.wait()
+        inter = InterComm(groups)
+        visitor = inter.send_recv_q(0, t)
+        inter.commit(); inter.wait()
+        node, local = rank // 2, rank % 2
+        ok_ring = got[0].item() == node * 2 + (local - 1) % 2
+        ok_inter = (visitor is None) if node == 1 else visitor[0].item() == rank + 2    # node 1 sends to node 0
+        out["comm classes"] = 0.0 if (ok_ring and ok_inter) else 1.0
+        ret[rank] = out
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_reference_module_paths_and_argument_lists_world4():
+    ret = mp.Manager().dict()
+    mp.spawn(_ref_names_worker, args=(4, 29900 + os.getpid() % 90, ret), nprocs=4, join=True)
+    _check(ret, 4)

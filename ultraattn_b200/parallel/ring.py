@@ -363,6 +363,135 @@ zigzag_ring_flash_attn_varlen_qkvpacked_func, zigzag_ring_flash_attn_varlen_kvpa
 
 
 # -------------------------------------------------------------------------------------------------
+# The per-strategy forward / backward functions and autograd classes under the reference's names
+# and positional signatures (ring_flash_attn/ring_flash_attn.py:7-200, zigzag_ring_flash_attn.py:
+# 78-356, stripe_flash_attn.py:7-252 and the two *_varlen.py files). They all run the one ring
+# above; what differs between the strategies is the mask rule chosen by ``kind``.
+# -------------------------------------------------------------------------------------------------
+def _bounds_of(cu_seqlens):
+    cu = [int(x) for x in cu_seqlens]
+    return list(zip(cu[:-1], cu[1:]))
+
+
+def _make_kernel_level(kind: str, varlen: bool = False):
+    base = _NAMES[kind] + ("_varlen" if varlen else "")
+
+    if not varlen:
+        def forward(process_group, q, k, v, softmax_scale, dropout_p=0, causal=True, window_size=(-1, -1),
+                    alibi_slopes=None, deterministic=False, PROC_INFO=None, opt=False):
+            _check_unsupported(dropout_p, alibi_slopes, window_size)
+            return ring_forward(q, k, v, process_group, kind, causal, softmax_scale)
+
+        def backward(process_group, dout, q, k, v, out, softmax_lse, softmax_scale, dropout_p=0, causal=True,
+                     window_size=(-1, -1), alibi_slopes=None, deterministic=False, PROC_INFO=None, opt=False):
+            _check_unsupported(dropout_p, alibi_slopes, window_size)
+            return ring_backward(dout.contiguous(), q, k, v, out, softmax_lse, process_group, kind, causal,
+                                 softmax_scale)
+    else:
+        def forward(process_group, q, k, v, cu_seqlens, max_seqlen, softmax_scale, dropout_p=0, causal=True,
+                    window_size=(-1, -1), alibi_slopes=None, deterministic=False):
+            _check_unsupported(dropout_p, alibi_slopes, window_size)
+            o, lse = ring_forward(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), process_group, kind, causal,
+                                  softmax_scale, _bounds_of(cu_seqlens))
+            return o.squeeze(0), lse.squeeze(0)
+
+        def backward(process_group, dout, q, k, v, out, softmax_lse, cu_seqlens, max_seqlen, softmax_scale,
+                     dropout_p=0, causal=True, window_size=(-1, -1), alibi_slopes=None, deterministic=False):
+            _check_unsupported(dropout_p, alibi_slopes, window_size)
+            lse = softmax_lse if softmax_lse.dim() == 3 else softmax_lse.unsqueeze(0)
+            grads = ring_backward(dout.unsqueeze(0).contiguous(), q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0),
+                                  out.unsqueeze(0), lse, process_group, kind, causal, softmax_scale,
+                                  _bounds_of(cu_seqlens))
+            return tuple(g.squeeze(0) for g in grads)
+    forward.__name__, backward.__name__ = base + "_forward", base + "_backward"
+    forward.__doc__ = (f"(out, lse) of {kind} attention on this rank's shard; positional signature of the "
+                       f"reference's ``{base}_forward``; lse is ``[batch, heads, tokens]`` (packed: ``[heads, tokens]``).")
+    backward.__doc__ = f"(dq, dk, dv); positional signature of the reference's ``{base}_backward``."
+    return forward, backward
+
+
+def _make_func_class(kind: str, name: str, varlen: bool = False):
+    """An autograd class whose ``apply`` takes the reference's argument list (``..., return_softmax,
+    group[, PROC_INFO, opt]``) and returns what the reference's returns (out, or (out, lse, None))."""
+    if not varlen:
+        def fwd(ctx, q, k, v, dropout_p, softmax_scale, causal, window_size, alibi_slopes, deterministic,
+                return_softmax, group, PROC_INFO=None, opt=False):
+            _check_unsupported(dropout_p, alibi_slopes, window_size)
+            o, lse = ring_forward(q, k, v, group, kind, causal, softmax_scale)
+            ctx.save_for_backward(q, k, v, o, lse)
+            ctx.args = (softmax_scale, causal, group, None)
+            ctx.n_in = 13
+            return (o, lse, None) if return_softmax else o
+    else:
+        def fwd(ctx, q, k, v, cu_seqlens, max_seqlen, dropout_p, softmax_scale, causal, window_size, alibi_slopes,
+                deterministic, return_softmax, group):
+            _check_unsupported(dropout_p, alibi_slopes, window_size)
+            bounds = _bounds_of(cu_seqlens)
+            o, lse = ring_forward(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), group, kind, causal,
+                                  softmax_scale, bounds)
+            ctx.save_for_backward(q, k, v, o, lse)
+            ctx.args = (softmax_scale, causal, group, bounds)
+            ctx.n_in = 13
+            return (o.squeeze(0), lse.squeeze(0), None) if return_softmax else o.squeeze(0)
+
+    def bwd(ctx, dout, *rest):
+        q, k, v, o, lse = ctx.saved_tensors
+        scale, causal, group, bounds = ctx.args
+        if bounds is None:
+            grads = ring_backward(dout.contiguous(), q, k, v, o, lse, group, kind, causal, scale)
+        else:
+            grads = ring_backward(dout.unsqueeze(0).contiguous(), q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0),
+                                  o, lse, group, kind, causal, scale, bounds)
+            grads = tuple(g.squeeze(0) for g in grads)
+        return tuple(grads) + (None,) * (ctx.n_in - 3)
+
+    return type(name, (torch.autograd.Function,), {"forward": staticmethod(fwd), "backward": staticmethod(bwd),
+                                                   "__doc__": f"{kind} attention as an autograd function with the "
+                                                              "reference's ``apply`` argument list."})
+
+
+ring_flash_attn_forward, ring_flash_attn_backward = _make_kernel_level("ring")
+zigzag_ring_flash_attn_forward, zigzag_ring_flash_attn_backward = _make_kernel_level("zigzag")
+stripe_flash_attn_forward, stripe_flash_attn_backward = _make_kernel_level("stripe")
+ring_flash_attn_varlen_forward, ring_flash_attn_varlen_backward = _make_kernel_level("ring", varlen=True)
+zigzag_ring_flash_attn_varlen_forward, zigzag_ring_flash_attn_varlen_backward = _make_kernel_level("zigzag", varlen=True)
+RingFlashAttnFunc = _make_func_class("ring", "RingFlashAttnFunc")
+ZigZagRingFlashAttnFunc = _make_func_class("zigzag", "ZigZagRingFlashAttnFunc")
+StripeFlashAttnFunc = _make_func_class("stripe", "StripeFlashAttnFunc")
+RingFlashAttnVarlenFunc = _make_func_class("ring", "RingFlashAttnVarlenFunc", varlen=True)
+ZigZagRingFlashAttnVarlenFunc = _make_func_class("zigzag", "ZigZagRingFlashAttnVarlenFunc", varlen=True)
+
+
+def get_half_index(cu_seqlens, *, front: bool):
+    """Index (slice for one sequence, boolean mask otherwise) of the front or back half of every
+    packed sequence (reference: zigzag_ring_flash_attn_varlen.py:23-40)."""
+    cu = [int(x) for x in cu_seqlens]
+    if len(cu) == 2:
+        half = cu[1] // 2
+        return slice(None, half) if front else slice(half, None)
+    index = torch.zeros(cu[-1], dtype=torch.bool)
+    for a, b in zip(cu[:-1], cu[1:]):
+        mid = (a + b) // 2
+        if front:
+            index[a:mid] = True
+        else:
+            index[mid:b] = True
+    return index
+
+
+def get_half_lse(lse: torch.Tensor, cu_seqlens, *, front: bool) -> torch.Tensor:
+    """The front or back half of every sequence of a padded lse ``[sequences, heads, max_len]``
+    (reference: zigzag_ring_flash_attn_varlen.py:42-55)."""
+    cu = [int(x) for x in cu_seqlens]
+    out = torch.zeros(lse.shape[0], lse.shape[1], lse.shape[2] // 2, dtype=lse.dtype, device=lse.device)
+    for i, (a, b) in enumerate(zip(cu[:-1], cu[1:])):
+        n = b - a
+        lo, hi = (0, n // 2) if front else (n // 2, n)
+        out[i, :, :hi - lo] = lse[i, :, lo:hi]
+    return out
+
+
+# -------------------------------------------------------------------------------------------------
 # input sharding helpers (reference: easy_context/zigzag_ring_attn/prepare_inputs.py:4-40)
 # -------------------------------------------------------------------------------------------------
 def shard_sequence(x: torch.Tensor, rank: int, world: int, kind: str, dim: int = 1) -> torch.Tensor:
@@ -393,42 +522,72 @@ def shard_packed(x: torch.Tensor, cu_seqlens, rank: int, world: int, kind: str):
 # -------------------------------------------------------------------------------------------------
 # Ulysses
 # -------------------------------------------------------------------------------------------------
-class _UlyssesFunc(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, q, k, v, softmax_scale, causal, group):
-        from ..api import local_plans
-        from ..patterns import named
-        a2a = A2AComm(group)
-        qh, kh, vh = (a2a.all_to_all(t, 2, 1) for t in (q, k, v))       # [B, S, H/sp, D]
-        pat = named.causal(1) if causal else named.full(1)
-        fplan, bplan = local_plans(pat, qh.shape[1], qh.device)
-        oh = torch.empty_like(qh)
-        lse = torch.empty(qh.shape[0], qh.shape[2], qh.shape[1], dtype=torch.float32, device=qh.device)
-        A.attn_fwd([qh], [kh], [vh], [(oh, lse)], fplan, softmax_scale)
-        ctx.save_for_backward(qh, kh, vh, oh, lse)
-        ctx.args = (softmax_scale, group, bplan)
-        return a2a.all_to_all(oh, 1, 2)
+def deepspeed_ulysses_attn_forward(process_groups, q_s, k_s, v_s, softmax_scale, dropout_p=0, causal=True,
+                                   window_size=(-1, -1), alibi_slopes=None, deterministic=False, PROC_INFO=None,
+                                   opt=False):
+    """Head-parallel forward on sequence shards ``[B, S/sp, H, D]``: all-to-all to ``[B, S, H/sp, D]``,
+    attention over whole sequences, all-to-all back. Returns ``(out_s, q_h, k_h, v_h, out_h, lse_h)``:
+    the output in the sequence sharding and the head-sharded tensors the backward takes (argument
+    list of head_parallel_attn/deepspeed_ulysses_attn.py:10-47, whose compute step is missing)."""
+    from ..api import local_plans
+    from ..patterns import named
+    _check_unsupported(dropout_p, alibi_slopes, window_size)
+    a2a = A2AComm(process_groups)
+    qh, kh, vh = (a2a.all_to_all(t, 2, 1) for t in (q_s, k_s, v_s))       # [B, S, H/sp, D]
+    fplan, _ = local_plans(named.causal(1) if causal else named.full(1), qh.shape[1], qh.device)
+    oh = torch.empty_like(qh)
+    lse = torch.empty(qh.shape[0], qh.shape[2], qh.shape[1], dtype=torch.float32, device=qh.device)
+    A.attn_fwd([qh], [kh], [vh], [(oh, lse)], fplan, softmax_scale)
+    return a2a.all_to_all(oh, 1, 2), qh, kh, vh, oh, lse
+
+
+def deepspeed_ulysses_attn_backward(process_group, dout_s, q_h, k_h, v_h, out_h, softmax_lse, softmax_scale=None,
+                                    dropout_p=0, causal=True, window_size=(-1, -1), alibi_slopes=None,
+                                    deterministic=False, opt=False):
+    """Gradients in the sequence sharding from the head-sharded tensors of the forward (argument
+    list of head_parallel_attn/deepspeed_ulysses_attn.py:49-95)."""
+    from ..api import local_backward, local_plans
+    from ..patterns import named
+    _check_unsupported(dropout_p, alibi_slopes, window_size)
+    a2a = A2AComm(process_group)
+    _, bplan = local_plans(named.causal(1) if causal else named.full(1), q_h.shape[1], q_h.device)
+    doh = a2a.all_to_all(dout_s.contiguous(), 2, 1)
+    dq, dk, dv = local_backward(q_h, k_h, v_h, out_h, softmax_lse, doh, bplan, softmax_scale)
+    return tuple(a2a.all_to_all(t, 1, 2) for t in (dq, dk, dv))
+
+
+class DeepSpeedUlyssesAttnFunc(torch.autograd.Function):
+    """``apply(q, k, v, dropout_p, softmax_scale, causal, window_size, alibi_slopes, deterministic,
+    return_softmax, groups[, PROC_INFO, opt])`` as in the reference (deepspeed_ulysses_attn.py:97-166)."""
 
     @staticmethod
-    def backward(ctx, d_o):
-        from ..api import local_backward
+    def forward(ctx, q, k, v, dropout_p, softmax_scale, causal, window_size, alibi_slopes, deterministic,
+                return_softmax, groups, PROC_INFO=None, opt=False):
+        out_s, qh, kh, vh, oh, lse = deepspeed_ulysses_attn_forward(groups, q, k, v, softmax_scale, dropout_p, causal,
+                                                                    window_size, alibi_slopes, deterministic)
+        ctx.save_for_backward(qh, kh, vh, oh, lse)
+        ctx.args = (softmax_scale, causal, groups)
+        return (out_s, lse, None) if return_softmax else out_s
+
+    @staticmethod
+    def backward(ctx, d_o, *rest):
         qh, kh, vh, oh, lse = ctx.saved_tensors
-        scale, group, bplan = ctx.args
-        a2a = A2AComm(group)
-        doh = a2a.all_to_all(d_o.contiguous(), 2, 1)
-        dq, dk, dv = local_backward(qh, kh, vh, oh, lse, doh, bplan, scale)
-        return tuple(a2a.all_to_all(t, 1, 2) for t in (dq, dk, dv)) + (None, None, None)
+        scale, causal, groups = ctx.args
+        grads = deepspeed_ulysses_attn_backward(groups, d_o, qh, kh, vh, oh, lse, scale, causal=causal)
+        return tuple(grads) + (None,) * 10
 
 
 def deepspeed_ulysses_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False,
                                 window_size=(-1, -1), alibi_slopes=None, deterministic=False,
-                                return_attn_probs=False, group=None, PROC_INFO=None):
+                                return_attn_probs=False, group=None, PROC_INFO=None, groups=None, opt=False):
     """Head-parallel attention: inputs are sequence shards ``[B, S/sp, H, D]``; an all-to-all
     re-shards to ``[B, S, H/sp, D]``, attention runs on whole sequences, a second all-to-all
-    restores the sequence sharding. (The reference's version is a stub whose compute step is
-    missing, head_parallel_attn/deepspeed_ulysses_attn.py:43-47.)"""
-    assert dropout_p == 0.0 and alibi_slopes is None
-    return _UlyssesFunc.apply(q, k, v, softmax_scale, causal, group)
+    restores the sequence sharding. ``groups`` (the reference's keyword) and ``group`` name the
+    same process group. (The reference's version is a stub whose compute step is missing,
+    head_parallel_attn/deepspeed_ulysses_attn.py:43-47.)"""
+    return DeepSpeedUlyssesAttnFunc.apply(q, k, v, dropout_p, softmax_scale, causal, window_size, alibi_slopes,
+                                          deterministic, return_attn_probs, groups if groups is not None else group,
+                                          PROC_INFO, opt)
 
 
 # -------------------------------------------------------------------------------------------------

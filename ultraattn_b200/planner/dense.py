@@ -82,6 +82,19 @@ def create_ablation_configs_for_full(CP: int) -> list:
     return [(CP // x, x) for x in range(1, CP + 1) if CP % x == 0]
 
 
+def ablation_dicts_for_full(hierarchy_cp: int, KERNEL_TILE_TYPEs=None) -> list:
+    """The (Y, X) grids of FULL attention in the record form of the reference's campaign
+    (search_algo/dense_utils.py:77-98): one dict per kernel-tile setting and grid, X ascending."""
+    kinds = ["w/o_kernel_tile"] if KERNEL_TILE_TYPEs is None else list(KERNEL_TILE_TYPEs)
+    return [{"Y": y, "X": x, "first_dim": 0, "KERNEL_TILE_TYPE": kind}
+            for kind in kinds for y, x in create_ablation_configs_for_full(hierarchy_cp)]
+
+
+def create_plan_key_suffixes_for_full(hierarchy_cp: int) -> list:
+    """Plan-key suffixes of those grids, in the same order (search_algo/dense_utils.py:100-103)."""
+    return [get_full_ablation_suffix(ad["Y"], ad["X"], ad["first_dim"]) for ad in ablation_dicts_for_full(hierarchy_cp)]
+
+
 def create_plan_for_full(CP: int, X: int, fob: int, m_config: Machine_Config = None, shape_config=None,
                          first_dim: int = 0) -> Execution_Plan:
     """Manual plan of FULL attention on a Y x X grid. Without ``shape_config`` the graph is
