@@ -16,3 +16,7 @@ def get_global_var(name):
 
 def set_global_var(name, value):
     _vars[name] = value
+
+
+def is_exist_global_var(name) -> bool:
+    return name in _vars

@@ -22,3 +22,9 @@ def fused_attn_backward(execution_plan, inp_row, inp_col, out_fwd, softmax_scale
 
 intra_attn_forward = orchestrated_attn_func
 intra_attn_backward = orchestrated_attn_backward
+
+
+def stream_wait_event(stream, event) -> None:
+    """Make a stream, or both streams of a pair, wait for an event (reference: :215-220)."""
+    for s in (stream if isinstance(stream, (list, tuple)) else [stream]):
+        s.wait_event(event)

@@ -3,7 +3,8 @@ import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-from ultraattn_b200.drivers.task2 import main  # noqa: E402,F401
+from ultraattn_b200.drivers.task2 import (main, prepare_inter_comp_plans,  # noqa: E402,F401
+                                          step4_profile_inter_bsa_exe_plans, step5_profile_baselines)
 
 if __name__ == "__main__":
     main()

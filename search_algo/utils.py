@@ -10,3 +10,4 @@ from ultraattn_b200.utils.misc import (Block_Attention_Config, all_wait_main_str
 from ultraattn_b200.utils.misc import (FinitePriorityQueue, calc_flops, calc_table_comp_relative_time,  # noqa: F401
                                        get_block_table_type, print_rank_0, report_memory,
                                        unique_list, use_all_cpus)
+from ultraattn_b200.planner.cost import convert_throughput_to_B  # noqa: F401,E402

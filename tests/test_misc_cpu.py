@@ -357,7 +357,8 @@ def test_every_reference_module_path_imports_and_exports():
                                            "Quad_LP_GUROBI", "ILP", "solve_global_causal"],
         "search_algo.manual_schedules": ["get_qo_schedule_table", "get_kv_schedule_table", "get_cc_optimal_schedule_table"],
         "search_algo.dense_utils": ["CP2ParD_map", "get_block_schedule_table_for_full", "create_plan_for_full",
-                                    "create_ablation_configs_for_full", "write_plan", "split_dense_configs"],
+                                    "create_ablation_configs_for_full", "create_plan_key_suffixes_for_full",
+                                    "write_plan", "split_dense_configs"],
         "search_algo.search_engine": ["Evaluation_Configs", "Dist_Attn_Config", "Dist_Attn_Schedule", "Machine_Config",
                                       "FlashAttn_Profile_Map", "Inter_Comp_Profile_Map", "Comm_Profile_Map",
                                       "get_cc_optimal_schedule_from_table"],
@@ -366,14 +367,19 @@ def test_every_reference_module_path_imports_and_exports():
                                                     "Comp_Fusion_Transformation"],
         "search_algo.execute_plan": ["Execution_Plan", "Fused_Execution_Plan"],
         "search_algo.database": ["Prof_DB"],
-        "search_algo.initialize": ["get_proc_info", "initialize_distribution"],
+        "search_algo.initialize": ["get_proc_info", "initialize_distribution", "initialize_prof_db",
+                                   "parse_slurm_tasks_per_node"],
         "search_algo.exp_configs": ["get_exp_configs", "get_exp_train_configs", "get_exp_infer_configs",
                                     "get_bsa_train_configs", "get_dense_train_configs", "get_bsa_infer_configs",
                                     "step0_top_down_decompose"],
         "search_algo.benchmark": ["benchmark_ops", "benchmark_orchestrate_bsa", "prepare_inter_comp_plans", "create_buf_dict"],
-        "search_algo.arguments": ["parse_args", "get_args"],
-        "search_algo.global_vars": ["get_global_var", "set_global_var"],
-        "search_algo.task1_bsa": ["main"], "search_algo.task2_bsa": ["main"], "search_algo.main": ["main"],
+        "search_algo.arguments": ["parse_args", "get_args", "parse_config", "recursive_update", "print_args",
+                                  "parse_parallel_args", "parse_shape_args", "parse_pattern_args", "parse_experiment_args"],
+        "search_algo.global_vars": ["get_global_var", "set_global_var", "TASK_STATUS"],
+        "search_algo.task1_bsa": ["main", "get_general_bsa_cc_optimal_schedule", "step1_generate_intra_bsa_exe_plans",
+                                  "step1_generate_intra_full_exe_plans", "step2_profile_intra_bsa_exe_plans",
+                                  "step2_profile_intra_full_exe_plans", "step3_generate_inter_bsa_exe_plans"],
+        "search_algo.task2_bsa": ["main", "step4_profile_inter_bsa_exe_plans"], "search_algo.main": ["main"],
         "search_algo.fusion_evaluate": ["main"], "search_algo.intra_attn_gen": ["main"],
         "orchestrated_attn": ["orchestrated_attn_func", "orchestrated_attn_backward", "OrchestratedAttnFunc",
                               "Input_Row_Fwd", "Input_Col_Fwd", "Output_Row_Fwd", "Output_Col_Fwd",
@@ -381,8 +387,11 @@ def test_every_reference_module_path_imports_and_exports():
         "orchestrated_attn.orchestrated_attn_impl": ["orchestrated_attn_forward", "orchestrated_attn_backward",
                                                      "fused_attn_forward", "fused_attn_backward",
                                                      "intra_attn_forward", "intra_attn_backward"],
-        "orchestrated_attn.utils": ["IntraComm", "InterComm", "IntraComm_fused", "InterComm_fused", "Integrated_Data"],
-        "orchestrated_attn.global_vars": ["FULL_DTYPE", "ncclcomm_dict", "cpu_group_dict", "streams"],
+        "orchestrated_attn.utils": ["IntraComm", "InterComm", "IntraComm_fused", "InterComm_fused", "Integrated_Data",
+                                    "Comm_Fused", "get_Q_shape_from_da_config", "get_K_shape_from_da_config",
+                                    "get_lse_shape_from_da_config", "print_rank_0"],
+        "orchestrated_attn.global_vars": ["FULL_DTYPE", "ncclcomm_dict", "cpu_group_dict", "streams",
+                                          "is_exist_global_var"],
         "ring_flash_attn": ["ring_flash_attn_func", "ring_flash_attn_kvpacked_func", "ring_flash_attn_qkvpacked_func",
                             "ring_flash_attn_backward", "ring_flash_attn_varlen_func",
                             "zigzag_ring_flash_attn_func", "zigzag_ring_flash_attn_varlen_func",
@@ -396,6 +405,31 @@ def test_every_reference_module_path_imports_and_exports():
                          "apply_zigzag_ring_attn_monkey_patch_llama", "apply_zigzag_ring_attn_monkey_patch_mistral",
                          "apply_dist_flash_attn_monkey_patch_llama",
                          "apply_unsloth_offloaded_gradient_checkpoint_monkey_patch"],
+        "ring_flash_attn.ring_flash_attn": ["ring_flash_attn_forward", "ring_flash_attn_backward", "RingFlashAttnFunc",
+                                            "ring_flash_attn_func", "ring_flash_attn_qkvpacked_func"],
+        "ring_flash_attn.zigzag_ring_flash_attn": ["zigzag_ring_flash_attn_forward", "zigzag_ring_flash_attn_backward",
+                                                   "ZigZagRingFlashAttnFunc", "zigzag_ring_flash_attn_func"],
+        "ring_flash_attn.stripe_flash_attn": ["stripe_flash_attn_forward", "stripe_flash_attn_backward",
+                                              "StripeFlashAttnFunc", "stripe_flash_attn_func"],
+        "ring_flash_attn.ring_flash_attn_varlen": ["ring_flash_attn_varlen_forward", "ring_flash_attn_varlen_backward",
+                                                   "RingFlashAttnVarlenFunc", "ring_flash_attn_varlen_func"],
+        "ring_flash_attn.zigzag_ring_flash_attn_varlen": ["get_half_index", "get_half_lse", "ZigZagRingFlashAttnVarlenFunc",
+                                                          "zigzag_ring_flash_attn_varlen_forward",
+                                                          "zigzag_ring_flash_attn_varlen_func"],
+        "ring_flash_attn.triton_utils": ["flatten_varlen_lse", "unflatten_varlen_lse"],
+        "head_parallel_attn.deepspeed_ulysses_attn": ["deepspeed_ulysses_attn_forward", "deepspeed_ulysses_attn_backward",
+                                                      "DeepSpeedUlyssesAttnFunc", "deepspeed_ulysses_attn_func"],
+        "hierarchy_attn.hierarchy_attn_impl": ["intra_attn_forward", "hierarchy_attn_forward", "hierarchy_attn_backward",
+                                               "overlapped_hierarchy_attn_forward", "overlapped_hierarchy_attn_backward",
+                                               "HierarchyAttnFunc", "hierarchy_attn_func"],
+        "hierarchy_attn.utils": ["IntraComm", "InterComm", "OverlappedInterComm", "wait_recursively",
+                                 "update_out_and_lse", "print_rank_0"],
+        "easy_context.zigzag_ring_attn.monkey_patch": ["apply_zigzag_ring_attn_monkey_patch_llama",
+                                                       "apply_zigzag_ring_attn_monkey_patch_mistral"],
+        "easy_context.zigzag_ring_attn.prepare_inputs": ["extract_local", "prepare_zigzag_ring_attn_inputs"],
+        "easy_context.dist_flash_attn.monkey_patch": ["apply_dist_flash_attn_monkey_patch_llama"],
+        "easy_context.unsloth_offloaded_gradient_checkpoint.monkey_patch": [
+            "Unsloth_Offloaded_Gradient_Checkpointer", "apply_unsloth_offloaded_gradient_checkpoint_monkey_patch"],
         "easy_context.dist_flash_attn.lightseq_async_attn": ["attention"],
         "easy_context.dist_flash_attn.async_communication": ["initialize_distributed", "get_sequence_parallel_group",
                                                             "get_sequence_parallel_rank", "get_sequence_parallel_size",

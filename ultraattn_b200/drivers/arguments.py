@@ -106,3 +106,62 @@ def parse_args(argv=None) -> RunConfig:
 
 def get_args() -> Optional[RunConfig]:
     return _args
+
+
+# ---- the reference's helper names (search_algo/arguments.py:4-70) ------------------------------
+def parse_parallel_args(parser) -> None:
+    parser.add_argument("--SP", type=int, nargs="+", default=None, help="sequence-parallel degrees (intra, inter)")
+
+
+def parse_shape_args(parser) -> None:
+    for name, what in (("Sq", "query tokens"), ("Skv", "key/value tokens"), ("Nhq", "query heads"),
+                       ("Nhkv", "key/value heads"), ("BS", "batch size"), ("D", "head dim")):
+        parser.add_argument(f"--{name}", type=int, default=None, help=what)
+
+
+def parse_pattern_args(parser) -> None:
+    parser.add_argument("--pattern_type", type=str, default=None,
+                        choices=[None, "causal", "full", "star", "stream", "stride", "global_local"])
+    parser.add_argument("--pattern_sparsity", type=float, default=None)
+
+
+def parse_experiment_args(parser) -> None:
+    parser.add_argument("--transform_mode", type=str, default=None, choices=[None, "None", "Greedy", "greedy", "bf"])
+    parser.add_argument("--lowering_type", type=str, default=None, choices=[None, "Flexflow", "ILP"])
+
+
+def recursive_update(config, args) -> None:
+    """Overwrite the leaves of a nested configuration dict with the command-line values of the
+    same name that were given (not None)."""
+    if not isinstance(config, dict):
+        return
+    for key, value in config.items():
+        if isinstance(value, dict):
+            recursive_update(value, args)
+        elif getattr(args, key, None) is not None:
+            config[key] = getattr(args, key)
+
+
+def parse_config(argv=None) -> dict:
+    """The YAML file named by ``--config`` as a nested dict, with command-line overrides applied."""
+    import yaml
+    ap = argparse.ArgumentParser(description="UltraAttn-style configuration")
+    ap.add_argument("--config", type=str, required=True)
+    for add in (parse_parallel_args, parse_shape_args, parse_pattern_args, parse_experiment_args):
+        add(ap)
+    ns = ap.parse_args(argv)
+    with open(ns.config) as f:
+        config = yaml.safe_load(f) or {}
+    recursive_update(config, ns)
+    return config
+
+
+def print_args(args) -> None:
+    """Print a parsed configuration on rank 0."""
+    if int(getattr(args, "rank", 0) or 0) != 0:
+        return
+    print("------------------------ arguments ------------------------", flush=True)
+    items = vars(args).items() if not isinstance(args, dict) else args.items()
+    for k, v in sorted(items):
+        print(f"  {k} {'.' * max(2, 48 - len(str(k)))} {v}", flush=True)
+    print("-------------------- end of arguments ---------------------", flush=True)

@@ -52,13 +52,26 @@ def print_and_reset_comm_stats(rank: Optional[int] = None) -> dict:
     return st
 
 
+def parse_slurm_tasks_per_node(tasks_per_node: str) -> int:
+    """``SLURM_TASKS_PER_NODE`` ("8", "4(x2)", "8,8") -> tasks on the first node."""
+    return int(str(tasks_per_node).split("(")[0].split(",")[0])
+
+
+def initialize_prof_db(gloo_global_group=None):
+    """The plan / profile database of this cluster and platform (``CLUSTER_NAME`` / ``PLATFORM``
+    from the environment), as the campaign drivers open it (reference: search_algo/initialize.py:19-23)."""
+    import os
+    from ..plandb.db import Prof_DB
+    return Prof_DB(os.environ.get("CLUSTER_NAME"), os.environ.get("PLATFORM"), gloo_global_group)
+
+
 def get_proc_info() -> dict:
     env = os.environ
     if "SLURM_PROCID" in env and "RANK" not in env:
         rank = int(env["SLURM_PROCID"])
         local_rank = int(env.get("SLURM_LOCALID", 0))
         world = int(env["SLURM_NTASKS"])
-        per_node = int(str(env.get("SLURM_TASKS_PER_NODE", world)).split("(")[0].split(",")[0])
+        per_node = parse_slurm_tasks_per_node(env.get("SLURM_TASKS_PER_NODE", world))
         node_id = int(env.get("SLURM_NODEID", rank // max(per_node, 1)))
         ip = env.get("SLURM_STEP_NODELIST", "127.0.0.1")
     elif "OMPI_COMM_WORLD_RANK" in env:

@@ -386,6 +386,22 @@ _UNIT = {"B": 1.0, "KB": 1e3, "MB": 1e6, "GB": 1e9, "TB": 1e12}
 _CB_LINE = re.compile(r"^SIZE (\d+),.*?BD/PAIR (\d*(?:\.\d*)?) ([A-Z]+)/s")
 
 
+def convert_throughput_to_B(size: float, unit: str) -> float:
+    """``size`` in ``unit`` (B, KB, MB, ... with decimal steps of 1000) -> bytes."""
+    names = ["B", "KB", "MB", "GB", "TB", "PB", "EB", "ZB", "YB"]
+    assert unit in names, f"invalid unit {unit!r}"
+    return size * 1000 ** names.index(unit)
+
+
+def create_schedule(da_config, m_config, split_degrees, S_map, schedule_table_func, hierarchy: int = 1):
+    """A ``Dist_Attn_Schedule`` (or a list of them) from a function that returns the allocation
+    table(s) for a partition (reference: search_algo/search_engine.py:951-957)."""
+    tables = schedule_table_func(split_degrees, S_map, da_config=da_config)
+    if isinstance(tables, list):
+        return [Dist_Attn_Schedule(da_config, m_config, split_degrees, S_map, t, hierarchy) for t in tables]
+    return Dist_Attn_Schedule(da_config, m_config, split_degrees, S_map, tables, hierarchy)
+
+
 def convert_profile_data_to_comm_map(file_name, num_gpus_div: int = 1) -> dict:
     out = {}
     for line in Path(file_name).read_text().splitlines():
