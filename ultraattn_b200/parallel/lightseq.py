@@ -161,3 +161,25 @@ def extract_local(value, rank: int, world_size: int, device=None, dim: int = 1):
     """This rank's contiguous chunk of ``value`` along ``dim``."""
     out = value.chunk(world_size, dim=dim)[rank]
     return out.to(device) if device is not None else out
+
+
+# ---- grouped-query helpers under the reference's names (lightseq_async_attn.py:221-247) ----------
+# The kernels here take fewer key/value heads directly (``kv_group``), so nothing in this package
+# calls these; they serve code written against the reference.
+def maybe_repeat_kv_fwd(nqh: int, kv: torch.Tensor) -> torch.Tensor:
+    """``[batch, kv_heads, tokens, dim]`` -> ``[batch, nqh, tokens, dim]`` (every head repeated in place)."""
+    rep = nqh // kv.shape[1]
+    return kv if rep == 1 else kv.repeat_interleave(rep, dim=1)
+
+
+def maybe_repeat_kv_bwd(nqh: int, kv: torch.Tensor) -> torch.Tensor:
+    """``[batch, tokens, kv_heads, dim]`` -> ``[batch, tokens, nqh, dim]``."""
+    rep = nqh // kv.shape[2]
+    return kv if rep == 1 else kv.repeat_interleave(rep, dim=2)
+
+
+def maybe_reduce_dkv(nkvh: int, dkv: torch.Tensor) -> torch.Tensor:
+    """Gradient of the repeat: ``[batch, tokens, nqh, dim]`` summed over each group of repeated heads."""
+    b, s, nqh, d = dkv.shape
+    rep = nqh // nkvh
+    return dkv if rep == 1 else dkv.reshape(b, s, nkvh, rep, d).sum(dim=3)
