@@ -464,3 +464,33 @@ def test_kernel_trace_summary_on_a_synthetic_launch():
     assert out["tail_ms_under_half_sms"] == 1.0                               # three of four SMs are done at 2 ms
     assert abs(out["sm_busy_fraction"] - 9 / 12) < 1e-4
     assert summarize(np.zeros((0, 4), dtype=np.int64)) == {"ctas": 0}
+
+
+def test_planner_helpers_accept_the_reference_argument_lists():
+    """`search_algo.manual_schedules` / `dense_utils` / `utils.calc_flops` called the way the
+    reference's own code calls them; expected values were produced by the reference's functions."""
+    import numpy as np
+    from search_algo.dense_utils import (create_ablation_configs_for_full, create_plan_for_full,
+                                         create_plan_key_suffixes_for_full, get_block_schedule_table_for_full)
+    from search_algo.manual_schedules import get_kv_schedule_table, get_qo_schedule_table
+    from search_algo.utils import calc_flops
+    S_map = np.array([[3, 2, 1, 0]])
+    qo = get_qo_schedule_table([4, 4, 1, 1], S_map, True)
+    assert qo.shape == (1, 1, 4, 4) and qo[0, 0].tolist() == [[3, -1, -1, -1], [3, 2, -1, -1], [3, 2, 1, -1], [3, 2, 1, 0]]
+    kv = get_kv_schedule_table([4, 4, 1, 1], S_map, True)
+    assert kv[0, 0].tolist() == [[3, -1, -1, -1], [2, 2, -1, -1], [1, 1, 1, -1], [0, 0, 0, 0]]
+    assert get_kv_schedule_table(3, True).tolist() == [[0, -1, -1], [1, 1, -1], [2, 2, 2]]       # short form
+    grid = get_block_schedule_table_for_full([4, 4, 1, 1], S_map, 2, None)
+    assert grid[0, 0].tolist() == [[3, 2, 3, 2], [3, 2, 3, 2], [1, 0, 1, 0], [1, 0, 1, 0]]
+    assert [list(calc_flops(2, (1024, 2048), 8, 128, f, 0.5)) for f in (0, 1, 2)] == \
+        [[8589934592.0, 8589934592.0], [17179869184.0, 21474836480.0], [25769803776.0, 30064771072.0]]
+    assert create_ablation_configs_for_full(4)[1] == {"Y": 2, "X": 2, "first_dim": 0, "KERNEL_TILE_TYPE": "w/o_kernel_tile"}
+    assert create_plan_key_suffixes_for_full(8) == ["_ablation=(Y=8,X=1,dim=0)", "_ablation=(Y=4,X=2,dim=0)",
+                                                    "_ablation=(Y=2,X=4,dim=0)", "_ablation=(Y=1,X=8,dim=0)"]
+    from ultraattn_b200.patterns.blocks import BSA_Config
+    from ultraattn_b200.planner.cost import Dist_Attn_Config, Machine_Config
+    da = Dist_Attn_Config.from_bsa_config(BSA_Config.create_full((4, 1)),
+                                          {"S": (4096, 4096), "Nh": (2, 2), "bs": 1, "D": 128}, hierarchy=1)
+    plan = create_plan_for_full(da, Machine_Config.b200_default(), 2, 1, 0)
+    assert plan.X == 2 and plan.fob == 1 and plan.verify() == []
+    assert create_plan_for_full(4, 2, 0).X == 2                                                  # short form
