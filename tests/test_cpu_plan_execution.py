@@ -209,3 +209,42 @@ def test_random_patterns_execute_correctly_world4():
     for r in range(4):
         assert isinstance(ret[r], float), ret[r]
         assert ret[r] < 2e-4, (r, ret[r])
+
+
+def _ref_harness_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from search_algo.benchmark import benchmark_orchestrate_bsa
+        from search_algo.execute_plan import Execution_Plan
+        from search_algo.search_engine import Evaluation_Configs
+        from ultraattn_b200 import patterns as P
+        from ultraattn_b200.planner import make_plan_collective
+        out = []
+        for fob in (0, 1):
+            plan = make_plan_collective(pattern=P.strided(8, 4, 2), cp=world, seq_len=1024, n_heads=2, head_dim=32,
+                                        fob=fob, plan_type="Flexflow", time_limit=3.0)
+            inter = Execution_Plan.create_one_node_exe_plan(fob)
+            exp = Evaluation_Configs(plan_type="Flexflow", MAX_QUEUE_SIZE=100, fob=fob, hierarchy=1, transform_mode="greedy")
+            res = benchmark_orchestrate_bsa(None, None, plan.da_config, exp, None, [inter], [{((1, 1), "k"): plan}],
+                                            warmup=1, num_iter=1, log=False)
+            out.append(res)
+        ret[rank] = out
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = f"{type(e).__name__}: {e}\\n{traceback.format_exc()}"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_harness_with_the_reference_argument_list():
+    """`search_algo.benchmark.benchmark_orchestrate_bsa(args, raw_f, da_config, exp_config, tensor_buf,
+    inter_plans, comp_plan_dicts, ...)`: one result dict per plan on rank 0, None elsewhere."""
+    ret = mp.Manager().dict()
+    mp.spawn(_ref_harness_worker, args=(2, 29500 + os.getpid() % 90, ret), nprocs=2, join=True)
+    for r in range(2):
+        assert isinstance(ret[r], list), ret[r]
+    for res in ret[0]:
+        assert len(res) == 1 and set(res[0]) == {"hfu", "time"} and float(res[0]["time"]) > 0
+    assert all(res == [None] for res in ret[1])

@@ -103,3 +103,45 @@ def benchmark_orchestrate_bsa(plan_fwd, plan_bwd, fob: int, device: torch.device
     _, hw = calc_flops(da.bs, da.S, da.Nh[0], da.D, False, fob, da.bsa_config.total_sparsity)
     plan = plan_fwd if fob == 0 else plan_bwd
     return {"time": t, "hfu": hw / t / ex.cp / 1e12, "sim_time": float(plan.end_time)}
+
+
+def benchmark_orchestrate_bsa_reference_form(args, raw_f, da_config, exp_config, tensor_buf, inter_bsa_execution_plans,
+                                             inter_comp_plans_dicts, warmup: int = 11, num_iter: int = 20,
+                                             log: bool = True, global_group=None, ncclcomm_global=None,
+                                             use_cudagraph: bool = False, mode: str = "test") -> list:
+    """The harness with the reference's argument list (search_algo/benchmark.py:336-619): a list
+    of inter-level plans, each with the dict of intra-level plans its compute kernels stand for,
+    measured for the pass ``exp_config.fob``; returns one ``{'hfu': TFLOP/s per rank, 'time': '%.3e'}``
+    per plan on rank 0 and ``None`` elsewhere. ``raw_f`` and ``tensor_buf`` (the reference's attention
+    callable and its one big buffer that every tile aliases) are accepted and not used: the plans
+    run on :class:`ultraattn_b200.runtime.PlanExecutor` with tensors of their own. One node per
+    inter-level plan (its single compute kernel = the intra-level plan); for more nodes use
+    ``make_plan(..., cp_inter=n)`` and the short form."""
+    from ..planner.graph import Dependent_Graph
+    from ..planner.schedule import Execution_Plan
+    assert len(inter_bsa_execution_plans) == len(inter_comp_plans_dicts), \
+        "inter_bsa_execution_plans and inter_comp_plans_dicts must correspond one to one"
+    fob = int(exp_config.fob)
+    cuda = torch.cuda.is_available() and dist.is_initialized() and dist.get_backend(global_group) == "nccl"
+    device = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    out = []
+    for inter_plan, comp_plans in zip(inter_bsa_execution_plans, inter_comp_plans_dicts):
+        assert len(inter_plan.gpu_kernel_lists) == 1 and len(comp_plans) == 1, \
+            "this form covers one node per inter-level plan"
+        plan = next(iter(comp_plans.values()))
+        if fob == 0:
+            plan_f, plan_b = plan, None
+        else:
+            # the backward needs a forward result: plan the forward on the same allocation
+            plan_f = Execution_Plan(Dependent_Graph(plan.d_graph.schedule, 0), 0, "Flexflow")
+            plan_b = plan
+        res = benchmark_orchestrate_bsa(plan_f, plan_b, fob, device, global_group,
+                                        warmup=min(int(warmup), 3), num_iter=max(1, min(int(num_iter), 4)), repeats=1)
+        if rank == 0:
+            if log:
+                print(f"hfu: {res['hfu']:.3f} Tflops/s, {1.0 / res['time']:.3f} iter/s, {res['time']:.3e} s/iter", flush=True)
+            out.append({"hfu": round(res["hfu"], 3), "time": f"{res['time']:.3e}"})
+        else:
+            out.append(None)
+    return out

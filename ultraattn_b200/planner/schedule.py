@@ -518,6 +518,10 @@ def create_one_node_exe_plan(fob: int, comp_time: float = 1.0) -> Execution_Plan
     return plan
 
 
+# the reference reaches it through the class (search_algo/execute_plan.py:138)
+Execution_Plan.create_one_node_exe_plan = staticmethod(create_one_node_exe_plan)
+
+
 class Fused_Execution_Plan:
     """FULL attention with kernel tiling on a Y x X rank grid: rank g computes the X query chunks of
     its row group against the Y key chunks ``g % X, g % X + X, ...`` as ONE kernel; inputs arrive by
