@@ -248,3 +248,66 @@ def test_harness_with_the_reference_argument_list():
     for res in ret[0]:
         assert len(res) == 1 and set(res[0]) == {"hfu", "time"} and float(res[0]["time"]) > 0
     assert all(res == [None] for res in ret[1])
+
+
+def _switch_over_worker(rank, world, port, dbroot, ret):
+    """A script written against the reference's modules, names and argument lists (the sequence of
+    calls its campaign makes for one configuration), run against this distribution."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), LOCAL_RANK=str(rank),
+                      WORLD_SIZE=str(world), CLUSTER_NAME="testbox", PLATFORM="CPU", UA_DATABASE_ROOT=dbroot)
+    try:
+        import numpy as np
+        from search_algo.initialize import initialize_distribution, initialize_prof_db
+        from search_algo.bsa_config import BSA_Config, BSA_Repr
+        from search_algo.utils import Block_Type
+        from search_algo.search_engine import Dist_Attn_Config, Evaluation_Configs
+        from search_algo.dependent_graph import Dependent_Graph
+        from search_algo.execute_plan import Execution_Plan
+        from search_algo.task1_bsa import get_general_bsa_cc_optimal_schedule
+        from search_algo.benchmark import benchmark_orchestrate_bsa
+        from search_algo.global_vars import get_global_var
+        ncclcomm_global, gloo_group = initialize_distribution()
+        assert get_global_var("PROC_INFO")["rank"] == rank and ncclcomm_global.world_size == world
+        prof_db = initialize_prof_db(gloo_group)
+        table = np.full((8, 8), Block_Type.EMPTY, dtype=object)
+        for i in range(8):
+            for j in range(i + 1):
+                if i == j:
+                    table[i, j] = Block_Type.CAUSAL
+                elif i - j <= 1 or (i - j) % 4 == 0:
+                    table[i, j] = Block_Type.FULL
+        bsa_repr = BSA_Repr(block_table=table, cmap=None)
+        bsa_config = BSA_Config(None, None, {"bsa_repr": bsa_repr, "CP": (world, 1)})
+        shape_config = {"Nh": (2, 2), "S": (1024, 1024), "bs": 1, "D": 32}
+        da_config = Dist_Attn_Config.from_bsa_config(bsa_config, shape_config=shape_config, hierarchy=1)
+        results = []
+        for fob in (0, 1):
+            exp_config = Evaluation_Configs(plan_type="Flexflow", MAX_QUEUE_SIZE=100, fob=fob, hierarchy=1,
+                                            transform_mode="greedy")
+            schedule = get_general_bsa_cc_optimal_schedule(exp_config, da_config, prof_db, gpu_tile_type="naive")
+            plan = Execution_Plan(Dependent_Graph(schedule, fob), fob, plan_type="Flexflow")
+            inter_plan = Execution_Plan.create_one_node_exe_plan(fob)
+            res = benchmark_orchestrate_bsa(None, None, da_config, exp_config, None,
+                                            inter_bsa_execution_plans=[inter_plan],
+                                            inter_comp_plans_dicts=[{((1, 1), str(bsa_repr)): plan}],
+                                            warmup=1, num_iter=1, log=False, global_group=None)
+            results.append((plan.verify(), res))
+        ret[rank] = results
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = f"{type(e).__name__}: {e}\\n{traceback.format_exc()}"
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_a_script_written_against_the_reference_runs_unchanged(tmp_path):
+    ret = mp.Manager().dict()
+    mp.spawn(_switch_over_worker, args=(2, 29600 + os.getpid() % 90, str(tmp_path), ret), nprocs=2, join=True)
+    for r in range(2):
+        assert isinstance(ret[r], list), ret[r]
+        for problems, _ in ret[r]:
+            assert problems == []
+    for _, res in ret[0]:
+        assert float(res[0]["time"]) > 0 and res[0]["hfu"] >= 0

@@ -27,7 +27,9 @@ from .exp_configs import step0_top_down_decompose
 
 
 def get_general_bsa_cc_optimal_schedule(fob, da_config, prof_db, gpu_tile_type=None, time_limit=60.0):
-    """Allocation (ILP #1 or the row-owner ablation) with database caching."""
+    """Allocation (ILP #1 or the row-owner ablation) with database caching. ``fob``: the pass, or
+    (the reference's form, search_algo/task1_bsa.py:86-143) an ``Evaluation_Configs`` that carries it."""
+    fob = int(getattr(fob, "fob", fob))
     hier = da_config.hierarchy
     key = allocation_key(fob, da_config.bsa_config, gpu_tile_type)
     hit = prof_db.get_allocation(key, hier)
