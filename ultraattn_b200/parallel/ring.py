@@ -293,8 +293,9 @@ def _check_unsupported(dropout_p, alibi_slopes, window_size):
 def _make_func(kind: str):
     def func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
              alibi_slopes=None, deterministic=False, return_attn_probs=False, group=None,
-             PROC_INFO=None, opt=False):
+             PROC_INFO=None, opt=False, groups=None):
         _check_unsupported(dropout_p, alibi_slopes, window_size)
+        group = groups if groups is not None else group        # the reference's keyword is ``groups``
         o, lse = _RingFunc.apply(q, k, v, softmax_scale, causal, group, kind)
         return (o, lse, None) if return_attn_probs else o
     func.__name__ = _NAMES[kind] + "_func"
@@ -387,6 +388,26 @@ def _make_kernel_level(kind: str, varlen: bool = False):
             _check_unsupported(dropout_p, alibi_slopes, window_size)
             return ring_backward(dout.contiguous(), q, k, v, out, softmax_lse, process_group, kind, causal,
                                  softmax_scale)
+    elif kind == "zigzag":
+        # the reference's zigzag forms carry two precomputed half-sequence indices (zigzag_ring_flash_attn_varlen.py:
+        # 58-70, 153-168); the kernels here mask by position, so they are accepted and not needed
+        def forward(process_group, q, k, v, cu_seqlens, max_seqlen, half_index0=None, half_index1=None,
+                    softmax_scale=None, dropout_p=0, causal=True, window_size=(-1, -1), alibi_slopes=None,
+                    deterministic=False):
+            _check_unsupported(dropout_p, alibi_slopes, window_size)
+            o, lse = ring_forward(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), process_group, kind, causal,
+                                  softmax_scale, _bounds_of(cu_seqlens))
+            return o.squeeze(0), lse.squeeze(0)
+
+        def backward(process_group, dout, q, k, v, out, softmax_lse, cu_seqlens, max_seqlen, half_index0=None,
+                     half_index1=None, softmax_scale=None, dropout_p=0, causal=True, window_size=(-1, -1),
+                     alibi_slopes=None, deterministic=False):
+            _check_unsupported(dropout_p, alibi_slopes, window_size)
+            lse = softmax_lse if softmax_lse.dim() == 3 else softmax_lse.unsqueeze(0)
+            grads = ring_backward(dout.unsqueeze(0).contiguous(), q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0),
+                                  out.unsqueeze(0), lse, process_group, kind, causal, softmax_scale,
+                                  _bounds_of(cu_seqlens))
+            return tuple(g.squeeze(0) for g in grads)
     else:
         def forward(process_group, q, k, v, cu_seqlens, max_seqlen, softmax_scale, dropout_p=0, causal=True,
                     window_size=(-1, -1), alibi_slopes=None, deterministic=False):
