@@ -22,3 +22,14 @@ def test_context_parallel_example_on_two_cpu_ranks():
     assert r.returncode == 0, r.stderr[-2000:]
     lines = [ln for ln in r.stdout.splitlines() if "max error against dense attention" in ln]
     assert len(lines) == 2 and all(float(ln.rsplit(" ", 1)[1]) < 1e-4 for ln in lines), r.stdout
+
+
+def test_reference_style_campaign_example_on_two_cpu_ranks(tmp_path):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(29890 + os.getpid() % 40),
+           os.path.join(ROOT, "examples", "reference_style_campaign.py")]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", UA_DATABASE_ROOT=str(tmp_path))
+    r = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("fob=")]
+    assert len(lines) == 2 and all("plan checks: ok" in ln for ln in lines), r.stdout
