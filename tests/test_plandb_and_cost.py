@@ -299,3 +299,14 @@ def test_ring_time_model_and_predictions():
     assert rec["speedup_fwd"] > 1.5 and "fused_bwd_ms" not in rec
     rec = predict("causal128k", 2, time_limit=3.0)
     assert abs(rec["zigzag_fwd_ms"] + rec["zigzag_bwd_ms"] - 242.6) / 242.6 < 0.1     # measured on 2 B200: 242.6 ms
+    # the ranks are not in lock step: under the star pattern one rank per step has four full tiles
+    # of work; the ring ends well before the sum of those (8 x 4 tiles) and not before a rank's own
+    # work plus the seven exchanges. Measured on 8 B200: 75.9 ms; predicted 45-76.
+    from ultraattn_b200.planner.cost import Machine_Config
+    tile = Machine_Config.b200_default().comp_profile_maps[1].get_comp_time_from_map_key((16384, 1, 32, 128, "1/1", False))[0]
+    assert 4 * tile < sparse["fwd_s"] < 0.6 * 8 * 4 * tile and 0.045 < sparse["fwd_s"] < 0.0759
+    meas = {"strided512k": 549.8, "gl512k": 626.1, "streaming512k": 85.7}        # ring on 8 B200, ms
+    for name, ms in meas.items():
+        rec = predict(name, 8, time_limit=3.0)
+        got = rec["ring_fwd_ms"] + rec.get("ring_bwd_ms", 0.0)
+        assert 0.7 * ms < got <= ms, (name, got, ms)                               # below, never above, the measurement
