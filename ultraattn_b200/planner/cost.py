@@ -601,7 +601,8 @@ def fused_step_time(table, cmap, pattern, seq_len: int, n_heads: int, head_dim: 
     leave as peer ``red.add``; where the machine profile has measured those transports
     (``Fused_Transport_Profile``) their throughput replaces the point-to-point link curve. The CTAs
     that stage do so before they take their first tile, so staging also costs compute time: its
-    duration times the share of the SMs that copy (``stage_s`` in the breakdown)."""
+    duration times the share of the SMs that copy (``stage_s`` in the breakdown). The dQ of foreign
+    rows leaves in a launch of its own after the backward kernel (``dq_push_s``)."""
     import numpy as _np
     m = m_config or Machine_Config.b200_default()
     table = _np.asarray(table)
@@ -651,9 +652,12 @@ def fused_step_time(table, cmap, pattern, seq_len: int, n_heads: int, head_dim: 
         launch = _np.array([B200_LAUNCH_S * 3, B200_LAUNCH_S * 5])
         share = min(copy_ctas, B200_SMS) / B200_SMS
         stage = [t_in(f_in) * share, t_in(b_in) * share]
+        # dQ of foreign rows is accumulated in a local fp32 mirror and pushed to its owner by a
+        # separate launch after the backward kernel: not overlapped with compute
+        dq_push = t_out(len(rows) * 2 * q_blk, "peer_red_add_f32")
         total = _np.array([max(comp_t[0] + stage[0], link[0]) + mem_f,
-                           max(comp_t[1] + stage[1], link[1]) + mem_b]) + launch
-        out["per_rank"].append({"rank": g, "tiles": len(tiles), "compute_s": comp_t.tolist(), "link_s": link, "stage_s": stage,
+                           max(comp_t[1] + stage[1], link[1]) + mem_b + dq_push]) + launch
+        out["per_rank"].append({"rank": g, "tiles": len(tiles), "compute_s": comp_t.tolist(), "link_s": link, "stage_s": stage, "dq_push_s": dq_push,
                                 "memory_s": [mem_f, mem_b], "total_s": total.tolist()})
     out["fwd_s"] = max(r["total_s"][0] for r in out["per_rank"])
     out["bwd_s"] = max(r["total_s"][1] for r in out["per_rank"])
