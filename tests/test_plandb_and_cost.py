@@ -3,6 +3,7 @@ import json
 import os
 
 import numpy as np
+import pytest
 
 from ultraattn_b200 import patterns as P
 from ultraattn_b200.patterns.blocks import BSA_Config
@@ -281,6 +282,24 @@ def test_fused_transport_profile_feeds_the_model(tmp_path):
     # staging takes SM time in proportion to the CTAs that copy
     assert abs(r_many["stage_s"][0] - r_many["link_s"][0]) < 1e-12
     assert abs(r_few["stage_s"][0] - r_few["link_s"][0] * 8 / 148) < 1e-12
+
+
+def test_partition_granularity_chosen_by_the_time_model():
+    """`plan_allocation(select="model")`: among the partitions at 1x / 2x / 4x the rank count, the
+    one with the shortest predicted step of the fused runtime; never predicted slower than the
+    balance rule's choice, same ownership convention, every tile assigned once."""
+    from ultraattn_b200.planner.cost import fused_step_time
+    from ultraattn_b200.runtime.context_parallel import plan_allocation
+    pat, S, H = P.strided(8, 4, 2), 65536, 8
+    shape = {"seq_len": S, "n_heads": H}
+    tb, cb = plan_allocation(pat, 4, 1, "ilp", time_limit=5.0)
+    tm, cm = plan_allocation(pat, 4, 1, "ilp", time_limit=5.0, select="model", shape=shape)
+    assert fused_step_time(tm, cm, pat, S, H)["step_s"] <= fused_step_time(tb, cb, pat, S, H)["step_s"] * (1 + 1e-9)
+    n = tm.shape[0]
+    assert n in (8, 16, 32) and ((tm >= 0) == (pat.refined(n) > 0)).all() and sorted(set(cm.tolist())) == [0, 1, 2, 3]
+    assert (np.diff(cm) >= 0).all()                                    # contiguous chunks, as callers shard
+    with pytest.raises(AssertionError, match="needs shape"):
+        plan_allocation(pat, 4, 1, "ilp", select="model")
 
 
 def test_ring_time_model_and_predictions():

@@ -18,11 +18,19 @@ from ..planner.pipeline import make_plan
 
 
 def plan_allocation(pattern: BSA_Repr, cp: int, fob: int = 1, allocation: str = "ilp",
-                    time_limit: float = 20.0, cmap=None):
+                    time_limit: float = 20.0, cmap=None, select: str = "balance", shape: Optional[dict] = None):
     """(table, cmap) of the tile allocation for ``cp`` ranks. ``cmap``: an ownership map (block ->
     rank), None for contiguous chunks, or ``"search"`` to let the planner pick among contiguous /
     residue-class / zigzag ownership (context remap; every rank then passes the blocks it owns
-    under the returned map, in increasing block order)."""
+    under the returned map, in increasing block order).
+
+    ``select``: how the partition granularity (1x, 2x, 4x the rank count) is chosen. ``"balance"``
+    (default) takes the coarsest one whose busiest rank is within 3 % of the mean. ``"model"``
+    solves all three and keeps the one for which the time model of the fused runtime
+    (``planner.cost.fused_step_time`` on the machine profile: tile times at that granularity,
+    staging, transfers, the passes around the kernels) predicts the shortest step; it needs
+    ``shape = {"seq_len": S, "n_heads": H[, "head_dim", "n_kv_heads", "batch"]}``. A finer
+    partition balances better but runs smaller tiles and moves more blocks; the model prices both."""
     cfg = BSA_Config(None, None, {"bsa_repr": pattern, "CP": (cp, 1)})
     if isinstance(cmap, str):
         assert cmap == "search", f"unknown cmap option {cmap!r}"
@@ -48,9 +56,29 @@ def plan_allocation(pattern: BSA_Repr, cp: int, fob: int = 1, allocation: str = 
     # busiest rank is within 3 % of the mean.
     base = max(cp, cfg.table.shape[0])
     best = None
+    assert select in ("balance", "model"), f"unknown select option {select!r}"
+    if select == "model":
+        assert shape is not None and "seq_len" in shape and "n_heads" in shape, \
+            "select='model' needs shape={'seq_len': ..., 'n_heads': ...}"
+        from ..planner.cost import fused_step_time
     for mult in ((1, 2, 4) if cmap is None and cp > 1 else (1,)):
-        al = solve_sparse_from_bsa(cfg, fob=fob, ParD=base * mult, time_limit=time_limit, cmap=cmap)
+        if select == "model" and shape["seq_len"] % (base * mult * 256):
+            continue                            # blocks must stay multiples of the kernels' 256-row tiles
+        try:
+            al = solve_sparse_from_bsa(cfg, fob=fob, ParD=base * mult, time_limit=time_limit, cmap=cmap)
+        except RuntimeError:
+            if best is None and mult == 1:
+                raise
+            continue                            # a finer partition the solver could not settle in time
         table = np.asarray(al.table)
+        if select == "model":
+            t = fused_step_time(table, np.asarray(al.cmap), pattern, shape["seq_len"], shape["n_heads"],
+                                shape.get("head_dim", 128), n_kv_heads=shape.get("n_kv_heads"),
+                                batch=shape.get("batch", 1))
+            score = t["step_s"] if fob else t["fwd_s"]
+            if best is None or score < best[0]:
+                best = (score, al)
+            continue
         vol = tile_volumes(pattern, table.shape[0])
         work = np.array([vol[table == r].sum() for r in range(cp)], dtype=float)
         imbalance = work.max() / max(work.mean(), 1e-9)
@@ -91,8 +119,10 @@ class ContextParallelAttention:
                  n_kv_heads: Optional[int] = None, batch: int = 1, allocation: str = "ilp",
                  plan_time_limit: float = 20.0, dtype=torch.bfloat16, cmap=None,
                  nvls_min_consumers: int = 2, plan=None, local_groups: bool = False,
-                 nvls_reduce: Optional[bool] = None, plan_type: str = "Flexflow"):
-        """``plan_type`` (NCCL path): how the launch order on the compute / send / receive streams
+                 nvls_reduce: Optional[bool] = None, plan_type: str = "Flexflow", select: str = "balance"):
+        """``select``: how the partition granularity is chosen, ``"balance"`` or ``"model"`` (see
+        :func:`plan_allocation`).
+        ``plan_type`` (NCCL path): how the launch order on the compute / send / receive streams
         is chosen, ``"Flexflow"`` (list scheduling) or ``"ILP"`` (the kernel-schedule integer
         program, reference search_algo/execute_plan.py:209-275).
         ``plan``: an earlier runtime's ``(table, cmap)`` to reuse instead of solving the
@@ -102,7 +132,8 @@ class ContextParallelAttention:
         self._ctor = dict(seq_len=seq_len, n_heads=n_heads, head_dim=head_dim, device=device, path=path,
                           n_kv_heads=n_kv_heads, batch=batch, allocation=allocation,
                           plan_time_limit=plan_time_limit, dtype=dtype, nvls_min_consumers=nvls_min_consumers,
-                          nvls_reduce=nvls_reduce, plan_type=plan_type)
+                          nvls_reduce=nvls_reduce, plan_type=plan_type, select=select)
+        shape = {"seq_len": seq_len, "n_heads": n_heads, "head_dim": head_dim, "n_kv_heads": n_kv_heads, "batch": batch}
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
@@ -112,7 +143,7 @@ class ContextParallelAttention:
         if path == "fused":
             from .fused import FusedContextParallel, SymmMemSpace
             box = [(plan if plan is not None else
-                    plan_allocation(pattern, self.world, 1, allocation, plan_time_limit, cmap))
+                    plan_allocation(pattern, self.world, 1, allocation, plan_time_limit, cmap, select, shape))
                    if self.rank == 0 else None]
             dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, 0), group=self.group)
             table, cm = box[0]
@@ -128,7 +159,7 @@ class ContextParallelAttention:
                       time_limit=plan_time_limit, cmap=cmap)
             if self.rank == 0 and allocation not in ("naive", "lightseq"):
                 # same partition granularity (and, with cmap="search", ownership) as the fused path
-                table0, cmap0 = plan_allocation(pattern, self.world, 1, allocation, plan_time_limit, cmap)
+                table0, cmap0 = plan_allocation(pattern, self.world, 1, allocation, plan_time_limit, cmap, select, shape)
                 kw["ParD"] = table0.shape[0]
                 if isinstance(cmap, str):
                     kw["cmap"] = cmap0
