@@ -366,6 +366,7 @@ def test_every_reference_module_path_imports_and_exports():
         "search_algo.graph_transformation_engine": ["Graph_Transformation_Engine", "Comp_Fusion_Substitution",
                                                     "Comp_Fusion_Transformation"],
         "search_algo.execute_plan": ["Execution_Plan", "Fused_Execution_Plan"],
+        "search_algo.search_comm": ["Brute_Force_Search_Engine", "get_configs"],
         "search_algo.database": ["Prof_DB"],
         "search_algo.initialize": ["get_proc_info", "initialize_distribution", "initialize_prof_db",
                                    "parse_slurm_tasks_per_node"],
