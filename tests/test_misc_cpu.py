@@ -364,7 +364,8 @@ def test_every_reference_module_path_imports_and_exports():
                                       "get_cc_optimal_schedule_from_table"],
         "search_algo.dependent_graph": ["Dependent_Graph", "Cuda_Kernel", "Comp_Kernel", "Comm_Kernel"],
         "search_algo.graph_transformation_engine": ["Graph_Transformation_Engine", "Comp_Fusion_Substitution",
-                                                    "Comp_Fusion_Transformation"],
+                                                    "Comp_Fusion_Transformation", "Graph_Substitution",
+                                                    "Graph_Transformation", "Comm_Rebuild_Engine"],
         "search_algo.execute_plan": ["Execution_Plan", "Fused_Execution_Plan"],
         "search_algo.search_comm": ["Brute_Force_Search_Engine", "get_configs"],
         "search_algo.database": ["Prof_DB"],

@@ -23,11 +23,39 @@ from .graph import Comp_Kernel, Dependent_Graph
 from .schedule import Execution_Plan
 
 
-class Comp_Fusion_Transformation:
-    """One rectangle: ``ids = (b, h, rows, cols, rank)``."""
+class Graph_Substitution:
+    """A rule that finds every place of a graph where one kind of rewrite applies."""
 
-    def __init__(self, ids: tuple):
-        self.ids = ids
+    def findall(self, d_graph: Dependent_Graph) -> list:
+        raise NotImplementedError
+
+    def findall_trans_in_d_graph(self, d_graph: Dependent_Graph, hierarchy_sp: int = 0) -> list:
+        """The reference's method name (search_algo/graph_transformation_engine.py:127); the rank
+        count is read from the graph here, so the second argument is accepted and unused."""
+        return self.findall(d_graph)
+
+
+class Graph_Transformation:
+    """One concrete rewrite of a graph, applied in place."""
+
+    def apply_on_d_graph(self, d_graph: Dependent_Graph) -> None:
+        raise NotImplementedError
+
+
+class Comm_Rebuild_Engine:
+    """Placeholder of the reference (search_algo/graph_transformation_engine.py:17-19, an empty
+    class there too): rebuilding point-to-point transfers into row / column broadcasts and
+    reductions is done by the plan lowering (``runtime.plan_ir``), not by a graph rewrite."""
+
+
+class Comp_Fusion_Transformation(Graph_Transformation):
+    """One rectangle: ``ids = (b, h, rows, cols, rank)``. The reference's constructor takes the
+    substitution first (``(sub, ids_tuple)``); both argument lists are accepted."""
+
+    def __init__(self, *args):
+        assert 1 <= len(args) <= 2, "Comp_Fusion_Transformation(ids) or (sub, ids)"
+        self.sub = args[0] if len(args) == 2 else None
+        self.ids = tuple(args[-1])
 
     @property
     def tiles(self) -> set:
@@ -72,7 +100,7 @@ class Comp_Fusion_Transformation:
         d_graph.kernel_dict[new_key] = new
 
 
-class Comp_Fusion_Substitution:
+class Comp_Fusion_Substitution(Graph_Substitution):
     """All rectangles of a given shape (x rows by y columns) in a graph."""
 
     def __init__(self, shape: tuple):
