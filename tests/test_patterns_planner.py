@@ -329,3 +329,28 @@ def test_random_patterns_plan_and_verify_property():
         assert ((al >= 0) == (fine > 0)).all() and al.max() < cp
 
     check()
+
+
+def test_fusion_engine_step_by_step_interface_matches_transform():
+    """The reference drives its engine in steps (shapes, rectangles, apply); doing the same by hand
+    with the greedy choice gives the plan that transform() returns."""
+    from search_algo.graph_transformation_engine import (Comp_Fusion_Transformation, Graph_Substitution,
+                                                         Graph_Transformation, Graph_Transformation_Engine)
+    g = _graph(P.full(1), 2, 8192, 0)
+    eng = Graph_Transformation_Engine(None, None, None)
+    best = eng.transform(copy.deepcopy(g), mode="greedy", plan_type="Flexflow")
+    eng.d_graph = g
+    subs = eng.calc_subs_dict()["comp_fusion"]
+    assert all(isinstance(s, Graph_Substitution) for s in subs)
+    assert [s.shape for s in subs] == eng.candidate_shapes(g)
+    every = eng.get_all_transformations()
+    assert all(isinstance(t, Graph_Transformation) for t in every)
+    assert sum(len(x) for x in eng.trans_sp) == len(every)
+    for sub in subs:
+        assert [t.ids for t in sub.findall_trans_in_d_graph(g, g.hierarchy_sp)] == [t.ids for t in sub.findall(g)]
+    chosen = eng.select_greedy(g)
+    plan = eng.apply_transformations(chosen, "Flexflow")
+    base = eng.apply_transformations([], "Flexflow")
+    assert abs(min(plan.end_time, base.end_time) - best.end_time) < 1e-9
+    t = every[0]
+    assert Comp_Fusion_Transformation(subs[0], t.ids).tiles == Comp_Fusion_Transformation(t.ids).tiles

@@ -153,9 +153,44 @@ class Graph_Transformation_Engine:
                     chosen.append(tr)
         return chosen
 
+    # ---- the reference's step-by-step interface (search_algo/graph_transformation_engine.py:176-263)
+    def calc_subs_dict(self) -> dict:
+        """``subs_dict['comp_fusion']``: one substitution per candidate shape, largest area first."""
+        assert hasattr(self, "d_graph"), "assign d_graph first (transform() does)"
+        self.comp_fusion_shapes = self.candidate_shapes(self.d_graph)
+        self.subs_dict = {"comp_fusion": [Comp_Fusion_Substitution(s) for s in self.comp_fusion_shapes],
+                          "comm_fusion": []}
+        return self.subs_dict
+
+    def get_all_transformations(self) -> list:
+        """``trans_all``: every rectangle of every shape; ``trans_sp[rank]`` groups them by rank."""
+        if not hasattr(self, "subs_dict"):
+            self.calc_subs_dict()
+        self.trans_all = [t for sub in self.subs_dict["comp_fusion"] for t in sub.findall(self.d_graph)]
+        self.trans_sp = [[] for _ in range(max(1, self.d_graph.hierarchy_sp))]
+        for t in self.trans_all:
+            self.trans_sp[t.ids[4]].append(t)
+        return self.trans_all
+
+    def apply_transformations(self, selected_trans: list, plan_type: str = None,
+                              time_limit: float = 20.0) -> Execution_Plan:
+        """Lower a copy of the graph with ``selected_trans`` applied."""
+        g = copy.deepcopy(self.d_graph)
+        for tr in selected_trans:
+            tr.apply_on_d_graph(g)
+        return Execution_Plan(g, g.fob, plan_type or getattr(self, "plan_type", "Flexflow"),
+                              time_limit=time_limit)
+
     def transform(self, d_graph: Dependent_Graph, transform_mode: str = "greedy",
-                  plan_type: str = "Flexflow", time_limit: float = 20.0) -> Execution_Plan:
-        """Return the best plan among the untransformed graph and the fused candidates."""
+                  plan_type: str = "Flexflow", time_limit: float = 20.0, mode: str = None) -> Execution_Plan:
+        """Return the best plan among the untransformed graph and the fused candidates. ``mode`` is
+        the reference's keyword for ``transform_mode``; its ``plan_type='automatic'`` is the list
+        schedule here."""
+        if mode is not None:
+            transform_mode = mode
+        if plan_type in ("automatic", "ablation1"):
+            plan_type = "Flexflow"
+        self.d_graph, self.plan_type = d_graph, plan_type
         base = Execution_Plan(copy.deepcopy(d_graph), d_graph.fob, plan_type, time_limit=time_limit)
         best = base
         if transform_mode == "greedy":
