@@ -107,3 +107,31 @@ def test_token_cross_entropy_wrappers_match_pytorch():
     work = logits.clone()
     got = E.xent_bwd_(work, tg, lse, torch.tensor(0.5))
     assert got is work and torch.allclose(got, x.grad, atol=1e-6) and got[2].abs().max() == 0
+
+
+def test_trainer_on_two_cpu_ranks_follows_the_single_rank_losses():
+    """The end-to-end trainer as fp32 CPU ranks: two context-parallel ranks (tokens sharded by the
+    plan's block ownership, attention through the plan executor over gloo, Adam sharded over the
+    ranks) must walk the same loss curve as one rank holding the whole sequence."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    args = ["--device", "cpu", "--path", "nccl", "--seq", "1024", "--layers", "2", "--hidden", "128", "--heads", "4",
+            "--head-dim", "32", "--ffn", "256", "--vocab", "512", "--blocks", "8", "--steps", "2", "--warmup", "1"]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+
+    def run(cmd):
+        r = subprocess.run(cmd, capture_output=True, text=True, cwd=root, env=env, timeout=900)
+        assert r.returncode == 0, r.stderr[-2000:]
+        return json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1])
+
+    one = run([sys.executable, "-m", "ultraattn_b200.drivers.train_llama"] + args)
+    two = run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+               "127.0.0.1", "--master-port", str(29930 + os.getpid() % 40), "-m",
+               "ultraattn_b200.drivers.train_llama"] + args)
+    assert one["n_gpus"] == 1 and two["n_gpus"] == 2 and two["path"] == "nccl" and one["device"] == "cpu"
+    assert len(one["losses"]) == 3 and one["losses"][0] > one["losses"][-1], one["losses"]   # it learns
+    for a, b in zip(one["losses"], two["losses"]):
+        assert abs(a - b) < 2e-5 * abs(a), (one["losses"], two["losses"])

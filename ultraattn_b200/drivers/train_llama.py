@@ -82,33 +82,46 @@ def main() -> None:
                          "and the GEMMs and report the attention / GEMM / other split")
     ap.add_argument("--offload-checkpoints", action="store_true",
                     help="keep the per-layer activation checkpoints in pinned host memory")
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
+                    help="cpu: fp32 ranks over gloo running the PyTorch restatements of the kernels (small shapes; "
+                         "checks the token sharding, the plan execution and the sharded optimizer without a GPU)")
     ap.add_argument("--estimate-memory", type=int, default=0, metavar="CP",
                     help="print the per-GPU memory plan for CP ranks and exit (needs no GPU)")
     a = ap.parse_args()
     if a.estimate_memory:
         from ..models.llama import estimate_memory
-        plan = estimate_memory(LlamaConfig(n_layers=a.layers, hidden=a.hidden, n_heads=a.heads, head_dim=128,
+        plan = estimate_memory(LlamaConfig(n_layers=a.layers, hidden=a.hidden, n_heads=a.heads, head_dim=a.head_dim,
                                            ffn=a.ffn, vocab=a.vocab), a.seq, a.estimate_memory, a.offload_checkpoints)
         print(json.dumps({k: round(v, 2) if isinstance(v, float) else v for k, v in plan.items()}))
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(dev)
+    on_gpu = a.device == "cuda"
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if on_gpu else torch.device("cpu")
+    if on_gpu:
+        torch.cuda.set_device(dev)
+    else:
+        assert a.path == "nccl" or world == 1, "--device cpu runs the plan executor (--path nccl)"
+        assert a.seq_algo == "cp" and not a.breakdown, "--device cpu: context-parallel path, no breakdown"
     group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         import datetime
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
+        if on_gpu:
+            dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
+        else:
+            dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=300))
         group = dist.group.WORLD
-    cfg = LlamaConfig(n_layers=a.layers, hidden=a.hidden, n_heads=a.heads, head_dim=128, ffn=a.ffn, vocab=a.vocab)
+    cfg = LlamaConfig(n_layers=a.layers, hidden=a.hidden, n_heads=a.heads, head_dim=a.head_dim, ffn=a.ffn,
+                      vocab=a.vocab)
     pattern = P.global_local(a.blocks, 1, 2)
     runtime = None
     if world > 1 and a.seq_algo == "ulysses":
         s_loc = a.seq // world
         pos = torch.arange(rank * s_loc, (rank + 1) * s_loc)
     elif world > 1:
-        runtime = ContextParallelAttention(pattern, a.seq, a.heads, 128, group=group, device=dev, path=a.path)
+        runtime = ContextParallelAttention(pattern, a.seq, a.heads, a.head_dim, group=group, device=dev, path=a.path)
         cmap = runtime.cmap
         par_d = runtime.table.shape[0]
         blk = a.seq // par_d
@@ -128,21 +141,32 @@ def main() -> None:
         return model.train_step(ids, targets, pos_dev, n_total_tokens=a.seq)
 
     loss = None
+    losses = []
     for _ in range(a.warmup):
         loss = step()
+        losses.append(loss)
     if world > 1:
         dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
+    if on_gpu:
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+    else:
+        import time
+        t_start = time.perf_counter()
     for _ in range(a.steps):
         loss = step()
-    e1.record()
+        losses.append(loss)
+    if on_gpu:
+        e1.record()
     if world > 1:
         dist.barrier()
-    torch.cuda.synchronize()
-    A.check_status(dev)
-    ms = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
+    if on_gpu:
+        torch.cuda.synchronize()
+        A.check_status(dev)
+        ms = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
+    else:
+        ms = torch.tensor([(time.perf_counter() - t_start) * 1e3 / a.steps])
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     split = None
@@ -156,8 +180,10 @@ def main() -> None:
         n_params = model.flat.numel()
         print(json.dumps({"metric": "e2e_tokens_per_s", "value": a.seq / (ms.item() / 1e3), "ms_per_step": ms.item(),
                           "n_gpus": world, "seq_len": a.seq, "layers": a.layers, "params": n_params, "loss": loss,
-                          "path": (a.path if a.seq_algo == "cp" else "ulysses-fused") if world > 1 else "local", "dtype": "bf16",
-                          "max_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
+                          "losses": losses,
+                          "path": (a.path if a.seq_algo == "cp" else "ulysses-fused") if world > 1 else "local",
+                          "dtype": "bf16" if on_gpu else "fp32", "device": a.device,
+                          "max_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30 if on_gpu else None,
                           **({"split_ms_max_over_ranks": split} if split else {})}), flush=True)
     if world > 1:
         dist.destroy_process_group()
