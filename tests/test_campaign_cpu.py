@@ -191,3 +191,60 @@ def test_step4_full_attention_takes_the_best_grid(tmp_path):
     assert got["_ablation=(w/o_gpu_tile,w/o_kernel_tile,Flexflow)"] == 4e-3      # Y = CP, X = 1 only
     assert got["_ablation=(w/o_kernel_tile,ILP)"] == 3e-3                         # best grid without kernel tile
     assert got["_ablation=(w_kernel_tile,ILP)"] == 2e-3                           # best of all
+
+
+def test_plan_generators_under_the_reference_argument_lists(tmp_path, monkeypatch):
+    """``generate_{intra,inter}_bsa_execution_plans(exp_config, da_config, prof_db, is_bypass_mode)``
+    and ``generate_general_full_execution_plans(exp_config, da_config, hierarchy, prof_db, ...)``:
+    first call writes the plans, bypass mode then finds every one, and bypass mode on an empty
+    database refuses instead of solving."""
+    import pytest
+    from search_algo.task1_bsa import (generate_general_full_execution_plans, generate_inter_bsa_execution_plans,
+                                       generate_intra_bsa_execution_plans)
+    from ultraattn_b200 import patterns as P
+    from ultraattn_b200.patterns.blocks import BSA_Config
+    from ultraattn_b200.plandb import ABLATION_SUFFIXES, Prof_DB
+    from ultraattn_b200.planner.cost import Dist_Attn_Config, Evaluation_Configs
+    monkeypatch.setenv("UA_DATABASE_ROOT", str(tmp_path))
+    db = Prof_DB("unit", "B200")
+    shape = {"S": (4096, 4096), "Nh": (2, 2), "bs": 1, "D": 128}
+    exp = Evaluation_Configs("ILP", 1, 0)
+    cfg = BSA_Config(None, None, {"bsa_repr": P.strided(4, 2, 1), "CP": (2, 1)})
+    da = Dist_Attn_Config.from_bsa_config(cfg, shape, 1)
+    with pytest.raises(AssertionError, match="bypass"):
+        generate_intra_bsa_execution_plans(exp, da, db, True)
+    keys = generate_intra_bsa_execution_plans(exp, da, db, False, time_limit=3.0)
+    assert len(keys) == len(ABLATION_SUFFIXES) and all(db.has_plan(k, 1) for k in keys)
+    assert generate_intra_bsa_execution_plans(exp, da, db, True) == keys
+    assert db.get_plan(keys[0], 1).verify() == []
+
+    full = Dist_Attn_Config.from_bsa_config(BSA_Config.create_full((4, 1)), shape, 1)
+    fkeys = generate_general_full_execution_plans(exp, full, 1, db, False)
+    assert len(fkeys) == 3 and generate_general_full_execution_plans(exp, full, 1, db, True) == fkeys   # 1x4, 2x2, 4x1
+    with pytest.raises(AssertionError, match="bypass"):
+        generate_general_full_execution_plans(Evaluation_Configs("ILP", 1, 1), full, 1, db, True)
+
+    cfg2 = BSA_Config(None, None, {"bsa_repr": P.strided(4, 2, 1), "CP": (1, 2)})
+    shape2 = {"S": (8192, 8192), "Nh": (2, 2), "bs": 1, "D": 128}
+    da2 = Dist_Attn_Config.from_bsa_config(cfg2, shape2, 0)
+    ikeys = generate_inter_bsa_execution_plans(exp, da2, db, False, time_limit=3.0)
+    assert exp.hierarchy == 0 and da2.hierarchy == 0
+    assert all(db.has_plan(k, 0) for k in ikeys) and generate_inter_bsa_execution_plans(exp, da2, db, True) == ikeys
+    assert db.get_plan(ikeys[-1], 0).verify() == []
+
+
+def test_inter_node_plans_of_the_dense_patterns(tmp_path, monkeypatch):
+    """Two nodes of two ranks, dense patterns: FULL gets the manual plans of every node grid
+    (shape-free, one per pass), causal is planned per shape; a second call finds all of them."""
+    from search_algo.task1_bsa import step3_generate_inter_dense_exe_plans
+    from ultraattn_b200.drivers.exp_configs import step0_top_down_decompose
+    from ultraattn_b200.plandb import Prof_DB
+    monkeypatch.setenv("UA_DATABASE_ROOT", str(tmp_path))
+    db = Prof_DB("unit", "B200")
+    space = step0_top_down_decompose("dense_train", max_intra=2, max_nodes=2, quick=True)
+    full_keys, causal_keys = step3_generate_inter_dense_exe_plans(space, db, time_limit=3.0)
+    assert full_keys and all("CP=(1, 2)" in k and db.has_plan(k, 0) for k in full_keys)
+    assert {k.split("_")[0] for k in full_keys} == {f"fob={f}" for f in space.fobs}
+    assert causal_keys and all(db.has_plan(k, 0) and db.get_plan(k, 0).verify() == [] for k in causal_keys)
+    again = step3_generate_inter_dense_exe_plans(space, db, time_limit=3.0)
+    assert again == (full_keys, causal_keys)

@@ -17,14 +17,22 @@ from ..plandb import Prof_DB, full_plan_key
 from ..planner.dense import create_ablation_configs_for_full, create_plan_for_full
 
 
-def generate(prof_db: Prof_DB, cp: int, fobs=(0, 1)) -> list:
-    """Store every missing (Y, X) plan; returns the keys that are present afterwards."""
+def full_plan_keys(cp: int, fobs=(0, 1), hierarchy: int = 1) -> list:
+    CP = (cp, 1) if hierarchy else (1, cp)
+    return [full_plan_key(fob, CP, Y, X) for fob in fobs for Y, X in create_ablation_configs_for_full(cp)]
+
+
+def generate(prof_db: Prof_DB, cp: int, fobs=(0, 1), hierarchy: int = 1) -> list:
+    """Store every missing (Y, X) plan of one level (1: the ``cp`` ranks of a node, 0: ``cp`` nodes);
+    returns the keys that are present afterwards."""
     keys = []
+    CP = (cp, 1) if hierarchy else (1, cp)
     for fob in fobs:
         for Y, X in create_ablation_configs_for_full(cp):
-            key = full_plan_key(fob, (cp, 1), Y, X)
-            if not prof_db.has_plan(key, 1):
-                prof_db.put_plan(key, create_plan_for_full(cp, X, fob, prof_db.m_config), 1)
+            key = full_plan_key(fob, CP, Y, X)
+            if not prof_db.has_plan(key, hierarchy):
+                prof_db.put_plan(key, create_plan_for_full(cp, X, fob, prof_db.m_config, hierarchy=hierarchy),
+                                 hierarchy)
             keys.append(key)
     return keys
 

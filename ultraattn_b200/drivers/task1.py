@@ -184,16 +184,86 @@ def step3_generate_inter_bsa_exe_plans(space, prof_db, time_limit=20.0) -> list:
                 work.append((fob, cfg, shape))
     if not dist.is_initialized() or dist.get_rank() == 0:
         for fob, cfg, shape in work:
-            da = Dist_Attn_Config.from_bsa_config(cfg, shape, 0)
-            prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
-            tiled = get_general_bsa_cc_optimal_schedule(fob, da, prof_db, None, time_limit)
-            for suf in ABLATION_SUFFIXES:
-                g = Dependent_Graph(tiled, fob, bsa_comp_key_suffixes=[suf])
-                prof_db.put_plan(prefix + suf, Execution_Plan(g, fob, "ILP" if "ILP" in suf else "Flexflow",
-                                                              time_limit=time_limit), 0)
+            _generate_inter_plans(fob, cfg, shape, prof_db, time_limit)
     if dist.is_initialized():
         dist.barrier()
     return work
+
+
+def step3_generate_inter_dense_exe_plans(space, prof_db, time_limit=20.0) -> tuple:
+    """Inter-node plans of the dense patterns (search_algo/task1_bsa.py:826-899): FULL attention
+    gets the shape-free manual plans of every node grid, like step 1 does inside a node; causal
+    attention is planned per shape like any block-sparse pattern. Returns (full keys, causal keys)."""
+    from ..utils.bsa_helpers import bsa_is_causal, bsa_is_full
+    from .intra_attn_gen import generate
+    prof_db.m_config_update_inter_bsa_profile()
+    multi = [c for c in space.inter_bsa_configs if c.CP[1] > 1]
+    full_keys, causal_keys = [], []
+    if not dist.is_initialized() or dist.get_rank() == 0:
+        for nodes in sorted({c.CP[1] for c in multi if bsa_is_full(c)}):
+            full_keys += generate(prof_db, nodes, space.fobs, hierarchy=0)
+        for fob in space.fobs:
+            for cfg in (c for c in multi if bsa_is_causal(c)):
+                for shape in space.shape_configs(cfg.CP[0] * cfg.CP[1]):
+                    causal_keys += _generate_inter_plans(fob, cfg, shape, prof_db, time_limit)
+    if dist.is_initialized():
+        dist.barrier()
+    return full_keys, causal_keys
+
+
+def _generate_inter_plans(fob, cfg, shape, prof_db, time_limit=20.0) -> list:
+    """Inter-node plans of one (pattern, shape, pass): one per ablation of the intra level, whose
+    measured times price the compute kernels of the inter graph."""
+    da = Dist_Attn_Config.from_bsa_config(cfg, shape, 0)
+    prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
+    keys = [prefix + suf for suf in ABLATION_SUFFIXES]
+    if all(prof_db.has_plan(k, 0) for k in keys):
+        print_rank_0(f"plans {prefix}: bypassed")
+        return keys
+    tiled = get_general_bsa_cc_optimal_schedule(fob, da, prof_db, None, time_limit)
+    for key, suf in zip(keys, ABLATION_SUFFIXES):
+        g = Dependent_Graph(tiled, fob, bsa_comp_key_suffixes=[suf])
+        prof_db.put_plan(key, Execution_Plan(g, fob, "ILP" if "ILP" in suf else "Flexflow", time_limit=time_limit), 0)
+    return keys
+
+
+# ---- the same generators under the reference's argument lists ------------------------------------
+def _check_bypass(keys, prof_db, hierarchy, is_bypass_mode) -> None:
+    if is_bypass_mode:
+        absent = [k for k in keys if not prof_db.has_plan(k, hierarchy)]
+        assert not absent, f"bypass mode: these plans are not in the database: {absent[:2]}"
+
+
+def generate_intra_bsa_execution_plans(exp_config, da_config, prof_db, is_bypass_mode: bool = False,
+                                       time_limit: float = 20.0) -> list:
+    """``(exp_config, da_config, prof_db, is_bypass_mode)``: search_algo/task1_bsa.py:153-241. In
+    bypass mode (ranks of a GPU job, which must not solve) every plan has to be stored already."""
+    exp_config.hierarchy = da_config.hierarchy = 1
+    cfg, shape = da_config.bsa_config, da_config.shape_config
+    _check_bypass([plan_key_prefix(exp_config.fob, cfg.CP, shape, cfg) + s for s in ABLATION_SUFFIXES], prof_db, 1,
+                  is_bypass_mode)
+    return generate_bsa_execution_plans(exp_config.fob, cfg, shape, prof_db, 1, time_limit)
+
+
+def generate_inter_bsa_execution_plans(exp_config, da_config, prof_db, is_bypass_mode: bool = False,
+                                       time_limit: float = 20.0) -> list:
+    """``(exp_config, da_config, prof_db, is_bypass_mode)``: search_algo/task1_bsa.py:501-578."""
+    exp_config.hierarchy = da_config.hierarchy = 0
+    cfg, shape = da_config.bsa_config, da_config.shape_config
+    _check_bypass([plan_key_prefix(exp_config.fob, cfg.CP, shape, cfg) + s for s in ABLATION_SUFFIXES], prof_db, 0,
+                  is_bypass_mode)
+    return _generate_inter_plans(exp_config.fob, cfg, shape, prof_db, time_limit)
+
+
+def generate_general_full_execution_plans(exp_config, da_config, hierarchy, prof_db,
+                                          is_bypass_mode: bool = False) -> list:
+    """Shape-free manual plans of FULL attention on every grid of ``da_config``'s rank count at one
+    level (search_algo/task1_bsa.py:615-669); returns the keys."""
+    from .intra_attn_gen import full_plan_keys, generate
+    exp_config.hierarchy = da_config.hierarchy = hierarchy
+    cp = da_config.bsa_config.CP[0 if hierarchy else 1]
+    _check_bypass(full_plan_keys(cp, [exp_config.fob], hierarchy), prof_db, hierarchy, is_bypass_mode)
+    return generate(prof_db, cp, [exp_config.fob], hierarchy)
 
 
 def main(argv=None) -> None:
@@ -210,6 +280,8 @@ def main(argv=None) -> None:
         step1_generate_intra_full_exe_plans(space, prof_db)
         step2_profile_intra_full_exe_plans(space, prof_db, device, info["world_size"])
     step3_generate_inter_bsa_exe_plans(space, prof_db)
+    if space.exp_class == "dense_train" and info["node_num"] > 1:
+        step3_generate_inter_dense_exe_plans(space, prof_db)     # + the manual node grids of FULL attention
     print_rank_0("task1 done")
     if dist.is_initialized():
         dist.destroy_process_group()

@@ -96,14 +96,15 @@ def create_plan_key_suffixes_for_full(hierarchy_cp: int) -> list:
 
 
 def create_plan_for_full(CP: int, X: int, fob: int, m_config: Machine_Config = None, shape_config=None,
-                         first_dim: int = 0) -> Execution_Plan:
+                         first_dim: int = 0, hierarchy: int = 1) -> Execution_Plan:
     """Manual plan of FULL attention on a Y x X grid. Without ``shape_config`` the graph is
-    shape-free (placeholder kernel times) and can be materialised for a shape later."""
-    cfg = BSA_Config.create_full((CP, 1))
+    shape-free (placeholder kernel times) and can be materialised for a shape later.
+    ``hierarchy``: 1 = the grid spans the ``CP`` ranks of a node, 0 = ``CP`` nodes."""
+    cfg = BSA_Config.create_full((CP, 1) if hierarchy else (1, CP))
     m_config = m_config or Machine_Config.b200_default()
     svg = shape_config is None
     shape = shape_config or {"S": (CP * 1024, CP * 1024), "Nh": (1, 1), "bs": 1, "D": 128}
-    da = Dist_Attn_Config.from_bsa_config(cfg, shape, hierarchy=1)
+    da = Dist_Attn_Config.from_bsa_config(cfg, shape, hierarchy=hierarchy)
     table = get_block_schedule_table_for_full(CP, X)
     sched = Dist_Attn_Schedule(da, m_config, (CP, CP, 1, 1), np.arange(CP)[None, :], table[None, None])
     g = Dependent_Graph(sched, fob, seqlen_variable_graph=svg)
