@@ -20,7 +20,8 @@ from search_algo.execute_plan import Execution_Plan  # noqa: E402
 from search_algo.global_vars import get_global_var  # noqa: E402
 from search_algo.initialize import initialize_distribution, initialize_prof_db  # noqa: E402
 from search_algo.search_engine import Dist_Attn_Config, Evaluation_Configs  # noqa: E402
-from search_algo.task1_bsa import get_general_bsa_cc_optimal_schedule  # noqa: E402
+from search_algo.task1_bsa import (generate_intra_bsa_execution_plans, get_general_bsa_cc_optimal_schedule,  # noqa: E402
+                                   profile_all_intra_BSA)
 from search_algo.utils import Block_Type  # noqa: E402
 
 
@@ -63,6 +64,18 @@ def main() -> None:
             print(f"fob={fob}: {len(plan.valid_kernels)} kernels, predicted {plan.end_time:.3e} s, "
                   f"measured {results[0]['time']} s, plan checks: {'ok' if plan.verify() == [] else plan.verify()}",
                   flush=True)
+
+    # the same configuration through the plan database, as the campaign does it: rank 0 writes the
+    # five ablation plans (a second call would find them: "bypass"), every rank then measures them
+    import torch.distributed as dist
+    exp_config = Evaluation_Configs(plan_type="ILP", MAX_QUEUE_SIZE=100, fob=0, hierarchy=1, transform_mode="greedy")
+    if rank == 0:
+        generate_intra_bsa_execution_plans(exp_config, da_config, prof_db, False)
+    dist.barrier(gloo_group)
+    generate_intra_bsa_execution_plans(exp_config, da_config, prof_db, True)      # bypass mode: all stored
+    measured = profile_all_intra_BSA(None, exp_config, da_config, ncclcomm_global, gloo_group, None, prof_db)
+    if rank == 0:
+        print(f"database: {len(measured)} ablation plans measured", flush=True)
 
 
 if __name__ == "__main__":

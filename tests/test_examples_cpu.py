@@ -33,3 +33,4 @@ def test_reference_style_campaign_example_on_two_cpu_ranks(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     lines = [ln for ln in r.stdout.splitlines() if ln.startswith("fob=")]
     assert len(lines) == 2 and all("plan checks: ok" in ln for ln in lines), r.stdout
+    assert "database: 5 ablation plans measured" in r.stdout, r.stdout[-2000:]

@@ -89,23 +89,47 @@ def step1_generate_intra_bsa_exe_plans(space, prof_db, time_limit=20.0) -> list:
     return work
 
 
+def _profile_intra_bsa_one(fob, cfg, shape, prof_db, device) -> list:
+    """Measure the stored intra plans (every ablation) of one (pass, pattern, shape) that have no
+    profile yet; every rank of the job calls this. Returns the keys measured now."""
+    done = []
+    prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
+    for suf in ABLATION_SUFFIXES:
+        key = prefix + suf
+        if prof_db.get_profile(key, 1) is not None:
+            continue
+        plan = prof_db.get_plan(key, 1)
+        other = prof_db.get_plan(plan_key_prefix(0, cfg.CP, shape, cfg) + suf, 1) if fob == 1 else plan
+        res = benchmark_orchestrate_bsa(other, plan if fob == 1 else None, fob, device)
+        if not dist.is_initialized() or dist.get_rank() == 0:
+            prof_db.put_profile(key, res["hfu"], res["time"], res["sim_time"], 1)
+        if dist.is_initialized():
+            dist.barrier()
+        done.append(key)
+    return done
+
+
 def step2_profile_intra_bsa_exe_plans(work, prof_db, device, world: int) -> None:
     """Measure every stored intra plan whose CP equals the number of ranks running now."""
     for fob, cfg, shape in work:
-        if cfg.CP[0] != world:
-            continue
-        prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
-        for suf in ABLATION_SUFFIXES:
-            key = prefix + suf
-            if prof_db.get_profile(key, 1) is not None:
-                continue
-            plan = prof_db.get_plan(key, 1)
-            other = prof_db.get_plan(plan_key_prefix(0, cfg.CP, shape, cfg) + suf, 1) if fob == 1 else plan
-            res = benchmark_orchestrate_bsa(other, plan if fob == 1 else None, fob, device)
-            if not dist.is_initialized() or dist.get_rank() == 0:
-                prof_db.put_profile(key, res["hfu"], res["time"], res["sim_time"], 1)
-            if dist.is_initialized():
-                dist.barrier()
+        if cfg.CP[0] == world:
+            _profile_intra_bsa_one(fob, cfg, shape, prof_db, device)
+
+
+def profile_all_intra_BSA(args, exp_config, da_config, ncclcomm_global=None, gloo_global_group=None,
+                          tensor_buf=None, prof_db=None) -> list:
+    """One configuration of step 2 under the reference's argument list (search_algo/task1_bsa.py:
+    244-359). The communicator, the control group and the preallocated buffer are accepted and
+    unused: the executor here uses the default process group and allocates per plan. Ranks beyond
+    the configuration's CP return at once, as there."""
+    assert prof_db is not None, "profile_all_intra_BSA needs the plan database"
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    cp = da_config.bsa_config.CP[0]
+    if cp != world:
+        print_rank_0(f"[WARN]: this configuration needs {cp} ranks, the job has {world}: skipped")
+        return []
+    device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    return _profile_intra_bsa_one(exp_config.fob, da_config.bsa_config, da_config.shape_config, prof_db, device)
 
 
 def _full_configs(space) -> list:
