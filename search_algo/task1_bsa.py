@@ -10,7 +10,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from ultraattn_b200.drivers.task1 import (generate_bsa_execution_plans, generate_general_full_execution_plans,  # noqa: E402,F401
                                           generate_inter_bsa_execution_plans, generate_intra_bsa_execution_plans,
                                           get_general_bsa_cc_optimal_schedule,
-                                          main, profile_all_intra_BSA, step1_generate_intra_bsa_exe_plans,
+                                          main, profile_all_intra_BSA, profile_all_intra_full, step1_generate_intra_bsa_exe_plans,
                                           step1_generate_intra_full_exe_plans,
                                           step2_profile_intra_bsa_exe_plans,
                                           step2_profile_intra_full_exe_plans,

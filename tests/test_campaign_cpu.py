@@ -48,6 +48,17 @@ def _worker(rank, world, port, root, ret):
                 for kt in (False, True):
                     p = fresh.get_profile(fprefix + full_profile_suffix(kt, Y, X))
                     assert p is not None and float(p["time"]) > 0 and float(p["sim_time"]) > 0, (fob, Y, X, kt)
+        # the per-configuration forms under the reference's argument lists find everything measured
+        from search_algo.task1_bsa import profile_all_intra_BSA, profile_all_intra_full
+        from search_algo.task2_bsa import profile_all_inter_BSA
+        from ultraattn_b200.planner.cost import Dist_Attn_Config, Evaluation_Configs
+        exp0 = Evaluation_Configs("ILP", 1, 0)
+        assert profile_all_intra_full(None, exp0, Dist_Attn_Config.from_bsa_config(full, shape, 1), None, None, None, db) == []
+        da_star = Dist_Attn_Config.from_bsa_config(cfg, shape, 1)
+        assert profile_all_intra_BSA(None, exp0, da_star, None, None, None, db) == []
+        inter_keys = profile_all_inter_BSA(None, exp0, da_star, None, None, None, db)
+        assert len(inter_keys) == (len(ABLATION_SUFFIXES) if rank == 0 else 0)
+        dist.barrier()
         # step 4 + baselines: the figure table gets its ring / zigzag / stripe columns
         from ultraattn_b200.drivers import report, task2
         causal = BSA_Config.create_causal((2, 1))

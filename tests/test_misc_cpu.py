@@ -354,7 +354,8 @@ def test_every_reference_module_path_imports_and_exports():
                               "get_factors", "closest_fraction", "unique_list", "use_all_cpus"],
         "search_algo.workload_partition": ["solve_sparse_from_bsa", "naive_allocate_strategy",
                                            "Quad_LP_GUROBI_from_block_config", "comp_balance_allocate_strategy",
-                                           "Quad_LP_GUROBI", "ILP", "solve_global_causal"],
+                                           "Quad_LP_GUROBI", "ILP", "solve_global_causal", "solve_custom_sparse",
+                                           "print_lp_result", "convert_result_to_np", "main"],
         "search_algo.manual_schedules": ["get_qo_schedule_table", "get_kv_schedule_table", "get_cc_optimal_schedule_table"],
         "search_algo.dense_utils": ["CP2ParD_map", "get_block_schedule_table_for_full", "create_plan_for_full",
                                     "create_ablation_configs_for_full", "create_plan_key_suffixes_for_full",
@@ -380,8 +381,13 @@ def test_every_reference_module_path_imports_and_exports():
         "search_algo.global_vars": ["get_global_var", "set_global_var", "TASK_STATUS"],
         "search_algo.task1_bsa": ["main", "get_general_bsa_cc_optimal_schedule", "step1_generate_intra_bsa_exe_plans",
                                   "step1_generate_intra_full_exe_plans", "step2_profile_intra_bsa_exe_plans",
-                                  "step2_profile_intra_full_exe_plans", "step3_generate_inter_bsa_exe_plans"],
-        "search_algo.task2_bsa": ["main", "step4_profile_inter_bsa_exe_plans"], "search_algo.main": ["main"],
+                                  "step2_profile_intra_full_exe_plans", "step3_generate_inter_bsa_exe_plans",
+                                  "step3_generate_inter_dense_exe_plans", "generate_intra_bsa_execution_plans",
+                                  "generate_inter_bsa_execution_plans", "generate_general_full_execution_plans",
+                                  "profile_all_intra_BSA", "profile_all_intra_full",
+                                  "get_general_bsa_cc_optimal_schedule_old"],
+        "search_algo.task2_bsa": ["main", "step4_profile_inter_bsa_exe_plans", "step4_profile_inter_full_exe_plans",
+                                  "profile_all_inter_BSA", "profile_all_inter_full"], "search_algo.main": ["main"],
         "search_algo.fusion_evaluate": ["main"], "search_algo.intra_attn_gen": ["main"],
         "orchestrated_attn": ["orchestrated_attn_func", "orchestrated_attn_backward", "OrchestratedAttnFunc",
                               "Input_Row_Fwd", "Input_Col_Fwd", "Output_Row_Fwd", "Output_Col_Fwd",
@@ -496,3 +502,25 @@ def test_planner_helpers_accept_the_reference_argument_lists():
     plan = create_plan_for_full(da, Machine_Config.b200_default(), 2, 1, 0)
     assert plan.X == 2 and plan.fob == 1 and plan.verify() == []
     assert create_plan_for_full(4, 2, 0).X == 2                                                  # short form
+
+
+def test_solver_result_helpers_of_workload_partition(capsys):
+    """``convert_result_to_np`` / ``print_lp_result`` read a solver's variable dictionary
+    (``x_i_j_k`` with a value attribute) into the allocation table; ``solve_custom_sparse`` solves
+    one parametric pattern and every non-empty tile gets a rank."""
+    import numpy as np
+    from search_algo.workload_partition import convert_result_to_np, print_lp_result, solve_custom_sparse
+
+    class Var:
+        def __init__(self, x):
+            self.X = x
+    own = {(1, 0): 0, (2, 0): 1, (2, 1): 1}
+    Vars = {f"x_{i}_{j}_{k}": Var(1.0 if r == k else 0.0) for (i, j), r in own.items() for k in range(2)}
+    table = convert_result_to_np(2, 3, Vars, "X", np.array([0, 1, 1]))
+    assert table.tolist() == [[0, -1, -1], [0, 1, -1], [1, 1, 1]]
+    print_lp_result(2, 3, Vars, "X", np.array([0, 1, 1]))
+    out = capsys.readouterr().out
+    assert "Allocation Matrix:" in out and out.strip().splitlines()[-1].split() == ["1", "1", "1"]
+    al = solve_custom_sparse(CP=2, Par_D=4, local_blocks=2, time_limit=5.0)
+    t = np.asarray(al.table)
+    assert t.shape == (4, 4) and (t[np.arange(4), np.arange(4)] >= 0).all() and t[0, 3] == -1

@@ -150,51 +150,73 @@ def step1_generate_intra_full_exe_plans(space, prof_db) -> list:
     return keys
 
 
-def step2_profile_intra_full_exe_plans(space, prof_db, device, world: int) -> None:
-    """Measure every grid (Y, X) of FULL attention on the ranks running now, without kernel tile
-    (the manual launch plan: one launch and one message per tile) and with it (gathers, one
-    launch, merge / reduce-scatter), under the keys the inter-level planner looks up
-    (``..._ablation=({w/o_kernel_tile|w_kernel_tile},Y=..,X=..,dim=0)``; reference:
-    search_algo/task1_bsa.py:404-470)."""
+def _profile_intra_full_one(fob, cfg, shape, prof_db, device, world: int) -> list:
+    """Measure every grid (Y, X) of FULL attention for one (pass, shape), without kernel tile (the
+    manual launch plan: one launch and one message per tile) and with it (gathers, one launch,
+    merge / reduce-scatter); every rank calls this. Returns the keys measured now."""
+    from ..planner.cost import Dist_Attn_Config as _DA
     from ..planner.dense import create_ablation_configs_for_full, create_plan_for_full
+    from ..planner.schedule import Fused_Execution_Plan
     from ..runtime.grid import GridExecutor
     from ..utils.misc import calc_flops
     from .benchmark import benchmark_ops
+    done = []
+    prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
+    for Y, X in create_ablation_configs_for_full(world):
+        for kernel_tile in (False, True):
+            key = prefix + full_profile_suffix(kernel_tile, Y, X)
+            if prof_db.get_profile(key, 1) is not None:
+                continue
+            if not kernel_tile:
+                pf = create_plan_for_full(world, X, 0, prof_db.m_config, shape_config=shape)
+                pb = create_plan_for_full(world, X, 1, prof_db.m_config, shape_config=shape) if fob else None
+                res = benchmark_orchestrate_bsa(pf, pb, fob, device)
+            else:
+                dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+                gx = GridExecutor(Y, X, device=device)
+                g = torch.Generator().manual_seed(dist.get_rank() if dist.is_initialized() else 0)
+                S_loc = shape["S"][0] // world
+                mk = lambda h: torch.randn(shape["bs"], S_loc, h, shape["D"], generator=g).to(dtype).to(device)
+                q, k, v, d_o = mk(shape["Nh"][0]), mk(shape["Nh"][1]), mk(shape["Nh"][1]), mk(shape["Nh"][0])
+                o, lse = gx.forward(q, k, v)
+                fn = (lambda: gx.forward(q, k, v)) if fob == 0 else (lambda: gx.backward(d_o, q, k, v, o, lse))
+                t = benchmark_ops(fn, 2, 2, 2, device)
+                _, hw = calc_flops(shape["bs"], shape["S"], shape["Nh"][0], shape["D"], False, fob, 1.0)
+                sim_t = Fused_Execution_Plan(Y, X, None, fob, prof_db.m_config).materialize(
+                    _DA.from_bsa_config(cfg, shape, 1))
+                res = {"time": t, "hfu": hw / t / world / 1e12, "sim_time": float(sim_t)}
+            if not dist.is_initialized() or dist.get_rank() == 0:
+                prof_db.put_profile(key, res["hfu"], res["time"], res["sim_time"], 1)
+            if dist.is_initialized():
+                dist.barrier()
+            done.append(key)
+    return done
+
+
+def step2_profile_intra_full_exe_plans(space, prof_db, device, world: int) -> None:
+    """Measure every grid (Y, X) of FULL attention on the ranks running now, under the keys the
+    inter-level planner looks up (``..._ablation=({w/o_kernel_tile|w_kernel_tile},Y=..,X=..,dim=0)``;
+    reference: search_algo/task1_bsa.py:404-470)."""
     for cfg in _full_configs(space):
         if cfg.CP[0] != world:
             continue
         for shape in space.shape_configs(world):
             for fob in space.fobs:
-                prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
-                for Y, X in create_ablation_configs_for_full(world):
-                    for kernel_tile in (False, True):
-                        key = prefix + full_profile_suffix(kernel_tile, Y, X)
-                        if prof_db.get_profile(key, 1) is not None:
-                            continue
-                        if not kernel_tile:
-                            pf = create_plan_for_full(world, X, 0, prof_db.m_config, shape_config=shape)
-                            pb = create_plan_for_full(world, X, 1, prof_db.m_config, shape_config=shape) if fob else None
-                            res = benchmark_orchestrate_bsa(pf, pb, fob, device)
-                        else:
-                            dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
-                            gx = GridExecutor(Y, X, device=device)
-                            g = torch.Generator().manual_seed(dist.get_rank() if dist.is_initialized() else 0)
-                            S_loc = shape["S"][0] // world
-                            mk = lambda h: torch.randn(shape["bs"], S_loc, h, shape["D"], generator=g).to(dtype).to(device)
-                            q, k, v, d_o = mk(shape["Nh"][0]), mk(shape["Nh"][1]), mk(shape["Nh"][1]), mk(shape["Nh"][0])
-                            o, lse = gx.forward(q, k, v)
-                            fn = (lambda: gx.forward(q, k, v)) if fob == 0 else (lambda: gx.backward(d_o, q, k, v, o, lse))
-                            t = benchmark_ops(fn, 2, 2, 2, device)
-                            _, hw = calc_flops(shape["bs"], shape["S"], shape["Nh"][0], shape["D"], False, fob, 1.0)
-                            from ..planner.schedule import Fused_Execution_Plan
-                            sim = Fused_Execution_Plan(Y, X, None, fob, prof_db.m_config)
-                            from ..planner.cost import Dist_Attn_Config as _DA
-                            sim_t = sim.materialize(_DA.from_bsa_config(cfg, shape, 1))
-                            res = {"time": t, "hfu": hw / t / world / 1e12, "sim_time": float(sim_t)}
-                        if not dist.is_initialized() or dist.get_rank() == 0:
-                            prof_db.put_profile(key, res["hfu"], res["time"], res["sim_time"], 1)
-                        if dist.is_initialized():
-                            dist.barrier()
+                _profile_intra_full_one(fob, cfg, shape, prof_db, device, world)
+
+
+def profile_all_intra_full(args, exp_config, da_config, ncclcomm_global=None, gloo_global_group=None,
+                           tensor_buf=None, prof_db=None) -> list:
+    """One FULL-attention configuration of step 2 under the reference's argument list
+    (search_algo/task1_bsa.py:362-498); see :func:`profile_all_intra_BSA` for the unused arguments."""
+    assert prof_db is not None, "profile_all_intra_full needs the plan database"
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    cfg = da_config.bsa_config
+    if cfg.CP[0] != world:
+        print_rank_0(f"[WARN]: this configuration needs {cfg.CP[0]} ranks, the job has {world}: skipped")
+        return []
+    device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    return _profile_intra_full_one(exp_config.fob, cfg, da_config.shape_config, prof_db, device, world)
 
 
 def step3_generate_inter_bsa_exe_plans(space, prof_db, time_limit=20.0) -> list:

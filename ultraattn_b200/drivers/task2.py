@@ -55,6 +55,29 @@ def prepare_inter_comp_plans(inter_plan, prof_db, da_config=None, node_id: int =
     return plans
 
 
+def _profile_inter_one(fob, cfg, shape, prof_db) -> list:
+    """Inter-level profiles of one (pass, pattern, shape) on a single node: the inter plan has one
+    compute kernel, so each ablation's time is that of its intra plan (for FULL attention, of the
+    best grid the ablation may use). Returns the keys written."""
+    written = []
+    if cfg.CP[1] != 1:
+        return written          # several nodes: measured by running the inter plan on all of them
+    prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
+    for suf in ABLATION_SUFFIXES:
+        intra = prof_db.get_profile(prefix + suf, 1)
+        if intra is None and cfg.bsa_repr.check_full():
+            # FULL attention is measured per (Y, X) grid: an ablation level stands for
+            # the best grid it may use (reference: search_algo/bsa_utils.py:53-70)
+            from ..utils.bsa_helpers import get_b2f_suf_map
+            cands = [prof_db.get_profile(prefix + s, 1) for s in get_b2f_suf_map(cfg.CP[0])[suf]]
+            cands = [c for c in cands if c is not None]
+            intra = min(cands, key=lambda c: float(c["time"])) if cands else None
+        if intra is not None:
+            prof_db.put_profile(prefix + suf, intra["hfu"], float(intra["time"]), float(intra["sim_time"]), 0)
+            written.append(prefix + suf)
+    return written
+
+
 def step4_profile_inter_bsa_exe_plans(space, prof_db, world: int) -> None:
     if dist.is_initialized() and dist.get_rank() != 0:
         return
@@ -63,19 +86,21 @@ def step4_profile_inter_bsa_exe_plans(space, prof_db, world: int) -> None:
             if cfg.CP[0] * cfg.CP[1] != world:
                 continue
             for shape in space.shape_configs(world):
-                prefix = plan_key_prefix(fob, cfg.CP, shape, cfg)
-                for suf in ABLATION_SUFFIXES:
-                    intra = prof_db.get_profile(prefix + suf, 1)
-                    if intra is None and cfg.CP[1] == 1 and cfg.bsa_repr.check_full():
-                        # FULL attention is measured per (Y, X) grid: an ablation level stands for
-                        # the best grid it may use (reference: search_algo/bsa_utils.py:53-70)
-                        from ..utils.bsa_helpers import get_b2f_suf_map
-                        cands = [prof_db.get_profile(prefix + s, 1) for s in get_b2f_suf_map(cfg.CP[0])[suf]]
-                        cands = [c for c in cands if c is not None]
-                        intra = min(cands, key=lambda c: float(c["time"])) if cands else None
-                    if intra is not None and cfg.CP[1] == 1:
-                        prof_db.put_profile(prefix + suf, intra["hfu"], float(intra["time"]),
-                                            float(intra["sim_time"]), 0)
+                _profile_inter_one(fob, cfg, shape, prof_db)
+
+
+def profile_all_inter_BSA(args, exp_config, da_config, ncclcomm_global=None, gloo_global_group=None,
+                          tensor_buf=None, prof_db=None) -> list:
+    """One configuration of step 4 under the reference's argument list (search_algo/task2_bsa.py:
+    38-147); rank 0 writes, the others return at once. Communicator, control group and buffer are
+    accepted and unused."""
+    assert prof_db is not None, "profile_all_inter_BSA needs the plan database"
+    if dist.is_initialized() and dist.get_rank() != 0:
+        return []
+    return _profile_inter_one(exp_config.fob, da_config.bsa_config, da_config.shape_config, prof_db)
+
+
+profile_all_inter_full = profile_all_inter_BSA      # FULL attention takes the same route (best grid per ablation)
 
 
 def step5_profile_baselines(space, prof_db, device, world: int, iters: int = 2) -> list:
