@@ -33,7 +33,6 @@ from the usual ``[q | k | v]`` layout (:func:`unpermute_qkv_weight` is its inver
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist
