@@ -5,7 +5,9 @@ CLUSTER_NAME ?= local
 PLATFORM ?= B200
 export CLUSTER_NAME PLATFORM
 
-.PHONY: build test test-gpu bench cluster_profile bsa_train dense_train bsa_infer report plan fusion_table full_plans predict
+.PHONY: build test test-gpu bench cluster_profile bsa_train dense_train bsa_infer report plan fusion_table full_plans predict \
+        figure6 figure7 figure8 figure9 figure10 figure11
+DB ?= database/$(CLUSTER_NAME)/$(PLATFORM)
 CONFIG ?= configs/stride.yaml
 
 build:            ## compile the sm_100a kernel library in-tree (nvcc; works without a GPU)
@@ -29,7 +31,23 @@ bsa_train dense_train bsa_infer:   ## planning + profiling campaign of one exper
 	$(PY) -m ultraattn_b200.drivers.launch --gpus $(GPUS) -- search_algo/task2_bsa.py --exp-class $@
 
 report:           ## figure tables from the profile database
-	$(PY) -m ultraattn_b200.drivers.report --db database/$(CLUSTER_NAME)/$(PLATFORM)
+	$(PY) -m ultraattn_b200.drivers.report --db $(DB)
+
+# The reference's scripts/Makefile names its campaigns after the figures they feed; same names here.
+figure7: bsa_train      ## block-sparse training patterns: campaign, then speed-ups over the baselines
+	$(PY) -m ultraattn_b200.drivers.report --db $(DB)
+figure8: dense_train    ## dense (full, causal) training
+	$(PY) -m ultraattn_b200.drivers.report --db $(DB)
+figure9: bsa_infer      ## star / streaming prefill
+	$(PY) -m ultraattn_b200.drivers.report --db $(DB)
+figure6:                ## end-to-end step times: 32 layers x (fwd + bwd) + a constant, from the database
+	$(PY) -m ultraattn_b200.drivers.report --db $(DB) --e2e-layers 32 --e2e-const $(or $(E2E_CONST),0)
+figure10:               ## strong and weak scalability across the rank counts in the database
+	$(PY) -m ultraattn_b200.drivers.report --db $(DB) --scalability strong
+	$(PY) -m ultraattn_b200.drivers.report --db $(DB) --scalability weak
+figure11:               ## predicted against measured times (outlier share, R^2)
+	$(PY) -m ultraattn_b200.drivers.report --db $(DB) --level intra --sim-accuracy
+	$(PY) -m ultraattn_b200.drivers.report --db $(DB) --level inter --sim-accuracy
 
 plan:             ## one configuration from a YAML file: plan, predicted time (add a launcher to run it)
 	$(PY) -m ultraattn_b200.drivers.main --config $(CONFIG) --plan-only

@@ -329,3 +329,46 @@ def test_ring_time_model_and_predictions():
         rec = predict(name, 8, time_limit=3.0)
         got = rec["ring_fwd_ms"] + rec.get("ring_bwd_ms", 0.0)
         assert 0.7 * ms < got <= ms, (name, got, ms)                               # below, never above, the measurement
+
+
+def test_scalability_tables_from_profile_rows():
+    """Strong scaling normalises GPU time (seconds x ranks) over one shape; weak scaling keeps
+    S^2 / ranks fixed and normalises time; a configuration seen on one rank count is left out."""
+    from ultraattn_b200.drivers.report import build_rows, scalability_rows
+
+    def key(fob, cp, S, suffix, repr_="[[2]]"):
+        return (f"fob={fob}_CP={cp}_shape_config={{S=({S}, {S})_Nh=(32, 32)_bs=1_D=128}}"
+                f"_bsa_config={{CP={cp}_repr={repr_}}}{suffix}")
+    ultra = "_ablation=(w_kernel_tile,ILP)"
+    prof = {}
+    # strong: S = 64k on 8 and 16 ranks; UltraAttn scales perfectly (4 s -> 2 s), the ring does not (8 s -> 6 s)
+    for cp, tu, tr in (((8, 1), 4.0, 8.0), ((8, 2), 2.0, 6.0)):
+        prof[key(0, cp, 65536, ultra)] = {"time": tu, "sim_time": tu}
+        prof[key(0, cp, 65536, "_ring")] = {"time": tr, "sim_time": tr}
+    # weak partner of (64k, 8 ranks): (128k, 32 ranks)
+    prof[key(0, (8, 4), 131072, ultra)] = {"time": 5.0, "sim_time": 5.0}
+    prof[key(0, (8, 4), 131072, "_ring")] = {"time": 16.0, "sim_time": 16.0}
+    # a lone configuration
+    prof[key(1, (8, 1), 16384, ultra, "[[1]]")] = {"time": 1.0, "sim_time": 1.0}
+    rows = build_rows(prof)
+    strong = scalability_rows(rows, "strong")
+    assert [(r["ranks"], r["S"]) for r in strong] == [(8, 65536), (16, 65536)]
+    assert strong[0]["ultraattn"] == 1.0 and strong[1]["ultraattn"] == 1.0
+    assert abs(strong[0]["ring"] - 0.5) < 1e-12 and abs(strong[1]["ring"] - 32.0 / 96.0) < 1e-12
+    assert strong[0]["zigzag"] is None and strong[0]["pattern"] == "[[2]]"
+    weak = scalability_rows(rows, "weak")
+    assert [(r["ranks"], r["S"]) for r in weak] == [(8, 65536), (32, 131072)]
+    assert weak[0]["ultraattn"] == 1.0 and abs(weak[1]["ultraattn"] - 0.8) < 1e-12 and abs(weak[1]["ring"] - 0.25) < 1e-12
+
+
+def test_scalability_table_from_the_kept_measurements(capsys):
+    """The 2- and 8-GPU measurements kept with the documentation give a strong-scaling table through the CLI."""
+    import os
+    from ultraattn_b200.drivers import report
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    assert report.main(["--bench-jsonl", os.path.join(root, "docs", "measurements", "bench_configs_b200.jsonl"),
+                        "--scalability", "strong"]) == 0
+    lines = [ln for ln in capsys.readouterr().out.splitlines() if ln.startswith("|  | strided512k")]
+    assert len(lines) == 2 and lines[0].split("|")[4].strip() == "2" and lines[0].split("|")[-2].strip() == "1.000"
+    eff8 = float(lines[1].split("|")[-2])
+    assert 0.9 < eff8 <= 1.0

@@ -129,6 +129,49 @@ def e2e_rows(rows: list, n_layers: int, time_wo_attn: float) -> list:
     return out
 
 
+SYSTEMS = ("ring", "zigzag", "stripe", "ultraattn")
+
+
+def scalability_rows(rows: list, mode: str = "strong") -> list:
+    """Relative performance across rank counts, the way the reference's scalability figures
+    normalise it. ``strong`` (plot/strong_scalability_training_pick.py:105-142): one pattern, pass
+    and shape on several rank counts; every system's GPU time (seconds x ranks) is divided into the
+    smallest GPU time of the group, so 1.0 marks the most efficient point and a flat line is perfect
+    scaling. ``weak`` (plot/weak_scalability_training.py:136-180): the work per GPU is fixed, which
+    for attention means S^2 / ranks (S doubles while the ranks quadruple); the smallest time of the
+    group is divided by each time. Rows are the figure rows of :func:`build_rows` or
+    :func:`rows_from_bench_lines`; groups seen on a single rank count are left out."""
+    assert mode in ("strong", "weak"), mode
+    groups: dict = {}
+    for r in rows:
+        cp = re.match(r"\((\d+), (\d+)\)", r.get("CP") or "")
+        sm = re.search(r"S=\((\d+), ?(\d+)\)", r.get("shape") or "")
+        if not cp or not sm:
+            continue
+        ranks, S = int(cp.group(1)) * int(cp.group(2)), int(sm.group(1))
+        pm = re.search(r"_repr=(.*?)\}?$", r["key"])
+        pattern = r.get("config") or (pm.group(1) if pm else r["key"])
+        rest = re.sub(r"S=\(\d+, ?\d+\)_?", "", r["shape"])
+        ident = (r.get("fob", ""), pattern, rest) + ((S,) if mode == "strong" else (S * S // ranks,))
+        groups.setdefault(ident, []).append((ranks, S, r))
+    out = []
+    for ident, members in sorted(groups.items(), key=lambda kv: tuple(str(x) for x in kv[0])):
+        if len({m[0] for m in members}) < 2:
+            continue
+        weight = (lambda n: n) if mode == "strong" else (lambda n: 1)
+        costs = [r[c] * weight(n) for n, _, r in members for c in SYSTEMS if r.get(c)]
+        if not costs:
+            continue
+        best = min(costs)
+        for n, S, r in sorted(members, key=lambda m: m[0]):
+            row = {"fob": ident[0], "pattern": ident[1] if len(str(ident[1])) <= 24 else str(ident[1])[:21] + "...",
+                   "shape": r["shape"], "ranks": n, "S": S}
+            for c in SYSTEMS:
+                row[c] = best / (r[c] * weight(n)) if r.get(c) else None
+            out.append(row)
+    return out
+
+
 def rows_from_bench_lines(lines) -> list:
     """Figure rows from ``bench_configs`` JSON lines (dicts or strings); times become seconds."""
     groups: dict = {}
@@ -231,6 +274,9 @@ def main(argv=None) -> int:
     ap.add_argument("--svg", default=None, help="also draw the speed-ups over the ring baseline as a bar chart")
     ap.add_argument("--sim-accuracy", action="store_true",
                     help="print predicted-vs-measured statistics instead of the table")
+    ap.add_argument("--scalability", default=None, choices=["strong", "weak"],
+                    help="print relative performance across rank counts (strong: fixed shape, GPU time; weak: "
+                         "fixed S^2 / ranks, time) instead of the table")
     ap.add_argument("--e2e-layers", type=int, default=0,
                     help="print end-to-end step times: layers x (fwd + bwd) + --e2e-const")
     ap.add_argument("--e2e-const", type=float, default=0.0, help="seconds per step outside attention")
@@ -251,6 +297,13 @@ def main(argv=None) -> int:
             return 0
         rows = build_rows(profile)
         title = f"{a.level}-level plans, speed-up over ring"
+    if a.scalability:
+        cols = ["fob", "pattern", "shape", "ranks"] + list(SYSTEMS)
+        print("| " + " | ".join(cols) + " |")
+        print("|" + "---|" * len(cols))
+        for r in scalability_rows(rows, a.scalability):
+            print("| " + " | ".join(_fmt(r.get(c)) for c in cols) + " |")
+        return 0
     if a.e2e_layers:
         cols = ["CP", "shape", "ring", "zigzag", "stripe", "ultraattn", "speedup_vs_best_baseline"]
         print("| " + " | ".join(cols) + " |")
