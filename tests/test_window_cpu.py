@@ -1,0 +1,127 @@
+"""Sliding-window attention assembled from the one-sided masks of the block-sparse kernels
+(usual order for the upper bound, reversed order for the lower bound) against dense masked
+attention: outputs, log-sum-exps and gradients, on the fp32 restatement of the kernels."""
+import math
+
+import pytest
+import torch
+
+from ultraattn_b200.ops import window as W
+
+
+def _dense(q, k, v, left, right, scale):
+    B, S, H, D = q.shape
+    g = H // k.shape[2]
+    kk, vv = k.repeat_interleave(g, 2), v.repeat_interleave(g, 2)
+    s = torch.einsum("bqhd,bkhd->bhqk", q, kk) * scale
+    r = torch.arange(S)[:, None]
+    c = torch.arange(S)[None, :]
+    mask = (c >= r - left) & (c <= r + right)
+    s = s.masked_fill(~mask, float("-inf"))
+    return torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), vv), torch.logsumexp(s, -1)
+
+
+@pytest.mark.parametrize("S,window,causal", [
+    (1024, (300, 0), False),         # causal band wider than a row block
+    (1024, (255, 0), True),          # exactly one row block
+    (768, (100, 37), False),         # two-sided, narrower than a row block
+    (640, (-1, 64), False),          # unbounded to the left
+    (640, (128, -1), False),         # unbounded to the right
+    (520, (300, 300), False),        # token count that is no multiple of the tiles
+    (512, (700, 0), True),           # window longer than the sequence: plain causal
+    (96, (0, 0), False),             # each token sees itself only
+])
+def test_window_attention_matches_dense_masked_attention(S, window, causal):
+    torch.manual_seed(S + window[0])
+    B, H, Hk, D = 2, 4, 2, 32
+    q = torch.randn(B, S, H, D, dtype=torch.float64).float().requires_grad_()
+    k = torch.randn(B, S, Hk, D).requires_grad_()
+    v = torch.randn(B, S, Hk, D).requires_grad_()
+    left = S if window[0] < 0 else window[0]
+    right = 0 if causal else (S if window[1] < 0 else window[1])
+    scale = 1.0 / math.sqrt(D)
+    o_ref, lse_ref = _dense(q, k, v, left, right, scale)
+    g = torch.randn_like(o_ref)
+    dq_ref, dk_ref, dv_ref = torch.autograd.grad(o_ref, (q, k, v), g)
+
+    o, lse = W.window_forward(q.detach(), k.detach(), v.detach(), window, causal)
+    assert (o - o_ref).abs().max() < 2e-5 and (lse - lse_ref).abs().max() < 2e-5
+    out = W.sliding_window_attention(q, k, v, window, causal)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), g)
+    for a, b in ((dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+        assert (a - b).abs().max() < 5e-5 * max(1.0, b.abs().max().item())
+
+
+def test_window_plan_covers_every_visible_pair_exactly_once():
+    """Count, per (query, key) pair, how many segments of the forward rows and of the backward
+    columns cover it: exactly the band, once each."""
+    S, left, right = 700, 290, 45
+    rows, cols = W.window_rows_cols(S, left, right)
+    r = torch.arange(S)[:, None]
+    c = torch.arange(S)[None, :]
+    band = ((c >= r - left) & (c <= r + right)).int()
+
+    def to_std(idx, slot):
+        return idx if slot == 0 else S - 1 - idx
+
+    fwd = torch.zeros(S, S, dtype=torch.int32)
+    for row in rows:
+        for seg in row.segs:
+            rr = torch.arange(row.q_len)[:, None]
+            cc = torch.arange(seg.length)[None, :]
+            vis = (cc <= rr + seg.diag) if seg.causal else torch.ones(row.q_len, seg.length, dtype=torch.bool)
+            qi = to_std(row.q_start + rr, row.q_src).expand_as(vis)[vis]
+            ki = to_std(seg.start + cc, seg.src).expand_as(vis)[vis]
+            fwd.index_put_((qi, ki), torch.ones_like(qi, dtype=torch.int32), accumulate=True)
+    assert torch.equal(fwd, band)
+    bwd = torch.zeros(S, S, dtype=torch.int32)
+    for col in cols:
+        for seg in col.segs:
+            rr = torch.arange(seg.length)[:, None]
+            cc = torch.arange(col.kv_len)[None, :]
+            vis = (cc <= rr + seg.diag) if seg.causal else torch.ones(seg.length, col.kv_len, dtype=torch.bool)
+            qi = to_std(seg.start + rr, seg.src).expand_as(vis)[vis]
+            ki = to_std(col.kv_start + cc, col.kv_src).expand_as(vis)[vis]
+            bwd.index_put_((qi, ki), torch.ones_like(qi, dtype=torch.int32), accumulate=True)
+    assert torch.equal(bwd, band)
+    # each gradient row of each slot is produced by at most one column (bf16 outputs are overwritten)
+    for slot in (0, 1):
+        covered = torch.zeros(S, dtype=torch.int32)
+        for col in cols:
+            if col.g_slot == slot:
+                covered[col.g_start:col.g_start + col.kv_len] += 1
+        assert covered.max() <= 1
+
+
+def test_window_size_through_the_flash_attention_calling_convention():
+    """``_flash_attn_forward`` / ``_flash_attn_backward`` with ``window_size``: the caller's output
+    buffer is filled, the 8-tuple keeps its layout, gradients land in the buffers passed in, with O
+    present or with a precomputed D."""
+    from ultraattn_b200.ops.flash_compat import _flash_attn_backward, _flash_attn_forward
+    torch.manual_seed(5)
+    B, S, H, Hk, D = 1, 600, 4, 4, 16
+    q = torch.randn(B, S, H, D).requires_grad_()
+    k = torch.randn(B, S, Hk, D).requires_grad_()
+    v = torch.randn(B, S, Hk, D).requires_grad_()
+    d_o = torch.randn(B, S, H, D)
+    o_ref, lse_ref = _dense(q, k, v, 260, 0, 1.0 / math.sqrt(D))
+    dq_ref, dk_ref, dv_ref = torch.autograd.grad(o_ref, (q, k, v), d_o)
+    buf = torch.full((B, S, H, D), 3.0)
+    with torch.no_grad():
+        ret = _flash_attn_forward(q, k, v, 0.0, None, True, window_size=(260, -1), alibi_slopes=None,
+                                  return_softmax=False, out=buf)
+        assert len(ret) == 8 and ret[0] is buf and (buf - o_ref).abs().max() < 2e-5
+        assert (ret[5] - lse_ref).abs().max() < 2e-5
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        out = _flash_attn_backward(d_o, q, k, v, buf, ret[5], dq, dk, dv, 0.0, None, True, (260, -1), None, False)
+        assert out[0] is dq and (dq - dq_ref).abs().max() < 5e-5 and (dk - dk_ref).abs().max() < 5e-5
+        assert (dv - dv_ref).abs().max() < 5e-5
+        dvec = (o_ref * d_o).sum(-1).transpose(1, 2).contiguous()
+        dq2 = torch.empty_like(q)
+        _flash_attn_backward(d_o, q, k, v, q, ret[5], dq2, dk, dv, 0.0, None, True, (260, -1), None, False,
+                             softmax_d=dvec)
+        assert (dq2 - dq_ref).abs().max() < 5e-5
+    with pytest.raises(AssertionError, match="varlen"):
+        from ultraattn_b200.ops.flash_compat import _flash_attn_varlen_forward
+        _flash_attn_varlen_forward(q[0], k[0], v[0], torch.tensor([0, S]), torch.tensor([0, S]), S, S, 0.0, None, True,
+                                   window_size=(16, 0))

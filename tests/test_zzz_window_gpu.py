@@ -1,0 +1,61 @@
+"""Sliding-window attention on the sm_100a kernels (two-part plan: usual and reversed token order)
+against dense masked attention in fp32."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA GPU")
+    from ultraattn_b200 import _lib
+    _lib.load()
+    return torch.device("cuda")
+
+
+def _dense(q, k, v, d_o, left, right):
+    q, k, v = (t.detach().float().requires_grad_() for t in (q, k, v))
+    S, g = q.shape[1], q.shape[2] // k.shape[2]
+    s = torch.einsum("bqhd,bkhd->bhqk", q, k.repeat_interleave(g, 2)) / math.sqrt(q.shape[-1])
+    r = torch.arange(S, device=q.device)[:, None]
+    c = torch.arange(S, device=q.device)[None, :]
+    s = s.masked_fill(~((c >= r - left) & (c <= r + right)), float("-inf"))
+    o = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), v.repeat_interleave(g, 2))
+    o.backward(d_o.float())
+    return o.detach(), torch.logsumexp(s, -1).detach(), q.grad, k.grad, v.grad
+
+
+def _close(got, ref, tol):
+    err = (got.float() - ref.float()).abs().max().item()
+    scale = ref.float().abs().max().item() + 1e-6
+    assert err <= tol * scale, f"max err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("S,window,causal", [(2048, (600, -1), True), (1000, (300, 200), False)])
+def test_sliding_window_attention_on_the_kernels(dev, S, window, causal):
+    from ultraattn_b200.ops import attention as A
+    from ultraattn_b200.ops.window import sliding_window_attention, window_forward
+    torch.manual_seed(S)
+    B, H, Hk, D = 1, 4, 2, 128
+    q = torch.randn(B, S, H, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(B, S, Hk, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(B, S, Hk, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    d_o = torch.randn(B, S, H, D, device=dev, dtype=torch.bfloat16)
+    left = window[0]
+    right = 0 if causal else window[1]
+    o_r, lse_r, dq_r, dk_r, dv_r = _dense(q, k, v, d_o, left, right)
+    with torch.no_grad():
+        _, lse = window_forward(q, k, v, window, causal)
+    A.check_status(dev)
+    _close(lse, lse_r, 1e-2)
+    o = sliding_window_attention(q, k, v, window, causal)
+    o.backward(d_o)
+    A.check_status(dev)
+    _close(o, o_r, 1.5e-2)
+    _close(q.grad, dq_r, 2e-2)
+    _close(k.grad, dk_r, 2e-2)
+    _close(v.grad, dv_r, 2e-2)

@@ -14,10 +14,13 @@ The fork's two additions are kept: ``out=`` lets the caller name the output buff
 ``softmax_d=`` passes a precomputed ``D = rowsum(dO * O)`` so that O itself need not be present
 (``out`` may then be any tensor of the right shape, as in the reference, which passes Q).
 Code written against those calls runs on the sm_100a kernels (CUDA tensors, bf16, head dim 128) or
-on the fp32 restatement (CPU tensors) by importing them from here. Dropout, ALiBi and sliding
-windows are not supported (the reference never uses them: ``dropout_p = 0``, ``window_size =
-(-1, -1)``, ``alibi_slopes = None`` at every call site). With ``Sq != Skv`` a causal mask is
-aligned to the bottom-right corner, as in flash-attention 2.1 and later.
+on the fp32 restatement (CPU tensors) by importing them from here. Sliding windows
+(``window_size = (left, right)``) run on the same kernels for ``Sq == Skv`` (``ops/window.py``: the
+band is split into a part in the usual token order and a part in reversed order, each of which
+needs a one-sided mask only). Dropout and ALiBi are not supported (the reference never uses them:
+``dropout_p = 0``, ``alibi_slopes = None`` at every call site, and ``window_size = (-1, -1)``).
+With ``Sq != Skv`` a causal mask is aligned to the bottom-right corner, as in flash-attention 2.1
+and later; the varlen calls take no windows.
 """
 from __future__ import annotations
 
@@ -28,12 +31,17 @@ import torch
 
 from . import attention as A
 from . import elementwise as E
+from . import window as W
 
 
-def _check(dropout_p, window_size, alibi_slopes):
+def _check(dropout_p, window_size, alibi_slopes, windows_ok: bool = False):
     assert dropout_p == 0.0, "dropout is not supported"
     assert alibi_slopes is None, "ALiBi is not supported"
-    assert tuple(window_size) == (-1, -1), "sliding windows are not supported"
+    assert windows_ok or tuple(window_size) == (-1, -1), "sliding windows are not supported by the varlen calls"
+
+
+def _windowed(window_size) -> bool:
+    return tuple(int(x) for x in window_size) != (-1, -1)
 
 
 def _scale(q, softmax_scale):
@@ -74,8 +82,11 @@ def _flash_attn_forward(q, k, v, dropout_p, softmax_scale, causal, window_size=(
                         return_softmax=False, out: Optional[torch.Tensor] = None):
     """``q`` ``[B, Sq, H, D]``, ``k`` / ``v`` ``[B, Skv, Hkv, D]``. Returns the fork's 8-tuple
     ``(out, q, k, v, out_padded, softmax_lse [B, H, Sq] fp32, S_dmask (None), rng_state (None))``."""
-    _check(dropout_p, window_size, alibi_slopes)
+    _check(dropout_p, window_size, alibi_slopes, windows_ok=True)
     sq, skv = q.shape[1], k.shape[1]
+    if _windowed(window_size):
+        o, lse = W.window_forward(q, k, v, window_size, bool(causal), _scale(q, softmax_scale), out)
+        return o, q, k, v, o, lse, None, None
     rows = [A.Row(0, 0, sq, (A.Seg(0, 0, skv, bool(causal), skv - sq),), 0, 0, False)]
     o, lse = _forward(q, k, v, rows, out, _scale(q, softmax_scale))
     return o, q, k, v, o, lse, None, None
@@ -86,8 +97,18 @@ def _flash_attn_backward(dout, q, k, v, out, softmax_lse, dq, dk, dv, dropout_p,
                          softmax_d: Optional[torch.Tensor] = None):
     """Writes ``dq``, ``dk``, ``dv`` in place; returns ``(dq, dk, dv, softmax_d)``. With
     ``softmax_d`` given, ``out`` is not read."""
-    _check(dropout_p, window_size, alibi_slopes)
+    _check(dropout_p, window_size, alibi_slopes, windows_ok=True)
     sq, skv = q.shape[1], k.shape[1]
+    if _windowed(window_size):
+        if softmax_d is None:
+            softmax_d = torch.empty(q.shape[0], q.shape[2], sq, dtype=torch.float32, device=q.device)
+            for b in range(q.shape[0]):
+                E.rowdot(out[b], dout[b], softmax_d[b])
+        g = W.window_backward(dout, q, k, v, out, softmax_lse, window_size, bool(causal), _scale(q, softmax_scale),
+                              softmax_d)
+        for dst, src in zip((dq, dk, dv), g):
+            dst.copy_(src)
+        return dq, dk, dv, softmax_d
     cols = [A.Col(0, 0, skv, (A.Seg(0, 0, sq, bool(causal), skv - sq),), 0, 0)]
     d = _backward(dout, q, k, v, out, softmax_lse, dq, dk, dv, cols, _scale(q, softmax_scale), softmax_d)
     return dq, dk, dv, d

@@ -1,0 +1,163 @@
+"""Sliding-window (local) attention on the block-sparse kernels, without a kernel of its own.
+
+Query ``r`` sees the keys ``r - left <= c <= r + right`` (flash-attention's ``window_size =
+(left, right)``, -1 = unbounded; ``causal`` sets ``right = 0``). The kernels mask one-sidedly: a
+segment is either fully visible or bounded from above by ``c <= r + diag``. A band needs both
+bounds, but never both inside one tile if the work is split in two:
+
+* part A, in the usual token order: row block ``[r0, r1)`` against the keys from ``r0`` on. Only
+  the upper bound can bind there (``c >= r0 >= r - left`` as long as the block is at most
+  ``left + 1`` rows long), which is the kernels' causal mask with ``diag = right``;
+* part B, in reversed token order (``r' = S - 1 - r``, ``c' = S - 1 - c``): the same row block
+  against the keys before ``r0``. Only the lower bound ``c >= r - left`` can bind there, and
+  reversed it reads ``c' <= r' + left``: again the kernels' causal mask.
+
+Both parts go into one forward launch (two query sources, two key/value sources, two outputs) and
+one backward launch; the partial results are merged by their log-sum-exps like the steps of a ring.
+The reversed copies cost three passes over Q, K, V (and dO) - small beside the attention itself.
+
+The reference's flash-attention fork accepts ``window_size`` in every call
+(ring_flash_attn/ring_flash_attn.py:33-43) and always passes ``(-1, -1)``.
+"""
+from __future__ import annotations
+
+import functools
+import math
+from typing import Optional
+
+import torch
+
+from . import attention as A
+from . import elementwise as E
+
+ROW_BLOCK = 256         # rows of the kernels' forward tile
+
+
+def _bounds(S: int, window_size, causal: bool) -> tuple[int, int]:
+    left, right = (int(x) for x in window_size)
+    left = S if left < 0 else min(left, S)
+    right = S if right < 0 else min(right, S)
+    if causal:
+        right = 0
+    return left, right
+
+
+def _partition(S: int, left: int) -> list:
+    """Row blocks [r0, r1): at most ``left + 1`` rows each, so that inside part A the lower bound
+    and inside part B the upper bound never bind."""
+    step = max(1, min(ROW_BLOCK, left + 1))
+    return [(a, min(S, a + step)) for a in range(0, S, step)]
+
+
+def window_rows_cols(S: int, left: int, right: int) -> tuple[list, list]:
+    """(forward rows, backward columns) of the two-part plan. Source / output slot 0 is the usual
+    token order, slot 1 the reversed one."""
+    blocks = _partition(S, left)
+    rows, cols = [], []
+    for r0, r1 in blocks:
+        n = r1 - r0
+        # part A
+        a_len = min(S, r1 + right) - r0
+        rows.append(A.Row(0, r0, n, (A.Seg(0, r0, a_len, right < S, right),), 0, r0, False))
+        q0 = max(0, r0 - right)                      # key block [r0, r1): rows from q0 to r1 reach it
+        cols.append(A.Col(0, r0, n, (A.Seg(0, q0, r1 - q0, right < S, q0 + right - r0),), 0, r0))
+        # part B, reversed order: row block [S - r1, S - r0), its keys start right behind it
+        b_len = min(left, r0)
+        if b_len > 0:
+            rows.append(A.Row(1, S - r1, n, (A.Seg(1, S - r0, b_len, left < S, left - n),), 1, S - r1, False))
+        c0 = S - r1                                  # the same block as a key block of the reversed order
+        q0 = max(0, c0 - left)
+        if c0 - q0 > 0:
+            cols.append(A.Col(1, c0, n, (A.Seg(1, q0, c0 - q0, left < S, q0 + left - c0),), 1, c0))
+    return rows, cols
+
+
+@functools.lru_cache(maxsize=32)
+def _plans(S: int, left: int, right: int, device_str: str):
+    rows, cols = window_rows_cols(S, left, right)
+    dev = torch.device(device_str)
+    return A.FwdPlan(rows, dev), A.BwdPlan(cols, dev)
+
+
+def _flip(t: torch.Tensor, dim: int = 1) -> torch.Tensor:
+    return t.flip(dim).contiguous()
+
+
+def window_forward(q, k, v, window_size, causal: bool = False, softmax_scale: Optional[float] = None,
+                   out: Optional[torch.Tensor] = None):
+    """``q`` ``[B, S, H, D]``, ``k`` / ``v`` ``[B, S, Hkv, D]`` -> ``(o [B, S, H, D], lse [B, H, S] fp32)``."""
+    B, S, H, D = q.shape
+    assert k.shape[1] == S, "sliding windows need as many keys as queries"
+    left, right = _bounds(S, window_size, causal)
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
+    fplan, _ = _plans(S, left, right, str(q.device))
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    qr, kr, vr = _flip(q), _flip(k), _flip(v)
+    o_a, o_b = torch.zeros_like(q), torch.zeros_like(q)
+    lse_a = torch.full((B, H, S), float("-inf"), dtype=torch.float32, device=q.device)
+    lse_b = torch.full_like(lse_a, float("-inf"))
+    A.attn_fwd([q, qr], [k, kr], [v, vr], [(o_a, lse_a), (o_b, lse_b)], fplan, scale)
+    o = out if out is not None else torch.empty_like(q)
+    lse = torch.empty_like(lse_a)
+    o_b, lse_b = _flip(o_b), _flip(lse_b, 2)
+    for b in range(B):
+        E.lse_merge([(o_a[b], lse_a[b]), (o_b[b], lse_b[b])], (o[b], lse[b]))
+    return o, lse
+
+
+def window_backward(d_o, q, k, v, o, lse, window_size, causal: bool = False,
+                    softmax_scale: Optional[float] = None, softmax_d: Optional[torch.Tensor] = None):
+    """Gradients ``(dq, dk, dv)`` in the dtypes of ``q``, ``k``, ``v``. ``lse`` is the merged
+    log-sum-exp the forward returned; with ``softmax_d`` (= rowsum(dO * O), ``[B, H, S]``) given,
+    ``o`` is not read."""
+    B, S, H, D = q.shape
+    left, right = _bounds(S, window_size, causal)
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
+    _, bplan = _plans(S, left, right, str(q.device))
+    q, k, v, d_o = q.contiguous(), k.contiguous(), v.contiguous(), d_o.contiguous()
+    if softmax_d is None:
+        softmax_d = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
+        for b in range(B):
+            E.rowdot(o[b], d_o[b], softmax_d[b])
+    lse = lse.float().contiguous()
+    softmax_d = softmax_d.float().contiguous()
+    f32 = lambda t: torch.zeros(t.shape, dtype=torch.float32, device=t.device)
+    dq_a, dq_b = f32(q), f32(q)
+    kv_a, kv_b = A.BwdKvOut(f32(k), f32(v)), A.BwdKvOut(f32(k), f32(v))
+    sides = [A.BwdQSide(q, d_o, lse, softmax_d, dq_a),
+             A.BwdQSide(_flip(q), _flip(d_o), _flip(lse, 2), _flip(softmax_d, 2), dq_b)]
+    A.attn_bwd(sides, [k, _flip(k)], [v, _flip(v)], [kv_a, kv_b], bplan, scale)
+    dq = (dq_a + dq_b.flip(1)).to(q.dtype)
+    dk = (kv_a.dk + kv_b.dk.flip(1)).to(k.dtype)
+    dv = (kv_a.dv + kv_b.dv.flip(1)).to(v.dtype)
+    return dq, dk, dv
+
+
+class _WindowFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, window_size, causal, softmax_scale):
+        o, lse = window_forward(q, k, v, window_size, causal, softmax_scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.args = (tuple(window_size), bool(causal), softmax_scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = window_backward(d_o, q, k, v, o, lse, *ctx.args)
+        return dq, dk, dv, None, None, None
+
+
+def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window_size=(-1, -1),
+                             causal: bool = False, softmax_scale: Optional[float] = None) -> torch.Tensor:
+    """``softmax(mask(Q K^T) * scale) V`` with the band mask ``r - left <= c <= r + right``; autograd.
+    ``[batch, tokens, heads, head_dim]`` tensors (bf16 and head dim 128 on CUDA; any float type and
+    head dim on CPU; a smaller head dim on CUDA runs zero-padded to 128 with the scale of the true
+    head dim); grouped-query K / V allowed."""
+    D = q.shape[-1]
+    if q.is_cuda and D < A.KERNEL_HEAD_DIM:
+        pad = A.KERNEL_HEAD_DIM - D
+        scale = softmax_scale if softmax_scale is not None else D ** -0.5
+        qp, kp, vp = (torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v))
+        return _WindowFunction.apply(qp, kp, vp, tuple(window_size), causal, scale)[..., :D]
+    return _WindowFunction.apply(q, k, v, tuple(window_size), causal, softmax_scale)
