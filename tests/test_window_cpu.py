@@ -121,7 +121,44 @@ def test_window_size_through_the_flash_attention_calling_convention():
         _flash_attn_backward(d_o, q, k, v, q, ret[5], dq2, dk, dv, 0.0, None, True, (260, -1), None, False,
                              softmax_d=dvec)
         assert (dq2 - dq_ref).abs().max() < 5e-5
-    with pytest.raises(AssertionError, match="varlen"):
-        from ultraattn_b200.ops.flash_compat import _flash_attn_varlen_forward
-        _flash_attn_varlen_forward(q[0], k[0], v[0], torch.tensor([0, S]), torch.tensor([0, S]), S, S, 0.0, None, True,
-                                   window_size=(16, 0))
+
+
+def test_windows_in_a_packed_batch():
+    """Three sequences packed along the token axis (one empty-ish short one): each attends only
+    itself and the window counts positions inside the sequence; operator with autograd and the
+    varlen calling convention against per-sequence dense masked attention."""
+    from ultraattn_b200.ops.flash_compat import _flash_attn_varlen_backward, _flash_attn_varlen_forward
+    torch.manual_seed(11)
+    lens = [300, 5, 415]
+    cu = torch.tensor([0, 300, 305, 720], dtype=torch.int32)
+    T, H, Hk, D = 720, 4, 2, 16
+    left, right = 130, 20
+    q = torch.randn(1, T, H, D).requires_grad_()
+    k = torch.randn(1, T, Hk, D).requires_grad_()
+    v = torch.randn(1, T, Hk, D).requires_grad_()
+    d_o = torch.randn(1, T, H, D)
+    outs, lses = [], []
+    for a, b in zip(cu[:-1].tolist(), cu[1:].tolist()):
+        o_i, lse_i = _dense(q[:, a:b], k[:, a:b], v[:, a:b], left, right, 1.0 / math.sqrt(D))
+        outs.append(o_i)
+        lses.append(lse_i)
+    o_ref = torch.cat(outs, 1)
+    dq_ref, dk_ref, dv_ref = torch.autograd.grad(o_ref, (q, k, v), d_o)
+
+    o = W.sliding_window_attention(q, k, v, (left, right), cu_seqlens=cu)
+    assert (o - o_ref).abs().max() < 2e-5
+    dq, dk, dv = torch.autograd.grad(o, (q, k, v), d_o)
+    for got, ref in ((dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+        assert (got - ref).abs().max() < 5e-5
+
+    with torch.no_grad():
+        ret = _flash_attn_varlen_forward(q[0], k[0], v[0], cu, cu, max(lens), max(lens), 0.0, None, False,
+                                         window_size=(left, right))
+        assert (ret[0] - o_ref[0]).abs().max() < 2e-5 and ret[5].shape == (3, H, max(lens))
+        for i, n in enumerate(lens):
+            assert (ret[5][i, :, :n] - lses[i][0]).abs().max() < 2e-5
+        gq, gk, gv = torch.empty_like(q[0]), torch.empty_like(k[0]), torch.empty_like(v[0])
+        _flash_attn_varlen_backward(d_o[0], q[0], k[0], v[0], ret[0], ret[5], gq, gk, gv, cu, cu, max(lens), max(lens),
+                                    0.0, None, False, window_size=(left, right))
+        assert (gq - dq_ref[0]).abs().max() < 5e-5 and (gk - dk_ref[0]).abs().max() < 5e-5
+        assert (gv - dv_ref[0]).abs().max() < 5e-5

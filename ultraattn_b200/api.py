@@ -135,11 +135,17 @@ class _VarlenAttention(torch.autograd.Function):
         return dq, dk, dv, None, None, None
 
 
-def varlen_attention(q, k, v, cu_seqlens, causal: bool = True, softmax_scale: Optional[float] = None):
+def varlen_attention(q, k, v, cu_seqlens, causal: bool = True, softmax_scale: Optional[float] = None,
+                     window_size=(-1, -1)):
     """Attention over a packed batch ``[total_tokens, heads, head_dim]`` (or with a leading batch
-    dimension of 1) where ``cu_seqlens`` gives the sequence boundaries."""
+    dimension of 1) where ``cu_seqlens`` gives the sequence boundaries. ``window_size = (left,
+    right)`` restricts every query to a band of its own sequence (``ops/window.py``)."""
     squeeze = q.dim() == 3
     if squeeze:
         q, k, v = q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)
-    o = _VarlenAttention.apply(q, k, v, tuple(int(x) for x in cu_seqlens), causal, softmax_scale)
+    if tuple(int(x) for x in window_size) != (-1, -1):
+        from .ops.window import sliding_window_attention
+        o = sliding_window_attention(q, k, v, window_size, causal, softmax_scale, cu_seqlens=cu_seqlens)
+    else:
+        o = _VarlenAttention.apply(q, k, v, tuple(int(x) for x in cu_seqlens), causal, softmax_scale)
     return o.squeeze(0) if squeeze else o

@@ -20,7 +20,7 @@ band is split into a part in the usual token order and a part in reversed order,
 needs a one-sided mask only). Dropout and ALiBi are not supported (the reference never uses them:
 ``dropout_p = 0``, ``alibi_slopes = None`` at every call site, and ``window_size = (-1, -1)``).
 With ``Sq != Skv`` a causal mask is aligned to the bottom-right corner, as in flash-attention 2.1
-and later; the varlen calls take no windows.
+and later. The varlen calls take windows when every sequence has as many keys as queries.
 """
 from __future__ import annotations
 
@@ -37,7 +37,7 @@ from . import window as W
 def _check(dropout_p, window_size, alibi_slopes, windows_ok: bool = False):
     assert dropout_p == 0.0, "dropout is not supported"
     assert alibi_slopes is None, "ALiBi is not supported"
-    assert windows_ok or tuple(window_size) == (-1, -1), "sliding windows are not supported by the varlen calls"
+    assert windows_ok or tuple(window_size) == (-1, -1), "sliding windows are not supported by this call"
 
 
 def _windowed(window_size) -> bool:
@@ -134,8 +134,15 @@ def _flash_attn_varlen_forward(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q
     """Packed batch: ``q`` ``[Tq, H, D]``, ``k`` / ``v`` ``[Tk, Hkv, D]``; sequence i spans
     ``cu_seqlens[i] : cu_seqlens[i + 1]`` and attends only itself. Returns the 8-tuple with
     ``softmax_lse`` padded ``[n_seq, H, max_seqlen_q]``."""
-    _check(dropout_p, window_size, alibi_slopes)
+    _check(dropout_p, window_size, alibi_slopes, windows_ok=True)
     assert block_table is None, "paged key/value caches are not supported"
+    if _windowed(window_size):
+        assert _bounds(cu_seqlens_q) == _bounds(cu_seqlens_k), "sliding windows need equal query and key lengths"
+        o, lse = W.window_forward(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), window_size, bool(causal),
+                                  _scale(q, softmax_scale), out.unsqueeze(0) if out is not None else None,
+                                  cu_seqlens=cu_seqlens_q)
+        o = o.squeeze(0)
+        return o, q, k, v, o, _pad_lse(lse[0], cu_seqlens_q, max_seqlen_q), None, None
     rows = []
     for (qa, qb), (ka, kb) in zip(_bounds(cu_seqlens_q), _bounds(cu_seqlens_k)):
         if qb > qa and kb > ka:
@@ -152,12 +159,22 @@ def _flash_attn_varlen_backward(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_
                                 softmax_d: Optional[torch.Tensor] = None):
     """``softmax_lse``: padded ``[n_seq, H, max_seqlen_q]`` (as returned by the forward) or packed
     ``[H, Tq]``. Writes ``dq``, ``dk``, ``dv`` (packed) in place."""
-    _check(dropout_p, window_size, alibi_slopes)
+    _check(dropout_p, window_size, alibi_slopes, windows_ok=True)
     bq, bk = _bounds(cu_seqlens_q), _bounds(cu_seqlens_k)
     if softmax_lse.dim() == 3:
         lse = torch.cat([softmax_lse[i, :, :b - a] for i, (a, b) in enumerate(bq)], dim=1)
     else:
         lse = softmax_lse
+    if _windowed(window_size):
+        assert bq == bk, "sliding windows need equal query and key lengths"
+        if softmax_d is None:
+            softmax_d = E.rowdot(out, dout)
+        g = W.window_backward(dout.unsqueeze(0), q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), out.unsqueeze(0),
+                              lse.unsqueeze(0), window_size, bool(causal), _scale(q, softmax_scale),
+                              softmax_d.unsqueeze(0), cu_seqlens=cu_seqlens_q)
+        for dst, src in zip((dq, dk, dv), g):
+            dst.copy_(src[0])
+        return dq, dk, dv, softmax_d
     cols = []
     for (qa, qb), (ka, kb) in zip(bq, bk):
         if qb > qa and kb > ka:

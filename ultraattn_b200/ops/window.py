@@ -49,34 +49,55 @@ def _partition(S: int, left: int) -> list:
     return [(a, min(S, a + step)) for a in range(0, S, step)]
 
 
-def window_rows_cols(S: int, left: int, right: int) -> tuple[list, list]:
-    """(forward rows, backward columns) of the two-part plan. Source / output slot 0 is the usual
-    token order, slot 1 the reversed one."""
+def window_rows_cols(S: int, left: int, right: int, base: int = 0, total: Optional[int] = None) -> tuple[list, list]:
+    """(forward rows, backward columns) of the two-part plan for one sequence of ``S`` tokens that
+    starts at token ``base`` of a buffer of ``total`` tokens (a packed batch; default: the sequence
+    is the buffer). Source / output slot 0 is the usual token order, slot 1 the buffer reversed,
+    where the sequence occupies ``[total - base - S, total - base)``."""
+    total = S if total is None else total
+    rbase = total - base - S
     blocks = _partition(S, left)
     rows, cols = [], []
     for r0, r1 in blocks:
         n = r1 - r0
         # part A
         a_len = min(S, r1 + right) - r0
-        rows.append(A.Row(0, r0, n, (A.Seg(0, r0, a_len, right < S, right),), 0, r0, False))
+        rows.append(A.Row(0, base + r0, n, (A.Seg(0, base + r0, a_len, right < S, right),), 0, base + r0, False))
         q0 = max(0, r0 - right)                      # key block [r0, r1): rows from q0 to r1 reach it
-        cols.append(A.Col(0, r0, n, (A.Seg(0, q0, r1 - q0, right < S, q0 + right - r0),), 0, r0))
+        cols.append(A.Col(0, base + r0, n, (A.Seg(0, base + q0, r1 - q0, right < S, q0 + right - r0),), 0, base + r0))
         # part B, reversed order: row block [S - r1, S - r0), its keys start right behind it
         b_len = min(left, r0)
         if b_len > 0:
-            rows.append(A.Row(1, S - r1, n, (A.Seg(1, S - r0, b_len, left < S, left - n),), 1, S - r1, False))
+            rows.append(A.Row(1, rbase + S - r1, n, (A.Seg(1, rbase + S - r0, b_len, left < S, left - n),), 1,
+                              rbase + S - r1, False))
         c0 = S - r1                                  # the same block as a key block of the reversed order
         q0 = max(0, c0 - left)
         if c0 - q0 > 0:
-            cols.append(A.Col(1, c0, n, (A.Seg(1, q0, c0 - q0, left < S, q0 + left - c0),), 1, c0))
+            cols.append(A.Col(1, rbase + c0, n, (A.Seg(1, rbase + q0, c0 - q0, left < S, q0 + left - c0),), 1,
+                              rbase + c0))
     return rows, cols
 
 
 @functools.lru_cache(maxsize=32)
-def _plans(S: int, left: int, right: int, device_str: str):
-    rows, cols = window_rows_cols(S, left, right)
+def _plans(bounds: tuple, total: int, window_size: tuple, causal: bool, device_str: str):
+    """Plans of a buffer of ``total`` tokens holding the sequences ``bounds`` = ((start, end), ...)."""
+    rows, cols = [], []
+    for a, b in bounds:
+        if b > a:
+            left, right = _bounds(b - a, window_size, causal)
+            r, c = window_rows_cols(b - a, left, right, a, total)
+            rows += r
+            cols += c
     dev = torch.device(device_str)
     return A.FwdPlan(rows, dev), A.BwdPlan(cols, dev)
+
+
+def _seq_bounds(cu_seqlens, S: int) -> tuple:
+    if cu_seqlens is None:
+        return ((0, S),)
+    cu = [int(x) for x in cu_seqlens]
+    assert cu[0] == 0 and cu[-1] <= S, "cu_seqlens must start at 0 and stay inside the buffer"
+    return tuple(zip(cu[:-1], cu[1:]))
 
 
 def _flip(t: torch.Tensor, dim: int = 1) -> torch.Tensor:
@@ -84,13 +105,14 @@ def _flip(t: torch.Tensor, dim: int = 1) -> torch.Tensor:
 
 
 def window_forward(q, k, v, window_size, causal: bool = False, softmax_scale: Optional[float] = None,
-                   out: Optional[torch.Tensor] = None):
-    """``q`` ``[B, S, H, D]``, ``k`` / ``v`` ``[B, S, Hkv, D]`` -> ``(o [B, S, H, D], lse [B, H, S] fp32)``."""
+                   out: Optional[torch.Tensor] = None, cu_seqlens=None):
+    """``q`` ``[B, S, H, D]``, ``k`` / ``v`` ``[B, S, Hkv, D]`` -> ``(o [B, S, H, D], lse [B, H, S] fp32)``.
+    With ``cu_seqlens`` the token axis is a packed batch: sequence i spans ``cu_seqlens[i] :
+    cu_seqlens[i + 1]``, attends only itself, and the window counts positions inside it."""
     B, S, H, D = q.shape
     assert k.shape[1] == S, "sliding windows need as many keys as queries"
-    left, right = _bounds(S, window_size, causal)
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    fplan, _ = _plans(S, left, right, str(q.device))
+    fplan, _ = _plans(_seq_bounds(cu_seqlens, S), S, tuple(int(x) for x in window_size), bool(causal), str(q.device))
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     qr, kr, vr = _flip(q), _flip(k), _flip(v)
     o_a, o_b = torch.zeros_like(q), torch.zeros_like(q)
@@ -106,14 +128,14 @@ def window_forward(q, k, v, window_size, causal: bool = False, softmax_scale: Op
 
 
 def window_backward(d_o, q, k, v, o, lse, window_size, causal: bool = False,
-                    softmax_scale: Optional[float] = None, softmax_d: Optional[torch.Tensor] = None):
+                    softmax_scale: Optional[float] = None, softmax_d: Optional[torch.Tensor] = None,
+                    cu_seqlens=None):
     """Gradients ``(dq, dk, dv)`` in the dtypes of ``q``, ``k``, ``v``. ``lse`` is the merged
     log-sum-exp the forward returned; with ``softmax_d`` (= rowsum(dO * O), ``[B, H, S]``) given,
     ``o`` is not read."""
     B, S, H, D = q.shape
-    left, right = _bounds(S, window_size, causal)
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    _, bplan = _plans(S, left, right, str(q.device))
+    _, bplan = _plans(_seq_bounds(cu_seqlens, S), S, tuple(int(x) for x in window_size), bool(causal), str(q.device))
     q, k, v, d_o = q.contiguous(), k.contiguous(), v.contiguous(), d_o.contiguous()
     if softmax_d is None:
         softmax_d = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
@@ -135,22 +157,25 @@ def window_backward(d_o, q, k, v, o, lse, window_size, causal: bool = False,
 
 class _WindowFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, window_size, causal, softmax_scale):
-        o, lse = window_forward(q, k, v, window_size, causal, softmax_scale)
+    def forward(ctx, q, k, v, window_size, causal, softmax_scale, cu_seqlens=None):
+        cu = None if cu_seqlens is None else tuple(int(x) for x in cu_seqlens)
+        o, lse = window_forward(q, k, v, window_size, causal, softmax_scale, cu_seqlens=cu)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.args = (tuple(window_size), bool(causal), softmax_scale)
+        ctx.args = (tuple(window_size), bool(causal), softmax_scale, None, cu)
         return o
 
     @staticmethod
     def backward(ctx, d_o):
         q, k, v, o, lse = ctx.saved_tensors
         dq, dk, dv = window_backward(d_o, q, k, v, o, lse, *ctx.args)
-        return dq, dk, dv, None, None, None
+        return dq, dk, dv, None, None, None, None
 
 
 def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window_size=(-1, -1),
-                             causal: bool = False, softmax_scale: Optional[float] = None) -> torch.Tensor:
+                             causal: bool = False, softmax_scale: Optional[float] = None,
+                             cu_seqlens=None) -> torch.Tensor:
     """``softmax(mask(Q K^T) * scale) V`` with the band mask ``r - left <= c <= r + right``; autograd.
+    ``cu_seqlens``: the token axis is a packed batch of sequences that attend only themselves.
     ``[batch, tokens, heads, head_dim]`` tensors (bf16 and head dim 128 on CUDA; any float type and
     head dim on CPU; a smaller head dim on CUDA runs zero-padded to 128 with the scale of the true
     head dim); grouped-query K / V allowed."""
@@ -159,5 +184,5 @@ def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
         pad = A.KERNEL_HEAD_DIM - D
         scale = softmax_scale if softmax_scale is not None else D ** -0.5
         qp, kp, vp = (torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v))
-        return _WindowFunction.apply(qp, kp, vp, tuple(window_size), causal, scale)[..., :D]
-    return _WindowFunction.apply(q, k, v, tuple(window_size), causal, softmax_scale)
+        return _WindowFunction.apply(qp, kp, vp, tuple(window_size), causal, scale, cu_seqlens)[..., :D]
+    return _WindowFunction.apply(q, k, v, tuple(window_size), causal, softmax_scale, cu_seqlens)
