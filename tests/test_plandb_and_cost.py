@@ -372,3 +372,27 @@ def test_scalability_table_from_the_kept_measurements(capsys):
     assert len(lines) == 2 and lines[0].split("|")[4].strip() == "2" and lines[0].split("|")[-2].strip() == "1.000"
     eff8 = float(lines[1].split("|")[-2])
     assert 0.9 < eff8 <= 1.0
+
+
+def test_precompute_allocations_driver(tmp_path, capsys):
+    """Shipped answers make the driver a no-op (nothing solved now); ``--resolve`` solves again and
+    writes tables that are valid allocations of the pattern."""
+    import json
+    from ultraattn_b200.drivers import precompute_allocations as D
+    from ultraattn_b200.planner import allocate
+    shipped = allocate._SHIPPED
+    try:
+        out = tmp_path / "a.json"
+        D.main(["--out", str(out), "--cp", "2", "--time-limit", "3", "--configs", "causal128k"])
+        assert "(0 solved now)" in capsys.readouterr().out and json.loads(out.read_text()) == {}
+        D.main(["--out", str(out), "--cp", "2", "--time-limit", "3", "--configs", "causal128k", "--resolve"])
+        data = json.loads(out.read_text())
+        assert data and all("CP=2" in k and "repr=[[2]]" in k for k in data)
+        for k, e in data.items():
+            t = e["table"]
+            assert len(t) == len(t[0]) and max(max(r) for r in t) == 1          # both ranks used, square
+            assert all(t[i][j] == -1 for i in range(len(t)) for j in range(i + 1, len(t)))   # causal: nothing above the diagonal
+        import os
+        assert "UA_PLAN_CACHE" not in os.environ or not os.environ["UA_PLAN_CACHE"].startswith("/tmp/ua_alloc_")
+    finally:
+        allocate._SHIPPED = shipped

@@ -20,17 +20,36 @@ import tempfile
 from pathlib import Path
 
 
-def main() -> None:
+def main(argv=None) -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", required=True)
     ap.add_argument("--cp", default="2,4,8")
     ap.add_argument("--time-limit", type=float, default=60.0)
     ap.add_argument("--configs", default=None)
-    a = ap.parse_args()
+    ap.add_argument("--resolve", action="store_true",
+                    help="solve again even where the shipped file has an answer (e.g. with a longer --time-limit)")
+    a = ap.parse_args(argv)
     work = tempfile.mkdtemp(prefix="ua_alloc_")
+    before = os.environ.get("UA_PLAN_CACHE")
     os.environ["UA_PLAN_CACHE"] = work
+    from ..planner import allocate
+    shipped = allocate._SHIPPED
+    try:
+        _run(a, work)
+    finally:                                    # a caller in the same process keeps its own cache setting
+        allocate._SHIPPED = shipped
+        if before is None:
+            os.environ.pop("UA_PLAN_CACHE", None)
+        else:
+            os.environ["UA_PLAN_CACHE"] = before
+
+
+def _run(a, work: str) -> None:
     from ..patterns.blocks import BSA_Config
+    from ..planner import allocate
     from ..planner.allocate import solve_sparse_from_bsa
+    if a.resolve:
+        allocate._SHIPPED = {}                  # the lookup then sees only what this run solves
     from ..runtime.context_parallel import plan_allocation
     from .bench_configs import CONFIGS
     names = a.configs.split(",") if a.configs else list(CONFIGS)
@@ -45,9 +64,11 @@ def main() -> None:
             print(f"{name} cp={cp}: ParD={table.shape[0]} fwd comm {al.comm_volume} ({al.status})", flush=True)
     out = Path(a.out)
     data = json.loads(out.read_text()) if out.exists() else {}
-    data.update(json.loads((Path(work) / "allocations.json").read_text()))
+    solved = Path(work) / "allocations.json"
+    fresh = json.loads(solved.read_text()) if solved.exists() else {}     # absent: every answer was shipped already
+    data.update(fresh)
     out.write_text(json.dumps(data, indent=0, sort_keys=True))
-    print(f"{len(data)} allocations in {out}")
+    print(f"{len(data)} allocations in {out} ({len(fresh)} solved now)")
 
 
 if __name__ == "__main__":
