@@ -52,45 +52,86 @@ def test_window_attention_matches_dense_masked_attention(S, window, causal):
         assert (a - b).abs().max() < 5e-5 * max(1.0, b.abs().max().item())
 
 
-def test_window_plan_covers_every_visible_pair_exactly_once():
-    """Count, per (query, key) pair, how many segments of the forward rows and of the backward
-    columns cover it: exactly the band, once each."""
-    S, left, right = 700, 290, 45
-    rows, cols = W.window_rows_cols(S, left, right)
-    r = torch.arange(S)[:, None]
-    c = torch.arange(S)[None, :]
-    band = ((c >= r - left) & (c <= r + right)).int()
-
+def _coverage(rows, cols, T):
+    """(forward, backward) count matrices [T, T]: how many segments cover each (query, key) pair,
+    in the usual token order."""
     def to_std(idx, slot):
-        return idx if slot == 0 else S - 1 - idx
+        return idx if slot == 0 else T - 1 - idx
 
-    fwd = torch.zeros(S, S, dtype=torch.int32)
+    def mark(mat, q_slot, q_start, q_len, k_slot, k_start, k_len, causal, diag):
+        rr = torch.arange(q_len)[:, None]
+        cc = torch.arange(k_len)[None, :]
+        vis = (cc <= rr + diag) if causal else torch.ones(q_len, k_len, dtype=torch.bool)
+        qi = to_std(q_start + rr, q_slot).expand_as(vis)[vis]
+        ki = to_std(k_start + cc, k_slot).expand_as(vis)[vis]
+        mat.index_put_((qi, ki), torch.ones_like(qi, dtype=torch.int32), accumulate=True)
+
+    fwd = torch.zeros(T, T, dtype=torch.int32)
     for row in rows:
         for seg in row.segs:
-            rr = torch.arange(row.q_len)[:, None]
-            cc = torch.arange(seg.length)[None, :]
-            vis = (cc <= rr + seg.diag) if seg.causal else torch.ones(row.q_len, seg.length, dtype=torch.bool)
-            qi = to_std(row.q_start + rr, row.q_src).expand_as(vis)[vis]
-            ki = to_std(seg.start + cc, seg.src).expand_as(vis)[vis]
-            fwd.index_put_((qi, ki), torch.ones_like(qi, dtype=torch.int32), accumulate=True)
-    assert torch.equal(fwd, band)
-    bwd = torch.zeros(S, S, dtype=torch.int32)
+            assert seg.src == row.q_src == row.o_slot and row.o_start == row.q_start
+            mark(fwd, row.q_src, row.q_start, row.q_len, seg.src, seg.start, seg.length, seg.causal, seg.diag)
+    bwd = torch.zeros(T, T, dtype=torch.int32)
     for col in cols:
         for seg in col.segs:
-            rr = torch.arange(seg.length)[:, None]
-            cc = torch.arange(col.kv_len)[None, :]
-            vis = (cc <= rr + seg.diag) if seg.causal else torch.ones(seg.length, col.kv_len, dtype=torch.bool)
-            qi = to_std(seg.start + rr, seg.src).expand_as(vis)[vis]
-            ki = to_std(col.kv_start + cc, col.kv_src).expand_as(vis)[vis]
-            bwd.index_put_((qi, ki), torch.ones_like(qi, dtype=torch.int32), accumulate=True)
-    assert torch.equal(bwd, band)
-    # each gradient row of each slot is produced by at most one column (bf16 outputs are overwritten)
+            assert seg.src == col.kv_src == col.g_slot and col.g_start == col.kv_start
+            mark(bwd, seg.src, seg.start, seg.length, col.kv_src, col.kv_start, col.kv_len, seg.causal, seg.diag)
+    return fwd, bwd
+
+
+def _band(bounds, T, left, right):
+    want = torch.zeros(T, T, dtype=torch.int32)
+    for a, b in bounds:
+        r = torch.arange(a, b)[:, None]
+        c = torch.arange(a, b)[None, :]
+        want[a:b, a:b] = ((c >= r - left) & (c <= r + right)).int()
+    return want
+
+
+def test_window_plan_covers_every_visible_pair_exactly_once():
+    """Count, per (query, key) pair, how many segments of the forward rows and of the backward
+    columns cover it: exactly the band, once each; and no gradient row has two writers."""
+    S, left, right = 700, 290, 45
+    rows, cols = W.window_rows_cols(S, left, right)
+    fwd, bwd = _coverage(rows, cols, S)
+    band = _band([(0, S)], S, left, right)
+    assert torch.equal(fwd, band) and torch.equal(bwd, band)
     for slot in (0, 1):
         covered = torch.zeros(S, dtype=torch.int32)
         for col in cols:
             if col.g_slot == slot:
                 covered[col.g_start:col.g_start + col.kv_len] += 1
         assert covered.max() <= 1
+
+
+def test_window_plans_of_random_shapes_and_packed_batches_cover_the_band():
+    """Forty random cases: sequence lengths from 1 to 900 tokens (up to three sequences packed in
+    one buffer, with slack behind them), windows from 0 to beyond the sequence, one- and two-sided."""
+    import random
+    rng = random.Random(7)
+    for _ in range(40):
+        lens = [rng.choice([1, 2, 17, 255, 256, 257, 400, 513, 900]) for _ in range(rng.randint(1, 3))]
+        slack = rng.choice([0, 0, 5])
+        T = sum(lens) + slack
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        bounds = list(zip(cu[:-1], cu[1:]))
+        window = (rng.choice([-1, 0, 1, 63, 254, 255, 256, 300, 1000]), rng.choice([-1, 0, 0, 1, 70, 256, 1000]))
+        causal = rng.random() < 0.3
+        rows, cols = [], []
+        for a, b in bounds:
+            left, right = W._bounds(b - a, window, causal)
+            r, c = W.window_rows_cols(b - a, left, right, a, T)
+            rows += r
+            cols += c
+        fwd, bwd = _coverage(rows, cols, T)
+        want = torch.zeros(T, T, dtype=torch.int32)
+        for a, b in bounds:
+            left, right = W._bounds(b - a, window, causal)
+            want += _band([(a, b)], T, left, right)
+        assert torch.equal(fwd, want), (lens, window, causal)
+        assert torch.equal(bwd, want), (lens, window, causal)
 
 
 def test_window_size_through_the_flash_attention_calling_convention():
