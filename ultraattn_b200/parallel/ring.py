@@ -552,9 +552,14 @@ def deepspeed_ulysses_attn_forward(process_groups, q_s, k_s, v_s, softmax_scale,
     list of head_parallel_attn/deepspeed_ulysses_attn.py:10-47, whose compute step is missing)."""
     from ..api import local_plans
     from ..patterns import named
-    _check_unsupported(dropout_p, alibi_slopes, window_size)
+    _check_unsupported(dropout_p, alibi_slopes, (-1, -1))
     a2a = A2AComm(process_groups)
     qh, kh, vh = (a2a.all_to_all(t, 2, 1) for t in (q_s, k_s, v_s))       # [B, S, H/sp, D]
+    if tuple(int(x) for x in window_size) != (-1, -1):
+        # whole sequences on every rank: a sliding window is the single-device operator
+        from ..ops.window import window_forward
+        oh, lse = window_forward(qh, kh, vh, window_size, bool(causal), softmax_scale)
+        return a2a.all_to_all(oh, 1, 2), qh, kh, vh, oh, lse
     fplan, _ = local_plans(named.causal(1) if causal else named.full(1), qh.shape[1], qh.device)
     oh = torch.empty_like(qh)
     lse = torch.empty(qh.shape[0], qh.shape[2], qh.shape[1], dtype=torch.float32, device=qh.device)
@@ -569,10 +574,14 @@ def deepspeed_ulysses_attn_backward(process_group, dout_s, q_h, k_h, v_h, out_h,
     list of head_parallel_attn/deepspeed_ulysses_attn.py:49-95)."""
     from ..api import local_backward, local_plans
     from ..patterns import named
-    _check_unsupported(dropout_p, alibi_slopes, window_size)
+    _check_unsupported(dropout_p, alibi_slopes, (-1, -1))
     a2a = A2AComm(process_group)
-    _, bplan = local_plans(named.causal(1) if causal else named.full(1), q_h.shape[1], q_h.device)
     doh = a2a.all_to_all(dout_s.contiguous(), 2, 1)
+    if tuple(int(x) for x in window_size) != (-1, -1):
+        from ..ops.window import window_backward
+        dq, dk, dv = window_backward(doh, q_h, k_h, v_h, out_h, softmax_lse, window_size, bool(causal), softmax_scale)
+        return tuple(a2a.all_to_all(t, 1, 2) for t in (dq, dk, dv))
+    _, bplan = local_plans(named.causal(1) if causal else named.full(1), q_h.shape[1], q_h.device)
     dq, dk, dv = local_backward(q_h, k_h, v_h, out_h, softmax_lse, doh, bplan, softmax_scale)
     return tuple(a2a.all_to_all(t, 1, 2) for t in (dq, dk, dv))
 
@@ -587,14 +596,15 @@ class DeepSpeedUlyssesAttnFunc(torch.autograd.Function):
         out_s, qh, kh, vh, oh, lse = deepspeed_ulysses_attn_forward(groups, q, k, v, softmax_scale, dropout_p, causal,
                                                                     window_size, alibi_slopes, deterministic)
         ctx.save_for_backward(qh, kh, vh, oh, lse)
-        ctx.args = (softmax_scale, causal, groups)
+        ctx.args = (softmax_scale, causal, groups, tuple(window_size))
         return (out_s, lse, None) if return_softmax else out_s
 
     @staticmethod
     def backward(ctx, d_o, *rest):
         qh, kh, vh, oh, lse = ctx.saved_tensors
-        scale, causal, groups = ctx.args
-        grads = deepspeed_ulysses_attn_backward(groups, d_o, qh, kh, vh, oh, lse, scale, causal=causal)
+        scale, causal, groups, window = ctx.args
+        grads = deepspeed_ulysses_attn_backward(groups, d_o, qh, kh, vh, oh, lse, scale, causal=causal,
+                                                window_size=window)
         return tuple(grads) + (None,) * 10
 
 
@@ -604,7 +614,8 @@ def deepspeed_ulysses_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, caus
     """Head-parallel attention: inputs are sequence shards ``[B, S/sp, H, D]``; an all-to-all
     re-shards to ``[B, S, H/sp, D]``, attention runs on whole sequences, a second all-to-all
     restores the sequence sharding. ``groups`` (the reference's keyword) and ``group`` name the
-    same process group. (The reference's version is a stub whose compute step is missing,
+    same process group. ``window_size``: sliding window (``ops/window.py``), the one context-parallel
+    strategy here that takes token-exact windows. (The reference's version is a stub whose compute step is missing,
     head_parallel_attn/deepspeed_ulysses_attn.py:43-47.)"""
     return DeepSpeedUlyssesAttnFunc.apply(q, k, v, dropout_p, softmax_scale, causal, window_size, alibi_slopes,
                                           deterministic, return_attn_probs, groups if groups is not None else group,
