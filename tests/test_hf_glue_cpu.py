@@ -12,18 +12,26 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, seq_algo, ret):
+def _worker(rank, world, port, seq_algo, ret, family="llama"):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         import easy_context
-        from transformers import LlamaConfig, LlamaForCausalLM
-        cfg = LlamaConfig(vocab_size=97, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
-                          num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
-                          attn_implementation="eager")
-        torch.manual_seed(0)
-        model = LlamaForCausalLM(cfg).train()
+        if family == "mistral":             # every layer attends a sliding window of 24 tokens
+            from transformers import MistralConfig, MistralForCausalLM
+            cfg = MistralConfig(vocab_size=97, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
+                                sliding_window=24, attn_implementation="eager")
+            torch.manual_seed(0)
+            model = MistralForCausalLM(cfg).train()
+        else:
+            from transformers import LlamaConfig, LlamaForCausalLM
+            cfg = LlamaConfig(vocab_size=97, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                              num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
+                              attn_implementation="eager")
+            torch.manual_seed(0)
+            model = LlamaForCausalLM(cfg).train()
         T = 64
         g = torch.Generator().manual_seed(1)
         ids = torch.randint(0, 97, (1, T), generator=g)
@@ -65,3 +73,22 @@ def test_hf_llama_context_parallel_world2(seq_algo):
     for r in range(2):
         assert isinstance(ret[r], tuple), ret[r]
         assert ret[r][0] < 1e-4 and ret[r][1] < 1e-4, (r, ret[r])
+
+
+def test_hf_mistral_sliding_window_head_parallel_world2():
+    """A Mistral whose layers use a sliding window: the registered head-parallel attention applies
+    the token-exact window (logits and weight gradients match the unsharded eager model), and a
+    strategy that cannot apply it refuses instead of attending too far back."""
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(2, 29100 + os.getpid() % 90, "ulysses_attn", ret, "mistral"), nprocs=2, join=True)
+    for r in range(2):
+        assert isinstance(ret[r], tuple), ret[r]
+        assert ret[r][0] < 1e-4 and ret[r][1] < 1e-4, (r, ret[r])
+    sys.path.insert(0, ROOT)
+    from ultraattn_b200.models.glue import make_attention_interface
+    fn = make_attention_interface("zigzag_ring_attn")
+    q = torch.randn(1, 2, 8, 4)
+    with pytest.raises(NotImplementedError, match="sliding_window"):
+        fn(None, q, q, q, None, 0.0, None, sliding_window=4)
+    with pytest.raises(NotImplementedError, match="dropout"):
+        fn(None, q, q, q, None, 0.1, None)

@@ -81,6 +81,19 @@ def make_attention_interface(seq_algo: str, group=None, runtime=None):
         q = query.transpose(1, 2).contiguous()
         k = key.transpose(1, 2).contiguous()
         v = value.transpose(1, 2).contiguous()
+        if dropout:
+            raise NotImplementedError("attention dropout is not implemented by these kernels (set attention_dropout=0)")
+        window = kwargs.get("sliding_window")
+        if window is not None:
+            # transformers hands a layer's sliding window (Mistral and others) to the attention
+            # function; only the head-parallel strategy holds whole sequences and can apply a
+            # token-exact band. Anything else must refuse rather than attend too far back.
+            if runtime is not None or kind != "ulysses":
+                raise NotImplementedError(
+                    f"sliding_window={window} needs seq_algo='ulysses' (token-exact windows are not part of the "
+                    f"{seq_algo!r} strategy; a block-level window is a pattern of the context-parallel runtime)")
+            out = fn(q, k, v, softmax_scale=scaling, causal=True, group=group, window_size=(int(window) - 1, 0))
+            return out, None
         if runtime is not None:
             out = runtime(q, k, v, scaling)
         else:
