@@ -92,3 +92,15 @@ def test_hf_mistral_sliding_window_head_parallel_world2():
         fn(None, q, q, q, None, 0.0, None, sliding_window=4)
     with pytest.raises(NotImplementedError, match="dropout"):
         fn(None, q, q, q, None, 0.1, None)
+    # a mask that is more than causal is reported (once), a causal one is not
+    import warnings
+    from ultraattn_b200.models import glue
+    glue._mask_warned[0] = False
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        glue._warn_if_not_causal(torch.ones(8, 8, dtype=torch.bool).tril()[None, None])
+        glue._warn_if_not_causal(torch.zeros(8, 8).masked_fill(~torch.ones(8, 8, dtype=torch.bool).tril(), float("-inf"))[None, None])
+    padded = torch.ones(8, 8, dtype=torch.bool).tril()
+    padded[:, :2] = False
+    with pytest.warns(RuntimeWarning, match="ignores attention_mask"):
+        glue._warn_if_not_causal(padded[None, None])

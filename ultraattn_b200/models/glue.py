@@ -50,6 +50,26 @@ def prepare_seq_parallel_inputs(seq_algo: str, input_ids, position_ids, target_i
     return out
 
 
+_mask_warned = [False]
+
+
+def _warn_if_not_causal(mask) -> None:
+    """The strategies apply a causal mask over the global positions themselves and do not read
+    ``attention_mask``. A mask that says more than "causal" (padding, packed documents) would be
+    dropped silently, so it is reported once; masks too large to compare cheaply are not checked."""
+    if mask is None or _mask_warned[0] or mask.dim() < 2 or mask.numel() > (1 << 24):
+        return
+    allowed = mask if mask.dtype == torch.bool else mask == 0
+    tq, tk = allowed.shape[-2], allowed.shape[-1]
+    causal = torch.ones(tq, tk, dtype=torch.bool, device=mask.device).tril(tk - tq)
+    if not torch.equal(allowed.reshape(-1, tq, tk), causal.expand(allowed.numel() // (tq * tk), tq, tk)):
+        import warnings
+        _mask_warned[0] = True
+        warnings.warn("the context-parallel attention function ignores attention_mask, and this mask is not a plain "
+                      "causal one (padding or packed sequences?): use the varlen strategies for packed batches",
+                      RuntimeWarning, stacklevel=3)
+
+
 def make_attention_interface(seq_algo: str, group=None, runtime=None):
     """An attention function with the calling convention of transformers' attention registry:
     ``(module, query[B,H,T,D], key, value, attention_mask, dropout, scaling, **kw) -> (out[B,T,H,D], None)``."""
@@ -83,6 +103,7 @@ def make_attention_interface(seq_algo: str, group=None, runtime=None):
         v = value.transpose(1, 2).contiguous()
         if dropout:
             raise NotImplementedError("attention dropout is not implemented by these kernels (set attention_dropout=0)")
+        _warn_if_not_causal(attention_mask)
         window = kwargs.get("sliding_window")
         if window is not None:
             # transformers hands a layer's sliding window (Mistral and others) to the attention
