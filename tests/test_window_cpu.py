@@ -74,7 +74,7 @@ def _coverage(rows, cols, T):
     bwd = torch.zeros(T, T, dtype=torch.int32)
     for col in cols:
         for seg in col.segs:
-            assert seg.src == col.kv_src == col.g_slot and col.g_start == col.kv_start
+            assert seg.src == col.kv_src and col.g_slot in (col.kv_src, 2) and col.g_start == col.kv_start
             mark(bwd, seg.src, seg.start, seg.length, col.kv_src, col.kv_start, col.kv_len, seg.causal, seg.diag)
     return fwd, bwd
 
@@ -203,3 +203,63 @@ def test_windows_in_a_packed_batch():
                                     0.0, None, False, window_size=(left, right))
         assert (gq - dq_ref[0]).abs().max() < 5e-5 and (gk - dk_ref[0]).abs().max() < 5e-5
         assert (gv - dv_ref[0]).abs().max() < 5e-5
+
+
+def _band_with_sinks(S, left, right, sink):
+    r = torch.arange(S)[:, None]
+    c = torch.arange(S)[None, :]
+    return ((c >= r - left) & (c <= r + right)) | ((c < sink) & (c <= r + right))
+
+
+@pytest.mark.parametrize("S,left,right,sink", [(1000, 300, 0, 4), (700, 255, 0, 256), (520, 40, 0, 41),
+                                               (900, 128, 30, 16), (300, 1000, 0, 8), (256, 100, 0, 3)])
+def test_attention_sinks_cover_and_match_dense(S, left, right, sink):
+    """Sliding window plus attention sinks (the first tokens stay visible to every later query):
+    every visible pair once in the forward rows and in the backward columns, and outputs and
+    gradients equal dense masked attention."""
+    l, r_ = W._bounds(S, (left, right), False)
+    rows, cols = W.window_rows_cols(S, l, r_, sink=sink)
+    fwd, bwd = _coverage(rows, cols, S)
+    want = _band_with_sinks(S, l, r_, sink).int()
+    assert torch.equal(fwd, want) and torch.equal(bwd, want)
+    for slot in (0, 1, 2):                  # one writer per gradient row and slot
+        covered = torch.zeros(S, dtype=torch.int32)
+        for col in cols:
+            if col.g_slot == slot:
+                covered[col.g_start:col.g_start + col.kv_len] += 1
+        assert covered.max() <= 1
+    torch.manual_seed(S + sink)
+    B, H, Hk, D = 1, 2, 1, 16
+    q = torch.randn(B, S, H, D).requires_grad_()
+    k = torch.randn(B, S, Hk, D).requires_grad_()
+    v = torch.randn(B, S, Hk, D).requires_grad_()
+    g = torch.randn(B, S, H, D)
+    sc = torch.einsum("bqhd,bkhd->bhqk", q, k.repeat_interleave(H // Hk, 2)) / math.sqrt(D)
+    sc = sc.masked_fill(~_band_with_sinks(S, l, r_, sink), float("-inf"))
+    o_ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc, -1), v.repeat_interleave(H // Hk, 2))
+    ref = torch.autograd.grad(o_ref, (q, k, v), g)
+    o = W.sliding_window_attention(q, k, v, (left, right), sink_tokens=sink)
+    assert (o - o_ref).abs().max() < 2e-5
+    got = torch.autograd.grad(o, (q, k, v), g)
+    for a, b in zip(got, ref):
+        assert (a - b).abs().max() < 5e-5 * max(1.0, b.abs().max().item())
+
+
+def test_too_many_sinks_are_refused():
+    with pytest.raises(AssertionError, match="sink tokens"):
+        W.window_rows_cols(1000, 50, 0, sink=52)
+
+
+def test_sinks_in_a_packed_batch():
+    """Every sequence of a packed batch has its own sinks; operator against per-sequence dense attention."""
+    torch.manual_seed(3)
+    cu = [0, 350, 400, 1000]
+    T, H, D, left, sink = 1000, 2, 16, 90, 5
+    q, k, v = (torch.randn(1, T, H, D) for _ in range(3))
+    o = W.sliding_window_attention(q, k, v, (left, 0), cu_seqlens=cu, sink_tokens=sink)
+    for a, b in zip(cu[:-1], cu[1:]):
+        n = b - a
+        sc = torch.einsum("bqhd,bkhd->bhqk", q[:, a:b], k[:, a:b]) / math.sqrt(D)
+        sc = sc.masked_fill(~_band_with_sinks(n, left, 0, sink), float("-inf"))
+        o_ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc, -1), v[:, a:b])
+        assert (o[:, a:b] - o_ref).abs().max() < 2e-5

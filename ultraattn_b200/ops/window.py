@@ -16,6 +16,11 @@ Both parts go into one forward launch (two query sources, two key/value sources,
 one backward launch; the partial results are merged by their log-sum-exps like the steps of a ring.
 The reversed copies cost three passes over Q, K, V (and dO) - small beside the attention itself.
 
+Attention sinks (the first ``sink_tokens`` keys stay visible to every later query: the exact,
+token-level form of the "streaming" pattern) add a third part: a fully visible segment ``[0,
+sink_tokens)`` for every row block behind the first, with the band clipped so that no key is
+counted twice; its dK / dV go to a buffer of their own and are added afterwards.
+
 The reference's flash-attention fork accepts ``window_size`` in every call
 (ring_flash_attn/ring_flash_attn.py:33-43) and always passes ``(-1, -1)``.
 """
@@ -49,43 +54,59 @@ def _partition(S: int, left: int) -> list:
     return [(a, min(S, a + step)) for a in range(0, S, step)]
 
 
-def window_rows_cols(S: int, left: int, right: int, base: int = 0, total: Optional[int] = None) -> tuple[list, list]:
-    """(forward rows, backward columns) of the two-part plan for one sequence of ``S`` tokens that
-    starts at token ``base`` of a buffer of ``total`` tokens (a packed batch; default: the sequence
-    is the buffer). Source / output slot 0 is the usual token order, slot 1 the buffer reversed,
-    where the sequence occupies ``[total - base - S, total - base)``."""
+def window_rows_cols(S: int, left: int, right: int, base: int = 0, total: Optional[int] = None,
+                     sink: int = 0) -> tuple[list, list]:
+    """(forward rows, backward columns) of the plan for one sequence of ``S`` tokens that starts at
+    token ``base`` of a buffer of ``total`` tokens (a packed batch; default: the sequence is the
+    buffer). Source / output slot 0 is the usual token order, slot 1 the buffer reversed, where the
+    sequence occupies ``[total - base - S, total - base)``. With ``sink`` > 0 the first ``sink``
+    keys are visible to every query behind the first row block (which sees them through its
+    causal part anyway); their gradients are collected in gradient slot 2 at rows ``base...``."""
     total = S if total is None else total
     rbase = total - base - S
     blocks = _partition(S, left)
+    sink = min(sink, S)
+    assert sink <= blocks[0][1], f"at most {blocks[0][1]} sink tokens fit the first row block of this window"
     rows, cols = [], []
     for r0, r1 in blocks:
         n = r1 - r0
-        # part A
+        s_here = sink if r0 > 0 else 0              # sink keys this block sees as a segment of their own
+        # part A (+ the sinks)
         a_len = min(S, r1 + right) - r0
-        rows.append(A.Row(0, base + r0, n, (A.Seg(0, base + r0, a_len, right < S, right),), 0, base + r0, False))
+        segs = (A.Seg(0, base + r0, a_len, right < S, right),)
+        if s_here:
+            segs = (A.Seg(0, base, s_here, False, 0),) + segs
+        rows.append(A.Row(0, base + r0, n, segs, 0, base + r0, False))
         q0 = max(0, r0 - right)                      # key block [r0, r1): rows from q0 to r1 reach it
         cols.append(A.Col(0, base + r0, n, (A.Seg(0, base + q0, r1 - q0, right < S, q0 + right - r0),), 0, base + r0))
-        # part B, reversed order: row block [S - r1, S - r0), its keys start right behind it
-        b_len = min(left, r0)
+        # part B, reversed order: row block [S - r1, S - r0), its keys start right behind it and
+        # stop before the sinks
+        b_len = min(left, r0 - s_here)
         if b_len > 0:
             rows.append(A.Row(1, rbase + S - r1, n, (A.Seg(1, rbase + S - r0, b_len, left < S, left - n),), 1,
                               rbase + S - r1, False))
         c0 = S - r1                                  # the same block as a key block of the reversed order
         q0 = max(0, c0 - left)
-        if c0 - q0 > 0:
-            cols.append(A.Col(1, rbase + c0, n, (A.Seg(1, rbase + q0, c0 - q0, left < S, q0 + left - c0),), 1,
+        if c0 - q0 > 0 and not (sink and r1 <= sink):
+            # as keys, the first `sink` tokens of the sequence belong to the sink part for every
+            # later row block, so in the reversed order the key block loses them
+            k_len = n if r0 >= sink else r1 - sink      # reversed, the sink keys are the tail of the first block
+            cols.append(A.Col(1, rbase + c0, k_len, (A.Seg(1, rbase + q0, c0 - q0, left < S, q0 + left - c0),), 1,
                               rbase + c0))
+    if sink and len(blocks) > 1:
+        first = blocks[0][1]
+        cols.append(A.Col(0, base, sink, (A.Seg(0, base + first, S - first, False, 0),), 2, base))
     return rows, cols
 
 
 @functools.lru_cache(maxsize=32)
-def _plans(bounds: tuple, total: int, window_size: tuple, causal: bool, device_str: str):
+def _plans(bounds: tuple, total: int, window_size: tuple, causal: bool, device_str: str, sink: int = 0):
     """Plans of a buffer of ``total`` tokens holding the sequences ``bounds`` = ((start, end), ...)."""
     rows, cols = [], []
     for a, b in bounds:
         if b > a:
             left, right = _bounds(b - a, window_size, causal)
-            r, c = window_rows_cols(b - a, left, right, a, total)
+            r, c = window_rows_cols(b - a, left, right, a, total, sink)
             rows += r
             cols += c
     dev = torch.device(device_str)
@@ -105,14 +126,16 @@ def _flip(t: torch.Tensor, dim: int = 1) -> torch.Tensor:
 
 
 def window_forward(q, k, v, window_size, causal: bool = False, softmax_scale: Optional[float] = None,
-                   out: Optional[torch.Tensor] = None, cu_seqlens=None):
+                   out: Optional[torch.Tensor] = None, cu_seqlens=None, sink_tokens: int = 0):
     """``q`` ``[B, S, H, D]``, ``k`` / ``v`` ``[B, S, Hkv, D]`` -> ``(o [B, S, H, D], lse [B, H, S] fp32)``.
     With ``cu_seqlens`` the token axis is a packed batch: sequence i spans ``cu_seqlens[i] :
-    cu_seqlens[i + 1]``, attends only itself, and the window counts positions inside it."""
+    cu_seqlens[i + 1]``, attends only itself, and the window counts positions inside it.
+    ``sink_tokens``: the first keys of every sequence that stay visible beyond the window."""
     B, S, H, D = q.shape
     assert k.shape[1] == S, "sliding windows need as many keys as queries"
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    fplan, _ = _plans(_seq_bounds(cu_seqlens, S), S, tuple(int(x) for x in window_size), bool(causal), str(q.device))
+    fplan, _ = _plans(_seq_bounds(cu_seqlens, S), S, tuple(int(x) for x in window_size), bool(causal), str(q.device),
+                      int(sink_tokens))
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     qr, kr, vr = _flip(q), _flip(k), _flip(v)
     o_a, o_b = torch.zeros_like(q), torch.zeros_like(q)
@@ -129,13 +152,14 @@ def window_forward(q, k, v, window_size, causal: bool = False, softmax_scale: Op
 
 def window_backward(d_o, q, k, v, o, lse, window_size, causal: bool = False,
                     softmax_scale: Optional[float] = None, softmax_d: Optional[torch.Tensor] = None,
-                    cu_seqlens=None):
+                    cu_seqlens=None, sink_tokens: int = 0):
     """Gradients ``(dq, dk, dv)`` in the dtypes of ``q``, ``k``, ``v``. ``lse`` is the merged
     log-sum-exp the forward returned; with ``softmax_d`` (= rowsum(dO * O), ``[B, H, S]``) given,
     ``o`` is not read."""
     B, S, H, D = q.shape
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    _, bplan = _plans(_seq_bounds(cu_seqlens, S), S, tuple(int(x) for x in window_size), bool(causal), str(q.device))
+    _, bplan = _plans(_seq_bounds(cu_seqlens, S), S, tuple(int(x) for x in window_size), bool(causal), str(q.device),
+                      int(sink_tokens))
     q, k, v, d_o = q.contiguous(), k.contiguous(), v.contiguous(), d_o.contiguous()
     if softmax_d is None:
         softmax_d = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
@@ -146,36 +170,41 @@ def window_backward(d_o, q, k, v, o, lse, window_size, causal: bool = False,
     f32 = lambda t: torch.zeros(t.shape, dtype=torch.float32, device=t.device)
     dq_a, dq_b = f32(q), f32(q)
     kv_a, kv_b = A.BwdKvOut(f32(k), f32(v)), A.BwdKvOut(f32(k), f32(v))
+    kv_outs = [kv_a, kv_b] + ([A.BwdKvOut(f32(k), f32(v))] if sink_tokens else [])     # slot 2: the sinks' share
     sides = [A.BwdQSide(q, d_o, lse, softmax_d, dq_a),
              A.BwdQSide(_flip(q), _flip(d_o), _flip(lse, 2), _flip(softmax_d, 2), dq_b)]
-    A.attn_bwd(sides, [k, _flip(k)], [v, _flip(v)], [kv_a, kv_b], bplan, scale)
+    A.attn_bwd(sides, [k, _flip(k)], [v, _flip(v)], kv_outs, bplan, scale)
     dq = (dq_a + dq_b.flip(1)).to(q.dtype)
-    dk = (kv_a.dk + kv_b.dk.flip(1)).to(k.dtype)
-    dv = (kv_a.dv + kv_b.dv.flip(1)).to(v.dtype)
-    return dq, dk, dv
+    dk32, dv32 = kv_a.dk + kv_b.dk.flip(1), kv_a.dv + kv_b.dv.flip(1)
+    if sink_tokens:
+        dk32 += kv_outs[2].dk
+        dv32 += kv_outs[2].dv
+    return dq, dk32.to(k.dtype), dv32.to(v.dtype)
 
 
 class _WindowFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, window_size, causal, softmax_scale, cu_seqlens=None):
+    def forward(ctx, q, k, v, window_size, causal, softmax_scale, cu_seqlens=None, sink_tokens=0):
         cu = None if cu_seqlens is None else tuple(int(x) for x in cu_seqlens)
-        o, lse = window_forward(q, k, v, window_size, causal, softmax_scale, cu_seqlens=cu)
+        o, lse = window_forward(q, k, v, window_size, causal, softmax_scale, cu_seqlens=cu, sink_tokens=sink_tokens)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.args = (tuple(window_size), bool(causal), softmax_scale, None, cu)
+        ctx.args = (tuple(window_size), bool(causal), softmax_scale, None, cu, int(sink_tokens))
         return o
 
     @staticmethod
     def backward(ctx, d_o):
         q, k, v, o, lse = ctx.saved_tensors
         dq, dk, dv = window_backward(d_o, q, k, v, o, lse, *ctx.args)
-        return dq, dk, dv, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None
 
 
 def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window_size=(-1, -1),
                              causal: bool = False, softmax_scale: Optional[float] = None,
-                             cu_seqlens=None) -> torch.Tensor:
+                             cu_seqlens=None, sink_tokens: int = 0) -> torch.Tensor:
     """``softmax(mask(Q K^T) * scale) V`` with the band mask ``r - left <= c <= r + right``; autograd.
     ``cu_seqlens``: the token axis is a packed batch of sequences that attend only themselves.
+    ``sink_tokens``: the first keys of every sequence stay visible to all later queries (attention
+    sinks of streaming inference; at most one row block: ``min(256, left + 1)`` tokens).
     ``[batch, tokens, heads, head_dim]`` tensors (bf16 and head dim 128 on CUDA; any float type and
     head dim on CPU; a smaller head dim on CUDA runs zero-padded to 128 with the scale of the true
     head dim); grouped-query K / V allowed."""
@@ -184,5 +213,5 @@ def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
         pad = A.KERNEL_HEAD_DIM - D
         scale = softmax_scale if softmax_scale is not None else D ** -0.5
         qp, kp, vp = (torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v))
-        return _WindowFunction.apply(qp, kp, vp, tuple(window_size), causal, scale, cu_seqlens)[..., :D]
-    return _WindowFunction.apply(q, k, v, tuple(window_size), causal, softmax_scale, cu_seqlens)
+        return _WindowFunction.apply(qp, kp, vp, tuple(window_size), causal, scale, cu_seqlens, sink_tokens)[..., :D]
+    return _WindowFunction.apply(q, k, v, tuple(window_size), causal, softmax_scale, cu_seqlens, sink_tokens)
