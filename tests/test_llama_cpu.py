@@ -9,7 +9,7 @@ from ultraattn_b200 import patterns as P
 from ultraattn_b200.models.llama import LlamaConfig, LlamaModel
 
 
-def _ref_loss(model: LlamaModel, params: dict, ids, targets, pattern):
+def _ref_loss(model: LlamaModel, params: dict, ids, targets, pattern, mask=None):
     c = model.cfg
     T = ids.shape[0]
     x = F.embedding(ids, params["embed"])
@@ -25,14 +25,16 @@ def _ref_loss(model: LlamaModel, params: dict, ids, targets, pattern):
         lo, hi = t[..., :half], t[..., half:]
         return torch.cat([lo * cos - hi * sin, hi * cos + lo * sin], -1)
 
-    mask = pattern.token_mask(T, T)
+    mask = pattern.token_mask(T, T) if mask is None else mask
+    nkv = c.kv_heads * c.head_dim
+    g = c.n_heads // c.kv_heads
     for i in range(c.n_layers):
         h = rms(x, params[f"l{i}.norm1"])
         qkv = h @ params[f"l{i}.wqkv"].t()
         nq = c.n_heads * c.head_dim
         q = rope(qkv[:, :nq].view(T, c.n_heads, c.head_dim))
-        k = rope(qkv[:, nq:2 * nq].view(T, c.n_heads, c.head_dim))
-        v = qkv[:, 2 * nq:].view(T, c.n_heads, c.head_dim)
+        k = rope(qkv[:, nq:nq + nkv].view(T, c.kv_heads, c.head_dim)).repeat_interleave(g, 1)
+        v = qkv[:, nq + nkv:].view(T, c.kv_heads, c.head_dim).repeat_interleave(g, 1)
         s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(c.head_dim)
         s = s.masked_fill(~mask[None], float("-inf"))
         o = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(T, nq)
@@ -135,3 +137,33 @@ def test_trainer_on_two_cpu_ranks_follows_the_single_rank_losses():
     assert len(one["losses"]) == 3 and one["losses"][0] > one["losses"][-1], one["losses"]   # it learns
     for a, b in zip(one["losses"], two["losses"]):
         assert abs(a - b) < 2e-5 * abs(a), (one["losses"], two["losses"])
+
+
+def test_mistral_style_model_with_sliding_window_and_grouped_query_heads():
+    """``LlamaConfig(sliding_window=..., n_kv_heads=...)`` (``LlamaConfig.mistral_7b()`` is that at
+    full size): loss and every weight gradient against plain PyTorch with the band mask; with
+    sink tokens the mask keeps the first tokens visible."""
+    for sinks in (0, 3):
+        torch.manual_seed(1)
+        cfg = LlamaConfig(n_layers=2, hidden=64, n_heads=4, head_dim=16, ffn=96, vocab=50, n_kv_heads=2,
+                          sliding_window=24, sink_tokens=sinks)
+        model = LlamaModel(cfg, lr=1e-2)
+        T = 96
+        ids = torch.randint(0, cfg.vocab, (T,))
+        tg = torch.randint(0, cfg.vocab, (T,))
+        r, c = torch.arange(T)[:, None], torch.arange(T)[None, :]
+        mask = ((c <= r) & (c >= r - 23)) | ((c < sinks) & (c <= r))
+        ref_params = {k: v.detach().clone().requires_grad_() for k, v in model.p.items()}
+        ref = _ref_loss(model, ref_params, ids, tg, None, mask)
+        ref.backward()
+        loss = model.loss(ids, tg, chunk=32)
+        loss.backward()
+        assert abs(loss.item() - ref.item()) < 1e-4
+        for name, p in model.p.items():
+            err = (p.grad - ref_params[name].grad).abs().max().item()
+            assert err < 2e-4, (sinks, name, err)
+    big = LlamaConfig.mistral_7b()
+    assert (big.kv_heads, big.ffn, big.sliding_window, big.n_layers) == (8, 14336, 4096, 32)
+    import pytest
+    with pytest.raises(NotImplementedError, match="sliding window"):
+        LlamaModel(cfg, runtime=object())

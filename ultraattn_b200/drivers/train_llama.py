@@ -83,6 +83,10 @@ def main() -> None:
     ap.add_argument("--offload-checkpoints", action="store_true",
                     help="keep the per-layer activation checkpoints in pinned host memory")
     ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--kv-heads", type=int, default=None, help="grouped-query attention: key/value heads")
+    ap.add_argument("--sliding-window", type=int, default=None,
+                    help="Mistral-style token-exact sliding window (one rank; replaces the block pattern)")
+    ap.add_argument("--sink-tokens", type=int, default=0, help="with --sliding-window: leading tokens that stay visible")
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
                     help="cpu: fp32 ranks over gloo running the PyTorch restatements of the kernels (small shapes; "
                          "checks the token sharding, the plan execution and the sharded optimizer without a GPU)")
@@ -114,7 +118,8 @@ def main() -> None:
             dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=300))
         group = dist.group.WORLD
     cfg = LlamaConfig(n_layers=a.layers, hidden=a.hidden, n_heads=a.heads, head_dim=a.head_dim, ffn=a.ffn,
-                      vocab=a.vocab)
+                      vocab=a.vocab, n_kv_heads=a.kv_heads, sliding_window=a.sliding_window, sink_tokens=a.sink_tokens)
+    assert a.sliding_window is None or world == 1, "--sliding-window runs on one rank"
     pattern = P.global_local(a.blocks, 1, 2)
     runtime = None
     if world > 1 and a.seq_algo == "ulysses":

@@ -48,6 +48,8 @@ class LlamaConfig:
     rope_base: float = 10000.0
     eps: float = 1e-5
     init_std: float = 0.02
+    sliding_window: Optional[int] = None     # Mistral: every query sees itself and the sliding_window - 1 tokens before it
+    sink_tokens: int = 0                     # with a sliding window: leading tokens that stay visible (streaming)
 
     @property
     def kv_heads(self) -> int:
@@ -56,6 +58,12 @@ class LlamaConfig:
     @classmethod
     def llama2_7b(cls) -> "LlamaConfig":
         return cls()
+
+    @classmethod
+    def mistral_7b(cls) -> "LlamaConfig":
+        """Mistral-7B-v0.1: the Llama block with grouped-query attention (8 key/value heads), a
+        14336-wide FFN and a 4096-token sliding window."""
+        return cls(ffn=14336, n_kv_heads=8, sliding_window=4096)
 
 
 # ------------------------------- differentiable ops over the kernels -----------------------------
@@ -284,6 +292,9 @@ class LlamaModel:
         contiguous token range ``[rank * S/world, (rank + 1) * S/world)``, and the rows of every
         ``wqkv`` are stored in destination-rank order (``permute_qkv_weight``)."""
         self.cfg = cfg
+        if cfg.sliding_window is not None and (runtime is not None or (seq_algo == "ulysses" and group is not None)):
+            raise NotImplementedError("a token-exact sliding window runs on whole sequences (one device); in the "
+                                      "context-parallel runtimes express it as a block pattern")
         self.seq_algo = seq_algo
         self.ulysses = None
         self.offload_checkpoints = offload_checkpoints
@@ -405,7 +416,15 @@ class LlamaModel:
         gu = _Linear.apply(h, p[f"l{li}.wgu"])
         return x + _Linear.apply(_Swiglu.apply(gu), p[f"l{li}.wdown"])
 
+    def _window(self):
+        w = self.cfg.sliding_window
+        return None if w is None else (int(w) - 1, 0)
+
     def _attn_fwd(self, q, k, v):
+        if self._window() is not None:
+            # token-exact causal band (ops/window.py); whole sequences only
+            from ..ops.window import window_forward
+            return window_forward(q, k, v, self._window(), True, sink_tokens=self.cfg.sink_tokens)
         if self.runtime is not None:
             # the fused runtime copies into its symmetric buffers anyway (strided views are fine)
             c = (lambda t: t) if getattr(self.runtime, "path", "") == "fused" else (lambda t: t.contiguous())
@@ -418,6 +437,9 @@ class LlamaModel:
         return o, lse
 
     def _attn_bwd(self, d_o, q, k, v, o, lse):
+        if self._window() is not None:
+            from ..ops.window import window_backward
+            return window_backward(d_o, q, k, v, o, lse, self._window(), True, sink_tokens=self.cfg.sink_tokens)
         if self.runtime is not None:
             c = (lambda t: t) if getattr(self.runtime, "path", "") == "fused" else (lambda t: t.contiguous())
             return self.runtime.backward(d_o.contiguous(), c(q), c(k), c(v), o, lse)
