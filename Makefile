@@ -5,7 +5,7 @@ CLUSTER_NAME ?= local
 PLATFORM ?= B200
 export CLUSTER_NAME PLATFORM
 
-.PHONY: build test test-gpu bench cluster_profile bsa_train dense_train bsa_infer report plan fusion_table full_plans predict \
+.PHONY: bench_masks build test test-gpu bench cluster_profile bsa_train dense_train bsa_infer report plan fusion_table full_plans predict \
         figure6 figure7 figure8 figure9 figure10 figure11
 DB ?= database/$(CLUSTER_NAME)/$(PLATFORM)
 CONFIG ?= configs/stride.yaml
@@ -48,6 +48,9 @@ figure10:               ## strong and weak scalability across the rank counts in
 figure11:               ## predicted against measured times (outlier share, R^2)
 	$(PY) -m ultraattn_b200.drivers.report --db $(DB) --level intra --sim-accuracy
 	$(PY) -m ultraattn_b200.drivers.report --db $(DB) --level inter --sim-accuracy
+
+bench_masks:      ## token-level masks (causal, sliding window, prefix-LM, documents) on the kernels: error and time
+	$(PY) -m ultraattn_b200.drivers.bench_masks
 
 plan:             ## one configuration from a YAML file: plan, predicted time (add a launcher to run it)
 	$(PY) -m ultraattn_b200.drivers.main --config $(CONFIG) --plan-only

@@ -263,3 +263,40 @@ def test_sinks_in_a_packed_batch():
         sc = sc.masked_fill(~_band_with_sinks(n, left, 0, sink), float("-inf"))
         o_ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc, -1), v[:, a:b])
         assert (o[:, a:b] - o_ref).abs().max() < 2e-5
+
+
+@pytest.mark.parametrize("S,prefix,cu", [(300, 100, None), (257, 0, None), (128, 500, None), (600, 70, [0, 50, 50, 400, 600])])
+def test_prefix_lm_mask(S, prefix, cu):
+    """Prefix-LM: bidirectional inside the prefix, causal behind it; also per sequence of a packed batch."""
+    import ultraattn_b200 as ua
+    torch.manual_seed(S)
+    H, Hk, D = 4, 2, 16
+    q = torch.randn(1, S, H, D).requires_grad_()
+    k = torch.randn(1, S, Hk, D).requires_grad_()
+    v = torch.randn(1, S, Hk, D).requires_grad_()
+    g = torch.randn(1, S, H, D)
+    mask = torch.zeros(S, S, dtype=torch.bool)
+    for a, b in zip(*(([0], [S]) if cu is None else (cu[:-1], cu[1:]))):
+        r = torch.arange(a, b)[:, None]
+        c = torch.arange(a, b)[None, :]
+        mask[a:b, a:b] = (c <= r) | (c < a + prefix)
+    sc = torch.einsum("bqhd,bkhd->bhqk", q, k.repeat_interleave(2, 2)) / math.sqrt(D)
+    o_ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc.masked_fill(~mask, float("-inf")), -1), v.repeat_interleave(2, 2))
+    ref = torch.autograd.grad(o_ref, (q, k, v), g)
+    o = ua.prefix_lm_attention(q, k, v, prefix, cu_seqlens=cu)
+    assert (o - o_ref).abs().max() < 2e-5
+    got = torch.autograd.grad(o, (q, k, v), g)
+    for x, y in zip(got, ref):
+        assert (x - y).abs().max() < 5e-5
+
+
+def test_mask_benchmark_driver_checks_every_mask():
+    """``drivers/bench_masks.py`` (the masks of the reference's FlexAttention benchmark as launch
+    plans of these kernels): every mask matches dense attention and reports its density and times."""
+    from ultraattn_b200.drivers.bench_masks import run
+    recs = run(512, 4, 2, 16, ["causal", "sliding_window", "prefix_lm", "document"], 120, 70, 5, 1, 16384,
+               torch.device("cpu"))
+    assert [r["mask"] for r in recs] == ["causal", "sliding_window", "prefix_lm", "document"]
+    for r in recs:
+        assert r["max_err"] < 2e-5 and 0 < r["density"] < 0.6 and r["fwd_ms"] > 0 and r["fwd_bwd_tflops"] > 0
+    assert recs[1]["density"] < recs[0]["density"] < recs[2]["density"]      # window < causal < prefix-LM

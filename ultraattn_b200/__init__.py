@@ -7,7 +7,7 @@ profile database), ``runtime`` (plan executors: gloo CPU reference, NCCL baselin
 points), ``models`` (Llama-style model built on the kernels).
 """
 from . import patterns  # noqa: F401
-from .api import attention  # noqa: F401
+from .api import attention, prefix_lm_attention, varlen_attention  # noqa: F401
 from .ops.window import sliding_window_attention  # noqa: F401
 
 __version__ = "0.1.0"

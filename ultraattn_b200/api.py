@@ -135,6 +135,67 @@ class _VarlenAttention(torch.autograd.Function):
         return dq, dk, dv, None, None, None
 
 
+class _PlannedAttention(torch.autograd.Function):
+    """Attention under a token-level launch plan (forward rows, backward columns) on one buffer."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, fplan, bplan, softmax_scale):
+        o = torch.zeros_like(q)
+        lse = torch.full((q.shape[0], q.shape[2], q.shape[1]), float("-inf"), dtype=torch.float32, device=q.device)
+        A.attn_fwd([q], [k], [v], [(o, lse)], fplan, softmax_scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.bplan, ctx.scale = bplan, softmax_scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = local_backward(q, k, v, o, lse, d_o.contiguous(), ctx.bplan, ctx.scale)
+        return dq, dk, dv, None, None, None
+
+
+def prefix_lm_plans(seq_len: int, prefix_length: int, device, cu_seqlens=None):
+    """Launch plans of the prefix-LM mask: the first ``prefix_length`` tokens of a sequence attend
+    each other in both directions, every later token attends causally (and so sees the whole
+    prefix). Token-exact on the block-sparse kernels: the prefix is one fully visible work item, the
+    rest one causal item whose diagonal is shifted by the prefix. With ``cu_seqlens`` every
+    sequence of the packed buffer has its own prefix (clipped to its length)."""
+    bounds = [(0, seq_len)] if cu_seqlens is None else list(zip([int(x) for x in cu_seqlens][:-1],
+                                                                 [int(x) for x in cu_seqlens][1:]))
+    key = ("prefix_lm", tuple(bounds), int(prefix_length), str(device))
+    if key not in _plan_cache:
+        rows, cols = [], []
+        for a, b in bounds:
+            n = b - a
+            p = max(0, min(int(prefix_length), n))
+            if p > 0:
+                rows.append(A.Row(0, a, p, (A.Seg(0, a, p, False, 0),), 0, a, False))
+                cols.append(A.Col(0, a, p, (A.Seg(0, a, n, False, 0),), 0, a))          # every token sees the prefix
+            if n > p:
+                rows.append(A.Row(0, a + p, n - p, (A.Seg(0, a, n, True, p),), 0, a + p, False))
+                cols.append(A.Col(0, a + p, n - p, (A.Seg(0, a + p, n - p, True, 0),), 0, a + p))
+        _plan_cache[key] = (A.FwdPlan(rows, device), A.BwdPlan(cols, device))
+    return _plan_cache[key]
+
+
+def prefix_lm_attention(q, k, v, prefix_length: int, softmax_scale: Optional[float] = None, cu_seqlens=None):
+    """Attention under the prefix-LM mask, with autograd. ``[batch, tokens, heads, head_dim]`` (or
+    packed ``[tokens, heads, head_dim]``); same dtype / head-dim rules as :func:`attention`."""
+    squeeze = q.dim() == 3
+    if squeeze:
+        q, k, v = q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)
+    D = q.shape[-1]
+    fplan, bplan = prefix_lm_plans(q.shape[1], prefix_length, q.device, cu_seqlens)
+    if q.is_cuda and D < A.KERNEL_HEAD_DIM:
+        pad = A.KERNEL_HEAD_DIM - D
+        scale = softmax_scale if softmax_scale is not None else D ** -0.5
+        qp, kp, vp = (torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v))
+        o = _PlannedAttention.apply(qp, kp, vp, fplan, bplan, scale)[..., :D]
+    else:
+        o = _PlannedAttention.apply(q.contiguous(), k.contiguous(), v.contiguous(), fplan, bplan, softmax_scale)
+    return o.squeeze(0) if squeeze else o
+
+
 def varlen_attention(q, k, v, cu_seqlens, causal: bool = True, softmax_scale: Optional[float] = None,
                      window_size=(-1, -1)):
     """Attention over a packed batch ``[total_tokens, heads, head_dim]`` (or with a leading batch
