@@ -300,3 +300,44 @@ def test_mask_benchmark_driver_checks_every_mask():
     for r in recs:
         assert r["max_err"] < 2e-5 and 0 < r["density"] < 0.6 and r["fwd_ms"] > 0 and r["fwd_bwd_tflops"] > 0
     assert recs[1]["density"] < recs[0]["density"] < recs[2]["density"]      # window < causal < prefix-LM
+
+
+@pytest.mark.parametrize("Sq,Skv,window,causal", [(300, 1000, (400, 0), True), (256, 700, (100, 30), False),
+                                                  (64, 64 + 513, (1000, 0), True), (500, 520, (10, -1), False),
+                                                  (1, 900, (300, 0), True)])
+def test_window_with_the_queries_at_the_end_of_a_longer_key_sequence(Sq, Skv, window, causal):
+    """A chunk of queries behind context keys (bottom-right aligned band): coverage of the plan,
+    outputs and gradients (those of the context keys included) against dense masked attention."""
+    off = Skv - Sq
+    left, right = W._bounds(Skv, window, causal)
+    r = torch.arange(Sq)[:, None] + off
+    c = torch.arange(Skv)[None, :]
+    band = (c >= r - left) & (c <= r + right)
+    rows, cols = W.window_rows_cols_suffix(Sq, Skv, left, right)
+    for items, is_fwd in ((rows, True), (cols, False)):
+        cover = torch.zeros(Sq, Skv, dtype=torch.int32)
+        for it in items:
+            for seg in it.segs:
+                q_slot, q_start, q_len = (it.q_src, it.q_start, it.q_len) if is_fwd else (seg.src, seg.start, seg.length)
+                k_slot, k_start, k_len = (seg.src, seg.start, seg.length) if is_fwd else (it.kv_src, it.kv_start, it.kv_len)
+                rr, cc = torch.arange(q_len)[:, None], torch.arange(k_len)[None, :]
+                vis = (cc <= rr + seg.diag) if seg.causal else torch.ones(q_len, k_len, dtype=torch.bool)
+                qi = (q_start + rr if q_slot == 0 else Sq - 1 - (q_start + rr)).expand_as(vis)[vis]
+                ki = (k_start + cc if k_slot == 0 else Skv - 1 - (k_start + cc)).expand_as(vis)[vis]
+                cover.index_put_((qi, ki), torch.ones_like(qi, dtype=torch.int32), accumulate=True)
+        assert torch.equal(cover, band.int()), ("rows" if is_fwd else "cols")
+    torch.manual_seed(Sq)
+    H, Hk, D = 4, 2, 16
+    q = torch.randn(1, Sq, H, D).requires_grad_()
+    k = torch.randn(1, Skv, Hk, D).requires_grad_()
+    v = torch.randn(1, Skv, Hk, D).requires_grad_()
+    g = torch.randn(1, Sq, H, D)
+    sc = torch.einsum("bqhd,bkhd->bhqk", q, k.repeat_interleave(2, 2)) / math.sqrt(D)
+    sc = sc.masked_fill(~band, float("-inf"))
+    o_ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc, -1), v.repeat_interleave(2, 2))
+    ref = torch.autograd.grad(o_ref, (q, k, v), g)
+    o = W.sliding_window_attention(q, k, v, window, causal)
+    assert (o - o_ref).abs().max() < 2e-5
+    got = torch.autograd.grad(o, (q, k, v), g)
+    for a, b in zip(got, ref):
+        assert (a - b).abs().max() < 5e-5 * max(1.0, b.abs().max().item())

@@ -15,7 +15,7 @@ The fork's two additions are kept: ``out=`` lets the caller name the output buff
 (``out`` may then be any tensor of the right shape, as in the reference, which passes Q).
 Code written against those calls runs on the sm_100a kernels (CUDA tensors, bf16, head dim 128) or
 on the fp32 restatement (CPU tensors) by importing them from here. Sliding windows
-(``window_size = (left, right)``) run on the same kernels for ``Sq == Skv`` (``ops/window.py``: the
+(``window_size = (left, right)``) run on the same kernels for ``Sq <= Skv`` (``ops/window.py``: the
 band is split into a part in the usual token order and a part in reversed order, each of which
 needs a one-sided mask only). Dropout and ALiBi are not supported (the reference never uses them:
 ``dropout_p = 0``, ``alibi_slopes = None`` at every call site, and ``window_size = (-1, -1)``).

@@ -99,6 +99,43 @@ def window_rows_cols(S: int, left: int, right: int, base: int = 0, total: Option
     return rows, cols
 
 
+def window_rows_cols_suffix(Sq: int, Skv: int, left: int, right: int) -> tuple[list, list]:
+    """The two-part plan when the ``Sq`` queries are the last tokens of a sequence of ``Skv`` keys
+    (a chunk behind cached or received context; the mask is aligned to the bottom-right corner as in
+    flash-attention): query ``r`` stands at position ``p = r + Skv - Sq`` and sees ``p - left <= c
+    <= p + right``. Slot 0: usual order; slot 1: the query buffer and the key buffer each
+    reversed. Of the keys in front of the first query only the last ``left`` can be seen."""
+    off = Skv - Sq
+    assert off >= 0, "more queries than keys"
+    rows, cols = [], []
+    for r0, r1 in _partition(Sq, left):
+        n, p0, p1 = r1 - r0, r0 + off, r1 + off
+        a_len = min(Skv, p1 + right) - p0
+        rows.append(A.Row(0, r0, n, (A.Seg(0, p0, a_len, right < Skv, right),), 0, r0, False))
+        q0 = max(0, r0 - right)
+        cols.append(A.Col(0, p0, n, (A.Seg(0, q0, r1 - q0, right < Skv, q0 + right - r0),), 0, p0))
+        b_len = min(left, p0)
+        if b_len > 0:
+            rows.append(A.Row(1, Sq - r1, n, (A.Seg(1, Skv - p0, b_len, left < Skv, left - n),), 1, Sq - r1, False))
+        c0 = Sq - r1                     # key block [p0, p1) starts here in the reversed key buffer, too
+        q0 = max(0, c0 - left)
+        if c0 - q0 > 0:
+            cols.append(A.Col(1, c0, n, (A.Seg(1, q0, c0 - q0, left < Skv, q0 + left - c0),), 1, c0))
+    lo = max(0, off - left)              # context keys [lo, off): reversed they start at Sq, behind every query
+    if off - lo > 0 and Sq > 0:
+        q0 = max(0, Sq - left)
+        cols.append(A.Col(1, Sq, off - lo, (A.Seg(1, q0, Sq - q0, left < Skv, q0 + left - Sq),), 1, Sq))
+    return rows, cols
+
+
+@functools.lru_cache(maxsize=32)
+def _plans_suffix(Sq: int, Skv: int, window_size: tuple, causal: bool, device_str: str):
+    left, right = _bounds(Skv, window_size, causal)
+    rows, cols = window_rows_cols_suffix(Sq, Skv, left, right)
+    dev = torch.device(device_str)
+    return A.FwdPlan(rows, dev), A.BwdPlan(cols, dev)
+
+
 @functools.lru_cache(maxsize=32)
 def _plans(bounds: tuple, total: int, window_size: tuple, causal: bool, device_str: str, sink: int = 0):
     """Plans of a buffer of ``total`` tokens holding the sequences ``bounds`` = ((start, end), ...)."""
@@ -121,21 +158,29 @@ def _seq_bounds(cu_seqlens, S: int) -> tuple:
     return tuple(zip(cu[:-1], cu[1:]))
 
 
+def _pick_plans(Sq: int, Skv: int, window_size, causal, device, cu_seqlens, sink_tokens):
+    window = tuple(int(x) for x in window_size)
+    if Skv != Sq:
+        assert Skv > Sq and cu_seqlens is None and not sink_tokens, \
+            "with more keys than queries the queries are the end of one sequence (no packing, no sinks)"
+        return _plans_suffix(Sq, Skv, window, bool(causal), str(device))
+    return _plans(_seq_bounds(cu_seqlens, Sq), Sq, window, bool(causal), str(device), int(sink_tokens))
+
+
 def _flip(t: torch.Tensor, dim: int = 1) -> torch.Tensor:
     return t.flip(dim).contiguous()
 
 
 def window_forward(q, k, v, window_size, causal: bool = False, softmax_scale: Optional[float] = None,
                    out: Optional[torch.Tensor] = None, cu_seqlens=None, sink_tokens: int = 0):
-    """``q`` ``[B, S, H, D]``, ``k`` / ``v`` ``[B, S, Hkv, D]`` -> ``(o [B, S, H, D], lse [B, H, S] fp32)``.
+    """``q`` ``[B, S, H, D]``, ``k`` / ``v`` ``[B, Skv, Hkv, D]`` -> ``(o [B, S, H, D], lse [B, H, S] fp32)``.
+    ``Skv > S``: the queries are the last ``S`` positions of the key sequence.
     With ``cu_seqlens`` the token axis is a packed batch: sequence i spans ``cu_seqlens[i] :
     cu_seqlens[i + 1]``, attends only itself, and the window counts positions inside it.
     ``sink_tokens``: the first keys of every sequence that stay visible beyond the window."""
     B, S, H, D = q.shape
-    assert k.shape[1] == S, "sliding windows need as many keys as queries"
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    fplan, _ = _plans(_seq_bounds(cu_seqlens, S), S, tuple(int(x) for x in window_size), bool(causal), str(q.device),
-                      int(sink_tokens))
+    fplan, _ = _pick_plans(S, k.shape[1], window_size, causal, q.device, cu_seqlens, sink_tokens)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     qr, kr, vr = _flip(q), _flip(k), _flip(v)
     o_a, o_b = torch.zeros_like(q), torch.zeros_like(q)
@@ -158,8 +203,7 @@ def window_backward(d_o, q, k, v, o, lse, window_size, causal: bool = False,
     ``o`` is not read."""
     B, S, H, D = q.shape
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    _, bplan = _plans(_seq_bounds(cu_seqlens, S), S, tuple(int(x) for x in window_size), bool(causal), str(q.device),
-                      int(sink_tokens))
+    _, bplan = _pick_plans(S, k.shape[1], window_size, causal, q.device, cu_seqlens, sink_tokens)
     q, k, v, d_o = q.contiguous(), k.contiguous(), v.contiguous(), d_o.contiguous()
     if softmax_d is None:
         softmax_d = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
