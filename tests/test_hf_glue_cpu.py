@@ -75,15 +75,17 @@ def test_hf_llama_context_parallel_world2(seq_algo):
         assert ret[r][0] < 1e-4 and ret[r][1] < 1e-4, (r, ret[r])
 
 
-def test_hf_mistral_sliding_window_head_parallel_world2():
-    """A Mistral whose layers use a sliding window: the registered head-parallel attention applies
-    the token-exact window (logits and weight gradients match the unsharded eager model), and a
-    strategy that cannot apply it refuses instead of attending too far back."""
-    ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(2, 29100 + os.getpid() % 90, "ulysses_attn", ret, "mistral"), nprocs=2, join=True)
-    for r in range(2):
-        assert isinstance(ret[r], tuple), ret[r]
-        assert ret[r][0] < 1e-4 and ret[r][1] < 1e-4, (r, ret[r])
+def test_hf_mistral_sliding_window_world2():
+    """A Mistral whose layers use a sliding window: the registered head-parallel and halo-exchange
+    attention functions apply the token-exact window (logits and weight gradients match the
+    unsharded eager model), and a strategy that cannot apply it refuses instead of attending too
+    far back."""
+    for i, seq_algo in enumerate(("ulysses_attn", "halo_attn")):
+        ret = mp.Manager().dict()
+        mp.spawn(_worker, args=(2, 29100 + (os.getpid() + 7 * i) % 90, seq_algo, ret, "mistral"), nprocs=2, join=True)
+        for r in range(2):
+            assert isinstance(ret[r], tuple), (seq_algo, ret[r])
+            assert ret[r][0] < 1e-4 and ret[r][1] < 1e-4, (seq_algo, r, ret[r])
     sys.path.insert(0, ROOT)
     from ultraattn_b200.models.glue import make_attention_interface
     fn = make_attention_interface("zigzag_ring_attn")

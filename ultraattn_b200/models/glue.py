@@ -16,7 +16,7 @@ from ..parallel import ring as R
 
 _KIND = {"zigzag_ring_attn": "zigzag", "zigzag": "zigzag", "ring_attn": "ring", "ring": "ring",
          "stripe_attn": "stripe", "stripe": "stripe", "ulysses_attn": "ulysses", "ulysses": "ulysses",
-         "dist_flash_attn": "lightseq", "lightseq": "lightseq", "data_parallel": None, "ultra_attn": "ring", "ultraattn": "ring"}
+         "dist_flash_attn": "lightseq", "lightseq": "lightseq", "halo_attn": "halo", "halo": "halo", "data_parallel": None, "ultra_attn": "ring", "ultraattn": "ring"}
 
 
 def shard_by_ownership(x: torch.Tensor, cmap, rank: int, dim: int = 1) -> torch.Tensor:
@@ -92,9 +92,16 @@ def make_attention_interface(seq_algo: str, group=None, runtime=None):
                 path="fused" if q.is_cuda else "nccl", dtype=q.dtype)
         return lightseq_runtimes[key](q, k, v, softmax_scale)
 
+    def halo_fn(q, k, v, softmax_scale=None, causal=True, group=None, window_size=None):
+        """Contiguous shards, the window's keys fetched from the preceding ranks (parallel/halo.py)."""
+        from ..parallel.halo import halo_window_attn_func
+        if window_size is None:
+            raise NotImplementedError("seq_algo='halo' is the strategy for layers with a sliding window; this layer has none")
+        return halo_window_attn_func(q, k, v, window_size, softmax_scale, causal, group)
+
     fn = {"ring": R.ring_flash_attn_func, "zigzag": R.zigzag_ring_flash_attn_func,
           "stripe": R.stripe_flash_attn_func, "ulysses": R.deepspeed_ulysses_attn_func,
-          "lightseq": lightseq_fn}[kind]
+          "lightseq": lightseq_fn, "halo": halo_fn}[kind]
 
     def attention_forward(module, query, key, value, attention_mask=None, dropout: float = 0.0,
                           scaling: Optional[float] = None, **kwargs):
@@ -107,12 +114,13 @@ def make_attention_interface(seq_algo: str, group=None, runtime=None):
         window = kwargs.get("sliding_window")
         if window is not None:
             # transformers hands a layer's sliding window (Mistral and others) to the attention
-            # function; only the head-parallel strategy holds whole sequences and can apply a
-            # token-exact band. Anything else must refuse rather than attend too far back.
-            if runtime is not None or kind != "ulysses":
+            # function. The head-parallel strategy holds whole sequences and the halo strategy
+            # fetches the window's keys, so both apply a token-exact band. Anything else must
+            # refuse rather than attend too far back.
+            if runtime is not None or kind not in ("ulysses", "halo"):
                 raise NotImplementedError(
-                    f"sliding_window={window} needs seq_algo='ulysses' (token-exact windows are not part of the "
-                    f"{seq_algo!r} strategy; a block-level window is a pattern of the context-parallel runtime)")
+                    f"sliding_window={window} needs seq_algo='halo' or 'ulysses' (token-exact windows are not part of "
+                    f"the {seq_algo!r} strategy; a block-level window is a pattern of the context-parallel runtime)")
             out = fn(q, k, v, softmax_scale=scaling, causal=True, group=group, window_size=(int(window) - 1, 0))
             return out, None
         if runtime is not None:

@@ -517,7 +517,7 @@ def get_half_lse(lse: torch.Tensor, cu_seqlens, *, front: bool) -> torch.Tensor:
 # -------------------------------------------------------------------------------------------------
 def shard_sequence(x: torch.Tensor, rank: int, world: int, kind: str, dim: int = 1) -> torch.Tensor:
     """This rank's shard of a full-sequence tensor under the layout each strategy expects."""
-    if kind == "ring" or kind == "ulysses":
+    if kind in ("ring", "ulysses", "halo"):
         return x.chunk(world, dim=dim)[rank].contiguous()
     if kind == "zigzag":
         ch = x.chunk(2 * world, dim=dim)
