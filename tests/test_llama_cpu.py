@@ -167,3 +167,31 @@ def test_mistral_style_model_with_sliding_window_and_grouped_query_heads():
     import pytest
     with pytest.raises(NotImplementedError, match="sliding window"):
         LlamaModel(cfg, runtime=object())
+
+
+def test_mistral_style_trainer_with_halo_exchange_follows_the_single_rank_losses():
+    """Sliding-window model (grouped-query heads, window of 300 tokens): four ranks with contiguous
+    shards of 256 tokens fetch the window's keys from up to two preceding ranks and walk the same
+    loss curve as one rank with the whole sequence."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    args = ["--device", "cpu", "--path", "nccl", "--seq", "1024", "--layers", "2", "--hidden", "128", "--heads", "4",
+            "--kv-heads", "2", "--head-dim", "32", "--ffn", "256", "--vocab", "512", "--steps", "2", "--warmup", "1",
+            "--sliding-window", "300"]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+
+    def run(cmd):
+        r = subprocess.run(cmd, capture_output=True, text=True, cwd=root, env=env, timeout=900)
+        assert r.returncode == 0, r.stderr[-2000:]
+        return json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1])
+
+    one = run([sys.executable, "-m", "ultraattn_b200.drivers.train_llama"] + args)
+    four = run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr",
+                "127.0.0.1", "--master-port", str(29960 + os.getpid() % 30), "-m",
+                "ultraattn_b200.drivers.train_llama"] + args + ["--seq-algo", "halo"])
+    assert four["n_gpus"] == 4 and four["path"] == "halo" and one["losses"][0] > one["losses"][-1]
+    for a, b in zip(one["losses"], four["losses"]):
+        assert abs(a - b) < 2e-5 * abs(a), (one["losses"], four["losses"])

@@ -74,9 +74,10 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--path", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--seq-algo", default="cp", choices=["cp", "ulysses"],
+    ap.add_argument("--seq-algo", default="cp", choices=["cp", "ulysses", "halo"],
                     help="cp: context-parallel attention; ulysses: head-parallel attention with the all-to-alls "
-                         "fused into the projection GEMMs")
+                         "fused into the projection GEMMs; halo: contiguous shards, --sliding-window keys fetched "
+                         "from the preceding ranks")
     ap.add_argument("--breakdown", action="store_true",
                     help="after the timed steps, run one more step with CUDA events around the attention calls "
                          "and the GEMMs and report the attention / GEMM / other split")
@@ -107,7 +108,7 @@ def main() -> None:
         torch.cuda.set_device(dev)
     else:
         assert a.path == "nccl" or world == 1, "--device cpu runs the plan executor (--path nccl)"
-        assert a.seq_algo == "cp" and not a.breakdown, "--device cpu: context-parallel path, no breakdown"
+        assert a.seq_algo in ("cp", "halo") and not a.breakdown, "--device cpu: context-parallel or halo path, no breakdown"
     group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -119,10 +120,11 @@ def main() -> None:
         group = dist.group.WORLD
     cfg = LlamaConfig(n_layers=a.layers, hidden=a.hidden, n_heads=a.heads, head_dim=a.head_dim, ffn=a.ffn,
                       vocab=a.vocab, n_kv_heads=a.kv_heads, sliding_window=a.sliding_window, sink_tokens=a.sink_tokens)
-    assert a.sliding_window is None or world == 1, "--sliding-window runs on one rank"
+    assert a.sliding_window is None or world == 1 or a.seq_algo == "halo", \
+        "--sliding-window runs on one rank or with --seq-algo halo"
     pattern = P.global_local(a.blocks, 1, 2)
     runtime = None
-    if world > 1 and a.seq_algo == "ulysses":
+    if world > 1 and a.seq_algo in ("ulysses", "halo"):
         s_loc = a.seq // world
         pos = torch.arange(rank * s_loc, (rank + 1) * s_loc)
     elif world > 1:
@@ -186,7 +188,7 @@ def main() -> None:
         print(json.dumps({"metric": "e2e_tokens_per_s", "value": a.seq / (ms.item() / 1e3), "ms_per_step": ms.item(),
                           "n_gpus": world, "seq_len": a.seq, "layers": a.layers, "params": n_params, "loss": loss,
                           "losses": losses,
-                          "path": (a.path if a.seq_algo == "cp" else "ulysses-fused") if world > 1 else "local",
+                          "path": ((a.path if a.seq_algo == "cp" else {"ulysses": "ulysses-fused", "halo": "halo"}[a.seq_algo]) if world > 1 else "local"),
                           "dtype": "bf16" if on_gpu else "fp32", "device": a.device,
                           "max_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30 if on_gpu else None,
                           **({"split_ms_max_over_ranks": split} if split else {})}), flush=True)

@@ -292,9 +292,12 @@ class LlamaModel:
         contiguous token range ``[rank * S/world, (rank + 1) * S/world)``, and the rows of every
         ``wqkv`` are stored in destination-rank order (``permute_qkv_weight``)."""
         self.cfg = cfg
-        if cfg.sliding_window is not None and (runtime is not None or (seq_algo == "ulysses" and group is not None)):
-            raise NotImplementedError("a token-exact sliding window runs on whole sequences (one device); in the "
-                                      "context-parallel runtimes express it as a block pattern")
+        if cfg.sliding_window is not None and (runtime is not None or (seq_algo != "halo" and group is not None)):
+            raise NotImplementedError("a token-exact sliding window runs on one device or with seq_algo='halo' "
+                                      "(contiguous shards); in the planner-driven runtimes express it as a block pattern")
+        if seq_algo == "halo":
+            assert cfg.sliding_window is not None and not cfg.sink_tokens, \
+                "seq_algo='halo' is the strategy of a sliding window (without sink tokens)"
         self.seq_algo = seq_algo
         self.ulysses = None
         self.offload_checkpoints = offload_checkpoints
@@ -373,7 +376,7 @@ class LlamaModel:
             assert seq_len is not None, "seq_algo='ulysses' needs seq_len"
             self.ulysses = FusedUlyssesAttention(group, self.device, seq_len, cfg.hidden, cfg.n_heads, cfg.kv_heads,
                                                  cfg.head_dim, pattern=pattern)
-        elif seq_algo not in ("cp", "ulysses"):
+        elif seq_algo not in ("cp", "ulysses", "halo"):
             raise ValueError(f"unknown seq_algo {seq_algo!r}")
 
     # ------------------------------- segments of a layer ---------------------------------------
@@ -422,7 +425,12 @@ class LlamaModel:
 
     def _attn_fwd(self, q, k, v):
         if self._window() is not None:
-            # token-exact causal band (ops/window.py); whole sequences only
+            if self.world > 1:              # contiguous shards: the window's keys come from the preceding ranks
+                from ..parallel.halo import halo_window_attn_forward
+                o, lse, _, _ = halo_window_attn_forward(self.group, q.contiguous(), k.contiguous(), v.contiguous(),
+                                                        self._window()[0])
+                return o, lse
+            # token-exact causal band (ops/window.py) on the whole sequence
             from ..ops.window import window_forward
             return window_forward(q, k, v, self._window(), True, sink_tokens=self.cfg.sink_tokens)
         if self.runtime is not None:
@@ -438,6 +446,11 @@ class LlamaModel:
 
     def _attn_bwd(self, d_o, q, k, v, o, lse):
         if self._window() is not None:
+            if self.world > 1:              # the halo is fetched again (recomputation, like q / k / v themselves)
+                from ..parallel.halo import halo_extend, halo_window_attn_backward
+                left = self._window()[0]
+                k_ext, v_ext = halo_extend(self.group, k.contiguous(), v.contiguous(), left)
+                return halo_window_attn_backward(self.group, d_o.contiguous(), q.contiguous(), k_ext, v_ext, o, lse, left)
             from ..ops.window import window_backward
             return window_backward(d_o, q, k, v, o, lse, self._window(), True, sink_tokens=self.cfg.sink_tokens)
         if self.runtime is not None:

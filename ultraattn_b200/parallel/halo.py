@@ -57,19 +57,24 @@ def _exchange(send_bufs: list, recv_shapes: list, like: torch.Tensor, group) -> 
     return out
 
 
-def halo_window_attn_forward(group, q, k, v, left: int, softmax_scale: Optional[float] = None):
-    """``q`` ``[B, S_loc, H, D]``, ``k`` / ``v`` ``[B, S_loc, Hkv, D]`` (this rank's contiguous shard).
-    Returns ``(o, lse, k_ext, v_ext)``: the output of the shard's queries and the key/value rows
-    ``[halo | shard]`` that the backward takes."""
+def halo_extend(group, k, v, left: int):
+    """``[halo | shard]`` key and value rows of this rank: the shard with the last ``left`` rows in
+    front of it, received from the ranks that hold them (every rank of the group calls this)."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
-    s_loc = q.shape[1]
+    s_loc = k.shape[1]
     recv, send = _halo_plan(rank, world, s_loc, left)
     kv = torch.stack([k, v])                                        # one message per peer and pass
     got = _exchange([(peer, kv[:, :, s_loc - n:]) for peer, n in send],
                     [(peer, (2, k.shape[0], n) + tuple(k.shape[2:])) for peer, n in recv], k, group)
-    k_ext = torch.cat([g[0] for g in got] + [k], dim=1)
-    v_ext = torch.cat([g[1] for g in got] + [v], dim=1)
+    return torch.cat([g[0] for g in got] + [k], dim=1), torch.cat([g[1] for g in got] + [v], dim=1)
+
+
+def halo_window_attn_forward(group, q, k, v, left: int, softmax_scale: Optional[float] = None):
+    """``q`` ``[B, S_loc, H, D]``, ``k`` / ``v`` ``[B, S_loc, Hkv, D]`` (this rank's contiguous shard).
+    Returns ``(o, lse, k_ext, v_ext)``: the output of the shard's queries and the key/value rows
+    ``[halo | shard]`` that the backward takes."""
+    k_ext, v_ext = halo_extend(group, k, v, left)
     o, lse = window_forward(q, k_ext, v_ext, (left, 0), True, softmax_scale)
     return o, lse, k_ext, v_ext
 
