@@ -44,7 +44,9 @@ def _one_baseline(rank, world, kind, causal):
         sh = lambda t: PL.shard_sequence(t, rank, world, "halo")
         kk2, vv2 = k[:, :, :2], v[:, :, :2]          # grouped-query heads
         ql, kl, vl = (sh(t).requires_grad_() for t in (q, kk2, vv2))
-        o = PL.halo_window_attn_func(ql, kl, vl, (left, 0))
+        # through the strategy's own name, and through the ring function's window_size argument
+        o = PL.halo_window_attn_func(ql, kl, vl, (left, 0)) if left != 64 else \
+            PL.ring_flash_attn_func(ql, kl, vl, causal=True, window_size=(left, 0))
         o.backward(sh(d_o))
         r, c = torch.arange(S)[:, None], torch.arange(S)[None, :]
         mask = (c >= r - left) & (c <= r)

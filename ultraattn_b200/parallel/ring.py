@@ -294,8 +294,15 @@ def _make_func(kind: str):
     def func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
              alibi_slopes=None, deterministic=False, return_attn_probs=False, group=None,
              PROC_INFO=None, opt=False, groups=None):
-        _check_unsupported(dropout_p, alibi_slopes, window_size)
         group = groups if groups is not None else group        # the reference's keyword is ``groups``
+        if kind == "ring" and tuple(int(x) for x in window_size) != (-1, -1) and not isinstance(group, dict):
+            # a causal sliding window over the ring's contiguous shards: only the window's keys
+            # travel (parallel/halo.py) instead of every shard going round
+            _check_unsupported(dropout_p, alibi_slopes, (-1, -1))
+            assert not return_attn_probs, "the windowed form returns the output only"
+            from .halo import halo_window_attn_func
+            return halo_window_attn_func(q, k, v, window_size, softmax_scale, causal, group)
+        _check_unsupported(dropout_p, alibi_slopes, window_size)
         o, lse = _RingFunc.apply(q, k, v, softmax_scale, causal, group, kind)
         return (o, lse, None) if return_attn_probs else o
     func.__name__ = _NAMES[kind] + "_func"
