@@ -7,7 +7,8 @@ The masks of the reference's mask benchmark (tests/flexattn_tests/flexattn.py:29
 torch FlexAttention on causal, sliding-window, prefix-LM and document masks as a candidate kernel
 backend): here each is a launch plan of the same attention kernels — causal and document masks as
 segment lists, prefix-LM as a fully visible prefix item plus a causal item with a shifted
-diagonal, the sliding window as the two-part plan of ``ops/window.py``. Its score modifications
+diagonal, the sliding window as the two-part plan of ``ops/window.py``, and ``streaming`` (window
+plus attention sinks, the token-exact form of the reference's block-level streaming pattern). Its score modifications
 (ALiBi, soft-capping) change the scores themselves and are not available on these kernels. Prints one JSON
 line per mask: density of the mask, max error against dense attention (sequence lengths up to
 ``--check-limit``), milliseconds and achieved TFLOP/s counted on the visible pairs only.
@@ -32,7 +33,7 @@ def _doc_bounds(seq: int, n_docs: int, seed: int = 0) -> list:
     return [0] + cuts + [seq]
 
 
-def build_masks(seq: int, window: int, prefix: int, n_docs: int) -> dict:
+def build_masks(seq: int, window: int, prefix: int, n_docs: int, sinks: int = 4) -> dict:
     """name -> (callable(q, k, v) -> o with autograd, dense boolean mask builder)."""
     r = lambda: torch.arange(seq)[:, None]
     c = lambda: torch.arange(seq)[None, :]
@@ -48,6 +49,8 @@ def build_masks(seq: int, window: int, prefix: int, n_docs: int) -> dict:
         "causal": (lambda q, k, v: api.varlen_attention(q, k, v, [0, seq], True), lambda: c() <= r()),
         "sliding_window": (lambda q, k, v: sliding_window_attention(q, k, v, (window - 1, 0), True),
                            lambda: (c() <= r()) & (c() > r() - window)),
+        "streaming": (lambda q, k, v: sliding_window_attention(q, k, v, (window - 1, 0), True, sink_tokens=sinks),
+                      lambda: (c() <= r()) & ((c() > r() - window) | (c() < sinks))),
         "prefix_lm": (lambda q, k, v: api.prefix_lm_attention(q, k, v, prefix), lambda: (c() <= r()) | (c() < prefix)),
         "document": (lambda q, k, v: api.varlen_attention(q, k, v, cu, True), doc_mask),
     }
@@ -126,7 +129,7 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--kv-heads", type=int, default=None)
     ap.add_argument("--head-dim", type=int, default=128)
-    ap.add_argument("--masks", default="causal,sliding_window,prefix_lm,document")
+    ap.add_argument("--masks", default="causal,sliding_window,streaming,prefix_lm,document")
     ap.add_argument("--window", type=int, default=1024)
     ap.add_argument("--prefix", type=int, default=1024)
     ap.add_argument("--docs", type=int, default=12)
