@@ -8,10 +8,11 @@ torch FlexAttention on causal, sliding-window, prefix-LM and document masks as a
 backend): here each is a launch plan of the same attention kernels — causal and document masks as
 segment lists, prefix-LM as a fully visible prefix item plus a causal item with a shifted
 diagonal, the sliding window as the two-part plan of ``ops/window.py``, and ``streaming`` (window
-plus attention sinks, the token-exact form of the reference's block-level streaming pattern). Its score modifications
-(ALiBi, soft-capping) change the scores themselves and are not available on these kernels. Prints one JSON
-line per mask: density of the mask, max error against dense attention (sequence lengths up to
-``--check-limit``), milliseconds and achieved TFLOP/s counted on the visible pairs only.
+plus attention sinks, the token-exact form of the reference's block-level streaming pattern). Its
+score modifications (ALiBi, soft-capping) change the scores themselves and are not available on
+these kernels. Prints one JSON line per mask: density of the mask, max error against dense
+attention (sequence lengths up to ``--check-limit``), milliseconds and achieved TFLOP/s counted on
+the visible pairs only.
 """
 from __future__ import annotations
 
