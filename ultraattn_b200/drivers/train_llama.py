@@ -188,7 +188,8 @@ def main() -> None:
         print(json.dumps({"metric": "e2e_tokens_per_s", "value": a.seq / (ms.item() / 1e3), "ms_per_step": ms.item(),
                           "n_gpus": world, "seq_len": a.seq, "layers": a.layers, "params": n_params, "loss": loss,
                           "losses": losses,
-                          "path": ((a.path if a.seq_algo == "cp" else {"ulysses": "ulysses-fused", "halo": "halo"}[a.seq_algo]) if world > 1 else "local"),
+                          "path": "local" if world == 1 else
+                                  {"cp": a.path, "ulysses": "ulysses-fused", "halo": "halo"}[a.seq_algo],
                           "dtype": "bf16" if on_gpu else "fp32", "device": a.device,
                           "max_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30 if on_gpu else None,
                           **({"split_ms_max_over_ranks": split} if split else {})}), flush=True)
