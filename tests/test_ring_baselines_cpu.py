@@ -39,6 +39,20 @@ def _one_baseline(rank, world, kind, causal):
         o_ref, _, dq, dk, dv = P.dense_attention_with_grads(q, k, v, d_o, pat)
         return max((o - sh(o_ref)).abs().max().item(), (ql.grad - sh(dq)).abs().max().item(),
                    (kl.grad - sh(dk)).abs().max().item(), (vl.grad - sh(dv)).abs().max().item())
+    if kind.startswith("halo2:"):                   # two-sided window: halos from both neighbours (or farther)
+        left, right = (int(x) for x in kind[6:].split(","))
+        sh = lambda t: PL.shard_sequence(t, rank, world, "halo")
+        ql, kl, vl = (sh(t).requires_grad_() for t in (q, k, v))
+        o = PL.halo_window_attn_func(ql, kl, vl, (left, right), causal=False)
+        o.backward(sh(d_o))
+        r, c = torch.arange(S)[:, None], torch.arange(S)[None, :]
+        mask = (c >= r - left) & (c <= r + right)
+        qq, kk, vv = (t.clone().requires_grad_() for t in (q, k, v))
+        sc = torch.einsum("bqhd,bkhd->bhqk", qq, kk) / D ** 0.5
+        o_ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc.masked_fill(~mask, float("-inf")), -1), vv)
+        o_ref.backward(d_o)
+        return max((o - sh(o_ref.detach())).abs().max().item(), (ql.grad - sh(qq.grad)).abs().max().item(),
+                   (kl.grad - sh(kk.grad)).abs().max().item(), (vl.grad - sh(vv.grad)).abs().max().item())
     if kind.startswith("halo:"):                    # causal sliding window by halo exchange; the window may span ranks
         left = int(kind[5:])
         sh = lambda t: PL.shard_sequence(t, rank, world, "halo")
@@ -94,7 +108,8 @@ def test_baselines_world4():
     patterns on four ranks, one process group."""
     cases = [("ring", True), ("ring", False), ("zigzag", True), ("stripe", True), ("ulysses", True),
              ("ulysses-window", True), ("ulysses-window", False), ("halo:20", True), ("halo:64", True),
-             ("halo:150", True), ("halo:1000", True), ("bsa:strided", False), ("bsa:global_local", False), ("bsa:star", False)]
+             ("halo:150", True), ("halo:1000", True), ("halo2:30,10", False), ("halo2:100,70", False),
+             ("halo2:0,64", False), ("bsa:strided", False), ("bsa:global_local", False), ("bsa:star", False)]
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(4, 29900 + os.getpid() % 90, cases, ret), nprocs=4, join=True)
     _check(ret, 4)

@@ -341,3 +341,49 @@ def test_window_with_the_queries_at_the_end_of_a_longer_key_sequence(Sq, Skv, wi
     got = torch.autograd.grad(o, (q, k, v), g)
     for a, b in zip(got, ref):
         assert (a - b).abs().max() < 5e-5 * max(1.0, b.abs().max().item())
+
+
+@pytest.mark.parametrize("Sq,Skv,off,window", [(300, 900, 250, (200, 120)), (256, 600, 0, (50, 400)), (100, 700, 300, (1000, 1000)),
+                                               (513, 700, 100, (64, 33)), (64, 64, 0, (10, 10))])
+def test_window_with_the_queries_in_the_middle_of_the_keys(Sq, Skv, off, window):
+    """Queries at positions ``off ... off + Sq`` of the key sequence (a shard between two halos):
+    plan coverage, outputs and all gradients through ``window_forward`` / ``window_backward``."""
+    left, right = W._bounds(Skv, window, False)
+    r = torch.arange(Sq)[:, None] + off
+    c = torch.arange(Skv)[None, :]
+    band = (c >= r - left) & (c <= r + right)
+    rows, cols = W.window_rows_cols_offset(Sq, Skv, left, right, off)
+    for items, is_fwd in ((rows, True), (cols, False)):
+        cover = torch.zeros(Sq, Skv, dtype=torch.int32)
+        for it in items:
+            for seg in it.segs:
+                q_slot, q_start, q_len = (it.q_src, it.q_start, it.q_len) if is_fwd else (seg.src, seg.start, seg.length)
+                k_slot, k_start, k_len = (seg.src, seg.start, seg.length) if is_fwd else (it.kv_src, it.kv_start, it.kv_len)
+                rr, cc = torch.arange(q_len)[:, None], torch.arange(k_len)[None, :]
+                vis = (cc <= rr + seg.diag) if seg.causal else torch.ones(q_len, k_len, dtype=torch.bool)
+                qi = (q_start + rr if q_slot == 0 else Sq - 1 - (q_start + rr)).expand_as(vis)[vis]
+                ki = (k_start + cc if k_slot == 0 else Skv - 1 - (k_start + cc)).expand_as(vis)[vis]
+                cover.index_put_((qi, ki), torch.ones_like(qi, dtype=torch.int32), accumulate=True)
+        assert torch.equal(cover, band.int()), ("rows" if is_fwd else "cols")
+    for slot in (0, 1):                     # one writer per gradient row and slot
+        covered = torch.zeros(Skv, dtype=torch.int32)
+        for col in cols:
+            if col.g_slot == slot:
+                covered[col.g_start:col.g_start + col.kv_len] += 1
+        assert covered.max() <= 1
+    torch.manual_seed(Sq + off)
+    H, Hk, D = 2, 1, 16
+    q = torch.randn(1, Sq, H, D).requires_grad_()
+    k = torch.randn(1, Skv, Hk, D).requires_grad_()
+    v = torch.randn(1, Skv, Hk, D).requires_grad_()
+    g = torch.randn(1, Sq, H, D)
+    sc = torch.einsum("bqhd,bkhd->bhqk", q, k.repeat_interleave(2, 2)) / math.sqrt(D)
+    sc = sc.masked_fill(~band, float("-inf"))
+    o_ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc, -1), v.repeat_interleave(2, 2))
+    ref = torch.autograd.grad(o_ref, (q, k, v), g)
+    with torch.no_grad():
+        o, lse = W.window_forward(q, k, v, window, False, q_offset=off)
+        got = W.window_backward(g, q, k, v, o, lse, window, False, q_offset=off)
+    assert (o - o_ref).abs().max() < 2e-5 and (lse - torch.logsumexp(sc, -1)).abs().max() < 2e-5
+    for a, b in zip(got, ref):
+        assert (a - b).abs().max() < 5e-5 * max(1.0, b.abs().max().item())

@@ -449,7 +449,7 @@ class LlamaModel:
             if self.world > 1:              # the halo is fetched again (recomputation, like q / k / v themselves)
                 from ..parallel.halo import halo_extend, halo_window_attn_backward
                 left = self._window()[0]
-                k_ext, v_ext = halo_extend(self.group, k.contiguous(), v.contiguous(), left)
+                k_ext, v_ext, _ = halo_extend(self.group, k.contiguous(), v.contiguous(), left)
                 return halo_window_attn_backward(self.group, d_o.contiguous(), q.contiguous(), k_ext, v_ext, o, lse, left)
             from ..ops.window import window_backward
             return window_backward(d_o, q, k, v, o, lse, self._window(), True, sink_tokens=self.cfg.sink_tokens)

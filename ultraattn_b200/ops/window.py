@@ -99,14 +99,17 @@ def window_rows_cols(S: int, left: int, right: int, base: int = 0, total: Option
     return rows, cols
 
 
-def window_rows_cols_suffix(Sq: int, Skv: int, left: int, right: int) -> tuple[list, list]:
-    """The two-part plan when the ``Sq`` queries are the last tokens of a sequence of ``Skv`` keys
-    (a chunk behind cached or received context; the mask is aligned to the bottom-right corner as in
-    flash-attention): query ``r`` stands at position ``p = r + Skv - Sq`` and sees ``p - left <= c
-    <= p + right``. Slot 0: usual order; slot 1: the query buffer and the key buffer each
-    reversed. Of the keys in front of the first query only the last ``left`` can be seen."""
-    off = Skv - Sq
-    assert off >= 0, "more queries than keys"
+def window_rows_cols_offset(Sq: int, Skv: int, left: int, right: int, off: Optional[int] = None) -> tuple[list, list]:
+    """The two-part plan when the ``Sq`` queries are a stretch of a longer sequence of ``Skv`` keys
+    (a chunk behind cached context, or a shard between the halos received from its neighbours):
+    query ``r`` stands at position ``p = r + off`` and sees ``p - left <= c <= p + right``. Default
+    ``off = Skv - Sq``: the queries are the last tokens (the bottom-right alignment of
+    flash-attention). Slot 0: usual order; slot 1: the query buffer and the key buffer each
+    reversed. Of the keys in front of the first query only the last ``left`` can be seen, of those
+    behind the last query only the first ``right``."""
+    off = Skv - Sq if off is None else off
+    tail = Skv - off - Sq                    # keys behind the last query
+    assert off >= 0 and tail >= 0, "the queries must lie inside the key sequence"
     rows, cols = [], []
     for r0, r1 in _partition(Sq, left):
         n, p0, p1 = r1 - r0, r0 + off, r1 + off
@@ -117,21 +120,32 @@ def window_rows_cols_suffix(Sq: int, Skv: int, left: int, right: int) -> tuple[l
         b_len = min(left, p0)
         if b_len > 0:
             rows.append(A.Row(1, Sq - r1, n, (A.Seg(1, Skv - p0, b_len, left < Skv, left - n),), 1, Sq - r1, False))
-        c0 = Sq - r1                     # key block [p0, p1) starts here in the reversed key buffer, too
+        c0 = Sq - r1                     # the block's start among the reversed queries; among the reversed keys it is c0 + tail
         q0 = max(0, c0 - left)
         if c0 - q0 > 0:
-            cols.append(A.Col(1, c0, n, (A.Seg(1, q0, c0 - q0, left < Skv, q0 + left - c0),), 1, c0))
-    lo = max(0, off - left)              # context keys [lo, off): reversed they start at Sq, behind every query
-    if off - lo > 0 and Sq > 0:
-        q0 = max(0, Sq - left)
-        cols.append(A.Col(1, Sq, off - lo, (A.Seg(1, q0, Sq - q0, left < Skv, q0 + left - Sq),), 1, Sq))
+            cols.append(A.Col(1, c0 + tail, n, (A.Seg(1, q0, c0 - q0, left < Skv, q0 + left - c0),), 1, c0 + tail))
+    if Sq > 0:
+        lo = max(0, off - left)          # keys in front, [lo, off): reversed they lie behind every query
+        if off - lo > 0:
+            q0 = max(0, Sq - left)
+            cols.append(A.Col(1, Sq + tail, off - lo, (A.Seg(1, q0, Sq - q0, left < Skv, q0 + left - Sq),), 1, Sq + tail))
+        hi = min(Skv, off + Sq + right)  # keys behind, [off + Sq, hi): seen by the last `right` queries
+        if hi - (off + Sq) > 0:
+            q0 = max(0, Sq - right)
+            cols.append(A.Col(0, off + Sq, hi - (off + Sq), (A.Seg(0, q0, Sq - q0, right < Skv, q0 + right - Sq),), 0,
+                              off + Sq))
     return rows, cols
 
 
+def window_rows_cols_suffix(Sq: int, Skv: int, left: int, right: int) -> tuple[list, list]:
+    """:func:`window_rows_cols_offset` with the queries at the end of the keys."""
+    return window_rows_cols_offset(Sq, Skv, left, right, Skv - Sq)
+
+
 @functools.lru_cache(maxsize=32)
-def _plans_suffix(Sq: int, Skv: int, window_size: tuple, causal: bool, device_str: str):
+def _plans_offset(Sq: int, Skv: int, off: int, window_size: tuple, causal: bool, device_str: str):
     left, right = _bounds(Skv, window_size, causal)
-    rows, cols = window_rows_cols_suffix(Sq, Skv, left, right)
+    rows, cols = window_rows_cols_offset(Sq, Skv, left, right, off)
     dev = torch.device(device_str)
     return A.FwdPlan(rows, dev), A.BwdPlan(cols, dev)
 
@@ -158,12 +172,12 @@ def _seq_bounds(cu_seqlens, S: int) -> tuple:
     return tuple(zip(cu[:-1], cu[1:]))
 
 
-def _pick_plans(Sq: int, Skv: int, window_size, causal, device, cu_seqlens, sink_tokens):
+def _pick_plans(Sq: int, Skv: int, window_size, causal, device, cu_seqlens, sink_tokens, q_offset=None):
     window = tuple(int(x) for x in window_size)
-    if Skv != Sq:
-        assert Skv > Sq and cu_seqlens is None and not sink_tokens, \
-            "with more keys than queries the queries are the end of one sequence (no packing, no sinks)"
-        return _plans_suffix(Sq, Skv, window, bool(causal), str(device))
+    if Skv != Sq or q_offset:
+        assert Skv >= Sq and cu_seqlens is None and not sink_tokens, \
+            "with more keys than queries the queries are a stretch of one sequence (no packing, no sinks)"
+        return _plans_offset(Sq, Skv, Skv - Sq if q_offset is None else int(q_offset), window, bool(causal), str(device))
     return _plans(_seq_bounds(cu_seqlens, Sq), Sq, window, bool(causal), str(device), int(sink_tokens))
 
 
@@ -172,15 +186,17 @@ def _flip(t: torch.Tensor, dim: int = 1) -> torch.Tensor:
 
 
 def window_forward(q, k, v, window_size, causal: bool = False, softmax_scale: Optional[float] = None,
-                   out: Optional[torch.Tensor] = None, cu_seqlens=None, sink_tokens: int = 0):
+                   out: Optional[torch.Tensor] = None, cu_seqlens=None, sink_tokens: int = 0,
+                   q_offset: Optional[int] = None):
     """``q`` ``[B, S, H, D]``, ``k`` / ``v`` ``[B, Skv, Hkv, D]`` -> ``(o [B, S, H, D], lse [B, H, S] fp32)``.
-    ``Skv > S``: the queries are the last ``S`` positions of the key sequence.
+    ``Skv > S``: the queries are the positions ``q_offset ... q_offset + S`` of the key sequence
+    (default: the last ``S``).
     With ``cu_seqlens`` the token axis is a packed batch: sequence i spans ``cu_seqlens[i] :
     cu_seqlens[i + 1]``, attends only itself, and the window counts positions inside it.
     ``sink_tokens``: the first keys of every sequence that stay visible beyond the window."""
     B, S, H, D = q.shape
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    fplan, _ = _pick_plans(S, k.shape[1], window_size, causal, q.device, cu_seqlens, sink_tokens)
+    fplan, _ = _pick_plans(S, k.shape[1], window_size, causal, q.device, cu_seqlens, sink_tokens, q_offset)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     qr, kr, vr = _flip(q), _flip(k), _flip(v)
     o_a, o_b = torch.zeros_like(q), torch.zeros_like(q)
@@ -197,13 +213,13 @@ def window_forward(q, k, v, window_size, causal: bool = False, softmax_scale: Op
 
 def window_backward(d_o, q, k, v, o, lse, window_size, causal: bool = False,
                     softmax_scale: Optional[float] = None, softmax_d: Optional[torch.Tensor] = None,
-                    cu_seqlens=None, sink_tokens: int = 0):
+                    cu_seqlens=None, sink_tokens: int = 0, q_offset: Optional[int] = None):
     """Gradients ``(dq, dk, dv)`` in the dtypes of ``q``, ``k``, ``v``. ``lse`` is the merged
     log-sum-exp the forward returned; with ``softmax_d`` (= rowsum(dO * O), ``[B, H, S]``) given,
     ``o`` is not read."""
     B, S, H, D = q.shape
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    _, bplan = _pick_plans(S, k.shape[1], window_size, causal, q.device, cu_seqlens, sink_tokens)
+    _, bplan = _pick_plans(S, k.shape[1], window_size, causal, q.device, cu_seqlens, sink_tokens, q_offset)
     q, k, v, d_o = q.contiguous(), k.contiguous(), v.contiguous(), d_o.contiguous()
     if softmax_d is None:
         softmax_d = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
