@@ -156,3 +156,36 @@ def test_launch_order_keeps_groups_together_heaviest_first():
         assert len(runs) == len(set(runs)) == 8                                  # each group is one run
     order = A._launch_order([(5, 0, 0), (9, 1, 0), (7, 1, 1), (6, 2, 0), (5, 0, 1)])
     assert order == [(9, 1, 0), (7, 1, 1), (6, 2, 0), (5, 0, 0), (5, 0, 1)]
+
+
+def test_public_flash_attention_functions_with_autograd():
+    """flash_attn_func and its packed / varlen forms: outputs and gradients against dense attention
+    (causal, grouped-query, more keys than queries, a sliding window)."""
+    from ultraattn_b200.ops.flash_compat import (flash_attn_func, flash_attn_kvpacked_func, flash_attn_qkvpacked_func,
+                                                 flash_attn_varlen_func)
+    torch.manual_seed(4)
+    Sq, Skv, H, Hk, D = 40, 72, 4, 2, 16
+    q = torch.randn(1, Sq, H, D, requires_grad=True)
+    k = torch.randn(1, Skv, Hk, D, requires_grad=True)
+    v = torch.randn(1, Skv, Hk, D, requires_grad=True)
+    d_o = torch.randn(1, Sq, H, D)
+    o_ref, lse_ref, dq_ref, dk_ref, dv_ref = _dense(q[0], k[0], v[0], d_o[0], True)
+    o, lse, _ = flash_attn_func(q, k, v, causal=True, return_attn_probs=True)
+    o.backward(d_o)
+    assert torch.allclose(o[0], o_ref, atol=1e-5) and torch.allclose(lse[0], lse_ref, atol=1e-5)
+    assert torch.allclose(q.grad[0], dq_ref, atol=1e-5) and torch.allclose(k.grad[0], dk_ref, atol=1e-5)
+    assert torch.allclose(v.grad[0], dv_ref, atol=1e-5)
+    o2 = flash_attn_kvpacked_func(q.detach(), torch.stack([k.detach(), v.detach()], dim=2), causal=True)
+    assert torch.allclose(o2, o.detach(), atol=1e-6)
+    qkv = torch.randn(1, 64, 3, 2, D)
+    o3 = flash_attn_qkvpacked_func(qkv, causal=True, window_size=(20, 0))
+    r, c = torch.arange(64)[:, None], torch.arange(64)[None, :]
+    s = torch.einsum("qhd,khd->hqk", qkv[0, :, 0], qkv[0, :, 1]) / math.sqrt(D)
+    s = s.masked_fill(~((c <= r) & (c >= r - 20)), float("-inf"))
+    assert torch.allclose(o3[0], torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), qkv[0, :, 2]), atol=1e-5)
+    cu = torch.tensor([0, 24, 64])
+    o4 = flash_attn_varlen_func(qkv[0, :, 0], qkv[0, :, 1], qkv[0, :, 2], cu, cu, 40, 40, causal=True)
+    for a, b in ((0, 24), (24, 64)):
+        s = torch.einsum("qhd,khd->hqk", qkv[0, a:b, 0], qkv[0, a:b, 1]) / math.sqrt(D)
+        s = s.masked_fill(~torch.ones(b - a, b - a, dtype=torch.bool).tril(), float("-inf"))
+        assert torch.allclose(o4[a:b], torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), qkv[0, a:b, 2]), atol=1e-5)

@@ -185,3 +185,62 @@ def _flash_attn_varlen_backward(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_
                   lse.unsqueeze(0).contiguous(), dq.unsqueeze(0), dk.unsqueeze(0), dv.unsqueeze(0), cols,
                   _scale(q, softmax_scale), None if softmax_d is None else softmax_d.unsqueeze(0))
     return dq, dk, dv, d.squeeze(0)
+
+
+# -------------------------------------------------------------------------------------------------
+# The public calling convention of flash-attention (flash_attn_func and its packed / varlen forms),
+# with autograd, for code that used the library directly (the reference's benchmark scripts and
+# LightSeq checks do: bench_ring_attn_old.py:2, easy_context/dist_flash_attn/lightseq_async_attn.py:547).
+# -------------------------------------------------------------------------------------------------
+class _FlashFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, softmax_scale, causal, window_size):
+        out = _flash_attn_forward(q, k, v, 0.0, softmax_scale, causal, window_size)
+        ctx.save_for_backward(q, k, v, out[0], out[5])
+        ctx.args = (softmax_scale, causal, tuple(window_size))
+        ctx.mark_non_differentiable(out[5])
+        return out[0], out[5]
+
+    @staticmethod
+    def backward(ctx, d_o, _d_lse):
+        q, k, v, o, lse = ctx.saved_tensors
+        scale, causal, window = ctx.args
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _flash_attn_backward(d_o.contiguous(), q, k, v, o, lse, dq, dk, dv, 0.0, scale, causal, window)
+        return dq, dk, dv, None, None, None
+
+
+def flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
+                    alibi_slopes=None, deterministic=False, return_attn_probs=False):
+    """``q`` ``[B, Sq, H, D]``, ``k`` / ``v`` ``[B, Skv, Hkv, D]`` -> ``out`` (or ``(out, lse, None)``
+    with ``return_attn_probs``); differentiable. Same dtype / head-dim rules as the private calls."""
+    _check(dropout_p, window_size, alibi_slopes, windows_ok=True)
+    o, lse = _FlashFunc.apply(q.contiguous(), k.contiguous(), v.contiguous(), softmax_scale, bool(causal),
+                              tuple(window_size))
+    return (o, lse, None) if return_attn_probs else o
+
+
+def flash_attn_qkvpacked_func(qkv, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
+                              alibi_slopes=None, deterministic=False, return_attn_probs=False):
+    """``qkv`` ``[B, S, 3, H, D]``."""
+    return flash_attn_func(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], dropout_p, softmax_scale, causal, window_size,
+                           alibi_slopes, deterministic, return_attn_probs)
+
+
+def flash_attn_kvpacked_func(q, kv, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
+                             alibi_slopes=None, deterministic=False, return_attn_probs=False):
+    """``q`` ``[B, Sq, H, D]``, ``kv`` ``[B, Skv, 2, Hkv, D]``."""
+    return flash_attn_func(q, kv[:, :, 0], kv[:, :, 1], dropout_p, softmax_scale, causal, window_size,
+                           alibi_slopes, deterministic, return_attn_probs)
+
+
+def flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q=None, max_seqlen_k=None,
+                           dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
+                           alibi_slopes=None, deterministic=False, return_attn_probs=False, block_table=None):
+    """Packed batch ``[tokens, heads, head_dim]``; every sequence has as many keys as queries."""
+    from ..api import varlen_attention
+    _check(dropout_p, window_size, alibi_slopes, windows_ok=True)
+    assert block_table is None, "paged key/value caches are not supported"
+    assert _bounds(cu_seqlens_q) == _bounds(cu_seqlens_k), "the differentiable varlen form needs equal query and key lengths"
+    assert not return_attn_probs, "use _flash_attn_varlen_forward for the log-sum-exp"
+    return varlen_attention(q, k, v, cu_seqlens_q, bool(causal), softmax_scale, window_size)
