@@ -387,3 +387,30 @@ def test_window_with_the_queries_in_the_middle_of_the_keys(Sq, Skv, off, window)
     assert (o - o_ref).abs().max() < 2e-5 and (lse - torch.logsumexp(sc, -1)).abs().max() < 2e-5
     for a, b in zip(got, ref):
         assert (a - b).abs().max() < 5e-5 * max(1.0, b.abs().max().item())
+
+
+def test_window_that_covers_every_sequence_takes_the_plain_path(monkeypatch):
+    """A window at least as long as every sequence is plain causal / full attention: no reversed
+    copies are made (here: making one would raise), results as usual."""
+    def no_flip(*a, **k):
+        raise AssertionError("a reversed copy was made")
+    monkeypatch.setattr(W, "_flip", no_flip)
+    torch.manual_seed(2)
+    cu = [0, 200, 500]
+    q = torch.randn(1, 500, 2, 16).requires_grad_()
+    k = torch.randn(1, 500, 2, 16).requires_grad_()
+    v = torch.randn(1, 500, 2, 16).requires_grad_()
+    g = torch.randn(1, 500, 2, 16)
+    o = W.sliding_window_attention(q, k, v, (4095, 0), True, cu_seqlens=cu, sink_tokens=4)
+    got = torch.autograd.grad(o, (q, k, v), g)
+    mask = torch.zeros(500, 500, dtype=torch.bool)
+    for a, b in zip(cu[:-1], cu[1:]):
+        mask[a:b, a:b] = torch.ones(b - a, b - a, dtype=torch.bool).tril()
+    sc = (torch.einsum("bqhd,bkhd->bhqk", q, k) / 4).masked_fill(~mask, float("-inf"))
+    o_ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc, -1), v)
+    ref = torch.autograd.grad(o_ref, (q, k, v), g)
+    assert (o - o_ref).abs().max() < 2e-5
+    for x, y in zip(got, ref):
+        assert (x - y).abs().max() < 5e-5
+    with pytest.raises(AssertionError, match="reversed copy"):       # a shorter window does need them
+        W.sliding_window_attention(q, k, v, (100, 0), True, cu_seqlens=cu)

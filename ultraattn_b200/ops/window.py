@@ -181,6 +181,27 @@ def _pick_plans(Sq: int, Skv: int, window_size, causal, device, cu_seqlens, sink
     return _plans(_seq_bounds(cu_seqlens, Sq), Sq, window, bool(causal), str(device), int(sink_tokens))
 
 
+def _whole_sequence_plans(Sq: int, Skv: int, window_size, causal, device, cu_seqlens, q_offset):
+    """When the window reaches over every sequence (a 4096-token window on 2048-token documents)
+    the band is plain causal or full attention: one work item per sequence in the usual order, no
+    reversed copies, no merge. Returns (forward plan, backward plan) or None."""
+    if Skv != Sq or q_offset:
+        return None
+    bounds = _seq_bounds(cu_seqlens, Sq)
+    kinds = set()
+    for a, b in bounds:
+        if b > a:
+            left, right = _bounds(b - a, window_size, causal)
+            if left < b - a - 1 or 0 < right < b - a - 1:
+                return None
+            kinds.add(right == 0)
+    if len(kinds) != 1:
+        return None
+    from ..api import varlen_plans
+    cu = [bounds[0][0]] + [b for _, b in bounds]
+    return varlen_plans(cu, kinds.pop(), device)
+
+
 def _flip(t: torch.Tensor, dim: int = 1) -> torch.Tensor:
     return t.flip(dim).contiguous()
 
@@ -196,8 +217,15 @@ def window_forward(q, k, v, window_size, causal: bool = False, softmax_scale: Op
     ``sink_tokens``: the first keys of every sequence that stay visible beyond the window."""
     B, S, H, D = q.shape
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    fplan, _ = _pick_plans(S, k.shape[1], window_size, causal, q.device, cu_seqlens, sink_tokens, q_offset)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    whole = _whole_sequence_plans(S, k.shape[1], window_size, causal, q.device, cu_seqlens, q_offset)
+    if whole is not None:
+        o = out if out is not None else torch.empty_like(q)
+        o.zero_()
+        lse = torch.full((B, H, S), float("-inf"), dtype=torch.float32, device=q.device)
+        A.attn_fwd([q], [k], [v], [(o, lse)], whole[0], scale)
+        return o, lse
+    fplan, _ = _pick_plans(S, k.shape[1], window_size, causal, q.device, cu_seqlens, sink_tokens, q_offset)
     qr, kr, vr = _flip(q), _flip(k), _flip(v)
     o_a, o_b = torch.zeros_like(q), torch.zeros_like(q)
     lse_a = torch.full((B, H, S), float("-inf"), dtype=torch.float32, device=q.device)
@@ -219,7 +247,6 @@ def window_backward(d_o, q, k, v, o, lse, window_size, causal: bool = False,
     ``o`` is not read."""
     B, S, H, D = q.shape
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    _, bplan = _pick_plans(S, k.shape[1], window_size, causal, q.device, cu_seqlens, sink_tokens, q_offset)
     q, k, v, d_o = q.contiguous(), k.contiguous(), v.contiguous(), d_o.contiguous()
     if softmax_d is None:
         softmax_d = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
@@ -228,6 +255,12 @@ def window_backward(d_o, q, k, v, o, lse, window_size, causal: bool = False,
     lse = lse.float().contiguous()
     softmax_d = softmax_d.float().contiguous()
     f32 = lambda t: torch.zeros(t.shape, dtype=torch.float32, device=t.device)
+    whole = _whole_sequence_plans(S, k.shape[1], window_size, causal, q.device, cu_seqlens, q_offset)
+    if whole is not None:
+        dq32, kv = f32(q), A.BwdKvOut(f32(k), f32(v))
+        A.attn_bwd([A.BwdQSide(q, d_o, lse, softmax_d, dq32)], [k], [v], [kv], whole[1], scale)
+        return dq32.to(q.dtype), kv.dk.to(k.dtype), kv.dv.to(v.dtype)
+    _, bplan = _pick_plans(S, k.shape[1], window_size, causal, q.device, cu_seqlens, sink_tokens, q_offset)
     dq_a, dq_b = f32(q), f32(q)
     kv_a, kv_b = A.BwdKvOut(f32(k), f32(v)), A.BwdKvOut(f32(k), f32(v))
     kv_outs = [kv_a, kv_b] + ([A.BwdKvOut(f32(k), f32(v))] if sink_tokens else [])     # slot 2: the sinks' share
